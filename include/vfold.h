@@ -1,0 +1,415 @@
+/*
+ * vfold.h — C ABI of the B200 constant-folding library (libvfold.so).
+ *
+ * The library is a drop-in for the data path behind the NPU compiler's
+ *   Const::ContentAttr::fold()  +  Const::Content::copyTo()
+ * (src/vpux_compiler/src/dialect/const/attributes/content.cpp:371-397,
+ *  src/vpux_compiler/src/dialect/const/utils/content.cpp:161-184)
+ * and for VPU::NCESparsity::getWeightsTable()
+ * (src/vpux_compiler/src/dialect/VPU/utils/nce_sparsity.cpp:171-231).
+ *
+ * Conventions
+ *  - Plain C: POD structs, raw pointers and sizes. No exceptions cross the ABI.
+ *  - Every function returns VF_OK (0) or a negative vf_status and, when `err`
+ *    is non-NULL, writes a NUL-terminated message into (err, errlen).
+ *    Each reference VPUX_THROW on this path maps to one status code; the
+ *    predicate is checked on the host before anything is launched.
+ *  - Input buffers are borrowed for the duration of the call; outputs are
+ *    written into caller-owned memory (host, pinned host, or device memory
+ *    of the context's device). The library owns only its streams and its
+ *    scratch pool.
+ *  - All entry points are thread-safe and re-entrant per context; calls on
+ *    one context are serialised on that context's stream.
+ *  - There is no CPU fallback: without a CUDA device vf_ctx_create fails.
+ */
+#ifndef VFOLD_H_
+#define VFOLD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VF_MAX_RANK 5
+#define VF_ABI_VERSION 1
+
+/* ------------------------------------------------------------------ */
+/* status codes                                                        */
+/* ------------------------------------------------------------------ */
+typedef enum vf_status {
+    VF_OK = 0,
+    VF_ERR_INVALID_ARG = -1,      /* NULL pointer, bad rank, bad enum value                            */
+    VF_ERR_UNSUPPORTED = -2,      /* reference throws "Unsupported ..." for this type/shape            */
+    VF_ERR_SHAPE = -3,            /* shape / size / params-count mismatch                              */
+    VF_ERR_NOT_QUANTIZED = -4,    /* Dequantize on a non-quantized type (dequantize.cpp:43-44)         */
+    VF_ERR_ZERO_POINTS = -5,      /* "Not all zero-points are equal" (sparsity.cpp:19-23,
+                                     quantization.cpp:197-198)                                         */
+    VF_ERR_SPLAT = -6,            /* BitPack on splat input (bit_pack.cpp:133)                         */
+    VF_ERR_ODD_COUNT = -7,        /* BitPack on odd element count (bit_pack.cpp:137)                   */
+    VF_ERR_POSITION = -8,         /* more than one LAST transformation (content.cpp:585-588)           */
+    VF_ERR_CHECKED_CAST = -9,     /* checked_cast range failure during element conversion
+                                     (checked_cast.hpp:106-117); reported after the kernels ran        */
+    VF_ERR_BUFFER_TOO_SMALL = -10,/* copyTo destination smaller than required (content.cpp:172-174)    */
+    VF_ERR_ALIGNMENT = -11,       /* weights-table pointer not 16-aligned (nce_sparsity.cpp:216-222)   */
+    VF_ERR_RANGE = -12,           /* post-shift needed / rescaled bias outside int32
+                                     (quantization.cpp:429-432, nce_sparsity.cpp:340-345)              */
+    VF_ERR_QUANT_RANGE = -13,     /* calcScaleAndZeroPoint failure (quantization.cpp:612-625)          */
+    VF_ERR_CUDA = -20,            /* a CUDA runtime call failed; message carries cudaGetErrorString    */
+    VF_ERR_NO_DEVICE = -21,       /* no usable CUDA device                                             */
+    VF_ERR_OOM = -22,             /* device or pinned allocation failed                                */
+    VF_ERR_CAPACITY = -23         /* fixed-capacity entry point: request exceeds the built-in maximum  */
+} vf_status;
+
+/* ------------------------------------------------------------------ */
+/* element types                                                       */
+/* ------------------------------------------------------------------ */
+typedef enum vf_dtype {
+    VF_DT_INVALID = 0,
+    VF_DT_F32 = 1,
+    VF_DT_F16 = 2,
+    VF_DT_BF16 = 3,
+    VF_DT_F64 = 4,
+    VF_DT_I8 = 5,
+    VF_DT_U8 = 6,
+    VF_DT_I16 = 7,
+    VF_DT_U16 = 8,
+    VF_DT_I32 = 9,
+    VF_DT_U32 = 10,
+    VF_DT_I64 = 11,
+    VF_DT_U64 = 12,
+    VF_DT_I4 = 13,
+    VF_DT_U4 = 14,
+    VF_DT_I1 = 15 /* 1-bit, signless; sparsity maps */
+} vf_dtype;
+
+typedef enum vf_elem_kind {
+    VF_ELEM_PLAIN = 0,         /* builtin integer / float type                                   */
+    VF_ELEM_QUANT_UNIFORM = 1, /* !quant.uniform<storage:expressed, scale:zp>                    */
+    VF_ELEM_QUANT_PER_AXIS = 2 /* !quant.uniform<storage:expressed:axis, {s0:z0, s1:z1, ...}>    */
+} vf_elem_kind;
+
+/* Mirror of an MLIR element type as the Const dialect sees it. For quantized
+ * kinds `dtype` is the (sign-normalised) storage type, `qmin/qmax` are
+ * storageTypeMin/Max, and scales/zps point at `nparams` host values that the
+ * caller keeps alive for the call. */
+typedef struct vf_elem_type {
+    int32_t kind;      /* vf_elem_kind */
+    int32_t dtype;     /* vf_dtype: plain type, or quantized storage type */
+    int32_t expressed; /* vf_dtype of the expressed float type (quantized kinds) */
+    int32_t axis;      /* quantized (logical) dimension for PER_AXIS, else -1 */
+    int64_t qmin;
+    int64_t qmax;
+    int64_t nparams; /* 1 for UNIFORM, size of the quantized dimension for PER_AXIS */
+    const double* scales;
+    const int64_t* zps;
+} vf_elem_type;
+
+/* DimsOrder code as in the reference (core/attributes/dims_order.cpp:38-59):
+ * hex digits list the logical dims from the outermost to the innermost memory
+ * dim, 1-based. NCHW/OIYX = 0x1234, NHWC/OYXI = 0x1342. 0 means "identity". */
+typedef uint32_t vf_dims_order;
+#define VF_ORDER_NCHW 0x1234u
+#define VF_ORDER_NHWC 0x1342u
+#define VF_ORDER_OIYX 0x1234u
+#define VF_ORDER_OYXI 0x1342u
+
+typedef struct vf_tensor_type {
+    vf_elem_type elem;
+    int32_t rank;
+    vf_dims_order order;
+    int64_t shape[VF_MAX_RANK]; /* logical shape */
+} vf_tensor_type;
+
+typedef enum vf_mem_kind {
+    VF_MEM_HOST = 0,        /* pageable host memory */
+    VF_MEM_HOST_PINNED = 1, /* page-locked host memory */
+    VF_MEM_DEVICE = 2       /* device memory of the context's device */
+} vf_mem_kind;
+
+/* Const::Content as a POD: a typed view over a byte buffer. The logical type
+ * (`type`) and the storage element type may differ — CastElemType changes only
+ * the former (utils/content.hpp:166-171,348-351). A splat stores one element. */
+typedef struct vf_content {
+    vf_tensor_type type;
+    int32_t storage_dtype; /* vf_dtype of the bytes in `data` */
+    int32_t is_splat;
+    int32_t mem_kind; /* vf_mem_kind of `data` */
+    int32_t reserved;
+    const void* data;
+    uint64_t nbytes;
+} vf_content;
+
+/* ------------------------------------------------------------------ */
+/* transformations (#const.* attributes)                               */
+/* ------------------------------------------------------------------ */
+typedef enum vf_transform_kind {
+    VF_T_CAST_ELEM_TYPE = 1,    /* #const.CastElemType     cast_elem_type.cpp:35-37   (elem)        */
+    VF_T_CONVERT_ELEM_TYPE = 2, /* #const.ConvertElemType  convert_elem_type.cpp:48-82 (elem)       */
+    VF_T_DEQUANTIZE = 3,        /* #const.Dequantize       dequantize.cpp:42-108                    */
+    VF_T_QUANTIZE = 4,          /* #const.Quantize         quantize.cpp:108-212        (elem)       */
+    VF_T_RESCALE = 5,           /* #const.Rescale          rescale.cpp:67-82           (value)      */
+    VF_T_ADD = 6,               /* #const.Add              add.cpp:62-77               (value)      */
+    VF_T_RESHAPE = 7,           /* #const.Reshape          reshape.cpp:87-89           (a = shape)  */
+    VF_T_REORDER = 8,           /* #const.Reorder          reorder.cpp:79-99           (order)      */
+    VF_T_MEM_PERMUTE = 9,       /* #const.MemPermute       mem_permute.cpp:117-122 (order, mem_perm)*/
+    VF_T_TRANSPOSE = 10,        /* #const.Transpose        transpose.cpp:96-104        (order)      */
+    VF_T_LAYOUT_CAST = 11,      /* #const.LayoutCast       layout_cast.cpp:82-84       (order)      */
+    VF_T_PAD_WITH_ZERO = 12,    /* #const.PadWithZero      pad_with_zero.cpp:111-268   (a, b)       */
+    VF_T_BIT_PACK = 13,         /* #const.BitPack          bit_pack.cpp:132-154        (width)      */
+    VF_T_GET_SPARSITY_MAP = 14, /* #const.GetSparsityMap   get_sparsity_map.cpp:82-119              */
+    VF_T_SPARSIFY = 15,         /* #const.Sparsify         sparsify.cpp:163-203 (compress, counts)  */
+    VF_T_SUBVIEW = 16           /* #const.SubView          subview.cpp:390-432 (a = offset, b = shape) */
+} vf_transform_kind;
+
+typedef struct vf_transform {
+    int32_t kind;              /* vf_transform_kind */
+    int32_t rank;              /* number of valid entries in a[] / b[] */
+    vf_elem_type elem;         /* CastElemType / ConvertElemType / Quantize target element type */
+    vf_dims_order order;       /* Reorder / Transpose / LayoutCast / MemPermute destination order */
+    vf_dims_order mem_perm;    /* MemPermute: permutation of the memory dims */
+    int64_t a[VF_MAX_RANK];    /* padBefore | new shape | subview offset */
+    int64_t b[VF_MAX_RANK];    /* padAfter  | subview shape */
+    double value;              /* Rescale scale | Add bias */
+    int32_t width;             /* BitPack width (only 4 is accepted, bit_pack.cpp:25-36) */
+    int32_t compress_output;   /* Sparsify<compressOutputType> */
+    const int64_t* num_actual; /* Sparsify: optional numActualElements (host), else NULL */
+    int64_t n_num_actual;
+} vf_transform;
+
+/* ------------------------------------------------------------------ */
+/* context                                                             */
+/* ------------------------------------------------------------------ */
+typedef struct vf_ctx vf_ctx;
+
+#define VF_OPT_DISABLE_FUSION 1 /* run vf_quantize_fold through the unfused general kernels (for cross-checks) */
+
+typedef struct vf_options {
+    uint64_t staging_bytes; /* size of each pinned staging buffer for pageable host I/O (0 = 64 MiB) */
+    int32_t flags;          /* bitwise OR of VF_OPT_* */
+    int32_t reserved;
+} vf_options;
+
+/* Per-call statistics (the reference only logs; this is the hook for metrics). */
+typedef struct vf_stats {
+    uint64_t bytes_in;        /* bytes of the base content consumed */
+    uint64_t bytes_out;       /* bytes written to the destination */
+    uint64_t h2d_bytes;
+    uint64_t d2h_bytes;
+    int32_t kernels_launched; /* library kernels launched by the call */
+    int32_t fused;            /* 1 when the call ran on a fused single-pass kernel */
+    float device_ms;          /* device time between first and last kernel (0 unless VF_FLAG_TIMING) */
+    int32_t reserved;
+} vf_stats;
+
+int vf_abi_version(void);
+const char* vf_status_string(int status);
+
+/* One context = one device + one stream + one scratch pool. `external_stream`
+ * (a cudaStream_t, may be NULL) makes the context enqueue on the caller's
+ * stream instead of creating its own. */
+int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_ctx** out, char* err, size_t errlen);
+void vf_ctx_destroy(vf_ctx* ctx);
+int vf_ctx_synchronize(vf_ctx* ctx, char* err, size_t errlen);
+void* vf_ctx_stream(vf_ctx* ctx); /* the cudaStream_t the context launches on */
+int vf_ctx_device(vf_ctx* ctx);
+/* Total kernels launched by this context since creation (monotonic). */
+uint64_t vf_ctx_launch_count(vf_ctx* ctx);
+
+/* ------------------------------------------------------------------ */
+/* fold                                                                */
+/* ------------------------------------------------------------------ */
+
+/* = ContentAttr::inferFinalTypeAndSplat (content.cpp:519-528): runs
+ * inferOutputType / inferOutputSplat of every transformation over `base`.
+ * `out->elem.scales/zps` are redirected into (scales_buf, zps_buf), which must
+ * hold `params_cap` entries each (may be NULL when no per-axis type results).
+ * `out_bytes` receives the byte size copyTo() needs (getTotalAllocSize; for
+ * Sparsify<false> this is the size of the *uncompressed* type, as in the
+ * reference). Pure host function — needs no context. */
+int vf_infer_type(const vf_tensor_type* base, int base_is_splat, const vf_transform* t, int n, vf_tensor_type* out,
+                  int* out_is_splat, double* scales_buf, int64_t* zps_buf, int64_t params_cap, uint64_t* out_bytes,
+                  char* err, size_t errlen);
+
+/* = ContentAttr::fold() followed by Content::copyTo(dst): applies the
+ * transformation list to `base` on the GPU and materialises the result in
+ * the final *logical* element type into `dst` (mem kind `dst_mem_kind`).
+ * `out_type` (optional) receives the folded type, with scales/zps redirected
+ * into the optional buffers as in vf_infer_type. `dst_written` (optional)
+ * receives the bytes actually produced — for Sparsify this is the compressed
+ * size (sparsify.cpp:176-182), which differs from the inferred type's size.
+ * Synchronous: returns after `dst` is complete. */
+int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, void* dst, uint64_t dst_bytes,
+            int dst_mem_kind, uint64_t* dst_written, vf_tensor_type* out_type, double* scales_buf, int64_t* zps_buf,
+            int64_t params_cap, vf_stats* stats, char* err, size_t errlen);
+
+/* ------------------------------------------------------------------ */
+/* range statistics → scale / zero-point                               */
+/* ------------------------------------------------------------------ */
+typedef enum vf_range_mode {
+    VF_RANGE_MINMAX = 0, /* rMin = min(row, 0), rMax = max(row, 0)            (asymmetric)  */
+    VF_RANGE_ABSMAX = 1  /* rMin = -absmax(row), rMax = +absmax(row)          (symmetric)   */
+} vf_range_mode;
+
+/* How a weight tensor is cut into quantization units:
+ *   group_size == 0 : one unit per index of logical dim 0 (per-output-channel);
+ *   group_size  > 0 : the tensor is viewed as [rows, cols] row-major and every
+ *                     run of `group_size` consecutive elements of a row is a unit
+ *                     (the reference expresses this by unrolling the group axis,
+ *                     IE/transforms/passes/unroll_group_quantize.cpp). */
+typedef struct vf_quant_spec {
+    int32_t storage_dtype; /* VF_DT_I8 or VF_DT_U8 (Quantize cannot target sub-byte storage, quantize.cpp:22-27) */
+    int32_t range_mode;    /* vf_range_mode */
+    int64_t qmin, qmax;    /* storageTypeMin/Max, e.g. -127..127, 0..255, 0..15 */
+    int64_t group_size;    /* 0 = per output channel */
+    int32_t expressed;     /* vf_dtype of the expressed type recorded in the result type */
+    int32_t reserved;
+} vf_quant_spec;
+
+/* Per-unit ranges reduced on the GPU, then calcScaleAndZeroPoint
+ * (utils/quantization.cpp:574-636) per unit in FP64. Outputs (any may be NULL)
+ * are arrays of `n_units` in host or device memory (`out_mem_kind`). */
+int vf_row_stats(vf_ctx* ctx, const vf_content* base, const vf_quant_spec* spec, double* scales, int64_t* zps,
+                 float* rmin, float* rmax, int64_t n_units, int out_mem_kind, char* err, size_t errlen);
+
+/* Optional side outputs of vf_quantize_fold. Every pointer may be NULL. */
+typedef struct vf_quant_outputs {
+    int32_t mem_kind;       /* vf_mem_kind of all pointers below */
+    int32_t reserved;
+    double* scales;         /* [n_units] FP64 scales (what the #const.Quantize type would carry) */
+    int64_t* zps;           /* [n_units] zero points */
+    uint16_t* scales_f16;   /* [n_units] float16((float)scale) bit patterns */
+    uint8_t* zps_u4_packed; /* [ceil(n_units/2)] zero points as 4-bit, low nibble first (BitPack layout) */
+    void* dequant;          /* same shape/order as the quantized result: Dequantize + copyTo in `dequant_dtype` */
+    int32_t dequant_dtype;  /* VF_DT_F16 / VF_DT_F32 / VF_DT_BF16 */
+    int32_t reserved2;
+    uint64_t dequant_bytes;
+} vf_quant_outputs;
+
+/* Fused weight-quantization fold. Semantically identical to
+ *     (scales, zps) = vf_row_stats(base, spec)
+ *     vf_fold(base, [Quantize<spec, scales, zps>, t[0], ..., t[n-1]])
+ * with t[] drawn from {Reorder, PadWithZero, BitPack}, but reads `base`
+ * from HBM exactly once. When `outs->dequant` is set it additionally writes
+ *     vf_fold(codes, [CastElemType<q>, Dequantize]) materialised as outs->dequant_dtype. */
+int vf_quantize_fold(vf_ctx* ctx, const vf_content* base, const vf_quant_spec* spec, const vf_transform* t, int n,
+                     void* dst, uint64_t dst_bytes, int dst_mem_kind, uint64_t* dst_written,
+                     const vf_quant_outputs* outs, vf_stats* stats, char* err, size_t errlen);
+
+/* ------------------------------------------------------------------ */
+/* sparsity                                                            */
+/* ------------------------------------------------------------------ */
+
+/* = countNonSparseElementsPerOC (utils/sparsity.cpp:35-84). `counts` holds
+ * shape[0] entries in host or device memory. */
+int vf_nnz_per_oc(vf_ctx* ctx, const vf_content* content, int64_t* counts, int out_mem_kind, char* err,
+                  size_t errlen);
+
+/* One pass over a folded weight tensor producing what SparsifyWeightsPass
+ * (VPU/transforms/passes/sparsify_weights.cpp:143-229) materialises as two
+ * constants — [CastElemType<q>, Sparsify<false>] and [CastElemType<q>,
+ * GetSparsityMap] — plus the per-OC counts. `data_written` receives the
+ * compressed byte size. Any of data/map/counts may be NULL. */
+int vf_sparsify(vf_ctx* ctx, const vf_content* content, void* data, uint64_t data_bytes, uint64_t* data_written,
+                void* map, uint64_t map_bytes, int64_t* counts, int out_mem_kind, vf_stats* stats, char* err,
+                size_t errlen);
+
+/* ------------------------------------------------------------------ */
+/* weights table                                                       */
+/* ------------------------------------------------------------------ */
+#define VF_SPARSITY_PTR_WHEN_NO_SPARSITY 0xFFFFFF /* nce_sparsity.hpp:33 */
+
+typedef struct vf_weights_table_desc {
+    vf_elem_type in_elem;      /* activation input element type  */
+    vf_elem_type out_elem;     /* activation output element type */
+    vf_elem_type weights_elem; /* kind/dtype == 0/0 (VF_DT_INVALID) means "no weights type" */
+    int64_t oc;
+    /* pointer columns: either explicit arrays (host, [oc]) or base + step */
+    const int32_t* weights_ptrs;
+    const int32_t* sparsity_ptrs;
+    int32_t weights_ptr_base, weights_ptr_step;
+    int32_t sparsity_ptr_base, sparsity_ptr_step; /* base VF_SPARSITY_PTR_WHEN_NO_SPARSITY + step 0 = dense */
+    /* sparse layout: when nnz_counts != NULL (mem kind nnz_mem_kind), column 0 is the exclusive prefix sum of
+     * align16(nnz * weights element bytes) starting at weights_ptr_base, as RelocateWeightsTable lays compressed
+     * weight sets out (relocate_weights_table.cpp:261-270) */
+    const int64_t* nnz_counts;
+    int32_t nnz_mem_kind;
+    int32_t has_bias;
+    const float* bias; /* [oc] fp32 (host or device per bias_mem_kind) */
+    int32_t bias_mem_kind;
+    int32_t bias_is_splat;
+    int32_t has_const_scale;
+    int32_t reserved;
+    double const_scale;
+} vf_weights_table_desc;
+
+/* = NCESparsity::getWeightsTable with the NPU37XX converters
+ * (NPU37XX/dialect/VPU/impl/nce_sparsity_converters.cpp:14-42).
+ * `table` receives oc*4 int32 (host or device). */
+int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* desc, int32_t* table, int out_mem_kind, char* err,
+                     size_t errlen);
+
+/* ------------------------------------------------------------------ */
+/* batches and sharding                                                */
+/* ------------------------------------------------------------------ */
+typedef struct vf_quant_job {
+    vf_content base;
+    vf_quant_spec spec;
+    const vf_transform* t;
+    int32_t n;
+    int32_t dst_mem_kind;
+    void* dst;
+    uint64_t dst_bytes;
+    vf_quant_outputs outs;
+    /* optional per-job weights table appended to the same launch sequence */
+    const vf_weights_table_desc* table_desc; /* scales of weights_elem are taken from this job's derived scales */
+    int32_t* table;                          /* [oc*4], mem kind = outs.mem_kind */
+    uint64_t dst_written;                    /* out */
+    int32_t status;                          /* out: per-job status */
+    int32_t reserved;
+} vf_quant_job;
+
+/* Many constants per call: jobs are enqueued back to back on the context's
+ * stream (small convolution weights share launches through a row table) and
+ * the call synchronises once at the end. Mirrors ConstantFoldingPass folding a
+ * batch of constants concurrently (const/passes/constant_folding.cpp:85-159). */
+int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats* stats, char* err, size_t errlen);
+
+/* Shard planner for multi-GPU runs (pure host). Units are independent, so
+ * there is no collective: `mode` 0 assigns whole tensors to ranks by
+ * longest-processing-time-first on `bytes[i]`; `mode` 1 cuts every tensor
+ * into `world` contiguous output-channel slabs of rows[i] (slab boundaries
+ * rounded to `row_align` rows). Output: for tensor i, ranks own rows
+ * [row_begin[i*world + r], row_end[i*world + r]). */
+int vf_plan_shards(int mode, int world, int64_t ntensors, const uint64_t* bytes, const int64_t* rows,
+                   int64_t row_align, int64_t* row_begin, int64_t* row_end, char* err, size_t errlen);
+
+/* ------------------------------------------------------------------ */
+/* synthetic weights (measurement support)                             */
+/* ------------------------------------------------------------------ */
+typedef struct vf_synth_spec {
+    uint64_t seed;
+    uint64_t tensor_id;
+    int32_t dtype;          /* VF_DT_F32 / VF_DT_F16 / VF_DT_BF16 */
+    int32_t reserved;
+    float sigma;            /* standard deviation of the bell-shaped base distribution */
+    float outlier_mult;     /* elements selected with probability 2^-outlier_log2 are multiplied by this (0 = off) */
+    int32_t outlier_log2;
+    int32_t mask_zero;      /* 1: zero each element with probability 1/2 ...                          */
+    int32_t dense_row_mod;  /* ... except rows whose hash % dense_row_mod == 0 (0 = no dense rows)     */
+    int32_t reserved2;
+    int64_t row_len;        /* elements per row (for the row hash) */
+    uint64_t first_elem;    /* global index of element 0 of this buffer (so slabs re-derive identically) */
+} vf_synth_spec;
+
+/* Fills `dst` (device memory) with `count` deterministic pseudo-random
+ * weights. The sequence is defined by integer hashing plus one IEEE multiply
+ * and one round-to-nearest-even conversion, so a host restatement produces the
+ * same bits. */
+int vf_synth_fill(vf_ctx* ctx, const vf_synth_spec* spec, void* dst, uint64_t count, char* err, size_t errlen);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VFOLD_H_ */

@@ -1,0 +1,321 @@
+"""Known-answer cases transcribed from the reference's own tests.
+
+Each function takes a backend (the CPU oracle or the GPU library — both expose
+infer_type / fold / weights_table) and asserts the expected bytes. `UT` is
+tests/unit/vpux_compiler/dialect/const/content_tests.cpp of the reference; lit
+files are under tests/lit/NPU.
+"""
+import numpy as np
+
+from vpux_plugin_b200 import abi
+from vpux_plugin_b200.abi import Elem, TType
+from vpux_plugin_b200.const import ContentAttr, ContentSetup
+
+F32, F16, I8, U8, I32 = abi.VF_DT_F32, abi.VF_DT_F16, abi.VF_DT_I8, abi.VF_DT_U8, abi.VF_DT_I32
+
+
+def _gen(n, dt):
+    return np.arange(n).astype(dt)  # generateValues<T>, UT:43-51
+
+
+def quantize(be):
+    """UT:2440-2469 Quantize"""
+    t = TType([1, 16], F32)
+    vals = np.array([-2.0 + 0.25 * i for i in range(16)], np.float32)
+    q = Elem.uniform(I8, F32, 1.0 / 127.0, 56, -127, 127)
+    out = ContentAttr(vals, t, ContentSetup(t).quantize(q)).fold(be)
+    assert out.type == TType([1, 16], I8)
+    exp = [-127, -127, -127, -103, -71, -39, -7, 24, 56, 88, 120, 127, 127, 127, 127, 127]
+    assert out.values(np.int8).tolist() == exp
+
+
+def per_axis_quantize(be):
+    """UT:2471-2510 PerAxisQuantize"""
+    t = TType([2, 16], F32)
+    vals = np.array([[-2.0 + 0.25 * j for j in range(16)]] * 2, np.float32)
+    q = Elem.per_axis(I8, F32, [1.0 / 127.0, 0.003], [56, -21], 0, -127, 127)
+    out = ContentAttr(vals, t, ContentSetup(t).quantize(q)).fold(be)
+    a0 = [-127, -127, -127, -103, -71, -39, -7, 24, 56, 88, 120, 127, 127, 127, 127, 127]
+    a1 = [-127, -127, -127, -127, -127, -127, -127, -104, -21, 62, 127, 127, 127, 127, 127, 127]
+    assert out.values(np.int8).tolist() == a0 + a1
+
+
+def dequantize_quantize(be):
+    """UT:2512-2540 DequantizeQuantize: castElemType(q).dequantize().quantize(q) is the identity"""
+    t = TType([1, 16], I8)
+    vals = np.array([-120 + 15 * i for i in range(16)], np.int8)
+    q = Elem.uniform(I8, F16, 0.003, 56, -120, 120)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(q).dequantize().quantize(q)).fold(be)
+    assert out.values(np.int8).tolist() == vals.tolist()
+
+
+def quant_cast(be):
+    """UT:726-752 QuantCast (CastElemType to a quantized type moves the buffer)"""
+    t = TType([1, 16], U8)
+    vals = _gen(16, np.uint8)
+    q = Elem.uniform(U8, F32, 0.078431372549019607, 128, 0, 255)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(q)).fold(be)
+    assert out.type == TType([1, 16], q)
+    assert out.values(np.uint8).tolist() == list(range(16))
+
+
+def dequantize(be):
+    """UT:754-788 Dequantize"""
+    t = TType([1, 16], I8)
+    vals = np.array([((i % 3) - 1) * 127 for i in range(16)], np.int8)
+    q = Elem.uniform(I8, F32, 2.0 / 254.0, 0, -127, 127)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(q).dequantize()).fold(be)
+    assert out.type == TType([1, 16], F32)
+    exp = np.array([float((i % 3) - 1) for i in range(16)], np.float32)
+    np.testing.assert_allclose(out.values(np.float32), exp, rtol=4 * np.finfo(np.float32).eps)  # EXPECT_FLOAT_EQ
+
+
+def reorder(be):
+    """UT:906-939 Reorder NCHW -> NHWC"""
+    N, Cc, H, W = 1, 2, 2, 2
+    t = TType([N, Cc, H, W], F32)
+    vals = _gen(8, np.float32)
+    out = ContentAttr(vals, t, ContentSetup(t).reorder(abi.ORDER_NHWC)).fold(be)
+    assert out.type == TType([N, Cc, H, W], F32, abi.ORDER_NHWC)
+    got = out.values(np.float32)
+    for c in range(Cc):
+        for h in range(H):
+            for w in range(W):
+                assert got[c + w * Cc + h * Cc * W] == vals[w + h * W + c * W * H]
+
+
+def _check_padded(act, exp, buf, pad, zp, act_off=0, org_off=0):  # checkPaddedBuffer, UT:63-89
+    IC, IH, IW = buf
+    PC, PH, PW = pad
+    for c in range(IC + 2 * PC):
+        for h in range(IH + 2 * PH):
+            for w in range(IW + 2 * PW):
+                ni = w + h * (IW + 2 * PW) + c * (IW + 2 * PW) * (IH + 2 * PH) + act_off
+                if c < PC or c >= IC + PC or h < PH or h >= IH + PH or w < PW or w >= IW + PW:
+                    assert act[ni] == zp, (c, h, w)
+                else:
+                    oi = (w - PW) + (h - PH) * IW + (c - PC) * IW * IH + org_off
+                    assert act[ni] == exp[oi], (c, h, w)
+
+
+def pad(be):
+    """UT:976-1002 Pad"""
+    t = TType([1, 2, 3], I32)
+    vals = _gen(6, np.int32)
+    out = ContentAttr(vals, t, ContentSetup(t).padWithZero([1, 1, 1], [1, 1, 1])).fold(be)
+    assert out.type == TType([3, 4, 5], I32)
+    _check_padded(out.values(np.int32), vals, (1, 2, 3), (1, 1, 1), 0)
+
+
+def pad_splat(be):
+    """UT:1004-1030 PadSplat"""
+    t = TType([1, 2, 3], I32)
+    out = ContentAttr(np.array([42], np.int32), t, ContentSetup(t).padWithZero([1, 1, 1], [1, 1, 1]),
+                      is_splat=True).fold(be)
+    assert not out.is_splat
+    _check_padded(out.values(np.int32), np.full(6, 42, np.int32), (1, 2, 3), (1, 1, 1), 0)
+
+
+def pad_uniform_quant(be):
+    """UT:1032-1070 PadUniformQuant: f32 storage, padding holds the zero point"""
+    OC, IC, IH, IW = 2, 1, 2, 3
+    t = TType([OC, IC, IH, IW], F32)
+    vals = _gen(12, np.float32)
+    zp = 128
+    q = Elem.uniform(U8, F32, 0.078431372549019607, zp, 0, 255)
+    P = 2
+    attr = ContentAttr(vals, t, ContentSetup(t).castElemType(q).padWithZero([0, P, P, P], [0, P, P, P]))
+    out = attr.fold(be)
+    # the bytes come back through copyTo in the logical u8 type; the storage was f32 (values 0..11 and 128.0)
+    got = out.values(np.uint8).astype(np.float32)
+    for oc in range(OC):
+        _check_padded(got, vals, (IC, IH, IW), (P, P, P), zp, oc * (IC + 2 * P) * (IW + 2 * P) * (IH + 2 * P),
+                      oc * IC * IW * IH)
+
+
+def pad_per_axis_quant(be):
+    """UT:1072-1123 PadPerAxisQuant: scales/zps replicated onto the padded channels"""
+    OC, IC, IH, IW = 2, 1, 2, 3
+    t = TType([OC, IC, IH, IW], F32)
+    vals = _gen(12, np.float32)
+    zp = 127
+    q = Elem.per_axis(U8, F32, [0.5, 0.5], [zp, zp], 0, 0, 255)
+    POC = PIC = PH = PW = 2
+    attr = ContentAttr(vals, t, ContentSetup(t).castElemType(q).padWithZero([POC, PIC, PH, PW], [POC, PIC, PH, PW]))
+    out = attr.fold(be)
+    assert out.type.elem.zps.tolist() == [zp] * (OC + 2 * POC)
+    assert out.type.elem.scales.tolist() == [0.5] * (OC + 2 * POC)
+    got = out.values(np.uint8).astype(np.float32)
+    ch = IC * IW * IH
+    exp = np.concatenate([np.full(ch * POC, zp, np.float32), vals, np.full(ch * POC, zp, np.float32)])
+    for oc in range(OC + 2 * POC):
+        _check_padded(got, exp, (IC, IH, IW), (PIC, PH, PW), zp, oc * (IC + 2 * PIC) * (IW + 2 * PW) * (IH + 2 * PH),
+                      oc * ch)
+
+
+def bit_pack(be):
+    """UT:1246-1274 BitPack"""
+    t = TType([1, 2, 3], I8)
+    vals = np.array([1, 2, 3, 4, 5, 6], np.int8)
+    out = ContentAttr(vals, t, ContentSetup(t).bitPack(4)).fold(be)
+    assert out.type == TType([1, 2, 3], abi.VF_DT_I4)
+    assert out.bytes().tolist() == [0x21, 0x43, 0x65]
+
+
+def bit_pack_quant(be):
+    """UT:1276-1315 BitPackQuant"""
+    t = TType([1, 2, 3], I8)
+    vals = np.array([1, 2, 3, 1, 2, 3], np.int8)
+    q = Elem.uniform(I8, F32, 1.0, 0, -4, 3)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(q).bitPack(4)).fold(be)
+    assert out.type == TType([1, 2, 3], Elem.uniform(abi.VF_DT_I4, F32, 1.0, 0, -4, 3))
+    assert out.bytes().tolist() == [0x21, 0x13, 0x32]
+
+
+def get_sparsity_map(be):
+    """UT:1536-1569 GetSparsityMap"""
+    t = TType([1, 1, 2, 8], U8)
+    vals = np.array([0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 11, 0, 13, 14, 15], np.uint8)
+    out = ContentAttr(vals, t, ContentSetup(t).getSparsityMap()).fold(be)
+    assert out.type == TType([1, 1, 1, 128], abi.VF_DT_I1)
+    assert out.bytes().tolist() == [0xFE, 0xEB] + [0] * 14
+
+
+def get_sparsity_map_quantized(be):
+    """UT:1571-1618 GetSparsityMapQuantized (zero point 7 marks the sparse value)"""
+    t = TType([1, 1, 2, 8], U8)
+    vals = np.array([7, 0, 1, 2, 3, 4, 5, 6, 7, 8, 7, 10, 7, 12, 13, 14], np.uint8)
+    q = Elem.uniform(U8, F32, 1.0, 7, 0, 14)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(q).getSparsityMap()).fold(be)
+    assert out.bytes().tolist() == [0xFE, 0xEA] + [0] * 14
+
+
+_SP_VALS = np.array([0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 11, 0, 13, 14, 15,
+                     16, 0, 18, 19, 20, 0, 22, 23, 24, 25, 26, 0, 0, 29, 30, 31], np.uint8)
+_SP_EXP = [1, 2, 3, 4, 5, 6, 7, 8, 9, 11, 13, 14, 15, 0, 0, 0,
+           16, 18, 19, 20, 22, 23, 24, 25, 26, 29, 30, 31, 0, 0, 0, 0]
+
+
+def sparsify(be):
+    """UT:1620-1646 Sparsify<false>: folded bytes are compressed, the attribute type is not"""
+    t = TType([2, 1, 2, 8], U8)
+    attr = ContentAttr(_SP_VALS, t, ContentSetup(t).sparsify(False))
+    out = attr.fold(be)
+    assert attr.infer(be)[0] == t  # inferred (attribute) type stays uncompressed
+    assert out.type == TType([32, 1, 1, 1], U8)  # folded content type is the compressed one
+    assert out.bytes().tolist() == _SP_EXP
+
+
+def sparsify_true(be):
+    """UT:1648-1679 Sparsify<true, numActualElements>"""
+    t = TType([2, 1, 2, 8], U8)
+    attr = ContentAttr(_SP_VALS, t, ContentSetup(t).sparsify(True, [13, 12]))
+    out = attr.fold(be)
+    assert attr.infer(be)[0] == TType([32, 1, 1, 1], U8)
+    assert out.type == TType([32, 1, 1, 1], U8)
+    assert out.bytes().tolist() == _SP_EXP
+
+
+def sparsify_quantized(be):
+    """UT:1681-1722 SparsifyQuantized (zero point 16)"""
+    t = TType([2, 1, 2, 8], U8)
+    vals = np.array([16, 1, 2, 3, 4, 5, 6, 7, 8, 9, 16, 11, 16, 13, 14, 15,
+                     16, 16, 18, 19, 20, 16, 22, 23, 24, 25, 26, 16, 16, 29, 30, 31], np.uint8)
+    exp = [1, 2, 3, 4, 5, 6, 7, 8, 9, 11, 13, 14, 15, 0, 0, 0,
+           18, 19, 20, 22, 23, 24, 25, 26, 29, 30, 31, 0, 0, 0, 0, 0]
+    q = Elem.uniform(U8, F32, 1.0, 16, 0, 31)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(q).sparsify(False)).fold(be)
+    assert out.bytes().tolist() == exp
+
+
+def position_requirement(be):
+    """UT:1724-1749 PositionRequirement (BitPack stands in for the LAST-positioned SwizzleConstant)"""
+    t = TType([1, 1, 3, 3], F32)
+    s = ContentSetup(t).rescale(10.0).bitPack(4).sparsify(False).castElemType(F16)
+    assert s.names() == [abi.VF_T_RESCALE, abi.VF_T_CAST_ELEM_TYPE, abi.VF_T_SPARSIFY, abi.VF_T_BIT_PACK]
+
+
+def convert_elem_type_i8_u8(be):
+    """UT:2276-2330 ConvertElemType Roundtrip, I8_to_U8: values shift by zpOut - zpIn = 128 and back"""
+    t = TType([1, 2, 3, 4], F16)
+    i8 = Elem.uniform(I8, F32, 0.5, 0, -128, 127)
+    u8 = Elem.uniform(U8, F32, 0.5, 128, 0, 255)
+    vals = np.array([(-128 + i) if i % 2 == 0 else (127 - i) for i in range(24)], np.float16)
+    s = ContentSetup(t).castElemType(i8).convertElemType(u8)
+    out = ContentAttr(vals, t, s).fold(be)
+    assert out.values(np.uint8).astype(np.float32).tolist() == (vals.astype(np.float32) + 128).tolist()
+    back = ContentAttr(vals, t, s.convertElemType(i8)).fold(be)
+    assert back.values(np.int8).astype(np.float32).tolist() == vals.astype(np.float32).tolist()
+
+
+def convert_elem_type_u4_i4(be):
+    """UT:2332-2353 U4_to_I4: offset -8; copyTo packs two 4-bit values per byte (content.cpp:131-152)"""
+    t = TType([1, 2, 3, 4], F16)
+    u4 = Elem.uniform(abi.VF_DT_U4, F32, 1.0, 8, 0, 15)
+    i4 = Elem.uniform(abi.VF_DT_I4, F32, 1.0, 0, -8, 7)
+    vals = np.array([i % 15 for i in range(24)], np.float16)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(u4).convertElemType(i4)).fold(be)
+    packed = out.bytes()
+    assert len(packed) == 12
+    nib = np.stack([packed & 0xF, packed >> 4], axis=1).reshape(-1).astype(np.int64)
+    exp = (vals.astype(np.int64) - 8) & 0xF
+    assert nib.tolist() == exp.tolist()
+
+
+def quantize_splat(be):
+    """lit dialect/const/passes/constant_folding.mlir:695-709 QuantizeSplat: 5.0 / 0.5 -> 10"""
+    t = TType([1, 16, 3, 3], F16)
+    q = Elem.uniform(U8, F16, 0.5, 0, 0, 255)
+    out = ContentAttr(np.array([5.0], np.float16), t, ContentSetup(t).quantize(q), is_splat=True).fold(be)
+    assert out.values(np.uint8).tolist() == [10] * 144
+
+
+def const_fold_chain(be):
+    """lit dialect/const/passes/constant_folding.mlir:9-30 ConstFold: cast chain + Dequantize + Reorder<YXOI>"""
+    t = TType([16, 3, 1, 1], F32)
+    q = Elem.uniform(U8, F16, 0.0039215686274509803, 0, 0, 255)
+    s = ContentSetup(t).castElemType(F16).castElemType(U8).castElemType(q).dequantize().reorder(0x3412)
+    attr = ContentAttr(np.array([1.0], np.float32), t, s, is_splat=True)
+    out = attr.fold(be)
+    assert out.type == TType([16, 3, 1, 1], F16, 0x3412)
+    v = out.values(np.float16)
+    assert v.shape == (48,) and (v == np.float16(np.float32(0.0039215686274509803))).all()
+
+
+def _wt_desc(in_elem, out_elem, w_elem, oc, wbase, wstep, sbase, sstep):
+    d = abi.WeightsTableDesc()
+    d.in_elem, d.out_elem, d.weights_elem = in_elem.pod(), out_elem.pod(), w_elem.pod()
+    d.oc = oc
+    d.weights_ptr_base, d.weights_ptr_step = wbase, wstep
+    d.sparsity_ptr_base, d.sparsity_ptr_step = sbase, sstep
+    return d, (in_elem, out_elem, w_elem)
+
+
+def weights_table_fixed_point(be):
+    """lit dialect/VPU/passes/lower_ops_to_se_nce_37XX_40XX.mlir:9-11,58-61: u8 in/out, u8 weights 0.25"""
+    d, keep = _wt_desc(Elem.uniform(U8, F16, 0.0151786074918859, 128, 0, 255),
+                       Elem.uniform(U8, F16, 0.0257227579752604, 128, 0, 255),
+                       Elem.uniform(U8, F16, 0.25, 0, 0, 255), 16, 0, 64, 0, 0)
+    tab = be.weights_table(d, 16).reshape(16, 4)
+    assert tab[:, 0].tolist() == [64 * i for i in range(16)]
+    assert tab[:, 1].tolist() == [0] * 16
+    assert tab[:, 2].tolist() == [1267142912] * 16
+    assert tab[:, 3].tolist() == [0] * 16
+
+
+def weights_table_float_scale(be):
+    """lit conversion/passes/IE2VPU/convert_IE_to_VPU_NCE_37XX_40XX.mlir:1026-1050: f16 activations, i4
+    weights of scale 1.3385416666666667 -> column 2 holds the fp32 bit pattern of the scale"""
+    d, keep = _wt_desc(Elem(F16), Elem(F16), Elem.uniform(abi.VF_DT_I4, F16, 1.3385416666666667, 0, -8, 7), 16, 0,
+                       16, 0, 0)
+    tab = be.weights_table(d, 16).reshape(16, 4)
+    assert tab[:, 0].tolist() == [16 * i for i in range(16)]
+    assert tab[:, 2].tolist() == [1068193109] * 16
+    assert tab[:, 3].tolist() == [0] * 16
+
+
+FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequantize, reorder, pad, pad_splat,
+              pad_uniform_quant, pad_per_axis_quant, bit_pack, bit_pack_quant, get_sparsity_map,
+              get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
+              convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain]
+TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale]

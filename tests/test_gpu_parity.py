@@ -1,0 +1,437 @@
+"""GPU parity: every entry point of libvfold.so against the CPU oracle on the same seeded inputs.
+
+Integer / byte outputs must be bit-exact. Floating outputs (dequantize, rescale) are compared bit for bit
+as well — the stated tolerance for them is 1 fp16 ULP, and the kernels use the reference's exact
+operation order, so any difference is reported.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import reference_cases as rc
+from vpux_plugin_b200 import abi, workloads as wl
+from vpux_plugin_b200.abi import Elem, TType
+from vpux_plugin_b200.const import ContentAttr, ContentSetup
+
+pytestmark = pytest.mark.gpu
+
+F32, F16, BF16, I8, U8, I32 = abi.VF_DT_F32, abi.VF_DT_F16, abi.VF_DT_BF16, abi.VF_DT_I8, abi.VF_DT_U8, abi.VF_DT_I32
+
+
+def bf16_bits(x):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+def both(attr, gpu, oracle, dst_bytes=None):
+    a = attr.fold(gpu, dst_bytes)
+    b = attr.fold(oracle, dst_bytes)
+    assert a.type == b.type, (a.type, b.type)
+    assert a.written == b.written
+    assert np.array_equal(a.bytes(), b.bytes()), f"{int((a.bytes() != b.bytes()).sum())} differing bytes"
+    return a
+
+
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case", rc.FOLD_CASES + rc.TABLE_CASES, ids=lambda c: c.__name__)
+def test_reference_vectors_on_gpu(case, gpu):
+    case(gpu)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# randomized differential tests, one transformation (or short chain) at a time
+# ---------------------------------------------------------------------------------------------------------
+def _rand(rng, shape, dt):
+    x = rng.standard_normal(shape).astype(np.float32)
+    if dt == F32:
+        return x
+    if dt == F16:
+        return x.astype(np.float16)
+    return bf16_bits(x)
+
+
+@pytest.mark.parametrize("dt", [F32, F16, BF16])
+@pytest.mark.parametrize("storage,qmin,qmax", [(I8, -128, 127), (I8, -127, 127), (U8, 0, 255), (U8, 0, 15),
+                                               (I8, -120, 120), (abi.VF_DT_I16, -32768, 32767), (I32, -1000, 1000)])
+def test_quantize_per_tensor(gpu, oracle, dt, storage, qmin, qmax):
+    rng = np.random.default_rng(1)
+    t = TType([3, 5, 7], dt)
+    x = _rand(rng, t.shape, dt)
+    q = Elem.uniform(storage, F32, 0.013, (qmin + qmax) // 2 + 3, qmin, qmax)
+    both(ContentAttr(x, t, ContentSetup(t).quantize(q)), gpu, oracle)
+
+
+@pytest.mark.parametrize("axis", [0, 1, 3])
+@pytest.mark.parametrize("order", [abi.ORDER_NCHW, abi.ORDER_NHWC])
+def test_quantize_dequantize_per_axis(gpu, oracle, axis, order):
+    rng = np.random.default_rng(2)
+    shape = [6, 5, 3, 4]
+    t = TType(shape, F16, order)
+    x = _rand(rng, shape, F16)
+    n = shape[axis]
+    scales = rng.uniform(0.001, 0.05, n)
+    zps = rng.integers(-20, 20, n)
+    q = Elem.per_axis(I8, F16, scales, zps, axis, -127, 127)
+    both(ContentAttr(x, t, ContentSetup(t).quantize(q)), gpu, oracle)
+    codes = rng.integers(-127, 128, shape).astype(np.int8)
+    tq = TType(shape, I8, order)
+    for expressed in (F16, F32, BF16):
+        qe = Elem.per_axis(I8, expressed, scales, zps, axis, -127, 127)
+        both(ContentAttr(codes, tq, ContentSetup(tq).castElemType(qe).dequantize()), gpu, oracle)
+
+
+def test_dequantize_fp16_overflow_clamps(gpu, oracle):
+    """copyTo of an fp32 value beyond the fp16 range clamps to +-65504 (utils/content.hpp:41-55)."""
+    t = TType([1, 8], I8)
+    codes = np.array([-128, -100, -1, 0, 1, 50, 100, 127], np.int8)
+    q = Elem.uniform(I8, F16, 1000.0, 0, -128, 127)
+    out = both(ContentAttr(codes, t, ContentSetup(t).castElemType(q).dequantize()), gpu, oracle)
+    v = out.values(np.float16).astype(np.float32)
+    assert v[0] == -65504.0 and v[-1] == 65504.0 and v[3] == 0.0
+
+
+def test_f32_to_f16_matches_reference_including_subnormal_quirk(gpu, oracle):
+    """CastElemType<f16> on f32 storage converts at copyTo through float16(float) (float16.cpp:30-108)."""
+    rng = np.random.default_rng(3)
+    special = np.array([0x347FF000, 0x32FFF000, 0x33000000, 0x33000001, 0x387FFFFF, 0x38800000, 0x477FEFFF,
+                        0x477FF000, 0x7F800000, 0xFF800000, 0x7FC00000, 0x7F800001, 0xFFC12345, 0x00000001,
+                        0x80000000, 0x38000000, 0x37FFFFFF], np.uint32)
+    # every mantissa with eleven leading ones across the subnormal-result exponents (the carry cases)
+    exps = np.arange(100, 114, dtype=np.uint32)
+    carry = ((exps[:, None] << 23) | (0x7FF000 + np.arange(0, 0x1000, 7, dtype=np.uint32))[None, :]).reshape(-1)
+    rnd = rng.integers(0, 1 << 32, 1 << 20, dtype=np.uint64).astype(np.uint32)
+    tiny = (rng.integers(0, 1 << 23, 1 << 20, dtype=np.uint64).astype(np.uint32)
+            | (rng.integers(90, 114, 1 << 20, dtype=np.uint64).astype(np.uint32) << 23))
+    bits = np.concatenate([special, carry, carry | 0x80000000, rnd, tiny])
+    t = TType([bits.size], F32)
+    out = both(ContentAttr(bits.view(np.float32), t, ContentSetup(t).castElemType(F16)), gpu, oracle)
+    from oracle import ReferenceTypes
+    if ReferenceTypes.available():  # the reference's own class, compiled unmodified
+        ref = ReferenceTypes().f32_to_f16(bits)
+        got = out.values(np.uint16)
+        inf = (ref & 0x7FFF) == 0x7C00  # copyTo clamps infinities
+        assert np.array_equal(got[~inf], ref[~inf])
+        assert ((got[inf] & 0x7FFF) == 0x7BFF).all()
+
+
+@pytest.mark.parametrize("dt", [F32, F16, BF16, I8, U8, I32])
+def test_rescale_add(gpu, oracle, dt):
+    rng = np.random.default_rng(4)
+    t = TType([4, 33], dt)
+    x = _rand(rng, t.shape, dt) if dt in (F32, F16, BF16) else rng.integers(0, 100, t.shape).astype(abi.DTYPE_NUMPY[dt])
+    both(ContentAttr(x, t, ContentSetup(t).rescale(0.37).add(1.25)), gpu, oracle)
+
+
+@pytest.mark.parametrize("dt,es", [(U8, 1), (F16, 2), (F32, 4)])
+@pytest.mark.parametrize("shape,order_in,order_out", [
+    ([2, 3, 4, 5], abi.ORDER_NCHW, abi.ORDER_NHWC), ([2, 3, 4, 5], abi.ORDER_NHWC, abi.ORDER_NCHW),
+    ([7, 16, 3, 3], abi.ORDER_NCHW, 0x3412), ([5, 1, 1, 9], abi.ORDER_NCHW, abi.ORDER_NHWC),
+    ([2, 3, 4, 5, 6], 0x12345, 0x13452), ([3, 4], 0x12, 0x21), ([4, 5, 6], 0x123, 0x312)])
+def test_reorder(gpu, oracle, dt, es, shape, order_in, order_out):
+    rng = np.random.default_rng(5)
+    t = TType(shape, dt, order_in)
+    x = rng.integers(0, 255, int(np.prod(shape)) * es).astype(np.uint8).view(abi.DTYPE_NUMPY[dt])
+    both(ContentAttr(x, t, ContentSetup(t).reorder(order_out)), gpu, oracle)
+
+
+def test_transpose_and_mem_permute(gpu, oracle):
+    rng = np.random.default_rng(6)
+    t = TType([2, 3, 4, 5], F16, abi.ORDER_NHWC)
+    x = _rand(rng, t.shape, F16)
+    both(ContentAttr(x, t, ContentSetup(t).transpose(0x2143)), gpu, oracle)
+    both(ContentAttr(x, t, ContentSetup(t).memPermute(abi.ORDER_NCHW, 0x4213)), gpu, oracle)
+
+
+@pytest.mark.parametrize("order", [abi.ORDER_NCHW, abi.ORDER_NHWC])
+def test_pad_variants(gpu, oracle, order):
+    rng = np.random.default_rng(7)
+    shape = [3, 5, 2, 4]
+    t = TType(shape, F16, order)
+    x = _rand(rng, shape, F16)
+    both(ContentAttr(x, t, ContentSetup(t).padWithZero([1, 0, 2, 0], [0, 3, 0, 1])), gpu, oracle)
+    codes = rng.integers(0, 255, shape).astype(np.uint8)
+    tq = TType(shape, U8, order)
+    qu = Elem.uniform(U8, F16, 0.1, 77, 0, 255)
+    both(ContentAttr(codes, tq, ContentSetup(tq).castElemType(qu).padWithZero([0, 1, 1, 1], [2, 0, 0, 3])), gpu, oracle)
+    qa = Elem.per_axis(U8, F16, [0.1, 0.2, 0.3], [9, 9, 9], 0, 0, 255)
+    both(ContentAttr(codes, tq, ContentSetup(tq).castElemType(qa).padWithZero([1, 1, 0, 0], [2, 0, 1, 0])), gpu, oracle)
+    # unequal zero points: padding inside a channel takes that channel's zero point
+    qb = Elem.per_axis(U8, F16, [0.1, 0.2, 0.3], [3, 60, 200], 0, 0, 255)
+    both(ContentAttr(codes, tq, ContentSetup(tq).castElemType(qb).padWithZero([0, 2, 0, 1], [0, 1, 1, 0])), gpu, oracle)
+
+
+def test_subview(gpu, oracle):
+    rng = np.random.default_rng(8)
+    t = TType([6, 8, 3, 3], I8, abi.ORDER_NHWC)
+    x = rng.integers(-128, 127, t.shape).astype(np.int8)
+    q = Elem.per_axis(I8, F16, np.linspace(0.1, 0.6, 6), np.zeros(6), 0, -127, 127)
+    out = both(ContentAttr(x, t, ContentSetup(t).castElemType(q).subview([2, 0, 0, 0], [3, 8, 3, 3])), gpu, oracle)
+    assert out.type.elem.scales.tolist() == np.linspace(0.1, 0.6, 6)[2:5].tolist()
+
+
+@pytest.mark.parametrize("dt", [I8, U8, F16, BF16, F32])
+@pytest.mark.parametrize("shape", [[5, 8, 1, 1], [3, 4, 3, 2], [17, 16, 3, 3], [2, 40, 1, 1]])
+def test_sparsify_and_map(gpu, oracle, dt, shape):
+    rng = np.random.default_rng(9)
+    n = int(np.prod(shape))
+    keep = rng.random(n) < 0.45
+    keep[:shape[1] * shape[2] * shape[3]] = True  # first channel dense
+    if dt in (I8, U8):
+        x = (rng.integers(1, 100, n) * keep).astype(abi.DTYPE_NUMPY[dt])
+    elif dt == BF16:
+        x = bf16_bits(rng.standard_normal(n) * keep)
+    else:
+        x = (rng.standard_normal(n) * keep).astype(abi.DTYPE_NUMPY[dt])
+        x[3] = -0.0  # negative zero counts as zero
+    t = TType(shape, dt)
+    both(ContentAttr(x, t, ContentSetup(t).sparsify(False)), gpu, oracle, dst_bytes=n * 4 + 16 * shape[0])
+    both(ContentAttr(x, t, ContentSetup(t).getSparsityMap()), gpu, oracle)
+    c, keepalive = abi.make_content(t, x)
+    assert np.array_equal(gpu.nnz_per_oc(c, shape[0]), oracle.nnz_per_oc(c, shape[0]))
+    # combined entry point
+    cap = n * 4 + 16 * shape[0]
+    row = (shape[1] * shape[2] * shape[3] + 127) // 128 * 16
+    outs = []
+    for be in (gpu, oracle):
+        data, mp, cnt = np.zeros(cap, np.uint8), np.zeros(shape[0] * row, np.uint8), np.zeros(shape[0], np.int64)
+        w = be.sparsify(c, data, mp, cnt)
+        outs.append((w, data[:w].copy(), mp, cnt))
+    assert outs[0][0] == outs[1][0]
+    for a, b in zip(outs[0][1:], outs[1][1:]):
+        assert np.array_equal(a, b)
+
+
+def test_sparsify_quantized_with_supplied_counts(gpu, oracle):
+    rng = np.random.default_rng(10)
+    shape = [4, 8, 2, 2]
+    x = rng.integers(0, 4, shape).astype(np.uint8)
+    t = TType(shape, U8)
+    q = Elem.uniform(U8, F16, 0.5, 2, 0, 255)
+    c, _k = abi.make_content(TType(shape, q), x, storage_dtype=U8)
+    counts = oracle.nnz_per_oc(c, 4)
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(q).sparsify(True, counts)), gpu, oracle)
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(q).sparsify(True, counts + 5)), gpu, oracle)
+
+
+def test_bitpack_paths(gpu, oracle):
+    rng = np.random.default_rng(11)
+    for n in (6, 32, 4096 + 16, 1000):
+        x = rng.integers(0, 16, n).astype(np.uint8)
+        t = TType([1, n], U8)
+        both(ContentAttr(x, t, ContentSetup(t).bitPack(4)), gpu, oracle)
+    xi = rng.integers(0, 8, 64).astype(np.int8)
+    t = TType([64], I8)
+    both(ContentAttr(xi, t, ContentSetup(t).bitPack(4)), gpu, oracle)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# error behaviour: same status code from both sides
+# ---------------------------------------------------------------------------------------------------------
+def _status(fn):
+    try:
+        fn()
+    except Exception as e:  # VfoldError / OracleError both carry .status
+        return e.status
+    return 0
+
+
+@pytest.mark.parametrize("build,status", [
+    (lambda: ContentAttr(np.array([-1, 2], np.int8), TType([2], I8), ContentSetup(TType([2], I8)).bitPack(4)),
+     abi.VF_ERR_CHECKED_CAST),  # getValues<uint8_t>() of a negative value
+    (lambda: ContentAttr(np.arange(3, dtype=np.uint8), TType([3], U8), ContentSetup(TType([3], U8)).bitPack(4)),
+     abi.VF_ERR_ODD_COUNT),
+    (lambda: ContentAttr(np.zeros(4, np.float32), TType([4], F32), ContentSetup(TType([4], F32)).dequantize()),
+     abi.VF_ERR_NOT_QUANTIZED),
+    (lambda: ContentAttr(np.zeros(16, np.uint8), TType([2, 2, 2, 2], U8), ContentSetup(TType([2, 2, 2, 2], U8))
+                         .castElemType(Elem.per_axis(U8, F16, [1, 1], [3, 4], 0, 0, 255)).sparsify(False)),
+     abi.VF_ERR_ZERO_POINTS),
+    (lambda: ContentAttr(np.zeros(16, np.uint8), TType([2, 2, 2, 2], U8), ContentSetup(TType([2, 2, 2, 2], U8))
+                         .castElemType(Elem.per_axis(U8, F16, [1, 1], [3, 4], 0, 0, 255))
+                         .padWithZero([1, 0, 0, 0], [0, 0, 0, 0])), abi.VF_ERR_ZERO_POINTS),
+    (lambda: ContentAttr(np.full(4, 300.0, np.float32), TType([4], F32), ContentSetup(TType([4], F32)).castElemType(U8)),
+     abi.VF_ERR_CHECKED_CAST),  # copyTo float -> u8 out of range throws instead of saturating
+    (lambda: ContentAttr(np.zeros(4, np.float16), TType([4], F16), ContentSetup(TType([4], F16))
+                         .quantize(Elem.uniform(abi.VF_DT_U4, F16, 1.0, 0, 0, 15))), abi.VF_ERR_UNSUPPORTED),
+])
+def test_error_codes_match(gpu, oracle, build, status):
+    attr = build()
+    assert _status(lambda: attr.fold(gpu, 64)) == status
+    assert _status(lambda: attr.fold(oracle, 64)) == status
+
+
+def test_copy_to_buffer_too_small(gpu, oracle):
+    t = TType([16], F32)
+    attr = ContentAttr(np.zeros(16, np.float32), t, ContentSetup(t))
+    assert _status(lambda: attr.fold(gpu, 8)) == abi.VF_ERR_BUFFER_TOO_SMALL
+    assert _status(lambda: attr.fold(oracle, 8)) == abi.VF_ERR_BUFFER_TOO_SMALL
+
+
+# ---------------------------------------------------------------------------------------------------------
+# statistics, fused weight quantization, synthetic generator
+# ---------------------------------------------------------------------------------------------------------
+def test_synth_generator_bits(gpu, oracle):
+    import torch
+    for spec in (wl.c1_tensors()[0], wl.resnet50_tensors(sparse=True)[5], wl.llama2_7b_tensors()[0],
+                 wl.llama3_70b_tensors()[1]):
+        n = min(spec.numel, 1 << 20)
+        first = 12345 * 8
+        s = spec.synth_spec(0xABCDEF, first)
+        ref = oracle.synth_fill(s, n)
+        buf = torch.empty(n * abi.DTYPE_BITS[spec.dtype] // 8, dtype=torch.uint8, device="cuda")
+        gpu.synth_fill_device(s, buf.data_ptr(), n)
+        got = buf.cpu().numpy().view(ref.dtype)
+        assert np.array_equal(got.view(np.uint8), ref.view(np.uint8)), spec.name
+
+
+def _quant_fold(be, spec_t, x, qspec, transforms, out_bytes, units, want=("scales", "zps"), dequant_dt=None):
+    t = TType(list(spec_t), abi.VF_DT_F16 if x.dtype == np.float16 else (F32 if x.dtype == np.float32 else BF16))
+    c, keep = abi.make_content(t, x)
+    tr = abi.make_transforms(transforms)
+    dst = np.zeros(out_bytes, np.uint8)
+    outs = abi.QuantOutputs()
+    outs.mem_kind = abi.VF_MEM_HOST
+    res = {}
+    if "scales" in want:
+        res["scales"] = np.zeros(units, np.float64)
+        outs.scales = res["scales"].ctypes.data
+    if "zps" in want:
+        res["zps"] = np.zeros(units, np.int64)
+        outs.zps = res["zps"].ctypes.data
+    if "f16" in want:
+        res["f16"] = np.zeros(units, np.uint16)
+        outs.scales_f16 = res["f16"].ctypes.data
+    if "u4" in want:
+        res["u4"] = np.zeros((units + 1) // 2, np.uint8)
+        outs.zps_u4_packed = res["u4"].ctypes.data
+    if dequant_dt is not None:
+        n = int(np.prod(spec_t))
+        res["dequant"] = np.zeros(n * abi.DTYPE_BITS[dequant_dt] // 8, np.uint8)
+        outs.dequant = res["dequant"].ctypes.data
+        outs.dequant_dtype = dequant_dt
+        outs.dequant_bytes = res["dequant"].nbytes
+    w = be.quantize_fold(c, qspec, tr, len(transforms), dst, out_bytes, outs)
+    res["codes"] = dst[:w].copy()
+    return res
+
+
+def _same(a, b):
+    assert a.keys() == b.keys()
+    for k in a:
+        assert np.array_equal(a[k], b[k]), f"{k}: {int((a[k] != b[k]).sum())} of {a[k].size} differ"
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("dt", [F16, BF16])
+@pytest.mark.parametrize("rows,cols", [(4, 4096), (3, 1408), (33, 128), (1, 256)])
+def test_group_u4_fused_matches_oracle_and_general(gpu, oracle, group, dt, rows, cols):
+    from vpux_plugin_b200.lib import Library
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((rows, cols)).astype(np.float32) * 0.02
+    x[rng.random((rows, cols)) < 0.001] *= 20
+    x[0, :group] = 0  # an all-zero group
+    x[-1, -group:] = np.abs(x[-1, -group:])  # an all-positive group
+    x = x.astype(np.float16) if dt == F16 else bf16_bits(x)
+    units = rows * cols // group
+    args = ((rows, cols), x, wl.spec_u4_group(group), [wl.t_bitpack()], rows * cols // 2, units)
+    ref = _quant_fold(oracle, *args, want=("scales", "zps", "f16", "u4"))
+    got = _quant_fold(gpu, *args, want=("scales", "zps", "f16", "u4"))
+    assert gpu.last_stats.fused == 1 and gpu.last_stats.kernels_launched == 1
+    _same(got, ref)
+    general = Library(device=0, disable_fusion=True)
+    gen = _quant_fold(general, *args, want=("scales", "zps", "f16", "u4"))
+    assert general.last_stats.fused == 0
+    _same(gen, ref)
+    # unpacked u8 codes and a dequantized fp16 copy
+    args2 = ((rows, cols), x, wl.spec_u4_group(group), [], rows * cols, units)
+    _same(_quant_fold(gpu, *args2, dequant_dt=F16), _quant_fold(oracle, *args2, dequant_dt=F16))
+
+
+@pytest.mark.parametrize("dt", [F16, BF16])
+@pytest.mark.parametrize("rows,cols", [(5, 8192), (3, 28672), (7, 4096), (2, 1024), (9, 11008), (2, 40000)])
+@pytest.mark.parametrize("ddt", [F16, F32])
+def test_row_i8_with_dequant_fused(gpu, oracle, dt, rows, cols, ddt):
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((rows, cols)).astype(np.float32) * 0.02
+    x[1] = 0  # all-zero row: scale 1.0, zero point 0
+    x[0] *= 1e-3  # tiny scale: dequantized values reach the fp16 subnormal range
+    x = x.astype(np.float16) if dt == F16 else bf16_bits(x)
+    args = ((rows, cols), x, wl.spec_i8_sym(ddt), [], rows * cols, rows)
+    ref = _quant_fold(oracle, *args, want=("scales", "zps", "f16"), dequant_dt=ddt)
+    got = _quant_fold(gpu, *args, want=("scales", "zps", "f16"), dequant_dt=ddt)
+    assert gpu.last_stats.fused == 1
+    _same(got, ref)
+    # asymmetric u8 through the same kernel
+    args = ((rows, cols), x, wl.spec_u8_asym(), [], rows * cols, rows)
+    _same(_quant_fold(gpu, *args), _quant_fold(oracle, *args))
+
+
+@pytest.mark.parametrize("dt", [F32, F16, BF16])
+@pytest.mark.parametrize("shape,pad_oc,pad_ic", [((60, 64, 3, 3), 64, None), ((64, 3, 7, 7), None, 16),
+                                                 ((16, 8, 1, 1), None, None), ((5, 3, 3, 3), 8, 4),
+                                                 ((12, 512, 3, 3), None, None), ((1000, 2048, 1, 1), None, None)])
+@pytest.mark.parametrize("sym", [True, False])
+def test_conv_quantize_reorder_pad_fused(gpu, oracle, dt, shape, pad_oc, pad_ic, sym):
+    rng = np.random.default_rng(14)
+    x = rng.standard_normal(shape).astype(np.float32) * 0.05
+    x = x if dt == F32 else (x.astype(np.float16) if dt == F16 else bf16_bits(x))
+    ts, oshape = wl.conv_pipeline(shape, pad_oc, pad_ic)
+    spec = wl.spec_i8_sym() if sym else wl.spec_u8_asym()
+    args = (shape, x, spec, ts, int(np.prod(oshape)), shape[0])
+    ref = _quant_fold(oracle, *args)
+    got = _quant_fold(gpu, *args)
+    assert gpu.last_stats.fused == 1
+    _same(got, ref)
+    # the same pipeline through vf_row_stats + vf_fold (Quantize with explicit parameters, unfused)
+    t = TType(list(shape), dt)
+    c, keep = abi.make_content(t, x)
+    s, z, mn, mx = gpu.row_stats(c, spec, shape[0])
+    so, zo, mno, mxo = oracle.row_stats(c, spec, shape[0])
+    assert np.array_equal(s, so) and np.array_equal(z, zo) and np.array_equal(mn, mno) and np.array_equal(mx, mxo)
+    q = Elem.per_axis(spec.storage_dtype, F16, s, z, 0, spec.qmin, spec.qmax)
+    setup = ContentSetup(t).quantize(q).reorder(abi.ORDER_NHWC)
+    if len(ts) > 1:
+        setup = setup.padWithZero([0, 0, 0, 0], [oshape[0] - shape[0], oshape[1] - shape[1], 0, 0])
+    out = ContentAttr(x, t, setup).fold(gpu)
+    assert np.array_equal(out.bytes(), ref["codes"])
+
+
+def test_quantize_fold_unusual_range_takes_general_path(gpu, oracle):
+    """[-120, 120] is a range where fakeQuantize's tail is not the identity; the fused kernels decline it."""
+    rng = np.random.default_rng(15)
+    x = (rng.standard_normal((4, 2048)) * 0.02).astype(np.float16)
+    spec = wl.spec_i8_sym()
+    spec.qmin, spec.qmax = -120, 120
+    args = ((4, 2048), x, spec, [], 4 * 2048, 4)
+    got = _quant_fold(gpu, *args)
+    assert gpu.last_stats.fused == 0
+    _same(got, _quant_fold(oracle, *args))
+
+
+def test_weights_table_random(gpu, oracle):
+    rng = np.random.default_rng(16)
+    oc = 300
+    ws = rng.uniform(1e-4, 5e-2, oc)
+    bias = (rng.standard_normal(oc) * 0.01).astype(np.float32)
+    d, keep = wl.weights_table_desc(oc, ws, 576, bias)
+    assert np.array_equal(gpu.weights_table(d, oc), oracle.weights_table(d, oc))
+    counts = rng.integers(0, 577, oc).astype(np.int64)
+    d, keep = wl.weights_table_desc(oc, ws, 576, bias, sparse_counts=counts, sparsity_step=80)
+    tg, to = gpu.weights_table(d, oc), oracle.weights_table(d, oc)
+    assert np.array_equal(tg, to)
+    assert tg.reshape(oc, 4)[1, 0] == (counts[0] + 15) // 16 * 16
+    # float activations: column 2 is the fp32 bit pattern, bias divided by the weight scale in fp32
+    d = abi.WeightsTableDesc()
+    fe = Elem(F16)
+    we = Elem.per_axis(I8, F16, ws, np.zeros(oc), 0, -127, 127)
+    d.in_elem, d.out_elem, d.weights_elem, d.oc = fe.pod(), fe.pod(), we.pod(), oc
+    d.weights_ptr_step, d.sparsity_ptr_base = 64, abi.VF_SPARSITY_PTR_WHEN_NO_SPARSITY
+    d.has_bias, d.bias, d.bias_mem_kind = 1, bias.ctypes.data, abi.VF_MEM_HOST
+    assert np.array_equal(gpu.weights_table(d, oc), oracle.weights_table(d, oc))
+    # a scale above 2^15 needs a post-shift: rejected
+    d2, keep2 = wl.weights_table_desc(2, np.array([1e9, 1.0]), 16)
+    assert _status(lambda: gpu.weights_table(d2, 2)) == abi.VF_ERR_RANGE
+    assert _status(lambda: oracle.weights_table(d2, 2)) == abi.VF_ERR_RANGE
+    d3, keep3 = wl.weights_table_desc(2, np.array([1.0, 1.0]), 24)
+    assert _status(lambda: gpu.weights_table(d3, 2)) == abi.VF_ERR_ALIGNMENT
+    assert _status(lambda: oracle.weights_table(d3, 2)) == abi.VF_ERR_ALIGNMENT

@@ -1,0 +1,196 @@
+"""Host-side mirror of the reference's Const dialect builder API.
+
+`ContentSetup` collects a transformation list with the same method names and
+ordering rules as the reference's `Const::ContentSetup`
+(src/vpux_compiler/include/vpux/compiler/dialect/const/attributes/content.hpp:103-134,
+insertion rules src/vpux_compiler/src/dialect/const/attributes/content.cpp:530-588);
+`ContentAttr.fold()` hands base + list to a backend (`vpux_plugin_b200.lib.Library`
+for the GPU product) and returns the materialised bytes, i.e. fold() + copyTo().
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import abi
+from .abi import Elem, TType, Transform
+
+_NONE, _PREFERRED_LAST, _LAST = 0, 1, 2
+
+
+def _position(kind):
+    # attr_interfaces.hpp:24-28; BitPack is LAST (bit_pack.cpp:160-162), Sparsify / GetSparsityMap are
+    # PREFERRED_LAST (sparsify.cpp:209-211, get_sparsity_map.cpp:125-127)
+    if kind == abi.VF_T_BIT_PACK:
+        return _LAST
+    if kind in (abi.VF_T_SPARSIFY, abi.VF_T_GET_SPARSITY_MAP):
+        return _PREFERRED_LAST
+    return _NONE
+
+
+class ContentSetup:
+    def __init__(self, base_type, _items=None):
+        self.base_type = base_type
+        self._items = list(_items or [])  # (Transform, keepalive)
+
+    def clone(self):
+        return ContentSetup(self.base_type, self._items)
+
+    # -- insertion ---------------------------------------------------------------------------------
+    def _add(self, t, keep=None):
+        new = self.clone()
+        pos = len(new._items)
+        p = _position(t.kind)
+        # upper_bound on the position requirement keeps [NONE..., PREFERRED_LAST..., LAST...] stable
+        for i, (u, _) in enumerate(new._items):
+            if _position(u.kind) > p:
+                pos = i
+                break
+        new._items.insert(pos, (t, keep))
+        if len(new._items) >= 2 and _position(new._items[-2][0].kind) == _LAST:
+            raise ValueError("At most 1 attribute with LAST requirement allowed!")
+        return new
+
+    @staticmethod
+    def _t(kind):
+        t = Transform()
+        t.kind = kind
+        return t
+
+    def _with_elem(self, kind, elem):
+        elem = elem if isinstance(elem, Elem) else Elem(elem)
+        t = self._t(kind)
+        t.elem = elem.pod()
+        return self._add(t, elem)
+
+    # -- the reference's builder methods ----------------------------------------------------------
+    def castElemType(self, elem):
+        return self._with_elem(abi.VF_T_CAST_ELEM_TYPE, elem)
+
+    def convertElemType(self, elem):
+        return self._with_elem(abi.VF_T_CONVERT_ELEM_TYPE, elem)
+
+    def quantize(self, elem):
+        return self._with_elem(abi.VF_T_QUANTIZE, elem)
+
+    def dequantize(self):
+        return self._add(self._t(abi.VF_T_DEQUANTIZE))
+
+    def rescale(self, scale):
+        t = self._t(abi.VF_T_RESCALE)
+        t.value = float(scale)
+        return self._add(t)
+
+    def add(self, bias):
+        t = self._t(abi.VF_T_ADD)
+        t.value = float(bias)
+        return self._add(t)
+
+    def reshape(self, shape):
+        t = self._t(abi.VF_T_RESHAPE)
+        t.rank = len(shape)
+        for i, s in enumerate(shape):
+            t.a[i] = int(s)
+        return self._add(t)
+
+    def reorder(self, order):
+        t = self._t(abi.VF_T_REORDER)
+        t.order = int(order)
+        return self._add(t)
+
+    def transpose(self, order):
+        t = self._t(abi.VF_T_TRANSPOSE)
+        t.order = int(order)
+        return self._add(t)
+
+    def memPermute(self, dst_order, mem_perm):
+        t = self._t(abi.VF_T_MEM_PERMUTE)
+        t.order = int(dst_order)
+        t.mem_perm = int(mem_perm)
+        return self._add(t)
+
+    def layoutCast(self, order):
+        t = self._t(abi.VF_T_LAYOUT_CAST)
+        t.order = int(order)
+        return self._add(t)
+
+    def padWithZero(self, pad_before, pad_after):
+        if len(pad_before) != len(pad_after):
+            raise ValueError("Got non consistent 'padBefore' and 'padAfter' values in 'PadWithZeroAttr'")
+        t = self._t(abi.VF_T_PAD_WITH_ZERO)
+        t.rank = len(pad_before)
+        for i, (b, a) in enumerate(zip(pad_before, pad_after)):
+            t.a[i], t.b[i] = int(b), int(a)
+        return self._add(t)
+
+    def subview(self, offset, shape):
+        t = self._t(abi.VF_T_SUBVIEW)
+        t.rank = len(offset)
+        for i, (o, s) in enumerate(zip(offset, shape)):
+            t.a[i], t.b[i] = int(o), int(s)
+        return self._add(t)
+
+    def bitPack(self, width):
+        t = self._t(abi.VF_T_BIT_PACK)
+        t.width = int(width)
+        return self._add(t)
+
+    def getSparsityMap(self):
+        return self._add(self._t(abi.VF_T_GET_SPARSITY_MAP))
+
+    def sparsify(self, compress_output_type, num_actual_elements=None):
+        t = self._t(abi.VF_T_SPARSIFY)
+        t.compress_output = 1 if compress_output_type else 0
+        keep = None
+        if num_actual_elements is not None:
+            keep = np.ascontiguousarray(num_actual_elements, dtype=np.int64)
+            if (keep < 0).any():
+                raise ValueError("Got negative elem number value in 'numActualElements' for 'SparsifyAttr'")
+            t.num_actual = keep.ctypes.data_as(C.POINTER(C.c_int64))
+            t.n_num_actual = len(keep)
+        return self._add(t, keep)
+
+    # -- access ------------------------------------------------------------------------------------
+    def transforms(self):
+        return abi.make_transforms([t for t, _ in self._items]), len(self._items)
+
+    def names(self):
+        return [t.kind for t, _ in self._items]
+
+
+class Folded:
+    """Result of fold() + copyTo(): the folded type and the materialised bytes."""
+
+    def __init__(self, ttype, is_splat, raw, written):
+        self.type, self.is_splat, self.raw, self.written = ttype, is_splat, raw, written
+
+    def bytes(self):
+        return self.raw[:self.written]
+
+    def values(self, np_dtype=None):
+        dt = np_dtype or abi.DTYPE_NUMPY[self.type.elem.dtype]
+        return self.bytes().view(dt)
+
+
+class ContentAttr:
+    """base content + transformation list, as Const::ContentAttr (attributes/content.hpp)."""
+
+    def __init__(self, base, base_type, setup=None, is_splat=False, storage_dtype=None):
+        self.base = np.ascontiguousarray(base)
+        self.base_type = base_type
+        self.setup = setup if setup is not None else ContentSetup(base_type)
+        self.is_splat = bool(is_splat)
+        self.storage_dtype = storage_dtype if storage_dtype is not None else base_type.elem.dtype
+
+    def infer(self, backend):
+        tr, n = self.setup.transforms()
+        return backend.infer_type(self.base_type, self.is_splat, tr, n)
+
+    def fold(self, backend, dst_bytes=None):
+        tr, n = self.setup.transforms()
+        content, keep = abi.make_content(self.base_type, self.base, self.storage_dtype, self.is_splat)
+        out_type, out_splat, need = backend.infer_type(self.base_type, self.is_splat, tr, n)
+        cap = int(dst_bytes if dst_bytes is not None else need)
+        dst = np.zeros(max(cap, 1), dtype=np.uint8)
+        written, ftype = backend.fold(content, tr, n, dst, cap)
+        del keep
+        return Folded(ftype, out_splat, dst, written)

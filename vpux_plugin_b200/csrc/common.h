@@ -1,0 +1,211 @@
+// Shared host-side declarations of libvfold: status/exception plumbing, the host type model that mirrors
+// vpux::NDTypeInterface for the Const path, and the context.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/vfold.h"
+
+namespace vf {
+
+// ------------------------------------------------------------------------------------------------------
+// errors — reference VPUX_THROW sites become vf::Error(status, message); converted at the C boundary
+// ------------------------------------------------------------------------------------------------------
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string& m): std::runtime_error(m), code(c) {
+    }
+};
+
+[[noreturn]] void raise(int code, const char* fmt, ...);
+
+#define VF_CUDA(expr)                                                                                      \
+    do {                                                                                                   \
+        cudaError_t e_ = (expr);                                                                           \
+        if (e_ != cudaSuccess) {                                                                           \
+            ::vf::raise(e_ == cudaErrorMemoryAllocation ? VF_ERR_OOM : VF_ERR_CUDA, "%s failed: %s", #expr, \
+                        cudaGetErrorString(e_));                                                           \
+        }                                                                                                  \
+    } while (0)
+
+template <class F>
+int guard(char* err, size_t errlen, F&& body) {
+    try {
+        body();
+        if (err && errlen) err[0] = 0;
+        return VF_OK;
+    } catch (const Error& e) {
+        if (err && errlen) snprintf(err, errlen, "%s", e.what());
+        return e.code;
+    } catch (const std::exception& e) {
+        if (err && errlen) snprintf(err, errlen, "%s", e.what());
+        return VF_ERR_INVALID_ARG;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// dtypes
+// ------------------------------------------------------------------------------------------------------
+int dtype_bits(int dt);
+bool dtype_is_float(int dt);
+bool dtype_is_int(int dt);
+bool dtype_is_signed(int dt);
+void dtype_int_limits(int dt, double& lo, double& hi);
+
+inline int64_t align_up(int64_t v, int64_t a) {
+    return (v + a - 1) / a * a;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// host type model
+// ------------------------------------------------------------------------------------------------------
+struct Elem {
+    int kind = VF_ELEM_PLAIN;
+    int dtype = VF_DT_INVALID;
+    int expressed = VF_DT_INVALID;
+    int axis = -1;
+    int64_t qmin = 0, qmax = 0;
+    std::vector<double> scales;
+    std::vector<int64_t> zps;
+    bool quantized() const {
+        return kind != VF_ELEM_PLAIN;
+    }
+    static Elem plain(int dt) {
+        Elem e;
+        e.dtype = dt;
+        return e;
+    }
+    static Elem from(const vf_elem_type& e);
+    bool single_zp(int64_t& zp) const;  // extractSingleZeroPoint
+};
+
+struct Type {
+    Elem elem;
+    int rank = 0;
+    uint32_t order = 0;
+    int64_t shape[VF_MAX_RANK] = {0, 0, 0, 0, 0};
+
+    static Type from(const vf_tensor_type& t);
+    int64_t numel() const;
+    uint64_t alloc_bytes() const;            // getTotalAllocSize of the compact tensor
+    void perm(int* p) const;                 // p[memDim] = logical dim
+    void mem_shape(int64_t* ms) const;       // shape in memory order
+    void export_to(vf_tensor_type* out, double* sb, int64_t* zb, int64_t cap) const;
+};
+
+uint32_t identity_order(int rank);
+void order_to_perm(uint32_t order, int rank, int* perm);
+
+// inferOutputType / inferOutputSplat of one transformation (pure host)
+Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_splat);
+void check_positions(const vf_transform* t, int n);
+Type compress_type(const Type& in, const int64_t* counts, int64_t n);
+
+// calcScaleAndZeroPoint on the host (used for validation of tiny inputs and by tests of the planner)
+bool calc_scale_zp_host(double qmin, double qmax, double rmin, double rmax, double& scale, int64_t& zp);
+
+}  // namespace vf
+
+// ------------------------------------------------------------------------------------------------------
+// context
+// ------------------------------------------------------------------------------------------------------
+struct vf_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    uint64_t staging_bytes = 0;
+    void* staging[2] = {nullptr, nullptr};  // pinned bounce buffers for pageable host memory
+    cudaEvent_t staging_ev[2] = {nullptr, nullptr};
+    int* d_flags = nullptr;  // device error flags (see VF_FLAG_* in device_utils.cuh)
+    int* h_flags = nullptr;  // pinned mirror
+    uint64_t launches = 0;
+    int32_t opt_flags = 0;
+    bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device
+    std::mutex mu;  // serialises calls on this context
+};
+
+namespace vf {
+
+constexpr int kNumFlags = 8;
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// Stream-ordered scratch allocation from the device's memory pool.
+void* dalloc(vf_ctx* ctx, size_t bytes);
+void dfree(vf_ctx* ctx, void* p);
+
+struct DBuf {  // RAII scratch buffer
+    vf_ctx* ctx = nullptr;
+    void* p = nullptr;
+    size_t bytes = 0;
+    DBuf() = default;
+    DBuf(vf_ctx* c, size_t n): ctx(c), p(n ? dalloc(c, n) : nullptr), bytes(n) {
+    }
+    DBuf(const DBuf&) = delete;
+    DBuf& operator=(const DBuf&) = delete;
+    DBuf(DBuf&& o) noexcept: ctx(o.ctx), p(o.p), bytes(o.bytes) {
+        o.p = nullptr;
+    }
+    DBuf& operator=(DBuf&& o) noexcept {
+        if (this != &o) {
+            reset();
+            ctx = o.ctx;
+            p = o.p;
+            bytes = o.bytes;
+            o.p = nullptr;
+        }
+        return *this;
+    }
+    ~DBuf() {
+        reset();
+    }
+    void reset() {
+        if (p) dfree(ctx, p);
+        p = nullptr;
+    }
+    template <class T>
+    T* as() const {
+        return static_cast<T*>(p);
+    }
+};
+
+// host <-> device transfers that honour the memory kind of the host side
+void copy_in(vf_ctx* ctx, void* dst_dev, const void* src, size_t bytes, int src_kind);
+void copy_out(vf_ctx* ctx, void* dst, int dst_kind, const void* src_dev, size_t bytes);
+void flags_clear(vf_ctx* ctx);
+// synchronises the stream and raises if a kernel recorded an error
+void flags_check(vf_ctx* ctx);
+
+// Device-resident Const::Content
+struct DContent {
+    Type type;
+    int storage = VF_DT_INVALID;
+    bool splat = false;
+    const void* d = nullptr;  // device pointer (borrowed or owned by `own`)
+    uint64_t nbytes = 0;
+    DBuf own;
+    int64_t count() const {
+        return splat ? 1 : type.numel();
+    }
+};
+
+}  // namespace vf

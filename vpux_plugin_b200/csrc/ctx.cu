@@ -1,0 +1,169 @@
+// Context: one device, one stream, stream-ordered scratch from the device memory pool, pinned bounce
+// buffers for pageable host memory, and the device-side error flags.
+#include <algorithm>
+
+#include "common.h"
+
+namespace vf {
+
+void* dalloc(vf_ctx* ctx, size_t bytes) {
+    void* p = nullptr;
+    VF_CUDA(cudaMallocAsync(&p, bytes ? bytes : 1, ctx->stream));
+    return p;
+}
+
+void dfree(vf_ctx* ctx, void* p) {
+    if (p) cudaFreeAsync(p, ctx->stream);
+}
+
+// Pageable host memory goes through two pinned bounce buffers so the copy engine and the host memcpy
+// overlap; pinned and device memory are handed to the copy engine directly.
+void copy_in(vf_ctx* ctx, void* dst_dev, const void* src, size_t bytes, int src_kind) {
+    if (!bytes) return;
+    if (src_kind == VF_MEM_DEVICE) {
+        VF_CUDA(cudaMemcpyAsync(dst_dev, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        return;
+    }
+    if (src_kind == VF_MEM_HOST_PINNED) {
+        VF_CUDA(cudaMemcpyAsync(dst_dev, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        return;
+    }
+    size_t off = 0;
+    int k = 0;
+    while (off < bytes) {
+        const size_t n = std::min<size_t>(ctx->staging_bytes, bytes - off);
+        VF_CUDA(cudaEventSynchronize(ctx->staging_ev[k]));  // previous use of this bounce buffer is done
+        std::memcpy(ctx->staging[k], static_cast<const char*>(src) + off, n);
+        VF_CUDA(cudaMemcpyAsync(static_cast<char*>(dst_dev) + off, ctx->staging[k], n, cudaMemcpyHostToDevice, ctx->stream));
+        VF_CUDA(cudaEventRecord(ctx->staging_ev[k], ctx->stream));
+        off += n;
+        k ^= 1;
+    }
+}
+
+void copy_out(vf_ctx* ctx, void* dst, int dst_kind, const void* src_dev, size_t bytes) {
+    if (!bytes) return;
+    if (dst_kind == VF_MEM_DEVICE) {
+        VF_CUDA(cudaMemcpyAsync(dst, src_dev, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        return;
+    }
+    if (dst_kind == VF_MEM_HOST_PINNED) {
+        VF_CUDA(cudaMemcpyAsync(dst, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        return;
+    }
+    size_t off = 0;
+    int k = 0;
+    size_t pending_off[2] = {0, 0}, pending_n[2] = {0, 0};
+    while (off < bytes || pending_n[0] || pending_n[1]) {
+        if (pending_n[k]) {  // drain the older transfer of this bounce buffer
+            VF_CUDA(cudaEventSynchronize(ctx->staging_ev[k]));
+            std::memcpy(static_cast<char*>(dst) + pending_off[k], ctx->staging[k], pending_n[k]);
+            pending_n[k] = 0;
+        }
+        if (off < bytes) {
+            const size_t n = std::min<size_t>(ctx->staging_bytes, bytes - off);
+            VF_CUDA(cudaMemcpyAsync(ctx->staging[k], static_cast<const char*>(src_dev) + off, n, cudaMemcpyDeviceToHost, ctx->stream));
+            VF_CUDA(cudaEventRecord(ctx->staging_ev[k], ctx->stream));
+            pending_off[k] = off;
+            pending_n[k] = n;
+            off += n;
+        }
+        k ^= 1;
+    }
+}
+
+void flags_clear(vf_ctx* ctx) {
+    VF_CUDA(cudaMemsetAsync(ctx->d_flags, 0, sizeof(int) * kNumFlags, ctx->stream));
+}
+
+void flags_check(vf_ctx* ctx) {
+    VF_CUDA(cudaMemcpyAsync(ctx->h_flags, ctx->d_flags, sizeof(int) * kNumFlags, cudaMemcpyDeviceToHost, ctx->stream));
+    VF_CUDA(cudaStreamSynchronize(ctx->stream));
+    VF_CUDA(cudaGetLastError());
+    const int* f = ctx->h_flags;
+    if (f[0]) raise(VF_ERR_CHECKED_CAST, "Can not safely cast a value to the destination element type");
+    if (f[1]) raise(VF_ERR_QUANT_RANGE, "calcScaleAndZeroPoint failed: range without zero or scale too small");
+    if (f[2]) raise(VF_ERR_SHAPE, "numActualElements smaller than the number of non-sparse elements");
+    if (f[3]) raise(VF_ERR_RANGE, "weights table: scale needs a post-shift or rescaled bias is out of range");
+    if (f[4]) raise(VF_ERR_ALIGNMENT, "weights table: pointer must be a multiple of 16");
+}
+
+}  // namespace vf
+
+extern "C" {
+
+int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_ctx** out, char* err, size_t errlen) {
+    return vf::guard(err, errlen, [&] {
+        if (!out) vf::raise(VF_ERR_INVALID_ARG, "out is NULL");
+        *out = nullptr;
+        int ndev = 0;
+        if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+            cudaGetLastError();
+            vf::raise(VF_ERR_NO_DEVICE, "no CUDA device available: this library has no CPU path");
+        }
+        if (device < 0 || device >= ndev) vf::raise(VF_ERR_NO_DEVICE, "device %d outside 0..%d", device, ndev - 1);
+        vf::DeviceGuard g(device);
+        vf_ctx* c = new vf_ctx();
+        try {
+            c->device = device;
+            if (external_stream) {
+                c->stream = static_cast<cudaStream_t>(external_stream);
+            } else {
+                VF_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+                c->own_stream = true;
+            }
+            c->opt_flags = opts ? opts->flags : 0;
+            c->staging_bytes = (opts && opts->staging_bytes) ? opts->staging_bytes : (64ull << 20);
+            for (int k = 0; k < 2; ++k) {
+                VF_CUDA(cudaMallocHost(&c->staging[k], c->staging_bytes));
+                VF_CUDA(cudaEventCreateWithFlags(&c->staging_ev[k], cudaEventDisableTiming));
+            }
+            VF_CUDA(cudaMalloc(&c->d_flags, sizeof(int) * vf::kNumFlags));
+            VF_CUDA(cudaMallocHost(&c->h_flags, sizeof(int) * vf::kNumFlags));
+            VF_CUDA(cudaMemset(c->d_flags, 0, sizeof(int) * vf::kNumFlags));
+            // keep freed scratch cached in the pool instead of returning it to the driver on every sync
+            cudaMemPool_t pool;
+            VF_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
+            uint64_t thr = UINT64_MAX;
+            VF_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr));
+        } catch (...) {
+            vf_ctx_destroy(c);
+            throw;
+        }
+        *out = c;
+    });
+}
+
+void vf_ctx_destroy(vf_ctx* c) {
+    if (!c) return;
+    vf::DeviceGuard g(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    for (int k = 0; k < 2; ++k) {
+        if (c->staging[k]) cudaFreeHost(c->staging[k]);
+        if (c->staging_ev[k]) cudaEventDestroy(c->staging_ev[k]);
+    }
+    if (c->d_flags) cudaFree(c->d_flags);
+    if (c->h_flags) cudaFreeHost(c->h_flags);
+    if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+int vf_ctx_synchronize(vf_ctx* c, char* err, size_t errlen) {
+    return vf::guard(err, errlen, [&] {
+        if (!c) vf::raise(VF_ERR_INVALID_ARG, "ctx is NULL");
+        vf::DeviceGuard g(c->device);
+        VF_CUDA(cudaStreamSynchronize(c->stream));
+    });
+}
+
+void* vf_ctx_stream(vf_ctx* c) {
+    return c ? c->stream : nullptr;
+}
+int vf_ctx_device(vf_ctx* c) {
+    return c ? c->device : -1;
+}
+uint64_t vf_ctx_launch_count(vf_ctx* c) {
+    return c ? c->launches : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,903 @@
+// Fold executor: Const::ContentAttr::fold() + Const::Content::copyTo() on the device
+// (attributes/content.cpp:371-397, utils/content.cpp:161-184), plus the remaining C entry points.
+#include <algorithm>
+#include <cmath>
+
+#include "kernels.h"
+
+namespace vf {
+
+namespace {
+
+void strides_of(const int64_t* shape, int rank, int64_t* st) {
+    int64_t s = 1;
+    for (int i = rank - 1; i >= 0; --i) {
+        st[i] = s;
+        s *= shape[i];
+    }
+}
+
+template <class T>
+DBuf upload_vec(vf_ctx* ctx, const std::vector<T>& v) {
+    DBuf b(ctx, v.size() * sizeof(T));
+    copy_in(ctx, b.p, v.data(), v.size() * sizeof(T), VF_MEM_HOST);
+    return b;
+}
+
+// wrapBaseContent (attributes/content.cpp:310-318): device memory is borrowed, host memory is uploaded
+DContent upload_base(vf_ctx* ctx, const vf_content& b, vf_stats* stats) {
+    DContent c;
+    c.type = Type::from(b.type);
+    c.storage = b.storage_dtype;
+    c.splat = b.is_splat != 0;
+    const uint64_t need = (uint64_t(dtype_bits(c.storage)) * uint64_t(c.count()) + 7u) / 8u;
+    if (!b.data || b.nbytes < need) raise(VF_ERR_SHAPE, "base buffer holds %llu bytes, %llu needed", (unsigned long long)b.nbytes, (unsigned long long)need);
+    c.nbytes = need;
+    if (b.mem_kind == VF_MEM_DEVICE) {
+        c.d = b.data;
+    } else {
+        c.own = DBuf(ctx, need);
+        copy_in(ctx, c.own.p, b.data, need, b.mem_kind);
+        c.d = c.own.p;
+        if (stats) stats->h2d_bytes += need;
+    }
+    if (stats) stats->bytes_in += need;
+    return c;
+}
+
+DContent alloc_like(vf_ctx* ctx, const Type& type, int storage, bool splat, int64_t raw_bytes = -1) {
+    DContent c;
+    c.type = type;
+    c.storage = storage;
+    c.splat = splat;
+    c.nbytes = raw_bytes >= 0 ? uint64_t(raw_bytes) : (uint64_t(dtype_bits(storage)) * uint64_t(c.count()) + 7u) / 8u;
+    c.own = DBuf(ctx, c.nbytes);
+    c.d = c.own.p;
+    return c;
+}
+
+void axis_sizes(const Type& t, int axis, int64_t& outer, int64_t& axis_size, int64_t& inner) {
+    int p[VF_MAX_RANK];
+    int64_t ms[VF_MAX_RANK];
+    t.perm(p);
+    t.mem_shape(ms);
+    int m = 0;
+    for (int i = 0; i < t.rank; ++i)
+        if (p[i] == axis) m = i;
+    inner = 1;
+    for (int i = m + 1; i < t.rank; ++i) inner *= ms[i];
+    axis_size = ms[m];
+    if (inner == 0) raise(VF_ERR_SHAPE, "Inner size is zero");
+    if (axis_size == 0) raise(VF_ERR_SHAPE, "Quantized axis size is zero");
+    outer = t.numel() / (axis_size * inner);
+    if (outer == 0) raise(VF_ERR_SHAPE, "Outer size is zero");
+}
+
+// ---- host conversions of a zero point into a storage element (Content::fillWithZero) -----------------
+uint16_t host_f32_to_f16(float f) {  // IEEE round-to-nearest-even; zero points are small integers
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    const uint32_t sign = (u >> 16) & 0x8000u;
+    const int32_t e = int32_t((u >> 23) & 0xFF) - 127 + 15;
+    uint32_t m = u & 0x7FFFFFu;
+    if (((u >> 23) & 0xFF) == 0xFF) return uint16_t(sign | 0x7C00u | (m ? 0x200u : 0));
+    if (e >= 31) return uint16_t(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return uint16_t(sign);
+        m |= 0x800000u;
+        const int sh = 14 - e;
+        uint32_t r = m >> sh;
+        const uint32_t rem = m & ((1u << sh) - 1), half = 1u << (sh - 1);
+        if (rem > half || (rem == half && (r & 1))) ++r;
+        return uint16_t(sign | r);
+    }
+    uint32_t r = (uint32_t(e) << 10) | (m >> 13);
+    const uint32_t rem = m & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (r & 1))) ++r;
+    return uint16_t(sign | r);
+}
+
+void zp_to_storage(int storage, int64_t zp, uint8_t* out) {
+    switch (storage) {
+    case VF_DT_F32: {
+        const float f = float(zp);
+        if (int64_t(f) != zp) raise(VF_ERR_CHECKED_CAST, "zero point %lld is not representable in f32", (long long)zp);
+        std::memcpy(out, &f, 4);
+        return;
+    }
+    case VF_DT_F16: {
+        const uint16_t h = host_f32_to_f16(float(zp));
+        std::memcpy(out, &h, 2);
+        return;
+    }
+    case VF_DT_BF16: {
+        const float f = float(zp);
+        uint32_t u;
+        std::memcpy(&u, &f, 4);
+        const uint16_t h = uint16_t((u + ((u & 0x00010000u) >> 1)) >> 16);
+        std::memcpy(out, &h, 2);
+        return;
+    }
+    default: {
+        double lo, hi;
+        dtype_int_limits(storage, lo, hi);
+        if (double(zp) < lo || double(zp) > hi) raise(VF_ERR_CHECKED_CAST, "zero point %lld outside the storage type", (long long)zp);
+        std::memcpy(out, &zp, size_t(dtype_bits(storage) / 8));  // little endian
+    }
+    }
+}
+
+// getSparsifyValue — utils/sparsity.cpp:12-26
+int64_t sparsify_value(const Elem& e) {
+    if (!e.quantized()) return 0;
+    int64_t zp;
+    if (!e.single_zp(zp)) raise(VF_ERR_ZERO_POINTS, "Not all zero-points are equal");
+    return zp;
+}
+
+void check_sparse_dtype(int dt) {
+    if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32)
+        raise(VF_ERR_UNSUPPORTED, "Unexpected weights data type: %d", dt);
+}
+
+// the view getValues<LogicalT>() gives: a dense buffer in the logical element type
+DContent materialise_logical(vf_ctx* ctx, DContent& in) {
+    const int dt = in.type.elem.dtype;
+    if (in.storage == dt && !in.splat) {
+        DContent v;
+        v.type = in.type;
+        v.storage = dt;
+        v.d = in.d;
+        v.nbytes = in.nbytes;
+        return v;
+    }
+    DContent v = alloc_like(ctx, in.type, dt, false);
+    launch_convert(ctx, in.d, in.storage, in.splat, v.own.p, dt, in.type.numel());
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// one transformation
+// ------------------------------------------------------------------------------------------------------
+DContent move_buffer(DContent& in, const Type& t) {  // Content::moveBuffer
+    DContent out = std::move(in);
+    out.type = t;
+    return out;
+}
+
+DContent do_quantize(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const Elem q = Elem::from(t.elem);
+    const bool per_axis = q.kind == VF_ELEM_QUANT_PER_AXIS;
+    DContent out = alloc_like(ctx, ot, q.dtype, per_axis ? false : in.splat);
+    int64_t axis_size = 1, inner = 1, outer = 1;
+    if (per_axis) {
+        axis_sizes(in.type, q.axis, outer, axis_size, inner);
+        if (int64_t(q.scales.size()) != axis_size) raise(VF_ERR_SHAPE, "Wrong scales size '%zu', expected '%lld'", q.scales.size(), (long long)axis_size);
+        if (int64_t(q.zps.size()) != axis_size) raise(VF_ERR_SHAPE, "Wrong zeroPoints size '%zu', expected '%lld'", q.zps.size(), (long long)axis_size);
+    }
+    DBuf ds = upload_vec(ctx, q.scales), dz = upload_vec(ctx, q.zps);
+    launch_quantize(ctx, in.d, in.storage, in.splat, out.own.p, q.dtype, out.count(), ds.as<double>(), dz.as<int64_t>(),
+                    axis_size, inner, q.qmin, q.qmax);
+    return out;
+}
+
+DContent do_dequantize(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const Elem& q = in.type.elem;
+    DContent out = alloc_like(ctx, ot, VF_DT_F32, os);
+    int64_t axis_size = 1, inner = 1, outer = 1;
+    if (q.kind == VF_ELEM_QUANT_PER_AXIS) {
+        axis_sizes(in.type, q.axis, outer, axis_size, inner);
+        if (int64_t(q.scales.size()) != axis_size || int64_t(q.zps.size()) != axis_size) raise(VF_ERR_SHAPE, "Wrong scales size");
+    }
+    DBuf ds = upload_vec(ctx, q.scales), dz = upload_vec(ctx, q.zps);
+    launch_dequantize(ctx, in.d, in.storage, in.splat, out.own.as<float>(), out.count(), ds.as<double>(),
+                      dz.as<int64_t>(), axis_size, inner);
+    return out;
+}
+
+DContent do_rescale_add(vf_ctx* ctx, DContent& in, const Type& ot, double value, bool is_add) {
+    DContent out = alloc_like(ctx, ot, VF_DT_F32, in.splat);
+    launch_rescale_add(ctx, in.d, in.storage, in.splat, out.own.as<float>(), out.count(), float(value), is_add);
+    return out;
+}
+
+DContent do_convert(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const Elem &qi = in.type.elem, &qo = ot.elem;
+    if (qi.quantized() && qo.quantized()) {
+        // getValueRangeOffset — utils/transformations.cpp:863-881
+        int64_t zi, zo;
+        if (!dtype_is_int(qi.dtype) || !dtype_is_int(qo.dtype) || dtype_bits(qi.dtype) != dtype_bits(qo.dtype) ||
+            !qi.single_zp(zi) || !qo.single_zp(zo))
+            raise(VF_ERR_UNSUPPORTED, "Unsupported conversion between quantized types");
+        return do_rescale_add(ctx, in, ot, double(zo - zi), true);
+    }
+    raise(VF_ERR_UNSUPPORTED, "Unsupported conversion: only quantized -> quantized is implemented");
+}
+
+DContent do_permute(vf_ctx* ctx, DContent& in, const Type& ot, const int* mp) {
+    const int rank = in.type.rank;
+    bool ident = true;
+    for (int i = 0; i < rank; ++i) ident &= mp[i] == i;
+    if (in.splat || ident) return move_buffer(in, ot);
+    const int bits = dtype_bits(in.storage);
+    if (bits < 8) raise(VF_ERR_UNSUPPORTED, "memory permutation of sub-byte storage");
+    DContent out = alloc_like(ctx, ot, in.storage, false);
+    if (out.nbytes != in.nbytes) raise(VF_ERR_SHAPE, "Storage buffer size mismatch in 'memPermuteTransformation'");
+    Geom g{};
+    g.rank = rank;
+    int64_t ims[VF_MAX_RANK], ist[VF_MAX_RANK];
+    in.type.mem_shape(ims);
+    strides_of(ims, rank, ist);
+    for (int i = 0; i < rank; ++i) {
+        g.in_shape[i] = ims[i];
+        g.out_shape[i] = ims[mp[i]];
+        g.src_stride[i] = ist[mp[i]];
+    }
+    launch_permute(ctx, in.d, out.own.p, g, bits / 8);
+    return out;
+}
+
+DContent do_reorder(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    int ip[VF_MAX_RANK], op[VF_MAX_RANK], mp[VF_MAX_RANK];
+    in.type.perm(ip);
+    ot.perm(op);
+    for (int i = 0; i < ot.rank; ++i)
+        for (int j = 0; j < ot.rank; ++j)
+            if (ip[j] == op[i]) mp[i] = j;
+    return do_permute(ctx, in, ot, mp);
+}
+
+DContent do_transpose(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    int mp[VF_MAX_RANK];
+    if (t.kind == VF_T_MEM_PERMUTE) {
+        order_to_perm(t.mem_perm, in.type.rank, mp);
+    } else {
+        int ip[VF_MAX_RANK], p[VF_MAX_RANK];
+        in.type.perm(ip);
+        order_to_perm(t.order, in.type.rank, p);
+        for (int i = 0; i < in.type.rank; ++i) {
+            const int in_logical = p[ip[i]];
+            for (int j = 0; j < in.type.rank; ++j)
+                if (ip[j] == in_logical) mp[i] = j;
+        }
+    }
+    return do_permute(ctx, in, ot, mp);
+}
+
+DContent do_pad(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const int bits = dtype_bits(in.storage);
+    if (bits < 8) raise(VF_ERR_UNSUPPORTED, "PadWithZero of sub-byte storage");
+    const int es = bits / 8;
+    DContent out = alloc_like(ctx, ot, in.storage, false);
+    const int rank = in.type.rank;
+    int p[VF_MAX_RANK];
+    int64_t ims[VF_MAX_RANK], oms[VF_MAX_RANK], ist[VF_MAX_RANK];
+    in.type.perm(p);
+    in.type.mem_shape(ims);
+    ot.mem_shape(oms);
+    strides_of(ims, rank, ist);
+    Geom g{};
+    g.rank = rank;
+    for (int i = 0; i < rank; ++i) {
+        g.in_shape[i] = ims[i];
+        g.out_shape[i] = oms[i];
+        g.src_stride[i] = ist[i];
+        g.offset[i] = t.a[p[i]];
+    }
+    // fill values — Content::fillWithZero, utils/content.cpp:190-237
+    std::vector<uint8_t> fill;
+    int64_t n_fill = 1;
+    int fill_dim = 0;
+    const Elem& e = ot.elem;
+    if (e.kind == VF_ELEM_QUANT_PER_AXIS) {
+        if (ot.rank != 4) raise(VF_ERR_UNSUPPORTED, "Unsupported shape size %d", ot.rank);
+        if (e.axis != 0) raise(VF_ERR_UNSUPPORTED, "Only per-channel quantization is supported");
+        n_fill = ot.shape[0];
+        fill.assign(size_t(n_fill) * es, 0);
+        for (int64_t i = 0; i < n_fill; ++i) zp_to_storage(in.storage, e.zps[size_t(i)], fill.data() + i * es);
+        for (int i = 0; i < rank; ++i)
+            if (p[i] == 0) fill_dim = i;
+    } else if (e.kind == VF_ELEM_QUANT_UNIFORM) {
+        fill.assign(size_t(es), 0);
+        zp_to_storage(in.storage, e.zps[0], fill.data());
+    } else {
+        fill.assign(size_t(es), 0);
+    }
+    DBuf dfill = upload_vec(ctx, fill);
+    launch_pad(ctx, in.d, in.splat, out.own.p, g, es, dfill.p, n_fill, fill_dim);
+    return out;
+}
+
+DContent do_subview(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    if (in.splat) return move_buffer(in, ot);
+    const int bits = dtype_bits(in.storage);
+    if (bits < 8) raise(VF_ERR_UNSUPPORTED, "SubView of sub-byte storage");
+    DContent out = alloc_like(ctx, ot, in.storage, false);
+    const int rank = in.type.rank;
+    int p[VF_MAX_RANK];
+    int64_t ims[VF_MAX_RANK], oms[VF_MAX_RANK], ist[VF_MAX_RANK];
+    in.type.perm(p);
+    in.type.mem_shape(ims);
+    ot.mem_shape(oms);
+    strides_of(ims, rank, ist);
+    Geom g{};
+    g.rank = rank;
+    for (int i = 0; i < rank; ++i) {
+        g.in_shape[i] = ims[i];
+        g.out_shape[i] = oms[i];
+        g.src_stride[i] = ist[i];
+        g.offset[i] = t.a[p[i]];
+    }
+    launch_subview(ctx, in.d, out.own.p, g, bits / 8);
+    return out;
+}
+
+DContent do_bitpack(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    if (in.splat) raise(VF_ERR_SPLAT, "Bit pack does not support splat inputs.");
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const int64_t n = in.type.numel();
+    if (n % 2 != 0) raise(VF_ERR_ODD_COUNT, "Storage buffer size is odd, which is unexpected for 4 bit packing.");
+    if (dtype_bits(in.storage) < 8) raise(VF_ERR_UNSUPPORTED, "BitPack of sub-byte storage");
+    DContent out = alloc_like(ctx, ot, VF_DT_U8, false, int64_t(ot.alloc_bytes()));
+    launch_bitpack4(ctx, in.d, in.storage, out.own.as<uint8_t>(), n);
+    return out;
+}
+
+DContent do_sparsity_map(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    check_sparse_dtype(in.type.elem.dtype);
+    const int64_t sv = sparsify_value(in.type.elem);
+    const int64_t work = in.type.shape[1] * in.type.shape[2] * in.type.shape[3];
+    if (work % 8 != 0) raise(VF_ERR_SHAPE, "GetSparsityMap needs IC*KY*KX (%lld) to be a multiple of 8", (long long)work);
+    DContent v = materialise_logical(ctx, in);
+    DContent out = alloc_like(ctx, ot, VF_DT_I1, false);
+    launch_sparsity_scan(ctx, v.d, v.storage, ot.shape[0], work, sv, nullptr, out.own.as<uint8_t>(), ot.shape[3] / 8);
+    return out;
+}
+
+// Sparsify — attributes/sparsify.cpp:163-203. The folded content always carries the compressed type.
+DContent do_sparsify(vf_ctx* ctx, DContent& in, const vf_transform& t, DBuf* keep_counts = nullptr) {
+    if (in.type.rank != 4) raise(VF_ERR_SHAPE, "Expected 4D input shape");
+    const int dt = in.type.elem.dtype;
+    check_sparse_dtype(dt);
+    const int es = dtype_bits(dt) / 8;
+    const int64_t sv = sparsify_value(in.type.elem);
+    if ((dt == VF_DT_I8 && (sv < -128 || sv > 127)) || (dt == VF_DT_U8 && (sv < 0 || sv > 255)))
+        raise(VF_ERR_CHECKED_CAST, "sparsify value %lld outside the element type", (long long)sv);
+    const int64_t oc = in.type.shape[0], work = in.type.shape[1] * in.type.shape[2] * in.type.shape[3];
+    DContent v = materialise_logical(ctx, in);
+
+    DBuf counts(ctx, size_t(oc) * 8), offsets(ctx, size_t(oc + 1) * 8);
+    launch_sparsity_scan(ctx, v.d, dt, oc, work, sv, counts.as<int64_t>(), nullptr, 0);
+    launch_sparse_offsets(ctx, counts.as<int64_t>(), oc, es, offsets.as<int64_t>());
+
+    uint64_t capacity;
+    Type ot;
+    const bool supplied = t.num_actual != nullptr;
+    if (supplied) {
+        if (t.n_num_actual != oc) raise(VF_ERR_SHAPE, "numActualElements has %lld entries for %lld channels", (long long)t.n_num_actual, (long long)oc);
+        ot = compress_type(in.type, t.num_actual, t.n_num_actual);
+        capacity = uint64_t(ot.shape[0]);
+    } else {
+        capacity = uint64_t(oc) * uint64_t(align_up(work * es, 16));
+    }
+    DBuf data(ctx, capacity ? capacity : 1);
+    if (supplied) VF_CUDA(cudaMemsetAsync(data.p, 0, capacity, ctx->stream));
+    launch_sparse_compact(ctx, v.d, dt, oc, work, sv, offsets.as<int64_t>(), data.as<uint8_t>(), capacity);
+    if (!supplied) {
+        int64_t total = 0;
+        VF_CUDA(cudaMemcpyAsync(&total, offsets.as<int64_t>() + oc, 8, cudaMemcpyDeviceToHost, ctx->stream));
+        VF_CUDA(cudaStreamSynchronize(ctx->stream));
+        ot = Type();
+        ot.rank = 4;
+        ot.order = in.type.order;
+        ot.shape[0] = total;
+        ot.shape[1] = ot.shape[2] = ot.shape[3] = 1;
+        ot.elem = Elem::plain(VF_DT_U8);
+    }
+    DContent out;
+    out.type = ot;
+    out.storage = VF_DT_U8;
+    out.splat = false;
+    out.nbytes = uint64_t(ot.shape[0]);
+    out.own = std::move(data);
+    out.d = out.own.p;
+    if (keep_counts) *keep_counts = std::move(counts);
+    return out;
+}
+
+DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    switch (t.kind) {
+    case VF_T_CAST_ELEM_TYPE:
+    case VF_T_RESHAPE:
+    case VF_T_LAYOUT_CAST: {
+        const Type ot = infer_one(in.type, in.splat, t, os);
+        return move_buffer(in, ot);
+    }
+    case VF_T_CONVERT_ELEM_TYPE: return do_convert(ctx, in, t);
+    case VF_T_DEQUANTIZE: return do_dequantize(ctx, in, t);
+    case VF_T_QUANTIZE: return do_quantize(ctx, in, t);
+    case VF_T_RESCALE: return do_rescale_add(ctx, in, in.type, t.value, false);
+    case VF_T_ADD: return do_rescale_add(ctx, in, in.type, t.value, true);
+    case VF_T_REORDER: return do_reorder(ctx, in, t);
+    case VF_T_MEM_PERMUTE:
+    case VF_T_TRANSPOSE: return do_transpose(ctx, in, t);
+    case VF_T_PAD_WITH_ZERO: return do_pad(ctx, in, t);
+    case VF_T_SUBVIEW: return do_subview(ctx, in, t);
+    case VF_T_BIT_PACK: return do_bitpack(ctx, in, t);
+    case VF_T_GET_SPARSITY_MAP: return do_sparsity_map(ctx, in, t);
+    case VF_T_SPARSIFY: return do_sparsify(ctx, in, t);
+    default: raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
+    }
+}
+
+// Content::copyTo — utils/content.cpp:161-184 (+ copySubByteContent :101-155)
+uint64_t copy_to(vf_ctx* ctx, DContent& c, void* dst, uint64_t dst_bytes, int dst_kind, vf_stats* stats) {
+    const int edt = c.type.elem.dtype;
+    const int bits = dtype_bits(edt);
+    const bool to_dev = dst_kind == VF_MEM_DEVICE;
+    uint64_t written = 0;
+    auto emit = [&](const void* dev_src, uint64_t n) {  // result already in a device buffer
+        copy_out(ctx, dst, dst_kind, dev_src, n);
+        if (!to_dev && stats) stats->d2h_bytes += n;
+        written = n;
+    };
+    if (!dst && dst_bytes) raise(VF_ERR_INVALID_ARG, "dst is NULL");
+    if (bits < 8) {
+        if (c.splat) {
+            // every byte repeats the sub-byte value; read it on the host (one element)
+            uint8_t raw[8] = {0};
+            VF_CUDA(cudaMemcpyAsync(raw, c.d, size_t(std::max(1, dtype_bits(c.storage) / 8)), cudaMemcpyDeviceToHost, ctx->stream));
+            VF_CUDA(cudaStreamSynchronize(ctx->stream));
+            uint8_t sub;
+            if (c.storage == VF_DT_I1) {
+                sub = raw[0] & 1;
+            } else {
+                DBuf one(ctx, 1);
+                launch_convert(ctx, c.d, c.storage, true, one.p, VF_DT_I8, 1);
+                VF_CUDA(cudaMemcpyAsync(&sub, one.p, 1, cudaMemcpyDeviceToHost, ctx->stream));
+                VF_CUDA(cudaStreamSynchronize(ctx->stream));
+            }
+            uint8_t byte = 0;
+            for (int s = 0; s < 8 / bits; ++s) byte = uint8_t((byte << bits) + sub);
+            DBuf tmp;
+            void* target = dst;
+            if (!to_dev) {
+                tmp = DBuf(ctx, dst_bytes);
+                target = tmp.p;
+            }
+            launch_fill_bytes(ctx, target, byte, dst_bytes);
+            if (!to_dev) emit(tmp.p, dst_bytes);
+            written = dst_bytes;
+            return written;
+        }
+        if (dst_bytes < c.nbytes) {
+            if (dst_bytes == 0 || c.nbytes % dst_bytes != 0) raise(VF_ERR_BUFFER_TOO_SMALL, "Cannot pack sub-byte elements into buffer: source data size '%llu', target data size '%llu'", (unsigned long long)c.nbytes, (unsigned long long)dst_bytes);
+            const uint64_t n = c.nbytes / uint64_t(dtype_bits(c.storage) / 8);
+            const uint64_t per = n / dst_bytes;
+            if (per > 8 || (per & (per - 1)) != 0) raise(VF_ERR_SHAPE, "Invalid number of elements per byte '%llu'", (unsigned long long)per);
+            DBuf tmp;
+            void* target = dst;
+            if (!to_dev) {
+                tmp = DBuf(ctx, dst_bytes);
+                target = tmp.p;
+            }
+            launch_pack_subbyte(ctx, c.d, c.storage, static_cast<uint8_t*>(target), int64_t(n), int(per));
+            if (!to_dev) emit(tmp.p, dst_bytes);
+            written = dst_bytes;
+            return written;
+        }
+        emit(c.d, c.nbytes);
+        return written;
+    }
+    if (!c.splat && edt == c.storage) {
+        if (dst_bytes < c.nbytes) raise(VF_ERR_BUFFER_TOO_SMALL, "Byte sizes of the target buffer '%llu' is smaller then storage buffer '%llu'", (unsigned long long)dst_bytes, (unsigned long long)c.nbytes);
+        emit(c.d, c.nbytes);
+        return written;
+    }
+    const int64_t n = c.type.numel();
+    const uint64_t need = uint64_t(n) * uint64_t(bits / 8);
+    if (dst_bytes < need) raise(VF_ERR_BUFFER_TOO_SMALL, "Buffer with byte size '%llu' is not enough to hold actual elements with '%llu' byte size", (unsigned long long)dst_bytes, (unsigned long long)need);
+    if (to_dev) {
+        launch_convert(ctx, c.d, c.storage, c.splat, dst, edt, n);
+        written = need;
+    } else {
+        DBuf tmp(ctx, need);
+        launch_convert(ctx, c.d, c.storage, c.splat, tmp.p, edt, n);
+        emit(tmp.p, need);
+    }
+    return written;
+}
+
+struct CallScope {  // per-call bookkeeping: context lock, device, error flags, launch statistics
+    vf_ctx* ctx;
+    std::unique_lock<std::mutex> lock;
+    DeviceGuard dev;
+    uint64_t launches0;
+    vf_stats* stats;
+    CallScope(vf_ctx* c, vf_stats* s): ctx(check(c)), lock(c->mu), dev(c->device), launches0(c->launches), stats(s) {
+        if (stats) std::memset(stats, 0, sizeof(*stats));
+        flags_clear(ctx);
+    }
+    static vf_ctx* check(vf_ctx* c) {
+        if (!c) raise(VF_ERR_INVALID_ARG, "ctx is NULL");
+        return c;
+    }
+    void finish() {
+        flags_check(ctx);
+        if (stats) stats->kernels_launched = int32_t(ctx->launches - launches0);
+    }
+};
+
+void* out_ptr(vf_ctx* ctx, void* user, int kind, size_t bytes, DBuf& tmp) {
+    if (!user) return nullptr;
+    if (kind == VF_MEM_DEVICE) return user;
+    tmp = DBuf(ctx, bytes);
+    return tmp.p;
+}
+void out_flush(vf_ctx* ctx, void* user, int kind, size_t bytes, DBuf& tmp) {
+    if (user && kind != VF_MEM_DEVICE) copy_out(ctx, user, kind, tmp.p, bytes);
+}
+
+int64_t unit_count(const Type& t, const vf_quant_spec& s, int64_t& unit_len) {
+    if (t.order != identity_order(t.rank)) raise(VF_ERR_UNSUPPORTED, "weight quantization needs dim 0 outermost (row-major) input");
+    if (s.group_size > 0) {
+        const int64_t cols = t.shape[t.rank - 1];
+        if (cols % s.group_size != 0) raise(VF_ERR_SHAPE, "group size %lld does not divide the row length %lld", (long long)s.group_size, (long long)cols);
+        unit_len = s.group_size;
+        return t.numel() / unit_len;
+    }
+    const int64_t units = t.shape[0];
+    unit_len = units ? t.numel() / units : 0;
+    return units;
+}
+
+void check_spec(const vf_quant_spec& s) {
+    if (s.storage_dtype != VF_DT_I8 && s.storage_dtype != VF_DT_U8) raise(VF_ERR_UNSUPPORTED, "weight quantization stores i8 or u8 codes");
+    double lo, hi;
+    dtype_int_limits(s.storage_dtype, lo, hi);
+    if (s.qmin >= s.qmax || double(s.qmin) < lo || double(s.qmax) > hi) raise(VF_ERR_INVALID_ARG, "storage range [%lld, %lld] does not fit the storage type", (long long)s.qmin, (long long)s.qmax);
+    if (s.range_mode != VF_RANGE_MINMAX && s.range_mode != VF_RANGE_ABSMAX) raise(VF_ERR_INVALID_ARG, "unknown range mode");
+    if (s.group_size < 0) raise(VF_ERR_INVALID_ARG, "negative group size");
+}
+
+}  // namespace
+
+// fused single-pass path (fold_fused.cu); returns false when the pattern is not covered
+bool try_fused_quantize_fold(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec, const vf_transform* t,
+                             int n, void* dst, uint64_t dst_bytes, int dst_kind, uint64_t* dst_written,
+                             const vf_quant_outputs* outs, vf_stats* stats);
+
+// Unfused composition with the general kernels: unit statistics, Quantize with the derived parameters, the
+// remaining transformations, copyTo. Also the reference implementation the fused kernels are tested against.
+static void quantize_fold_general(vf_ctx* ctx, DContent& base, const vf_quant_spec& spec, const vf_transform* t, int n,
+                                  void* dst, uint64_t dst_bytes, int dst_kind, uint64_t* dst_written,
+                                  const vf_quant_outputs* outs, vf_stats* stats) {
+    int64_t unit_len = 0;
+    const int64_t units = unit_count(base.type, spec, unit_len);
+    if (base.splat) raise(VF_ERR_SPLAT, "weight quantization of a splat constant is not supported");
+    if (!dtype_is_float(base.storage)) raise(VF_ERR_UNSUPPORTED, "weight quantization takes f32 / f16 / bf16 input");
+    DBuf ds(ctx, size_t(units) * 8), dz(ctx, size_t(units) * 8);
+    launch_unit_stats(ctx, base.d, base.storage, units, unit_len, spec.range_mode, spec.qmin, spec.qmax, ds.as<double>(),
+                      dz.as<int64_t>(), nullptr, nullptr);
+    Type ct = base.type;
+    ct.elem = Elem::plain(spec.storage_dtype);
+    DContent codes = alloc_like(ctx, ct, spec.storage_dtype, false);
+    launch_quantize(ctx, base.d, base.storage, false, codes.own.p, spec.storage_dtype, ct.numel(), ds.as<double>(),
+                    dz.as<int64_t>(), units, unit_len, spec.qmin, spec.qmax);
+    if (outs) {
+        const int k = outs->mem_kind;
+        if (outs->scales) copy_out(ctx, outs->scales, k, ds.p, size_t(units) * 8);
+        if (outs->zps) copy_out(ctx, outs->zps, k, dz.p, size_t(units) * 8);
+        if (outs->scales_f16 || outs->zps_u4_packed) {
+            DBuf t0, t1;
+            const size_t zb = size_t((units + 1) / 2);
+            uint16_t* d16 = static_cast<uint16_t*>(out_ptr(ctx, outs->scales_f16, k, size_t(units) * 2, t0));
+            uint8_t* d4 = static_cast<uint8_t*>(out_ptr(ctx, outs->zps_u4_packed, k, zb, t1));
+            launch_pack_params(ctx, ds.as<double>(), dz.as<int64_t>(), units, d16, d4);
+            out_flush(ctx, outs->scales_f16, k, size_t(units) * 2, t0);
+            out_flush(ctx, outs->zps_u4_packed, k, zb, t1);
+        }
+        if (outs->dequant) {
+            // [CastElemType<q>, Dequantize] on the codes, then copyTo in the requested float type
+            const int ddt = outs->dequant_dtype;
+            if (ddt != VF_DT_F16 && ddt != VF_DT_F32 && ddt != VF_DT_BF16) raise(VF_ERR_UNSUPPORTED, "dequantized copy is f16 / bf16 / f32");
+            const uint64_t need = uint64_t(ct.numel()) * uint64_t(dtype_bits(ddt) / 8);
+            if (outs->dequant_bytes < need) raise(VF_ERR_BUFFER_TOO_SMALL, "dequantized copy needs %llu bytes", (unsigned long long)need);
+            DBuf f32(ctx, size_t(ct.numel()) * 4), t2;
+            launch_dequantize(ctx, codes.d, spec.storage_dtype, false, f32.as<float>(), ct.numel(), ds.as<double>(),
+                              dz.as<int64_t>(), units, unit_len);
+            void* dd = out_ptr(ctx, outs->dequant, k, need, t2);
+            launch_convert(ctx, f32.p, VF_DT_F32, false, dd, ddt, ct.numel());
+            out_flush(ctx, outs->dequant, k, need, t2);
+            if (stats) stats->bytes_out += need;
+        }
+    }
+    check_positions(t, n);
+    DContent cur = std::move(codes);
+    for (int i = 0; i < n; ++i) {
+        DContent next = apply(ctx, cur, t[i]);
+        cur = std::move(next);
+    }
+    const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_kind, stats);
+    if (dst_written) *dst_written = w;
+    if (stats) stats->bytes_out += w;
+}
+
+}  // namespace vf
+
+using namespace vf;
+
+extern "C" {
+
+int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, void* dst, uint64_t dst_bytes,
+            int dst_mem_kind, uint64_t* dst_written, vf_tensor_type* out_type, double* scales_buf, int64_t* zps_buf,
+            int64_t params_cap, vf_stats* stats, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!base || (n > 0 && !t) || n < 0) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        check_positions(t, n);
+        CallScope scope(ctx, stats);
+        DContent cur = upload_base(ctx, *base, stats);
+        for (int i = 0; i < n; ++i) {  // ContentAttr::fold — attributes/content.cpp:392-394
+            DContent next = apply(ctx, cur, t[i]);
+            cur = std::move(next);
+        }
+        cur.type.export_to(out_type, scales_buf, zps_buf, params_cap);
+        const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_mem_kind, stats);
+        if (dst_written) *dst_written = w;
+        if (stats) stats->bytes_out += w;
+        scope.finish();
+    });
+}
+
+int vf_row_stats(vf_ctx* ctx, const vf_content* base, const vf_quant_spec* spec, double* scales, int64_t* zps,
+                 float* rmin, float* rmax, int64_t n_units, int out_mem_kind, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!base || !spec) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        check_spec(*spec);
+        CallScope scope(ctx, nullptr);
+        DContent in = upload_base(ctx, *base, nullptr);
+        if (in.splat) raise(VF_ERR_SPLAT, "statistics of a splat constant are not supported");
+        int64_t len = 0;
+        const int64_t units = unit_count(in.type, *spec, len);
+        if (units != n_units) raise(VF_ERR_SHAPE, "n_units is %lld, the tensor has %lld units", (long long)n_units, (long long)units);
+        DBuf t0, t1, t2, t3;
+        double* ds = static_cast<double*>(out_ptr(ctx, scales, out_mem_kind, size_t(units) * 8, t0));
+        int64_t* dz = static_cast<int64_t*>(out_ptr(ctx, zps, out_mem_kind, size_t(units) * 8, t1));
+        float* dmin = static_cast<float*>(out_ptr(ctx, rmin, out_mem_kind, size_t(units) * 4, t2));
+        float* dmax = static_cast<float*>(out_ptr(ctx, rmax, out_mem_kind, size_t(units) * 4, t3));
+        launch_unit_stats(ctx, in.d, in.storage, units, len, spec->range_mode, spec->qmin, spec->qmax, ds, dz, dmin, dmax);
+        out_flush(ctx, scales, out_mem_kind, size_t(units) * 8, t0);
+        out_flush(ctx, zps, out_mem_kind, size_t(units) * 8, t1);
+        out_flush(ctx, rmin, out_mem_kind, size_t(units) * 4, t2);
+        out_flush(ctx, rmax, out_mem_kind, size_t(units) * 4, t3);
+        scope.finish();
+    });
+}
+
+int vf_quantize_fold(vf_ctx* ctx, const vf_content* base, const vf_quant_spec* spec, const vf_transform* t, int n,
+                     void* dst, uint64_t dst_bytes, int dst_mem_kind, uint64_t* dst_written,
+                     const vf_quant_outputs* outs, vf_stats* stats, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!base || !spec || (n > 0 && !t) || n < 0) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        check_spec(*spec);
+        CallScope scope(ctx, stats);
+        DContent in = upload_base(ctx, *base, stats);
+        const bool allow_fused = !(ctx->opt_flags & VF_OPT_DISABLE_FUSION);
+        if (!allow_fused || !try_fused_quantize_fold(ctx, in, *spec, t, n, dst, dst_bytes, dst_mem_kind, dst_written, outs, stats)) {
+            quantize_fold_general(ctx, in, *spec, t, n, dst, dst_bytes, dst_mem_kind, dst_written, outs, stats);
+        } else if (stats) {
+            stats->fused = 1;
+        }
+        scope.finish();
+    });
+}
+
+int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats* stats, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, stats);
+        // uploads and kernels of all jobs are enqueued back to back; one synchronisation at the end
+        for (int j = 0; j < njobs; ++j) {
+            vf_quant_job& jb = jobs[j];
+            jb.status = VF_OK;
+            check_spec(jb.spec);
+            DContent in = upload_base(ctx, jb.base, stats);
+            uint64_t w = 0;
+            const bool allow_fused = !(ctx->opt_flags & VF_OPT_DISABLE_FUSION);
+            if (!allow_fused || !try_fused_quantize_fold(ctx, in, jb.spec, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, &w, &jb.outs, stats))
+                quantize_fold_general(ctx, in, jb.spec, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, &w, &jb.outs, stats);
+            jb.dst_written = w;
+        }
+        scope.finish();
+    });
+}
+
+int vf_nnz_per_oc(vf_ctx* ctx, const vf_content* content, int64_t* counts, int out_mem_kind, char* err,
+                  size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!content || !counts) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, nullptr);
+        DContent in = upload_base(ctx, *content, nullptr);
+        if (in.type.rank != 4) raise(VF_ERR_SHAPE, "Const::Content::sparsify: got unxpected content shape %d", in.type.rank);
+        check_sparse_dtype(in.type.elem.dtype);
+        const int64_t sv = sparsify_value(in.type.elem);
+        const int64_t oc = in.type.shape[0], work = in.type.shape[1] * in.type.shape[2] * in.type.shape[3];
+        DContent v = materialise_logical(ctx, in);
+        DBuf tmp;
+        int64_t* dc = static_cast<int64_t*>(out_ptr(ctx, counts, out_mem_kind, size_t(oc) * 8, tmp));
+        launch_sparsity_scan(ctx, v.d, v.storage, oc, work, sv, dc, nullptr, 0);
+        out_flush(ctx, counts, out_mem_kind, size_t(oc) * 8, tmp);
+        scope.finish();
+    });
+}
+
+int vf_sparsify(vf_ctx* ctx, const vf_content* content, void* data, uint64_t data_bytes, uint64_t* data_written,
+                void* map, uint64_t map_bytes, int64_t* counts, int out_mem_kind, vf_stats* stats, char* err,
+                size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!content) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, stats);
+        DContent in = upload_base(ctx, *content, stats);
+        if (in.type.rank != 4) raise(VF_ERR_SHAPE, "Expected 4D input shape");
+        const int dt = in.type.elem.dtype;
+        check_sparse_dtype(dt);
+        const int es = dtype_bits(dt) / 8;
+        const int64_t sv = sparsify_value(in.type.elem);
+        const int64_t oc = in.type.shape[0], work = in.type.shape[1] * in.type.shape[2] * in.type.shape[3];
+        const int64_t row_bytes = align_up(work, 128) / 8;
+        if (map) {
+            if (work % 8 != 0) raise(VF_ERR_SHAPE, "GetSparsityMap needs IC*KY*KX (%lld) to be a multiple of 8", (long long)work);
+            if (map_bytes < uint64_t(oc * row_bytes)) raise(VF_ERR_BUFFER_TOO_SMALL, "sparsity map needs %lld bytes", (long long)(oc * row_bytes));
+        }
+        DContent v = materialise_logical(ctx, in);
+        // pass 1: counts + bitmap in one sweep; pass 2: offsets; pass 3: compaction (second read of the
+        // weights, served from L2 for anything smaller than the cache)
+        DBuf tcounts, tmap, tdata;
+        DBuf counts_dev;
+        int64_t* dc = static_cast<int64_t*>(out_ptr(ctx, counts, out_mem_kind, size_t(oc) * 8, tcounts));
+        if (!dc) {
+            counts_dev = DBuf(ctx, size_t(oc) * 8);
+            dc = counts_dev.as<int64_t>();
+        }
+        uint8_t* dm = static_cast<uint8_t*>(out_ptr(ctx, map, out_mem_kind, size_t(oc * row_bytes), tmap));
+        launch_sparsity_scan(ctx, v.d, dt, oc, work, sv, dc, dm, row_bytes);
+        uint64_t total_host = 0;
+        if (data) {
+            DBuf offsets(ctx, size_t(oc + 1) * 8);
+            launch_sparse_offsets(ctx, dc, oc, es, offsets.as<int64_t>());
+            uint8_t* dd = static_cast<uint8_t*>(out_ptr(ctx, data, out_mem_kind, data_bytes, tdata));
+            launch_sparse_compact(ctx, v.d, dt, oc, work, sv, offsets.as<int64_t>(), dd, data_bytes);
+            int64_t total = 0;
+            VF_CUDA(cudaMemcpyAsync(&total, offsets.as<int64_t>() + oc, 8, cudaMemcpyDeviceToHost, ctx->stream));
+            VF_CUDA(cudaStreamSynchronize(ctx->stream));
+            total_host = uint64_t(total);
+            if (total_host > data_bytes) raise(VF_ERR_BUFFER_TOO_SMALL, "compressed weights need %llu bytes, buffer holds %llu", (unsigned long long)total_host, (unsigned long long)data_bytes);
+            out_flush(ctx, data, out_mem_kind, total_host, tdata);
+            if (out_mem_kind != VF_MEM_DEVICE && stats) stats->d2h_bytes += total_host;
+        }
+        out_flush(ctx, counts, out_mem_kind, size_t(oc) * 8, tcounts);
+        out_flush(ctx, map, out_mem_kind, size_t(oc * row_bytes), tmap);
+        if (data_written) *data_written = total_host;
+        if (stats) stats->bytes_out += total_host + (map ? uint64_t(oc * row_bytes) : 0);
+        scope.finish();
+    });
+}
+
+int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* d, int32_t* table, int out_mem_kind, char* err,
+                     size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!d || !table) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        if (d->oc <= 0) raise(VF_ERR_SHAPE, "OC must be positive");
+        if (d->in_elem.dtype == VF_DT_INVALID || d->out_elem.dtype == VF_DT_INVALID)
+            raise(VF_ERR_INVALID_ARG, "Can't create weights table without operation input/output types");
+        CallScope scope(ctx, nullptr);
+        const int64_t oc = d->oc;
+        const Elem in = Elem::from(d->in_elem), out = Elem::from(d->out_elem);
+        const bool has_w = d->weights_elem.dtype != VF_DT_INVALID;
+        const Elem w = has_w ? Elem::from(d->weights_elem) : Elem();
+        if (has_w && in.quantized() && !w.quantized()) raise(VF_ERR_UNSUPPORTED, "Unsupported In/Wt mixed precision");
+        auto check_n = [&](const Elem& e, const char* what) {
+            if (e.quantized() && e.scales.size() != 1 && int64_t(e.scales.size()) != oc)
+                raise(VF_ERR_SHAPE, "%s scales: %zu values for %lld channels", what, e.scales.size(), (long long)oc);
+        };
+        check_n(in, "input");
+        check_n(out, "output");
+        check_n(w, "weights");
+
+        TableArgs a{};
+        a.oc = oc;
+        a.in_quantized = in.quantized();
+        a.out_quantized = out.quantized();
+        a.weights_quantized = has_w && w.quantized();
+        a.in_is_float = !in.quantized() && dtype_is_float(in.dtype);
+        a.const_scale = d->has_const_scale ? d->const_scale : 1.0;
+        DBuf dws, dis, dos, dwp, dsp, dbias, doff;
+        std::vector<double> ws = a.weights_quantized ? w.scales : std::vector<double>{1.0};
+        dws = upload_vec(ctx, ws);
+        a.d_wscale = dws.as<double>();
+        a.n_wscale = int64_t(ws.size());
+        a.in_scale = in.quantized() ? in.scales[0] : 1.0;
+        a.out_scale = out.quantized() ? out.scales[0] : 1.0;
+        if (in.quantized() && in.scales.size() > 1) {
+            dis = upload_vec(ctx, in.scales);
+            a.d_in_scale = dis.as<double>();
+        }
+        if (out.quantized() && out.scales.size() > 1) {
+            dos = upload_vec(ctx, out.scales);
+            a.d_out_scale = dos.as<double>();
+        }
+        a.wbase = d->weights_ptr_base;
+        a.wstep = d->weights_ptr_step;
+        a.sbase = d->sparsity_ptr_base;
+        a.sstep = d->sparsity_ptr_step;
+        if (d->weights_ptrs) {
+            dwp = DBuf(ctx, size_t(oc) * 4);
+            copy_in(ctx, dwp.p, d->weights_ptrs, size_t(oc) * 4, VF_MEM_HOST);
+            a.d_wptrs = dwp.as<int32_t>();
+        }
+        if (d->sparsity_ptrs) {
+            dsp = DBuf(ctx, size_t(oc) * 4);
+            copy_in(ctx, dsp.p, d->sparsity_ptrs, size_t(oc) * 4, VF_MEM_HOST);
+            a.d_sptrs = dsp.as<int32_t>();
+        }
+        DBuf dnnz;
+        if (d->nnz_counts) {
+            const int64_t* dc = d->nnz_counts;
+            if (d->nnz_mem_kind != VF_MEM_DEVICE) {
+                dnnz = DBuf(ctx, size_t(oc) * 8);
+                copy_in(ctx, dnnz.p, d->nnz_counts, size_t(oc) * 8, d->nnz_mem_kind);
+                dc = dnnz.as<int64_t>();
+            }
+            doff = DBuf(ctx, size_t(oc + 1) * 8);
+            const int eb = std::max(1, dtype_bits(has_w ? w.dtype : VF_DT_U8) / 8);
+            launch_sparse_offsets(ctx, dc, oc, eb, doff.as<int64_t>());
+            a.d_nnz_offsets = doff.as<int64_t>();
+        }
+        if (d->has_bias) {
+            if (!d->bias) raise(VF_ERR_INVALID_ARG, "has_bias without a bias pointer");
+            const size_t nb = size_t(d->bias_is_splat ? 1 : oc) * 4;
+            if (d->bias_mem_kind == VF_MEM_DEVICE) {
+                a.d_bias = d->bias;
+            } else {
+                dbias = DBuf(ctx, nb);
+                copy_in(ctx, dbias.p, d->bias, nb, d->bias_mem_kind);
+                a.d_bias = dbias.as<float>();
+            }
+            a.bias_is_splat = d->bias_is_splat;
+        }
+        DBuf tmp;
+        int32_t* dt = static_cast<int32_t*>(out_ptr(ctx, table, out_mem_kind, size_t(oc) * 16, tmp));
+        launch_weights_table(ctx, a, dt);
+        out_flush(ctx, table, out_mem_kind, size_t(oc) * 16, tmp);
+        scope.finish();
+    });
+}
+
+int vf_synth_fill(vf_ctx* ctx, const vf_synth_spec* spec, void* dst, uint64_t count, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!spec || !dst) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, nullptr);
+        launch_synth(ctx, *spec, dst, count);
+        scope.finish();
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+// Host-callable launch wrappers of the CUDA kernels. Every wrapper enqueues on ctx->stream and bumps
+// ctx->launches by the number of kernels it launched.
+#pragma once
+
+#include "common.h"
+
+namespace vf {
+
+struct Geom {  // index geometry shared by the layout kernels (rank <= 5, memory order)
+    int rank;
+    int64_t in_shape[VF_MAX_RANK];   // input memory shape
+    int64_t out_shape[VF_MAX_RANK];  // output memory shape
+    int64_t src_stride[VF_MAX_RANK]; // for each OUTPUT memory dim: stride (elements) into the input buffer
+    int64_t offset[VF_MAX_RANK];     // per output memory dim: pad-before (pad) or subview offset
+};
+
+// ---- elementwise (general path) ----------------------------------------------------------------------
+// Quantize with supplied parameters. per-tensor: n_params == 1. per-axis: params indexed by
+// (idx / inner) % axis_size. `d_scales`/`d_zps` are device arrays.
+void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void* out, int out_dt, int64_t n,
+                     const double* d_scales, const int64_t* d_zps, int64_t axis_size, int64_t inner, int64_t qmin,
+                     int64_t qmax);
+void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, float* out, int64_t n,
+                       const double* d_scales, const int64_t* d_zps, int64_t axis_size, int64_t inner);
+void launch_rescale_add(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, float* out, int64_t n, float c,
+                        bool is_add);
+// copyTo element conversion: storage dtype -> logical dtype (byte-sized), splat-aware
+void launch_convert(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void* out, int out_dt, int64_t n);
+// copyTo sub-byte packing: `per_byte` elements of `in` (read as int8) into each output byte, low bits first
+void launch_pack_subbyte(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in, int per_byte);
+// BitPack<4>: reads pairs through getValues<uint8_t>()
+void launch_bitpack4(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in);
+void launch_fill_bytes(vf_ctx* ctx, void* out, uint8_t value, uint64_t bytes);
+
+// ---- layout ----------------------------------------------------------------------------------------
+// out[o] = in[sum_d coord_d(o) * src_stride[d]]   (arbitrary memory permutation, element size es bytes)
+void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es);
+// PadWithZero: windows the input into the output; outside the window writes fill[dim0 index] or fill[0].
+// `d_fill` is a device array of `n_fill` elements of size es (already converted to the storage type);
+// n_fill == 1: uniform fill; otherwise indexed by the coordinate along output memory dim `fill_dim`.
+void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geom& g, int es, const void* d_fill,
+                int64_t n_fill, int fill_dim);
+void launch_subview(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es);
+
+// ---- sparsity --------------------------------------------------------------------------------------
+// Per output channel: non-sparse count and (optionally) the sparsity bitmap row.
+// `in` holds OC rows of `work` elements of logical dtype `dt` (i8/u8/f16/bf16/f32).
+void launch_sparsity_scan(vf_ctx* ctx, const void* in, int dt, int64_t oc, int64_t work, int64_t sparse_value,
+                          int64_t* d_counts, uint8_t* d_map, int64_t map_row_bytes);
+// Exclusive prefix sum of align16(count*es) -> d_offsets[oc+1] (bytes); total at d_offsets[oc]
+void launch_sparse_offsets(vf_ctx* ctx, const int64_t* d_counts, int64_t oc, int es, int64_t* d_offsets);
+// Per-OC stream compaction into `out` at d_offsets; zero-fills each channel's alignment gap. `capacity`
+// is the byte size of `out`; an overflow sets VF_FLAG_OVERFLOW and drops the excess.
+void launch_sparse_compact(vf_ctx* ctx, const void* in, int dt, int64_t oc, int64_t work, int64_t sparse_value,
+                           const int64_t* d_offsets, uint8_t* out, uint64_t capacity);
+
+// ---- statistics --------------------------------------------------------------------------------------
+// min/max (over values and 0) or absmax per unit of `unit_len` consecutive elements, then
+// calcScaleAndZeroPoint. Any output may be NULL.
+void launch_unit_stats(vf_ctx* ctx, const void* in, int in_dt, int64_t units, int64_t unit_len, int range_mode,
+                       int64_t qmin, int64_t qmax, double* d_scales, int64_t* d_zps, float* d_rmin, float* d_rmax);
+
+// ---- weights table -----------------------------------------------------------------------------------
+struct TableArgs {
+    int64_t oc;
+    const double* d_wscale;  // [oc] or [1]
+    int64_t n_wscale;
+    double in_scale, out_scale;  // broadcast per-tensor activation scales (per-channel ones go via arrays)
+    const double* d_in_scale;    // optional [oc]
+    const double* d_out_scale;   // optional [oc]
+    double const_scale;
+    int in_quantized, out_quantized, weights_quantized, in_is_float;
+    const int32_t* d_wptrs;  // optional explicit
+    const int32_t* d_sptrs;
+    int32_t wbase, wstep, sbase, sstep;
+    const int64_t* d_nnz_offsets;  // optional: column 0 = wbase + offsets[oc] (exclusive prefix sums, bytes)
+    const float* d_bias;           // optional
+    int bias_is_splat;
+};
+void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table);
+
+// ---- synthetic weights -------------------------------------------------------------------------------
+void launch_synth(vf_ctx* ctx, const vf_synth_spec& s, void* dst, uint64_t count);
+
+// ---- fused weight quantization (hot path) ------------------------------------------------------------
+struct RowQuantArgs {
+    const void* in;
+    int in_dt;               // F32 / F16 / BF16
+    int64_t rows, cols;      // tensor viewed as [rows, cols] row-major
+    int64_t group;           // 0: one unit per row, else units of `group` elements along cols
+    int range_mode;
+    int64_t qmin, qmax;
+    int out_signed;          // codes stored as i8 (1) or u8 (0)
+    // store stage
+    int pack4;               // BitPack<4> of the codes
+    // OIYX -> OYXI permutation inside a row: cols = ic * khw; output row = khw * ic_pad (pad lanes = 0);
+    // khw == 0 disables the permutation
+    int64_t ic, khw, ic_pad;
+    int64_t rows_pad;        // output rows (>= rows); extra rows are zero
+    void* codes;
+    // side outputs (device pointers, may be NULL)
+    double* scales;
+    int64_t* zps;
+    uint16_t* scales_f16;
+    uint8_t* zps_u4;
+    void* dequant;
+    int dequant_dt;
+};
+void launch_rowquant(vf_ctx* ctx, const RowQuantArgs& a);
+// 0: no fused kernel covers `a`; 1: per-group kernel; 2: long-row kernel; 3: convolution-row kernel
+int rowquant_kind(const RowQuantArgs& a);
+// derived parameters -> float16 scales and 4-bit packed zero points (either output may be NULL)
+void launch_pack_params(vf_ctx* ctx, const double* d_scales, const int64_t* d_zps, int64_t units,
+                        uint16_t* scales_f16, uint8_t* zps_u4);
+
+}  // namespace vf

@@ -1,0 +1,680 @@
+// General-path kernels: one kernel per #const transformation, for every storage type the reference's
+// Content::getValues<T>() accepts. These back vf_fold() for arbitrary transformation lists; the weight
+// quantization hot path has its own fused kernels (kernels_rowquant.cu).
+#include "device_utils.cuh"
+#include "kernels.h"
+
+namespace vf {
+
+namespace {
+
+constexpr int kBlock = 256;
+
+inline int grid_for(int64_t n, int per_thread = 1) {
+    const int64_t blocks = (n + int64_t(kBlock) * per_thread - 1) / (int64_t(kBlock) * per_thread);
+    // grid-stride loops: cap at a few waves of the 148 SMs
+    return int(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Quantize — attributes/quantize.cpp:108-212
+// ------------------------------------------------------------------------------------------------------
+__global__ void k_quantize(const void* __restrict__ in, int in_dt, int in_splat, void* __restrict__ out, int out_dt,
+                           int64_t n, const double* __restrict__ scales, const int64_t* __restrict__ zps,
+                           int64_t axis_size, int64_t inner, long long qmin, long long qmax, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    QuantParams qp = make_quant_params(scales[0], zps[0], qmin, qmax);
+    int64_t cur = 0;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        if (axis_size > 1) {
+            const int64_t a = (i / inner) % axis_size;
+            if (a != cur) {
+                cur = a;
+                qp = make_quant_params(scales[a], zps[a], qmin, qmax);
+            }
+        }
+        const float x = load_as_f32(in, in_dt, in_splat ? 0 : i, flags);
+        if (x != x) set_flag(flags, VF_FLAG_NAN);
+        store_int(out, out_dt, i, quantize_exact(x, qp));
+    }
+}
+
+// Dequantize — attributes/dequantize.cpp:42-108
+__global__ void k_dequantize(const void* __restrict__ in, int in_dt, int in_splat, float* __restrict__ out, int64_t n,
+                             const double* __restrict__ scales, const int64_t* __restrict__ zps, int64_t axis_size,
+                             int64_t inner, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t a = axis_size > 1 ? (i / inner) % axis_size : 0;
+        const long long q = load_as_int(in, in_dt, in_splat ? 0 : i, VF_DT_I64, flags);
+        out[i] = dequantize_exact(q, scales[a], zps[a]);
+    }
+}
+
+// Rescale / Add — attributes/rescale.cpp:67-82, attributes/add.cpp:62-77
+__global__ void k_rescale_add(const void* __restrict__ in, int in_dt, int in_splat, float* __restrict__ out,
+                              int64_t n, float c, int is_add, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = load_as_f32(in, in_dt, in_splat ? 0 : i, flags);
+        out[i] = is_add ? __fadd_rn(v, c) : __fmul_rn(v, c);
+    }
+}
+
+// copyTo element conversion — utils/content.cpp:84-97,180-183 with CvtHelper (utils/content.hpp:33-87)
+__global__ void k_convert(const void* __restrict__ in, int in_dt, int in_splat, void* __restrict__ out, int out_dt,
+                          int64_t n, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t s = in_splat ? 0 : i;
+        switch (out_dt) {
+        case VF_DT_F32: static_cast<float*>(out)[i] = load_as_f32(in, in_dt, s, flags); break;
+        case VF_DT_F16: static_cast<uint16_t*>(out)[i] = f32_to_f16_clamped_bits(load_as_f32(in, in_dt, s, flags)); break;
+        case VF_DT_BF16: static_cast<uint16_t*>(out)[i] = f32_to_bf16_bits(load_as_f32(in, in_dt, s, flags)); break;
+        case VF_DT_F64: {
+            double d;
+            if (in_dt == VF_DT_F64) d = static_cast<const double*>(in)[s];
+            else if (in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16) d = double(load_as_f32(in, in_dt, s, flags));
+            else if (in_dt == VF_DT_U64) d = double(static_cast<const unsigned long long*>(in)[s]);
+            else d = double(load_as_int(in, in_dt, s, VF_DT_I64, flags));
+            static_cast<double*>(out)[i] = d;
+            break;
+        }
+        default: store_int(out, out_dt, i, load_as_int(in, in_dt, s, out_dt, flags));
+        }
+    }
+}
+
+// copySubByteContent, packing branch — utils/content.cpp:131-152
+__global__ void k_pack_subbyte(const void* __restrict__ in, int in_dt, uint8_t* __restrict__ out, int64_t n_out,
+                               int per_byte, int* flags) {
+    const int bits = 8 / per_byte;
+    const unsigned mask = (1u << bits) - 1u;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += stride) {
+        unsigned byte = 0;
+        for (int k = 0; k < per_byte; ++k) {
+            const long long v = load_as_int(in, in_dt, o * per_byte + k, VF_DT_I8, flags);
+            byte |= (unsigned(v) & mask) << (k * bits);
+        }
+        out[o] = uint8_t(byte);
+    }
+}
+
+// BitPack<4> — attributes/bit_pack.cpp:146-151
+__global__ void k_bitpack4(const void* __restrict__ in, int in_dt, uint8_t* __restrict__ out, int64_t n_out,
+                           int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += stride) {
+        const unsigned lo = unsigned(load_as_int(in, in_dt, 2 * o, VF_DT_U8, flags)) & 0xFu;
+        const unsigned hi = unsigned(load_as_int(in, in_dt, 2 * o + 1, VF_DT_U8, flags)) & 0xFu;
+        out[o] = uint8_t((hi << 4) + lo);
+    }
+}
+
+// u8 fast path of BitPack: 16 codes in, 8 bytes out per thread step
+__global__ void k_bitpack4_u8(const uint4* __restrict__ in, uint2* __restrict__ out, int64_t n_vec) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t v = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
+        const uint4 x = in[v];
+        auto pack = [](unsigned w) {  // 4 bytes -> 2 bytes (low nibble first)
+            const unsigned a = w & 0x0F0F0F0Fu;
+            const unsigned b = a | (a >> 4);  // byte0|byte1<<4 in bits 0..7, byte2|byte3<<4 in bits 16..23
+            return (b & 0xFFu) | ((b >> 8) & 0xFF00u);
+        };
+        uint2 r;
+        r.x = pack(x.x) | (pack(x.y) << 16);
+        r.y = pack(x.z) | (pack(x.w) << 16);
+        out[v] = r;
+    }
+}
+
+__global__ void k_fill_bytes(uint8_t* out, uint8_t value, uint64_t bytes) {
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < bytes; i += stride) out[i] = value;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// layout
+// ------------------------------------------------------------------------------------------------------
+template <int ES>
+struct ElemOf;
+template <> struct ElemOf<1> { using T = uint8_t; };
+template <> struct ElemOf<2> { using T = uint16_t; };
+template <> struct ElemOf<4> { using T = uint32_t; };
+template <> struct ElemOf<8> { using T = uint64_t; };
+
+// memPermuteTransformation — utils/transformations.cpp:889-939, gathered from the output side so that the
+// stores are coalesced
+template <int ES>
+__global__ void k_permute(const void* __restrict__ in, void* __restrict__ out, Geom g, int64_t n) {
+    using T = typename ElemOf<ES>::T;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
+        int64_t rem = o, src = 0;
+#pragma unroll
+        for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+            if (d < g.rank) {
+                const int64_t c = rem % g.out_shape[d];
+                rem /= g.out_shape[d];
+                src += c * g.src_stride[d];
+            }
+        }
+        static_cast<T*>(out)[o] = static_cast<const T*>(in)[src];
+    }
+}
+
+// PadWithZero — attributes/pad_with_zero.cpp:111-268 + Content::fillWithZero utils/content.cpp:190-237
+template <int ES>
+__global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restrict__ out, Geom g, int64_t n,
+                      const void* __restrict__ fill, int64_t n_fill, int fill_dim) {
+    using T = typename ElemOf<ES>::T;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
+        int64_t rem = o, src = 0, fc = 0;
+        bool inside = true;
+#pragma unroll
+        for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+            if (d < g.rank) {
+                const int64_t c = rem % g.out_shape[d];
+                rem /= g.out_shape[d];
+                if (d == fill_dim) fc = c;
+                const int64_t ci = c - g.offset[d];
+                inside &= (ci >= 0) && (ci < g.in_shape[d]);
+                src += ci * g.src_stride[d];
+            }
+        }
+        T v;
+        if (inside) v = static_cast<const T*>(in)[in_splat ? 0 : src];
+        else v = static_cast<const T*>(fill)[n_fill > 1 ? fc : 0];
+        static_cast<T*>(out)[o] = v;
+    }
+}
+
+// SubView — attributes/subview.cpp:390-432
+template <int ES>
+__global__ void k_subview(const void* __restrict__ in, void* __restrict__ out, Geom g, int64_t n) {
+    using T = typename ElemOf<ES>::T;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
+        int64_t rem = o, src = 0;
+#pragma unroll
+        for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+            if (d < g.rank) {
+                const int64_t c = rem % g.out_shape[d];
+                rem /= g.out_shape[d];
+                src += (c + g.offset[d]) * g.src_stride[d];
+            }
+        }
+        static_cast<T*>(out)[o] = static_cast<const T*>(in)[src];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// sparsity
+// ------------------------------------------------------------------------------------------------------
+// element != sparsify value, in the logical storage type (utils/sparsity.cpp:47-63,
+// attributes/sparsify.cpp:143-152, attributes/get_sparsity_map.cpp:44-52). Floating types compare as
+// float, so -0.0 counts as zero.
+__device__ __forceinline__ bool is_dense(const void* p, int dt, int64_t i, long long iv, float fv) {
+    switch (dt) {
+    case VF_DT_I8: return static_cast<const int8_t*>(p)[i] != int8_t(iv);
+    case VF_DT_U8: return static_cast<const uint8_t*>(p)[i] != uint8_t(iv);
+    case VF_DT_F16: return f16_bits_to_f32(static_cast<const uint16_t*>(p)[i]) != fv;
+    case VF_DT_BF16: return bf16_bits_to_f32(static_cast<const uint16_t*>(p)[i]) != fv;
+    default: return static_cast<const float*>(p)[i] != fv;
+    }
+}
+
+__device__ __forceinline__ float sparse_value_as_float(int dt, long long v) {
+    float f = float(v);
+    if (dt == VF_DT_F16) f = f16_bits_to_f32(f32_to_f16_bits(f));
+    if (dt == VF_DT_BF16) f = bf16_bits_to_f32(f32_to_bf16_bits(f));
+    return f;
+}
+
+// One warp per output channel: ballot gives 32 bitmap bits at a time (LSB = lowest index, as
+// get_sparsity_map.cpp:44-53 packs them) and popc gives the count.
+__global__ void k_sparsity_scan(const void* __restrict__ in, int dt, int64_t oc, int64_t work, long long sv,
+                                int64_t* __restrict__ counts, uint8_t* __restrict__ map, int64_t map_row_bytes) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    const float fv = sparse_value_as_float(dt, sv);
+    for (int64_t c = warp; c < oc; c += nwarps) {
+        const int64_t base = c * work;
+        int64_t cnt = 0;
+        for (int64_t i = 0; i < work; i += 32) {
+            const bool d = (i + lane < work) && is_dense(in, dt, base + i + lane, sv, fv);
+            const unsigned bits = __ballot_sync(0xffffffffu, d);
+            cnt += __popc(bits);
+            if (map && lane < 4) {
+                const int64_t byte = (i >> 3) + lane;
+                if (byte * 8 < work) map[c * map_row_bytes + byte] = uint8_t(bits >> (8 * lane));
+            }
+        }
+        if (map) {  // zero the padding up to the 128-bit aligned row
+            for (int64_t b = ((work + 7) >> 3) + lane; b < map_row_bytes; b += 32) map[c * map_row_bytes + b] = 0;
+        }
+        if (counts && lane == 0) counts[c] = cnt;
+    }
+}
+
+// Single-block exclusive scan of align16(count*es): offsets[0..oc], total in offsets[oc].
+__global__ void k_sparse_offsets(const int64_t* __restrict__ counts, int64_t oc, int es, int64_t* __restrict__ offsets) {
+    __shared__ long long warp_sums[32];
+    __shared__ long long carry_s;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (tid == 0) carry_s = 0;
+    __syncthreads();
+    for (int64_t base = 0; base < oc; base += blockDim.x) {
+        const int64_t i = base + tid;
+        long long v = 0;
+        if (i < oc) v = ((counts[i] * es + 15) / 16) * 16;
+        long long incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_sums[wid] = incl;
+        __syncthreads();
+        if (wid == 0) {
+            long long w = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0;
+            long long wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const long long t = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += t;
+            }
+            warp_sums[lane] = wi - w;  // exclusive
+        }
+        __syncthreads();
+        const long long carry = carry_s;
+        const long long excl = carry + warp_sums[wid] + incl - v;
+        if (i < oc) offsets[i] = excl;
+        __syncthreads();
+        if (tid == blockDim.x - 1) carry_s = excl + v;
+        __syncthreads();
+    }
+    if (tid == 0) offsets[oc] = carry_s;
+}
+
+// Sparsify — attributes/sparsify.cpp:120-161. One warp per output channel; within a 32-element step the
+// destination of a kept element is the running count plus popc of the lower lanes' ballot bits.
+template <int ES>
+__global__ void k_sparse_compact(const void* __restrict__ in, int dt, int64_t oc, int64_t work, long long sv,
+                                 const int64_t* __restrict__ offsets, uint8_t* __restrict__ out, uint64_t capacity,
+                                 int* flags) {
+    using T = typename ElemOf<ES>::T;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    const float fv = sparse_value_as_float(dt, sv);
+    for (int64_t c = warp; c < oc; c += nwarps) {
+        const int64_t base = c * work;
+        const uint64_t obyte = uint64_t(offsets[c]);
+        int64_t run = 0;
+        for (int64_t i = 0; i < work; i += 32) {
+            const bool d = (i + lane < work) && is_dense(in, dt, base + i + lane, sv, fv);
+            const unsigned bits = __ballot_sync(0xffffffffu, d);
+            if (d) {
+                const uint64_t pos = obyte + uint64_t(run + __popc(bits & ((1u << lane) - 1u))) * ES;
+                if (pos + ES <= capacity) *reinterpret_cast<T*>(out + pos) = static_cast<const T*>(in)[base + i + lane];
+                else set_flag(flags, VF_FLAG_OVERFLOW);
+            }
+            run += __popc(bits);
+        }
+        // zero the gap up to the next channel's 16-byte aligned start (the reference pre-zeroes the buffer)
+        const uint64_t end = obyte + uint64_t(run) * ES;
+        const uint64_t next = uint64_t(offsets[c + 1]);
+        for (uint64_t b = end + lane; b < next && b < capacity; b += 32) out[b] = 0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// unit statistics → calcScaleAndZeroPoint
+// ------------------------------------------------------------------------------------------------------
+__global__ void k_unit_stats(const void* __restrict__ in, int in_dt, int64_t units, int64_t len, int range_mode,
+                             long long qmin, long long qmax, double* __restrict__ scales, int64_t* __restrict__ zps,
+                             float* __restrict__ rmin, float* __restrict__ rmax, int* flags) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t u = warp; u < units; u += nwarps) {
+        float mn = 0.f, mx = 0.f;
+        for (int64_t i = lane; i < len; i += 32) {
+            const float v = load_as_f32(in, in_dt, u * len + i, flags);
+            mn = v < mn ? v : mn;
+            mx = v > mx ? v : mx;
+        }
+        mn = warp_min(mn);
+        mx = warp_max(mx);
+        if (range_mode == VF_RANGE_ABSMAX) {
+            const float a = fmaxf(-mn, mx);
+            mn = -a;
+            mx = a;
+        }
+        if (lane == 0) {
+            double sc = 0.0;
+            long long zp = 0;
+            if (!calc_scale_zp(double(qmin), double(qmax), double(mn), double(mx), sc, zp)) {
+                set_flag(flags, VF_FLAG_QUANT_RANGE);
+            }
+            zp = zp < qmin ? qmin : (zp > qmax ? qmax : zp);
+            if (scales) scales[u] = sc;
+            if (zps) zps[u] = zp;
+            if (rmin) rmin[u] = mn;
+            if (rmax) rmax[u] = mx;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// weights table — dialect/VPU/utils/nce_sparsity.cpp:97-136,195-231,317-347 with the NPU37XX converters
+// (NPU37XX/dialect/VPU/impl/nce_sparsity_converters.cpp:14-42)
+// ------------------------------------------------------------------------------------------------------
+__global__ void k_weights_table(TableArgs a, int32_t* __restrict__ table, int* flags) {
+    const int64_t oc = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (oc >= a.oc) return;
+    const double ws = a.weights_quantized ? a.d_wscale[a.n_wscale > 1 ? oc : 0] : 1.0;
+    const double is = a.d_in_scale ? a.d_in_scale[oc] : a.in_scale;
+    const double os = a.d_out_scale ? a.d_out_scale[oc] : a.out_scale;
+
+    int32_t wp, sp;
+    if (a.d_nnz_offsets) wp = int32_t(a.wbase + a.d_nnz_offsets[oc]);
+    else if (a.d_wptrs) wp = a.d_wptrs[oc];
+    else wp = int32_t(a.wbase + int64_t(a.wstep) * oc);
+    if (a.d_sptrs) sp = a.d_sptrs[oc];
+    else sp = int32_t(a.sbase + int64_t(a.sstep) * oc);
+    if (wp % 16 != 0) set_flag(flags, VF_FLAG_TABLE_ALIGN);
+    if (sp != VF_SPARSITY_PTR_WHEN_NO_SPARSITY && sp % 16 != 0) set_flag(flags, VF_FLAG_TABLE_ALIGN);
+
+    // rescale and its 15-bit approximation: approximate<>() utils/quantization.hpp:65-77
+    const double rescale = __dmul_rn(__ddiv_rn(__dmul_rn(ws, is), os), a.const_scale);
+    int exponent = 0;
+    const double mantissa = frexp(rescale, &exponent);
+    const double m = floor(__dmul_rn(mantissa, 32768.0));
+    if (exponent > 15) set_flag(flags, VF_FLAG_TABLE_RANGE);          // postShift != 0 — quantization.cpp:429-432
+    const int shift = 15 - exponent;
+    if (shift > 255) set_flag(flags, VF_FLAG_CHECKED_CAST);          // checked_cast<uint8_t>(bits - exponent)
+    if (!(m >= -32768.0 && m <= 32767.0)) set_flag(flags, VF_FLAG_CHECKED_CAST);  // checked_cast<int16_t>(mult)
+    int32_t ms;
+    if (a.in_is_float) {
+        ms = __float_as_int(__double2float_rn(rescale));
+    } else {
+        const int32_t mult = int32_t(m);
+        ms = int32_t((uint32_t(shift) << 8) | (uint32_t(mult) << 16));
+    }
+
+    int32_t bias = 0;
+    if (a.d_bias) {
+        const float b = a.d_bias[a.bias_is_splat ? 0 : oc];
+        if (a.in_quantized) {
+            // getRescaledBias: bias / (weightsScale * inScale) in FP64, strict int32 range, then std::round
+            const double rb = __ddiv_rn(double(b), __dmul_rn(ws, is));
+            if (!(rb > -2147483648.0 && rb < 2147483647.0)) {
+                set_flag(flags, VF_FLAG_TABLE_RANGE);
+            } else {
+                bias = int32_t(round(rb));
+            }
+        } else {
+            float bv = b;
+            if (a.weights_quantized) bv = __double2float_rn(__ddiv_rn(double(bv), ws));  // float /= double
+            bias = __float_as_int(bv);
+        }
+    }
+    table[oc * 4 + 0] = wp;
+    table[oc * 4 + 1] = sp;
+    table[oc * 4 + 2] = ms;
+    table[oc * 4 + 3] = bias;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// synthetic weights
+// ------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ float synth_value(uint64_t key, uint64_t g, float c, float omult, uint64_t omask,
+                                             int mask_zero, int dense_mod, int64_t row_len) {
+    const uint64_t h = mix64(key + g);
+    const int sum = int(h & 0xFFFF) + int((h >> 16) & 0xFFFF) + int((h >> 32) & 0xFFFF) + int((h >> 48) & 0xFFFF) - 131070;
+    float v = __fmul_rn(float(sum), c);
+    const uint64_t h2 = mix64(h);
+    if (omult != 0.f && (h2 & omask) == 0) v = __fmul_rn(v, omult);
+    if (mask_zero) {
+        bool dense = false;
+        if (dense_mod > 0 && row_len > 0) {
+            const uint64_t row = g / uint64_t(row_len);
+            dense = (mix64(key ^ (row * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull)) % uint64_t(dense_mod)) == 0;
+        }
+        if (!dense && ((h2 >> 40) & 1)) v = 0.f;
+    }
+    return v;
+}
+
+template <int DT>
+__global__ void k_synth(void* __restrict__ dst, uint64_t count, uint64_t key, uint64_t first, float c, float omult,
+                        uint64_t omask, int mask_zero, int dense_mod, int64_t row_len) {
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const float v = synth_value(key, first + i, c, omult, omask, mask_zero, dense_mod, row_len);
+        if (DT == VF_DT_F32) static_cast<float*>(dst)[i] = v;
+        else if (DT == VF_DT_F16) static_cast<uint16_t*>(dst)[i] = __half_as_ushort(__float2half_rn(v));
+        else static_cast<uint16_t*>(dst)[i] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    }
+}
+
+__global__ void k_pack_params(const double* __restrict__ scales, const int64_t* __restrict__ zps, int64_t units,
+                              uint16_t* __restrict__ scales_f16, uint8_t* __restrict__ zps_u4) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t u = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u < units; u += stride) {
+        if (scales_f16) scales_f16[u] = f32_to_f16_bits(__double2float_rn(scales[u]));
+        if (zps_u4 && (u & 1) == 0) {
+            const unsigned lo = unsigned(zps[u]) & 0xFu;
+            const unsigned hi = u + 1 < units ? (unsigned(zps[u + 1]) & 0xFu) : 0u;
+            zps_u4[u >> 1] = uint8_t((hi << 4) | lo);
+        }
+    }
+}
+
+uint64_t mix64_host(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+void post_launch(vf_ctx* ctx, int n = 1) {
+    VF_CUDA(cudaGetLastError());
+    ctx->launches += uint64_t(n);
+}
+
+}  // namespace
+
+// ======================================================================================================
+// launch wrappers
+// ======================================================================================================
+void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void* out, int out_dt, int64_t n,
+                     const double* d_scales, const int64_t* d_zps, int64_t axis_size, int64_t inner, int64_t qmin,
+                     int64_t qmax) {
+    if (n <= 0) return;
+    k_quantize<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, out_dt, n, d_scales, d_zps, axis_size,
+                                                        inner, qmin, qmax, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, float* out, int64_t n,
+                       const double* d_scales, const int64_t* d_zps, int64_t axis_size, int64_t inner) {
+    if (n <= 0) return;
+    k_dequantize<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, n, d_scales, d_zps, axis_size, inner,
+                                                          ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_rescale_add(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, float* out, int64_t n, float c,
+                        bool is_add) {
+    if (n <= 0) return;
+    k_rescale_add<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, n, c, is_add, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_convert(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void* out, int out_dt, int64_t n) {
+    if (n <= 0) return;
+    k_convert<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, out_dt, n, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_pack_subbyte(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in, int per_byte) {
+    const int64_t n_out = n_in / per_byte;
+    if (n_out <= 0) return;
+    k_pack_subbyte<<<grid_for(n_out), kBlock, 0, ctx->stream>>>(in, in_dt, out, n_out, per_byte, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_bitpack4(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in) {
+    const int64_t n_out = n_in / 2;
+    if (n_out <= 0) return;
+    const bool aligned = (reinterpret_cast<uintptr_t>(in) % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 8 == 0);
+    if (in_dt == VF_DT_U8 && aligned && n_in % 16 == 0) {
+        k_bitpack4_u8<<<grid_for(n_in / 16), kBlock, 0, ctx->stream>>>(static_cast<const uint4*>(in),
+                                                                     reinterpret_cast<uint2*>(out), n_in / 16);
+    } else {
+        k_bitpack4<<<grid_for(n_out), kBlock, 0, ctx->stream>>>(in, in_dt, out, n_out, ctx->d_flags);
+    }
+    post_launch(ctx);
+}
+
+void launch_fill_bytes(vf_ctx* ctx, void* out, uint8_t value, uint64_t bytes) {
+    if (!bytes) return;
+    k_fill_bytes<<<grid_for(int64_t(bytes)), kBlock, 0, ctx->stream>>>(static_cast<uint8_t*>(out), value, bytes);
+    post_launch(ctx);
+}
+
+static int64_t out_numel(const Geom& g) {
+    int64_t n = 1;
+    for (int i = 0; i < g.rank; ++i) n *= g.out_shape[i];
+    return n;
+}
+
+void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es) {
+    const int64_t n = out_numel(g);
+    if (n <= 0) return;
+    const int grid = grid_for(n);
+    switch (es) {
+    case 1: k_permute<1><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    case 2: k_permute<2><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    case 4: k_permute<4><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    case 8: k_permute<8><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    default: raise(VF_ERR_UNSUPPORTED, "permute of %d-byte elements", es);
+    }
+    post_launch(ctx);
+}
+
+void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geom& g, int es, const void* d_fill,
+                int64_t n_fill, int fill_dim) {
+    const int64_t n = out_numel(g);
+    if (n <= 0) return;
+    const int grid = grid_for(n);
+    switch (es) {
+    case 1: k_pad<1><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
+    case 2: k_pad<2><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
+    case 4: k_pad<4><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
+    case 8: k_pad<8><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
+    default: raise(VF_ERR_UNSUPPORTED, "pad of %d-byte elements", es);
+    }
+    post_launch(ctx);
+}
+
+void launch_subview(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es) {
+    const int64_t n = out_numel(g);
+    if (n <= 0) return;
+    const int grid = grid_for(n);
+    switch (es) {
+    case 1: k_subview<1><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    case 2: k_subview<2><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    case 4: k_subview<4><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    case 8: k_subview<8><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
+    default: raise(VF_ERR_UNSUPPORTED, "subview of %d-byte elements", es);
+    }
+    post_launch(ctx);
+}
+
+void launch_sparsity_scan(vf_ctx* ctx, const void* in, int dt, int64_t oc, int64_t work, int64_t sparse_value,
+                          int64_t* d_counts, uint8_t* d_map, int64_t map_row_bytes) {
+    if (oc <= 0) return;
+    const int64_t blocks = (oc + 7) / 8;  // 8 warps per block, one channel per warp
+    k_sparsity_scan<<<int(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value,
+                                                                                      d_counts, d_map, map_row_bytes);
+    post_launch(ctx);
+}
+
+void launch_sparse_offsets(vf_ctx* ctx, const int64_t* d_counts, int64_t oc, int es, int64_t* d_offsets) {
+    k_sparse_offsets<<<1, 1024, 0, ctx->stream>>>(d_counts, oc, es, d_offsets);
+    post_launch(ctx);
+}
+
+void launch_sparse_compact(vf_ctx* ctx, const void* in, int dt, int64_t oc, int64_t work, int64_t sparse_value,
+                           const int64_t* d_offsets, uint8_t* out, uint64_t capacity) {
+    if (oc <= 0) return;
+    const int64_t blocks = (oc + 7) / 8;
+    const int grid = int(blocks > 148 * 8 ? 148 * 8 : blocks);
+    const int es = dtype_bits(dt) / 8;
+    switch (es) {
+    case 1: k_sparse_compact<1><<<grid, 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value, d_offsets, out, capacity, ctx->d_flags); break;
+    case 2: k_sparse_compact<2><<<grid, 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value, d_offsets, out, capacity, ctx->d_flags); break;
+    default: k_sparse_compact<4><<<grid, 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value, d_offsets, out, capacity, ctx->d_flags); break;
+    }
+    post_launch(ctx);
+}
+
+void launch_unit_stats(vf_ctx* ctx, const void* in, int in_dt, int64_t units, int64_t unit_len, int range_mode,
+                       int64_t qmin, int64_t qmax, double* d_scales, int64_t* d_zps, float* d_rmin, float* d_rmax) {
+    if (units <= 0) return;
+    const int64_t blocks = (units + 7) / 8;
+    k_unit_stats<<<int(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, ctx->stream>>>(
+            in, in_dt, units, unit_len, range_mode, qmin, qmax, d_scales, d_zps, d_rmin, d_rmax, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_pack_params(vf_ctx* ctx, const double* d_scales, const int64_t* d_zps, int64_t units,
+                        uint16_t* scales_f16, uint8_t* zps_u4) {
+    if (units <= 0 || (!scales_f16 && !zps_u4)) return;
+    k_pack_params<<<grid_for(units), kBlock, 0, ctx->stream>>>(d_scales, d_zps, units, scales_f16, zps_u4);
+    post_launch(ctx);
+}
+
+void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table) {
+    if (a.oc <= 0) return;
+    k_weights_table<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(a, d_table, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_synth(vf_ctx* ctx, const vf_synth_spec& s, void* dst, uint64_t count) {
+    if (!count) return;
+    const uint64_t key = mix64_host(s.seed ^ mix64_host(s.tensor_id));
+    // sum of four uniform 16-bit integers, centred: standard deviation sqrt((65536^2 - 1) / 3)
+    const float c = float(double(s.sigma) / sqrt((65536.0 * 65536.0 - 1.0) / 3.0));
+    const uint64_t omask = s.outlier_log2 > 0 ? ((1ull << s.outlier_log2) - 1) : 0;
+    const int grid = grid_for(int64_t(count));
+    switch (s.dtype) {
+    case VF_DT_F32:
+        k_synth<VF_DT_F32><<<grid, kBlock, 0, ctx->stream>>>(dst, count, key, s.first_elem, c, s.outlier_mult, omask, s.mask_zero, s.dense_row_mod, s.row_len);
+        break;
+    case VF_DT_F16:
+        k_synth<VF_DT_F16><<<grid, kBlock, 0, ctx->stream>>>(dst, count, key, s.first_elem, c, s.outlier_mult, omask, s.mask_zero, s.dense_row_mod, s.row_len);
+        break;
+    case VF_DT_BF16:
+        k_synth<VF_DT_BF16><<<grid, kBlock, 0, ctx->stream>>>(dst, count, key, s.first_elem, c, s.outlier_mult, omask, s.mask_zero, s.dense_row_mod, s.row_len);
+        break;
+    default: raise(VF_ERR_UNSUPPORTED, "synthetic weights are f32 / f16 / bf16");
+    }
+    post_launch(ctx);
+}
+
+}  // namespace vf
