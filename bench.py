@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Weight-fold benchmark: input GB/s of the Const fold hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c5slab|c2|c3|c1] [--impl reference]
+
+One step = one pass of the fold over the whole workload (every tensor of this rank's shard). The default
+workload is the Llama-2-7B-shaped set (fp16 -> per-group-128 asymmetric u4, bit-packed, fp16 scales and packed
+u4 zero points; 13.2 GB of input), the largest configuration that fits one GPU; with N > 1 the tensors are
+sharded across ranks (longest-processing-time-first, no collective). Prints ONE JSON line on rank 0.
+
+`value`  : device-resident throughput (inputs already in HBM), CUDA events on the launching stream,
+           max over ranks.
+`e2e`    : same metric through the C ABI with pinned HOST buffers; H2D and D2H inside the timed region.
+`roofline`: algorithmic bytes of the launches in the timed region / their device time, against the measured
+           HBM copy peak.
+`cpu_baseline`: the CPU oracle (a port of the reference's fold code) on a bounded sample, host threads.
+`--impl reference`: times that CPU port alone, on all host threads, each step a bounded sample.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from vpux_plugin_b200 import abi, workloads as wl  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
+
+# DRAM traffic per element of the dominant kernel from the committed ncu capture of a smaller case of the same
+# kernel (dram__bytes_read.sum + dram__bytes_write.sum) / elements; traffic grows in proportion to the
+# elements processed. None until a capture exists for the kernel.
+NCU_TRAFFIC_BYTES_PER_ELEM = {"c4": None, "c5slab": None, "c2": None, "c3": None, "c1": None}
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--workload", default="c4")
+    p.add_argument("--impl", default="b200")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-cpu", action="store_true")
+    p.add_argument("--scale", type=float, default=1.0, help="fraction of the layer count (for profiling captures)")
+    p.add_argument("--profile", action="store_true",
+                   help="profiling capture mode: no end-to-end / CPU legs, warm-up count taken as given")
+    return p.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# workload definitions
+# ---------------------------------------------------------------------------------------------------------
+class Workload:
+    def __init__(self, key, scale):
+        self.key = key
+        if key == "c4":
+            layers = max(1, int(round(32 * scale)))
+            self.tensors = wl.llama2_7b_tensors(layers=layers)
+            self.spec = wl.spec_u4_group(128)
+            self.desc = ("c4: Llama-2-7B-shaped linear weights (%d layers + lm_head), fp16 N(0,0.02) with 1/1024 "
+                         "outliers x20 -> per-group(128) asymmetric u4, bit-packed, fp16 scales + packed u4 zero "
+                         "points" % layers)
+            self.alg_bytes_per_elem = 2.0 + 0.5 + (2.0 + 0.5) / 128.0
+            self.kernel = "k_group<half,128>"
+            self.shard_mode = 0
+        elif key == "c5slab":
+            # one eighth (by output-channel slabs) of the Llama-3-70B-shaped set: what each GPU of an 8-GPU job holds
+            layers = max(1, int(round(80 * scale)))
+            self.tensors = wl.llama3_70b_tensors(layers=layers)
+            self.spec = wl.spec_i8_sym(abi.VF_DT_F16)
+            self.desc = ("c5slab: 1/8 output-channel slab of Llama-3-70B-shaped weights (%d layers + embed + lm_head), "
+                         "bf16 N(0,0.02) -> per-channel symmetric i8 + dequantized fp16 copy" % layers)
+            self.alg_bytes_per_elem = 2.0 + 1.0 + 2.0
+            self.kernel = "k_row<bf16>"
+            self.shard_mode = 1
+        else:
+            raise SystemExit(f"workload {key} is measured by tests/ and profiles/, not by bench.py")
+        self.seed = wl.SEEDS["c4" if key == "c4" else "c5"]
+
+
+def shard(workload, world, rank, slab_world=None):
+    """[(TensorSpec, row_begin, row_end)] owned by `rank`."""
+    from vpux_plugin_b200.lib import plan_shards
+    ts = workload.tensors
+    if workload.key == "c5slab":
+        # fixed 8-way slabbing defines the per-GPU unit of work; rank r of an N-GPU job takes slab r
+        rb, re = plan_shards(1, 8, [t.nbytes for t in ts], [t.rows for t in ts], 1)
+        return [(t, int(rb[i, rank % 8]), int(re[i, rank % 8])) for i, t in enumerate(ts)]
+    rb, re = plan_shards(0, world, [t.nbytes for t in ts], [t.rows for t in ts], 1)
+    return [(t, int(rb[i, rank]), int(re[i, rank])) for i, t in enumerate(ts) if re[i, rank] > rb[i, rank]]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", uuid, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.f.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the CPU arm (oracle port of the reference's fold code)
+# ---------------------------------------------------------------------------------------------------------
+def cpu_arm(workload, budget_s, steps=1, warmup=0):
+    """Times the oracle on a bounded sample of `workload`; returns (GB/s, cores, sample description, ms/step)."""
+    from oracle import Oracle
+    cores = os.cpu_count() or 1
+    cpu = Oracle(nthreads=cores)
+    t0 = workload.tensors[0]
+    cols = t0.shape[1]
+    rows = min(t0.rows, 512)
+
+    def run(rows):
+        spec = wl.TensorSpec(t0.name, (rows, cols), t0.dtype, t0.sigma, t0.tensor_id, t0.outlier_mult, t0.outlier_log2)
+        x = cpu.synth_fill(spec.synth_spec(workload.seed), spec.numel)
+        tt = abi.TType([rows, cols], t0.dtype)
+        c, keep = abi.make_content(tt, x)
+        n = rows * cols
+        outs = abi.QuantOutputs()
+        outs.mem_kind = abi.VF_MEM_HOST
+        if workload.key == "c4":
+            units = n // 128
+            f16, u4 = np.zeros(units, np.uint16), np.zeros((units + 1) // 2, np.uint8)
+            outs.scales_f16, outs.zps_u4_packed = f16.ctypes.data, u4.ctypes.data
+            tr, ntr, ob = abi.make_transforms([wl.t_bitpack()]), 1, n // 2
+        else:
+            dq = np.zeros(n, np.uint16)
+            outs.dequant, outs.dequant_dtype, outs.dequant_bytes = dq.ctypes.data, abi.VF_DT_F16, dq.nbytes
+            tr, ntr, ob = abi.make_transforms([]), 0, n
+        dst = np.zeros(ob, np.uint8)
+        t = time.perf_counter()
+        cpu.quantize_fold(c, workload.spec, tr, ntr, dst, ob, outs)
+        return time.perf_counter() - t, n * abi.DTYPE_BITS[t0.dtype] // 8
+
+    dt, nb = run(rows)  # calibration
+    rate = nb / dt
+    per_step_budget = budget_s / max(1, steps + warmup)
+    rows = int(min(t0.rows * 4, max(rows, rate * per_step_budget / (cols * abi.DTYPE_BITS[t0.dtype] // 8))))
+    rows = max(64, rows // 64 * 64)
+    for _ in range(warmup):
+        run(rows)
+    times = []
+    for _ in range(steps):
+        dt, nb = run(rows)
+        times.append(dt)
+    tot = sum(times)
+    sample = f"{rows}x{cols} {'fp16' if t0.dtype == abi.VF_DT_F16 else 'bf16'} slab of tensor '{t0.name}' ({nb / 1e6:.1f} MB) per step"
+    return nb * steps / tot / 1e9, cores, sample, tot / steps * 1e3
+
+
+def reference_arm(args, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    v, cores, sample, ms = cpu_arm(workload, budget_s=60.0, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": "weight_fold_input_throughput", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload.desc},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU port of the reference's fold code (the reference itself needs MLIR/OpenVINO and cannot be built here)",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the GPU arm
+# ---------------------------------------------------------------------------------------------------------
+def gpu_arm(args, workload):
+    import torch
+    import torch.distributed as dist
+
+    from vpux_plugin_b200.lib import Library
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    stream = torch.cuda.Stream(device=dev)  # the library launches on this stream; the timing events are recorded on it
+    torch.cuda.set_stream(stream)
+    lib = Library(device=local, stream=stream.cuda_stream)
+
+    mine = shard(workload, world, rank)
+    is_c4 = workload.key == "c4"
+
+    # ---- device-resident buffers (allocated and filled outside the timed region) ------------------------
+    jobs = (abi.QuantJob * len(mine))()
+    keep = []
+    in_bytes = 0
+    elems = 0
+    tr = abi.make_transforms([wl.t_bitpack()] if is_c4 else [])
+    ntr = 1 if is_c4 else 0
+    host_jobs = (abi.QuantJob * len(mine))()
+    h2d = d2h = 0
+    for j, (t, r0, r1) in enumerate(mine):
+        rows, cols = r1 - r0, t.row_len
+        n = rows * cols
+        es = abi.DTYPE_BITS[t.dtype] // 8
+        src = torch.empty(n * es, dtype=torch.uint8, device=dev)
+        lib.synth_fill_device(t.synth_spec(workload.seed, r0 * cols), src.data_ptr(), n)
+        tt = abi.TType([rows, cols], t.dtype)
+        outs = abi.QuantOutputs()
+        outs.mem_kind = abi.VF_MEM_DEVICE
+        if is_c4:
+            units = n // 128
+            dst = torch.empty(n // 2, dtype=torch.uint8, device=dev)
+            s16 = torch.empty(units, dtype=torch.int16, device=dev)
+            z4 = torch.empty((units + 1) // 2, dtype=torch.uint8, device=dev)
+            outs.scales_f16, outs.zps_u4_packed = s16.data_ptr(), z4.data_ptr()
+            side = [s16, z4]
+        else:
+            dst = torch.empty(n, dtype=torch.uint8, device=dev)
+            dq = torch.empty(n, dtype=torch.int16, device=dev)
+            sc = torch.empty(rows, dtype=torch.float64, device=dev)
+            outs.dequant, outs.dequant_dtype, outs.dequant_bytes = dq.data_ptr(), abi.VF_DT_F16, n * 2
+            outs.scales = sc.data_ptr()
+            side = [dq, sc]
+        c, k = abi.make_content(tt, None, ptr=src.data_ptr(), nbytes=n * es, mem_kind=abi.VF_MEM_DEVICE)
+        jb = jobs[j]
+        jb.base, jb.spec, jb.t, jb.n = c, workload.spec, tr, ntr
+        jb.dst, jb.dst_bytes, jb.dst_mem_kind, jb.outs = dst.data_ptr(), dst.numel(), abi.VF_MEM_DEVICE, outs
+        keep += [src, dst, side, k, tt]
+        in_bytes += n * es
+        elems += n
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            tms = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms = float(tms.item())
+        return ms
+
+    uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid).replace("GPU-", "")
+    total_in = torch.tensor([float(in_bytes), float(elems)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(total_in)
+    total_in_bytes, total_elems = float(total_in[0].item()), float(total_in[1].item())
+
+    warmup = args.warmup if args.profile else max(3, args.warmup)
+    sampler = ClockSampler(uuid) if rank == 0 else None
+    l0 = lib.launch_count
+    ms = timed(lambda: lib.quantize_fold_batch(jobs), args.steps, warmup)
+    launches = (lib.launch_count - l0) // (args.steps + warmup)  # library kernels launched per step
+    clocks = sampler.stop() if sampler else None
+    value = total_in_bytes * args.steps / (ms * 1e-3) / 1e9
+
+    # ---- end to end: pinned host buffers in and out, copies inside the timed region ----------------------
+    e2e = None
+    if not args.no_e2e and not args.profile:
+        hk = []
+        for j, (t, r0, r1) in enumerate(mine):
+            rows, cols = r1 - r0, t.row_len
+            n = rows * cols
+            es = abi.DTYPE_BITS[t.dtype] // 8
+            src_dev = keep[5 * j]
+            hin = torch.empty(n * es, dtype=torch.uint8, pin_memory=True)
+            hin.copy_(src_dev)
+            tt = abi.TType([rows, cols], t.dtype)
+            outs = abi.QuantOutputs()
+            outs.mem_kind = abi.VF_MEM_HOST_PINNED
+            if is_c4:
+                units = n // 128
+                hdst = torch.empty(n // 2, dtype=torch.uint8, pin_memory=True)
+                h16 = torch.empty(units, dtype=torch.int16, pin_memory=True)
+                h4 = torch.empty((units + 1) // 2, dtype=torch.uint8, pin_memory=True)
+                outs.scales_f16, outs.zps_u4_packed = h16.data_ptr(), h4.data_ptr()
+                side = [h16, h4]
+                d2h += hdst.numel() + units * 2 + (units + 1) // 2
+            else:
+                hdst = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+                hdq = torch.empty(n, dtype=torch.int16, pin_memory=True)
+                hsc = torch.empty(rows, dtype=torch.float64, pin_memory=True)
+                outs.dequant, outs.dequant_dtype, outs.dequant_bytes = hdq.data_ptr(), abi.VF_DT_F16, n * 2
+                outs.scales = hsc.data_ptr()
+                side = [hdq, hsc]
+                d2h += n + n * 2 + rows * 8
+            c, k = abi.make_content(tt, None, ptr=hin.data_ptr(), nbytes=n * es, mem_kind=abi.VF_MEM_HOST_PINNED)
+            jb = host_jobs[j]
+            jb.base, jb.spec, jb.t, jb.n = c, workload.spec, tr, ntr
+            jb.dst, jb.dst_bytes, jb.dst_mem_kind, jb.outs = hdst.data_ptr(), hdst.numel(), abi.VF_MEM_HOST_PINNED, outs
+            hk += [hin, hdst, side, k, tt]
+            h2d += n * es
+        e2e_steps = min(args.steps, 5)
+        # host wall clock brackets a fully synchronous call (the batch call returns after the last D2H)
+        for _ in range(1):
+            lib.quantize_fold_batch(host_jobs)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            lib.quantize_fold_batch(host_jobs)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        barrier()
+        if world > 1:
+            tdt = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(tdt, op=dist.ReduceOp.MAX)
+            dt = float(tdt.item())
+            tb = torch.tensor([float(h2d), float(d2h)], device=dev, dtype=torch.float64)
+            dist.all_reduce(tb)
+            h2d, d2h = int(tb[0].item()), int(tb[1].item())
+        e2e = {"value": total_in_bytes * e2e_steps / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
+               "path": "vf_quantize_fold_batch with pinned host input and output buffers"}
+        del hk
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    # roofline of the dominant kernel: every launch in the timed region is that kernel; per-GPU figure
+    alg_bytes = total_elems / world * workload.alg_bytes_per_elem * args.steps
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    tpe = NCU_TRAFFIC_BYTES_PER_ELEM.get(workload.key)
+    n_launch = max(1, launches)
+    roofline = {"bound": "hbm", "kernel": workload.kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": peak_src,
+                "algorithmic_bytes_per_launch": total_elems / world * workload.alg_bytes_per_elem / n_launch,
+                "avg_launch_us": ms * 1e3 / args.steps / n_launch,
+                "traffic": (tpe * total_elems / world / n_launch) if tpe else None}
+
+    cpu = None
+    if not args.no_cpu and not args.profile and world == 1:
+        v, cores, sample, _ = cpu_arm(workload, budget_s=15.0)
+        cpu = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+
+    line = {
+        "metric": "weight_fold_input_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak" if workload.key == "c5slab" else "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload.desc, "input_bytes": int(total_in_bytes), "tensors_rank0": len(mine),
+                   "sharding": "whole tensors, longest-processing-time-first" if workload.shard_mode == 0 else
+                   "output-channel slabs", "l2": "inputs (GBs) far larger than the 126 MB L2; no flush needed"},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": int(launches * args.steps),
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    workload = Workload(args.workload, args.scale)
+    if args.impl == "reference":
+        reference_arm(args, workload)
+    else:
+        gpu_arm(args, workload)
+
+
+if __name__ == "__main__":
+    main()

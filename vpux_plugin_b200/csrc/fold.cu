@@ -3,7 +3,7 @@
 #include <algorithm>
 #include <cmath>
 
-#include "kernels.h"
+#include "fused.h"
 
 namespace vf {
 
@@ -580,11 +580,6 @@ void check_spec(const vf_quant_spec& s) {
 
 }  // namespace
 
-// fused single-pass path (fold_fused.cu); returns false when the pattern is not covered
-bool try_fused_quantize_fold(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec, const vf_transform* t,
-                             int n, void* dst, uint64_t dst_bytes, int dst_kind, uint64_t* dst_written,
-                             const vf_quant_outputs* outs, vf_stats* stats);
-
 // Unfused composition with the general kernels: unit statistics, Quantize with the derived parameters, the
 // remaining transformations, copyTo. Also the reference implementation the fused kernels are tested against.
 static void quantize_fold_general(vf_ctx* ctx, DContent& base, const vf_quant_spec& spec, const vf_transform* t, int n,
@@ -701,10 +696,14 @@ int vf_quantize_fold(vf_ctx* ctx, const vf_content* base, const vf_quant_spec* s
         CallScope scope(ctx, stats);
         DContent in = upload_base(ctx, *base, stats);
         const bool allow_fused = !(ctx->opt_flags & VF_OPT_DISABLE_FUSION);
-        if (!allow_fused || !try_fused_quantize_fold(ctx, in, *spec, t, n, dst, dst_bytes, dst_mem_kind, dst_written, outs, stats)) {
+        std::vector<FusedJob> fj(1);
+        if (allow_fused && fused_prepare(ctx, in, *spec, t, n, dst, dst_bytes, dst_mem_kind, outs, fj[0])) {
+            fused_launch(ctx, fj, 0, 1);
+            fused_finish(ctx, fj[0], dst_written, stats);
+            if (stats) stats->fused = 1;
+        } else {
+            fj.clear();
             quantize_fold_general(ctx, in, *spec, t, n, dst, dst_bytes, dst_mem_kind, dst_written, outs, stats);
-        } else if (stats) {
-            stats->fused = 1;
         }
         scope.finish();
     });
@@ -714,18 +713,51 @@ int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats*
     return guard(err, errlen, [&] {
         if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
         CallScope scope(ctx, stats);
-        // uploads and kernels of all jobs are enqueued back to back; one synchronisation at the end
+        // Jobs that map onto a fused kernel are collected into job tables: consecutive compatible jobs run as
+        // ONE launch. Device-resident jobs therefore cost one launch per pattern for the whole batch. Jobs with
+        // host memory are flushed every kFlushBytes of device staging so that uploads, kernels and downloads
+        // of successive sub-batches follow each other on the stream with bounded staging memory. One
+        // synchronisation at the end.
+        constexpr uint64_t kFlushBytes = 1ull << 30;
+        const bool allow_fused = !(ctx->opt_flags & VF_OPT_DISABLE_FUSION);
+        std::vector<DContent> bases;
+        std::vector<FusedJob> fj;
+        std::vector<int> owner;
+        uint64_t staged = 0;
+        auto flush = [&] {
+            if (fj.empty()) return;
+            fused_launch(ctx, fj, 0, fj.size());
+            for (size_t k = 0; k < fj.size(); ++k) {
+                uint64_t w = 0;
+                fused_finish(ctx, fj[k], &w, stats);
+                jobs[owner[k]].dst_written = w;
+            }
+            if (stats) stats->fused = 1;
+            fj.clear();
+            bases.clear();
+            owner.clear();
+            staged = 0;
+        };
         for (int j = 0; j < njobs; ++j) {
             vf_quant_job& jb = jobs[j];
             jb.status = VF_OK;
             check_spec(jb.spec);
             DContent in = upload_base(ctx, jb.base, stats);
-            uint64_t w = 0;
-            const bool allow_fused = !(ctx->opt_flags & VF_OPT_DISABLE_FUSION);
-            if (!allow_fused || !try_fused_quantize_fold(ctx, in, jb.spec, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, &w, &jb.outs, stats))
+            FusedJob cand;
+            if (allow_fused && fused_prepare(ctx, in, jb.spec, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, &jb.outs, cand)) {
+                staged += in.own.bytes + cand.tc.buf.bytes + cand.td.buf.bytes;
+                bases.push_back(std::move(in));
+                fj.push_back(std::move(cand));
+                owner.push_back(j);
+                if (staged >= kFlushBytes) flush();
+            } else {
+                flush();
+                uint64_t w = 0;
                 quantize_fold_general(ctx, in, jb.spec, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, &w, &jb.outs, stats);
-            jb.dst_written = w;
+                jb.dst_written = w;
+            }
         }
+        flush();
         scope.finish();
     });
 }

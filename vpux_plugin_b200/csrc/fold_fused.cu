@@ -1,9 +1,9 @@
 // Pattern matcher in front of the fused weight-quantization kernels: recognises the transformation lists
 // that upstream passes build for weights (Quantize [+ Reorder<NHWC>] [+ PadWithZero] | [+ BitPack]) and maps
-// them onto one launch of kernels_rowquant.cu. Anything else returns false and takes the general path.
+// them onto the job tables of kernels_rowquant.cu. Anything else is declined and takes the general path.
 #include <algorithm>
 
-#include "kernels.h"
+#include "fused.h"
 
 namespace vf {
 
@@ -28,33 +28,27 @@ bool tail_is_identity(int64_t qmin, int64_t qmax) {
     return true;
 }
 
-struct Tmp {  // device staging for an output that lives in host memory
-    DBuf buf;
-    void* user = nullptr;
-    int kind = VF_MEM_DEVICE;
-    size_t bytes = 0;
-    void* bind(vf_ctx* ctx, void* u, int k, size_t n) {
-        user = u;
-        kind = k;
-        bytes = n;
-        if (!u) return nullptr;
-        if (k == VF_MEM_DEVICE) return u;
-        buf = DBuf(ctx, n);
-        return buf.p;
-    }
-    void flush(vf_ctx* ctx, vf_stats* stats) {
-        if (user && kind != VF_MEM_DEVICE) {
-            copy_out(ctx, user, kind, buf.p, bytes);
-            if (stats) stats->d2h_bytes += bytes;
-        }
-    }
-};
-
 }  // namespace
 
-bool try_fused_quantize_fold(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec, const vf_transform* t,
-                             int n, void* dst, uint64_t dst_bytes, int dst_kind, uint64_t* dst_written,
-                             const vf_quant_outputs* outs, vf_stats* stats) {
+void* OutStage::bind(vf_ctx* ctx, void* u, int k, size_t n) {
+    user = u;
+    kind = k;
+    bytes = n;
+    if (!u) return nullptr;
+    if (k == VF_MEM_DEVICE) return u;
+    buf = DBuf(ctx, n);
+    return buf.p;
+}
+
+void OutStage::flush(vf_ctx* ctx, vf_stats* stats) {
+    if (user && kind != VF_MEM_DEVICE) {
+        copy_out(ctx, user, kind, buf.p, bytes);
+        if (stats) stats->d2h_bytes += bytes;
+    }
+}
+
+bool fused_prepare(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec, const vf_transform* t, int n,
+                   void* dst, uint64_t dst_bytes, int dst_kind, const vf_quant_outputs* outs, FusedJob& job) {
     const Type& bt = base.type;
     if (base.splat || bt.elem.quantized()) return false;
     if (base.storage != VF_DT_F32 && base.storage != VF_DT_F16 && base.storage != VF_DT_BF16) return false;
@@ -62,7 +56,8 @@ bool try_fused_quantize_fold(vf_ctx* ctx, const DContent& base, const vf_quant_s
     if (spec.qmax - spec.qmin > 255 || !tail_is_identity(spec.qmin, spec.qmax)) return false;
     if (bt.numel() == 0) return false;
 
-    RowQuantArgs a{};
+    RowQuantArgs& a = job.a;
+    a = RowQuantArgs{};
     a.in = base.d;
     a.in_dt = base.storage;
     a.range_mode = spec.range_mode;
@@ -118,40 +113,54 @@ bool try_fused_quantize_fold(vf_ctx* ctx, const DContent& base, const vf_quant_s
         const int ddt = outs->dequant_dtype;
         if (ddt != VF_DT_F16 && ddt != VF_DT_F32 && ddt != VF_DT_BF16) return false;
         if (a.khw > 0 || a.rows_pad != a.rows || a.pack4) return false;
+        a.dequant_dt = ddt;
     }
+    if (outs && outs->zps_u4_packed && a.group == 0) return false;  // packed zero points: per-group kernel only
 
-    Tmp tc, ts, tz, t16, t4, td;
-    a.codes = tc.bind(ctx, dst, dst_kind, out_bytes);
-    if (!a.codes) raise(VF_ERR_INVALID_ARG, "dst is NULL");
-    uint64_t dq_bytes = 0;
+    if (!dst) raise(VF_ERR_INVALID_ARG, "dst is NULL");
+    if (dst_bytes < out_bytes) raise(VF_ERR_BUFFER_TOO_SMALL, "Byte sizes of the target buffer '%llu' is smaller then storage buffer '%llu'", (unsigned long long)dst_bytes, (unsigned long long)out_bytes);
+    a.codes = job.tc.bind(ctx, dst, dst_kind, out_bytes);
+    job.out_bytes = out_bytes;
+    job.dq_bytes = 0;
     if (outs) {
         const int k = outs->mem_kind;
-        a.scales = static_cast<double*>(ts.bind(ctx, outs->scales, k, size_t(units) * 8));
-        a.zps = static_cast<int64_t*>(tz.bind(ctx, outs->zps, k, size_t(units) * 8));
-        a.scales_f16 = static_cast<uint16_t*>(t16.bind(ctx, outs->scales_f16, k, size_t(units) * 2));
-        a.zps_u4 = static_cast<uint8_t*>(t4.bind(ctx, outs->zps_u4_packed, k, size_t((units + 1) / 2)));
+        a.scales = static_cast<double*>(job.ts.bind(ctx, outs->scales, k, size_t(units) * 8));
+        a.zps = static_cast<int64_t*>(job.tz.bind(ctx, outs->zps, k, size_t(units) * 8));
+        a.scales_f16 = static_cast<uint16_t*>(job.t16.bind(ctx, outs->scales_f16, k, size_t(units) * 2));
+        a.zps_u4 = static_cast<uint8_t*>(job.t4.bind(ctx, outs->zps_u4_packed, k, size_t((units + 1) / 2)));
         if (outs->dequant) {
-            dq_bytes = uint64_t(bt.numel()) * uint64_t(dtype_bits(outs->dequant_dtype) / 8);
-            if (outs->dequant_bytes < dq_bytes) raise(VF_ERR_BUFFER_TOO_SMALL, "dequantized copy needs %llu bytes", (unsigned long long)dq_bytes);
-            a.dequant = td.bind(ctx, outs->dequant, k, dq_bytes);
-            a.dequant_dt = outs->dequant_dtype;
+            job.dq_bytes = uint64_t(bt.numel()) * uint64_t(dtype_bits(outs->dequant_dtype) / 8);
+            if (outs->dequant_bytes < job.dq_bytes) raise(VF_ERR_BUFFER_TOO_SMALL, "dequantized copy needs %llu bytes", (unsigned long long)job.dq_bytes);
+            a.dequant = job.td.bind(ctx, outs->dequant, k, job.dq_bytes);
         }
     }
-    if (rowquant_kind(a) == 0) return false;
-    if (a.zps_u4 && a.group == 0) return false;  // packed zero points come from the per-group kernel only
-    if (dst_bytes < out_bytes) raise(VF_ERR_BUFFER_TOO_SMALL, "Byte sizes of the target buffer '%llu' is smaller then storage buffer '%llu'", (unsigned long long)dst_bytes, (unsigned long long)out_bytes);
+    job.kind = rowquant_kind(a);
+    return job.kind != 0;
+}
 
-    launch_rowquant(ctx, a);
+void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end) {
+    // consecutive jobs with the same kernel and launch-uniform parameters share one launch
+    size_t i = begin;
+    std::vector<RowQuantArgs> table;
+    while (i < end) {
+        size_t j = i + 1;
+        while (j < end && jobs[j].kind == jobs[i].kind && rowquant_compatible(jobs[i].a, jobs[j].a)) ++j;
+        table.clear();
+        for (size_t k = i; k < j; ++k) table.push_back(jobs[k].a);
+        launch_rowquant_batch(ctx, jobs[i].kind, table);
+        i = j;
+    }
+}
 
-    tc.flush(ctx, stats);
-    ts.flush(ctx, stats);
-    tz.flush(ctx, stats);
-    t16.flush(ctx, stats);
-    t4.flush(ctx, stats);
-    td.flush(ctx, stats);
-    if (dst_written) *dst_written = out_bytes;
-    if (stats) stats->bytes_out += out_bytes + dq_bytes;
-    return true;
+void fused_finish(vf_ctx* ctx, FusedJob& job, uint64_t* dst_written, vf_stats* stats) {
+    job.tc.flush(ctx, stats);
+    job.ts.flush(ctx, stats);
+    job.tz.flush(ctx, stats);
+    job.t16.flush(ctx, stats);
+    job.t4.flush(ctx, stats);
+    job.td.flush(ctx, stats);
+    if (dst_written) *dst_written = job.out_bytes;
+    if (stats) stats->bytes_out += job.out_bytes + job.dq_bytes;
 }
 
 }  // namespace vf

@@ -105,8 +105,11 @@ struct RowQuantArgs {
     uint8_t* zps_u4;
     void* dequant;
     int dequant_dt;
+    int64_t unit_begin;      // filled by launch_rowquant_batch: index of this job's first chunk / row in the launch
 };
-void launch_rowquant(vf_ctx* ctx, const RowQuantArgs& a);
+// Launches all `jobs` (same kind, pairwise rowquant_compatible) with ONE kernel over a device job table.
+void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& jobs);
+bool rowquant_compatible(const RowQuantArgs& a, const RowQuantArgs& b);
 // 0: no fused kernel covers `a`; 1: per-group kernel; 2: long-row kernel; 3: convolution-row kernel
 int rowquant_kind(const RowQuantArgs& a);
 // derived parameters -> float16 scales and 4-bit packed zero points (either output may be NULL)
