@@ -1,13 +1,13 @@
 // Fused weight-quantization kernels (the hot path): range statistics, calcScaleAndZeroPoint, Quantize and
 // the store stage (BitPack / OIYX->OYXI reorder / zero padding / Dequantize copy) in ONE pass over the
 // input. All of them are bandwidth-bound: the unit (group chunk or row) is staged in shared memory with
-// 16-byte asynchronous copies (cp.async), statistics are reduced on packed 16-bit pairs with shuffles, the
-// quantization sweep re-reads shared memory, stores are 4..16 bytes per lane and coalesced. One launch
-// processes a whole table of tensors so that small tensors do not pay a launch and a tail each.
+// 16-byte asynchronous copies (cp.async), statistics run on packed 16-bit pairs, the quantization sweep
+// re-reads shared memory, stores are 16 bytes per lane. One launch processes a whole table of tensors so that
+// small tensors do not pay a launch and a tail each.
 //
 // Arithmetic contract: codes equal the reference's fakeQuantize chain bit for bit. The per-element fast path
 // evaluates  t = fma(x, inv, c)  with inv = fl((L-1)/range), c = fl(-inLow*inv)  instead of the reference's
-// fl(fl((x-inLow)/range) * (L-1)); both lie within 7.6e-5 of each other for 8-bit ranges, so whenever t is
+// fl(fl((x-inLow)/range) * (L-1)); both lie within 8.4e-5 of each other for 8-bit ranges, so whenever t is
 // further than kGuard from a rounding boundary (x.5) both round to the same integer. Elements inside the guard
 // band (about 0.04 %) are recomputed with the exact operation sequence.
 #include <algorithm>
@@ -26,7 +26,7 @@ constexpr float kGuard = 2.0e-4f;
 
 struct UnitQ {  // per-unit constants
     float inv;     // fl((L-1) / range)
-    float c;       // fl(-inLow * inv) (+ bias, see k_row)
+    float c;       // fl(-inLow * inv) (+ qmin where noted)
     float in_low;  // exact path
     float range;   // fl(inHigh - inLow)
 };
@@ -39,7 +39,7 @@ struct LaunchParams {  // uniform over all jobs of one launch
     int64_t total_units;  // chunks (k_group) or rows (k_row / k_conv) over all jobs
 };
 
-// Per-unit parameters from the unit's range; executed by one lane per unit.
+// Per-unit parameters from the unit's range.
 __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchParams& p, double& scale, long long& zp,
                                             UnitQ& u, int* flags) {
     mn = fminf(mn, 0.f);  // the range always contains zero (calcScaleAndZeroPoint requires it)
@@ -81,12 +81,14 @@ struct P2<__half> {
     using T = __half2;
     static __device__ __forceinline__ float lo(uint32_t w) { return __half2float(__ushort_as_half(uint16_t(w))); }
     static __device__ __forceinline__ float hi(uint32_t w) { return __half2float(__ushort_as_half(uint16_t(w >> 16))); }
+    static __device__ __forceinline__ float2 both(uint32_t w) { return __half22float2(*reinterpret_cast<__half2*>(&w)); }
 };
 template <>
 struct P2<__nv_bfloat16> {
     using T = __nv_bfloat162;
     static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
     static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+    static __device__ __forceinline__ float2 both(uint32_t w) { return make_float2(lo(w), hi(w)); }
 };
 
 template <typename InT>
@@ -98,22 +100,29 @@ __device__ __forceinline__ uint32_t as_u32(T2 v) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// min and max of the eight 16-bit values of a 16-byte vector, as (min, -max) packed in one 32-bit pair so that
-// a single packed-min reduces both.
+// running element-wise min / max over 16-byte vectors (two 32-bit pair registers)
 template <typename InT>
-__device__ __forceinline__ uint32_t minnegmax8(const uint4& d) {
+struct MinMax2 {
     using T2 = typename P2<InT>::T;
-    const T2 a = as_p2<InT>(d.x), b = as_p2<InT>(d.y), c = as_p2<InT>(d.z), e = as_p2<InT>(d.w);
-    const T2 mn = __hmin2(__hmin2(a, b), __hmin2(c, e));
-    const T2 mx = __hmax2(__hmax2(a, b), __hmax2(c, e));
-    const T2 mn1 = __hmin2(mn, __lowhigh2highlow(mn));        // both halves: min
-    const T2 ng1 = __hneg2(__hmax2(mx, __lowhigh2highlow(mx)));  // both halves: -max
-    return __byte_perm(as_u32(mn1), as_u32(ng1), 0x5410);     // (lo = min, hi = -max)
-}
-template <typename InT>
-__device__ __forceinline__ uint32_t pmin(uint32_t x, uint32_t y) {
-    return as_u32(__hmin2(as_p2<InT>(x), as_p2<InT>(y)));
-}
+    T2 mn, mx;
+    __device__ __forceinline__ MinMax2() {
+        mn = as_p2<InT>(0u);
+        mx = as_p2<InT>(0u);
+    }
+    __device__ __forceinline__ void add(const uint4& d) {
+        const T2 a = as_p2<InT>(d.x), b = as_p2<InT>(d.y), c = as_p2<InT>(d.z), e = as_p2<InT>(d.w);
+        mn = __hmin2(mn, __hmin2(__hmin2(a, b), __hmin2(c, e)));
+        mx = __hmax2(mx, __hmax2(__hmax2(a, b), __hmax2(c, e)));
+    }
+    __device__ __forceinline__ float min_f() const {
+        const uint32_t w = as_u32(mn);
+        return fminf(P2<InT>::lo(w), P2<InT>::hi(w));
+    }
+    __device__ __forceinline__ float max_f() const {
+        const uint32_t w = as_u32(mx);
+        return fmaxf(P2<InT>::lo(w), P2<InT>::hi(w));
+    }
+};
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
     const uint32_t s = uint32_t(__cvta_generic_to_shared(smem_dst));
@@ -132,8 +141,8 @@ __device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float
     bool bad = false;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float x0 = P2<InT>::lo(w[i]), x1 = P2<InT>::hi(w[i]);
-        const float t0 = __fmaf_rn(x0, inv, c), t1 = __fmaf_rn(x1, inv, c);
+        const float2 x = P2<InT>::both(w[i]);
+        const float t0 = __fmaf_rn(x.x, inv, c), t1 = __fmaf_rn(x.y, inv, c);
         m[2 * i] = __fadd_rn(t0, kMagic);
         m[2 * i + 1] = __fadd_rn(t1, kMagic);
         const float r0 = __fsub_rn(t0, __fsub_rn(m[2 * i], kMagic));
@@ -170,6 +179,21 @@ __device__ __noinline__ uint2 quant8_exact_bytes(uint4 d, float in_low, float ra
         }                                                                                          \
     } while (0)
 
+// eight patterns (kMagicBits + n) -> eight nibbles of n in one word, element 0 in the low nibble (BitPack<4>)
+__device__ __forceinline__ uint32_t pack_nibbles(const float* m) {
+    uint32_t w = __float_as_uint(m[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) w += __float_as_uint(m[i]) << (4 * i);
+    constexpr uint32_t kC = uint32_t(kMagicBits) * 0x11111111u;  // the magic part of the sum
+    return w - kC;
+}
+// four patterns -> four low bytes
+__device__ __forceinline__ uint32_t pack_bytes4(const float* m) {
+    const uint32_t a = __byte_perm(__float_as_uint(m[0]), __float_as_uint(m[1]), 0x0040);
+    const uint32_t b = __byte_perm(__float_as_uint(m[2]), __float_as_uint(m[3]), 0x0040);
+    return __byte_perm(a, b, 0x5410);
+}
+
 // Dequantize + copyTo of one code into a 16-bit float type
 __device__ __forceinline__ uint16_t dequant16(int code, long long zp, double scale, int dt) {
     const float f = dequantize_exact(code, scale, zp);
@@ -188,119 +212,145 @@ __device__ __forceinline__ int find_job(const RowQuantArgs* __restrict__ jobs, i
 
 // ======================================================================================================
 // K_group: units of G consecutive elements (per-group quantization), 2-byte input.
-// A warp owns a chunk of 32 consecutive groups (32*G elements): each lane copies V = G/8 vectors into the
-// warp's shared-memory stage; every group is reduced by the G/8 lanes that hold it; lane g then derives the
-// parameters of group g (all 32 lanes busy in the FP64 section); parameters travel back by shuffle for the
-// quantization sweep. Warps loop over the chunks of all jobs of the launch.
+// A warp owns a chunk of 32 consecutive groups (32*G elements, contiguous in memory). The chunk is copied
+// into the warp's shared-memory stage with coalesced 16-byte cp.async (lane l copies vectors l, l+32, ...);
+// afterwards LANE g OWNS GROUP g: it reads the group's V = G/8 vectors back (XOR-swizzled so that both access
+// patterns are free of bank conflicts), reduces min/max on packed pairs, derives scale / zero point (all 32
+// lanes busy in the FP64 section), quantizes and stores its own 16-byte pieces. No shuffles on the data path.
+// Warps loop over the chunks of all jobs of the launch.
 // ======================================================================================================
 template <typename InT, int G, bool PACK4>
 __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
-    constexpr int V = G / 8;       // vectors per lane per chunk
-    constexpr int LPG = G / 8;     // lanes per group within one vector row
-    constexpr int GPL = 32 / LPG;  // groups completed per vector row
+    constexpr int V = G / 8;  // vectors per group = vectors per lane per chunk
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint4* stage = smem_u4 + wid * (V * 32);
     const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
 
+    int j = 0;
+    int64_t job_end = 0;  // first chunk of the next job
+    // job fields, reloaded only when the warp moves to another job
+    const InT* in = nullptr;
+    uint8_t* codes = nullptr;
+    double* o_scales = nullptr;
+    int64_t* o_zps = nullptr;
+    uint16_t* o_f16 = nullptr;
+    uint8_t* o_u4 = nullptr;
+    void* o_deq = nullptr;
+    int64_t total_groups = 0, unit_begin = 0;
+
     for (int64_t chunk = int64_t(blockIdx.x) * (blockDim.x >> 5) + wid; chunk < p.total_units; chunk += nwarps) {
-        const int j = find_job(jobs, p.njobs, chunk);
-        const RowQuantArgs& J = jobs[j];
-        const int64_t total_groups = J.rows * (J.cols / G);
-        const int64_t g0 = (chunk - J.unit_begin) * 32;
+        if (chunk >= job_end) {
+            j = find_job(jobs, p.njobs, chunk);
+            const RowQuantArgs J = jobs[j];
+            in = static_cast<const InT*>(J.in);
+            codes = static_cast<uint8_t*>(J.codes);
+            o_scales = J.scales;
+            o_zps = J.zps;
+            o_f16 = J.scales_f16;
+            o_u4 = J.zps_u4;
+            o_deq = J.dequant;
+            total_groups = J.rows * (J.cols / G);
+            unit_begin = J.unit_begin;
+            job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+        }
+        const int64_t g0 = (chunk - unit_begin) * 32;
         const int64_t total_elems = total_groups * G;
         const int64_t e0 = g0 * G;
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(J.in) + e0);
+        const uint4* src = reinterpret_cast<const uint4*>(in + e0);
 
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            const int64_t e = e0 + int64_t(v) * 256 + lane * 8;
-            cp_async16(stage + v * 32 + lane, src + v * 32 + lane, e < total_elems);
+            const int i = v * 32 + lane;  // vector index inside the chunk
+            cp_async16(stage + (i ^ ((i / V) & 7)), src + i, e0 + int64_t(i) * 8 < total_elems);
         }
-        cp_async_wait_all();  // each lane reads back only what it copied itself: no warp barrier needed
+        cp_async_wait_all();
+        __syncwarp();  // lanes read vectors copied by other lanes
 
-        // ---- statistics: lane g ends up with (min, -max) of group g0+g ---------------------------------
-        uint32_t mine = 0;
-#pragma unroll 4
-        for (int v = 0; v < V; ++v) {
-            uint32_t r = minnegmax8<InT>(stage[v * 32 + lane]);
+        // ---- statistics of group g0+lane ----------------------------------------------------------------
+        // vector k of this lane's group sits at the swizzled position of logical index lane*V + k
+        const int sw = lane & 7;
+        const int base = lane * V;
+#define VF_MINE(k) stage[(base + (k)) ^ sw]
+        MinMax2<InT> mm;
 #pragma unroll
-            for (int o = LPG / 2; o > 0; o >>= 1) r = pmin<InT>(r, __shfl_xor_sync(0xffffffffu, r, o));
-            const uint32_t t = __shfl_sync(0xffffffffu, r, ((lane - v * GPL) & (GPL - 1)) * LPG);
-            if (lane / GPL == v) mine = t;
-        }
+        for (int k = 0; k < V; ++k) mm.add(VF_MINE(k));
 
-        // ---- parameters of group g0+lane ----------------------------------------------------------------
         double scale;
         long long zp;
         UnitQ u;
-        derive_unit(P2<InT>::lo(mine), -P2<InT>::hi(mine), p, scale, zp, u, flags);
+        derive_unit(mm.min_f(), mm.max_f(), p, scale, zp, u, flags);
         const int64_t g = g0 + lane;
         const bool g_ok = g < total_groups;
         if (g_ok) {
-            if (J.scales) J.scales[g] = scale;
-            if (J.zps) J.zps[g] = zp;
-            if (J.scales_f16) J.scales_f16[g] = f32_to_f16_bits(__double2float_rn(scale));
+            if (o_scales) o_scales[g] = scale;
+            if (o_zps) o_zps[g] = zp;
+            if (o_f16) o_f16[g] = f32_to_f16_bits(__double2float_rn(scale));
         }
-        if (J.zps_u4) {
+        if (o_u4) {
             const int hi = __shfl_down_sync(0xffffffffu, int(zp), 1);
             if ((lane & 1) == 0 && g_ok) {
                 const int hv = (g + 1 < total_groups) ? (hi & 0xF) : 0;
-                J.zps_u4[g >> 1] = uint8_t((hv << 4) | (int(zp) & 0xF));
+                o_u4[g >> 1] = uint8_t((hv << 4) | (int(zp) & 0xF));
             }
         }
 
-        // ---- quantize + store ----------------------------------------------------------------------------
+        // ---- quantize + store: the lane's group is G consecutive codes ----------------------------------
         const int add = p.qmin;  // code = n + qmin
-#pragma unroll 2
-        for (int v = 0; v < V; ++v) {
-            const int owner = v * GPL + lane / LPG;
-            const float inv = __shfl_sync(0xffffffffu, u.inv, owner);
-            const float c = __shfl_sync(0xffffffffu, u.c, owner);
-            const uint4 d = stage[v * 32 + lane];
-            float m[8];
-            const bool bad = quant8<InT>(d, inv, c, m);
-            if (__any_sync(0xffffffffu, bad)) {
-                const float in_low = __shfl_sync(0xffffffffu, u.in_low, owner);
-                const float range = __shfl_sync(0xffffffffu, u.range, owner);
-                if (bad) VF_QUANT8_EXACT(InT, d, in_low, range, p.lm1, 0, m);
-            }
-            const int64_t e = e0 + int64_t(v) * 256 + lane * 8;
-            const bool ok = e < total_elems;
-            int code[8];
+        if (PACK4) {
+            uint4* dst = reinterpret_cast<uint4*>(codes + (e0 >> 1) + int64_t(lane) * (G / 2));
+#pragma unroll 1
+            for (int k4 = 0; k4 < V / 4; ++k4) {  // four vectors = 32 codes = 16 packed bytes
+                uint32_t w[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) code[i] = __float_as_int(m[i]);  // kMagicBits + n
-            if (PACK4) {
-                // sum of (kMagicBits + n_i) << 4i; the constant part is removed once
-                uint32_t w = uint32_t(code[0]);
-#pragma unroll
-                for (int i = 1; i < 8; ++i) w += uint32_t(code[i]) << (4 * i);
-                constexpr uint32_t kC = uint32_t(kMagicBits) * 0x11111111u;
-                w -= kC;
-                if (add != 0) {  // signed 4-bit ranges: add qmin to every nibble, modulo 16
-                    const uint32_t q = uint32_t(add) & 0xFu;
-                    w = ((w & 0x0F0F0F0Fu) + q * 0x01010101u) & 0x0F0F0F0Fu | ((((w >> 4) & 0x0F0F0F0Fu) + q * 0x01010101u) & 0x0F0F0F0Fu) << 4;
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 d = VF_MINE(k4 * 4 + q);
+                    float m[8];
+                    if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, 0, m);
+                    w[q] = pack_nibbles(m);
+                    if (add != 0) {  // signed 4-bit ranges: add qmin to every nibble, modulo 16
+                        const uint32_t qq = (uint32_t(add) & 0xFu) * 0x01010101u;
+                        w[q] = (((w[q] & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) | (((((w[q] >> 4) & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) << 4);
+                    }
                 }
-                if (ok) reinterpret_cast<uint32_t*>(J.codes)[e >> 3] = w;
-            } else {
-                uint2 w;
-                w.x = uint32_t((code[0] + add) & 0xFF) | (uint32_t((code[1] + add) & 0xFF) << 8) |
-                      (uint32_t((code[2] + add) & 0xFF) << 16) | (uint32_t((code[3] + add) & 0xFF) << 24);
-                w.y = uint32_t((code[4] + add) & 0xFF) | (uint32_t((code[5] + add) & 0xFF) << 8) |
-                      (uint32_t((code[6] + add) & 0xFF) << 16) | (uint32_t((code[7] + add) & 0xFF) << 24);
-                if (ok) reinterpret_cast<uint2*>(J.codes)[e >> 3] = w;
+                if (g_ok) dst[k4] = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            if (J.dequant) {  // optional Dequantize copy (not on the benchmarked path): exact FP64 formula
-                const double sc = __shfl_sync(0xffffffffu, scale, owner);
-                const int z = __shfl_sync(0xffffffffu, int(zp), owner);
+        } else {
+            uint4* dst = reinterpret_cast<uint4*>(codes + e0 + int64_t(lane) * G);
+#pragma unroll 1
+            for (int k2 = 0; k2 < V / 2; ++k2) {  // two vectors = 16 codes = 16 bytes
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const uint4 d = VF_MINE(k2 * 2 + q);
+                    float m[8];
+                    if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, 0, m);
+                    if (add != 0) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) m[i] = __int_as_float(__float_as_int(m[i]) + add);
+                    }
+                    w[2 * q] = pack_bytes4(m);
+                    w[2 * q + 1] = pack_bytes4(m + 4);
+                }
+                if (g_ok) dst[k2] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        if (o_deq && g_ok) {  // optional Dequantize copy (not on the benchmarked path): exact FP64 formula
+            const int64_t eg = e0 + int64_t(lane) * G;
+#pragma unroll 1
+            for (int k = 0; k < V; ++k) {
+                const uint4 d = VF_MINE(k);
+                float m[8];
+                if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, 0, m);
+#pragma unroll 1
                 for (int i = 0; i < 8; ++i) {
-                    const int q = ((code[i] - kMagicBits) + add);
-                    if (!ok) continue;
-                    if (p.dequant_dt == VF_DT_F32) static_cast<float*>(J.dequant)[e + i] = dequantize_exact(q, sc, z);
-                    else static_cast<uint16_t*>(J.dequant)[e + i] = dequant16(q, z, sc, p.dequant_dt);
+                    const int q = (__float_as_int(m[i]) - kMagicBits) + add;
+                    if (p.dequant_dt == VF_DT_F32) static_cast<float*>(o_deq)[eg + k * 8 + i] = dequantize_exact(q, scale, zp);
+                    else static_cast<uint16_t*>(o_deq)[eg + k * 8 + i] = dequant16(q, zp, scale, p.dequant_dt);
                 }
             }
         }
+        __syncwarp();  // the stage is overwritten by the next chunk's copies
     }
 }
 
@@ -308,85 +358,103 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
 // K_row: one unit per row, 16-byte aligned rows of a [rows, cols] matrix (per-output-channel quantization of
 // linear weights), 2-byte input. One CTA per row, looping over the rows of all jobs; the row is staged in
 // shared memory. The optional Dequantize copy uses a per-row table of the L possible outputs (each entry
-// computed with the exact FP64 formula), so the sweep costs one shared-memory lookup per element.
+// computed with the exact FP64 formula, indexed by the code byte), so the sweep costs one shared-memory
+// lookup per element.
 // ======================================================================================================
-template <typename InT>
-__global__ void __launch_bounds__(256) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
+template <typename InT, int THREADS>
+__global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
     extern __shared__ uint4 smem_u4[];
-    __shared__ uint32_t s_red[8];
+    __shared__ float s_mn[THREADS / 32], s_mx[THREADS / 32];
     __shared__ UnitQ s_u;
     __shared__ double s_scale;
     __shared__ long long s_zp;
-    __shared__ uint32_t s_lut[256];  // dequantized value of code index n (16-bit types in the low half)
+    __shared__ uint32_t s_lut[256];  // dequantized value of code byte b (16-bit types in the low half)
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int bias = p.qmin;  // code = n + qmin
 
-    for (int64_t row = blockIdx.x; row < p.total_units; row += gridDim.x) {
-        const int j = find_job(jobs, p.njobs, row);
-        const RowQuantArgs& J = jobs[j];
-        const int64_t r = row - J.unit_begin;
-        const int64_t cols = J.cols;
-        const int nvec = int(cols >> 3);
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(J.in) + r * cols);
-        for (int i = tid; i < nvec; i += 256) cp_async16(smem_u4 + i, src + i, true);
-        cp_async_wait_all();
+    int j = 0;
+    int64_t job_end = 0;
+    const InT* in = nullptr;
+    uint8_t* o_codes = nullptr;
+    double* o_scales = nullptr;
+    int64_t* o_zps = nullptr;
+    uint16_t* o_f16 = nullptr;
+    void* o_deq = nullptr;
+    int64_t cols = 0, unit_begin = 0;
 
-        uint32_t acc = 0;
-        for (int i = tid; i < nvec; i += 256) acc = pmin<InT>(acc, minnegmax8<InT>(smem_u4[i]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc = pmin<InT>(acc, __shfl_xor_sync(0xffffffffu, acc, o));
-        if (lane == 0) s_red[wid] = acc;
+    for (int64_t row = blockIdx.x; row < p.total_units; row += gridDim.x) {
+        if (row >= job_end) {
+            j = find_job(jobs, p.njobs, row);
+            const RowQuantArgs J = jobs[j];
+            in = static_cast<const InT*>(J.in);
+            o_codes = static_cast<uint8_t*>(J.codes);
+            o_scales = J.scales;
+            o_zps = J.zps;
+            o_f16 = J.scales_f16;
+            o_deq = J.dequant;
+            cols = J.cols;
+            unit_begin = J.unit_begin;
+            job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+        }
+        const int64_t r = row - unit_begin;
+        const int nvec = int(cols >> 3);
+        const uint4* src = reinterpret_cast<const uint4*>(in + r * cols);
+        for (int i = tid; i < nvec; i += THREADS) cp_async16(smem_u4 + i, src + i, true);
+        cp_async_wait_all();  // every thread reads back only the vectors it copied itself
+
+        MinMax2<InT> mm;
+        for (int i = tid; i < nvec; i += THREADS) mm.add(smem_u4[i]);
+        float mn = warp_min(mm.min_f()), mx = warp_max(mm.max_f());
+        if (lane == 0) {
+            s_mn[wid] = mn;
+            s_mx[wid] = mx;
+        }
         __syncthreads();
         if (wid == 0) {
-            acc = lane < 8 ? s_red[lane] : 0u;
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) acc = pmin<InT>(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+            mn = lane < THREADS / 32 ? s_mn[lane] : 0.f;
+            mx = lane < THREADS / 32 ? s_mx[lane] : 0.f;
+            mn = warp_min(mn);
+            mx = warp_max(mx);
             if (lane == 0) {
                 double scale;
                 long long zp;
                 UnitQ u;
-                derive_unit(P2<InT>::lo(acc), -P2<InT>::hi(acc), p, scale, zp, u, flags);
-                // shift the rounding target by qmin so that the low byte of (t + magic) is the signed code.
-                // The shift is exact only for the constant, so it is applied to c before the fma; the guard
-                // band covers the additional rounding error (|c + qmin| <= 255).
+                derive_unit(mn, mx, p, scale, zp, u, flags);
+                // shift the rounding target by qmin so that the low byte of (t + magic) is the code in two's
+                // complement; the extra rounding of the constant stays inside the guard band (|c + qmin| <= 255)
                 u.c = __fadd_rn(u.c, float(bias));
                 s_u = u;
                 s_scale = scale;
                 s_zp = zp;
-                if (J.scales) J.scales[r] = scale;
-                if (J.zps) J.zps[r] = zp;
-                if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+                if (o_scales) o_scales[r] = scale;
+                if (o_zps) o_zps[r] = zp;
+                if (o_f16) o_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
             }
         }
         __syncthreads();
         const UnitQ u = s_u;
-        if (J.dequant) {
-            if (tid <= p.lm1) {
-                const float f = dequantize_exact(tid + bias, s_scale, s_zp);
-                s_lut[tid] = p.dequant_dt == VF_DT_F32 ? __float_as_uint(f)
-                             : (p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f));
+        if (o_deq) {
+            for (int n = tid; n <= p.lm1; n += THREADS) {
+                const int code = n + bias;
+                const float f = dequantize_exact(code, s_scale, s_zp);
+                s_lut[code & 0xFF] = p.dequant_dt == VF_DT_F32 ? __float_as_uint(f)
+                                     : (p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f));
             }
             __syncthreads();
         }
-        uint2* codes = reinterpret_cast<uint2*>(static_cast<uint8_t*>(J.codes) + r * cols);
-        for (int i = tid; i < nvec; i += 256) {
+        uint2* codes = reinterpret_cast<uint2*>(o_codes + r * cols);
+        const int ddt = o_deq ? p.dequant_dt : 0;
+        for (int i = tid; i < nvec; i += THREADS) {
             const uint4 d = smem_u4[i];
             float m[8];
-            const bool bad = quant8<InT>(d, u.inv, u.c, m);
-            if (bad) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, bias, m);
-            uint32_t b[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) b[k] = __float_as_uint(m[k]);  // low byte = code (two's complement)
-            uint2 w;
-            w.x = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
-            w.y = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
-            codes[i] = w;
-            if (J.dequant) {
+            if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, bias, m);
+            codes[i] = make_uint2(pack_bytes4(m), pack_bytes4(m + 4));
+            if (ddt) {
                 uint32_t q[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) q[k] = s_lut[(b[k] - uint32_t(bias)) & 0xFFu];
-                if (p.dequant_dt == VF_DT_F32) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(J.dequant) + r * cols);
+                for (int k = 0; k < 8; ++k) q[k] = s_lut[__float_as_uint(m[k]) & 0xFFu];
+                if (ddt == VF_DT_F32) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(o_deq) + r * cols);
                     dst[2 * i] = make_float4(__uint_as_float(q[0]), __uint_as_float(q[1]), __uint_as_float(q[2]), __uint_as_float(q[3]));
                     dst[2 * i + 1] = make_float4(__uint_as_float(q[4]), __uint_as_float(q[5]), __uint_as_float(q[6]), __uint_as_float(q[7]));
                 } else {
@@ -395,11 +463,11 @@ __global__ void __launch_bounds__(256) k_row(const RowQuantArgs* __restrict__ jo
                     o.y = __byte_perm(q[2], q[3], 0x5410);
                     o.z = __byte_perm(q[4], q[5], 0x5410);
                     o.w = __byte_perm(q[6], q[7], 0x5410);
-                    reinterpret_cast<uint4*>(static_cast<uint16_t*>(J.dequant) + r * cols)[i] = o;
+                    reinterpret_cast<uint4*>(static_cast<uint16_t*>(o_deq) + r * cols)[i] = o;
                 }
             }
         }
-        __syncthreads();  // stage, s_u and s_lut are rewritten by the next row
+        __syncthreads();  // s_u and s_lut are rewritten by the next row
     }
 }
 
@@ -418,7 +486,7 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
 
     for (int64_t row = int64_t(blockIdx.x) * (blockDim.x >> 5) + wid; row < p.total_units; row += nwarps) {
         const int j = find_job(jobs, p.njobs, row);
-        const RowQuantArgs& J = jobs[j];
+        const RowQuantArgs J = jobs[j];
         const int64_t r = row - J.unit_begin;
         const int64_t khw = J.khw > 0 ? J.khw : 1;
         const int64_t ic = J.khw > 0 ? J.ic : J.cols;
@@ -441,6 +509,7 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
         double scale = 0.0;
         long long zp = 0;
         UnitQ u;
+        u.inv = u.c = u.in_low = u.range = 0.f;
         if (lane == 0) {
             derive_unit(mn, mx, p, scale, zp, u, flags);
             if (J.scales) J.scales[r] = scale;
@@ -515,6 +584,24 @@ void launch_group_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams&
     }
 }
 
+template <typename InT, int THREADS>
+void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, size_t smem) {
+    // persistent grid sized by how many CTAs fit an SM (shared memory and 2048 threads)
+    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(2048 / THREADS, (220 * 1024) / (smem + 2048)));
+    const int grid = int(std::min<int64_t>(p.total_units, int64_t(148) * int64_t(per_sm)));
+    set_smem(k_row<InT, THREADS>, smem);
+    k_row<InT, THREADS><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    post_launch(ctx);
+}
+
+template <typename InT>
+void launch_row_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, int64_t max_cols) {
+    const size_t smem = size_t(max_cols) * 2;
+    if (max_cols <= 8192) launch_row_n<InT, 128>(ctx, d_jobs, p, smem);
+    else if (max_cols <= 16384) launch_row_n<InT, 256>(ctx, d_jobs, p, smem);
+    else launch_row_n<InT, 512>(ctx, d_jobs, p, smem);
+}
+
 }  // namespace
 
 // Which fused kernel covers `a`? 0 = none, 1 = group, 2 = row, 3 = conv
@@ -523,7 +610,7 @@ int rowquant_kind(const RowQuantArgs& a) {
     const bool aligned16 = reinterpret_cast<uintptr_t>(a.in) % 16 == 0;
     if (a.group > 0) {
         if (two_byte && aligned16 && a.khw == 0 && a.rows_pad == a.rows && (a.group == 32 || a.group == 64 || a.group == 128) &&
-            reinterpret_cast<uintptr_t>(a.codes) % 8 == 0 && (!a.dequant || reinterpret_cast<uintptr_t>(a.dequant) % 16 == 0))
+            reinterpret_cast<uintptr_t>(a.codes) % 16 == 0)
             return 1;
         return 0;
     }
@@ -568,17 +655,8 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         if (a0.in_dt == VF_DT_F16) launch_group_t<__half>(ctx, d_jobs, p, a0.group, a0.pack4 != 0);
         else launch_group_t<__nv_bfloat16>(ctx, d_jobs, p, a0.group, a0.pack4 != 0);
     } else if (kind == 2) {
-        const size_t smem = size_t(max_cols) * 2;
-        const int per_sm = int(std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / (smem + 2048))));
-        const int grid = int(std::min<int64_t>(units, int64_t(148) * per_sm));
-        if (a0.in_dt == VF_DT_F16) {
-            set_smem(k_row<__half>, smem);
-            k_row<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
-        } else {
-            set_smem(k_row<__nv_bfloat16>, smem);
-            k_row<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
-        }
-        post_launch(ctx);
+        if (a0.in_dt == VF_DT_F16) launch_row_t<__half>(ctx, d_jobs, p, max_cols);
+        else launch_row_t<__nv_bfloat16>(ctx, d_jobs, p, max_cols);
     } else if (kind == 3) {
         const int stage_bytes = int((max_out_row + 15) & ~int64_t(15));
         const size_t smem = size_t(stage_bytes) * 8;
