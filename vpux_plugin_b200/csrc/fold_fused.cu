@@ -139,16 +139,20 @@ bool fused_prepare(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec,
 }
 
 void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end) {
-    // consecutive jobs with the same kernel and launch-uniform parameters share one launch
-    size_t i = begin;
+    // jobs are independent, so they are regrouped: all jobs with the same kernel and launch-uniform parameters
+    // share one launch, wherever they sit in the batch
+    std::vector<char> done(end - begin, 0);
     std::vector<RowQuantArgs> table;
-    while (i < end) {
-        size_t j = i + 1;
-        while (j < end && jobs[j].kind == jobs[i].kind && rowquant_compatible(jobs[i].a, jobs[j].a)) ++j;
+    for (size_t i = begin; i < end; ++i) {
+        if (done[i - begin]) continue;
         table.clear();
-        for (size_t k = i; k < j; ++k) table.push_back(jobs[k].a);
+        for (size_t k = i; k < end; ++k) {
+            if (!done[k - begin] && jobs[k].kind == jobs[i].kind && rowquant_compatible(jobs[i].a, jobs[k].a)) {
+                table.push_back(jobs[k].a);
+                done[k - begin] = 1;
+            }
+        }
         launch_rowquant_batch(ctx, jobs[i].kind, table);
-        i = j;
     }
 }
 

@@ -135,10 +135,11 @@ __device__ __forceinline__ void cp_async_wait_all() {
 
 // Fast quantization of the eight elements of one vector: returns the eight rounded values as floats with the
 // magic constant still added (bit pattern = kMagicBits + n) and whether any of them fell into the guard band.
+// The largest rounding residual is tracked with max (no per-element branch); one comparison per vector.
 template <typename InT>
 __device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float* m) {
     const uint32_t w[4] = {d.x, d.y, d.z, d.w};
-    bool bad = false;
+    float worst = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 x = P2<InT>::both(w[i]);
@@ -147,10 +148,9 @@ __device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float
         m[2 * i + 1] = __fadd_rn(t1, kMagic);
         const float r0 = __fsub_rn(t0, __fsub_rn(m[2 * i], kMagic));
         const float r1 = __fsub_rn(t1, __fsub_rn(m[2 * i + 1], kMagic));
-        bad |= fabsf(r0) > 0.5f - kGuard;
-        bad |= fabsf(r1) > 0.5f - kGuard;
+        worst = fmaxf(worst, fmaxf(fabsf(r0), fabsf(r1)));
     }
-    return bad;
+    return worst > 0.5f - kGuard;
 }
 
 // Exact recomputation of the eight elements (rare). Everything travels by value so that the caller's
@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
     constexpr int V = G / 8;  // vectors per group = vectors per lane per chunk
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    uint4* stage = smem_u4 + wid * (V * 32);
+    uint4* stage = smem_u4 + wid * ((V + 1) * 32);
     const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
 
     int j = 0;
@@ -259,19 +259,25 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
         const int64_t e0 = g0 * G;
         const uint4* src = reinterpret_cast<const uint4*>(in + e0);
 
+        // vector i of the chunk is stored at i + i / V: every group's V vectors are followed by one vector of
+        // padding, so the copy (lanes write consecutive vectors) and the sweeps (lane g reads group g, lane
+        // stride V + 1 vectors) both spread over all banks
+        const uint4* src_l = src + lane;
+        uint4* dst_l = stage + lane + lane / V;
+        if (e0 + int64_t(32) * G <= total_elems) {
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            const int i = v * 32 + lane;  // vector index inside the chunk
-            cp_async16(stage + (i ^ ((i / V) & 7)), src + i, e0 + int64_t(i) * 8 < total_elems);
+            for (int v = 0; v < V; ++v) cp_async16(dst_l + v * 32 + (v * 32) / V, src_l + v * 32, true);
+        } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+                cp_async16(dst_l + v * 32 + (v * 32) / V, src_l + v * 32, e0 + int64_t(v * 32 + lane) * 8 < total_elems);
         }
         cp_async_wait_all();
         __syncwarp();  // lanes read vectors copied by other lanes
 
         // ---- statistics of group g0+lane ----------------------------------------------------------------
-        // vector k of this lane's group sits at the swizzled position of logical index lane*V + k
-        const int sw = lane & 7;
-        const int base = lane * V;
-#define VF_MINE(k) stage[(base + (k)) ^ sw]
+        const uint4* mine = stage + lane * (V + 1);
+#define VF_MINE(k) mine[(k)]
         MinMax2<InT> mm;
 #pragma unroll
         for (int k = 0; k < V; ++k) mm.add(VF_MINE(k));
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
 // computed with the exact FP64 formula, indexed by the code byte), so the sweep costs one shared-memory
 // lookup per element.
 // ======================================================================================================
-template <typename InT, int THREADS>
+template <typename InT, int THREADS, int DQ>  // DQ: 0 = no dequantized copy, 1 = 16-bit float copy, 2 = f32 copy
 __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
     extern __shared__ uint4 smem_u4[];
     __shared__ float s_mn[THREADS / 32], s_mx[THREADS / 32];
@@ -379,7 +385,7 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
     double* o_scales = nullptr;
     int64_t* o_zps = nullptr;
     uint16_t* o_f16 = nullptr;
-    void* o_deq = nullptr;
+    uint8_t* o_deq = nullptr;
     int64_t cols = 0, unit_begin = 0;
 
     for (int64_t row = blockIdx.x; row < p.total_units; row += gridDim.x) {
@@ -391,7 +397,7 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
             o_scales = J.scales;
             o_zps = J.zps;
             o_f16 = J.scales_f16;
-            o_deq = J.dequant;
+            o_deq = static_cast<uint8_t*>(J.dequant);
             cols = J.cols;
             unit_begin = J.unit_begin;
             job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
@@ -433,37 +439,37 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
         }
         __syncthreads();
         const UnitQ u = s_u;
-        if (o_deq) {
+        if (DQ != 0) {
             for (int n = tid; n <= p.lm1; n += THREADS) {
                 const int code = n + bias;
                 const float f = dequantize_exact(code, s_scale, s_zp);
-                s_lut[code & 0xFF] = p.dequant_dt == VF_DT_F32 ? __float_as_uint(f)
+                s_lut[code & 0xFF] = DQ == 2 ? __float_as_uint(f)
                                      : (p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f));
             }
             __syncthreads();
         }
         uint2* codes = reinterpret_cast<uint2*>(o_codes + r * cols);
-        const int ddt = o_deq ? p.dequant_dt : 0;
+        uint4* deq16 = reinterpret_cast<uint4*>(o_deq + r * cols * 2);
+        float4* deq32 = reinterpret_cast<float4*>(o_deq + r * cols * 4);
         for (int i = tid; i < nvec; i += THREADS) {
             const uint4 d = smem_u4[i];
             float m[8];
             if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, bias, m);
-            codes[i] = make_uint2(pack_bytes4(m), pack_bytes4(m + 4));
-            if (ddt) {
+            const uint32_t w0 = pack_bytes4(m), w1 = pack_bytes4(m + 4);
+            codes[i] = make_uint2(w0, w1);
+            if (DQ != 0) {
                 uint32_t q[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) q[k] = s_lut[__float_as_uint(m[k]) & 0xFFu];
-                if (ddt == VF_DT_F32) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(o_deq) + r * cols);
-                    dst[2 * i] = make_float4(__uint_as_float(q[0]), __uint_as_float(q[1]), __uint_as_float(q[2]), __uint_as_float(q[3]));
-                    dst[2 * i + 1] = make_float4(__uint_as_float(q[4]), __uint_as_float(q[5]), __uint_as_float(q[6]), __uint_as_float(q[7]));
+                for (int k = 0; k < 4; ++k) {
+                    q[k] = s_lut[(w0 >> (8 * k)) & 0xFFu];
+                    q[4 + k] = s_lut[(w1 >> (8 * k)) & 0xFFu];
+                }
+                if (DQ == 2) {
+                    deq32[2 * i] = make_float4(__uint_as_float(q[0]), __uint_as_float(q[1]), __uint_as_float(q[2]), __uint_as_float(q[3]));
+                    deq32[2 * i + 1] = make_float4(__uint_as_float(q[4]), __uint_as_float(q[5]), __uint_as_float(q[6]), __uint_as_float(q[7]));
                 } else {
-                    uint4 o;
-                    o.x = __byte_perm(q[0], q[1], 0x5410);
-                    o.y = __byte_perm(q[2], q[3], 0x5410);
-                    o.z = __byte_perm(q[4], q[5], 0x5410);
-                    o.w = __byte_perm(q[6], q[7], 0x5410);
-                    reinterpret_cast<uint4*>(static_cast<uint16_t*>(o_deq) + r * cols)[i] = o;
+                    deq16[i] = make_uint4(__byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
+                                          __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
                 }
             }
         }
@@ -560,7 +566,7 @@ void set_smem(K kernel, size_t bytes) {
 
 template <typename InT, int G>
 void launch_group_g(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, bool pack4) {
-    const size_t smem = size_t(8) * (G / 8) * 32 * 16;  // 8 warps x (G/8 * 32) vectors
+    const size_t smem = size_t(8) * (G / 8 + 1) * 32 * 16;  // 8 warps x 32 groups x (G/8 + 1 padding) vectors
     // persistent grid: three CTAs per SM (launch bounds), every warp strides over the chunk list
     const int64_t want = (p.total_units + 7) / 8;
     const int grid = int(std::min<int64_t>(want, 148 * 3));
@@ -585,21 +591,28 @@ void launch_group_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams&
 }
 
 template <typename InT, int THREADS>
-void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, size_t smem) {
-    // persistent grid sized by how many CTAs fit an SM (shared memory and 2048 threads)
-    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(2048 / THREADS, (220 * 1024) / (smem + 2048)));
+void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, size_t smem, int dq) {
+    // persistent grid sized by how many CTAs fit an SM (shared memory, 2048 threads, 64K registers at <= 64 each)
+    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(1024 / THREADS, (220 * 1024) / (smem + 2048)));
     const int grid = int(std::min<int64_t>(p.total_units, int64_t(148) * int64_t(per_sm)));
-    set_smem(k_row<InT, THREADS>, smem);
-    k_row<InT, THREADS><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    if (dq == 0) {
+        set_smem(k_row<InT, THREADS, 0>, smem);
+        k_row<InT, THREADS, 0><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    } else if (dq == 1) {
+        set_smem(k_row<InT, THREADS, 1>, smem);
+        k_row<InT, THREADS, 1><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    } else {
+        set_smem(k_row<InT, THREADS, 2>, smem);
+        k_row<InT, THREADS, 2><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    }
     post_launch(ctx);
 }
 
 template <typename InT>
-void launch_row_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, int64_t max_cols) {
+void launch_row_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, int64_t max_cols, int dq) {
     const size_t smem = size_t(max_cols) * 2;
-    if (max_cols <= 8192) launch_row_n<InT, 128>(ctx, d_jobs, p, smem);
-    else if (max_cols <= 16384) launch_row_n<InT, 256>(ctx, d_jobs, p, smem);
-    else launch_row_n<InT, 512>(ctx, d_jobs, p, smem);
+    if (max_cols <= 8192) launch_row_n<InT, 256>(ctx, d_jobs, p, smem, dq);
+    else launch_row_n<InT, 512>(ctx, d_jobs, p, smem, dq);
 }
 
 }  // namespace
@@ -655,8 +668,9 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         if (a0.in_dt == VF_DT_F16) launch_group_t<__half>(ctx, d_jobs, p, a0.group, a0.pack4 != 0);
         else launch_group_t<__nv_bfloat16>(ctx, d_jobs, p, a0.group, a0.pack4 != 0);
     } else if (kind == 2) {
-        if (a0.in_dt == VF_DT_F16) launch_row_t<__half>(ctx, d_jobs, p, max_cols);
-        else launch_row_t<__nv_bfloat16>(ctx, d_jobs, p, max_cols);
+        const int dq = !a0.dequant ? 0 : (a0.dequant_dt == VF_DT_F32 ? 2 : 1);
+        if (a0.in_dt == VF_DT_F16) launch_row_t<__half>(ctx, d_jobs, p, max_cols, dq);
+        else launch_row_t<__nv_bfloat16>(ctx, d_jobs, p, max_cols, dq);
     } else if (kind == 3) {
         const int stage_bytes = int((max_out_row + 15) & ~int64_t(15));
         const size_t smem = size_t(stage_bytes) * 8;
@@ -671,8 +685,11 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
 
 // Jobs may share a launch when the launch-uniform parameters agree.
 bool rowquant_compatible(const RowQuantArgs& a, const RowQuantArgs& b) {
+    // long rows get their own launch: shared memory and block size are chosen per launch from the longest row
+    const bool long_a = a.group == 0 && a.cols > 8192, long_b = b.group == 0 && b.cols > 8192;
     return a.in_dt == b.in_dt && a.group == b.group && a.range_mode == b.range_mode && a.qmin == b.qmin && a.qmax == b.qmax &&
-           a.pack4 == b.pack4 && a.dequant_dt == b.dequant_dt && a.out_signed == b.out_signed;
+           a.pack4 == b.pack4 && a.dequant_dt == b.dequant_dt && a.out_signed == b.out_signed &&
+           (a.dequant != nullptr) == (b.dequant != nullptr) && long_a == long_b;
 }
 
 }  // namespace vf
