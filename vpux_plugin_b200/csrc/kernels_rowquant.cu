@@ -7,9 +7,11 @@
 //
 // Arithmetic contract: codes equal the reference's fakeQuantize chain bit for bit. The per-element fast path
 // evaluates  t = fma(x, inv, c)  with inv = fl((L-1)/range), c = fl(-inLow*inv)  instead of the reference's
-// fl(fl((x-inLow)/range) * (L-1)); both lie within 8.4e-5 of each other for 8-bit ranges, so whenever t is
-// further than kGuard from a rounding boundary (x.5) both round to the same integer. Elements inside the guard
-// band (about 0.04 %) are recomputed with the exact operation sequence.
+// fl(fl((x-inLow)/range) * (L-1)). Six roundings separate the two (constant, reciprocal, fma; subtraction,
+// division, multiplication), each at most 2^-24 * (L-1) in absolute terms, plus one more when qmin is folded
+// into the constant: |t - reference| < 4.2e-7 * L. Whenever t is further than guard = 8e-7 * L from a rounding
+// boundary (x.5) both round to the same integer; elements inside the guard band (2e-4 wide for 8-bit ranges,
+// 1.3e-5 for 4-bit) are recomputed with the exact operation sequence.
 #include <algorithm>
 #include <vector>
 
@@ -22,7 +24,7 @@ namespace {
 
 constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to the nearest integer (ties to even)
 constexpr int kMagicBits = 0x4B400000; // its bit pattern; the low byte is zero
-constexpr float kGuard = 2.0e-4f;
+constexpr float kGuardPerLevel = 8.0e-7f;
 
 struct UnitQ {  // per-unit constants
     float inv;     // fl((L-1) / range)
@@ -36,6 +38,7 @@ struct LaunchParams {  // uniform over all jobs of one launch
     int qmin, qmax, lm1;
     int dequant_dt;
     int njobs;
+    float thr;            // 0.5 - guard: largest rounding residual the fast path accepts
     int64_t total_units;  // chunks (k_group) or rows (k_row / k_conv) over all jobs
 };
 
@@ -137,7 +140,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // magic constant still added (bit pattern = kMagicBits + n) and whether any of them fell into the guard band.
 // The largest rounding residual is tracked with max (no per-element branch); one comparison per vector.
 template <typename InT>
-__device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float* m) {
+__device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float thr, float* m) {
     const uint32_t w[4] = {d.x, d.y, d.z, d.w};
     float worst = 0.f;
 #pragma unroll
@@ -150,33 +153,44 @@ __device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float
         const float r1 = __fsub_rn(t1, __fsub_rn(m[2 * i + 1], kMagic));
         worst = fmaxf(worst, fmaxf(fabsf(r0), fabsf(r1)));
     }
-    return worst > 0.5f - kGuard;
+    return worst > thr;
 }
 
-// Exact recomputation of the eight elements (rare). Everything travels by value so that the caller's
-// registers never need an address: returns the eight indices n (0..255) as bytes.
+// Repair of a vector that has an element in the guard band (rare): every element is re-evaluated, those inside
+// the band with the exact sequence. Everything travels by value so that the caller's registers never need an
+// address; returns the eight indices n (0..255) as bytes. `bias` is what the caller folded into c.
+__device__ __forceinline__ uint32_t quant1_fix(float x, float inv, float c, float thr, float in_low, float range,
+                                               int lm1, int bias) {
+    const float t = __fmaf_rn(x, inv, c);
+    const float m = __fadd_rn(t, kMagic);
+    const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
+    int n = (__float_as_int(m) - kMagicBits) - bias;
+    if (fabsf(resid) > thr) n = quant_index_exact(x, in_low, range, lm1);
+    return uint32_t(min(max(n, 0), lm1));
+}
 template <typename InT>
-__device__ __noinline__ uint2 quant8_exact_bytes(uint4 d, float in_low, float range, int lm1) {
+__device__ __noinline__ uint2 quant8_fix_bytes(uint4 d, float inv, float c, float thr, float in_low, float range,
+                                               int lm1, int bias) {
     uint2 r;
-    r.x = uint32_t(quant_index_exact(P2<InT>::lo(d.x), in_low, range, lm1)) |
-          (uint32_t(quant_index_exact(P2<InT>::hi(d.x), in_low, range, lm1)) << 8) |
-          (uint32_t(quant_index_exact(P2<InT>::lo(d.y), in_low, range, lm1)) << 16) |
-          (uint32_t(quant_index_exact(P2<InT>::hi(d.y), in_low, range, lm1)) << 24);
-    r.y = uint32_t(quant_index_exact(P2<InT>::lo(d.z), in_low, range, lm1)) |
-          (uint32_t(quant_index_exact(P2<InT>::hi(d.z), in_low, range, lm1)) << 8) |
-          (uint32_t(quant_index_exact(P2<InT>::lo(d.w), in_low, range, lm1)) << 16) |
-          (uint32_t(quant_index_exact(P2<InT>::hi(d.w), in_low, range, lm1)) << 24);
+    r.x = quant1_fix(P2<InT>::lo(d.x), inv, c, thr, in_low, range, lm1, bias) |
+          (quant1_fix(P2<InT>::hi(d.x), inv, c, thr, in_low, range, lm1, bias) << 8) |
+          (quant1_fix(P2<InT>::lo(d.y), inv, c, thr, in_low, range, lm1, bias) << 16) |
+          (quant1_fix(P2<InT>::hi(d.y), inv, c, thr, in_low, range, lm1, bias) << 24);
+    r.y = quant1_fix(P2<InT>::lo(d.z), inv, c, thr, in_low, range, lm1, bias) |
+          (quant1_fix(P2<InT>::hi(d.z), inv, c, thr, in_low, range, lm1, bias) << 8) |
+          (quant1_fix(P2<InT>::lo(d.w), inv, c, thr, in_low, range, lm1, bias) << 16) |
+          (quant1_fix(P2<InT>::hi(d.w), inv, c, thr, in_low, range, lm1, bias) << 24);
     return r;
 }
 
-// Overwrites m[] with the patterns kMagicBits + n + bias of the exactly recomputed elements.
-#define VF_QUANT8_EXACT(InT, d, in_low, range, lm1, bias, m)                                       \
-    do {                                                                                           \
-        const uint2 ex_ = quant8_exact_bytes<InT>(d, in_low, range, lm1);                          \
-        _Pragma("unroll") for (int k_ = 0; k_ < 4; ++k_) {                                         \
-            m[k_] = __int_as_float(kMagicBits + int((ex_.x >> (8 * k_)) & 0xFFu) + (bias));        \
-            m[4 + k_] = __int_as_float(kMagicBits + int((ex_.y >> (8 * k_)) & 0xFFu) + (bias));    \
-        }                                                                                          \
+// Overwrites m[] with the patterns kMagicBits + n + bias of the repaired vector.
+#define VF_QUANT8_FIX(InT, d, u, thr, lm1, bias, m)                                                        \
+    do {                                                                                                   \
+        const uint2 ex_ = quant8_fix_bytes<InT>(d, (u).inv, (u).c, thr, (u).in_low, (u).range, lm1, bias); \
+        _Pragma("unroll") for (int k_ = 0; k_ < 4; ++k_) {                                                 \
+            m[k_] = __int_as_float(kMagicBits + int((ex_.x >> (8 * k_)) & 0xFFu) + (bias));                \
+            m[4 + k_] = __int_as_float(kMagicBits + int((ex_.y >> (8 * k_)) & 0xFFu) + (bias));            \
+        }                                                                                                  \
     } while (0)
 
 // eight patterns (kMagicBits + n) -> eight nibbles of n in one word, element 0 in the low nibble (BitPack<4>)
@@ -312,7 +326,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
                 for (int q = 0; q < 4; ++q) {
                     const uint4 d = VF_MINE(k4 * 4 + q);
                     float m[8];
-                    if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, 0, m);
+                    if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, 0, m);
                     w[q] = pack_nibbles(m);
                     if (add != 0) {  // signed 4-bit ranges: add qmin to every nibble, modulo 16
                         const uint32_t qq = (uint32_t(add) & 0xFu) * 0x01010101u;
@@ -330,7 +344,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
                 for (int q = 0; q < 2; ++q) {
                     const uint4 d = VF_MINE(k2 * 2 + q);
                     float m[8];
-                    if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, 0, m);
+                    if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, 0, m);
                     if (add != 0) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) m[i] = __int_as_float(__float_as_int(m[i]) + add);
@@ -347,7 +361,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
             for (int k = 0; k < V; ++k) {
                 const uint4 d = VF_MINE(k);
                 float m[8];
-                if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, 0, m);
+                if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, 0, m);
 #pragma unroll 1
                 for (int i = 0; i < 8; ++i) {
                     const int q = (__float_as_int(m[i]) - kMagicBits) + add;
@@ -454,15 +468,17 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
         for (int i = tid; i < nvec; i += THREADS) {
             const uint4 d = smem_u4[i];
             float m[8];
-            if (quant8<InT>(d, u.inv, u.c, m)) VF_QUANT8_EXACT(InT, d, u.in_low, u.range, p.lm1, bias, m);
+            if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, bias, m);
             const uint32_t w0 = pack_bytes4(m), w1 = pack_bytes4(m + 4);
             codes[i] = make_uint2(w0, w1);
             if (DQ != 0) {
                 uint32_t q[8];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    q[k] = s_lut[(w0 >> (8 * k)) & 0xFFu];
-                    q[4 + k] = s_lut[(w1 >> (8 * k)) & 0xFFu];
+                for (int k = 0; k < 4; ++k) {  // byte k of w, already scaled to the entry's byte offset
+                    const uint32_t o0 = (k == 0 ? (w0 << 2) : (w0 >> (8 * k - 2))) & 0x3FCu;
+                    const uint32_t o1 = (k == 0 ? (w1 << 2) : (w1 >> (8 * k - 2))) & 0x3FCu;
+                    q[k] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(s_lut) + o0);
+                    q[4 + k] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(s_lut) + o1);
                 }
                 if (DQ == 2) {
                     deq32[2 * i] = make_float4(__uint_as_float(q[0]), __uint_as_float(q[1]), __uint_as_float(q[2]), __uint_as_float(q[3]));
@@ -536,7 +552,7 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
             const float m = __fadd_rn(t, kMagic);
             int n = __float_as_int(m) - kMagicBits;
             const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
-            if (fabsf(resid) > 0.5f - kGuard) n = quant_index_exact(x, u.in_low, u.range, p.lm1);
+            if (fabsf(resid) > p.thr) n = quant_index_exact(x, u.in_low, u.range, p.lm1);
             n = min(max(n, 0), p.lm1);
             // input index i = icIdx * khw + s  ->  output index s * ic_pad + icIdx
             const int64_t ici = i / khw, s = i - ici * khw;
@@ -650,6 +666,7 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
     p.lm1 = int(a0.qmax - a0.qmin);
     p.dequant_dt = a0.dequant_dt;
     p.njobs = int(jobs.size());
+    p.thr = 0.5f - kGuardPerLevel * float(p.lm1 + 1);
     int64_t units = 0, max_cols = 0, max_out_row = 0;
     for (auto& a : jobs) {
         a.unit_begin = units;
