@@ -315,6 +315,23 @@ int vf_sparsify(vf_ctx* ctx, const vf_content* content, void* data, uint64_t dat
                 void* map, uint64_t map_bytes, int64_t* counts, int out_mem_kind, vf_stats* stats, char* err,
                 size_t errlen);
 
+/* Allocation-free variant of vf_sparsify. It has no counterpart in the reference: it exists for embedders
+ * that forbid device allocations while the compiler runs (for example a serving process whose allocator owns
+ * all device memory and hands the fold a fixed arena — a cudaMalloc there fails or stalls every stream).
+ * The per-call scratch (per-channel counts and output offsets) lives in a fixed array inside the library
+ * image, 1 MiB per GPU that loads the library, so at most VF_NOALLOC_MAX_OC output channels per call;
+ * larger requests return VF_ERR_CAPACITY. The call makes no cudaMalloc / cudaFree / memory-pool request.
+ *   weights      : [oc][work] elements of `dtype` (i8 / u8 / f16 / bf16 / f32) in DEVICE memory
+ *   sparse_value : element value treated as zero (the zero point; 0 for plain types)
+ *   data, map, counts : DEVICE memory, laid out exactly as vf_sparsify writes them; each may be NULL
+ * All calls on one GPU share the scratch array and it keeps the previous call's contents (everything read is
+ * rewritten first); calls that overlap in time on the same GPU race on it — serialise them. The first call on
+ * a device looks up the array's device address; issue that first call before any stream capture. */
+#define VF_NOALLOC_MAX_OC 65536
+int vf_sparsify_noalloc(vf_ctx* ctx, const void* weights, int32_t dtype, int64_t oc, int64_t work,
+                        int64_t sparse_value, void* data, uint64_t data_bytes, uint64_t* data_written, void* map,
+                        uint64_t map_bytes, int64_t* counts, char* err, size_t errlen);
+
 /* ------------------------------------------------------------------ */
 /* weights table                                                       */
 /* ------------------------------------------------------------------ */
