@@ -120,8 +120,11 @@ bool calc_scale_zp_host(double qmin, double qmax, double rmin, double rmax, doub
 // ------------------------------------------------------------------------------------------------------
 struct vf_ctx {
     int device = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;  // the stream all helpers enqueue on (swapped between lanes inside a batch)
     bool own_stream = false;
+    cudaStream_t main_stream = nullptr;  // the context's own / the caller's stream
+    cudaStream_t lane_stream = nullptr;  // second lane for batches with host memory: its transfers overlap lane 0's
+    cudaEvent_t lane_ev[2] = {nullptr, nullptr};
     uint64_t staging_bytes = 0;
     void* staging[2] = {nullptr, nullptr};  // pinned bounce buffers for pageable host memory
     cudaEvent_t staging_ev[2] = {nullptr, nullptr};

@@ -112,6 +112,9 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
                 VF_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
                 c->own_stream = true;
             }
+            c->main_stream = c->stream;
+            VF_CUDA(cudaStreamCreateWithFlags(&c->lane_stream, cudaStreamNonBlocking));
+            for (int k = 0; k < 2; ++k) VF_CUDA(cudaEventCreateWithFlags(&c->lane_ev[k], cudaEventDisableTiming));
             c->opt_flags = opts ? opts->flags : 0;
             c->staging_bytes = (opts && opts->staging_bytes) ? opts->staging_bytes : (64ull << 20);
             for (int k = 0; k < 2; ++k) {
@@ -144,7 +147,11 @@ void vf_ctx_destroy(vf_ctx* c) {
     }
     if (c->d_flags) cudaFree(c->d_flags);
     if (c->h_flags) cudaFreeHost(c->h_flags);
-    if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
+    if (c->lane_stream) cudaStreamSynchronize(c->lane_stream);
+    for (int k = 0; k < 2; ++k)
+        if (c->lane_ev[k]) cudaEventDestroy(c->lane_ev[k]);
+    if (c->lane_stream) cudaStreamDestroy(c->lane_stream);
+    if (c->own_stream && c->main_stream) cudaStreamDestroy(c->main_stream);
     delete c;
 }
 

@@ -718,13 +718,31 @@ int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats*
         // host memory are flushed every kFlushBytes of device staging so that uploads, kernels and downloads
         // of successive sub-batches follow each other on the stream with bounded staging memory. One
         // synchronisation at the end.
-        constexpr uint64_t kFlushBytes = 1ull << 30;
+        // Sub-batches alternate between two stream lanes, so the downloads of one sub-batch overlap the uploads
+        // of the next (PCIe is full duplex); everything a sub-batch allocates is freed on its own lane.
+        constexpr uint64_t kFlushBytes = 512ull << 20;
         const bool allow_fused = !(ctx->opt_flags & VF_OPT_DISABLE_FUSION);
+        bool any_host = false;
+        for (int j = 0; j < njobs; ++j) {
+            const vf_quant_job& jb = jobs[j];
+            any_host |= jb.base.mem_kind != VF_MEM_DEVICE || jb.dst_mem_kind != VF_MEM_DEVICE || jb.outs.mem_kind != VF_MEM_DEVICE;
+        }
+        struct LaneGuard {  // whatever happens, the context ends up on its main stream
+            vf_ctx* c;
+            ~LaneGuard() {
+                c->stream = c->main_stream;
+            }
+        } lane_guard{ctx};
+        int lane = 0;
+        if (any_host) {
+            VF_CUDA(cudaEventRecord(ctx->lane_ev[0], ctx->main_stream));
+            VF_CUDA(cudaStreamWaitEvent(ctx->lane_stream, ctx->lane_ev[0], 0));
+        }
         std::vector<DContent> bases;
         std::vector<FusedJob> fj;
         std::vector<int> owner;
         uint64_t staged = 0;
-        auto flush = [&] {
+        auto flush = [&](bool switch_lane) {
             if (fj.empty()) return;
             fused_launch(ctx, fj, 0, fj.size());
             for (size_t k = 0; k < fj.size(); ++k) {
@@ -737,6 +755,10 @@ int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats*
             bases.clear();
             owner.clear();
             staged = 0;
+            if (any_host && switch_lane) {
+                lane ^= 1;
+                ctx->stream = lane ? ctx->lane_stream : ctx->main_stream;
+            }
         };
         for (int j = 0; j < njobs; ++j) {
             vf_quant_job& jb = jobs[j];
@@ -749,15 +771,20 @@ int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats*
                 bases.push_back(std::move(in));
                 fj.push_back(std::move(cand));
                 owner.push_back(j);
-                if (staged >= kFlushBytes) flush();
+                if (staged >= kFlushBytes) flush(true);
             } else {
-                flush();
+                flush(false);  // stay on this lane: `in` was uploaded on it
                 uint64_t w = 0;
                 quantize_fold_general(ctx, in, jb.spec, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, &w, &jb.outs, stats);
                 jb.dst_written = w;
             }
         }
-        flush();
+        flush(false);
+        ctx->stream = ctx->main_stream;
+        if (any_host) {  // join the second lane before the final synchronisation
+            VF_CUDA(cudaEventRecord(ctx->lane_ev[1], ctx->lane_stream));
+            VF_CUDA(cudaStreamWaitEvent(ctx->main_stream, ctx->lane_ev[1], 0));
+        }
         scope.finish();
     });
 }
