@@ -389,8 +389,12 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
     __shared__ double s_scale;
     __shared__ long long s_zp;
     __shared__ uint32_t s_lut[256];  // dequantized value of code byte b (16-bit types in the low half)
+    constexpr int kFixCap = 1024;    // vectors noted for repair per row; beyond that the sweep repairs inline
+    __shared__ int s_fix[kFixCap];
+    __shared__ int s_nfix;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int bias = p.qmin;  // code = n + qmin
+    if (tid == 0) s_nfix = 0;  // made visible by the first barrier of the row loop
 
     int j = 0;
     int64_t job_end = 0;
@@ -465,10 +469,17 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
         uint2* codes = reinterpret_cast<uint2*>(o_codes + r * cols);
         uint4* deq16 = reinterpret_cast<uint4*>(o_deq + r * cols * 2);
         float4* deq32 = reinterpret_cast<float4*>(o_deq + r * cols * 4);
+        const float thr = p.thr;
         for (int i = tid; i < nvec; i += THREADS) {
             const uint4 d = smem_u4[i];
             float m[8];
-            if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, bias, m);
+            if (quant8<InT>(d, u.inv, u.c, thr, m)) {
+                // a vector with an element in the guard band is noted and repaired after the sweep by eight
+                // threads at once, so the sweep itself never diverges into the exact sequence
+                const int slot = atomicAdd(&s_nfix, 1);
+                if (slot < kFixCap) s_fix[slot] = i;
+                else VF_QUANT8_FIX(InT, d, u, thr, p.lm1, bias, m);
+            }
             const uint32_t w0 = pack_bytes4(m), w1 = pack_bytes4(m + 4);
             codes[i] = make_uint2(w0, w1);
             if (DQ != 0) {
@@ -489,7 +500,26 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
                 }
             }
         }
-        __syncthreads();  // s_u and s_lut are rewritten by the next row
+        __syncthreads();
+        // repair: one thread per element of every noted vector; elements outside the guard band keep the
+        // value the sweep stored, the others are recomputed exactly and patched in place
+        const int nfix = min(s_nfix, kFixCap);
+        for (int e = tid; e < nfix * 8; e += THREADS) {
+            const int i = s_fix[e >> 3], k = e & 7;
+            const uint32_t pair = reinterpret_cast<const uint32_t*>(smem_u4 + i)[k >> 1];
+            const float x = (k & 1) ? P2<InT>::hi(pair) : P2<InT>::lo(pair);
+            const float t = __fmaf_rn(x, u.inv, u.c);
+            const float mg = __fadd_rn(t, kMagic);
+            if (fabsf(__fsub_rn(t, __fsub_rn(mg, kMagic))) > thr) {
+                const int code = quant_index_exact(x, u.in_low, u.range, p.lm1) + bias;
+                const int64_t pos = r * cols + int64_t(i) * 8 + k;
+                o_codes[pos] = uint8_t(code);
+                if (DQ == 1) reinterpret_cast<uint16_t*>(o_deq)[pos] = uint16_t(s_lut[code & 0xFF]);
+                if (DQ == 2) reinterpret_cast<uint32_t*>(o_deq)[pos] = s_lut[code & 0xFF];
+            }
+        }
+        __syncthreads();  // s_u, s_lut and the repair list are rewritten by the next row
+        if (tid == 0) s_nfix = 0;
     }
 }
 
