@@ -82,8 +82,22 @@ class Workload:
             self.alg_bytes_per_elem = 2.0 + 1.0 + 2.0
             self.kernel = "k_row<bf16>"
             self.shard_mode = 1
+        elif key in ("c1", "c2", "c3"):
+            # convolution weights: small (<= 51 MB), so the L2 is flushed between timed steps
+            self.tensors = wl.c1_tensors() if key == "c1" else wl.resnet50_tensors(sparse=key == "c3")
+            self.spec = wl.spec_u8_asym() if key == "c1" else wl.spec_i8_sym()
+            self.desc = {"c1": "c1: conv 60x64x3x3 fp32 -> per-channel asymmetric u8, OIYX->OYXI, O padded to 64",
+                         "c2": "c2: ResNet-50 v1.5 weight set (53 convs + FC) fp16 -> per-channel symmetric i8, OIYX->OYXI, "
+                               "stem IC 3->16",
+                         "c3": "c3: ResNet-50 v1.5 weight set, Bernoulli(1/2) masked with 1 channel in 10 dense: c2 fold, then "
+                               "Sparsify + GetSparsityMap + per-channel counts on the folded i8 codes"}[key]
+            self.alg_bytes_per_elem = {"c1": 4.0 + 64.0 / 60.0, "c2": 3.0, "c3": 2.0 + 1.0 + 1.0 + 0.55 + 0.125}[key]
+            self.kernel = "k_conv (+ k_row for aligned rows >= 1024)" if key != "c3" else "k_conv/k_row + k_sparsity_scan + k_sparse_offsets + k_sparse_compact"
+            self.shard_mode = 0
+            self.seed = wl.SEEDS[key]
+            return
         else:
-            raise SystemExit(f"workload {key} is measured by tests/ and profiles/, not by bench.py")
+            raise SystemExit(f"unknown workload {key}")
         self.seed = wl.SEEDS["c4" if key == "c4" else "c5"]
 
 
@@ -411,11 +425,109 @@ def gpu_arm(args, workload):
         dist.destroy_process_group()
 
 
+def conv_arm(args, workload):
+    """Workloads c1-c3 (convolution weight sets, 0.14-51 MB), single GPU, device resident. The set fits the L2,
+    so every step is timed on its own and a buffer larger than the L2 is written between steps."""
+    import torch
+
+    from vpux_plugin_b200.lib import Library
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    lib = Library(device=0, stream=stream.cuda_stream)
+    key = workload.key
+    specs = workload.tensors
+    jobs = (abi.QuantJob * len(specs))()
+    keep, folded = [], []
+    in_bytes = elems = 0
+    for j, s in enumerate(specs):
+        if key == "c1":
+            ts, oshape = wl.conv_pipeline(s.shape, pad_oc_to=64)
+        else:
+            ts, oshape = wl.conv_pipeline(s.shape, pad_ic_to=16 if s.name == "stem" else None)
+        tr = abi.make_transforms(ts)
+        src = torch.empty(s.nbytes, dtype=torch.uint8, device=dev)
+        lib.synth_fill_device(s.synth_spec(workload.seed), src.data_ptr(), s.numel)
+        dst = torch.empty(int(np.prod(oshape)), dtype=torch.uint8, device=dev)
+        sc = torch.empty(s.shape[0], dtype=torch.float64, device=dev)
+        o = abi.QuantOutputs()
+        o.mem_kind, o.scales = abi.VF_MEM_DEVICE, sc.data_ptr()
+        c, k = abi.make_content(abi.TType(list(s.shape), s.dtype), None, ptr=src.data_ptr(), nbytes=s.nbytes,
+                                mem_kind=abi.VF_MEM_DEVICE)
+        jb = jobs[j]
+        jb.base, jb.spec, jb.t, jb.n = c, workload.spec, tr, len(ts)
+        jb.dst, jb.dst_bytes, jb.dst_mem_kind, jb.outs = dst.data_ptr(), dst.numel(), abi.VF_MEM_DEVICE, o
+        keep += [tr, src, sc, k]
+        folded.append((dst, oshape))
+        in_bytes += s.nbytes
+        elems += s.numel
+    sparse = []
+    if key == "c3":  # sparsify stage on the folded codes (zero point 0: plain i8 view)
+        for dst, oshape in folded:
+            oc, work = oshape[0], oshape[1] * oshape[2] * oshape[3]
+            row = (work + 127) // 128 * 16
+            cap = oc * ((work + 15) // 16 * 16)
+            c, k = abi.make_content(abi.TType(list(oshape), abi.VF_DT_I8, abi.ORDER_NHWC), None, ptr=dst.data_ptr(),
+                                    nbytes=dst.numel(), mem_kind=abi.VF_MEM_DEVICE)
+            data = torch.empty(cap, dtype=torch.uint8, device=dev)
+            mp = torch.empty(oc * row, dtype=torch.uint8, device=dev)
+            cnt = torch.empty(oc, dtype=torch.int64, device=dev)
+            sparse.append((c, k, data, mp, cnt, cap, oc * row))
+
+    def step():
+        lib.quantize_fold_batch(jobs)
+        for c, k, data, mp, cnt, cap, mb in sparse:
+            lib.sparsify(c, data.data_ptr(), mp.data_ptr(), cnt.data_ptr(), out_mem_kind=abi.VF_MEM_DEVICE, data_bytes=cap,
+                         map_bytes=mb)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    warmup = args.warmup if args.profile else max(3, args.warmup)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    uuid = "GPU-" + str(torch.cuda.get_device_properties(0).uuid).replace("GPU-", "")
+    sampler = ClockSampler(uuid)
+    l0 = lib.launch_count
+    ms = 0.0
+    for _ in range(args.steps):
+        flush.fill_(1)  # evicts the previous step's inputs and outputs from the 126 MB L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms += e0.elapsed_time(e1)
+    launches = (lib.launch_count - l0) // args.steps
+    clocks = sampler.stop()
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    achieved = elems * workload.alg_bytes_per_elem * args.steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "weight_fold_input_throughput", "value": in_bytes * args.steps / (ms * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload.desc, "input_bytes": in_bytes, "tensors_rank0": len(specs),
+                   "l2": "256 MiB written between timed steps (inputs fit the 126 MB L2)"},
+        "roofline": {"bound": "hbm", "kernel": workload.kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                     "note": "whole step (all launches of the step, host gaps between synchronous calls included)"},
+        "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": int(launches * args.steps),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse()
     workload = Workload(args.workload, args.scale)
     if args.impl == "reference":
         reference_arm(args, workload)
+    elif args.workload in ("c1", "c2", "c3"):
+        conv_arm(args, workload)
     else:
         gpu_arm(args, workload)
 

@@ -600,6 +600,96 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
     }
 }
 
+// ======================================================================================================
+// K_convv: the vectorised form of K_conv for 2-byte inputs whose rows are 16-byte multiples (every ResNet-style
+// convolution with IC % 8 == 0). One warp per output channel: the row is copied into the warp's shared-memory
+// stage with cp.async, min/max run on packed pairs, the codes are written back into the stage in input order
+// (8 bytes per vector, over the vector they came from) and then copied out — straight for 1x1 kernels, transposed OIYX->OYXI otherwise
+// (for every kernel tap s the lanes gather four codes of consecutive input channels and store one word).
+// ======================================================================================================
+template <typename InT>
+__global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int in_vecs,
+                                               int code_bytes, int* flags) {
+    extern __shared__ uint4 smem_u4[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint4* in_stage = smem_u4 + size_t(wid) * size_t(in_vecs);
+    // the codes of vector v (8 bytes) overwrite the first half of the 16-byte slot the vector was read from
+    const uint8_t* code_bytes_p = reinterpret_cast<const uint8_t*>(in_stage);
+    (void)code_bytes;
+    const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
+    const float thr = p.thr;
+    int64_t job_end = 0;
+    RowQuantArgs J;
+
+    for (int64_t row = int64_t(blockIdx.x) * (blockDim.x >> 5) + wid; row < p.total_units; row += nwarps) {
+        if (row >= job_end) {
+            const int j = find_job(jobs, p.njobs, row);
+            J = jobs[j];
+            job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+        }
+        const int64_t r = row - J.unit_begin;
+        const int khw = J.khw > 0 ? int(J.khw) : 1;
+        const int ic = J.khw > 0 ? int(J.ic) : int(J.cols);
+        const int ic_pad = J.khw > 0 ? int(J.ic_pad) : int(J.cols);
+        const int out_words = (khw * ic_pad) >> 2;
+        uint32_t* out = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(J.codes) + r * (int64_t(khw) * ic_pad));
+        if (r >= J.rows) {  // padded output channel
+            for (int w = lane; w < out_words; w += 32) out[w] = 0u;
+            continue;
+        }
+        const int nvec = int(J.cols >> 3);
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(J.in) + r * J.cols);
+        for (int v = lane; v < nvec; v += 32) cp_async16(in_stage + v, src + v, true);
+        cp_async_wait_all();  // each lane reads back only the vectors it copied itself
+
+        MinMax2<InT> mm;
+        for (int v = lane; v < nvec; v += 32) mm.add(in_stage[v]);
+        const float mn = warp_min(mm.min_f()), mx = warp_max(mm.max_f());
+        UnitQ u;
+        u.inv = u.c = u.in_low = u.range = 0.f;
+        if (lane == 0) {
+            double scale;
+            long long zp;
+            derive_unit(mn, mx, p, scale, zp, u, flags);
+            u.c = __fadd_rn(u.c, float(p.qmin));  // low byte of (t + magic) = code
+            if (J.scales) J.scales[r] = scale;
+            if (J.zps) J.zps[r] = zp;
+            if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+        }
+        u.inv = __shfl_sync(0xffffffffu, u.inv, 0);
+        u.c = __shfl_sync(0xffffffffu, u.c, 0);
+        u.in_low = __shfl_sync(0xffffffffu, u.in_low, 0);
+        u.range = __shfl_sync(0xffffffffu, u.range, 0);
+
+        for (int v = lane; v < nvec; v += 32) {
+            const uint4 d = in_stage[v];
+            float m[8];
+            if (quant8<InT>(d, u.inv, u.c, thr, m)) VF_QUANT8_FIX(InT, d, u, thr, p.lm1, p.qmin, m);
+            *reinterpret_cast<uint2*>(in_stage + v) = make_uint2(pack_bytes4(m), pack_bytes4(m + 4));
+        }
+        __syncwarp();
+        if (J.khw <= 0) {
+            const uint32_t* c32 = reinterpret_cast<const uint32_t*>(in_stage);
+            for (int w = lane; w < out_words; w += 32) out[w] = c32[(w >> 1) * 4 + (w & 1)];
+        } else {
+            const int icw = ic >> 2, padw = ic_pad >> 2;
+            for (int s = 0; s < khw; ++s) {
+                uint32_t* orow = out + s * padw;
+                for (int w = lane; w < padw; w += 32) {
+                    uint32_t word = 0;
+                    if (w < icw) {
+                        const int i0 = (w * 4) * khw + s;  // input index = channel * khw + tap
+                        auto code_at = [&](int i) { return uint32_t(code_bytes_p[(i >> 3) * 16 + (i & 7)]); };
+                        word = code_at(i0) | (code_at(i0 + khw) << 8) | (code_at(i0 + 2 * khw) << 16) | (code_at(i0 + 3 * khw) << 24);
+                    }
+                    orow[w] = word;
+                }
+            }
+        }
+        __syncwarp();  // both stages are rewritten by the next row
+    }
+}
+
 void post_launch(vf_ctx* ctx) {
     VF_CUDA(cudaGetLastError());
     ctx->launches += 1;
@@ -679,6 +769,10 @@ int rowquant_kind(const RowQuantArgs& a) {
         return 2;
     if (!a.pack4 && !a.dequant && !a.zps_u4) {
         const int64_t out_row = a.khw > 0 ? a.khw * a.ic_pad : a.cols;
+        const int64_t ic = a.khw > 0 ? a.ic : a.cols, ic_pad = a.khw > 0 ? a.ic_pad : a.cols;
+        if (two_byte && aligned16 && a.cols % 8 == 0 && a.cols <= 4608 && out_row <= 4608 && ic % 4 == 0 && ic_pad % 4 == 0 &&
+            reinterpret_cast<uintptr_t>(a.codes) % 4 == 0)
+            return 4;
         if (out_row <= 24 * 1024) return 3;
     }
     return 0;
@@ -718,6 +812,21 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         const int dq = !a0.dequant ? 0 : (a0.dequant_dt == VF_DT_F32 ? 2 : 1);
         if (a0.in_dt == VF_DT_F16) launch_row_t<__half>(ctx, d_jobs, p, max_cols, dq);
         else launch_row_t<__nv_bfloat16>(ctx, d_jobs, p, max_cols, dq);
+    } else if (kind == 4) {
+        const int in_vecs = int((max_cols + 7) / 8);
+        const int code_bytes = int((std::max(max_cols, max_out_row) + 15) & ~int64_t(15));
+        const size_t smem = size_t(8) * size_t(in_vecs) * 16;
+        const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024)));
+        const int64_t blocks = (units + 7) / 8;
+        const int grid = int(std::min<int64_t>(blocks, int64_t(148) * int64_t(per_sm)));
+        if (a0.in_dt == VF_DT_F16) {
+            set_smem(k_convv<__half>, smem);
+            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, code_bytes, ctx->d_flags);
+        } else {
+            set_smem(k_convv<__nv_bfloat16>, smem);
+            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, code_bytes, ctx->d_flags);
+        }
+        post_launch(ctx);
     } else if (kind == 3) {
         const int stage_bytes = int((max_out_row + 15) & ~int64_t(15));
         const size_t smem = size_t(stage_bytes) * 8;
