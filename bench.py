@@ -38,7 +38,9 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 # DRAM traffic per element of the dominant kernel from the committed ncu capture of a smaller case of the same
 # kernel (dram__bytes_read.sum + dram__bytes_write.sum) / elements; traffic grows in proportion to the
 # elements processed. None until a capture exists for the kernel.
-NCU_TRAFFIC_BYTES_PER_ELEM = {"c4": None, "c5slab": None, "c2": None, "c3": None, "c1": None}
+# c4: k_group on 333.4 M elements read 669.49 MB and wrote 156.01 MB; c5slab: k_row on 340.3 M elements read
+# 680.65 MB and wrote 970.77 MB (profiles/k_group_c4.md, profiles/k_row_c5slab.md). The conv workloads fit in L2.
+NCU_TRAFFIC_BYTES_PER_ELEM = {"c4": 2.476, "c5slab": 4.853, "c2": None, "c3": None, "c1": None}
 
 
 def parse():
