@@ -466,8 +466,10 @@ def conv_arm(args, workload):
         in_bytes += s.nbytes
         elems += s.numel
     sparse = []
+    sjobs = None
     if key == "c3":  # sparsify stage on the folded codes (zero point 0: plain i8 view)
-        for dst, oshape in folded:
+        sjobs = (abi.SparsifyJob * len(folded))()
+        for j, (dst, oshape) in enumerate(folded):
             oc, work = oshape[0], oshape[1] * oshape[2] * oshape[3]
             row = (work + 127) // 128 * 16
             cap = oc * ((work + 15) // 16 * 16)
@@ -477,12 +479,14 @@ def conv_arm(args, workload):
             mp = torch.empty(oc * row, dtype=torch.uint8, device=dev)
             cnt = torch.empty(oc, dtype=torch.int64, device=dev)
             sparse.append((c, k, data, mp, cnt, cap, oc * row))
+            sj = sjobs[j]
+            sj.content, sj.data, sj.data_bytes = c, data.data_ptr(), cap
+            sj.map, sj.map_bytes, sj.counts = mp.data_ptr(), oc * row, cnt.data_ptr()
 
     def step():
         lib.quantize_fold_batch(jobs)
-        for c, k, data, mp, cnt, cap, mb in sparse:
-            lib.sparsify(c, data.data_ptr(), mp.data_ptr(), cnt.data_ptr(), out_mem_kind=abi.VF_MEM_DEVICE, data_bytes=cap,
-                         map_bytes=mb)
+        if sjobs is not None:
+            lib.sparsify_batch(sjobs, out_mem_kind=abi.VF_MEM_DEVICE)
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     warmup = args.warmup if args.profile else max(3, args.warmup)

@@ -315,6 +315,26 @@ int vf_sparsify(vf_ctx* ctx, const vf_content* content, void* data, uint64_t dat
                 void* map, uint64_t map_bytes, int64_t* counts, int out_mem_kind, vf_stats* stats, char* err,
                 size_t errlen);
 
+/* vf_sparsify over many weight tensors per call: what SparsifyWeightsPass does for every NCE operation of a
+ * network (sparsify_weights.cpp:143-229). All tensors share three kernel launches and one read-back of the
+ * compressed sizes, so a set of small convolution weights costs microseconds instead of one synchronous
+ * round trip per tensor. Per job: any of data/map/counts may be NULL; `data_written` receives the compressed
+ * byte size. All outputs of the call live in memory of kind `out_mem_kind`. The first failing job ends the
+ * call; its `status` holds the code that is also returned. */
+typedef struct vf_sparsify_job {
+    vf_content content;
+    void* data;
+    uint64_t data_bytes;
+    void* map;
+    uint64_t map_bytes;
+    int64_t* counts;
+    uint64_t data_written; /* out */
+    int32_t status;        /* out */
+    int32_t reserved;
+} vf_sparsify_job;
+int vf_sparsify_batch(vf_ctx* ctx, vf_sparsify_job* jobs, int njobs, int out_mem_kind, vf_stats* stats, char* err,
+                      size_t errlen);
+
 /* Allocation-free variant of vf_sparsify. It has no counterpart in the reference: it exists for embedders
  * that forbid device allocations while the compiler runs (for example a serving process whose allocator owns
  * all device memory and hands the fold a fixed arena — a cudaMalloc there fails or stalls every stream).

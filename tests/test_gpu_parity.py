@@ -202,6 +202,76 @@ def test_sparsify_and_map(gpu, oracle, dt, shape):
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("density", [0.0, 0.07, 0.5, 0.93, 1.0])
+def test_sparsify_batch(gpu, oracle, density):
+    """Many tensors per call: long rows (several 32-vector steps with a carried remainder), rows that do not
+    allow 16-byte accesses, every element type, a quantized type with a non-zero zero point, jobs without
+    data / map / counts."""
+    rng = np.random.default_rng(int(density * 100) + 3)
+    specs = [([64, 128, 3, 3], I8, None), ([7, 512, 3, 3], U8, 3), ([5, 8, 1, 1], I8, None), ([33, 64, 1, 1], U8, 200),
+             ([9, 72, 2, 2], F16, None), ([3, 4, 3, 2], F16, None), ([4, 136, 1, 1], BF16, None),
+             ([6, 100, 1, 2], F32, None), ([2, 16, 7, 7], I8, None), ([130, 16, 1, 1], I8, None)]
+    jobs = (abi.SparsifyJob * len(specs))()
+    keep, expect, bufs = [], [], []
+    for j, (shape, dt, zp) in enumerate(specs):
+        n = int(np.prod(shape))
+        work = n // shape[0]
+        m = rng.random(n) < density
+        if dt in (I8, U8):
+            fill = 0 if zp is None else zp
+            vals = rng.integers(1, 100, n)
+            vals[vals == fill] += 1
+            x = np.where(m, vals, fill).astype(abi.DTYPE_NUMPY[dt])
+        elif dt == BF16:
+            x = bf16_bits((rng.standard_normal(n) + 3.0) * m)
+        else:
+            x = ((rng.standard_normal(n) + 3.0) * m).astype(abi.DTYPE_NUMPY[dt])
+            if n > 5 and not m[5]:
+                x[5] = -0.0
+        elem = dt if zp is None else Elem.uniform(dt, F16, 0.25, zp, 0, 255)
+        c, k = abi.make_content(TType(shape, elem), x, storage_dtype=dt)
+        row = (work + 127) // 128 * 16
+        cap = n * x.itemsize + 16 * shape[0]
+        want_data, want_map, want_cnt = j != 2, (work % 8 == 0) and j != 3, j != 4
+        od, om, oc_ = np.zeros(cap, np.uint8), np.zeros(shape[0] * row, np.uint8), np.zeros(shape[0], np.int64)
+        w = oracle.sparsify(c, od if want_data else None, om if want_map else None, oc_ if want_cnt else None)
+        gd, gm, gc = np.full(cap, 0xAB, np.uint8), np.full(shape[0] * row, 0xAB, np.uint8), np.full(shape[0], -1, np.int64)
+        jb = jobs[j]
+        jb.content = c
+        if want_data:
+            jb.data, jb.data_bytes = gd.ctypes.data, cap
+        if want_map:
+            jb.map, jb.map_bytes = gm.ctypes.data, gm.nbytes
+        if want_cnt:
+            jb.counts = gc.ctypes.data
+        keep += [c, k, x]
+        expect.append((w, od, om, oc_, want_data, want_map, want_cnt))
+        bufs.append((gd, gm, gc))
+    gpu.sparsify_batch(jobs)
+    assert gpu.last_stats.kernels_launched <= 4
+    for j, ((w, od, om, oc_, want_data, want_map, want_cnt), (gd, gm, gc)) in enumerate(zip(expect, bufs)):
+        if want_data:
+            assert jobs[j].data_written == w, j
+            assert np.array_equal(gd[:w], od[:w]), j
+        if want_map:
+            assert np.array_equal(gm, om), j
+        if want_cnt:
+            assert np.array_equal(gc, oc_), j
+
+
+def test_sparsify_batch_buffer_too_small(gpu):
+    x = np.ones([4, 16, 1, 1], np.int8)
+    c, _k = abi.make_content(TType([4, 16, 1, 1], I8), x)
+    jobs = (abi.SparsifyJob * 1)()
+    out = np.zeros(32, np.uint8)
+    jobs[0].content, jobs[0].data, jobs[0].data_bytes = c, out.ctypes.data, 32
+    from vpux_plugin_b200.lib import VfoldError
+    with pytest.raises(VfoldError) as e:
+        gpu.sparsify_batch(jobs)
+    assert e.value.status == abi.VF_ERR_BUFFER_TOO_SMALL
+    assert jobs[0].status == abi.VF_ERR_BUFFER_TOO_SMALL
+
+
 def test_sparsify_quantized_with_supplied_counts(gpu, oracle):
     rng = np.random.default_rng(10)
     shape = [4, 8, 2, 2]

@@ -119,6 +119,12 @@ class QuantJob(C.Structure):
                 ("status", C.c_int32), ("reserved", C.c_int32)]
 
 
+class SparsifyJob(C.Structure):
+    _fields_ = [("content", Content), ("data", C.c_void_p), ("data_bytes", C.c_uint64), ("map", C.c_void_p),
+                ("map_bytes", C.c_uint64), ("counts", C.c_void_p), ("data_written", C.c_uint64),
+                ("status", C.c_int32), ("reserved", C.c_int32)]
+
+
 class SynthSpec(C.Structure):
     _fields_ = [("seed", C.c_uint64), ("tensor_id", C.c_uint64), ("dtype", C.c_int32), ("reserved", C.c_int32),
                 ("sigma", C.c_float), ("outlier_mult", C.c_float), ("outlier_log2", C.c_int32),

@@ -301,4 +301,25 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// ---- sparsity test ------------------------------------------------------------------------------------
+// element != sparsify value, in the logical storage type (utils/sparsity.cpp:47-63,
+// attributes/sparsify.cpp:143-152, attributes/get_sparsity_map.cpp:44-52). Floating types compare as
+// float, so -0.0 counts as zero.
+__device__ __forceinline__ bool is_dense(const void* p, int dt, int64_t i, long long iv, float fv) {
+    switch (dt) {
+    case VF_DT_I8: return static_cast<const int8_t*>(p)[i] != int8_t(iv);
+    case VF_DT_U8: return static_cast<const uint8_t*>(p)[i] != uint8_t(iv);
+    case VF_DT_F16: return f16_bits_to_f32(static_cast<const uint16_t*>(p)[i]) != fv;
+    case VF_DT_BF16: return bf16_bits_to_f32(static_cast<const uint16_t*>(p)[i]) != fv;
+    default: return static_cast<const float*>(p)[i] != fv;
+    }
+}
+
+__device__ __forceinline__ float sparse_value_as_float(int dt, long long v) {
+    float f = float(v);
+    if (dt == VF_DT_F16) f = f16_bits_to_f32(f32_to_f16_bits(f));
+    if (dt == VF_DT_BF16) f = bf16_bits_to_f32(f32_to_bf16_bits(f));
+    return f;
+}
+
 }  // namespace vf

@@ -808,54 +808,105 @@ int vf_nnz_per_oc(vf_ctx* ctx, const vf_content* content, int64_t* counts, int o
     });
 }
 
+// Sparsify + GetSparsityMap + counts of `n` tensors: all tensors share three launches (counts and bitmaps,
+// offsets, compaction; the compaction's second read of the weights is served from L2 for anything smaller
+// than the cache) and ONE read-back of the compressed sizes.
+static void sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem_kind, vf_stats* stats) {
+    struct PerJob {
+        DContent in, v;
+        DBuf tcounts, tmap, tdata, counts_dev, offsets;
+        int64_t oc = 0, row_bytes = 0;
+    };
+    std::vector<PerJob> pj(static_cast<size_t>(n));
+    std::vector<SparseJob> sj(static_cast<size_t>(n));
+    for (int j = 0; j < n; ++j) {
+        vf_sparsify_job& jb = jobs[j];
+        PerJob& p = pj[j];
+        jb.status = VF_OK;
+        jb.data_written = 0;
+        p.in = upload_base(ctx, jb.content, stats);
+        if (p.in.type.rank != 4) raise(VF_ERR_SHAPE, "Expected 4D input shape");
+        const int dt = p.in.type.elem.dtype;
+        check_sparse_dtype(dt);
+        const int64_t oc = p.in.type.shape[0], work = p.in.type.shape[1] * p.in.type.shape[2] * p.in.type.shape[3];
+        p.oc = oc;
+        p.row_bytes = align_up(work, 128) / 8;
+        if (jb.map) {
+            if (work % 8 != 0) raise(VF_ERR_SHAPE, "GetSparsityMap needs IC*KY*KX (%lld) to be a multiple of 8", (long long)work);
+            if (jb.map_bytes < uint64_t(oc * p.row_bytes)) raise(VF_ERR_BUFFER_TOO_SMALL, "sparsity map needs %lld bytes", (long long)(oc * p.row_bytes));
+        }
+        p.v = materialise_logical(ctx, p.in);
+        SparseJob& s = sj[j];
+        s.in = p.v.d;
+        s.dt = dt;
+        s.es = dtype_bits(dt) / 8;
+        s.oc = oc;
+        s.work = work;
+        s.sv = sparsify_value(p.in.type.elem);
+        s.counts = static_cast<int64_t*>(out_ptr(ctx, jb.counts, out_mem_kind, size_t(oc) * 8, p.tcounts));
+        if (!s.counts) {
+            p.counts_dev = DBuf(ctx, size_t(oc) * 8);
+            s.counts = p.counts_dev.as<int64_t>();
+        }
+        s.map = static_cast<uint8_t*>(out_ptr(ctx, jb.map, out_mem_kind, size_t(oc * p.row_bytes), p.tmap));
+        s.map_row_bytes = p.row_bytes;
+        s.data = static_cast<uint8_t*>(out_ptr(ctx, jb.data, out_mem_kind, jb.data_bytes, p.tdata));
+        s.capacity = jb.data_bytes;
+        s.offsets = nullptr;
+        if (s.data) {
+            p.offsets = DBuf(ctx, size_t(oc + 1) * 8);
+            s.offsets = p.offsets.as<int64_t>();
+        }
+    }
+    DBuf totals(ctx, size_t(n) * 8);
+    launch_sparsify_batch(ctx, sj, totals.as<int64_t>());
+    std::vector<int64_t> total_host(static_cast<size_t>(n), 0);
+    VF_CUDA(cudaMemcpyAsync(total_host.data(), totals.p, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    VF_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (int j = 0; j < n; ++j) {
+        vf_sparsify_job& jb = jobs[j];
+        PerJob& p = pj[j];
+        const uint64_t total = uint64_t(total_host[j]);
+        if (jb.data && total > jb.data_bytes) {
+            jb.status = VF_ERR_BUFFER_TOO_SMALL;
+            raise(VF_ERR_BUFFER_TOO_SMALL, "compressed weights need %llu bytes, buffer holds %llu", (unsigned long long)total, (unsigned long long)jb.data_bytes);
+        }
+        if (jb.data) {
+            out_flush(ctx, jb.data, out_mem_kind, total, p.tdata);
+            if (out_mem_kind != VF_MEM_DEVICE && stats) stats->d2h_bytes += total;
+        }
+        out_flush(ctx, jb.counts, out_mem_kind, size_t(p.oc) * 8, p.tcounts);
+        out_flush(ctx, jb.map, out_mem_kind, size_t(p.oc * p.row_bytes), p.tmap);
+        jb.data_written = total;
+        if (stats) stats->bytes_out += total + (jb.map ? uint64_t(p.oc * p.row_bytes) : 0);
+    }
+}
+
 int vf_sparsify(vf_ctx* ctx, const vf_content* content, void* data, uint64_t data_bytes, uint64_t* data_written,
                 void* map, uint64_t map_bytes, int64_t* counts, int out_mem_kind, vf_stats* stats, char* err,
                 size_t errlen) {
     return guard(err, errlen, [&] {
         if (!content) raise(VF_ERR_INVALID_ARG, "NULL argument");
         CallScope scope(ctx, stats);
-        DContent in = upload_base(ctx, *content, stats);
-        if (in.type.rank != 4) raise(VF_ERR_SHAPE, "Expected 4D input shape");
-        const int dt = in.type.elem.dtype;
-        check_sparse_dtype(dt);
-        const int es = dtype_bits(dt) / 8;
-        const int64_t sv = sparsify_value(in.type.elem);
-        const int64_t oc = in.type.shape[0], work = in.type.shape[1] * in.type.shape[2] * in.type.shape[3];
-        const int64_t row_bytes = align_up(work, 128) / 8;
-        if (map) {
-            if (work % 8 != 0) raise(VF_ERR_SHAPE, "GetSparsityMap needs IC*KY*KX (%lld) to be a multiple of 8", (long long)work);
-            if (map_bytes < uint64_t(oc * row_bytes)) raise(VF_ERR_BUFFER_TOO_SMALL, "sparsity map needs %lld bytes", (long long)(oc * row_bytes));
-        }
-        DContent v = materialise_logical(ctx, in);
-        // pass 1: counts + bitmap in one sweep; pass 2: offsets; pass 3: compaction (second read of the
-        // weights, served from L2 for anything smaller than the cache)
-        DBuf tcounts, tmap, tdata;
-        DBuf counts_dev;
-        int64_t* dc = static_cast<int64_t*>(out_ptr(ctx, counts, out_mem_kind, size_t(oc) * 8, tcounts));
-        if (!dc) {
-            counts_dev = DBuf(ctx, size_t(oc) * 8);
-            dc = counts_dev.as<int64_t>();
-        }
-        uint8_t* dm = static_cast<uint8_t*>(out_ptr(ctx, map, out_mem_kind, size_t(oc * row_bytes), tmap));
-        launch_sparsity_scan(ctx, v.d, dt, oc, work, sv, dc, dm, row_bytes);
-        uint64_t total_host = 0;
-        if (data) {
-            DBuf offsets(ctx, size_t(oc + 1) * 8);
-            launch_sparse_offsets(ctx, dc, oc, es, offsets.as<int64_t>());
-            uint8_t* dd = static_cast<uint8_t*>(out_ptr(ctx, data, out_mem_kind, data_bytes, tdata));
-            launch_sparse_compact(ctx, v.d, dt, oc, work, sv, offsets.as<int64_t>(), dd, data_bytes);
-            int64_t total = 0;
-            VF_CUDA(cudaMemcpyAsync(&total, offsets.as<int64_t>() + oc, 8, cudaMemcpyDeviceToHost, ctx->stream));
-            VF_CUDA(cudaStreamSynchronize(ctx->stream));
-            total_host = uint64_t(total);
-            if (total_host > data_bytes) raise(VF_ERR_BUFFER_TOO_SMALL, "compressed weights need %llu bytes, buffer holds %llu", (unsigned long long)total_host, (unsigned long long)data_bytes);
-            out_flush(ctx, data, out_mem_kind, total_host, tdata);
-            if (out_mem_kind != VF_MEM_DEVICE && stats) stats->d2h_bytes += total_host;
-        }
-        out_flush(ctx, counts, out_mem_kind, size_t(oc) * 8, tcounts);
-        out_flush(ctx, map, out_mem_kind, size_t(oc * row_bytes), tmap);
-        if (data_written) *data_written = total_host;
-        if (stats) stats->bytes_out += total_host + (map ? uint64_t(oc * row_bytes) : 0);
+        vf_sparsify_job jb{};
+        jb.content = *content;
+        jb.data = data;
+        jb.data_bytes = data_bytes;
+        jb.map = map;
+        jb.map_bytes = map_bytes;
+        jb.counts = counts;
+        sparsify_many(ctx, &jb, 1, out_mem_kind, stats);
+        if (data_written) *data_written = jb.data_written;
+        scope.finish();
+    });
+}
+
+int vf_sparsify_batch(vf_ctx* ctx, vf_sparsify_job* jobs, int njobs, int out_mem_kind, vf_stats* stats, char* err,
+                      size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, stats);
+        if (njobs > 0) sparsify_many(ctx, jobs, njobs, out_mem_kind, stats);
         scope.finish();
     });
 }

@@ -54,6 +54,25 @@ void launch_sparse_offsets(vf_ctx* ctx, const int64_t* d_counts, int64_t oc, int
 void launch_sparse_compact(vf_ctx* ctx, const void* in, int dt, int64_t oc, int64_t work, int64_t sparse_value,
                            const int64_t* d_offsets, uint8_t* out, uint64_t capacity);
 
+// Many tensors per launch. One entry per tensor; all pointers are device pointers.
+struct SparseJob {
+    const void* in;         // [oc][work] elements of logical dtype `dt`
+    int dt, es;             // element type and its size in bytes
+    int64_t oc, work;
+    long long sv;           // sparsify value
+    int64_t* counts;        // [oc], always written
+    uint8_t* map;           // optional bitmap, rows of map_row_bytes
+    int64_t map_row_bytes;
+    int64_t* offsets;       // [oc + 1] byte offsets of the compacted rows (scratch); NULL when `data` is NULL
+    uint8_t* data;          // optional compacted output
+    uint64_t capacity;      // bytes behind `data`
+    int vec;                // rows, map and data allow 16-byte accesses (set by launch_sparsify_batch)
+    int64_t unit_begin;     // index of this tensor's first output channel in the launch (set by the launcher)
+};
+// Three launches for the whole list: counts + bitmaps, per-tensor offsets (total bytes of tensor j into
+// d_totals[j]; 0 for tensors without `data`), compaction. An overflow of `capacity` sets VF_FLAG_OVERFLOW.
+void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d_totals);
+
 // ---- statistics --------------------------------------------------------------------------------------
 // min/max (over values and 0) or absmax per unit of `unit_len` consecutive elements, then
 // calcScaleAndZeroPoint. Any output may be NULL.

@@ -28,7 +28,7 @@ def _load():
                           "(the package has no CPU fallback)")
     lib = C.CDLL(LIB_PATH)
     for name in ("vf_infer_type", "vf_fold", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
-                 "vf_nnz_per_oc", "vf_sparsify", "vf_weights_table", "vf_synth_fill", "vf_plan_shards",
+                 "vf_nnz_per_oc", "vf_sparsify", "vf_sparsify_batch", "vf_weights_table", "vf_synth_fill", "vf_plan_shards",
                  "vf_ctx_create", "vf_ctx_synchronize", "vf_abi_version", "vf_ctx_device"):
         getattr(lib, name).restype = C.c_int
     lib.vf_ctx_destroy.restype = None
@@ -203,6 +203,13 @@ class Library:
                                   C.byref(self.last_stats), err, C.c_size_t(512))
         self._check(st, err)
         return written.value
+
+    def sparsify_batch(self, jobs, out_mem_kind=abi.VF_MEM_HOST):
+        """jobs: ctypes array of abi.SparsifyJob; `data_written` of every job is filled in."""
+        err = self._err()
+        st = self.lib.vf_sparsify_batch(self.ctx, jobs, len(jobs), int(out_mem_kind), C.byref(self.last_stats), err,
+                                        C.c_size_t(512))
+        self._check(st, err)
 
     def weights_table(self, desc, oc, table=None, out_mem_kind=abi.VF_MEM_HOST):
         if table is None:
