@@ -141,17 +141,23 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // The largest rounding residual is tracked with max (no per-element branch); one comparison per vector.
 template <typename InT>
 __device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float thr, float* m) {
+    // Packed two-wide fp32 instructions (sm_100): each is the same IEEE round-to-nearest operation on both
+    // halves, so the results equal the scalar sequence bit for bit at half the issue slots. t - s is formed
+    // as fma(s, -1, t): the product is exact, so it rounds once like the subtraction.
     const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+    const float2 inv2 = make_float2(inv, inv), c2 = make_float2(c, c);
+    const float2 mg = make_float2(kMagic, kMagic), nmg = make_float2(-kMagic, -kMagic), neg1 = make_float2(-1.f, -1.f);
     float worst = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 x = P2<InT>::both(w[i]);
-        const float t0 = __fmaf_rn(x.x, inv, c), t1 = __fmaf_rn(x.y, inv, c);
-        m[2 * i] = __fadd_rn(t0, kMagic);
-        m[2 * i + 1] = __fadd_rn(t1, kMagic);
-        const float r0 = __fsub_rn(t0, __fsub_rn(m[2 * i], kMagic));
-        const float r1 = __fsub_rn(t1, __fsub_rn(m[2 * i + 1], kMagic));
-        worst = fmaxf(worst, fmaxf(fabsf(r0), fabsf(r1)));
+        const float2 t = __ffma2_rn(x, inv2, c2);
+        const float2 mm = __fadd2_rn(t, mg);
+        const float2 s = __fadd2_rn(mm, nmg);
+        const float2 r = __ffma2_rn(s, neg1, t);
+        m[2 * i] = mm.x;
+        m[2 * i + 1] = mm.y;
+        worst = fmaxf(worst, fmaxf(fabsf(r.x), fabsf(r.y)));
     }
     return worst > thr;
 }
@@ -376,25 +382,46 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
 
 // ======================================================================================================
 // K_row: one unit per row, 16-byte aligned rows of a [rows, cols] matrix (per-output-channel quantization of
-// linear weights), 2-byte input. One CTA per row, looping over the rows of all jobs; the row is staged in
-// shared memory. The optional Dequantize copy uses a per-row table of the L possible outputs (each entry
-// computed with the exact FP64 formula, indexed by the code byte), so the sweep costs one shared-memory
-// lookup per element.
+// linear weights), 2-byte input. A CTA of 256 threads is split into 256 / T independent row groups: the T
+// threads of a group stage one row in shared memory and walk the rows of all jobs on their own, synchronising
+// through the group's named barrier only. While one group sits in the scalar FP64 derivation of its row's
+// scale, the other groups of the SM keep sweeping. The optional Dequantize copy uses a per-row table of the L
+// possible outputs (each entry computed with the exact FP64 formula, indexed by the code byte), so the sweep
+// costs one shared-memory lookup per element.
 // ======================================================================================================
-template <typename InT, int THREADS, int DQ>  // DQ: 0 = no dequantized copy, 1 = 16-bit float copy, 2 = f32 copy
-__global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
-    extern __shared__ uint4 smem_u4[];
-    __shared__ float s_mn[THREADS / 32], s_mx[THREADS / 32];
-    __shared__ UnitQ s_u;
-    __shared__ double s_scale;
-    __shared__ long long s_zp;
-    __shared__ uint32_t s_lut[256];  // dequantized value of code byte b (16-bit types in the low half)
-    constexpr int kFixCap = 1024;    // vectors noted for repair per row; beyond that the sweep repairs inline
-    __shared__ int s_fix[kFixCap];
-    __shared__ int s_nfix;
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+template <int T>
+__device__ __forceinline__ void group_sync(int bar_id) {
+    if (T == 256) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(T) : "memory");
+}
+
+template <typename InT, int T, int DQ>  // DQ: 0 = no dequantized copy, 1 = 16-bit float copy, 2 = f32 copy
+__global__ void __launch_bounds__(256) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs,
+                                             int* flags) {
+    constexpr int THREADS = T;
+    constexpr int kGroups = 256 / T;
+    constexpr int kFixCap = 256;  // vectors noted for repair per row; beyond that the sweep repairs inline
+    extern __shared__ uint4 smem_all[];
+    struct GroupShared {
+        float mn[T / 32], mx[T / 32];
+        UnitQ u;
+        double scale;
+        long long zp;
+        uint32_t lut[256];  // dequantized value of code byte b (16-bit types in the low half)
+        int fix[kFixCap];
+        int nfix;
+    };
+    __shared__ GroupShared gs_all[kGroups];
+    const int grp = threadIdx.x / T, tid = threadIdx.x % T, lane = tid & 31, wid = tid >> 5;
+    GroupShared& gs = gs_all[grp];
+    float* const s_mn = gs.mn;
+    float* const s_mx = gs.mx;
+    uint32_t* const s_lut = gs.lut;
+    int* const s_fix = gs.fix;
+    uint4* const smem_u4 = smem_all + size_t(grp) * size_t(stage_vecs);
+    const int bar_id = 1 + grp;
     const int bias = p.qmin;  // code = n + qmin
-    if (tid == 0) s_nfix = 0;  // made visible by the first barrier of the row loop
+    if (tid == 0) gs.nfix = 0;  // made visible by the first barrier of the row loop
 
     int j = 0;
     int64_t job_end = 0;
@@ -406,7 +433,8 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
     uint8_t* o_deq = nullptr;
     int64_t cols = 0, unit_begin = 0;
 
-    for (int64_t row = blockIdx.x; row < p.total_units; row += gridDim.x) {
+    const int64_t row_stride = int64_t(gridDim.x) * kGroups;
+    for (int64_t row = int64_t(blockIdx.x) * kGroups + grp; row < p.total_units; row += row_stride) {
         if (row >= job_end) {
             j = find_job(jobs, p.njobs, row);
             const RowQuantArgs J = jobs[j];
@@ -433,7 +461,7 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
             s_mn[wid] = mn;
             s_mx[wid] = mx;
         }
-        __syncthreads();
+        group_sync<T>(bar_id);
         if (wid == 0) {
             mn = lane < THREADS / 32 ? s_mn[lane] : 0.f;
             mx = lane < THREADS / 32 ? s_mx[lane] : 0.f;
@@ -447,36 +475,39 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
                 // shift the rounding target by qmin so that the low byte of (t + magic) is the code in two's
                 // complement; the extra rounding of the constant stays inside the guard band (|c + qmin| <= 255)
                 u.c = __fadd_rn(u.c, float(bias));
-                s_u = u;
-                s_scale = scale;
-                s_zp = zp;
+                gs.u = u;
+                gs.scale = scale;
+                gs.zp = zp;
                 if (o_scales) o_scales[r] = scale;
                 if (o_zps) o_zps[r] = zp;
                 if (o_f16) o_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
             }
         }
-        __syncthreads();
-        const UnitQ u = s_u;
+        group_sync<T>(bar_id);
+        const UnitQ u = gs.u;
         if (DQ != 0) {
+            const double scale = gs.scale;
+            const long long zp = gs.zp;
             for (int n = tid; n <= p.lm1; n += THREADS) {
                 const int code = n + bias;
-                const float f = dequantize_exact(code, s_scale, s_zp);
+                const float f = dequantize_exact(code, scale, zp);
                 s_lut[code & 0xFF] = DQ == 2 ? __float_as_uint(f)
                                      : (p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f));
             }
-            __syncthreads();
+            group_sync<T>(bar_id);
         }
         uint2* codes = reinterpret_cast<uint2*>(o_codes + r * cols);
         uint4* deq16 = reinterpret_cast<uint4*>(o_deq + r * cols * 2);
         float4* deq32 = reinterpret_cast<float4*>(o_deq + r * cols * 4);
         const float thr = p.thr;
+#pragma unroll 2
         for (int i = tid; i < nvec; i += THREADS) {
             const uint4 d = smem_u4[i];
             float m[8];
             if (quant8<InT>(d, u.inv, u.c, thr, m)) {
                 // a vector with an element in the guard band is noted and repaired after the sweep by eight
                 // threads at once, so the sweep itself never diverges into the exact sequence
-                const int slot = atomicAdd(&s_nfix, 1);
+                const int slot = atomicAdd(&gs.nfix, 1);
                 if (slot < kFixCap) s_fix[slot] = i;
                 else VF_QUANT8_FIX(InT, d, u, thr, p.lm1, bias, m);
             }
@@ -500,10 +531,10 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
                 }
             }
         }
-        __syncthreads();
+        group_sync<T>(bar_id);
         // repair: one thread per element of every noted vector; elements outside the guard band keep the
         // value the sweep stored, the others are recomputed exactly and patched in place
-        const int nfix = min(s_nfix, kFixCap);
+        const int nfix = min(gs.nfix, kFixCap);
         for (int e = tid; e < nfix * 8; e += THREADS) {
             const int i = s_fix[e >> 3], k = e & 7;
             const uint32_t pair = reinterpret_cast<const uint32_t*>(smem_u4 + i)[k >> 1];
@@ -518,8 +549,8 @@ __global__ void __launch_bounds__(THREADS) k_row(const RowQuantArgs* __restrict_
                 if (DQ == 2) reinterpret_cast<uint32_t*>(o_deq)[pos] = s_lut[code & 0xFF];
             }
         }
-        __syncthreads();  // s_u, s_lut and the repair list are rewritten by the next row
-        if (tid == 0) s_nfix = 0;
+        group_sync<T>(bar_id);  // u, the table and the repair list are rewritten by the next row
+        if (tid == 0) gs.nfix = 0;
     }
 }
 
@@ -726,29 +757,37 @@ void launch_group_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams&
     }
 }
 
-template <typename InT, int THREADS>
-void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, size_t smem, int dq) {
-    // persistent grid sized by how many CTAs fit an SM (shared memory, 2048 threads, 64K registers at <= 64 each)
-    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(1024 / THREADS, (220 * 1024) / (smem + 2048)));
-    const int grid = int(std::min<int64_t>(p.total_units, int64_t(148) * int64_t(per_sm)));
+template <typename InT, int T>
+void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, int64_t max_cols, int dq) {
+    constexpr int kGroups = 256 / T;
+    const int stage_vecs = int((max_cols + 7) / 8);
+    const size_t smem = size_t(kGroups) * size_t(stage_vecs) * 16;
+    // persistent grid sized by how many CTAs fit an SM: shared memory (the stages plus about 2.2 KB of per-group
+    // state and 1 KB the hardware reserves per CTA) and 64K registers at <= 64 per thread
+    const size_t per_cta = smem + size_t(kGroups) * 2304 + 1024;
+    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (227 * 1024) / per_cta));
+    const int64_t ctas = (p.total_units + kGroups - 1) / kGroups;
+    const int grid = int(std::min<int64_t>(ctas, int64_t(148) * int64_t(per_sm)));
     if (dq == 0) {
-        set_smem(k_row<InT, THREADS, 0>, smem);
-        k_row<InT, THREADS, 0><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+        set_smem(k_row<InT, T, 0>, smem);
+        k_row<InT, T, 0><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     } else if (dq == 1) {
-        set_smem(k_row<InT, THREADS, 1>, smem);
-        k_row<InT, THREADS, 1><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+        set_smem(k_row<InT, T, 1>, smem);
+        k_row<InT, T, 1><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     } else {
-        set_smem(k_row<InT, THREADS, 2>, smem);
-        k_row<InT, THREADS, 2><<<grid, THREADS, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+        set_smem(k_row<InT, T, 2>, smem);
+        k_row<InT, T, 2><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     }
     post_launch(ctx);
 }
 
 template <typename InT>
 void launch_row_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, int64_t max_cols, int dq) {
-    const size_t smem = size_t(max_cols) * 2;
-    if (max_cols <= 8192) launch_row_n<InT, 256>(ctx, d_jobs, p, smem, dq);
-    else launch_row_n<InT, 512>(ctx, d_jobs, p, smem, dq);
+    // threads per row: enough vectors per thread to amortise the per-row work, few enough that the rows in
+    // flight on an SM (and with them the independent barriers) stay numerous
+    if (max_cols <= 8192) launch_row_n<InT, 64>(ctx, d_jobs, p, max_cols, dq);
+    else if (max_cols <= 16384) launch_row_n<InT, 128>(ctx, d_jobs, p, max_cols, dq);
+    else launch_row_n<InT, 256>(ctx, d_jobs, p, max_cols, dq);
 }
 
 }  // namespace
