@@ -389,6 +389,25 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
 // possible outputs (each entry computed with the exact FP64 formula, indexed by the code byte), so the sweep
 // costs one shared-memory lookup per element.
 // ======================================================================================================
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// stores through the global window: the compiler then knows they cannot alias the shared-memory stage
+__device__ __forceinline__ void st_global_v2(void* p, uint32_t a, uint32_t b) {
+    asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(__cvta_generic_to_global(p)), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(__cvta_generic_to_global(p)), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
 template <int T>
 __device__ __forceinline__ void group_sync(int bar_id) {
     if (T == 256) __syncthreads();
@@ -396,32 +415,39 @@ __device__ __forceinline__ void group_sync(int bar_id) {
 }
 
 template <typename InT, int T, int DQ>  // DQ: 0 = no dequantized copy, 1 = 16-bit float copy, 2 = f32 copy
-__global__ void __launch_bounds__(256) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs,
+__global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs,
                                              int* flags) {
     constexpr int THREADS = T;
     constexpr int kGroups = 256 / T;
-    constexpr int kFixCap = 256;  // vectors noted for repair per row; beyond that the sweep repairs inline
+    constexpr int kFixCap = 128;  // vectors noted for repair per row; beyond that the sweep repairs inline
     extern __shared__ uint4 smem_all[];
     struct GroupShared {
         float mn[T / 32], mx[T / 32];
         UnitQ u;
         double scale;
         long long zp;
-        uint32_t lut[256];  // dequantized value of code byte b (16-bit types in the low half)
-        int fix[kFixCap];
-        int nfix;
+        int fix[kFixCap];   // vectors with an element in the guard band
+        int fix2[kFixCap];  // elements in the guard band
+        int nfix, nfix2;
     };
     __shared__ GroupShared gs_all[kGroups];
+    // dequantized value of code byte b: 16-bit entries (DQ == 1) or 32-bit entries; aligned to its size so that
+    // an entry's address is the table's address OR the entry's offset
+    __shared__ __align__(1024) uint32_t s_lut_all[kGroups][256];
     const int grp = threadIdx.x / T, tid = threadIdx.x % T, lane = tid & 31, wid = tid >> 5;
     GroupShared& gs = gs_all[grp];
     float* const s_mn = gs.mn;
     float* const s_mx = gs.mx;
-    uint32_t* const s_lut = gs.lut;
+    uint32_t* const s_lut = s_lut_all[grp];
+    const uint32_t lut_sh = uint32_t(__cvta_generic_to_shared(s_lut));
     int* const s_fix = gs.fix;
     uint4* const smem_u4 = smem_all + size_t(grp) * size_t(stage_vecs);
     const int bar_id = 1 + grp;
     const int bias = p.qmin;  // code = n + qmin
-    if (tid == 0) gs.nfix = 0;  // made visible by the first barrier of the row loop
+    if (tid == 0) {  // made visible by the first barrier of the row loop
+        gs.nfix = 0;
+        gs.nfix2 = 0;
+    }
 
     int j = 0;
     int64_t job_end = 0;
@@ -491,66 +517,95 @@ __global__ void __launch_bounds__(256) k_row(const RowQuantArgs* __restrict__ jo
             for (int n = tid; n <= p.lm1; n += THREADS) {
                 const int code = n + bias;
                 const float f = dequantize_exact(code, scale, zp);
-                s_lut[code & 0xFF] = DQ == 2 ? __float_as_uint(f)
-                                     : (p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f));
+                if (DQ == 2) s_lut[code & 0xFF] = __float_as_uint(f);
+                else reinterpret_cast<uint16_t*>(s_lut)[code & 0xFF] = p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f);
             }
             group_sync<T>(bar_id);
         }
-        uint2* codes = reinterpret_cast<uint2*>(o_codes + r * cols);
-        uint4* deq16 = reinterpret_cast<uint4*>(o_deq + r * cols * 2);
-        float4* deq32 = reinterpret_cast<float4*>(o_deq + r * cols * 4);
+        uint8_t* const codes_row = o_codes + r * cols;
+        uint8_t* const deq_row = DQ == 0 ? nullptr : o_deq + r * cols * (DQ == 1 ? 2 : 4);
         const float thr = p.thr;
-#pragma unroll 2
-        for (int i = tid; i < nvec; i += THREADS) {
-            const uint4 d = smem_u4[i];
-            float m[8];
-            if (quant8<InT>(d, u.inv, u.c, thr, m)) {
-                // a vector with an element in the guard band is noted and repaired after the sweep by eight
-                // threads at once, so the sweep itself never diverges into the exact sequence
-                const int slot = atomicAdd(&gs.nfix, 1);
-                if (slot < kFixCap) s_fix[slot] = i;
-                else VF_QUANT8_FIX(InT, d, u, thr, p.lm1, bias, m);
-            }
-            const uint32_t w0 = pack_bytes4(m), w1 = pack_bytes4(m + 4);
-            codes[i] = make_uint2(w0, w1);
-            if (DQ != 0) {
-                uint32_t q[8];
+        // The sweep handles kBatch vectors per step: all shared-memory loads of the step are issued first, then
+        // the independent arithmetic chains and the stores.
+        constexpr int kBatch = 4;
+        for (int i0 = tid; i0 < nvec; i0 += kBatch * THREADS) {
+            uint4 d[kBatch];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {  // byte k of w, already scaled to the entry's byte offset
-                    const uint32_t o0 = (k == 0 ? (w0 << 2) : (w0 >> (8 * k - 2))) & 0x3FCu;
-                    const uint32_t o1 = (k == 0 ? (w1 << 2) : (w1 >> (8 * k - 2))) & 0x3FCu;
-                    q[k] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(s_lut) + o0);
-                    q[4 + k] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(s_lut) + o1);
+            for (int b = 0; b < kBatch; ++b) {
+                const int i = i0 + b * THREADS;
+                d[b] = i < nvec ? smem_u4[i] : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                const int i = i0 + b * THREADS;
+                if (i >= nvec) break;
+                float m[8];
+                if (quant8<InT>(d[b], u.inv, u.c, thr, m)) {
+                    // a vector with an element in the guard band is noted and repaired after the sweep, so the
+                    // sweep itself never diverges into the exact sequence
+                    const int slot = atomicAdd(&gs.nfix, 1);
+                    if (slot < kFixCap) s_fix[slot] = i;
+                    else VF_QUANT8_FIX(InT, d[b], u, thr, p.lm1, bias, m);
                 }
-                if (DQ == 2) {
-                    deq32[2 * i] = make_float4(__uint_as_float(q[0]), __uint_as_float(q[1]), __uint_as_float(q[2]), __uint_as_float(q[3]));
-                    deq32[2 * i + 1] = make_float4(__uint_as_float(q[4]), __uint_as_float(q[5]), __uint_as_float(q[6]), __uint_as_float(q[7]));
-                } else {
-                    deq16[i] = make_uint4(__byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
-                                          __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
+                const uint32_t w0 = pack_bytes4(m), w1 = pack_bytes4(m + 4);
+                st_global_v2(codes_row + size_t(i) * 8, w0, w1);
+                if (DQ != 0) {
+                    // table entry of byte k of w: shift the byte to the entry's offset, mask it and OR the table's
+                    // (size-aligned) shared-memory address in, all in one logic instruction after the shift
+                    constexpr int kSh = DQ == 1 ? 1 : 2;
+                    constexpr uint32_t kMask = DQ == 1 ? 0x1FEu : 0x3FCu;
+                    uint32_t q[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t o0 = ((k == 0 ? (w0 << kSh) : (w0 >> (8 * k - kSh))) & kMask) | lut_sh;
+                        const uint32_t o1 = ((k == 0 ? (w1 << kSh) : (w1 >> (8 * k - kSh))) & kMask) | lut_sh;
+                        q[k] = DQ == 1 ? lds_u16(o0) : lds_u32(o0);
+                        q[4 + k] = DQ == 1 ? lds_u16(o1) : lds_u32(o1);
+                    }
+                    if (DQ == 2) {
+                        st_global_v4(deq_row + size_t(i) * 32, q[0], q[1], q[2], q[3]);
+                        st_global_v4(deq_row + size_t(i) * 32 + 16, q[4], q[5], q[6], q[7]);
+                    } else {
+                        st_global_v4(deq_row + size_t(i) * 16, __byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
+                                     __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
+                    }
                 }
             }
         }
         group_sync<T>(bar_id);
-        // repair: one thread per element of every noted vector; elements outside the guard band keep the
-        // value the sweep stored, the others are recomputed exactly and patched in place
+        // Repair in two steps so that the exact sequence runs on full warps: first one thread per element of
+        // every noted vector lists the elements that really lie in the guard band, then the listed elements are
+        // recomputed exactly and patched in place (the others keep what the sweep stored).
         const int nfix = min(gs.nfix, kFixCap);
-        for (int e = tid; e < nfix * 8; e += THREADS) {
-            const int i = s_fix[e >> 3], k = e & 7;
-            const uint32_t pair = reinterpret_cast<const uint32_t*>(smem_u4 + i)[k >> 1];
-            const float x = (k & 1) ? P2<InT>::hi(pair) : P2<InT>::lo(pair);
-            const float t = __fmaf_rn(x, u.inv, u.c);
-            const float mg = __fadd_rn(t, kMagic);
-            if (fabsf(__fsub_rn(t, __fsub_rn(mg, kMagic))) > thr) {
+        if (nfix > 0) {
+            const uint16_t* row16 = reinterpret_cast<const uint16_t*>(smem_u4);
+            auto patch = [&](int idx) {
+                const float x = P2<InT>::lo(uint32_t(row16[idx]));
                 const int code = quant_index_exact(x, u.in_low, u.range, p.lm1) + bias;
-                const int64_t pos = r * cols + int64_t(i) * 8 + k;
-                o_codes[pos] = uint8_t(code);
-                if (DQ == 1) reinterpret_cast<uint16_t*>(o_deq)[pos] = uint16_t(s_lut[code & 0xFF]);
-                if (DQ == 2) reinterpret_cast<uint32_t*>(o_deq)[pos] = s_lut[code & 0xFF];
+                codes_row[idx] = uint8_t(code);
+                if (DQ == 1) reinterpret_cast<uint16_t*>(deq_row)[idx] = reinterpret_cast<const uint16_t*>(s_lut)[code & 0xFF];
+                if (DQ == 2) reinterpret_cast<uint32_t*>(deq_row)[idx] = s_lut[code & 0xFF];
+            };
+            for (int e = tid; e < nfix * 8; e += THREADS) {
+                const int idx = s_fix[e >> 3] * 8 + (e & 7);
+                const float x = P2<InT>::lo(uint32_t(row16[idx]));
+                const float t = __fmaf_rn(x, u.inv, u.c);
+                const float mg = __fadd_rn(t, kMagic);
+                if (fabsf(__fsub_rn(t, __fsub_rn(mg, kMagic))) > thr) {
+                    const int slot = atomicAdd(&gs.nfix2, 1);
+                    if (slot < kFixCap) gs.fix2[slot] = idx;
+                    else patch(idx);
+                }
             }
+            group_sync<T>(bar_id);
+            const int nfix2 = min(gs.nfix2, kFixCap);
+            for (int e = tid; e < nfix2; e += THREADS) patch(gs.fix2[e]);
         }
         group_sync<T>(bar_id);  // u, the table and the repair list are rewritten by the next row
-        if (tid == 0) gs.nfix = 0;
+        if (tid == 0) {
+            gs.nfix = 0;
+            gs.nfix2 = 0;
+        }
     }
 }
 
@@ -762,20 +817,21 @@ void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p
     constexpr int kGroups = 256 / T;
     const int stage_vecs = int((max_cols + 7) / 8);
     const size_t smem = size_t(kGroups) * size_t(stage_vecs) * 16;
-    // persistent grid sized by how many CTAs fit an SM: shared memory (the stages plus about 2.2 KB of per-group
-    // state and 1 KB the hardware reserves per CTA) and 64K registers at <= 64 per thread
-    const size_t per_cta = smem + size_t(kGroups) * 2304 + 1024;
-    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (227 * 1024) / per_cta));
+    // persistent grid: as many CTAs as the runtime says fit an SM (shared memory and registers both count)
+    auto ctas_per_sm = [&](auto kernel) {
+        set_smem(kernel, smem);
+        int n = 0;
+        VF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, smem));
+        return std::max(1, n);
+    };
+    const int per_sm = dq == 0 ? ctas_per_sm(k_row<InT, T, 0>) : dq == 1 ? ctas_per_sm(k_row<InT, T, 1>) : ctas_per_sm(k_row<InT, T, 2>);
     const int64_t ctas = (p.total_units + kGroups - 1) / kGroups;
     const int grid = int(std::min<int64_t>(ctas, int64_t(148) * int64_t(per_sm)));
     if (dq == 0) {
-        set_smem(k_row<InT, T, 0>, smem);
         k_row<InT, T, 0><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     } else if (dq == 1) {
-        set_smem(k_row<InT, T, 1>, smem);
         k_row<InT, T, 1><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     } else {
-        set_smem(k_row<InT, T, 2>, smem);
         k_row<InT, T, 2><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     }
     post_launch(ctx);
