@@ -230,6 +230,25 @@ __device__ __forceinline__ int find_job(const RowQuantArgs* __restrict__ jobs, i
     return lo;
 }
 
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// stores through the global window (no memory clobber: they never alias the shared-memory stage, so the
+// compiler may move shared-memory loads across them; barriers still order them)
+__device__ __forceinline__ void st_global_v2(void* p, uint32_t a, uint32_t b) {
+    asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(__cvta_generic_to_global(p)), "r"(a), "r"(b));
+}
+__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(__cvta_generic_to_global(p)), "r"(a), "r"(b), "r"(c), "r"(d));
+}
+
 // ======================================================================================================
 // K_group: units of G consecutive elements (per-group quantization), 2-byte input.
 // A warp owns a chunk of 32 consecutive groups (32*G elements, contiguous in memory). The chunk is copied
@@ -339,7 +358,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
                         w[q] = (((w[q] & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) | (((((w[q] >> 4) & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) << 4);
                     }
                 }
-                if (g_ok) dst[k4] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (g_ok) st_global_v4(dst + k4, w[0], w[1], w[2], w[3]);
             }
         } else {
             uint4* dst = reinterpret_cast<uint4*>(codes + e0 + int64_t(lane) * G);
@@ -358,7 +377,7 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
                     w[2 * q] = pack_bytes4(m);
                     w[2 * q + 1] = pack_bytes4(m + 4);
                 }
-                if (g_ok) dst[k2] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (g_ok) st_global_v4(dst + k2, w[0], w[1], w[2], w[3]);
             }
         }
         if (o_deq && g_ok) {  // optional Dequantize copy (not on the benchmarked path): exact FP64 formula
@@ -389,25 +408,6 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
 // possible outputs (each entry computed with the exact FP64 formula, indexed by the code byte), so the sweep
 // costs one shared-memory lookup per element.
 // ======================================================================================================
-__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-// stores through the global window: the compiler then knows they cannot alias the shared-memory stage
-__device__ __forceinline__ void st_global_v2(void* p, uint32_t a, uint32_t b) {
-    asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(__cvta_generic_to_global(p)), "r"(a), "r"(b) : "memory");
-}
-__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(__cvta_generic_to_global(p)), "r"(a), "r"(b), "r"(c), "r"(d)
-                 : "memory");
-}
-
 template <int T>
 __device__ __forceinline__ void group_sync(int bar_id) {
     if (T == 256) __syncthreads();
