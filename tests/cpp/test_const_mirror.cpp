@@ -1,0 +1,211 @@
+// Tests of the C++ host mirror (include/vfold_const.hpp) written the way the reference's own unit tests of
+// the Const dialect are (tests/unit/vpux_compiler/dialect/const/content_tests.cpp, cited as UT:lines):
+// build a ContentAttr through ContentSetup, fold(), compare getValues<T>() with the expected numbers.
+//
+//   test_const_mirror --host   builder / type-inference / error checks that need no GPU
+//   test_const_mirror          everything, folding on cuda:0
+// Exit code 0 = all checks passed; every failed check prints its location.
+#include <cstdio>
+#include <cstring>
+#include <numeric>
+
+#include "vfold_const.hpp"
+
+using namespace vfold;
+
+static int g_failed = 0;
+#define EXPECT(cond)                                                        \
+    do {                                                                    \
+        if (!(cond)) {                                                      \
+            std::printf("%s:%d: EXPECT(%s) failed\n", __FILE__, __LINE__, #cond); \
+            ++g_failed;                                                     \
+        }                                                                   \
+    } while (0)
+
+template <typename T>
+static std::vector<T> generateValues(size_t n) {  // UT:43-51
+    std::vector<T> v(n);
+    for (size_t i = 0; i < n; ++i) v[i] = static_cast<T>(i);
+    return v;
+}
+
+template <typename T>
+static size_t bytesOf(const std::vector<T>& v) {
+    return v.size() * sizeof(T);
+}
+
+// ---- host-only ------------------------------------------------------------------------------------------
+static void positionRequirement() {  // UT:1724-1749 (BitPack stands in for the LAST-positioned SwizzleConstant)
+    const TensorType baseType({1, 1, 3, 3}, VF_DT_F32);
+    const auto setup = Const::ContentSetup(baseType).rescale(10.0).bitPack(4).sparsify(false).castElemType(VF_DT_F16);
+    const std::vector<int> expected = {VF_T_RESCALE, VF_T_CAST_ELEM_TYPE, VF_T_SPARSIFY, VF_T_BIT_PACK};
+    EXPECT(setup.getTransformationKinds() == expected);
+    bool thrown = false;
+    try {
+        (void)setup.bitPack(4);
+    } catch (const Exception& e) {
+        thrown = e.status() == VF_ERR_POSITION;
+    }
+    EXPECT(thrown);  // "At most 1 attribute with LAST requirement allowed!"
+}
+
+static void inferTypes() {
+    const TensorType baseType({2, 4, 3, 3}, VF_DT_F32);
+    const std::vector<float> vals(72, 1.0f);
+    const auto q = ElemType::perAxis(VF_DT_I8, VF_DT_F32, {0.1, 0.2}, {0, 0}, 0, -127, 127);
+    // Quantize yields the plain storage type (quantize.cpp:108-212); CastElemType re-attaches the quantized type
+    const auto attr = Const::ContentSetup(baseType)
+                              .quantize(q)
+                              .castElemType(q)
+                              .reorder(VF_ORDER_NHWC)
+                              .padWithZero({0, 0, 0, 0}, {14, 12, 0, 0})
+                              .get(vals.data(), bytesOf(vals));
+    const TensorType t = attr.getType();
+    EXPECT((t.getShape() == std::vector<int64_t>{16, 16, 3, 3}));
+    EXPECT(t.getDimsOrder() == VF_ORDER_NHWC);
+    EXPECT(t.getElementType().kind() == VF_ELEM_QUANT_PER_AXIS);
+    EXPECT(t.getElementType().scales().size() == 16);  // padded channels extend the per-axis parameters
+    EXPECT(!attr.isSplat());
+
+    bool thrown = false;
+    try {  // Dequantize on a plain type
+        (void)Const::ContentSetup(baseType).dequantize().get(vals.data(), bytesOf(vals)).getType();
+    } catch (const Exception& e) {
+        thrown = e.status() == VF_ERR_NOT_QUANTIZED;
+    }
+    EXPECT(thrown);
+    thrown = false;
+    try {
+        (void)Const::ContentSetup(baseType).padWithZero({0, 0}, {1, 1, 1});
+    } catch (const Exception& e) {
+        thrown = e.status() == VF_ERR_SHAPE;
+    }
+    EXPECT(thrown);
+}
+
+// ---- folding on the GPU ------------------------------------------------------------------------------------
+static void quantize(const Context& ctx) {  // UT:2440-2469
+    const TensorType baseType({1, 16}, VF_DT_F32);
+    std::vector<float> vals(16);
+    for (int i = 0; i < 16; ++i) vals[i] = -2.0f + 0.25f * float(i);
+    const auto q = ElemType::uniform(VF_DT_I8, VF_DT_F32, 1.0 / 127.0, 56, -127, 127);
+    const auto content = Const::ContentSetup(baseType).quantize(q).get(vals.data(), bytesOf(vals)).fold(ctx);
+    EXPECT(content.getType().getElementType().dtype() == VF_DT_I8);
+    const std::vector<int> expected = {-127, -127, -127, -103, -71, -39, -7, 24, 56, 88, 120, 127, 127, 127, 127, 127};
+    EXPECT(content.getValues<int>() == expected);
+}
+
+static void dequantize(const Context& ctx) {  // after UT:754-788, with a non-zero zero point: (v - zp) * scale
+    const TensorType baseType({1, 16}, VF_DT_I8);
+    std::vector<int8_t> vals(16);
+    for (int i = 0; i < 16; ++i) vals[i] = int8_t(-8 + i);
+    const double scale = 0.5;
+    const int64_t zp = 3;
+    const auto q = ElemType::uniform(VF_DT_I8, VF_DT_F32, scale, zp, -128, 127);
+    const auto content = Const::ContentSetup(baseType).castElemType(q).dequantize().get(vals.data(), bytesOf(vals)).fold(ctx);
+    EXPECT(content.getType().getElementType().dtype() == VF_DT_F32);
+    const auto got = content.getValues<float>();
+    for (int i = 0; i < 16; ++i) EXPECT(got[size_t(i)] == float((vals[size_t(i)] - zp) * scale));
+}
+
+static void reorder(const Context& ctx) {  // UT:906-939 NCHW -> NHWC
+    const int64_t C = 2, H = 2, W = 2;
+    const TensorType baseType({1, C, H, W}, VF_DT_F32);
+    const auto vals = generateValues<float>(8);
+    const auto content = Const::ContentSetup(baseType).reorder(VF_ORDER_NHWC).get(vals.data(), bytesOf(vals)).fold(ctx);
+    EXPECT(content.getType().getDimsOrder() == VF_ORDER_NHWC);
+    const auto got = content.getValues<float>();
+    for (int64_t c = 0; c < C; ++c)
+        for (int64_t h = 0; h < H; ++h)
+            for (int64_t w = 0; w < W; ++w) EXPECT(got[size_t(c + w * C + h * C * W)] == vals[size_t(w + h * W + c * W * H)]);
+}
+
+static void padWithZeroSplat(const Context& ctx) {  // UT:1013-1050: a padded splat is no longer a splat
+    const TensorType baseType({1, 2, 2, 2}, VF_DT_F32);
+    const float splat = 7.0f;
+    const auto attr = Const::ContentSetup(baseType).padWithZero({0, 1, 0, 0}, {0, 1, 0, 0}).get(&splat, sizeof(splat), true);
+    const auto content = attr.fold(ctx);
+    EXPECT(!content.isSplat());
+    EXPECT((content.getType().getShape() == std::vector<int64_t>{1, 4, 2, 2}));
+    const auto got = content.getValues<float>();
+    for (size_t i = 0; i < got.size(); ++i) EXPECT(got[i] == ((i >= 4 && i < 12) ? splat : 0.0f));
+}
+
+static void bitPack(const Context& ctx) {  // UT:1246-1274
+    const TensorType baseType({1, 2, 3}, VF_DT_I8);
+    const std::vector<int8_t> vals = {1, 2, 3, 4, 5, 6};
+    const auto content = Const::ContentSetup(baseType).bitPack(4).get(vals.data(), bytesOf(vals)).fold(ctx);
+    EXPECT(content.getType().getElementType().dtype() == VF_DT_I4);
+    EXPECT((content.getRawStorageBuf() == std::vector<uint8_t>{0x21, 0x43, 0x65}));
+    EXPECT((content.getValues<int>() == std::vector<int>{1, 2, 3, 4, 5, 6}));
+}
+
+static void getSparsityMap(const Context& ctx) {  // UT:1536-1569
+    const TensorType baseType({1, 1, 2, 8}, VF_DT_U8);
+    const std::vector<uint8_t> vals = {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 11, 0, 13, 14, 15};
+    const auto content = Const::ContentSetup(baseType).getSparsityMap().get(vals.data(), bytesOf(vals)).fold(ctx);
+    EXPECT((content.getType().getShape() == std::vector<int64_t>{1, 1, 1, 128}));
+    std::vector<uint8_t> expected(16, 0);
+    expected[0] = 0xFE;
+    expected[1] = 0xEB;
+    EXPECT(content.getRawStorageBuf() == expected);
+}
+
+static void sparsifyQuantized(const Context& ctx) {  // UT:1681-1722 (zero point 16)
+    const TensorType baseType({2, 1, 2, 8}, VF_DT_U8);
+    const std::vector<uint8_t> vals = {16, 1,  2,  3,  4,  5,  6,  7,  8,  9,  16, 11, 16, 13, 14, 15,
+                                       16, 16, 18, 19, 20, 16, 22, 23, 24, 25, 26, 16, 16, 29, 30, 31};
+    const std::vector<uint8_t> expected = {1,  2,  3,  4,  5,  6,  7,  8,  9,  11, 13, 14, 15, 0, 0, 0,
+                                           18, 19, 20, 22, 23, 24, 25, 26, 29, 30, 31, 0,  0,  0, 0, 0};
+    const auto q = ElemType::uniform(VF_DT_U8, VF_DT_F32, 1.0, 16, 0, 31);
+    const auto content = Const::ContentSetup(baseType).castElemType(q).sparsify(false).get(vals.data(), bytesOf(vals)).fold(ctx);
+    EXPECT(content.getRawStorageBuf() == expected);
+}
+
+static void dequantizeQuantize(const Context& ctx) {  // UT:2512-2540: the chain is the identity
+    const TensorType baseType({1, 16}, VF_DT_I8);
+    std::vector<int8_t> vals(16);
+    for (int i = 0; i < 16; ++i) vals[size_t(i)] = int8_t(-120 + 15 * i);
+    const auto q = ElemType::uniform(VF_DT_I8, VF_DT_F16, 0.003, 56, -120, 120);
+    const auto content = Const::ContentSetup(baseType).castElemType(q).dequantize().quantize(q).get(vals.data(), bytesOf(vals)).fold(ctx);
+    const auto got = content.getValues<int>();
+    for (int i = 0; i < 16; ++i) EXPECT(got[size_t(i)] == vals[size_t(i)]);
+}
+
+static void copyToTooSmall(const Context& ctx) {  // utils/content.cpp:172-174
+    const TensorType baseType({4}, VF_DT_F32);
+    const auto vals = generateValues<float>(4);
+    bool thrown = false;
+    try {
+        (void)Const::ContentSetup(baseType).get(vals.data(), bytesOf(vals)).fold(ctx, 8);
+    } catch (const Exception& e) {
+        thrown = e.status() == VF_ERR_BUFFER_TOO_SMALL;
+    }
+    EXPECT(thrown);
+}
+
+int main(int argc, char** argv) {
+    const bool hostOnly = argc > 1 && std::strcmp(argv[1], "--host") == 0;
+    EXPECT(vf_abi_version() == VF_ABI_VERSION);
+    positionRequirement();
+    inferTypes();
+    if (!hostOnly) {
+        try {
+            const Context ctx(0);
+            quantize(ctx);
+            dequantize(ctx);
+            reorder(ctx);
+            padWithZeroSplat(ctx);
+            bitPack(ctx);
+            getSparsityMap(ctx);
+            sparsifyQuantized(ctx);
+            dequantizeQuantize(ctx);
+            copyToTooSmall(ctx);
+        } catch (const Exception& e) {
+            std::printf("unexpected vfold::Exception %d: %s\n", e.status(), e.what());
+            ++g_failed;
+        }
+    }
+    std::printf("%s: %d failed check(s)\n", hostOnly ? "host" : "all", g_failed);
+    return g_failed == 0 ? 0 : 1;
+}
