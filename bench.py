@@ -483,10 +483,32 @@ def conv_arm(args, workload):
             sj.content, sj.data, sj.data_bytes = c, data.data_ptr(), cap
             sj.map, sj.map_bytes, sj.counts = mp.data_ptr(), oc * row, cnt.data_ptr()
 
+    tjobs = None
+    if key in ("c2", "c3"):  # one weights table per tensor: scales from the fold's device output, fp32 bias
+        tjobs = (abi.WeightsTableJob * len(specs))()
+        for j, s in enumerate(specs):
+            oc = s.shape[0]
+            oshape = folded[j][1]
+            bias = torch.empty(oc, dtype=torch.float32, device=dev)
+            lib.synth_fill_device(wl.bias_for(workload.seed, s.tensor_id, oc), bias.data_ptr(), oc)
+            d, k = wl.weights_table_desc(oc, np.ones(oc), oshape[1] * oshape[2] * oshape[3])
+            d.has_bias, d.bias, d.bias_mem_kind = 1, bias.data_ptr(), abi.VF_MEM_DEVICE
+            if key == "c3":  # sparse pointers: prefix sums of the aligned set sizes, bitmap rows
+                d.weights_ptr_step = 0
+                d.nnz_counts, d.nnz_mem_kind = sparse[j][4].data_ptr(), abi.VF_MEM_DEVICE
+                d.sparsity_ptr_base, d.sparsity_ptr_step = 0, sparse[j][6] // oc
+            tab = torch.empty(oc * 4, dtype=torch.int32, device=dev)
+            tj = tjobs[j]
+            tj.desc, tj.table = d, tab.data_ptr()
+            tj.weights_scales, tj.scales_mem_kind = jobs[j].outs.scales, abi.VF_MEM_DEVICE
+            keep += [bias, k, tab]
+
     def step():
         lib.quantize_fold_batch(jobs)
         if sjobs is not None:
             lib.sparsify_batch(sjobs, out_mem_kind=abi.VF_MEM_DEVICE)
+        if tjobs is not None:
+            lib.weights_table_batch(tjobs, out_mem_kind=abi.VF_MEM_DEVICE)
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     warmup = args.warmup if args.profile else max(3, args.warmup)

@@ -387,6 +387,22 @@ typedef struct vf_weights_table_desc {
 int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* desc, int32_t* table, int out_mem_kind, char* err,
                      size_t errlen);
 
+/* The weights tables of many NCE operations in one call (one kernel launch for all rows of all tables, one
+ * more for all sparse-pointer prefix sums): what createWeightsTableTensor does per operation
+ * (VPU/utils/const_utils.cpp:24-41), batched like the constants themselves. `weights_scales` (optional) holds
+ * desc.oc FP64 weight scales in memory of kind `scales_mem_kind` and replaces the scale values of
+ * desc.weights_elem, which then only describes the type: pass the `scales` output of the tensor's
+ * vf_quantize_fold job (device memory) and the table is built without a round trip through the host. */
+typedef struct vf_weights_table_job {
+    vf_weights_table_desc desc;
+    const double* weights_scales;
+    int32_t scales_mem_kind; /* vf_mem_kind of weights_scales */
+    int32_t status;          /* out */
+    int32_t* table;          /* [desc.oc * 4], memory kind = the call's out_mem_kind */
+} vf_weights_table_job;
+int vf_weights_table_batch(vf_ctx* ctx, vf_weights_table_job* jobs, int njobs, int out_mem_kind, char* err,
+                           size_t errlen);
+
 /* ------------------------------------------------------------------ */
 /* batches and sharding                                                */
 /* ------------------------------------------------------------------ */
@@ -398,12 +414,9 @@ typedef struct vf_quant_job {
     int32_t dst_mem_kind;
     void* dst;
     uint64_t dst_bytes;
-    vf_quant_outputs outs;
-    /* optional per-job weights table appended to the same launch sequence */
-    const vf_weights_table_desc* table_desc; /* scales of weights_elem are taken from this job's derived scales */
-    int32_t* table;                          /* [oc*4], mem kind = outs.mem_kind */
-    uint64_t dst_written;                    /* out */
-    int32_t status;                          /* out: per-job status */
+    vf_quant_outputs outs;   /* outs.scales in device memory feeds vf_weights_table_batch directly */
+    uint64_t dst_written;    /* out */
+    int32_t status;          /* out: per-job status */
     int32_t reserved;
 } vf_quant_job;
 

@@ -314,8 +314,38 @@ def weights_table_float_scale(be):
     assert tab[:, 3].tolist() == [0] * 16
 
 
+def copy_to_i4(be):
+    """UT:440-466 CopyTo_I4: CastElemType to a 4-bit integer packs two values per byte at copyTo, low nibble first"""
+    t = TType([4], U8)
+    out = ContentAttr(np.array([1, 7, 10, 15], np.uint8), t, ContentSetup(t).castElemType(abi.VF_DT_U4)).fold(be)
+    assert not out.is_splat
+    assert out.bytes().tolist() == [0x71, 0xFA]
+
+
+def copy_to_i1(be):
+    """UT:468-496 CopyTo_I1: eight 1-bit values per byte, element 0 in bit 0"""
+    t = TType([16], U8)
+    vals = np.array([0, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 1, 1, 1, 1, 0], np.uint8)
+    out = ContentAttr(vals, t, ContentSetup(t).castElemType(abi.VF_DT_I1)).fold(be)
+    assert out.bytes().tolist() == [0xC8, 0x7F]
+
+
+def sparsity_ptr_stepping(be):
+    """lit dialect/VPU/passes/recompute_sparsity_ptrs.mlir:12-31: a 16x16x4x4 filter has sparsity-map rows of
+    align(256, 128) / 8 = 32 bytes (map type 16x1x1x256xi1), so the sparsity pointers step by 32"""
+    t = TType([16, 16, 4, 4], F16)
+    attr = ContentAttr(np.zeros(16 * 16 * 16, np.float16), t, ContentSetup(t).reorder(abi.ORDER_NHWC).getSparsityMap())
+    mt = attr.infer(be)[0]
+    assert mt == TType([16, 1, 1, 256], abi.VF_DT_I1)
+    row_bytes = mt.shape[3] // 8
+    d, keep = _wt_desc(Elem(F16), Elem(F16), Elem(F16), 16, 0, 16, 0, row_bytes)
+    tab = be.weights_table(d, 16).reshape(16, 4)
+    assert tab[:, 1].tolist() == [32 * i for i in range(16)]
+
+
 FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequantize, reorder, pad, pad_splat,
               pad_uniform_quant, pad_per_axis_quant, bit_pack, bit_pack_quant, get_sparsity_map,
               get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
-              convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain]
-TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale]
+              convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain, copy_to_i4,
+              copy_to_i1]
+TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale, sparsity_ptr_stepping]

@@ -505,3 +505,36 @@ def test_weights_table_random(gpu, oracle):
     d3, keep3 = wl.weights_table_desc(2, np.array([1.0, 1.0]), 24)
     assert _status(lambda: gpu.weights_table(d3, 2)) == abi.VF_ERR_ALIGNMENT
     assert _status(lambda: oracle.weights_table(d3, 2)) == abi.VF_ERR_ALIGNMENT
+
+
+def test_weights_table_batch(gpu, oracle):
+    """Many tables per call (dense and sparse pointers, with and without bias, 1..2500 channels); weight scales
+    either inside the descriptor or as a separate FP64 array; one launch for all rows."""
+    rng = np.random.default_rng(17)
+    ocs = [1, 16, 64, 300, 1000, 2500, 33]
+    jobs = (abi.WeightsTableJob * len(ocs))()
+    tables, expect, keep = [], [], []
+    for j, oc in enumerate(ocs):
+        ws = rng.uniform(1e-4, 5e-2, oc)
+        bias = (rng.standard_normal(oc) * 0.01).astype(np.float32) if j % 2 == 0 else None
+        counts = rng.integers(0, 577, oc).astype(np.int64) if j % 3 == 1 else None
+        d, k = wl.weights_table_desc(oc, ws, 576, bias, sparse_counts=counts, sparsity_step=80 if counts is not None else 0)
+        expect.append(oracle.weights_table(d, oc))
+        tab = np.full(oc * 4, -1, np.int32)
+        jobs[j].desc, jobs[j].table = d, tab.ctypes.data
+        if j >= 4:  # scales passed beside the descriptor; the descriptor's own values must then be ignored
+            wrong = abi.Elem.per_axis(I8, F16, np.full(oc, 123.0), np.zeros(oc, np.int64), 0, -127, 127)
+            jobs[j].desc.weights_elem = wrong.pod()
+            sc = np.ascontiguousarray(ws, np.float64)
+            jobs[j].weights_scales, jobs[j].scales_mem_kind = sc.ctypes.data, abi.VF_MEM_HOST
+            keep += [wrong, sc]
+        tables.append(tab)
+        keep += [d, k]
+    l0 = gpu.launch_count
+    gpu.weights_table_batch(jobs)
+    assert gpu.launch_count - l0 == 2  # all prefix sums + all rows
+    for j, (tab, exp) in enumerate(zip(tables, expect)):
+        assert np.array_equal(tab, exp), j
+    # an invalid job ends the call and is marked
+    jobs[2].desc.weights_ptr_step = 24
+    assert _status(lambda: gpu.weights_table_batch(jobs)) == abi.VF_ERR_ALIGNMENT

@@ -115,8 +115,12 @@ class WeightsTableDesc(C.Structure):
 class QuantJob(C.Structure):
     _fields_ = [("base", Content), ("spec", QuantSpec), ("t", C.POINTER(Transform)), ("n", C.c_int32),
                 ("dst_mem_kind", C.c_int32), ("dst", C.c_void_p), ("dst_bytes", C.c_uint64), ("outs", QuantOutputs),
-                ("table_desc", C.POINTER(WeightsTableDesc)), ("table", C.c_void_p), ("dst_written", C.c_uint64),
-                ("status", C.c_int32), ("reserved", C.c_int32)]
+                ("dst_written", C.c_uint64), ("status", C.c_int32), ("reserved", C.c_int32)]
+
+
+class WeightsTableJob(C.Structure):
+    _fields_ = [("desc", WeightsTableDesc), ("weights_scales", C.c_void_p), ("scales_mem_kind", C.c_int32),
+                ("status", C.c_int32), ("table", C.c_void_p)]
 
 
 class SparsifyJob(C.Structure):

@@ -853,10 +853,17 @@ static void sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem
         s.data = static_cast<uint8_t*>(out_ptr(ctx, jb.data, out_mem_kind, jb.data_bytes, p.tdata));
         s.capacity = jb.data_bytes;
         s.offsets = nullptr;
-        if (s.data) {
-            p.offsets = DBuf(ctx, size_t(oc + 1) * 8);
-            s.offsets = p.offsets.as<int64_t>();
-        }
+    }
+    // one scratch allocation for the offsets of all tensors and the per-tensor totals
+    size_t off_elems = 0;
+    for (int j = 0; j < n; ++j)
+        if (sj[j].data) off_elems += size_t(sj[j].oc + 1);
+    DBuf all_offsets(ctx, off_elems * 8);
+    off_elems = 0;
+    for (int j = 0; j < n; ++j) {
+        if (!sj[j].data) continue;
+        sj[j].offsets = all_offsets.as<int64_t>() + off_elems;
+        off_elems += size_t(sj[j].oc + 1);
     }
     DBuf totals(ctx, size_t(n) * 8);
     launch_sparsify_batch(ctx, sj, totals.as<int64_t>());
@@ -911,14 +918,19 @@ int vf_sparsify_batch(vf_ctx* ctx, vf_sparsify_job* jobs, int njobs, int out_mem
     });
 }
 
-int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* d, int32_t* table, int out_mem_kind, char* err,
-                     size_t errlen) {
-    return guard(err, errlen, [&] {
-        if (!d || !table) raise(VF_ERR_INVALID_ARG, "NULL argument");
+}  // extern "C"
+
+// Translates one weights-table descriptor into kernel arguments. Host arrays are uploaded into buffers kept in
+// `keep`; a count array queues an entry in `offs` (the prefix sums are launched by the caller, for all tables at
+// once). `w_scales` / `w_kind`: optional replacement of the weight scales by an array of `oc` values that may
+// already live in device memory (the scales a quantization job of the same tensor derived).
+static TableArgs table_prepare(vf_ctx* ctx, const vf_weights_table_desc* d, const double* w_scales, int w_kind, int32_t* d_table,
+                               std::vector<DBuf>& keep, std::vector<OffsetsJob>& offs) {
+    {
+        if (!d) raise(VF_ERR_INVALID_ARG, "NULL argument");
         if (d->oc <= 0) raise(VF_ERR_SHAPE, "OC must be positive");
         if (d->in_elem.dtype == VF_DT_INVALID || d->out_elem.dtype == VF_DT_INVALID)
             raise(VF_ERR_INVALID_ARG, "Can't create weights table without operation input/output types");
-        CallScope scope(ctx, nullptr);
         const int64_t oc = d->oc;
         const Elem in = Elem::from(d->in_elem), out = Elem::from(d->out_elem);
         const bool has_w = d->weights_elem.dtype != VF_DT_INVALID;
@@ -930,73 +942,102 @@ int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* d, int32_t* table
         };
         check_n(in, "input");
         check_n(out, "output");
-        check_n(w, "weights");
+        if (!w_scales) check_n(w, "weights");
 
+        auto upload = [&](const void* src, size_t bytes, int kind) {  // -> device pointer, buffer kept alive
+            keep.emplace_back(ctx, bytes);
+            copy_in(ctx, keep.back().p, src, bytes, kind);
+            return keep.back().p;
+        };
         TableArgs a{};
         a.oc = oc;
+        a.d_table = d_table;
         a.in_quantized = in.quantized();
         a.out_quantized = out.quantized();
         a.weights_quantized = has_w && w.quantized();
         a.in_is_float = !in.quantized() && dtype_is_float(in.dtype);
         a.const_scale = d->has_const_scale ? d->const_scale : 1.0;
-        DBuf dws, dis, dos, dwp, dsp, dbias, doff;
-        std::vector<double> ws = a.weights_quantized ? w.scales : std::vector<double>{1.0};
-        dws = upload_vec(ctx, ws);
-        a.d_wscale = dws.as<double>();
-        a.n_wscale = int64_t(ws.size());
+        if (a.weights_quantized && w_scales) {
+            a.d_wscale = w_kind == VF_MEM_DEVICE ? w_scales : static_cast<const double*>(upload(w_scales, size_t(oc) * 8, w_kind));
+            a.n_wscale = oc;
+        } else {
+            const std::vector<double> ws = a.weights_quantized ? w.scales : std::vector<double>{1.0};
+            a.d_wscale = static_cast<const double*>(upload(ws.data(), ws.size() * 8, VF_MEM_HOST));
+            a.n_wscale = int64_t(ws.size());
+        }
         a.in_scale = in.quantized() ? in.scales[0] : 1.0;
         a.out_scale = out.quantized() ? out.scales[0] : 1.0;
-        if (in.quantized() && in.scales.size() > 1) {
-            dis = upload_vec(ctx, in.scales);
-            a.d_in_scale = dis.as<double>();
-        }
-        if (out.quantized() && out.scales.size() > 1) {
-            dos = upload_vec(ctx, out.scales);
-            a.d_out_scale = dos.as<double>();
-        }
+        if (in.quantized() && in.scales.size() > 1) a.d_in_scale = static_cast<const double*>(upload(in.scales.data(), in.scales.size() * 8, VF_MEM_HOST));
+        if (out.quantized() && out.scales.size() > 1) a.d_out_scale = static_cast<const double*>(upload(out.scales.data(), out.scales.size() * 8, VF_MEM_HOST));
         a.wbase = d->weights_ptr_base;
         a.wstep = d->weights_ptr_step;
         a.sbase = d->sparsity_ptr_base;
         a.sstep = d->sparsity_ptr_step;
-        if (d->weights_ptrs) {
-            dwp = DBuf(ctx, size_t(oc) * 4);
-            copy_in(ctx, dwp.p, d->weights_ptrs, size_t(oc) * 4, VF_MEM_HOST);
-            a.d_wptrs = dwp.as<int32_t>();
-        }
-        if (d->sparsity_ptrs) {
-            dsp = DBuf(ctx, size_t(oc) * 4);
-            copy_in(ctx, dsp.p, d->sparsity_ptrs, size_t(oc) * 4, VF_MEM_HOST);
-            a.d_sptrs = dsp.as<int32_t>();
-        }
-        DBuf dnnz;
+        if (d->weights_ptrs) a.d_wptrs = static_cast<const int32_t*>(upload(d->weights_ptrs, size_t(oc) * 4, VF_MEM_HOST));
+        if (d->sparsity_ptrs) a.d_sptrs = static_cast<const int32_t*>(upload(d->sparsity_ptrs, size_t(oc) * 4, VF_MEM_HOST));
         if (d->nnz_counts) {
             const int64_t* dc = d->nnz_counts;
-            if (d->nnz_mem_kind != VF_MEM_DEVICE) {
-                dnnz = DBuf(ctx, size_t(oc) * 8);
-                copy_in(ctx, dnnz.p, d->nnz_counts, size_t(oc) * 8, d->nnz_mem_kind);
-                dc = dnnz.as<int64_t>();
-            }
-            doff = DBuf(ctx, size_t(oc + 1) * 8);
+            if (d->nnz_mem_kind != VF_MEM_DEVICE) dc = static_cast<const int64_t*>(upload(d->nnz_counts, size_t(oc) * 8, d->nnz_mem_kind));
+            keep.emplace_back(ctx, size_t(oc + 1) * 8);
+            int64_t* doff = keep.back().as<int64_t>();
             const int eb = std::max(1, dtype_bits(has_w ? w.dtype : VF_DT_U8) / 8);
-            launch_sparse_offsets(ctx, dc, oc, eb, doff.as<int64_t>());
-            a.d_nnz_offsets = doff.as<int64_t>();
+            offs.push_back(OffsetsJob{dc, oc, eb, doff});
+            a.d_nnz_offsets = doff;
         }
         if (d->has_bias) {
             if (!d->bias) raise(VF_ERR_INVALID_ARG, "has_bias without a bias pointer");
             const size_t nb = size_t(d->bias_is_splat ? 1 : oc) * 4;
-            if (d->bias_mem_kind == VF_MEM_DEVICE) {
-                a.d_bias = d->bias;
-            } else {
-                dbias = DBuf(ctx, nb);
-                copy_in(ctx, dbias.p, d->bias, nb, d->bias_mem_kind);
-                a.d_bias = dbias.as<float>();
-            }
+            a.d_bias = d->bias_mem_kind == VF_MEM_DEVICE ? d->bias : static_cast<const float*>(upload(d->bias, nb, d->bias_mem_kind));
             a.bias_is_splat = d->bias_is_splat;
         }
+        return a;
+    }
+}
+
+extern "C" {
+
+int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* d, int32_t* table, int out_mem_kind, char* err,
+                     size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (!d || !table) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, nullptr);
+        std::vector<DBuf> keep;
+        std::vector<OffsetsJob> offs;
+        keep.reserve(16);
         DBuf tmp;
-        int32_t* dt = static_cast<int32_t*>(out_ptr(ctx, table, out_mem_kind, size_t(oc) * 16, tmp));
+        int32_t* dt = static_cast<int32_t*>(out_ptr(ctx, table, out_mem_kind, size_t(d->oc > 0 ? d->oc : 0) * 16, tmp));
+        const TableArgs a = table_prepare(ctx, d, nullptr, VF_MEM_HOST, dt, keep, offs);
+        launch_offsets_batch(ctx, offs);
         launch_weights_table(ctx, a, dt);
-        out_flush(ctx, table, out_mem_kind, size_t(oc) * 16, tmp);
+        out_flush(ctx, table, out_mem_kind, size_t(d->oc) * 16, tmp);
+        scope.finish();
+    });
+}
+
+int vf_weights_table_batch(vf_ctx* ctx, vf_weights_table_job* jobs, int njobs, int out_mem_kind, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        CallScope scope(ctx, nullptr);
+        std::vector<DBuf> keep;
+        std::vector<OffsetsJob> offs;
+        std::vector<TableArgs> tabs;
+        std::vector<DBuf> stage(static_cast<size_t>(njobs));
+        keep.reserve(size_t(njobs) * 8 + 8);  // pointers into `keep` entries stay valid: no reallocation below
+        for (int j = 0; j < njobs; ++j) {
+            vf_weights_table_job& jb = jobs[j];
+            jb.status = VF_OK;
+            if (!jb.table) raise(VF_ERR_INVALID_ARG, "job %d: table is NULL", j);
+            int32_t* dt = static_cast<int32_t*>(out_ptr(ctx, jb.table, out_mem_kind, size_t(jb.desc.oc > 0 ? jb.desc.oc : 0) * 16, stage[j]));
+            try {
+                tabs.push_back(table_prepare(ctx, &jb.desc, jb.weights_scales, jb.scales_mem_kind, dt, keep, offs));
+            } catch (const Error& e) {
+                jb.status = e.code;
+                throw;
+            }
+        }
+        launch_offsets_batch(ctx, offs);
+        launch_weights_table_batch(ctx, tabs);
+        for (int j = 0; j < njobs; ++j) out_flush(ctx, jobs[j].table, out_mem_kind, size_t(jobs[j].desc.oc) * 16, stage[j]);
         scope.finish();
     });
 }

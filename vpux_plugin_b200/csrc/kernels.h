@@ -72,6 +72,14 @@ struct SparseJob {
 // Three launches for the whole list: counts + bitmaps, per-tensor offsets (total bytes of tensor j into
 // d_totals[j]; 0 for tensors without `data`), compaction. An overflow of `capacity` sets VF_FLAG_OVERFLOW.
 void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d_totals);
+// Exclusive prefix sums of align16(count * es) for many count arrays in one launch (one CTA per entry).
+struct OffsetsJob {
+    const int64_t* counts;  // [oc]
+    int64_t oc;
+    int es;
+    int64_t* offsets;       // [oc + 1]
+};
+void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs);
 
 // ---- statistics --------------------------------------------------------------------------------------
 // min/max (over values and 0) or absmax per unit of `unit_len` consecutive elements, then
@@ -95,8 +103,12 @@ struct TableArgs {
     const int64_t* d_nnz_offsets;  // optional: column 0 = wbase + offsets[oc] (exclusive prefix sums, bytes)
     const float* d_bias;           // optional
     int bias_is_splat;
+    int32_t* d_table;              // batch launches: where this table goes
+    int64_t unit_begin;            // batch launches: index of this table's first row (set by the launcher)
 };
 void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table);
+// All tables of `tabs` (each with its d_table) in one launch over a device copy of the list.
+void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs);
 
 // ---- synthetic weights -------------------------------------------------------------------------------
 void launch_synth(vf_ctx* ctx, const vf_synth_spec& s, void* dst, uint64_t count);

@@ -355,9 +355,7 @@ __global__ void k_unit_stats(const void* __restrict__ in, int in_dt, int64_t uni
 // weights table — dialect/VPU/utils/nce_sparsity.cpp:97-136,195-231,317-347 with the NPU37XX converters
 // (NPU37XX/dialect/VPU/impl/nce_sparsity_converters.cpp:14-42)
 // ------------------------------------------------------------------------------------------------------
-__global__ void k_weights_table(TableArgs a, int32_t* __restrict__ table, int* flags) {
-    const int64_t oc = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (oc >= a.oc) return;
+__device__ __forceinline__ void weights_table_row(const TableArgs& a, int64_t oc, int32_t* __restrict__ table, int* flags) {
     const double ws = a.weights_quantized ? a.d_wscale[a.n_wscale > 1 ? oc : 0] : 1.0;
     const double is = a.d_in_scale ? a.d_in_scale[oc] : a.in_scale;
     const double os = a.d_out_scale ? a.d_out_scale[oc] : a.out_scale;
@@ -409,6 +407,25 @@ __global__ void k_weights_table(TableArgs a, int32_t* __restrict__ table, int* f
     table[oc * 4 + 1] = sp;
     table[oc * 4 + 2] = ms;
     table[oc * 4 + 3] = bias;
+}
+
+__global__ void k_weights_table(TableArgs a, int32_t* __restrict__ table, int* flags) {
+    const int64_t oc = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (oc < a.oc) weights_table_row(a, oc, table, flags);
+}
+
+// Many tables per launch: thread u handles row u - unit_begin of the table whose range holds u.
+__global__ void k_weights_table_batch(const TableArgs* __restrict__ tabs, int n, int64_t total, int* flags) {
+    const int64_t u = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (u >= total) return;
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {  // last table whose unit_begin <= u
+        const int mid = (lo + hi + 1) >> 1;
+        if (tabs[mid].unit_begin <= u) lo = mid;
+        else hi = mid - 1;
+    }
+    const TableArgs a = tabs[lo];
+    weights_table_row(a, u - a.unit_begin, a.d_table, flags);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -633,6 +650,19 @@ void launch_pack_params(vf_ctx* ctx, const double* d_scales, const int64_t* d_zp
 void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table) {
     if (a.oc <= 0) return;
     k_weights_table<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(a, d_table, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
+    if (tabs.empty()) return;
+    int64_t total = 0;
+    for (auto& t : tabs) {
+        t.unit_begin = total;
+        total += t.oc;
+    }
+    DBuf d(ctx, tabs.size() * sizeof(TableArgs));
+    copy_in(ctx, d.p, tabs.data(), tabs.size() * sizeof(TableArgs), VF_MEM_HOST);
+    k_weights_table_batch<<<int((total + 127) / 128), 128, 0, ctx->stream>>>(d.as<TableArgs>(), int(tabs.size()), total, ctx->d_flags);
     post_launch(ctx);
 }
 

@@ -137,22 +137,17 @@ __global__ void __launch_bounds__(kWarps * 32) k_sparse_scan_batch(const SparseJ
 // ------------------------------------------------------------------------------------------------------
 // pass 2: one CTA per tensor, exclusive scan of align16(count * es) -> offsets[0..oc], total -> totals[j]
 // ------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) k_sparse_offsets_batch(const SparseJob* __restrict__ jobs,
-                                                               int64_t* __restrict__ totals) {
+__device__ __forceinline__ void block_offsets(const int64_t* __restrict__ counts, int64_t oc, int es, int64_t* __restrict__ offsets,
+                                              int64_t* total_out) {
     __shared__ long long warp_sums[32];
     __shared__ long long carry_s;
-    const SparseJob J = jobs[blockIdx.x];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    if (!J.offsets) {
-        if (tid == 0) totals[blockIdx.x] = 0;
-        return;
-    }
     if (tid == 0) carry_s = 0;
     __syncthreads();
-    for (int64_t base = 0; base < J.oc; base += blockDim.x) {
+    for (int64_t base = 0; base < oc; base += blockDim.x) {
         const int64_t i = base + tid;
         long long v = 0;
-        if (i < J.oc) v = ((J.counts[i] * J.es + 15) / 16) * 16;
+        if (i < oc) v = ((counts[i] * es + 15) / 16) * 16;
         long long incl = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -173,15 +168,30 @@ __global__ void __launch_bounds__(1024) k_sparse_offsets_batch(const SparseJob* 
         }
         __syncthreads();
         const long long excl = carry_s + warp_sums[wid] + incl - v;
-        if (i < J.oc) J.offsets[i] = excl;
+        if (i < oc) offsets[i] = excl;
         __syncthreads();
         if (tid == blockDim.x - 1) carry_s = excl + v;
         __syncthreads();
     }
     if (tid == 0) {
-        J.offsets[J.oc] = carry_s;
-        totals[blockIdx.x] = carry_s;
+        offsets[oc] = carry_s;
+        if (total_out) *total_out = carry_s;
     }
+}
+
+__global__ void __launch_bounds__(1024) k_sparse_offsets_batch(const SparseJob* __restrict__ jobs,
+                                                               int64_t* __restrict__ totals) {
+    const SparseJob J = jobs[blockIdx.x];
+    if (!J.offsets) {
+        if (threadIdx.x == 0) totals[blockIdx.x] = 0;
+        return;
+    }
+    block_offsets(J.counts, J.oc, J.es, J.offsets, totals + blockIdx.x);
+}
+
+__global__ void __launch_bounds__(1024) k_offsets_batch(const OffsetsJob* __restrict__ jobs) {
+    const OffsetsJob J = jobs[blockIdx.x];
+    block_offsets(J.counts, J.oc, J.es, J.offsets, nullptr);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -329,6 +339,15 @@ void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d
         VF_CUDA(cudaGetLastError());
         ctx->launches += 1;
     }
+}
+
+void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs) {
+    if (jobs.empty()) return;
+    DBuf d(ctx, jobs.size() * sizeof(OffsetsJob));
+    copy_in(ctx, d.p, jobs.data(), jobs.size() * sizeof(OffsetsJob), VF_MEM_HOST);
+    k_offsets_batch<<<int(jobs.size()), 1024, 0, ctx->stream>>>(d.as<OffsetsJob>());
+    VF_CUDA(cudaGetLastError());
+    ctx->launches += 1;
 }
 
 }  // namespace vf

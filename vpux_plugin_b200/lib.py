@@ -28,7 +28,7 @@ def _load():
                           "(the package has no CPU fallback)")
     lib = C.CDLL(LIB_PATH)
     for name in ("vf_infer_type", "vf_fold", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
-                 "vf_nnz_per_oc", "vf_sparsify", "vf_sparsify_batch", "vf_weights_table", "vf_synth_fill", "vf_plan_shards",
+                 "vf_nnz_per_oc", "vf_sparsify", "vf_sparsify_batch", "vf_weights_table", "vf_weights_table_batch", "vf_synth_fill", "vf_plan_shards",
                  "vf_ctx_create", "vf_ctx_synchronize", "vf_abi_version", "vf_ctx_device"):
         getattr(lib, name).restype = C.c_int
     lib.vf_ctx_destroy.restype = None
@@ -218,6 +218,12 @@ class Library:
         st = self.lib.vf_weights_table(self.ctx, C.byref(desc), _ptr(table), int(out_mem_kind), err, C.c_size_t(512))
         self._check(st, err)
         return table
+
+    def weights_table_batch(self, jobs, out_mem_kind=abi.VF_MEM_HOST):
+        """jobs: ctypes array of abi.WeightsTableJob (tables in memory of kind `out_mem_kind`)."""
+        err = self._err()
+        st = self.lib.vf_weights_table_batch(self.ctx, jobs, len(jobs), int(out_mem_kind), err, C.c_size_t(512))
+        self._check(st, err)
 
     def synth_fill_device(self, spec, dst_ptr, count):
         err = self._err()
