@@ -565,6 +565,20 @@ def conv_arm(args, workload):
         ms += e0.elapsed_time(e1)
     launches = (lib.launch_count - l0) // args.steps
     clocks = sampler.stop()
+    stage = None
+    if sjobs is not None and not args.profile:  # the sparsify stage alone, on the folded i8 codes
+        sms = 0.0
+        code_bytes = sum(int(d.numel()) for d, _ in folded)
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            lib.sparsify_batch(sjobs, out_mem_kind=abi.VF_MEM_DEVICE)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            sms += e0.elapsed_time(e1)
+        stage = {"name": "sparsify + sparsity map + counts on the folded i8 codes", "input_bytes": code_bytes,
+                 "ms_per_step": sms / args.steps, "value": code_bytes * args.steps / (sms * 1e-3) / 1e9, "unit": "GB/s"}
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
@@ -582,6 +596,8 @@ def conv_arm(args, workload):
                      "note": "whole step (all launches of the step, host gaps between synchronous calls included)"},
         "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": int(launches * args.steps),
     }
+    if stage is not None:
+        line["stage"] = stage
     print(json.dumps(line), flush=True)
 
 
