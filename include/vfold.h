@@ -232,6 +232,19 @@ int vf_infer_type(const vf_tensor_type* base, int base_is_splat, const vf_transf
                   int* out_is_splat, double* scales_buf, int64_t* zps_buf, int64_t params_cap, uint64_t* out_bytes,
                   char* err, size_t errlen);
 
+/* = the rewriting ContentSetup::addTransformation performs whenever a transformation is appended
+ * (content.cpp:530-588): t[0..n) are added one at a time — inserted by position requirement, then
+ * fuseConsecutiveTransformations, foldTransformation, moveSubViewBefore and moveReshapeBefore
+ * (utils/transformations.cpp:385-712) run until none applies. The resulting list folds to the same bytes with
+ * fewer passes, and a SubView that reaches the front lets the caller upload only the slab it selects.
+ * `out` receives at most `out_cap` entries (n is always enough), `*n_out` their number. Quantization
+ * parameters of the resulting entries are stored in (scales_buf, zps_buf), `params_cap` entries each;
+ * numActualElements arrays keep pointing at the caller's. Pure host function. Rules that involve
+ * ChangeShapeAndElemType, RelocateWeightsTable or Fuse are outside this library and never fire. */
+int vf_optimize_transforms(const vf_tensor_type* base, const vf_transform* t, int n, vf_transform* out, int out_cap,
+                           int* n_out, double* scales_buf, int64_t* zps_buf, int64_t params_cap, char* err,
+                           size_t errlen);
+
 /* = ContentAttr::fold() followed by Content::copyTo(dst): applies the
  * transformation list to `base` on the GPU and materialises the result in
  * the final *logical* element type into `dst` (mem kind `dst_mem_kind`).

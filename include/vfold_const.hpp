@@ -403,6 +403,36 @@ public:
         return append(std::move(it));
     }
 
+    // The list after the rewriting the reference performs on every insertion (content.cpp:530-588): consecutive
+    // transformations fused, no-op reorders dropped, SubView / Reshape moved towards the front. The builders
+    // above keep the list as given; this returns the list the reference's ContentSetup would hold.
+    ContentSetup optimize() const {
+        const vf_tensor_type base = _baseType.pod();
+        const std::vector<vf_transform> in = pods();
+        std::vector<vf_transform> out(in.size() + 1);
+        std::vector<double> sb(1 << 16);
+        std::vector<int64_t> zb(1 << 16);
+        int n = 0;
+        char err[512] = {0};
+        details::check(vf_optimize_transforms(&base, in.data(), int(in.size()), out.data(), int(out.size()), &n, sb.data(), zb.data(),
+                                              int64_t(sb.size()), err, sizeof(err)),
+                       err);
+        ContentSetup res(_baseType);
+        for (int i = 0; i < n; ++i) {
+            auto it = std::make_shared<Item>();
+            it->t = out[size_t(i)];
+            const int k = it->t.kind;
+            if (k == VF_T_CAST_ELEM_TYPE || k == VF_T_CONVERT_ELEM_TYPE || k == VF_T_QUANTIZE) it->elem = ElemType::fromPod(it->t.elem);
+            if (it->t.num_actual) it->counts.assign(it->t.num_actual, it->t.num_actual + it->t.n_num_actual);
+            res._items.push_back(std::move(it));
+        }
+        return res;
+    }
+    // parameters of transformation i (for checks in tests)
+    vf_transform at(size_t i) const {
+        return pods().at(i);
+    }
+
     // = ContentSetup::get(): the attribute over `base` (bytes in `storage`, borrowed until fold() returns)
     inline ContentAttr get(const void* base, size_t baseBytes, bool isSplat = false, vf_dtype storage = VF_DT_INVALID) const;
 

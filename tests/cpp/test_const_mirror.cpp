@@ -83,6 +83,26 @@ static void inferTypes() {
     EXPECT(thrown);
 }
 
+static void optimizedLists() {
+    // content_setup.cpp:720-747 FuseSubView
+    const TensorType i8({1, 7, 5}, VF_DT_I8);
+    auto fused = Const::ContentSetup(i8).subview({0, 1, 2}, {1, 6, 3}).subview({0, 1, 1}, {1, 2, 1}).optimize();
+    EXPECT(fused.size() == 1);
+    EXPECT(fused.at(0).kind == VF_T_SUBVIEW && fused.at(0).a[1] == 2 && fused.at(0).a[2] == 3 && fused.at(0).b[1] == 2);
+    // content_setup.cpp:903-930 SwapTransposeAndSubView
+    const TensorType chw({4, 8, 3}, VF_DT_I8);
+    auto swapped = Const::ContentSetup(chw).transpose(0x321).subview({0, 1, 2}, {3, 2, 1}).optimize();
+    EXPECT((swapped.getTransformationKinds() == std::vector<int>{VF_T_SUBVIEW, VF_T_TRANSPOSE}));
+    EXPECT(swapped.at(0).a[0] == 2 && swapped.at(0).a[1] == 1 && swapped.at(0).a[2] == 0);
+    EXPECT(swapped.at(0).b[0] == 1 && swapped.at(0).b[1] == 2 && swapped.at(0).b[2] == 3);
+    // content_setup.cpp:1257-1294: a per-axis type is sliced together with the view
+    const TensorType u8({2, 8, 3}, VF_DT_U8);
+    const auto perAxis = ElemType::perAxis(VF_DT_U8, VF_DT_F32, {2.0, 0.5}, {127, 127}, 0, 0, 255);
+    auto sliced = Const::ContentSetup(u8).castElemType(perAxis).subview({0, 1, 1}, {1, 2, 1}).optimize();
+    EXPECT((sliced.getTransformationKinds() == std::vector<int>{VF_T_SUBVIEW, VF_T_CAST_ELEM_TYPE}));
+    EXPECT(sliced.at(1).elem.nparams == 1 && sliced.at(1).elem.scales[0] == 2.0);
+}
+
 // ---- folding on the GPU ------------------------------------------------------------------------------------
 static void quantize(const Context& ctx) {  // UT:2440-2469
     const TensorType baseType({1, 16}, VF_DT_F32);
@@ -189,6 +209,7 @@ int main(int argc, char** argv) {
     EXPECT(vf_abi_version() == VF_ABI_VERSION);
     positionRequirement();
     inferTypes();
+    optimizedLists();
     if (!hostOnly) {
         try {
             const Context ctx(0);

@@ -149,6 +149,23 @@ class ContentSetup:
             t.n_num_actual = len(keep)
         return self._add(t, keep)
 
+    def optimized(self):
+        """The list after the rewriting the reference applies on every insertion (content.cpp:530-588: fuse
+        consecutive transformations, drop no-op reorders, move SubView / Reshape towards the front). The builder
+        methods above keep the list exactly as given so that tests control it; call this to get the list the
+        reference's ContentSetup would hold."""
+        from . import lib
+        tr, n = self.transforms()
+        out, n_out, keep = lib.optimize_transforms(self.base_type, tr, n)
+        items = []
+        for i in range(n_out):
+            t = Transform()
+            C.memmove(C.byref(t), C.byref(out[i]), C.sizeof(Transform))
+            items.append((t, keep if i == 0 else None))
+        res = ContentSetup(self.base_type, items)
+        res._keep_src = [k for _, k in self._items]  # numActualElements arrays are shared with this setup
+        return res
+
     # -- access ------------------------------------------------------------------------------------
     def transforms(self):
         return abi.make_transforms([t for t, _ in self._items]), len(self._items)

@@ -27,7 +27,7 @@ def _load():
         raise ImportError(f"{LIB_PATH} is missing: build it with `python -m vpux_plugin_b200.build` "
                           "(the package has no CPU fallback)")
     lib = C.CDLL(LIB_PATH)
-    for name in ("vf_infer_type", "vf_fold", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
+    for name in ("vf_infer_type", "vf_optimize_transforms", "vf_fold", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
                  "vf_nnz_per_oc", "vf_sparsify", "vf_sparsify_batch", "vf_weights_table", "vf_weights_table_batch", "vf_synth_fill", "vf_plan_shards",
                  "vf_ctx_create", "vf_ctx_synchronize", "vf_abi_version", "vf_ctx_device"):
         getattr(lib, name).restype = C.c_int
@@ -91,6 +91,21 @@ def infer_type(base_type, is_splat, transforms, n, params_cap=1 << 16):
     if st != 0:
         raise VfoldError(st, err.value.decode(errors="replace"))
     return abi.TType.from_pod(out), bool(osplat.value), nbytes.value
+
+
+def optimize_transforms(base_type, transforms, n, params_cap=1 << 16):
+    """vf_optimize_transforms (pure host): returns (ctypes array of abi.Transform, count, keepalive)."""
+    out = (abi.Transform * max(n, 1))()
+    n_out = C.c_int(0)
+    sb = np.zeros(params_cap, np.float64)
+    zb = np.zeros(params_cap, np.int64)
+    err = C.create_string_buffer(512)
+    bt = base_type.pod()
+    st = raw().vf_optimize_transforms(C.byref(bt), transforms, n, out, max(n, 1), C.byref(n_out), _ptr(sb), _ptr(zb),
+                                      C.c_int64(params_cap), err, C.c_size_t(512))
+    if st != 0:
+        raise VfoldError(st, err.value.decode(errors="replace"))
+    return out, n_out.value, (sb, zb, transforms)
 
 
 class Library:
