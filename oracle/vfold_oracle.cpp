@@ -880,12 +880,63 @@ Content tf_rescale_add(const Content& in, bool is_add, double value, const Type&
 }
 
 // ConvertElemTypeAttr::transform (quant -> quant) — convert_elem_type.cpp:22-29,48-60;
-// getValueRangeOffset — CD/utils/transformations.cpp:863-881. Sub-byte unpacking :62-77 is not restated.
+// getValueRangeOffset — CD/utils/transformations.cpp:863-881; sub-byte unpacking convert_elem_type.cpp:62-79
+// with subByteConversion, VC/src/utils/convert_utils.cpp:17-75.
+Content sub_byte_conversion(const Content& in, const Type& outType, bool outSplat, int bits) {
+    Content out = Content::alloc(outType, outType.elem.dtype, outSplat);
+    const int per = 8 / bits;
+    const uint8_t* src = in.ptr;
+    const uint64_t nbytes = (uint64_t(bits) * uint64_t(in.splat ? 1 : in.type.numel()) + 7) / 8;
+    const int64_t n = out.splat ? 1 : outType.numel();
+    // the output type picks the branch; 1-bit values are always treated as unsigned (:27)
+    if (outType.elem.dtype == VF_DT_U8 || bits == 1) {
+        const unsigned mask = (1u << bits) - 1u;
+        uint8_t* dst = out.mdata();
+        if (in.splat) {
+            const uint8_t first = uint8_t(src[0] & mask);  // :33-36
+            for (int64_t i = 0; i < n; ++i) dst[i] = first;
+        } else {
+            for (uint64_t b = 0; b < nbytes; ++b)
+                for (int k = 0; k < per; ++k) {
+                    const int64_t o = int64_t(b) * per + k;
+                    if (o < n) dst[o] = uint8_t((src[b] >> (k * bits)) & mask);
+                }
+        }
+    } else {
+        const int8_t* s8 = reinterpret_cast<const int8_t*>(src);
+        int8_t* dst = reinterpret_cast<int8_t*>(out.mdata());
+        const int rshift = 8 - bits;
+        if (in.splat) {
+            const int8_t second = int8_t(s8[0] >> rshift);  // the last element of the first byte (:53-56)
+            for (int64_t i = 0; i < n; ++i) dst[i] = second;
+        } else {
+            for (uint64_t b = 0; b < nbytes; ++b)
+                for (int k = 0; k < per; ++k) {
+                    const int64_t o = int64_t(b) * per + k;
+                    if (o >= n) continue;
+                    const int lshift = rshift - k * bits;
+                    int8_t v = int8_t(uint8_t(s8[b]) << lshift);
+                    v = int8_t(v >> rshift);
+                    dst[o] = v;
+                }
+        }
+    }
+    return out;
+}
+
 Content tf_convert(const Content& in, const vf_transform& t) {
     bool osplat;
     const Type outType = infer_one(in.type, in.splat, t, osplat);
     const Elem& qi = in.type.elem;
     const Elem& qo = outType.elem;
+    if (!qi.quantized() && !qo.quantized()) {
+        const int bits = dtype_bits(qi.dtype);
+        const bool out_byte = qo.dtype == VF_DT_I8 || qo.dtype == VF_DT_U8;
+        const bool same_sign = dtype_is_signed_int(qi.dtype) == dtype_is_signed_int(qo.dtype);
+        if (dtype_is_int(qi.dtype) && bits < 8 && out_byte && (same_sign || bits == 1) && in.storage == qi.dtype)
+            return sub_byte_conversion(in, outType, osplat, bits);
+        fail(VF_ERR_UNSUPPORTED, "Unsupported conversion");
+    }
     if (qi.quantized() && qo.quantized()) {
         if (!dtype_is_int(qi.dtype) || !dtype_is_int(qo.dtype) || dtype_bits(qi.dtype) != dtype_bits(qo.dtype))
             fail(VF_ERR_UNSUPPORTED, "Unsupported conversion");

@@ -330,6 +330,32 @@ def copy_to_i1(be):
     assert out.bytes().tolist() == [0xC8, 0x7F]
 
 
+def convert_elem_type_sub_byte(be):
+    """tests/unit/vpux_compiler/dialect/const/attributes/convert_elem_type.cpp:41-308 and lit
+    dialect/const/passes/constant_folding.mlir:713-830: ConvertElemType unpacks 1- and 4-bit constants to bytes.
+    Signless and unsigned 4-bit types take the masking branch (U4 here), signed ones are sign-extended (I4);
+    a splat yields the first element of its byte when masking and the last one when sign-extending."""
+    U4, I4, I1 = abi.VF_DT_U4, abi.VF_DT_I4, abi.VF_DT_I1
+    packed = np.array([0x66, 0x85, 0x2F, 0xDE], np.uint8)
+
+    def run(vals, shape, src, dst, splat=False):
+        t = TType(shape, src)
+        out = ContentAttr(np.asarray(vals, np.uint8), t, ContentSetup(t).convertElemType(dst), is_splat=splat,
+                          storage_dtype=src).fold(be)
+        assert out.type == TType(shape, dst) and out.is_splat == splat
+        return out.bytes().tolist()
+
+    assert run(packed, [1, 1, 2, 4], U4, U8) == [0x06, 0x06, 0x05, 0x08, 0x0F, 0x02, 0x0E, 0x0D]  # UT:74-106, 141-173
+    assert run([0xDD], [1, 1, 2, 4], U4, U8, splat=True) == [0x0D] * 8                              # UT:41-72, 108-139
+    assert run(packed, [1, 1, 2, 4], I4, I8) == [0x06, 0x06, 0x05, 0xF8, 0xFF, 0x02, 0xFE, 0xFD]  # UT:208-240
+    assert run([0xDD], [1, 1, 2, 4], I4, I8, splat=True) == [0xFD] * 8                              # UT:175-206
+    assert run([0x0D, 0x82], [1, 1, 2, 8], I1, I8) == [1, 0, 1, 1, 0, 0, 0, 0, 0, 1, 0, 0, 0, 0, 0, 1]  # UT:275-308
+    assert run([0xFF], [1, 1, 2, 8], I1, I8, splat=True) == [1] * 16                                 # UT:242-273
+    assert run([0x10, 0x32, 0x54, 0x76], [2, 4], U4, U8) == list(range(8))                         # lit :757-775
+    assert run([0x22], [2, 4], U4, U8, splat=True) == [2] * 8                                       # lit :739-755
+    assert run([0xEE], [2, 4], I4, I8, splat=True) == [0xFE] * 8                                    # lit :777-793 (-2)
+
+
 def sparsity_ptr_stepping(be):
     """lit dialect/VPU/passes/recompute_sparsity_ptrs.mlir:12-31: a 16x16x4x4 filter has sparsity-map rows of
     align(256, 128) / 8 = 32 bytes (map type 16x1x1x256xi1), so the sparsity pointers step by 32"""
@@ -347,5 +373,5 @@ FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequ
               pad_uniform_quant, pad_per_axis_quant, bit_pack, bit_pack_quant, get_sparsity_map,
               get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
               convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain, copy_to_i4,
-              copy_to_i1]
+              copy_to_i1, convert_elem_type_sub_byte]
 TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale, sparsity_ptr_stepping]

@@ -272,6 +272,27 @@ def test_sparsify_batch_buffer_too_small(gpu):
     assert jobs[0].status == abi.VF_ERR_BUFFER_TOO_SMALL
 
 
+@pytest.mark.parametrize("src,dst", [(abi.VF_DT_U4, U8), (abi.VF_DT_I4, I8), (abi.VF_DT_I1, I8), (abi.VF_DT_I1, U8)])
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 63, 4096, 100003])
+def test_convert_elem_type_unpacks_sub_byte(gpu, oracle, src, dst, n):
+    """ConvertElemType on 1- and 4-bit storage (convert_utils.cpp:17-75): element counts that are not multiples
+    of eight exercise the tail, the large one the vector path; splats take their own branch."""
+    rng = np.random.default_rng(n)
+    bits = 1 if src == abi.VF_DT_I1 else 4
+    raw = rng.integers(0, 256, (n * bits + 7) // 8).astype(np.uint8)
+    t = TType([n], src)
+    both(ContentAttr(raw, t, ContentSetup(t).convertElemType(dst), storage_dtype=src), gpu, oracle)
+    both(ContentAttr(raw[:1], t, ContentSetup(t).convertElemType(dst), is_splat=True, storage_dtype=src), gpu, oracle)
+
+
+def test_convert_elem_type_rejects_sign_changes(gpu, oracle):
+    t = TType([8], abi.VF_DT_U4)
+    raw = np.zeros(4, np.uint8)
+    for be in (gpu, oracle):
+        assert _status(lambda: ContentAttr(raw, t, ContentSetup(t).convertElemType(I8), storage_dtype=abi.VF_DT_U4).fold(be)) \
+            == abi.VF_ERR_UNSUPPORTED
+
+
 def test_sparsify_quantized_with_supplied_counts(gpu, oracle):
     rng = np.random.default_rng(10)
     shape = [4, 8, 2, 2]

@@ -217,7 +217,31 @@ DContent do_convert(vf_ctx* ctx, DContent& in, const vf_transform& t) {
             raise(VF_ERR_UNSUPPORTED, "Unsupported conversion between quantized types");
         return do_rescale_add(ctx, in, ot, double(zo - zi), true);
     }
-    raise(VF_ERR_UNSUPPORTED, "Unsupported conversion: only quantized -> quantized is implemented");
+    if (qi.quantized()) raise(VF_ERR_UNSUPPORTED, "Unsupported conversion from a quantized type to a plain one");
+    // sub-byte unpacking — convert_elem_type.cpp:66-79, utils/convert_utils.cpp:17-75. Signless types travel as
+    // the unsigned dtypes of this ABI, so "same signedness" is (i4 -> i8) or (u4 -> u8); 1-bit inputs go
+    // anywhere and always take the masking branch.
+    const int bits = dtype_bits(qi.dtype);
+    const bool out_byte = qo.dtype == VF_DT_I8 || qo.dtype == VF_DT_U8;
+    const bool same_sign = dtype_is_signed(qi.dtype) == dtype_is_signed(qo.dtype);
+    if (!qo.quantized() && dtype_is_int(qi.dtype) && bits < 8 && out_byte && (same_sign || bits == 1) && in.storage == qi.dtype) {
+        const bool sign = qo.dtype == VF_DT_I8 && bits != 1;
+        DContent out = alloc_like(ctx, ot, qo.dtype, in.splat);
+        if (in.splat) {
+            // the masking branch unpacks the first element of the byte, the sign-extending branch the last one
+            // (convert_utils.cpp:33-36, 53-56): one byte in, one element out
+            uint8_t src = 0;
+            VF_CUDA(cudaMemcpyAsync(&src, in.d, 1, cudaMemcpyDeviceToHost, ctx->stream));
+            VF_CUDA(cudaStreamSynchronize(ctx->stream));
+            const uint8_t v = sign ? uint8_t(int8_t(src) >> (8 - bits)) : uint8_t(src & ((1u << bits) - 1u));
+            copy_in(ctx, out.own.p, &v, 1, VF_MEM_HOST);
+            VF_CUDA(cudaStreamSynchronize(ctx->stream));  // `v` leaves scope
+        } else {
+            launch_unpack_subbyte(ctx, static_cast<const uint8_t*>(in.d), out.own.as<uint8_t>(), ot.numel(), bits, sign);
+        }
+        return out;
+    }
+    raise(VF_ERR_UNSUPPORTED, "Unsupported conversion: neither quantized -> quantized nor a sub-byte unpack");
 }
 
 DContent do_permute(vf_ctx* ctx, DContent& in, const Type& ot, const int* mp) {

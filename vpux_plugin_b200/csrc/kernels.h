@@ -28,6 +28,8 @@ void launch_rescale_add(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, f
 void launch_convert(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void* out, int out_dt, int64_t n);
 // copyTo sub-byte packing: `per_byte` elements of `in` (read as int8) into each output byte, low bits first
 void launch_pack_subbyte(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in, int per_byte);
+// subByteConversion: `n_out` elements of `bits` (1 / 2 / 4) bits each, low bits first, to one byte each
+void launch_unpack_subbyte(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t n_out, int bits, bool sign_extend);
 // BitPack<4>: reads pairs through getValues<uint8_t>()
 void launch_bitpack4(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in);
 void launch_fill_bytes(vf_ctx* ctx, void* out, uint8_t value, uint64_t bytes);

@@ -101,6 +101,42 @@ __global__ void k_pack_subbyte(const void* __restrict__ in, int in_dt, uint8_t* 
     }
 }
 
+// subByteConversion — utils/convert_utils.cpp:17-75: 1-, 2- or 4-bit elements (low bits first) to one byte
+// each. A thread expands 8 elements: it reads `BITS` input bytes as one word and writes 8 bytes. `sign` selects
+// the sign-extending branch (:47-66), otherwise the masking branch (:28-46).
+template <int BITS>
+__global__ void k_unpack_subbyte(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n_out, int sign) {
+    constexpr unsigned kMask = (1u << BITS) - 1u;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int64_t groups = (n_out + 7) / 8;
+    const bool aligned = (reinterpret_cast<uintptr_t>(in) % BITS) == 0 && (reinterpret_cast<uintptr_t>(out) % 8) == 0;
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+        const int64_t o0 = g * 8;
+        const int left = int(n_out - o0 < 8 ? n_out - o0 : 8);
+        uint32_t w = 0;
+        if (aligned && left == 8) {
+            if (BITS == 4) w = *reinterpret_cast<const uint32_t*>(in + g * 4);
+            else if (BITS == 2) w = *reinterpret_cast<const uint16_t*>(in + g * 2);
+            else w = in[g];
+        } else {
+            const int nbytes = (left * BITS + 7) / 8;
+            for (int b = 0; b < nbytes; ++b) w |= uint32_t(in[g * BITS + b]) << (8 * b);
+        }
+        uint32_t r[2] = {0u, 0u};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t v = (w >> (k * BITS)) & kMask;
+            if (sign) v = uint32_t(int32_t(v << (32 - BITS)) >> (32 - BITS)) & 0xFFu;
+            r[k >> 2] |= v << (8 * (k & 3));
+        }
+        if (aligned && left == 8) {
+            *reinterpret_cast<uint2*>(out + o0) = make_uint2(r[0], r[1]);
+        } else {
+            for (int k = 0; k < left; ++k) out[o0 + k] = uint8_t(r[k >> 2] >> (8 * (k & 3)));
+        }
+    }
+}
+
 // BitPack<4> — attributes/bit_pack.cpp:146-151
 __global__ void k_bitpack4(const void* __restrict__ in, int in_dt, uint8_t* __restrict__ out, int64_t n_out,
                            int* flags) {
@@ -650,6 +686,19 @@ void launch_pack_params(vf_ctx* ctx, const double* d_scales, const int64_t* d_zp
 void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table) {
     if (a.oc <= 0) return;
     k_weights_table<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(a, d_table, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_unpack_subbyte(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t n_out, int bits, bool sign_extend) {
+    if (n_out <= 0) return;
+    const int grid = grid_for((n_out + 7) / 8);
+    const int s = sign_extend ? 1 : 0;
+    switch (bits) {
+    case 1: k_unpack_subbyte<1><<<grid, kBlock, 0, ctx->stream>>>(in, out, n_out, s); break;
+    case 2: k_unpack_subbyte<2><<<grid, kBlock, 0, ctx->stream>>>(in, out, n_out, s); break;
+    case 4: k_unpack_subbyte<4><<<grid, kBlock, 0, ctx->stream>>>(in, out, n_out, s); break;
+    default: raise(VF_ERR_UNSUPPORTED, "Invalid number of elements per byte for %d-bit elements", bits);
+    }
     post_launch(ctx);
 }
 
