@@ -160,8 +160,14 @@ typedef enum vf_transform_kind {
     VF_T_BIT_PACK = 13,         /* #const.BitPack          bit_pack.cpp:132-154        (width)      */
     VF_T_GET_SPARSITY_MAP = 14, /* #const.GetSparsityMap   get_sparsity_map.cpp:82-119              */
     VF_T_SPARSIFY = 15,         /* #const.Sparsify         sparsify.cpp:163-203 (compress, counts)  */
-    VF_T_SUBVIEW = 16           /* #const.SubView          subview.cpp:390-432 (a = offset, b = shape) */
+    VF_T_SUBVIEW = 16,          /* #const.SubView          subview.cpp:390-432 (a = offset, b = shape) */
+    VF_T_SWIZZLE_CONSTANT = 17  /* #const.SwizzleConstant  swizzle_transform.cpp:163-215
+                                   (a[0] = swizzle key 0..5, a[1] = arch: VF_ARCH_NPU37XX / VF_ARCH_NPU40XX) */
 } vf_transform_kind;
+
+/* VPU::ArchKind values SwizzleConstant carries (VPU/attributes.td:47-50) */
+#define VF_ARCH_NPU37XX 3
+#define VF_ARCH_NPU40XX 4
 
 typedef struct vf_transform {
     int32_t kind;              /* vf_transform_kind */

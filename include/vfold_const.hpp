@@ -393,6 +393,13 @@ public:
         it->t.width = width;
         return append(std::move(it));
     }
+    ContentSetup swizzleConstant(uint64_t swizzleKey, uint64_t arch) const {
+        auto it = make(VF_T_SWIZZLE_CONSTANT);
+        it->t.rank = 2;
+        it->t.a[0] = int64_t(swizzleKey);
+        it->t.a[1] = int64_t(arch);
+        return append(std::move(it));
+    }
     ContentSetup getSparsityMap() const { return append(make(VF_T_GET_SPARSITY_MAP)); }
     ContentSetup sparsify(bool compressOutputType, const std::vector<int64_t>& numActualElements = {}) const {
         auto it = make(VF_T_SPARSIFY);
@@ -456,7 +463,7 @@ private:
         std::vector<int64_t> counts;
     };
     static int position(int kind) {  // 0 = NONE, 1 = PREFERRED_LAST, 2 = LAST
-        if (kind == VF_T_BIT_PACK) return 2;
+        if (kind == VF_T_BIT_PACK || kind == VF_T_SWIZZLE_CONSTANT) return 2;
         if (kind == VF_T_SPARSIFY || kind == VF_T_GET_SPARSITY_MAP) return 1;
         return 0;
     }

@@ -767,6 +767,28 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
         out_splat = false;
         break;
     }
+    case VF_T_SWIZZLE_CONSTANT: {  // swizzle_transform.cpp:127-156
+        const int64_t arch = t.a[1];
+        if (arch != VF_ARCH_NPU37XX && arch != VF_ARCH_NPU40XX)
+            fail(VF_ERR_UNSUPPORTED, "Architecture %lld does not support swizzling", (long long)arch);
+        if (t.a[0] < 0) fail(VF_ERR_INVALID_ARG, "negative swizzle key");
+        const int64_t total = int64_t((uint64_t(in.numel()) * uint64_t(dtype_bits(in.elem.dtype)) + 7) / 8);
+        const int64_t new_size = align_up(total, arch == VF_ARCH_NPU40XX ? 1024 : 512);  // swizzling_utils.hpp:26-27
+        for (int i = 0; i < in.rank; ++i) out.shape[i] = 1;
+        if (!in.elem.quantized() && dtype_bits(in.elem.dtype) == 1) {
+            out.shape[0] = new_size * 8;
+        } else if (!in.elem.quantized() && in.elem.dtype == VF_DT_F16) {
+            out.shape[0] = new_size / 2;
+        } else {
+            out.shape[0] = new_size;
+            Elem e;
+            e.kind = VF_ELEM_PLAIN;
+            e.dtype = VF_DT_U8;
+            out.elem = e;
+        }
+        out_splat = false;
+        break;
+    }
     default:
         fail(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
@@ -775,6 +797,7 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
 
 int position_requirement(int kind) {  // CI/attr_interfaces.hpp:24-28; bit_pack.cpp:160-162; sparsify.cpp:209-211
     switch (kind) {
+    case VF_T_SWIZZLE_CONSTANT:    // swizzle_transform.cpp:221-223
     case VF_T_BIT_PACK: return 2;  // LAST
     case VF_T_SPARSIFY:
     case VF_T_GET_SPARSITY_MAP: return 1;  // PREFERRED_LAST
@@ -1300,6 +1323,56 @@ Content move_buffer(Content& in, const Type& type) {  // Content::moveBuffer —
     return out;
 }
 
+uint64_t copy_to(const Content& c, uint8_t* dst, uint64_t dst_bytes);
+
+// SwizzleConstantAttr::transform — CD/attributes/swizzle_transform.cpp:163-215 with
+// BufferSwizzleTransform::swizzle (VC/include/vpux/compiler/utils/swizzle_transform.hpp:56-76) and
+// AddressTransform (swizzle_transform.cpp:37-83)
+Content tf_swizzle(const Content& in, const vf_transform& t) {
+    bool osplat;
+    const Type outType = infer_one(in.type, in.splat, t, osplat);
+    const uint32_t key = uint32_t(t.a[0]);
+    const bool npu40 = t.a[1] == VF_ARCH_NPU40XX;
+    const uint64_t inTotal = type_bytes(in.type);
+    const uint64_t newSize = uint64_t(align_up(int64_t(inTotal), npu40 ? 1024 : 512));
+    std::vector<uint8_t> values(newSize, 0);
+    copy_to(in, values.data(), inTotal);
+    if (newSize > inTotal) {
+        const uint8_t pad = in.splat ? values[0] : uint8_t(0);
+        std::fill(values.begin() + long(inTotal), values.end(), pad);
+    }
+    Content out = Content::alloc(outType, outType.elem.dtype, false, int64_t(newSize));
+    if (in.splat) {
+        std::memcpy(out.mdata(), values.data(), newSize);
+        return out;
+    }
+    // setStaggerBits
+    const uint32_t staggerBits = key % 6u;
+    const uint32_t staggerMask = (1u << staggerBits) - 1u;
+    uint32_t shift = 9u - staggerBits, log2Width = 4u, ramCutMask = (1u << 9) - 1u;
+    if (npu40) {
+        ++shift;
+        ++log2Width;
+        ramCutMask = (1u << 10) - 1u;
+    }
+    const uint32_t width = 1u << log2Width;
+    const uint64_t iterations = ((newSize + width - 1) >> log2Width);
+    uint32_t dpuAddr = 0;
+    for (uint64_t i = 0; i < iterations; ++i) {
+        uint32_t stagger = dpuAddr >> log2Width;  // getPhysicalAddress
+        stagger &= (1u << 11) - 1u;
+        stagger >>= 5;
+        stagger &= staggerMask;
+        stagger <<= shift;
+        uint32_t phy = dpuAddr + stagger;
+        phy &= ramCutMask;
+        phy += dpuAddr & ~ramCutMask;
+        std::memcpy(out.mdata() + phy, values.data() + dpuAddr, width);
+        dpuAddr += width;
+    }
+    return out;
+}
+
 Content apply(Content& in, const vf_transform& t, int nthreads) {
     bool osplat;
     switch (t.kind) {
@@ -1322,6 +1395,7 @@ Content apply(Content& in, const vf_transform& t, int nthreads) {
     case VF_T_BIT_PACK: return tf_bitpack(in, t);
     case VF_T_GET_SPARSITY_MAP: return tf_sparsity_map(in, t);
     case VF_T_SPARSIFY: return tf_sparsify(in, t, nthreads);
+    case VF_T_SWIZZLE_CONSTANT: return tf_swizzle(in, t);
     default: fail(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }

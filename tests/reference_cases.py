@@ -229,8 +229,10 @@ def sparsify_quantized(be):
 
 
 def position_requirement(be):
-    """UT:1724-1749 PositionRequirement (BitPack stands in for the LAST-positioned SwizzleConstant)"""
+    """UT:1724-1749 PositionRequirement: SwizzleConstant is LAST, Sparsify PREFERRED_LAST; the same with BitPack"""
     t = TType([1, 1, 3, 3], F32)
+    s = ContentSetup(t).rescale(10.0).swizzleConstant(5, abi.VF_ARCH_NPU37XX).sparsify(False).castElemType(F16)
+    assert s.names() == [abi.VF_T_RESCALE, abi.VF_T_CAST_ELEM_TYPE, abi.VF_T_SPARSIFY, abi.VF_T_SWIZZLE_CONSTANT]
     s = ContentSetup(t).rescale(10.0).bitPack(4).sparsify(False).castElemType(F16)
     assert s.names() == [abi.VF_T_RESCALE, abi.VF_T_CAST_ELEM_TYPE, abi.VF_T_SPARSIFY, abi.VF_T_BIT_PACK]
 
@@ -356,6 +358,36 @@ def convert_elem_type_sub_byte(be):
     assert run([0xEE], [2, 4], I4, I8, splat=True) == [0xFE] * 8                                    # lit :777-793 (-2)
 
 
+def swizzle_constant(be):
+    """UT:1872-2180 SwizzleConstant_*: the result is a flat buffer of the swizzling-aligned size (512 bytes on
+    NPU37XX) whose first chunk stays in place; 1-bit and fp16 constants keep their element type, the rest
+    become u8; a splat pads with its own bytes and is no longer a splat."""
+    arch = abi.VF_ARCH_NPU37XX
+
+    def run(vals, shape, dt, cast=None, splat=False):
+        t = TType(shape, dt)
+        s = ContentSetup(t)
+        if cast is not None:
+            s = s.castElemType(cast)
+        out = ContentAttr(np.asarray(vals), t, s.swizzleConstant(5, arch), is_splat=splat).fold(be)
+        assert not out.is_splat and out.written == 512
+        return out
+
+    bits = [0, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 1, 1, 1, 1, 0]
+    o = run(np.array(bits, np.uint8), [1, 1, 4, 4], U8, cast=abi.VF_DT_I1)          # UT:1872-1909
+    assert o.type == TType([4096, 1, 1, 1], abi.VF_DT_I1) and o.bytes()[:2].tolist() == [0xC8, 0x7F]
+    o = run(np.array([1, 7, 10, 15], np.uint8), [1, 1, 2, 2], U8, cast=abi.VF_DT_U4)  # UT:1911-1950
+    assert o.type == TType([512, 1, 1, 1], U8) and o.bytes()[:2].tolist() == [0x71, 0xFA]
+    o = run(np.array([255, 100, 0, 1], np.uint8), [1, 1, 2, 2], U8)                  # UT:1952-1984
+    assert o.type == TType([512, 1, 1, 1], U8) and o.bytes()[:4].tolist() == [255, 100, 0, 1]
+    o = run(np.array([700, 800, 900, 900], np.float32), [1, 1, 2, 2], F32)           # UT:1986-2018
+    assert o.bytes()[:16].view(np.float32).tolist() == [700, 800, 900, 900]
+    o = run(np.array([1], np.uint8), [1, 1, 4, 4], U8, cast=abi.VF_DT_I1, splat=True)  # UT:2020-2060
+    assert o.bytes().tolist() == [0xFF] * 512
+    o = run(np.array([7], np.uint8), [1, 1, 2, 2], U8, splat=True)                   # after UT:2104-2140
+    assert o.bytes().tolist() == [7] * 512
+
+
 def sparsity_ptr_stepping(be):
     """lit dialect/VPU/passes/recompute_sparsity_ptrs.mlir:12-31: a 16x16x4x4 filter has sparsity-map rows of
     align(256, 128) / 8 = 32 bytes (map type 16x1x1x256xi1), so the sparsity pointers step by 32"""
@@ -373,5 +405,5 @@ FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequ
               pad_uniform_quant, pad_per_axis_quant, bit_pack, bit_pack_quant, get_sparsity_map,
               get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
               convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain, copy_to_i4,
-              copy_to_i1, convert_elem_type_sub_byte]
+              copy_to_i1, convert_elem_type_sub_byte, swizzle_constant]
 TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale, sparsity_ptr_stepping]

@@ -285,6 +285,39 @@ def test_convert_elem_type_unpacks_sub_byte(gpu, oracle, src, dst, n):
     both(ContentAttr(raw[:1], t, ContentSetup(t).convertElemType(dst), is_splat=True, storage_dtype=src), gpu, oracle)
 
 
+def _physical(addr, key, arch):
+    """AddressTransform::getPhysicalAddress (swizzle_transform.cpp:71-83) on whole-chunk addresses."""
+    log2w, cut = (5, (1 << 10) - 1) if arch == abi.VF_ARCH_NPU40XX else (4, (1 << 9) - 1)
+    bits = key % 6
+    shift = 9 - bits + (1 if arch == abi.VF_ARCH_NPU40XX else 0)
+    s = (((addr >> log2w) & 0x7FF) >> 5) & ((1 << bits) - 1)
+    return (((addr + (s << shift)) & cut) + (addr & ~cut)), 1 << log2w
+
+
+@pytest.mark.parametrize("arch", [abi.VF_ARCH_NPU37XX, abi.VF_ARCH_NPU40XX])
+@pytest.mark.parametrize("key", [0, 1, 3, 5])
+@pytest.mark.parametrize("dt,n", [(U8, 100000), (F16, 33333), (F32, 5000), (I8, 512)])
+def test_swizzle_constant(gpu, oracle, arch, key, dt, n):
+    """GPU == oracle, and the result is the chunk permutation the address transform defines (checked here
+    independently of both), padded with zeros to the swizzling-aligned size."""
+    rng = np.random.default_rng(key * 10 + n)
+    x = rng.integers(0, 256, n * abi.DTYPE_NUMPY[dt]().itemsize).astype(np.uint8).view(abi.DTYPE_NUMPY[dt])
+    t = TType([n], dt)
+    out = both(ContentAttr(x, t, ContentSetup(t).swizzleConstant(key, arch)), gpu, oracle).bytes()
+    align = 1024 if arch == abi.VF_ARCH_NPU40XX else 512
+    raw = x.view(np.uint8)
+    assert out.size == (raw.size + align - 1) // align * align
+    padded = np.zeros(out.size, np.uint8)
+    padded[:raw.size] = raw
+    expect = np.zeros_like(padded)
+    w = _physical(0, key, arch)[1]
+    for a in range(0, out.size, w):
+        p = _physical(a, key, arch)[0]
+        expect[p:p + w] = padded[a:a + w]
+    assert np.array_equal(out, expect)
+    assert np.array_equal(np.sort(out), np.sort(padded))  # a permutation of the padded bytes
+
+
 def test_convert_elem_type_rejects_sign_changes(gpu, oracle):
     t = TType([8], abi.VF_DT_U4)
     raw = np.zeros(4, np.uint8)

@@ -50,7 +50,8 @@ VF_MEM_HOST, VF_MEM_HOST_PINNED, VF_MEM_DEVICE = 0, 1, 2
 
 (VF_T_CAST_ELEM_TYPE, VF_T_CONVERT_ELEM_TYPE, VF_T_DEQUANTIZE, VF_T_QUANTIZE, VF_T_RESCALE, VF_T_ADD, VF_T_RESHAPE,
  VF_T_REORDER, VF_T_MEM_PERMUTE, VF_T_TRANSPOSE, VF_T_LAYOUT_CAST, VF_T_PAD_WITH_ZERO, VF_T_BIT_PACK,
- VF_T_GET_SPARSITY_MAP, VF_T_SPARSIFY, VF_T_SUBVIEW) = range(1, 17)
+ VF_T_GET_SPARSITY_MAP, VF_T_SPARSIFY, VF_T_SUBVIEW, VF_T_SWIZZLE_CONSTANT) = range(1, 18)
+VF_ARCH_NPU37XX, VF_ARCH_NPU40XX = 3, 4
 
 VF_RANGE_MINMAX, VF_RANGE_ABSMAX = 0, 1
 VF_SPARSITY_PTR_WHEN_NO_SPARSITY = 0xFFFFFF

@@ -20,7 +20,7 @@ _NONE, _PREFERRED_LAST, _LAST = 0, 1, 2
 def _position(kind):
     # attr_interfaces.hpp:24-28; BitPack is LAST (bit_pack.cpp:160-162), Sparsify / GetSparsityMap are
     # PREFERRED_LAST (sparsify.cpp:209-211, get_sparsity_map.cpp:125-127)
-    if kind == abi.VF_T_BIT_PACK:
+    if kind in (abi.VF_T_BIT_PACK, abi.VF_T_SWIZZLE_CONSTANT):  # swizzle_transform.cpp:221-223
         return _LAST
     if kind in (abi.VF_T_SPARSIFY, abi.VF_T_GET_SPARSITY_MAP):
         return _PREFERRED_LAST
@@ -132,6 +132,12 @@ class ContentSetup:
     def bitPack(self, width):
         t = self._t(abi.VF_T_BIT_PACK)
         t.width = int(width)
+        return self._add(t)
+
+    def swizzleConstant(self, swizzle_key, arch):
+        t = self._t(abi.VF_T_SWIZZLE_CONSTANT)
+        t.rank = 2
+        t.a[0], t.a[1] = int(swizzle_key), int(arch)
         return self._add(t)
 
     def getSparsityMap(self):

@@ -108,6 +108,7 @@ void order_to_perm(uint32_t order, int rank, int* perm);
 // inferOutputType / inferOutputSplat of one transformation (pure host)
 Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_splat);
 void check_positions(const vf_transform* t, int n);
+int64_t swizzle_size_alignment(int arch);  // bytes a swizzled buffer's size is aligned to
 Type compress_type(const Type& in, const int64_t* counts, int64_t n);
 
 // calcScaleAndZeroPoint on the host (used for validation of tiny inputs and by tests of the planner)

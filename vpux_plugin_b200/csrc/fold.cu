@@ -446,6 +446,8 @@ DContent do_sparsify(vf_ctx* ctx, DContent& in, const vf_transform& t, DBuf* kee
     return out;
 }
 
+DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t);
+
 DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     bool os;
     switch (t.kind) {
@@ -468,6 +470,7 @@ DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     case VF_T_BIT_PACK: return do_bitpack(ctx, in, t);
     case VF_T_GET_SPARSITY_MAP: return do_sparsity_map(ctx, in, t);
     case VF_T_SPARSIFY: return do_sparsify(ctx, in, t);
+    case VF_T_SWIZZLE_CONSTANT: return do_swizzle(ctx, in, t);
     default: raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }
@@ -548,6 +551,32 @@ uint64_t copy_to(vf_ctx* ctx, DContent& c, void* dst, uint64_t dst_bytes, int ds
         emit(tmp.p, need);
     }
     return written;
+}
+
+// SwizzleConstant — attributes/swizzle_transform.cpp:163-215: materialise the content as copyTo would, pad it
+// to the swizzling-aligned size (zeros, or the first byte of a splat) and permute its RAM-cut chunks.
+DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const uint64_t in_total = in.type.alloc_bytes();
+    const uint64_t new_size = uint64_t(align_up(int64_t(in_total), swizzle_size_alignment(int(t.a[1]))));
+    DBuf lin(ctx, new_size);
+    copy_to(ctx, in, lin.p, in_total, VF_MEM_DEVICE, nullptr);
+    if (new_size > in_total) {
+        uint8_t pad = 0;
+        if (in.splat) {
+            VF_CUDA(cudaMemcpyAsync(&pad, lin.p, 1, cudaMemcpyDeviceToHost, ctx->stream));
+            VF_CUDA(cudaStreamSynchronize(ctx->stream));
+        }
+        launch_fill_bytes(ctx, lin.as<uint8_t>() + in_total, pad, new_size - in_total);
+    }
+    DContent out = alloc_like(ctx, ot, ot.elem.dtype, false, int64_t(new_size));
+    if (in.splat) {  // every chunk holds the same bytes: nothing to permute
+        VF_CUDA(cudaMemcpyAsync(out.own.p, lin.p, new_size, cudaMemcpyDeviceToDevice, ctx->stream));
+    } else {
+        launch_swizzle(ctx, lin.p, out.own.p, new_size, int(t.a[0]), int(t.a[1]));
+    }
+    return out;
 }
 
 struct CallScope {  // per-call bookkeeping: context lock, device, error flags, launch statistics

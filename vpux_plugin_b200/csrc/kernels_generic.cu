@@ -137,6 +137,27 @@ __global__ void k_unpack_subbyte(const uint8_t* __restrict__ in, uint8_t* __rest
     }
 }
 
+// SwizzleConstant — BufferSwizzleTransform::swizzle (utils/swizzle_transform.hpp:56-76) with
+// AddressTransform::getPhysicalAddress (attributes/swizzle_transform.cpp:71-83): every chunk of the RAM-cut
+// data width (16 bytes on NPU37XX, 32 on NPU40XX) moves to its staggered address inside its RAM-cut block.
+// A pure permutation of 16-byte vectors: one vector per thread step, loads and stores both 16 bytes wide.
+__global__ void k_swizzle(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t n_vec, uint32_t log2w,
+                          uint32_t stagger_mask, uint32_t shift, uint32_t cut_mask) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t v = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
+        const uint32_t addr = uint32_t(v) << 4;
+        const uint32_t dpu = addr & ~((1u << log2w) - 1u);  // the chunk this vector belongs to
+        uint32_t s = dpu >> log2w;
+        s &= (1u << 11) - 1u;
+        s >>= 5;
+        s &= stagger_mask;
+        s <<= shift;
+        uint32_t phy = (dpu + s) & cut_mask;
+        phy += dpu & ~cut_mask;
+        out[(phy + (addr - dpu)) >> 4] = in[v];
+    }
+}
+
 // BitPack<4> — attributes/bit_pack.cpp:146-151
 __global__ void k_bitpack4(const void* __restrict__ in, int in_dt, uint8_t* __restrict__ out, int64_t n_out,
                            int* flags) {
@@ -686,6 +707,23 @@ void launch_pack_params(vf_ctx* ctx, const double* d_scales, const int64_t* d_zp
 void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table) {
     if (a.oc <= 0) return;
     k_weights_table<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(a, d_table, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_swizzle(vf_ctx* ctx, const void* in, void* out, uint64_t bytes, int swizzle_key, int arch) {
+    if (!bytes) return;
+    if (bytes >= (1ull << 32)) raise(VF_ERR_UNSUPPORTED, "swizzled constants are addressed with 32 bits");
+    // AddressTransform::setStaggerBits — attributes/swizzle_transform.cpp:37-56
+    const uint32_t bits = uint32_t(swizzle_key) % 6u;
+    uint32_t shift = 9u - bits, log2w = 4u, cut_mask = (1u << 9) - 1u;
+    if (arch == VF_ARCH_NPU40XX) {
+        shift += 1;
+        log2w += 1;
+        cut_mask = (1u << 10) - 1u;
+    }
+    const int64_t n_vec = int64_t(bytes / 16);
+    k_swizzle<<<grid_for(n_vec), kBlock, 0, ctx->stream>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec, log2w,
+                                                          (1u << bits) - 1u, shift, cut_mask);
     post_launch(ctx);
 }
 

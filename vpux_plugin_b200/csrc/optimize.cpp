@@ -27,7 +27,7 @@ struct Item {
 using List = std::vector<Item>;
 
 int position(int kind) {  // attr_interfaces.hpp:24-28
-    if (kind == VF_T_BIT_PACK) return 2;
+    if (kind == VF_T_BIT_PACK || kind == VF_T_SWIZZLE_CONSTANT) return 2;
     if (kind == VF_T_SPARSIFY || kind == VF_T_GET_SPARSITY_MAP) return 1;
     return 0;
 }

@@ -321,14 +321,37 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
         out_splat = false;
         return out;
 
+    case VF_T_SWIZZLE_CONSTANT: {  // swizzle_transform.cpp:127-156: a flat buffer of the swizzling-aligned size
+        const int64_t arch = t.a[1];
+        if (arch != VF_ARCH_NPU37XX && arch != VF_ARCH_NPU40XX) raise(VF_ERR_UNSUPPORTED, "Architecture %lld does not support swizzling", (long long)arch);
+        if (t.a[0] < 0) raise(VF_ERR_INVALID_ARG, "negative swizzle key");
+        const int64_t new_size = align_up(int64_t(in.alloc_bytes()), swizzle_size_alignment(int(arch)));
+        for (int i = 0; i < in.rank; ++i) out.shape[i] = 1;
+        if (!in.elem.quantized() && dtype_bits(in.elem.dtype) == 1) {
+            out.shape[0] = new_size * 8;  // 1-bit types keep their type
+        } else if (!in.elem.quantized() && in.elem.dtype == VF_DT_F16) {
+            out.shape[0] = new_size / 2;
+        } else {
+            out.shape[0] = new_size;
+            out.elem = Elem::plain(VF_DT_U8);
+        }
+        out_splat = false;
+        return out;
+    }
+
     default:
         raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }
 
+int64_t swizzle_size_alignment(int arch) {  // utils/swizzling_utils.hpp:26-27
+    return arch == VF_ARCH_NPU40XX ? 1024 : 512;
+}
+
 void check_positions(const vf_transform* t, int n) {
-    // attributes/content.cpp:585-588 — a LAST transformation (BitPack) may only be the final one
-    if (n >= 2 && t[n - 2].kind == VF_T_BIT_PACK) raise(VF_ERR_POSITION, "At most 1 attribute with LAST requirement allowed!");
+    // attributes/content.cpp:585-588 — a LAST transformation (BitPack, SwizzleConstant) may only be the final one
+    if (n >= 2 && (t[n - 2].kind == VF_T_BIT_PACK || t[n - 2].kind == VF_T_SWIZZLE_CONSTANT))
+        raise(VF_ERR_POSITION, "At most 1 attribute with LAST requirement allowed!");
 }
 
 bool calc_scale_zp_host(double qmin, double qmax, double rmin, double rmax, double& scale, int64_t& zp) {
