@@ -129,8 +129,15 @@ struct vf_ctx {
     uint64_t staging_bytes = 0;
     void* staging[2] = {nullptr, nullptr};  // pinned bounce buffers for pageable host memory
     cudaEvent_t staging_ev[2] = {nullptr, nullptr};
+    // job tables of the batched launches: a pinned staging area and its device twin, filled front to back within
+    // one call (calls are synchronous, so the area is free again when the next call starts)
+    static constexpr size_t kTableBytes = 1u << 20;
+    char* table_host = nullptr;
+    char* table_dev = nullptr;
+    size_t table_used = 0;
     int* d_flags = nullptr;  // device error flags (see VF_FLAG_* in device_utils.cuh)
     int* h_flags = nullptr;  // pinned mirror
+    bool flags_dirty = false;  // the device flags may be non-zero (a call found something or ended early)
     uint64_t launches = 0;
     int32_t opt_flags = 0;
     bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device
@@ -195,6 +202,9 @@ struct DBuf {  // RAII scratch buffer
 // host <-> device transfers that honour the memory kind of the host side
 void copy_in(vf_ctx* ctx, void* dst_dev, const void* src, size_t bytes, int src_kind);
 void copy_out(vf_ctx* ctx, void* dst, int dst_kind, const void* src_dev, size_t bytes);
+// Copies a job table to the device and returns where it is. Small tables go through the context's table area
+// (one asynchronous copy, nothing allocated); `fallback` owns the memory of a table that does not fit.
+const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallback);
 void flags_clear(vf_ctx* ctx);
 // synchronises the stream and raises if a kernel recorded an error
 void flags_check(vf_ctx* ctx);

@@ -72,8 +72,26 @@ void copy_out(vf_ctx* ctx, void* dst, int dst_kind, const void* src_dev, size_t 
     }
 }
 
+const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallback) {
+    const size_t need = (bytes + 255) & ~size_t(255);
+    if (ctx->table_host && ctx->table_used + need <= vf_ctx::kTableBytes) {
+        char* h = ctx->table_host + ctx->table_used;
+        char* d = ctx->table_dev + ctx->table_used;
+        ctx->table_used += need;
+        std::memcpy(h, src, bytes);
+        VF_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        return d;
+    }
+    fallback = DBuf(ctx, bytes);
+    copy_in(ctx, fallback.p, src, bytes, VF_MEM_HOST);
+    return fallback.p;
+}
+
+// The flags are zero unless a call found something or ended early: only then is the next call's clearing real.
 void flags_clear(vf_ctx* ctx) {
-    VF_CUDA(cudaMemsetAsync(ctx->d_flags, 0, sizeof(int) * kNumFlags, ctx->stream));
+    ctx->table_used = 0;  // a new call: the previous call's job tables are no longer in use
+    if (ctx->flags_dirty) VF_CUDA(cudaMemsetAsync(ctx->d_flags, 0, sizeof(int) * kNumFlags, ctx->stream));
+    ctx->flags_dirty = true;  // until flags_check has seen them all zero
 }
 
 void flags_check(vf_ctx* ctx) {
@@ -81,6 +99,9 @@ void flags_check(vf_ctx* ctx) {
     VF_CUDA(cudaStreamSynchronize(ctx->stream));
     VF_CUDA(cudaGetLastError());
     const int* f = ctx->h_flags;
+    bool any = false;
+    for (int i = 0; i < kNumFlags; ++i) any |= f[i] != 0;
+    if (!any) ctx->flags_dirty = false;
     if (f[0]) raise(VF_ERR_CHECKED_CAST, "Can not safely cast a value to the destination element type");
     if (f[1]) raise(VF_ERR_QUANT_RANGE, "calcScaleAndZeroPoint failed: range without zero or scale too small");
     if (f[2]) raise(VF_ERR_SHAPE, "numActualElements smaller than the number of non-sparse elements");
@@ -124,6 +145,8 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
             VF_CUDA(cudaMalloc(&c->d_flags, sizeof(int) * vf::kNumFlags));
             VF_CUDA(cudaMallocHost(&c->h_flags, sizeof(int) * vf::kNumFlags));
             VF_CUDA(cudaMemset(c->d_flags, 0, sizeof(int) * vf::kNumFlags));
+            VF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->table_host), vf_ctx::kTableBytes));
+            VF_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->table_dev), vf_ctx::kTableBytes));
             // keep freed scratch cached in the pool instead of returning it to the driver on every sync
             cudaMemPool_t pool;
             VF_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
@@ -145,6 +168,8 @@ void vf_ctx_destroy(vf_ctx* c) {
         if (c->staging[k]) cudaFreeHost(c->staging[k]);
         if (c->staging_ev[k]) cudaEventDestroy(c->staging_ev[k]);
     }
+    if (c->table_host) cudaFreeHost(c->table_host);
+    if (c->table_dev) cudaFree(c->table_dev);
     if (c->d_flags) cudaFree(c->d_flags);
     if (c->h_flags) cudaFreeHost(c->h_flags);
     if (c->lane_stream) cudaStreamSynchronize(c->lane_stream);

@@ -593,9 +593,19 @@ struct CallScope {  // per-call bookkeeping: context lock, device, error flags, 
         if (!c) raise(VF_ERR_INVALID_ARG, "ctx is NULL");
         return c;
     }
+    bool finished = false;
     void finish() {
         flags_check(ctx);
+        finished = true;
         if (stats) stats->kernels_launched = int32_t(ctx->launches - launches0);
+    }
+    // A call that ends early (an exception on its way to the caller) still waits for what it enqueued: the
+    // caller's buffers and the context's job-table area must not be in use once the call has returned.
+    ~CallScope() {
+        if (finished) return;
+        cudaStreamSynchronize(ctx->main_stream);
+        if (ctx->lane_stream) cudaStreamSynchronize(ctx->lane_stream);
+        cudaGetLastError();
     }
 };
 

@@ -14,7 +14,20 @@ namespace {
 //   trunc(fl(fl(fl(n / (L-1)) * (qHigh - qLow)) + qLow)) == n + qmin   for all n in [0, L-1]
 // (utils/quantization.cpp:1001). True for the usual ranges (0..255, -128..127, -127..127, 0..15, -8..7) but not
 // for every range (e.g. -120..120), so it is evaluated here with the same fp32 operations.
-bool tail_is_identity(int64_t qmin, int64_t qmax) {
+bool tail_is_identity_uncached(int64_t qmin, int64_t qmax);
+
+bool tail_is_identity(int64_t qmin, int64_t qmax) {  // a batch asks the same question for every job
+    static thread_local int64_t last_min = 1, last_max = 0;
+    static thread_local bool last = false;
+    if (qmin != last_min || qmax != last_max) {
+        last = tail_is_identity_uncached(qmin, qmax);
+        last_min = qmin;
+        last_max = qmax;
+    }
+    return last;
+}
+
+bool tail_is_identity_uncached(int64_t qmin, int64_t qmax) {
     const volatile float lm1 = float(qmax - qmin + 1) - 1.0f;
     const volatile float qlow = float(qmin), qhigh = float(qmax);
     const volatile float qrange = qhigh - qlow;

@@ -747,9 +747,9 @@ void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
         t.unit_begin = total;
         total += t.oc;
     }
-    DBuf d(ctx, tabs.size() * sizeof(TableArgs));
-    copy_in(ctx, d.p, tabs.data(), tabs.size() * sizeof(TableArgs), VF_MEM_HOST);
-    k_weights_table_batch<<<int((total + 127) / 128), 128, 0, ctx->stream>>>(d.as<TableArgs>(), int(tabs.size()), total, ctx->d_flags);
+    DBuf d;
+    const TableArgs* d_tabs = static_cast<const TableArgs*>(upload_table(ctx, tabs.data(), tabs.size() * sizeof(TableArgs), d));
+    k_weights_table_batch<<<int((total + 127) / 128), 128, 0, ctx->stream>>>(d_tabs, int(tabs.size()), total, ctx->d_flags);
     post_launch(ctx);
 }
 

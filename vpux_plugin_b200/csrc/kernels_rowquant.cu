@@ -902,9 +902,9 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         max_out_row = std::max(max_out_row, a.khw > 0 ? a.khw * a.ic_pad : a.cols);
     }
     p.total_units = units;
-    DBuf table(ctx, jobs.size() * sizeof(RowQuantArgs));
-    copy_in(ctx, table.p, jobs.data(), jobs.size() * sizeof(RowQuantArgs), VF_MEM_HOST);
-    const RowQuantArgs* d_jobs = table.as<RowQuantArgs>();
+    DBuf table;
+    const RowQuantArgs* d_jobs =
+            static_cast<const RowQuantArgs*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(RowQuantArgs), table));
 
     if (kind == 1) {
         if (a0.in_dt == VF_DT_F16) launch_group_t<__half>(ctx, d_jobs, p, a0.group, a0.pack4 != 0);

@@ -324,9 +324,8 @@ void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d
                 (!j.data || a16(j.data));
         any_data |= j.data != nullptr;
     }
-    DBuf table(ctx, jobs.size() * sizeof(SparseJob));
-    copy_in(ctx, table.p, jobs.data(), jobs.size() * sizeof(SparseJob), VF_MEM_HOST);
-    const SparseJob* d_jobs = table.as<SparseJob>();
+    DBuf table;
+    const SparseJob* d_jobs = static_cast<const SparseJob*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(SparseJob), table));
     const int grid = int(std::min<int64_t>((units + kWarps - 1) / kWarps, int64_t(148) * 8));
     const int njobs = int(jobs.size());
     k_sparse_scan_batch<<<grid, kWarps * 32, 0, ctx->stream>>>(d_jobs, njobs, units);
@@ -343,9 +342,9 @@ void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d
 
 void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs) {
     if (jobs.empty()) return;
-    DBuf d(ctx, jobs.size() * sizeof(OffsetsJob));
-    copy_in(ctx, d.p, jobs.data(), jobs.size() * sizeof(OffsetsJob), VF_MEM_HOST);
-    k_offsets_batch<<<int(jobs.size()), 1024, 0, ctx->stream>>>(d.as<OffsetsJob>());
+    DBuf d;
+    const OffsetsJob* d_jobs = static_cast<const OffsetsJob*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(OffsetsJob), d));
+    k_offsets_batch<<<int(jobs.size()), 1024, 0, ctx->stream>>>(d_jobs);
     VF_CUDA(cudaGetLastError());
     ctx->launches += 1;
 }
