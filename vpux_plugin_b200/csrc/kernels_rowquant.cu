@@ -206,9 +206,12 @@ __device__ __noinline__ uint2 quant8_fix_bytes(uint4 d, float inv, float c, floa
 
 // eight patterns (kMagicBits + n) -> eight nibbles of n in one word, element 0 in the low nibble (BitPack<4>)
 __device__ __forceinline__ uint32_t pack_nibbles(const float* m) {
-    uint32_t w = __float_as_uint(m[0]);
-#pragma unroll
-    for (int i = 1; i < 8; ++i) w += __float_as_uint(m[i]) << (4 * i);
+    // summed as a tree (three dependent multiply-adds instead of seven)
+    const uint32_t a = __float_as_uint(m[0]) + (__float_as_uint(m[1]) << 4);
+    const uint32_t b = __float_as_uint(m[2]) + (__float_as_uint(m[3]) << 4);
+    const uint32_t c = __float_as_uint(m[4]) + (__float_as_uint(m[5]) << 4);
+    const uint32_t d = __float_as_uint(m[6]) + (__float_as_uint(m[7]) << 4);
+    const uint32_t w = (a + (b << 8)) + ((c + (d << 8)) << 16);
     constexpr uint32_t kC = uint32_t(kMagicBits) * 0x11111111u;  // the magic part of the sum
     return w - kC;
 }
