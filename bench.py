@@ -51,6 +51,8 @@ def parse():
     p.add_argument("--workload", default="c4")
     p.add_argument("--impl", default="b200")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--sync-calls", action="store_true",
+                   help="device-resident arm: every library call synchronises (default: pipelined calls, VF_OPT_ASYNC)")
     p.add_argument("--no-cpu", action="store_true")
     p.add_argument("--scale", type=float, default=1.0, help="fraction of the layer count (for profiling captures)")
     p.add_argument("--profile", action="store_true",
@@ -283,7 +285,9 @@ def gpu_arm(args, workload):
     dev = torch.device("cuda", local)
     stream = torch.cuda.Stream(device=dev)  # the library launches on this stream; the timing events are recorded on it
     torch.cuda.set_stream(stream)
-    lib = Library(device=local, stream=stream.cuda_stream)
+    # device-resident arm: the K steps are K batch calls enqueued back to back (VF_OPT_ASYNC), one
+    # synchronisation at the end; the end-to-end arm below moves host memory and synchronises in every call
+    lib = Library(device=local, stream=stream.cuda_stream, pipelined=not args.sync_calls)
 
     mine = shard(workload, world, rank)
     is_c4 = workload.key == "c4"
@@ -343,6 +347,7 @@ def gpu_arm(args, workload):
             fn()
         e1.record(stream)
         torch.cuda.synchronize()
+        lib.synchronize()  # raises if a kernel of the pipelined calls reported an error
         ms = e0.elapsed_time(e1)
         barrier()
         if world > 1:
@@ -457,7 +462,9 @@ def gpu_arm(args, workload):
         "data": "synthetic",
         "config": {"workload": workload.desc, "input_bytes": int(total_in_bytes), "tensors_rank0": len(mine),
                    "sharding": "whole tensors, longest-processing-time-first" if workload.shard_mode == 0 else
-                   "output-channel slabs", "l2": "inputs (GBs) far larger than the 126 MB L2; no flush needed"},
+                   "output-channel slabs", "l2": "inputs (GBs) far larger than the 126 MB L2; no flush needed",
+                   "calls": "synchronous" if args.sync_calls else "pipelined (VF_OPT_ASYNC): K batch calls enqueued back to back, "
+                   "one synchronisation after the last"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": int(launches * args.steps),
     }
     print(json.dumps(line), flush=True)

@@ -561,6 +561,46 @@ def test_weights_table_random(gpu, oracle):
     assert _status(lambda: oracle.weights_table(d3, 2)) == abi.VF_ERR_ALIGNMENT
 
 
+def test_pipelined_batches_defer_kernel_errors_to_the_next_synchronisation(oracle):
+    """VF_OPT_ASYNC: device-resident batch calls return once enqueued; results equal the synchronous ones, a
+    kernel-side failure is reported by synchronize() and does not stick to later calls."""
+    import torch
+    from vpux_plugin_b200.lib import Library
+    lib = Library(device=0, pipelined=True)
+    dev = torch.device("cuda", 0)
+    oc = 300
+    rng = np.random.default_rng(23)
+    ws = rng.uniform(1e-4, 5e-2, oc)
+
+    def job(scales):
+        d, keep = wl.weights_table_desc(oc, scales, 576)
+        tab = torch.full((oc * 4,), -1, dtype=torch.int32, device=dev)
+        jobs = (abi.WeightsTableJob * 1)()
+        jobs[0].desc, jobs[0].table = d, tab.data_ptr()
+        return jobs, tab, d, keep
+
+    good = [job(ws) for _ in range(40)]  # many calls in flight before the first synchronisation
+    for jobs, _, _, _ in good:
+        lib.weights_table_batch(jobs, out_mem_kind=abi.VF_MEM_DEVICE)
+    lib.synchronize()
+    exp = oracle.weights_table(good[0][2], oc)
+    for _, tab, _, _ in good:
+        assert np.array_equal(tab.cpu().numpy(), exp)
+    bad_scales = ws.copy()
+    bad_scales[7] = 1e9  # needs a post-shift: the kernel flags it
+    bad = job(bad_scales)
+    lib.weights_table_batch(bad[0], out_mem_kind=abi.VF_MEM_DEVICE)  # returns: nothing has been checked yet
+    assert _status(lib.synchronize) == abi.VF_ERR_RANGE
+    again = job(ws)
+    lib.weights_table_batch(again[0], out_mem_kind=abi.VF_MEM_DEVICE)
+    lib.synchronize()
+    assert np.array_equal(again[1].cpu().numpy(), exp)
+    # a call that touches host memory synchronises by itself
+    host_tab = lib.weights_table(good[0][2], oc)
+    assert np.array_equal(host_tab, exp)
+    lib.close()
+
+
 def test_weights_table_batch(gpu, oracle):
     """Many tables per call (dense and sparse pointers, with and without bias, 1..2500 channels); weight scales
     either inside the descriptor or as a separate FP64 array; one launch for all rows."""

@@ -138,6 +138,7 @@ struct vf_ctx {
     int* d_flags = nullptr;  // device error flags (see VF_FLAG_* in device_utils.cuh)
     int* h_flags = nullptr;  // pinned mirror
     bool flags_dirty = false;  // the device flags may be non-zero (a call found something or ended early)
+    bool deferred = false;     // VF_OPT_ASYNC: calls have returned whose kernels are still unchecked
     uint64_t launches = 0;
     int32_t opt_flags = 0;
     bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device

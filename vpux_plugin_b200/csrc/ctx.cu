@@ -74,6 +74,11 @@ void copy_out(vf_ctx* ctx, void* dst, int dst_kind, const void* src_dev, size_t 
 
 const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallback) {
     const size_t need = (bytes + 255) & ~size_t(255);
+    if (ctx->deferred && ctx->table_host && need <= vf_ctx::kTableBytes && ctx->table_used + need > vf_ctx::kTableBytes) {
+        // deferred calls still read their tables: wait for them before the area is reused from the start
+        VF_CUDA(cudaStreamSynchronize(ctx->stream));
+        ctx->table_used = 0;
+    }
     if (ctx->table_host && ctx->table_used + need <= vf_ctx::kTableBytes) {
         char* h = ctx->table_host + ctx->table_used;
         char* d = ctx->table_dev + ctx->table_used;
@@ -89,6 +94,7 @@ const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallb
 
 // The flags are zero unless a call found something or ended early: only then is the next call's clearing real.
 void flags_clear(vf_ctx* ctx) {
+    if (ctx->deferred) return;  // unchecked work is in flight: its flags and job tables stay as they are
     ctx->table_used = 0;  // a new call: the previous call's job tables are no longer in use
     if (ctx->flags_dirty) VF_CUDA(cudaMemsetAsync(ctx->d_flags, 0, sizeof(int) * kNumFlags, ctx->stream));
     ctx->flags_dirty = true;  // until flags_check has seen them all zero
@@ -98,10 +104,11 @@ void flags_check(vf_ctx* ctx) {
     VF_CUDA(cudaMemcpyAsync(ctx->h_flags, ctx->d_flags, sizeof(int) * kNumFlags, cudaMemcpyDeviceToHost, ctx->stream));
     VF_CUDA(cudaStreamSynchronize(ctx->stream));
     VF_CUDA(cudaGetLastError());
+    ctx->deferred = false;  // everything enqueued so far has finished and is being checked now
     const int* f = ctx->h_flags;
     bool any = false;
     for (int i = 0; i < kNumFlags; ++i) any |= f[i] != 0;
-    if (!any) ctx->flags_dirty = false;
+    ctx->flags_dirty = any;
     if (f[0]) raise(VF_ERR_CHECKED_CAST, "Can not safely cast a value to the destination element type");
     if (f[1]) raise(VF_ERR_QUANT_RANGE, "calcScaleAndZeroPoint failed: range without zero or scale too small");
     if (f[2]) raise(VF_ERR_SHAPE, "numActualElements smaller than the number of non-sparse elements");
@@ -183,8 +190,10 @@ void vf_ctx_destroy(vf_ctx* c) {
 int vf_ctx_synchronize(vf_ctx* c, char* err, size_t errlen) {
     return vf::guard(err, errlen, [&] {
         if (!c) vf::raise(VF_ERR_INVALID_ARG, "ctx is NULL");
+        std::lock_guard<std::mutex> lock(c->mu);
         vf::DeviceGuard g(c->device);
-        VF_CUDA(cudaStreamSynchronize(c->stream));
+        if (c->deferred) vf::flags_check(c);  // reports what the deferred calls' kernels found
+        else VF_CUDA(cudaStreamSynchronize(c->stream));
     });
 }
 

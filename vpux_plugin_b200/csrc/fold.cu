@@ -594,8 +594,14 @@ struct CallScope {  // per-call bookkeeping: context lock, device, error flags, 
         return c;
     }
     bool finished = false;
+    bool may_defer = false;  // set by calls that touched device memory only
     void finish() {
-        flags_check(ctx);
+        if (may_defer && (ctx->opt_flags & VF_OPT_ASYNC)) {
+            VF_CUDA(cudaGetLastError());
+            ctx->deferred = true;  // the next synchronising call reports what these kernels found
+        } else {
+            flags_check(ctx);
+        }
         finished = true;
         if (stats) stats->kernels_launched = int32_t(ctx->launches - launches0);
     }
@@ -848,6 +854,7 @@ int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats*
             VF_CUDA(cudaEventRecord(ctx->lane_ev[1], ctx->lane_stream));
             VF_CUDA(cudaStreamWaitEvent(ctx->main_stream, ctx->lane_ev[1], 0));
         }
+        scope.may_defer = !any_host;
         scope.finish();
     });
 }
@@ -1101,6 +1108,7 @@ int vf_weights_table_batch(vf_ctx* ctx, vf_weights_table_job* jobs, int njobs, i
         launch_offsets_batch(ctx, offs);
         launch_weights_table_batch(ctx, tabs);
         for (int j = 0; j < njobs; ++j) out_flush(ctx, jobs[j].table, out_mem_kind, size_t(jobs[j].desc.oc) * 16, stage[j]);
+        scope.may_defer = out_mem_kind == VF_MEM_DEVICE;
         scope.finish();
     });
 }
