@@ -490,6 +490,43 @@ def test_row_i8_with_dequant_fused(gpu, oracle, dt, rows, cols, ddt):
     _same(_quant_fold(gpu, *args), _quant_fold(oracle, *args))
 
 
+@pytest.mark.parametrize("dt", [F16, BF16])
+def test_rows_and_groups_made_of_exact_ties(gpu, oracle, dt):
+    """Every element sits exactly on a rounding boundary (x * (L-1) / range = integer + 1/2 in exact
+    arithmetic), so every vector enters the guard band: the repair lists overflow, the inline repair runs, and
+    half-away rounding must agree with the reference for each element. Rows: absmax 127 * 2^-7, values
+    (2m+1) * 2^-8. Groups of 128 (u4): min 0, max 15 * 2^-4, values (2m+1) * 2^-5."""
+    rng = np.random.default_rng(31)
+    to = (lambda a: a.astype(np.float16)) if dt == F16 else bf16_bits
+    for rows, cols in ((6, 8192), (2, 28672), (3, 2048)):
+        m = rng.integers(-60, 60, (rows, cols))
+        x = ((2 * m + 1) * 2.0 ** -8).astype(np.float32)
+        x[:, 0] = 127 * 2.0 ** -7
+        x[0, 1] = -127 * 2.0 ** -7
+        args = ((rows, cols), to(x), wl.spec_i8_sym(F16), [], rows * cols, rows)
+        _same(_quant_fold(gpu, *args, want=("scales", "zps"), dequant_dt=F16),
+              _quant_fold(oracle, *args, want=("scales", "zps"), dequant_dt=F16))
+        assert gpu.last_stats.fused == 1
+        args = ((rows, cols), to(x), wl.spec_u8_asym(), [], rows * cols, rows)
+        _same(_quant_fold(gpu, *args), _quant_fold(oracle, *args))
+    rows, cols = 8, 4096
+    m = rng.integers(0, 15, (rows, cols))
+    x = ((2 * m + 1) * 2.0 ** -5).astype(np.float32)
+    x[:, ::128] = 0.0
+    x[:, 1::128] = 15 * 2.0 ** -4
+    args = ((rows, cols), to(x), wl.spec_u4_group(128), [wl.t_bitpack()], rows * cols // 2, rows * cols // 128)
+    _same(_quant_fold(gpu, *args, want=("scales", "zps", "f16", "u4")), _quant_fold(oracle, *args, want=("scales", "zps", "f16", "u4")))
+    assert gpu.last_stats.fused == 1
+    # convolution rows through the per-channel kernels
+    shape = (16, 64, 3, 3)
+    m = rng.integers(-60, 60, shape)
+    xc = ((2 * m + 1) * 2.0 ** -8).astype(np.float32)
+    xc[:, 0, 0, 0] = 127 * 2.0 ** -7
+    ts, oshape = wl.conv_pipeline(shape)
+    args = (shape, to(xc), wl.spec_i8_sym(), ts, int(np.prod(oshape)), shape[0])
+    _same(_quant_fold(gpu, *args), _quant_fold(oracle, *args))
+
+
 @pytest.mark.parametrize("dt", [F32, F16, BF16])
 @pytest.mark.parametrize("shape,pad_oc,pad_ic", [((60, 64, 3, 3), 64, None), ((64, 3, 7, 7), None, 16),
                                                  ((16, 8, 1, 1), None, None), ((5, 3, 3, 3), 8, 4),
