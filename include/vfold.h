@@ -271,6 +271,21 @@ int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, v
             int dst_mem_kind, uint64_t* dst_written, vf_tensor_type* out_type, double* scales_buf, int64_t* zps_buf,
             int64_t params_cap, vf_stats* stats, char* err, size_t errlen);
 
+/* = FuseAttr::transform (attributes/fuse_transform.cpp:31-63): the constants of one NCE operation — weights
+ * table, weights, sparsity map, activations, in that order — are folded one after the other and laid end to
+ * end in `dst` exactly as copyTo() materialises each (1-bit maps arrive packed eight per byte). A part whose
+ * `base` is NULL is absent. `offset` / `bytes` receive where each part landed. */
+typedef struct vf_fuse_part {
+    const vf_content* base;
+    const vf_transform* t;
+    int32_t n;
+    int32_t reserved;
+    uint64_t offset; /* out */
+    uint64_t bytes;  /* out */
+} vf_fuse_part;
+int vf_fuse(vf_ctx* ctx, vf_fuse_part* parts, int nparts, void* dst, uint64_t dst_bytes, int dst_mem_kind,
+            uint64_t* dst_written, vf_stats* stats, char* err, size_t errlen);
+
 /* ------------------------------------------------------------------ */
 /* range statistics → scale / zero-point                               */
 /* ------------------------------------------------------------------ */

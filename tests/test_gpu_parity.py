@@ -318,6 +318,37 @@ def test_swizzle_constant(gpu, oracle, arch, key, dt, n):
     assert np.array_equal(np.sort(out), np.sort(padded))  # a permutation of the padded bytes
 
 
+def test_fuse_lays_the_folded_constants_end_to_end(gpu, oracle):
+    """vf_fuse = FuseAttr::transform (fuse_transform.cpp:31-63): weights table, weights, sparsity map, activations,
+    each folded and materialised like copyTo(); the map is 1-bit data packed eight per byte; absent parts skip."""
+    rng = np.random.default_rng(41)
+    oc, ic = 16, 32
+    tt = TType([oc, 1, 1, 4], I32)
+    table = rng.integers(0, 1 << 20, oc * 4).astype(np.int32)
+    wt = TType([oc, ic, 1, 1], I8)
+    w = (rng.integers(-100, 100, oc * ic) * (rng.random(oc * ic) < 0.5)).astype(np.int8)
+    q = Elem.per_axis(I8, F16, rng.uniform(0.01, 0.1, oc), np.zeros(oc, np.int64), 0, -127, 127)
+    parts = [ContentAttr(table, tt, ContentSetup(tt)),
+             ContentAttr(w, wt, ContentSetup(wt).castElemType(q).reorder(abi.ORDER_NHWC).sparsify(False)),
+             ContentAttr(w, wt, ContentSetup(wt).castElemType(q).reorder(abi.ORDER_NHWC).getSparsityMap()),
+             None]
+    cap = 1 << 16
+    fused, where = gpu.fuse(parts, cap)
+    expect, at = [], 0
+    for p, (off, size) in zip(parts, where):
+        assert off == at
+        if p is None:
+            assert size == 0
+            continue
+        b = p.fold(oracle, cap).bytes()
+        assert size == b.size
+        expect.append(b)
+        at += size
+    assert np.array_equal(fused, np.concatenate(expect))
+    assert where[2][1] == oc * 16  # 32 one-bit values per channel in rows of 128 bits
+    assert _status(lambda: gpu.fuse(parts, 100)) == abi.VF_ERR_BUFFER_TOO_SMALL
+
+
 def test_convert_elem_type_rejects_sign_changes(gpu, oracle):
     t = TType([8], abi.VF_DT_U4)
     raw = np.zeros(4, np.uint8)

@@ -130,6 +130,11 @@ class SparsifyJob(C.Structure):
                 ("status", C.c_int32), ("reserved", C.c_int32)]
 
 
+class FusePart(C.Structure):
+    _fields_ = [("base", C.POINTER(Content)), ("t", C.POINTER(Transform)), ("n", C.c_int32), ("reserved", C.c_int32),
+                ("offset", C.c_uint64), ("bytes", C.c_uint64)]
+
+
 class SynthSpec(C.Structure):
     _fields_ = [("seed", C.c_uint64), ("tensor_id", C.c_uint64), ("dtype", C.c_int32), ("reserved", C.c_int32),
                 ("sigma", C.c_float), ("outlier_mult", C.c_float), ("outlier_log2", C.c_int32),

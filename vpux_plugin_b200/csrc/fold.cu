@@ -731,6 +731,42 @@ int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, v
     });
 }
 
+int vf_fuse(vf_ctx* ctx, vf_fuse_part* parts, int nparts, void* dst, uint64_t dst_bytes, int dst_mem_kind,
+            uint64_t* dst_written, vf_stats* stats, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (nparts < 0 || (nparts > 0 && !parts) || (!dst && dst_bytes)) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        for (int p = 0; p < nparts; ++p) {
+            if (!parts[p].base) continue;
+            if ((parts[p].n > 0 && !parts[p].t) || parts[p].n < 0) raise(VF_ERR_INVALID_ARG, "part %d: NULL transformation list", p);
+            check_positions(parts[p].t, parts[p].n);
+        }
+        CallScope scope(ctx, stats);
+        uint64_t at = 0;  // FuseAttr::transform — attributes/fuse_transform.cpp:31-63
+        for (int p = 0; p < nparts; ++p) {
+            vf_fuse_part& part = parts[p];
+            part.offset = at;
+            part.bytes = 0;
+            if (!part.base) continue;  // an absent constant (no sparsity map, no activations ...)
+            DContent cur = upload_base(ctx, *part.base, stats);
+            for (int i = 0; i < part.n; ++i) {
+                DContent next = apply(ctx, cur, part.t[i]);
+                cur = std::move(next);
+            }
+            // appendContentToVector (:20-29): the part's total allocation size, checked against what is left
+            const uint64_t need = cur.type.alloc_bytes();
+            if (at + need > dst_bytes)
+                raise(VF_ERR_BUFFER_TOO_SMALL, "Overflow during fusing buffer size %llu, size after copying %llu", (unsigned long long)dst_bytes,
+                      (unsigned long long)(at + need));
+            const uint64_t w = copy_to(ctx, cur, static_cast<char*>(dst) + at, need, dst_mem_kind, stats);
+            part.bytes = w;
+            at += w;
+        }
+        if (dst_written) *dst_written = at;
+        if (stats) stats->bytes_out += at;
+        scope.finish();
+    });
+}
+
 int vf_row_stats(vf_ctx* ctx, const vf_content* base, const vf_quant_spec* spec, double* scales, int64_t* zps,
                  float* rmin, float* rmax, int64_t n_units, int out_mem_kind, char* err, size_t errlen) {
     return guard(err, errlen, [&] {

@@ -27,7 +27,7 @@ def _load():
         raise ImportError(f"{LIB_PATH} is missing: build it with `python -m vpux_plugin_b200.build` "
                           "(the package has no CPU fallback)")
     lib = C.CDLL(LIB_PATH)
-    for name in ("vf_infer_type", "vf_optimize_transforms", "vf_fold", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
+    for name in ("vf_infer_type", "vf_optimize_transforms", "vf_fold", "vf_fuse", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
                  "vf_nnz_per_oc", "vf_sparsify", "vf_sparsify_batch", "vf_weights_table", "vf_weights_table_batch", "vf_synth_fill", "vf_plan_shards",
                  "vf_ctx_create", "vf_ctx_synchronize", "vf_abi_version", "vf_ctx_device"):
         getattr(lib, name).restype = C.c_int
@@ -175,6 +175,25 @@ class Library:
                               C.c_int64(params_cap), C.byref(self.last_stats), err, C.c_size_t(512))
         self._check(st, err)
         return written.value, abi.TType.from_pod(out)
+
+    def fuse(self, attrs, dst_bytes):
+        """vf_fuse over a list of const.ContentAttr (None = absent part): returns (bytes, [(offset, size), ...])."""
+        parts = (abi.FusePart * len(attrs))()
+        keep = []
+        for p, a in zip(parts, attrs):
+            if a is None:
+                continue
+            c, k = abi.make_content(a.base_type, a.base, a.storage_dtype, a.is_splat)
+            tr, n = a.setup.transforms()
+            p.base, p.t, p.n = C.pointer(c), tr, n
+            keep += [c, k, tr]
+        dst = np.zeros(max(int(dst_bytes), 1), np.uint8)
+        written = C.c_uint64(0)
+        err = self._err()
+        st = self.lib.vf_fuse(self.ctx, parts, len(attrs), _ptr(dst), C.c_uint64(dst_bytes), abi.VF_MEM_HOST,
+                              C.byref(written), C.byref(self.last_stats), err, C.c_size_t(512))
+        self._check(st, err)
+        return dst[:written.value], [(int(p.offset), int(p.bytes)) for p in parts]
 
     def row_stats(self, content, spec, n_units):
         scales = np.zeros(n_units, np.float64)
