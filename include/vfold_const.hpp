@@ -238,6 +238,11 @@ public:
     vf_ctx* get() const {
         return _ctx;
     }
+    // Waits for the context's stream; with VF_OPT_ASYNC this is also where deferred kernel-side failures surface.
+    void synchronize() const {
+        char err[512] = {0};
+        details::check(vf_ctx_synchronize(_ctx, err, sizeof(err)), err);
+    }
 
 private:
     vf_ctx* _ctx = nullptr;

@@ -145,7 +145,8 @@ struct RowQuantArgs {
 // Launches all `jobs` (same kind, pairwise rowquant_compatible) with ONE kernel over a device job table.
 void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& jobs);
 bool rowquant_compatible(const RowQuantArgs& a, const RowQuantArgs& b);
-// 0: no fused kernel covers `a`; 1: per-group kernel; 2: long-row kernel; 3: convolution-row kernel
+// 0: no fused kernel covers `a`; 1: per-group kernel (k_group); 2: row kernel (k_row); 3: scalar convolution-row
+// kernel (k_conv); 4: vectorised convolution-row kernel (k_convv)
 int rowquant_kind(const RowQuantArgs& a);
 // derived parameters -> float16 scales and 4-bit packed zero points (either output may be NULL)
 void launch_pack_params(vf_ctx* ctx, const double* d_scales, const int64_t* d_zps, int64_t units,

@@ -857,7 +857,7 @@ void launch_row_t(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p
 
 }  // namespace
 
-// Which fused kernel covers `a`? 0 = none, 1 = group, 2 = row, 3 = conv
+// Which fused kernel covers `a`? 0 = none, 1 = group, 2 = row, 3 = conv (scalar), 4 = conv (vectorised)
 int rowquant_kind(const RowQuantArgs& a) {
     const bool two_byte = a.in_dt == VF_DT_F16 || a.in_dt == VF_DT_BF16;
     const bool aligned16 = reinterpret_cast<uintptr_t>(a.in) % 16 == 0;
