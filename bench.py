@@ -43,6 +43,28 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 NCU_TRAFFIC_BYTES_PER_ELEM = {"c4": 2.476, "c5slab": 4.853, "c2": None, "c3": None, "c1": None}
 
 
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keeps the process's stdout for the one JSON line: file descriptor 1 is pointed at stderr for everything
+    else (NCCL prints its version banner on stdout whatever NCCL_DEBUG_FILE says)."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def parse():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -261,7 +283,7 @@ def reference_arm(args, workload):
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU port of the reference's fold code (the reference itself needs MLIR/OpenVINO and cannot be built here)",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -278,8 +300,6 @@ def gpu_arm(args, workload):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL writes its version banner and warnings to stdout by default; stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -467,7 +487,7 @@ def gpu_arm(args, workload):
                    "one synchronisation after the last"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": int(launches * args.steps),
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -607,11 +627,12 @@ def conv_arm(args, workload):
     }
     if stage is not None:
         line["stage"] = stage
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main():
     args = parse()
+    claim_stdout()
     workload = Workload(args.workload, args.scale)
     if args.impl == "reference":
         reference_arm(args, workload)
