@@ -161,13 +161,31 @@ typedef enum vf_transform_kind {
     VF_T_GET_SPARSITY_MAP = 14, /* #const.GetSparsityMap   get_sparsity_map.cpp:82-119              */
     VF_T_SPARSIFY = 15,         /* #const.Sparsify         sparsify.cpp:163-203 (compress, counts)  */
     VF_T_SUBVIEW = 16,          /* #const.SubView          subview.cpp:390-432 (a = offset, b = shape) */
-    VF_T_SWIZZLE_CONSTANT = 17  /* #const.SwizzleConstant  swizzle_transform.cpp:163-215
+    VF_T_SWIZZLE_CONSTANT = 17, /* #const.SwizzleConstant  swizzle_transform.cpp:163-215
                                    (a[0] = swizzle key 0..5, a[1] = arch: VF_ARCH_NPU37XX / VF_ARCH_NPU40XX) */
+    VF_T_RELOCATE_WEIGHTS_TABLE = 18 /* #const.RelocateWeightsTable relocate_weights_table.cpp:203-292 (relocate) */
 } vf_transform_kind;
 
 /* VPU::ArchKind values SwizzleConstant carries (VPU/attributes.td:47-50) */
 #define VF_ARCH_NPU37XX 3
 #define VF_ARCH_NPU40XX 4
+
+/* Parameters of #const.RelocateWeightsTable (const/attributes.td:697-748). Entry c of `weights_ptr` and of
+ * `offsets` describes cluster c: the base address of its weights and the first channel it owns. */
+#define VF_MAX_CLUSTERS 8
+typedef struct vf_relocate {
+    int32_t n_clusters;                   /* 1 .. VF_MAX_CLUSTERS */
+    int32_t sparsity_ptr;                 /* sparsityPtr */
+    int32_t weights_ptr[VF_MAX_CLUSTERS]; /* weightsPtr */
+    int64_t offsets[VF_MAX_CLUSTERS];     /* offsets (channels) */
+    int64_t weights_table_size;           /* weightsTableSize, bytes: the first size / 16 rows are patched */
+    int64_t weights_elem_bit_size;        /* weightsElemBitSize; 0 = absent */
+    const int64_t* num_elems;             /* weightsCompression numElems per channel (host), NULL = no compression */
+    int64_t n_num_elems;
+    int64_t compression_axis;             /* weightsCompression axis (only the optimiser reads it) */
+    int64_t alignment;                    /* weightsCompression alignment; 0 = VPU_WEIGHT_SET_BYTE_ALIGNMENT (16) */
+    int64_t channel_offset;               /* channelOffset; 0 = absent */
+} vf_relocate;
 
 typedef struct vf_transform {
     int32_t kind;              /* vf_transform_kind */
@@ -182,6 +200,7 @@ typedef struct vf_transform {
     int32_t compress_output;   /* Sparsify<compressOutputType> */
     const int64_t* num_actual; /* Sparsify: optional numActualElements (host), else NULL */
     int64_t n_num_actual;
+    vf_relocate relocate;      /* RelocateWeightsTable */
 } vf_transform;
 
 /* ------------------------------------------------------------------ */

@@ -405,6 +405,38 @@ public:
         it->t.a[1] = int64_t(arch);
         return append(std::move(it));
     }
+    // VPUIP::SparsityCompressionAttr as RelocateWeightsTable reads it (alignment 0 = the 16-byte default)
+    struct SparsityCompression {
+        int64_t axis = 0;
+        std::vector<int64_t> numElems;
+        int64_t alignment = 0;
+    };
+    // content_setup.cpp:82-92
+    ContentSetup relocateWeightsTablePointers(const std::vector<uint32_t>& weightsPtr, uint64_t sparsityPtr,
+                                              const std::vector<int64_t>& offsets, uint64_t weightsTableSize,
+                                              uint64_t weightsElemBitSize = 0, const SparsityCompression* weightsCompression = nullptr,
+                                              uint64_t channelOffset = 0) const {
+        if (weightsPtr.size() != offsets.size() || offsets.empty() || offsets.size() > VF_MAX_CLUSTERS)
+            throw Exception(VF_ERR_INVALID_ARG, "weightsPtr and offsets need one entry per cluster");
+        auto it = make(VF_T_RELOCATE_WEIGHTS_TABLE);
+        vf_relocate& r = it->t.relocate;
+        r.n_clusters = int32_t(offsets.size());
+        r.sparsity_ptr = int32_t(sparsityPtr);
+        for (size_t i = 0; i < offsets.size(); ++i) {
+            r.weights_ptr[i] = int32_t(weightsPtr[i]);
+            r.offsets[i] = offsets[i];
+        }
+        r.weights_table_size = int64_t(weightsTableSize);
+        r.weights_elem_bit_size = int64_t(weightsElemBitSize);
+        r.channel_offset = int64_t(channelOffset);
+        if (weightsCompression) {
+            it->numElems = weightsCompression->numElems;
+            it->hasCompression = true;
+            r.compression_axis = weightsCompression->axis;
+            r.alignment = weightsCompression->alignment;
+        }
+        return append(std::move(it));
+    }
     ContentSetup getSparsityMap() const { return append(make(VF_T_GET_SPARSITY_MAP)); }
     ContentSetup sparsify(bool compressOutputType, const std::vector<int64_t>& numActualElements = {}) const {
         auto it = make(VF_T_SPARSIFY);
@@ -436,6 +468,10 @@ public:
             const int k = it->t.kind;
             if (k == VF_T_CAST_ELEM_TYPE || k == VF_T_CONVERT_ELEM_TYPE || k == VF_T_QUANTIZE) it->elem = ElemType::fromPod(it->t.elem);
             if (it->t.num_actual) it->counts.assign(it->t.num_actual, it->t.num_actual + it->t.n_num_actual);
+            if (k == VF_T_RELOCATE_WEIGHTS_TABLE && it->t.relocate.num_elems) {
+                it->numElems.assign(it->t.relocate.num_elems, it->t.relocate.num_elems + it->t.relocate.n_num_elems);
+                it->hasCompression = true;
+            }
             res._items.push_back(std::move(it));
         }
         return res;
@@ -456,6 +492,9 @@ public:
             t.elem = it->elem.pod();
             t.num_actual = it->counts.empty() ? nullptr : it->counts.data();
             t.n_num_actual = int64_t(it->counts.size());
+            static const int64_t kNone = 0;  // an empty numElems list is still "compressed"
+            t.relocate.num_elems = !it->hasCompression ? nullptr : it->numElems.empty() ? &kNone : it->numElems.data();
+            t.relocate.n_num_elems = it->hasCompression ? int64_t(it->numElems.size()) : 0;
             v.push_back(t);
         }
         return v;
@@ -466,6 +505,8 @@ private:
         vf_transform t{};
         ElemType elem;
         std::vector<int64_t> counts;
+        std::vector<int64_t> numElems;  // RelocateWeightsTable weightsCompression
+        bool hasCompression = false;
     };
     static int position(int kind) {  // 0 = NONE, 1 = PREFERRED_LAST, 2 = LAST
         if (kind == VF_T_BIT_PACK || kind == VF_T_SWIZZLE_CONSTANT) return 2;

@@ -789,6 +789,16 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
         out_splat = false;
         break;
     }
+    case VF_T_RELOCATE_WEIGHTS_TABLE: {  // relocate_weights_table.cpp:194-200
+        const vf_relocate& r = t.relocate;
+        if (r.n_clusters < 1 || r.n_clusters > VF_MAX_CLUSTERS) fail(VF_ERR_INVALID_ARG, "RelocateWeightsTable with %d clusters", r.n_clusters);
+        if (in.elem.quantized() || dtype_bits(in.elem.dtype) != 32 || dtype_is_float(in.elem.dtype))
+            fail(VF_ERR_UNSUPPORTED, "RelocateWeightsTable patches tables of 32-bit integers");
+        if (r.weights_table_size < 0 || r.weights_table_size / 4 > in.numel())
+            fail(VF_ERR_SHAPE, "weightsTableSize %lld exceeds the constant", (long long)r.weights_table_size);
+        out_splat = in_splat;
+        break;
+    }
     default:
         fail(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
@@ -1373,6 +1383,72 @@ Content tf_swizzle(const Content& in, const vf_transform& t) {
     return out;
 }
 
+// RelocateWeightsTableAttr::transform — CD/attributes/relocate_weights_table.cpp:203-292
+Content tf_relocate(const Content& in, const vf_transform& t) {
+    bool osplat;
+    const Type outType = infer_one(in.type, in.splat, t, osplat);
+    const vf_relocate& r = t.relocate;
+    Content out = Content::alloc(outType, outType.elem.dtype, false);
+    copy_to(in, out.mdata(), type_bytes(in.type));  // a splat is filled in (:211-213), anything else is copied
+    int32_t* values = reinterpret_cast<int32_t*>(out.mdata());
+    const int64_t entries = r.weights_table_size / 4;
+    const int64_t perOC = 4;  // WEIGHT_TABLE_NUM_ELEMENTS_PER_OC
+    uint32_t weightStep = 0, sparsityStep = 0;  // int32 in the reference; unsigned here so that overflow wraps
+    if (entries >= 2 * perOC) {
+        weightStep = uint32_t(values[perOC]) - uint32_t(values[0]);
+        sparsityStep = uint32_t(values[perOC + 1]) - uint32_t(values[1]);
+    }
+    if (r.channel_offset < INT32_MIN || r.channel_offset > INT32_MAX) fail(VF_ERR_CHECKED_CAST, "channelOffset outside int32");
+    const uint32_t chanOff = uint32_t(int32_t(r.channel_offset));
+    uint32_t weightsPtrOffset = chanOff * weightStep;
+    const uint32_t sparsityPtrOffset = chanOff * sparsityStep;
+    const int64_t OC = entries / perOC;
+    bool segmented = false;
+    for (int c = 1; c < r.n_clusters; ++c) segmented = segmented || r.offsets[c] != r.offsets[c - 1];
+    auto new_cluster = [&](int64_t oc, int cl) { return segmented && cl + 1 < r.n_clusters && oc >= r.offsets[cl + 1]; };
+    std::vector<int64_t> ptrSteps(size_t(std::max<int64_t>(OC, 0)));
+    if (r.num_elems) {
+        if (r.channel_offset < 0 || r.n_num_elems < OC + r.channel_offset)
+            fail(VF_ERR_SHAPE, "Invalid weights compression with %lld elements for %lld channels", (long long)r.n_num_elems, (long long)OC);
+        if (r.weights_elem_bit_size <= 0) fail(VF_ERR_INVALID_ARG, "Missing weights element type attribute");
+        const int64_t alignment = r.alignment ? r.alignment : 16;  // VPU_WEIGHT_SET_BYTE_ALIGNMENT
+        if (alignment < 0) fail(VF_ERR_INVALID_ARG, "negative weightsCompression alignment");
+        auto setBytes = [&](int64_t oc) { return align_up((r.num_elems[oc] * r.weights_elem_bit_size + 7) / 8, alignment); };
+        int64_t sliced = 0;
+        for (int64_t oc = 0; oc < r.channel_offset; ++oc) sliced += setBytes(oc);
+        weightsPtrOffset = uint32_t(sliced);
+        int64_t ptrOffset = 0;
+        int cl = 0;
+        for (int64_t oc = 0; oc < OC; ++oc) {
+            if (new_cluster(oc, cl)) {
+                ++cl;
+                ptrOffset = 0;
+            }
+            ptrSteps[size_t(oc)] = ptrOffset;
+            ptrOffset += setBytes(oc + r.channel_offset);
+        }
+    } else {
+        int cl = 0;
+        for (int64_t oc = 0; oc < OC; ++oc) {
+            if (new_cluster(oc, cl)) ++cl;
+            ptrSteps[size_t(oc)] = int64_t(int32_t(weightStep)) * (oc - r.offsets[cl]);
+        }
+    }
+    int cl = 0;
+    for (int64_t oc = 0; oc < OC; ++oc) {
+        if (new_cluster(oc, cl)) ++cl;
+        const int64_t w = int64_t(r.weights_ptr[cl]) + ptrSteps[size_t(oc)];
+        if (w < INT32_MIN || w > INT32_MAX) fail(VF_ERR_CHECKED_CAST, "weights pointer %lld outside int32", (long long)w);
+        values[oc * perOC] = int32_t(uint32_t(w) + weightsPtrOffset);
+        if (values[oc * perOC + 1] != 0xFFFFFF) {  // SPARSITY_PTR_WHEN_NO_SPARSITY (nce_sparsity.hpp:34)
+            const int64_t sp = int64_t(r.sparsity_ptr) + (oc - r.offsets[cl]) * int64_t(int32_t(sparsityStep));
+            if (sp < INT32_MIN || sp > INT32_MAX) fail(VF_ERR_CHECKED_CAST, "sparsity pointer %lld outside int32", (long long)sp);
+            values[oc * perOC + 1] = int32_t(uint32_t(sp) + sparsityPtrOffset);
+        }
+    }
+    return out;
+}
+
 Content apply(Content& in, const vf_transform& t, int nthreads) {
     bool osplat;
     switch (t.kind) {
@@ -1396,6 +1472,7 @@ Content apply(Content& in, const vf_transform& t, int nthreads) {
     case VF_T_GET_SPARSITY_MAP: return tf_sparsity_map(in, t);
     case VF_T_SPARSIFY: return tf_sparsify(in, t, nthreads);
     case VF_T_SWIZZLE_CONSTANT: return tf_swizzle(in, t);
+    case VF_T_RELOCATE_WEIGHTS_TABLE: return tf_relocate(in, t);
     default: fail(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }

@@ -101,6 +101,20 @@ static void optimizedLists() {
     auto sliced = Const::ContentSetup(u8).castElemType(perAxis).subview({0, 1, 1}, {1, 2, 1}).optimize();
     EXPECT((sliced.getTransformationKinds() == std::vector<int>{VF_T_SUBVIEW, VF_T_CAST_ELEM_TYPE}));
     EXPECT(sliced.at(1).elem.nparams == 1 && sliced.at(1).elem.scales[0] == 2.0);
+    // content_setup.cpp:1644-1648: a SubView of one cluster moves before RelocateWeightsTable, which keeps that
+    // cluster's pointer and the slice of the compression entries
+    const TensorType table({8, 1, 1, 4}, VF_DT_I32);
+    Const::ContentSetup::SparsityCompression comp;
+    comp.numElems = {1, 2, 3, 4, 5, 6, 7, 8};
+    comp.alignment = 16;
+    auto relocated = Const::ContentSetup(table)
+                             .relocateWeightsTablePointers({100, 200, 300, 400}, 200, {0, 2, 4, 6}, 128, 16, &comp, 0)
+                             .subview({4, 0, 0, 0}, {2, 1, 1, 4})
+                             .optimize();
+    EXPECT((relocated.getTransformationKinds() == std::vector<int>{VF_T_SUBVIEW, VF_T_RELOCATE_WEIGHTS_TABLE}));
+    const vf_relocate r = relocated.at(1).relocate;
+    EXPECT(r.n_clusters == 1 && r.weights_ptr[0] == 300 && r.offsets[0] == 0 && r.weights_table_size == 32 && r.channel_offset == 0);
+    EXPECT(r.n_num_elems == 2 && r.num_elems[0] == 5 && r.num_elems[1] == 6);
 }
 
 // ---- folding on the GPU ------------------------------------------------------------------------------------
@@ -192,6 +206,17 @@ static void dequantizeQuantize(const Context& ctx) {  // UT:2512-2540: the chain
     for (int i = 0; i < 16; ++i) EXPECT(got[size_t(i)] == vals[size_t(i)]);
 }
 
+static void relocateWeightsTable(const Context& ctx) {  // lit const/passes/constant_folding.mlir:597-611
+    const TensorType baseType({4, 1, 1, 4}, VF_DT_I32);
+    const std::vector<int32_t> vals = {1, 2, 3, 3, 2, 4, 4, 4, 3, 6, 5, 5, 4, 8, 6, 6};
+    const auto content = Const::ContentSetup(baseType)
+                                 .relocateWeightsTablePointers({10, 20}, 5, {0, 2}, 64, 16)
+                                 .get(vals.data(), bytesOf(vals))
+                                 .fold(ctx);
+    const std::vector<int32_t> expected = {10, 5, 3, 3, 11, 7, 4, 4, 20, 5, 5, 5, 21, 7, 6, 6};
+    EXPECT(content.getValues<int32_t>() == expected);
+}
+
 static void copyToTooSmall(const Context& ctx) {  // utils/content.cpp:172-174
     const TensorType baseType({4}, VF_DT_F32);
     const auto vals = generateValues<float>(4);
@@ -221,6 +246,7 @@ int main(int argc, char** argv) {
             getSparsityMap(ctx);
             sparsifyQuantized(ctx);
             dequantizeQuantize(ctx);
+            relocateWeightsTable(ctx);
             copyToTooSmall(ctx);
         } catch (const Exception& e) {
             std::printf("unexpected vfold::Exception %d: %s\n", e.status(), e.what());

@@ -388,6 +388,49 @@ def swizzle_constant(be):
     assert o.bytes().tolist() == [7] * 512
 
 
+def relocate_weights_table(be):
+    """lit dialect/const/passes/constant_folding.mlir:566-625 (Relocate*): columns 0 / 1 of each table row are
+    rebased on the cluster's weights pointer and the sparsity pointer; the steps between channels come from
+    the first two rows; a table inside a larger fused constant is patched over weightsTableSize bytes only;
+    with weightsCompression the weights pointers follow the aligned compressed set sizes."""
+    I32 = abi.VF_DT_I32
+
+    def run(vals, shape, setup_fn, splat=False):
+        t = TType(shape, I32)
+        out = ContentAttr(np.asarray(vals, np.int32), t, setup_fn(ContentSetup(t)), is_splat=splat).fold(be)
+        return out.values(np.int32).tolist()
+
+    five = [1, 2, 3, 3, 2, 4, 4, 4, 3, 6, 5, 5, 4, 8, 6, 6, 5, 10, 7, 7]
+    # :566-581 single cluster, and the same table sliced first (channelOffset = 2)
+    assert run(five, [5, 1, 1, 4], lambda s: s.relocateWeightsTablePointers([10], 15, [0], 80, 16)) == \
+        [10, 15, 3, 3, 11, 17, 4, 4, 12, 19, 5, 5, 13, 21, 6, 6, 14, 23, 7, 7]
+    assert run(five, [5, 1, 1, 4], lambda s: s.subview([2, 0, 0, 0], [2, 1, 1, 4]).relocateWeightsTablePointers(
+        [10], 15, [0], 32, 16, channel_offset=2)) == [12, 19, 5, 5, 13, 21, 6, 6]
+    # :585-593 a table of 3 rows at the front of a fused constant
+    fused = [1, 2, 1, 2, 2, 4, 2, 3, 3, 6, 4, 5, 0, 0, 0, 0]
+    assert run(fused, [1, 1, 1, 16], lambda s: s.relocateWeightsTablePointers([10], 15, [0], 48, 16)) == \
+        [10, 15, 1, 2, 11, 17, 2, 3, 12, 19, 4, 5, 0, 0, 0, 0]
+    # :597-611 two clusters of two channels
+    four = five[:16]
+    assert run(four, [4, 1, 1, 4], lambda s: s.relocateWeightsTablePointers([10, 20], 5, [0, 2], 64, 16)) == \
+        [10, 5, 3, 3, 11, 7, 4, 4, 20, 5, 5, 5, 21, 7, 6, 6]
+    assert run(four, [4, 1, 1, 4], lambda s: s.subview([2, 0, 0, 0], [2, 1, 1, 4]).relocateWeightsTablePointers(
+        [20], 5, [0], 32, 16, channel_offset=0)) == [20, 5, 5, 5, 21, 7, 6, 6]
+    # :615-624 compressed weights: 24 fp16 elements per channel = 48 bytes, five channels sliced away in front
+    sparse = [1, 2, 3, 3, 21, 4, 4, 4, 41, 6, 5, 5, 61, 8, 6, 6, 81, 10, 7, 7]
+    comp = {"axis": 0, "numElems": [24] * 10, "alignment": 16}
+    assert run(sparse, [5, 1, 1, 4], lambda s: s.relocateWeightsTablePointers(
+        [10], 15, [0], 80, 16, weights_compression=comp, channel_offset=5)) == \
+        [250, 25, 3, 3, 298, 27, 4, 4, 346, 29, 5, 5, 394, 31, 6, 6, 442, 33, 7, 7]
+    # a row whose sparsity pointer says "no sparsity" keeps it (relocate_weights_table.cpp:286-289)
+    nosp = [0, 0xFFFFFF, 9, 9, 16, 0xFFFFFF, 9, 9]
+    assert run(nosp, [2, 1, 1, 4], lambda s: s.relocateWeightsTablePointers([100], 7, [0], 32, 16)) == \
+        [100, 0xFFFFFF, 9, 9, 116, 0xFFFFFF, 9, 9]
+    # a splat table is filled in first (:207-214): equal rows, so both steps are zero
+    assert run([3], [2, 1, 1, 4], lambda s: s.relocateWeightsTablePointers([100], 7, [0], 32, 16), splat=True) == \
+        [100, 7, 3, 3, 100, 7, 3, 3]
+
+
 def sparsity_ptr_stepping(be):
     """lit dialect/VPU/passes/recompute_sparsity_ptrs.mlir:12-31: a 16x16x4x4 filter has sparsity-map rows of
     align(256, 128) / 8 = 32 bytes (map type 16x1x1x256xi1), so the sparsity pointers step by 32"""
@@ -405,5 +448,5 @@ FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequ
               pad_uniform_quant, pad_per_axis_quant, bit_pack, bit_pack_quant, get_sparsity_map,
               get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
               convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain, copy_to_i4,
-              copy_to_i1, convert_elem_type_sub_byte, swizzle_constant]
+              copy_to_i1, convert_elem_type_sub_byte, swizzle_constant, relocate_weights_table]
 TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale, sparsity_ptr_stepping]

@@ -700,3 +700,69 @@ def test_weights_table_batch(gpu, oracle):
     # an invalid job ends the call and is marked
     jobs[2].desc.weights_ptr_step = 24
     assert _status(lambda: gpu.weights_table_batch(jobs)) == abi.VF_ERR_ALIGNMENT
+
+
+# ---------------------------------------------------------------------------------------------------------
+# RelocateWeightsTable (relocate_weights_table.cpp:203-292)
+def _relocate_case(rng, oc, n_cl, compressed, chan, tail=0):
+    tab = np.zeros((oc + tail, 4), np.int32)
+    tab[:oc, 0] = np.arange(oc) * (int(rng.integers(1, 512)) * 16)
+    no_sparsity = (rng.integers(0, 8, oc) == 0) & (np.arange(oc) >= 2)  # rows 0 and 1 give the pointer steps
+    tab[:oc, 1] = np.where(no_sparsity, 0xFFFFFF, np.arange(oc) * int(rng.integers(0, 64)))
+    tab[:, 2:] = rng.integers(-(1 << 31), 1 << 31, (oc + tail, 2), dtype=np.int64).astype(np.int32)
+    bounds = sorted(int(v) for v in rng.choice(np.arange(1, oc), n_cl - 1, replace=False)) if n_cl > 1 else []
+    offs = [0] + bounds
+    comp = None
+    if compressed:
+        comp = {"axis": 0, "numElems": rng.integers(0, 5000, oc + chan), "alignment": int(rng.choice([0, 16, 32]))}
+    t = TType([oc + tail, 1, 1, 4], abi.VF_DT_I32)
+    s = ContentSetup(t).relocateWeightsTablePointers([int(v) for v in rng.integers(0, 1 << 22, n_cl)],
+                                                     int(rng.integers(0, 1 << 22)), offs, oc * 16,
+                                                     int(rng.choice([4, 8, 16])), comp, chan)
+    return ContentAttr(tab, t, s)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("oc,n_cl,compressed,chan,tail", [
+    (1, 1, False, 0, 0), (2, 1, False, 3, 0), (64, 2, False, 0, 0), (64, 4, True, 0, 0), (1000, 8, True, 0, 3),
+    (4096, 6, False, 0, 0), (4096, 1, True, 17, 0), (8192, 8, True, 0, 1)])
+def test_relocate_weights_table(gpu, oracle, oc, n_cl, compressed, chan, tail):
+    rng = np.random.default_rng(oc * 31 + n_cl)
+    both(_relocate_case(rng, oc, n_cl, compressed, chan, tail), gpu, oracle)
+
+
+@pytest.mark.gpu
+def test_relocate_weights_table_cluster_walk(gpu, oracle):
+    """Cluster offsets that repeat or go backwards: the reference moves on by one cluster per channel at most."""
+    rng = np.random.default_rng(5)
+    tab = np.zeros((12, 4), np.int32)
+    tab[:, 0] = np.arange(12) * 32
+    tab[:, 1] = np.arange(12) * 4
+    t = TType([12, 1, 1, 4], abi.VF_DT_I32)
+    for offs in ([0, 0, 5], [0, 3, 3, 3], [0, 7, 2], [4, 0, 6], [0, 20], [0, 1, 2, 3, 4, 5, 6, 7]):
+        ptrs = [int(v) for v in rng.integers(0, 1 << 20, len(offs))]
+        both(ContentAttr(tab, t, ContentSetup(t).relocateWeightsTablePointers(ptrs, 9, offs, 12 * 16, 16)), gpu, oracle)
+
+
+@pytest.mark.gpu
+def test_relocate_weights_table_errors(gpu, oracle):
+    from vpux_plugin_b200.lib import VfoldError
+    t = TType([4, 1, 1, 4], abi.VF_DT_I32)
+    tab = np.zeros((4, 4), np.int32)
+    tab[:, 0] = np.arange(4) * (1 << 29)  # weightsPtr + 3 steps leaves int32: checked_cast throws
+    s = ContentSetup(t).relocateWeightsTablePointers([1 << 30], 0, [0], 64, 16)
+    for be in (gpu, oracle):
+        with pytest.raises(Exception) as e:
+            ContentAttr(tab, t, s).fold(be)
+        assert e.value.status == abi.VF_ERR_CHECKED_CAST
+    with pytest.raises(VfoldError) as e:  # too few numElems for the channels
+        ContentAttr(tab, t, ContentSetup(t).relocateWeightsTablePointers(
+            [0], 0, [0], 64, 16, {"numElems": [1, 2, 3]})).fold(gpu)
+    assert e.value.status == abi.VF_ERR_SHAPE
+    with pytest.raises(VfoldError) as e:  # a table larger than the constant
+        ContentAttr(tab, t, ContentSetup(t).relocateWeightsTablePointers([0], 0, [0], 80, 16)).fold(gpu)
+    assert e.value.status == abi.VF_ERR_SHAPE
+    f = TType([4, 1, 1, 4], F32)
+    with pytest.raises(VfoldError) as e:  # not a table of 32-bit integers
+        ContentAttr(tab.astype(np.float32), f, ContentSetup(f).relocateWeightsTablePointers([0], 0, [0], 64, 16)).fold(gpu)
+    assert e.value.status == abi.VF_ERR_UNSUPPORTED

@@ -39,6 +39,11 @@ def _items(setup):
             n = e.nparams if e.kind != K.VF_ELEM_PLAIN else 0
             out.append(("cast" if k == K.VF_T_CAST_ELEM_TYPE else "convert", e.kind, e.dtype,
                         [e.scales[i] for i in range(n)], [e.zps[i] for i in range(n)]))
+        elif k == K.VF_T_RELOCATE_WEIGHTS_TABLE:
+            r = t.relocate
+            out.append(("relocate", list(r.weights_ptr[:r.n_clusters]), r.sparsity_ptr, list(r.offsets[:r.n_clusters]),
+                        r.weights_table_size, r.channel_offset,
+                        [r.num_elems[i] for i in range(r.n_num_elems)] if r.num_elems else None))
         else:
             out.append((k,))
     return out
@@ -133,6 +138,89 @@ def test_swap_reshape_and_subview(base, reshape, off, shp, exp_reshape, exp_off,
     ([1, 16, 1, 8], [128, 1], [0, 0], [64, 1]), ([1, 16, 48, 1], [1, 16, 12, 4], [0, 0, 9, 0], [1, 16, 3, 4])])
 def test_do_not_swap_reshape_and_subview(base, reshape, off, shp):
     assert _items(S(base).reshape(reshape).subview(off, shp).optimized()) == [("reshape", reshape), ("subview", off, shp)]
+
+
+def _comp(num_elems):
+    return None if num_elems is None else {"axis": 0, "numElems": num_elems, "alignment": 16}
+
+
+# CS:1621-1648 swapRelocateWeightsTableAndSubView: (base shape, SubView, Relocate in, Relocate expected), a Relocate
+# given as (weightsPtr, sparsityPtr, offsets, weightsTableSize, channelOffset, numElems)
+RELOCATE_SWAPS = [
+    ([4, 1, 1, 4], ([0, 0, 0, 0], [2, 1, 1, 4]), ([100], 16777215, [0], 64, 0, None), ([100], 16777215, [0], 32, 0, None)),
+    ([4, 1, 1, 4], ([1, 0, 0, 0], [2, 1, 1, 4]), ([100], 16777215, [0], 64, 0, None), ([100], 16777215, [0], 32, 1, None)),
+    ([4, 1, 1, 4], ([2, 0, 0, 0], [2, 1, 1, 4]), ([100], 200, [0], 64, 0, [1, 2, 3, 4]), ([100], 200, [0], 32, 2, [1, 2, 3, 4])),
+    ([4, 1, 1, 4], ([2, 0, 0, 0], [2, 1, 1, 4]), ([100], 200, [0], 64, 2, [1, 2, 3, 4]), ([100], 200, [0], 32, 4, [1, 2, 3, 4])),
+    ([8, 1, 1, 4], ([4, 0, 0, 0], [2, 1, 1, 4]), ([100, 200, 300, 400], 16777215, [0, 2, 4, 6], 128, 0, None),
+     ([300], 16777215, [0], 32, 0, None)),
+    ([8, 1, 1, 4], ([4, 0, 0, 0], [2, 1, 1, 4]), ([100, 200, 300, 400], 200, [0, 2, 4, 6], 128, 0, [1, 2, 3, 4, 5, 6, 7, 8]),
+     ([300], 200, [0], 32, 0, [5, 6])),
+]
+
+
+def _relocate(s, p):
+    wp, sp, offs, size, chan, ne = p
+    return s.relocateWeightsTablePointers(wp, sp, offs, size, 16, _comp(ne), chan)
+
+
+@pytest.mark.parametrize("base,sub,rin,rexp", RELOCATE_SWAPS)
+def test_swap_relocate_weights_table_and_subview(base, sub, rin, rexp):
+    got = _items(_relocate(S(base, abi.VF_DT_I32), rin).subview(*sub).optimized())
+    assert got == [("subview", sub[0], sub[1]), ("relocate",) + tuple(rexp)]
+
+
+def test_do_not_swap_relocate_weights_table_and_subview():
+    # CS:1655-1685: a slice that starts inside a cluster stays behind the Relocate
+    rin = ([100, 200, 300, 400], 16777215, [0, 2, 4, 6], 128, 0, None)
+    got = _items(_relocate(S([8, 1, 1, 4], abi.VF_DT_I32), rin).subview([3, 0, 0, 0], [2, 1, 1, 4]).optimized())
+    assert got == [("relocate",) + tuple(rin), ("subview", [3, 0, 0, 0], [2, 1, 1, 4])]
+    # transformations.cpp:166-170, 175-188: one channel, or a slice of another dim, is not swapped either
+    rin = ([100], 7, [0], 64, 0, None)
+    for sub in (([1, 0, 0, 0], [1, 1, 1, 4]), ([0, 0, 0, 1], [2, 1, 1, 2])):
+        got = _items(_relocate(S([4, 1, 1, 4], abi.VF_DT_I32), rin).subview(*sub).optimized())
+        assert got == [("relocate",) + tuple(rin), ("subview", sub[0], sub[1])]
+
+
+def _relocate_fold_pair(be, seed, n=60):
+    """Relocate then SubView folds to the same table as the rewritten SubView then Relocate."""
+    rng = np.random.default_rng(seed)
+    swapped = 0
+    for _ in range(n):
+        n_cl = int(rng.integers(1, 4))
+        per = int(rng.integers(2, 5))
+        oc = n_cl * per
+        wstep, sstep = int(rng.integers(1, 64)) * 16, int(rng.integers(0, 9))
+        tab = np.zeros((oc, 4), np.int32)
+        tab[:, 0] = np.arange(oc) * wstep
+        tab[:, 1] = np.arange(oc) * sstep if sstep else 0xFFFFFF
+        tab[:, 2:] = rng.integers(-1000, 1000, (oc, 2))
+        segmented = n_cl > 1 and rng.integers(0, 2) == 1
+        offs = [c * per for c in range(n_cl)] if segmented else [0] * n_cl
+        ne = [int(v) for v in rng.integers(1, 200, oc)] if rng.integers(0, 2) else None
+        rin = ([int(v) for v in rng.integers(0, 1 << 20, n_cl)], int(rng.integers(0, 1 << 20)), offs, oc * 16, 0, ne)
+        if segmented and rng.integers(0, 4):
+            c = int(rng.integers(0, n_cl))
+            sub = ([c * per, 0, 0, 0], [per, 1, 1, 4])
+        else:
+            lo = int(rng.integers(0, oc - 1))
+            sub = ([lo, 0, 0, 0], [int(rng.integers(1, oc - lo + 1)), 1, 1, 4])
+        t = TType([oc, 1, 1, 4], abi.VF_DT_I32)
+        s = _relocate(ContentSetup(t), rin).subview(*sub)
+        so = s.optimized()
+        a = ContentAttr(tab, t, s).fold(be)
+        b = ContentAttr(tab, t, so).fold(be)
+        assert a.type == b.type and np.array_equal(a.bytes(), b.bytes()), (rin, sub)
+        swapped += so.names()[0] == K.VF_T_SUBVIEW
+    assert swapped > n // 4
+
+
+def test_relocate_swap_folds_to_the_same_table_on_the_oracle(oracle):
+    _relocate_fold_pair(oracle, 31)
+
+
+@pytest.mark.gpu
+def test_relocate_swap_folds_to_the_same_table_on_the_gpu(gpu):
+    _relocate_fold_pair(gpu, 32)
 
 
 def test_move_reshape_before_and_chains():

@@ -50,7 +50,7 @@ VF_MEM_HOST, VF_MEM_HOST_PINNED, VF_MEM_DEVICE = 0, 1, 2
 
 (VF_T_CAST_ELEM_TYPE, VF_T_CONVERT_ELEM_TYPE, VF_T_DEQUANTIZE, VF_T_QUANTIZE, VF_T_RESCALE, VF_T_ADD, VF_T_RESHAPE,
  VF_T_REORDER, VF_T_MEM_PERMUTE, VF_T_TRANSPOSE, VF_T_LAYOUT_CAST, VF_T_PAD_WITH_ZERO, VF_T_BIT_PACK,
- VF_T_GET_SPARSITY_MAP, VF_T_SPARSIFY, VF_T_SUBVIEW, VF_T_SWIZZLE_CONSTANT) = range(1, 18)
+ VF_T_GET_SPARSITY_MAP, VF_T_SPARSIFY, VF_T_SUBVIEW, VF_T_SWIZZLE_CONSTANT, VF_T_RELOCATE_WEIGHTS_TABLE) = range(1, 19)
 VF_ARCH_NPU37XX, VF_ARCH_NPU40XX = 3, 4
 
 VF_RANGE_MINMAX, VF_RANGE_ABSMAX = 0, 1
@@ -75,11 +75,21 @@ class Content(C.Structure):
                 ("reserved", C.c_int32), ("data", C.c_void_p), ("nbytes", C.c_uint64)]
 
 
+VF_MAX_CLUSTERS = 8
+
+
+class Relocate(C.Structure):
+    _fields_ = [("n_clusters", C.c_int32), ("sparsity_ptr", C.c_int32), ("weights_ptr", C.c_int32 * VF_MAX_CLUSTERS),
+                ("offsets", C.c_int64 * VF_MAX_CLUSTERS), ("weights_table_size", C.c_int64),
+                ("weights_elem_bit_size", C.c_int64), ("num_elems", C.POINTER(C.c_int64)), ("n_num_elems", C.c_int64),
+                ("compression_axis", C.c_int64), ("alignment", C.c_int64), ("channel_offset", C.c_int64)]
+
+
 class Transform(C.Structure):
     _fields_ = [("kind", C.c_int32), ("rank", C.c_int32), ("elem", ElemType), ("order", C.c_uint32),
                 ("mem_perm", C.c_uint32), ("a", C.c_int64 * VF_MAX_RANK), ("b", C.c_int64 * VF_MAX_RANK),
                 ("value", C.c_double), ("width", C.c_int32), ("compress_output", C.c_int32),
-                ("num_actual", C.POINTER(C.c_int64)), ("n_num_actual", C.c_int64)]
+                ("num_actual", C.POINTER(C.c_int64)), ("n_num_actual", C.c_int64), ("relocate", Relocate)]
 
 
 class Options(C.Structure):

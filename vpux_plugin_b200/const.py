@@ -140,6 +140,30 @@ class ContentSetup:
         t.a[0], t.a[1] = int(swizzle_key), int(arch)
         return self._add(t)
 
+    def relocateWeightsTablePointers(self, weights_ptr, sparsity_ptr, offsets, weights_table_size,
+                                     weights_elem_bit_size=0, weights_compression=None, channel_offset=0):
+        """content_setup.cpp:82-92. `weights_compression` is None or a dict {"axis", "numElems", "alignment"}
+        (VPUIP::SparsityCompressionAttr; alignment 0 / missing = the 16-byte default)."""
+        if len(weights_ptr) != len(offsets) or not 1 <= len(offsets) <= abi.VF_MAX_CLUSTERS:
+            raise ValueError("weightsPtr and offsets need one entry per cluster (1..%d)" % abi.VF_MAX_CLUSTERS)
+        t = self._t(abi.VF_T_RELOCATE_WEIGHTS_TABLE)
+        r = t.relocate
+        r.n_clusters = len(offsets)
+        r.sparsity_ptr = int(sparsity_ptr)
+        for i, (w, o) in enumerate(zip(weights_ptr, offsets)):
+            r.weights_ptr[i], r.offsets[i] = int(w), int(o)
+        r.weights_table_size = int(weights_table_size)
+        r.weights_elem_bit_size = int(weights_elem_bit_size or 0)
+        r.channel_offset = int(channel_offset or 0)
+        keep = None
+        if weights_compression is not None:
+            keep = np.ascontiguousarray(weights_compression["numElems"], dtype=np.int64)
+            r.num_elems = keep.ctypes.data_as(C.POINTER(C.c_int64))
+            r.n_num_elems = len(keep)
+            r.compression_axis = int(weights_compression.get("axis", 0))
+            r.alignment = int(weights_compression.get("alignment", 0) or 0)
+        return self._add(t, keep)
+
     def getSparsityMap(self):
         return self._add(self._t(abi.VF_T_GET_SPARSITY_MAP))
 

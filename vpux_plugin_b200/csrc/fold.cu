@@ -447,6 +447,7 @@ DContent do_sparsify(vf_ctx* ctx, DContent& in, const vf_transform& t, DBuf* kee
 }
 
 DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t);
+DContent do_relocate(vf_ctx* ctx, DContent& in, const vf_transform& t);
 
 DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     bool os;
@@ -471,6 +472,7 @@ DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     case VF_T_GET_SPARSITY_MAP: return do_sparsity_map(ctx, in, t);
     case VF_T_SPARSIFY: return do_sparsify(ctx, in, t);
     case VF_T_SWIZZLE_CONSTANT: return do_swizzle(ctx, in, t);
+    case VF_T_RELOCATE_WEIGHTS_TABLE: return do_relocate(ctx, in, t);
     default: raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }
@@ -576,6 +578,61 @@ DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     } else {
         launch_swizzle(ctx, lin.p, out.own.p, new_size, int(t.a[0]), int(t.a[1]));
     }
+    return out;
+}
+
+// RelocateWeightsTable — attributes/relocate_weights_table.cpp:203-292. The host prepares what depends on the
+// attribute alone (cluster boundaries, and with weightsCompression the byte offset of every channel's
+// compressed weight set); the kernel reads the pointer steps from the table itself and patches the rows.
+DContent do_relocate(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const vf_relocate& r = t.relocate;
+    DContent lin = materialise_logical(ctx, in);  // a splat is filled in, like the reference's copyTo into a temp buffer
+    DContent out = alloc_like(ctx, ot, ot.elem.dtype, false);
+    RelocateArgs a{};
+    a.oc = r.weights_table_size / 4 / 4;  // numWTEntries / WEIGHT_TABLE_NUM_ELEMENTS_PER_OC
+    a.n_clusters = r.n_clusters;
+    a.sparsity_ptr = r.sparsity_ptr;
+    if (r.channel_offset < INT32_MIN || r.channel_offset > INT32_MAX) raise(VF_ERR_CHECKED_CAST, "channelOffset %lld outside int32", (long long)r.channel_offset);
+    a.channel_offset = int32_t(r.channel_offset);
+    bool segmented = false;
+    for (int c = 0; c < r.n_clusters; ++c) {
+        a.weights_ptr[c] = r.weights_ptr[c];
+        a.offsets[c] = r.offsets[c];
+        if (c && r.offsets[c] != r.offsets[c - 1]) segmented = true;
+    }
+    // the reference walks the channels in order and moves to cluster c + 1 at the first channel >= offsets[c + 1],
+    // one cluster per channel at most: cluster c + 1 starts at cross[c + 1]
+    a.cross[0] = -1;
+    for (int c = 1; c < r.n_clusters; ++c) a.cross[c] = segmented ? std::max(r.offsets[c], a.cross[c - 1] + 1) : INT64_MAX;
+    DBuf d_steps;
+    if (r.num_elems) {
+        if (r.channel_offset < 0 || r.n_num_elems < a.oc + r.channel_offset)
+            raise(VF_ERR_SHAPE, "Invalid weights compression with %lld elements for %lld channels", (long long)r.n_num_elems, (long long)a.oc);
+        if (r.weights_elem_bit_size <= 0) raise(VF_ERR_INVALID_ARG, "Missing weights element type attribute");
+        const int64_t alignment = r.alignment ? r.alignment : 16;  // VPU_WEIGHT_SET_BYTE_ALIGNMENT
+        if (alignment < 0) raise(VF_ERR_INVALID_ARG, "negative weightsCompression alignment");
+        auto set_bytes = [&](int64_t oc) { return align_up((r.num_elems[oc] * r.weights_elem_bit_size + 7) / 8, alignment); };
+        int64_t front = 0;
+        for (int64_t oc = 0; oc < r.channel_offset; ++oc) front += set_bytes(oc);
+        a.wptr_offset = uint32_t(front);
+        std::vector<int64_t> steps(size_t(std::max<int64_t>(a.oc, 1)));
+        int64_t ptr = 0;
+        int cl = 0;
+        for (int64_t oc = 0; oc < a.oc; ++oc) {
+            if (cl + 1 < r.n_clusters && oc >= a.cross[cl + 1]) {
+                ++cl;
+                ptr = 0;
+            }
+            steps[size_t(oc)] = ptr;
+            ptr += set_bytes(oc + r.channel_offset);
+        }
+        d_steps = upload_vec(ctx, steps);
+        a.d_steps = d_steps.as<int64_t>();
+    }
+    if (out.nbytes) VF_CUDA(cudaMemcpyAsync(out.own.p, lin.d, out.nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    launch_relocate(ctx, static_cast<const int32_t*>(lin.d), out.own.as<int32_t>(), a);
     return out;
 }
 

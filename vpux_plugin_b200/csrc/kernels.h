@@ -114,6 +114,21 @@ void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table);
 // All tables of `tabs` (each with its d_table) in one launch over a device copy of the list.
 void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs);
 
+// RelocateWeightsTable: rows [0, oc) of a weights table `in` -> `out` with columns 0 / 1 rebased
+struct RelocateArgs {
+    int64_t oc;                            // rows to patch
+    int in_splat;                          // `in` holds one element
+    int n_clusters;
+    int32_t weights_ptr[VF_MAX_CLUSTERS];
+    int64_t offsets[VF_MAX_CLUSTERS];      // first channel of each cluster
+    int64_t cross[VF_MAX_CLUSTERS];        // first row that belongs to cluster c (cross[0] unused)
+    int32_t sparsity_ptr;
+    int32_t channel_offset;
+    const int64_t* d_steps;                // optional [oc]: byte offset of each channel's compressed weight set
+    uint32_t wptr_offset;                  // with d_steps: bytes of the channel_offset sets sliced away in front
+};
+void launch_relocate(vf_ctx* ctx, const int32_t* in, int32_t* out, const RelocateArgs& a);
+
 // ---- synthetic weights -------------------------------------------------------------------------------
 void launch_synth(vf_ctx* ctx, const vf_synth_spec& s, void* dst, uint64_t count);
 

@@ -485,6 +485,38 @@ __global__ void k_weights_table_batch(const TableArgs* __restrict__ tabs, int n,
     weights_table_row(a, u - a.unit_begin, a.d_table, flags);
 }
 
+// RelocateWeightsTable — attributes/relocate_weights_table.cpp:203-292. One thread per table row of four
+// 32-bit entries: columns 0 and 1 are rewritten from the cluster's base pointers, columns 2 and 3 are copied.
+// The steps between consecutive channels come from the first two rows of the INPUT table, so the pass writes a
+// new buffer. Rows past `oc` (a table inside a larger fused constant) are copied unchanged by the caller.
+__global__ void k_relocate(const int32_t* __restrict__ in, int32_t* __restrict__ out, RelocateArgs a, int* flags) {
+    const int64_t oc = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (oc >= a.oc) return;
+    int32_t row[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) row[c] = a.in_splat ? in[0] : in[oc * 4 + c];
+    uint32_t wstep = 0, sstep = 0;  // int32 differences; they wrap like the two's-complement machine the reference runs on
+    if (a.oc >= 2 && !a.in_splat) {
+        wstep = uint32_t(in[4]) - uint32_t(in[0]);
+        sstep = uint32_t(in[5]) - uint32_t(in[1]);
+    }
+    int cl = 0;  // cluster of this channel: boundaries the reference's sequential walk has crossed at oc
+    for (int c = 1; c < a.n_clusters; ++c) cl += a.cross[c] <= oc ? 1 : 0;
+    const int64_t rel = oc - a.offsets[cl];
+    const int64_t step = a.d_steps ? a.d_steps[oc] : int64_t(int32_t(wstep)) * rel;
+    const uint32_t woff = a.d_steps ? a.wptr_offset : uint32_t(a.channel_offset) * wstep;
+    const int64_t w = int64_t(a.weights_ptr[cl]) + step;
+    if (w < INT32_MIN || w > INT32_MAX) set_flag(flags, VF_FLAG_CHECKED_CAST);
+    row[0] = int32_t(uint32_t(w) + woff);
+    if (row[1] != 0xFFFFFF) {  // SPARSITY_PTR_WHEN_NO_SPARSITY stays
+        const int64_t s = int64_t(a.sparsity_ptr) + rel * int64_t(int32_t(sstep));
+        if (s < INT32_MIN || s > INT32_MAX) set_flag(flags, VF_FLAG_CHECKED_CAST);
+        row[1] = int32_t(uint32_t(s) + uint32_t(a.channel_offset) * sstep);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) out[oc * 4 + c] = row[c];
+}
+
 // ------------------------------------------------------------------------------------------------------
 // synthetic weights
 // ------------------------------------------------------------------------------------------------------
@@ -750,6 +782,12 @@ void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
     DBuf d;
     const TableArgs* d_tabs = static_cast<const TableArgs*>(upload_table(ctx, tabs.data(), tabs.size() * sizeof(TableArgs), d));
     k_weights_table_batch<<<int((total + 127) / 128), 128, 0, ctx->stream>>>(d_tabs, int(tabs.size()), total, ctx->d_flags);
+    post_launch(ctx);
+}
+
+void launch_relocate(vf_ctx* ctx, const int32_t* in, int32_t* out, const RelocateArgs& a) {
+    if (a.oc <= 0) return;
+    k_relocate<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(in, out, a, ctx->d_flags);
     post_launch(ctx);
 }
 

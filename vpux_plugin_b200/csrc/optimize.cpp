@@ -7,8 +7,8 @@
 //   moveReshapeBefore               utils/transformations.cpp:657-712
 // Pure host code. A shorter list means fewer passes over the data on the device, and a SubView moved to the
 // front means only the needed slab is uploaded and folded.
-// Not covered (their transformations are outside this library): ChangeShapeAndElemType, RelocateWeightsTable,
-// Fuse; a Reshape is therefore not moved before a Dequantize of a per-axis type (that rewrite needs
+// Not covered (their transformations are outside this library): ChangeShapeAndElemType and Fuse as list
+// entries; a Reshape is therefore not moved before a Dequantize of a per-axis type (that rewrite needs
 // ChangeShapeAndElemType, transformations.cpp:338-378).
 #include <algorithm>
 #include <functional>
@@ -258,6 +258,39 @@ Result move_subview_before(List& l, size_t cur, const Type& base) {
             prev.t.a[i] = pb[i];
             prev.t.b[i] = pa[i];
         }
+        break;
+    }
+    case VF_T_RELOCATE_WEIGHTS_TABLE: {  // prepareRelocateWeightsTableSwap (:157-270)
+        vf_relocate r = prev.t.relocate;
+        const int64_t sub_size = sub.t.b[0], sub_off = sub.t.a[0];
+        if (sub_size <= 1) return {cur, false};  // one channel cannot give the pointer steps
+        for (int d = rank - 1; d >= 1; --d)      // only slices of the channel dim
+            if (sub.t.a[d] > 0 || sub.t.b[d] < prev_in.shape[d]) return {cur, false};
+        const uint64_t total_channels = uint64_t(prev_in.shape[0]);
+        if (total_channels == 0) return {cur, false};
+        const uint64_t entry = uint64_t(r.weights_table_size) / 4 / total_channels;
+        bool different = false;
+        for (int c = 1; c < r.n_clusters; ++c) different = different || r.offsets[c] != r.offsets[c - 1];
+        if (different) {  // the slice must be exactly one cluster's channels
+            int idx = -1;
+            for (int c = 0; c < r.n_clusters && idx < 0; ++c)
+                if (r.offsets[c] == sub_off) idx = c;
+            if (idx < 0) return {cur, false};
+            if (idx + 1 < r.n_clusters && r.offsets[idx + 1] - sub_off != sub_size) return {cur, false};
+            if (r.num_elems) {  // the compression entries of the slice
+                if (r.compression_axis != 0) return {cur, false};
+                if (sub_off < 0 || sub_off + sub_size > r.n_num_elems) return {cur, false};
+                r.num_elems += sub_off;
+                r.n_num_elems = sub_size;
+            }
+            r.weights_ptr[0] = r.weights_ptr[idx];
+            r.offsets[0] = 0;
+            r.n_clusters = 1;
+        } else {  // same cluster everywhere: the slice only shifts the first channel
+            r.channel_offset += sub_off;
+        }
+        r.weights_table_size = int64_t(entry * uint64_t(sub_size) * 4);
+        prev.t.relocate = r;
         break;
     }
     default: return {cur, false};

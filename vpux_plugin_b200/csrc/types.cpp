@@ -339,6 +339,17 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
         return out;
     }
 
+    case VF_T_RELOCATE_WEIGHTS_TABLE: {  // relocate_weights_table.cpp:194-200: type and splatness pass through
+        const vf_relocate& r = t.relocate;
+        if (r.n_clusters < 1 || r.n_clusters > VF_MAX_CLUSTERS) raise(VF_ERR_INVALID_ARG, "RelocateWeightsTable with %d clusters (1..%d)", r.n_clusters, VF_MAX_CLUSTERS);
+        if (in.elem.quantized() || dtype_bits(in.elem.dtype) != 32 || dtype_is_float(in.elem.dtype))
+            raise(VF_ERR_UNSUPPORTED, "RelocateWeightsTable patches tables of 32-bit integers");
+        if (r.weights_table_size < 0 || r.weights_table_size / 4 > in.numel())
+            raise(VF_ERR_SHAPE, "weightsTableSize %lld exceeds the constant (%lld entries)", (long long)r.weights_table_size, (long long)in.numel());
+        out_splat = in_splat;
+        return out;
+    }
+
     default:
         raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
