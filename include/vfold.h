@@ -497,6 +497,76 @@ int vf_plan_shards(int mode, int world, int64_t ntensors, const uint64_t* bytes,
                    int64_t row_align, int64_t* row_begin, int64_t* row_end, char* err, size_t errlen);
 
 /* ------------------------------------------------------------------ */
+/* folding in the background with a cache of folded contents           */
+/* ------------------------------------------------------------------ */
+/* Replaces Const::BackgroundConstantFolding + Const::ConstantFoldingCache
+ * (const/utils/constant_folding_in_background.cpp:17-241, constant_folding_cache.cpp:15-245): requests are
+ * queued by the compiler thread, folded by worker threads (each with its own context and stream on the
+ * device), and the folded Const::Content objects stay in device memory, keyed by (base content,
+ * transformation list). A later fold of the same attribute is a device-to-destination copy.
+ *
+ * Identity of a base content: `base_id` != 0 is the caller's identity of the bytes (the reference's uniqued
+ * attribute pointer); `base_id` == 0 makes the library hash the bytes on the GPU (vf_content_hash), so equal
+ * bytes in different buffers share one cache entry. `base->data` is borrowed: it must stay valid until the
+ * request has been processed (vf_folder_wait_idle) — the reference's ContentAttr keeps its base alive as well.
+ * Transformation lists are copied at the call. */
+typedef struct vf_folder vf_folder;
+
+typedef struct vf_folder_options {
+    uint64_t memory_limit_bytes; /* memoryUsageLimit: bytes of folded contents the cache may hold (0 = 4 GiB) */
+    double clean_threshold;      /* cacheCleanThreshold: a clean-up shrinks the cache to this share of the limit (0 = 0.8) */
+    int32_t max_concurrent_tasks;/* worker threads = streams folding at the same time (0 = 2) */
+    int32_t collect_statistics;
+} vf_folder_options;
+
+/* details::CacheStatistics (constant_folding_cache.hpp:102-124) plus what the log line adds */
+typedef struct vf_folder_stats {
+    uint64_t added;             /* numElementsAddedToCache */
+    uint64_t erased;            /* numElementsErasedFromCache */
+    uint64_t hits;              /* numCacheHits */
+    uint64_t misses;            /* numCacheMisses */
+    uint64_t duplicated;        /* numDuplicatedRequests */
+    uint64_t max_queue;         /* maximum number of requests in queue */
+    uint64_t max_cache_size;    /* maximum number of elements in cache */
+    uint64_t max_memory_used;   /* maximum memory used by cache */
+    uint64_t memory_used;       /* current memory used by cache */
+    uint64_t cache_size;        /* current number of elements */
+    uint64_t failed;            /* requests whose fold raised an error (nothing is cached for them) */
+    uint64_t partial;           /* requests folded from a cached prefix (tryFoldingPartially) */
+} vf_folder_stats;
+
+int vf_folder_create(int device, const vf_folder_options* opts, vf_folder** out, char* err, size_t errlen);
+/* Sends the termination token, waits for the workers (stopFoldingListener) and frees the cache. */
+void vf_folder_destroy(vf_folder* folder);
+
+/* FoldingRequest{attr, newTransformation}: `new_index` is the position of the transformation that was just
+ * appended to `t` (the request is then tried from the cached content of t[0 .. new_index)), or -1. */
+int vf_folder_enqueue(vf_folder* folder, const vf_content* base, uint64_t base_id, const vf_transform* t, int n,
+                      int new_index, char* err, size_t errlen);
+/* EquivalenceRequest{originalAttr, newAttr}: both lists fold to the same content; a cached result of the
+ * original is re-keyed to the new list, otherwise the new list is folded. */
+int vf_folder_enqueue_equivalence(vf_folder* folder, const vf_content* base, uint64_t base_id, const vf_transform* t_orig,
+                                  int n_orig, const vf_transform* t_new, int n_new, char* err, size_t errlen);
+/* Blocks until the queue is empty and no worker is folding (tests use it where the reference's sleep). */
+int vf_folder_wait_idle(vf_folder* folder, char* err, size_t errlen);
+/* ConstantFoldingCache::hasContent: `*found`; a hit raises the entry's priority (refCount + 1). */
+int vf_folder_has_content(vf_folder* folder, const vf_content* base, uint64_t base_id, const vf_transform* t, int n,
+                          int* found, char* err, size_t errlen);
+/* ContentAttr::fold() + copyTo() through the cache (attributes/content.cpp:371-397): a cached content is
+ * copied out (`*from_cache` = 1, its refCount drops by one), anything else is folded now and not cached.
+ * Arguments as vf_fold. */
+int vf_folder_fold(vf_folder* folder, const vf_content* base, uint64_t base_id, const vf_transform* t, int n, void* dst,
+                   uint64_t dst_bytes, int dst_mem_kind, uint64_t* dst_written, vf_tensor_type* out_type,
+                   double* scales_buf, int64_t* zps_buf, int64_t params_cap, int* from_cache, char* err, size_t errlen);
+/* ConstantFoldingCache::removeContent */
+int vf_folder_remove(vf_folder* folder, const vf_content* base, uint64_t base_id, const vf_transform* t, int n,
+                     char* err, size_t errlen);
+int vf_folder_statistics(vf_folder* folder, vf_folder_stats* out);
+/* 128-bit hash of a content's storage bytes, computed on the GPU (host memory is uploaded first). The same
+ * bytes give the same hash wherever they live and however the buffer is aligned. */
+int vf_content_hash(vf_ctx* ctx, const vf_content* content, uint64_t out[2], char* err, size_t errlen);
+
+/* ------------------------------------------------------------------ */
 /* synthetic weights (measurement support)                             */
 /* ------------------------------------------------------------------ */
 typedef struct vf_synth_spec {

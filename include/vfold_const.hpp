@@ -607,7 +607,20 @@ public:
         return Content(TensorType::fromPod(outPod), splat, std::move(dst));
     }
 
+    // the POD view of the base content (borrowing this attribute's buffer)
+    vf_content basePod() const {
+        vf_content c{};
+        c.type = _setup.getBaseType().pod();
+        c.storage_dtype = _storage;
+        c.is_splat = _splat ? 1 : 0;
+        c.mem_kind = VF_MEM_HOST;
+        c.data = _base;
+        c.nbytes = _baseBytes;
+        return c;
+    }
+
 private:
+    friend class BackgroundConstantFolding;
     static constexpr int64_t kParamsCap = 1 << 16;
     TensorType infer(bool& splat, uint64_t& bytes) const {
         const vf_tensor_type base = _setup.getBaseType().pod();
@@ -634,6 +647,90 @@ private:
 inline ContentAttr ContentSetup::get(const void* base, size_t baseBytes, bool isSplat, vf_dtype storage) const {
     return ContentAttr(*this, base, baseBytes, isSplat, storage);
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Const::BackgroundConstantFolding + Const::ConstantFoldingCache (utils/constant_folding_in_background.hpp:25-72,
+// utils/constant_folding_cache.hpp:130-262) over vf_folder: requests are folded by worker threads on the
+// device and the folded contents are cached there; fold() is ContentAttr::fold() through that cache.
+// The base buffer of a queued attribute must stay valid until waitIdle() (or the destructor) returns.
+// ---------------------------------------------------------------------------------------------------------
+class BackgroundConstantFolding {
+public:
+    // memoryUsageLimit in MB as in the reference (0 = the library's default)
+    BackgroundConstantFolding(int device, size_t maxConcurrentTasks, bool collectStatistics, size_t memoryUsageLimit = 0,
+                              double cacheCleanThreshold = 0.8) {
+        vf_folder_options o{};
+        o.memory_limit_bytes = uint64_t(memoryUsageLimit) << 20;
+        o.clean_threshold = cacheCleanThreshold;
+        o.max_concurrent_tasks = int32_t(maxConcurrentTasks);
+        o.collect_statistics = collectStatistics ? 1 : 0;
+        char err[512] = {0};
+        details::check(vf_folder_create(device, &o, &_folder, err, sizeof(err)), err);
+    }
+    ~BackgroundConstantFolding() {
+        vf_folder_destroy(_folder);
+    }
+    BackgroundConstantFolding(const BackgroundConstantFolding&) = delete;
+    BackgroundConstantFolding& operator=(const BackgroundConstantFolding&) = delete;
+
+    // ConstantFoldingCache::enqueueRequest(FoldingRequest{attr, newTransformation}); `newIndex` = position of the
+    // transformation appended last, -1 for none; `baseId` = the caller's identity of the base bytes, 0 = hash them
+    void enqueueRequest(const ContentAttr& attr, int newIndex = -1, uint64_t baseId = 0) {
+        const vf_content c = attr.basePod();
+        const std::vector<vf_transform> t = attr.transform().pods();
+        char err[512] = {0};
+        details::check(vf_folder_enqueue(_folder, &c, baseId, t.data(), int(t.size()), newIndex, err, sizeof(err)), err);
+    }
+    void enqueueRequest(const ContentAttr& originalAttr, const ContentAttr& newAttr, uint64_t baseId = 0) {  // EquivalenceRequest
+        const vf_content c = originalAttr.basePod();
+        const std::vector<vf_transform> t0 = originalAttr.transform().pods(), t1 = newAttr.transform().pods();
+        char err[512] = {0};
+        details::check(vf_folder_enqueue_equivalence(_folder, &c, baseId, t0.data(), int(t0.size()), t1.data(), int(t1.size()), err,
+                                                     sizeof(err)),
+                       err);
+    }
+    void waitIdle() {
+        char err[512] = {0};
+        details::check(vf_folder_wait_idle(_folder, err, sizeof(err)), err);
+    }
+    bool hasContent(const ContentAttr& attr, uint64_t baseId = 0) {
+        const vf_content c = attr.basePod();
+        const std::vector<vf_transform> t = attr.transform().pods();
+        int found = 0;
+        char err[512] = {0};
+        details::check(vf_folder_has_content(_folder, &c, baseId, t.data(), int(t.size()), &found, err, sizeof(err)), err);
+        return found != 0;
+    }
+    // ContentAttr::fold() with the cache consulted first (attributes/content.cpp:371-397)
+    Content fold(const ContentAttr& attr, bool* fromCache = nullptr, uint64_t baseId = 0) {
+        bool splat;
+        uint64_t need;
+        attr.infer(splat, need);
+        const vf_content c = attr.basePod();
+        const std::vector<vf_transform> t = attr.transform().pods();
+        std::vector<uint8_t> dst(size_t(need ? need : 1));
+        uint64_t written = 0;
+        vf_tensor_type outPod{};
+        std::vector<double> sb(ContentAttr::kParamsCap);
+        std::vector<int64_t> zb(ContentAttr::kParamsCap);
+        int hit = 0;
+        char err[512] = {0};
+        details::check(vf_folder_fold(_folder, &c, baseId, t.data(), int(t.size()), dst.data(), need, VF_MEM_HOST, &written, &outPod,
+                                      sb.data(), zb.data(), ContentAttr::kParamsCap, &hit, err, sizeof(err)),
+                       err);
+        if (fromCache) *fromCache = hit != 0;
+        dst.resize(size_t(written));
+        return Content(TensorType::fromPod(outPod), splat, std::move(dst));
+    }
+    vf_folder_stats getStatistics() {
+        vf_folder_stats s{};
+        vf_folder_statistics(_folder, &s);
+        return s;
+    }
+
+private:
+    vf_folder* _folder = nullptr;
+};
 
 }  // namespace Const
 }  // namespace vfold

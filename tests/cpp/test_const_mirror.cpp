@@ -217,6 +217,31 @@ static void relocateWeightsTable(const Context& ctx) {  // lit const/passes/cons
     EXPECT(content.getValues<int32_t>() == expected);
 }
 
+static void foldingInBackground() {  // constant_folding_in_background_tests.cpp:36-52, 88-106 and :156-196
+    Const::BackgroundConstantFolding folding(0, 2, true, 3 * 1024, 0.8);
+    const TensorType baseType({100}, VF_DT_F32);
+    const float baseValue = 1.0f;
+    auto setup = Const::ContentSetup(baseType);
+    for (int i = 0; i < 5; ++i) setup = setup.add(1.0);
+    const auto attr = setup.get(&baseValue, sizeof(baseValue), true);
+    folding.enqueueRequest(attr);
+    folding.waitIdle();
+    bool fromCache = false;
+    const auto content = folding.fold(attr, &fromCache);
+    EXPECT(fromCache);
+    EXPECT(content.getValues<float>() == std::vector<float>(100, 6.0f));
+    // an equivalence request re-keys the cached result of the two SubViews to the fused one
+    const auto attr1 = Const::ContentSetup(baseType).subview({0}, {50}).subview({10}, {30}).get(&baseValue, sizeof(baseValue), true);
+    const auto attr2 = Const::ContentSetup(baseType).subview({0}, {30}).get(&baseValue, sizeof(baseValue), true);
+    folding.enqueueRequest(attr1);
+    folding.enqueueRequest(attr1, attr2);
+    folding.waitIdle();
+    EXPECT(folding.hasContent(attr2));
+    EXPECT(!folding.hasContent(attr1));
+    const vf_folder_stats st = folding.getStatistics();
+    EXPECT(st.added == 2 && st.failed == 0 && st.hits == 1);
+}
+
 static void copyToTooSmall(const Context& ctx) {  // utils/content.cpp:172-174
     const TensorType baseType({4}, VF_DT_F32);
     const auto vals = generateValues<float>(4);
@@ -248,6 +273,7 @@ int main(int argc, char** argv) {
             dequantizeQuantize(ctx);
             relocateWeightsTable(ctx);
             copyToTooSmall(ctx);
+            foldingInBackground();
         } catch (const Exception& e) {
             std::printf("unexpected vfold::Exception %d: %s\n", e.status(), e.what());
             ++g_failed;

@@ -285,3 +285,13 @@ def make_transforms(items):
     for i, t in enumerate(items):
         arr[i] = t
     return arr
+
+
+class FolderOptions(C.Structure):
+    _fields_ = [("memory_limit_bytes", C.c_uint64), ("clean_threshold", C.c_double), ("max_concurrent_tasks", C.c_int32),
+                ("collect_statistics", C.c_int32)]
+
+
+class FolderStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("added", "erased", "hits", "misses", "duplicated", "max_queue", "max_cache_size",
+                                          "max_memory_used", "memory_used", "cache_size", "failed", "partial")]

@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cmath>
 
+#include "fold_internal.h"
 #include "fused.h"
 
 namespace vf {
@@ -760,6 +761,70 @@ static void quantize_fold_general(vf_ctx* ctx, DContent& base, const vf_quant_sp
     const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_kind, stats);
     if (dst_written) *dst_written = w;
     if (stats) stats->bytes_out += w;
+}
+
+// ---- folding without copyTo (the background folder's cache keeps Const::Content objects) -----------------
+Folded fold_keep(vf_ctx* ctx, const vf_content& base, const vf_transform* t, int n) {
+    if ((n > 0 && !t) || n < 0) raise(VF_ERR_INVALID_ARG, "NULL argument");
+    check_positions(t, n);
+    CallScope scope(ctx, nullptr);
+    DContent cur = upload_base(ctx, base, nullptr);
+    for (int i = 0; i < n; ++i) {
+        DContent next = apply(ctx, cur, t[i]);
+        cur = std::move(next);
+    }
+    Folded f;
+    f.type = cur.type;
+    f.storage = cur.storage;
+    f.splat = cur.splat;
+    f.nbytes = cur.nbytes;
+    // Content::copyUnownedBuffer: the cache owns its bytes, whatever the folded content borrowed
+    VF_CUDA(cudaMallocAsync(&f.data, size_t(std::max<uint64_t>(f.nbytes, 1)), ctx->stream));
+    cudaError_t e = f.nbytes ? cudaMemcpyAsync(f.data, cur.d, size_t(f.nbytes), cudaMemcpyDeviceToDevice, ctx->stream) : cudaSuccess;
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFreeAsync(f.data, ctx->stream);
+        raise(VF_ERR_CUDA, "copy of the folded content failed: %s", cudaGetErrorString(e));
+    }
+    try {
+        scope.finish();
+    } catch (...) {
+        cudaFreeAsync(f.data, ctx->stream);
+        throw;
+    }
+    return f;
+}
+
+void* upload_keep(vf_ctx* ctx, const vf_content& base, uint64_t* nbytes) {
+    CallScope scope(ctx, nullptr);
+    const uint64_t count = base.is_splat ? 1 : uint64_t(Type::from(base.type).numel());
+    const uint64_t need = (uint64_t(dtype_bits(base.storage_dtype)) * count + 7u) / 8u;
+    if (!base.data || base.nbytes < need) raise(VF_ERR_SHAPE, "base buffer holds %llu bytes, %llu needed", (unsigned long long)base.nbytes, (unsigned long long)need);
+    void* d = nullptr;
+    VF_CUDA(cudaMallocAsync(&d, size_t(std::max<uint64_t>(need, 1)), ctx->stream));
+    try {
+        copy_in(ctx, d, base.data, size_t(need), base.mem_kind);
+        VF_CUDA(cudaStreamSynchronize(ctx->stream));
+        scope.finish();
+    } catch (...) {
+        cudaFreeAsync(d, ctx->stream);
+        throw;
+    }
+    if (nbytes) *nbytes = need;
+    return d;
+}
+
+vf_content as_content(const Folded& f, std::vector<double>& sb, std::vector<int64_t>& zb) {
+    vf_content c{};
+    sb.assign(std::max<size_t>(f.type.elem.scales.size(), 1), 0.0);
+    zb.assign(std::max<size_t>(f.type.elem.zps.size(), 1), 0);
+    f.type.export_to(&c.type, sb.data(), zb.data(), int64_t(sb.size()));
+    c.storage_dtype = f.storage;
+    c.is_splat = f.splat ? 1 : 0;
+    c.mem_kind = VF_MEM_DEVICE;
+    c.data = f.data;
+    c.nbytes = f.nbytes;
+    return c;
 }
 
 }  // namespace vf

@@ -266,3 +266,120 @@ class Library:
         st = self.lib.vf_synth_fill(self.ctx, C.byref(spec), C.c_void_p(int(dst_ptr)), C.c_uint64(count), err,
                                     C.c_size_t(512))
         self._check(st, err)
+
+
+class Folder:
+    """vf_folder: folding in the background with a cache of folded contents, the counterpart of
+    Const::BackgroundConstantFolding + Const::ConstantFoldingCache
+    (const/utils/constant_folding_in_background.cpp, constant_folding_cache.cpp).
+
+    Takes const.ContentAttr objects. Also a fold backend: `attr.fold(folder)` is ContentAttr::fold() through the
+    cache. `base_id` = 0 lets the library hash the base bytes on the GPU; the base arrays of queued attributes
+    are kept alive here until wait_idle() / close()."""
+
+    def __init__(self, device=0, memory_limit_bytes=0, clean_threshold=0.0, max_concurrent_tasks=0, collect_statistics=True):
+        self.lib = raw()
+        for name in ("vf_folder_create", "vf_folder_enqueue", "vf_folder_enqueue_equivalence", "vf_folder_wait_idle",
+                     "vf_folder_has_content", "vf_folder_fold", "vf_folder_remove", "vf_folder_statistics", "vf_content_hash"):
+            getattr(self.lib, name).restype = C.c_int
+        self.lib.vf_folder_destroy.restype = None
+        self.lib.vf_folder_destroy.argtypes = [C.c_void_p]
+        opts = abi.FolderOptions(int(memory_limit_bytes), float(clean_threshold), int(max_concurrent_tasks),
+                                 1 if collect_statistics else 0)
+        self.h = C.c_void_p()
+        err = C.create_string_buffer(512)
+        st = self.lib.vf_folder_create(int(device), C.byref(opts), C.byref(self.h), err, C.c_size_t(512))
+        if st != 0:
+            raise VfoldError(st, err.value.decode(errors="replace"))
+        self._keep = []
+        self.from_cache = None  # whether the last fold() was served from the cache
+
+    def close(self):
+        if self.h:
+            self.lib.vf_folder_destroy(self.h)
+            self.h = C.c_void_p()
+            self._keep = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _check(st, err):
+        if st != 0:
+            raise VfoldError(st, err.value.decode(errors="replace"))
+
+    @staticmethod
+    def _parts(attr):
+        content, keep = abi.make_content(attr.base_type, attr.base, attr.storage_dtype, attr.is_splat)
+        tr, n = attr.setup.transforms()
+        return content, tr, n, (keep, attr)
+
+    def enqueue(self, attr, new_index=-1, base_id=0):
+        content, tr, n, keep = self._parts(attr)
+        self._keep.append(keep)
+        err = C.create_string_buffer(512)
+        self._check(self.lib.vf_folder_enqueue(self.h, C.byref(content), C.c_uint64(base_id), tr, n, int(new_index), err,
+                                               C.c_size_t(512)), err)
+
+    def enqueue_equivalence(self, original, new, base_id=0):
+        content, tr0, n0, keep0 = self._parts(original)
+        _, tr1, n1, keep1 = self._parts(new)
+        self._keep += [keep0, keep1]
+        err = C.create_string_buffer(512)
+        self._check(self.lib.vf_folder_enqueue_equivalence(self.h, C.byref(content), C.c_uint64(base_id), tr0, n0, tr1, n1,
+                                                           err, C.c_size_t(512)), err)
+
+    def wait_idle(self):
+        err = C.create_string_buffer(512)
+        self._check(self.lib.vf_folder_wait_idle(self.h, err, C.c_size_t(512)), err)
+        self._keep = []
+
+    def has_content(self, attr, base_id=0):
+        content, tr, n, keep = self._parts(attr)
+        found = C.c_int(0)
+        err = C.create_string_buffer(512)
+        self._check(self.lib.vf_folder_has_content(self.h, C.byref(content), C.c_uint64(base_id), tr, n, C.byref(found),
+                                                   err, C.c_size_t(512)), err)
+        return bool(found.value)
+
+    def remove(self, attr, base_id=0):
+        content, tr, n, keep = self._parts(attr)
+        err = C.create_string_buffer(512)
+        self._check(self.lib.vf_folder_remove(self.h, C.byref(content), C.c_uint64(base_id), tr, n, err, C.c_size_t(512)), err)
+
+    def statistics(self):
+        s = abi.FolderStats()
+        self.lib.vf_folder_statistics(self.h, C.byref(s))
+        return {n: int(getattr(s, n)) for n, _ in abi.FolderStats._fields_}
+
+    # -- fold backend (what const.ContentAttr.fold calls) ---------------------------------------------
+    def infer_type(self, base_type, is_splat, transforms, n):
+        return infer_type(base_type, is_splat, transforms, n)
+
+    def fold(self, content, transforms, n, dst, dst_bytes, params_cap=1 << 16, dst_mem_kind=abi.VF_MEM_HOST, base_id=0):
+        out = abi.TensorType()
+        sb = np.zeros(params_cap, np.float64)
+        zb = np.zeros(params_cap, np.int64)
+        written = C.c_uint64(0)
+        hit = C.c_int(0)
+        err = C.create_string_buffer(512)
+        st = self.lib.vf_folder_fold(self.h, C.byref(content), C.c_uint64(base_id), transforms, n, _ptr(dst),
+                                     C.c_uint64(dst_bytes), int(dst_mem_kind), C.byref(written), C.byref(out), _ptr(sb),
+                                     _ptr(zb), C.c_int64(params_cap), C.byref(hit), err, C.c_size_t(512))
+        self._check(st, err)
+        self.from_cache = bool(hit.value)
+        return written.value, abi.TType.from_pod(out)
+
+
+def content_hash(library, content):
+    """vf_content_hash on a Library's context: (h0, h1)."""
+    out = (C.c_uint64 * 2)()
+    err = C.create_string_buffer(512)
+    library.lib.vf_content_hash.restype = C.c_int
+    st = library.lib.vf_content_hash(library.ctx, C.byref(content), out, err, C.c_size_t(512))
+    if st != 0:
+        raise VfoldError(st, err.value.decode(errors="replace"))
+    return int(out[0]), int(out[1])
