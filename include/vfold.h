@@ -56,6 +56,7 @@ typedef enum vf_status {
     VF_ERR_RANGE = -12,           /* post-shift needed / rescaled bias outside int32
                                      (quantization.cpp:429-432, nce_sparsity.cpp:340-345)              */
     VF_ERR_QUANT_RANGE = -13,     /* calcScaleAndZeroPoint failure (quantization.cpp:612-625)          */
+    VF_ERR_NOT_NORMAL = -14,      /* ScalarMultInverse of a non-normal float (inverse.cpp:58-59)       */
     VF_ERR_CUDA = -20,            /* a CUDA runtime call failed; message carries cudaGetErrorString    */
     VF_ERR_NO_DEVICE = -21,       /* no usable CUDA device                                             */
     VF_ERR_OOM = -22,             /* device or pinned allocation failed                                */
@@ -163,7 +164,13 @@ typedef enum vf_transform_kind {
     VF_T_SUBVIEW = 16,          /* #const.SubView          subview.cpp:390-432 (a = offset, b = shape) */
     VF_T_SWIZZLE_CONSTANT = 17, /* #const.SwizzleConstant  swizzle_transform.cpp:163-215
                                    (a[0] = swizzle key 0..5, a[1] = arch: VF_ARCH_NPU37XX / VF_ARCH_NPU40XX) */
-    VF_T_RELOCATE_WEIGHTS_TABLE = 18 /* #const.RelocateWeightsTable relocate_weights_table.cpp:203-292 (relocate) */
+    VF_T_RELOCATE_WEIGHTS_TABLE = 18, /* #const.RelocateWeightsTable relocate_weights_table.cpp:203-292 (relocate) */
+    VF_T_REVERSE = 19,            /* #const.Reverse           reverse.cpp:46-105          (a[0] = axis)              */
+    VF_T_BROADCAST = 20,          /* #const.Broadcast         broadcast.cpp:66-124        (a[0] = axis, a[1] = value) */
+    VF_T_EXPAND_DILATED = 21,     /* #const.ExpandDilated     expand_dilated.cpp:72-131   (a[0], a[1] = dilations Y, X) */
+    VF_T_SCALAR_MULT_INVERSE = 22,/* #const.ScalarMultInverse inverse.cpp:40-66                                      */
+    VF_T_CHANGE_SHAPE_AND_ELEM_TYPE = 23 /* #const.ChangeShapeAndElemType change_shape_and_elem_type.cpp:62-79
+                                            (a = shape, elem) */
 } vf_transform_kind;
 
 /* VPU::ArchKind values SwizzleConstant carries (VPU/attributes.td:47-50) */

@@ -437,6 +437,34 @@ public:
         }
         return append(std::move(it));
     }
+    ContentSetup reverse(int64_t axis) const {
+        auto it = make(VF_T_REVERSE);
+        it->t.rank = 1;
+        it->t.a[0] = axis;
+        return append(std::move(it));
+    }
+    ContentSetup broadcast(int64_t axis, int64_t value) const {
+        auto it = make(VF_T_BROADCAST);
+        it->t.rank = 2;
+        it->t.a[0] = axis;
+        it->t.a[1] = value;
+        return append(std::move(it));
+    }
+    ContentSetup expandDilated(const std::vector<int64_t>& dilations) const {
+        if (dilations.size() != 2) throw Exception(VF_ERR_INVALID_ARG, "ExpandDilated takes the Y and X dilations");
+        auto it = make(VF_T_EXPAND_DILATED);
+        it->t.rank = 2;
+        it->t.a[0] = dilations[0];
+        it->t.a[1] = dilations[1];
+        return append(std::move(it));
+    }
+    ContentSetup scalarMultInverse() const { return append(make(VF_T_SCALAR_MULT_INVERSE)); }
+    ContentSetup changeShapeAndElemType(const std::vector<int64_t>& shape, const ElemType& e) const {
+        auto it = make(VF_T_CHANGE_SHAPE_AND_ELEM_TYPE);
+        fill(it->t.a, it->t.rank, shape);
+        it->elem = e;
+        return append(std::move(it));
+    }
     ContentSetup getSparsityMap() const { return append(make(VF_T_GET_SPARSITY_MAP)); }
     ContentSetup sparsify(bool compressOutputType, const std::vector<int64_t>& numActualElements = {}) const {
         auto it = make(VF_T_SPARSIFY);
@@ -466,7 +494,8 @@ public:
             auto it = std::make_shared<Item>();
             it->t = out[size_t(i)];
             const int k = it->t.kind;
-            if (k == VF_T_CAST_ELEM_TYPE || k == VF_T_CONVERT_ELEM_TYPE || k == VF_T_QUANTIZE) it->elem = ElemType::fromPod(it->t.elem);
+            if (k == VF_T_CAST_ELEM_TYPE || k == VF_T_CONVERT_ELEM_TYPE || k == VF_T_QUANTIZE || k == VF_T_CHANGE_SHAPE_AND_ELEM_TYPE)
+                it->elem = ElemType::fromPod(it->t.elem);
             if (it->t.num_actual) it->counts.assign(it->t.num_actual, it->t.num_actual + it->t.n_num_actual);
             if (k == VF_T_RELOCATE_WEIGHTS_TABLE && it->t.relocate.num_elems) {
                 it->numElems.assign(it->t.relocate.num_elems, it->t.relocate.num_elems + it->t.relocate.n_num_elems);

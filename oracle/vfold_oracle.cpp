@@ -654,16 +654,41 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
     case VF_T_RESCALE:
     case VF_T_ADD:
         break;
-    case VF_T_RESHAPE: {  // reshape.cpp:60-85 (plain element types only here)
+    case VF_T_RESHAPE:                      // reshape.cpp:74-77 -> changeShape, VC/src/core/type_interfaces.cpp:208-231
+    case VF_T_CHANGE_SHAPE_AND_ELEM_TYPE: {  // change_shape_and_elem_type.cpp:62-66 -> changeShapeElemType :253-269
         if (t.rank < 1 || t.rank > VF_MAX_RANK) fail(VF_ERR_INVALID_ARG, "bad reshape rank");
         int64_t n = 1;
         for (int i = 0; i < t.rank; ++i) n *= t.a[i];
         if (n != in.numel()) fail(VF_ERR_SHAPE, "Reshape changes the number of elements");
-        if (in.elem.kind == VF_ELEM_QUANT_PER_AXIS)
-            fail(VF_ERR_UNSUPPORTED, "Reshape of a per-axis quantized type is not supported");
         out.rank = t.rank;
         for (int i = 0; i < VF_MAX_RANK; ++i) out.shape[i] = i < t.rank ? t.a[i] : 0;
-        out.order = identity_order(t.rank);
+        const bool origIsIdentity = in.order == identity_order(in.rank);
+        if (origIsIdentity) out.order = identity_order(t.rank);
+        else if (in.rank != t.rank) fail(VF_ERR_SHAPE, "Order is incompatible with the new shape");
+        if (t.kind == VF_T_CHANGE_SHAPE_AND_ELEM_TYPE) {
+            out.elem = elem_from_pod(t.elem);
+        } else if (in.elem.kind == VF_ELEM_QUANT_PER_AXIS) {
+            // getQuantizedAxis — VC/src/utils/types.cpp:140-162
+            const int axis = in.elem.axis;
+            if (axis >= 0 && axis < in.rank && in.shape[axis] != 1) {
+                int64_t fullSizeIncludingAxis = 1;
+                for (int i = 0; i <= axis; ++i) fullSizeIncludingAxis *= in.shape[i];
+                int64_t accumSize = 1;
+                for (int i = 0; i < t.rank; ++i) {
+                    accumSize *= t.a[i];
+                    if (accumSize == fullSizeIncludingAxis && t.a[i] == in.shape[axis]) {
+                        out.elem.axis = i;
+                        break;
+                    }
+                    if (accumSize > fullSizeIncludingAxis) break;
+                }
+            }
+        }
+        if (out.elem.kind == VF_ELEM_QUANT_PER_AXIS) {  // validateQuantElemType — VC/src/utils/quantization.cpp:86-116
+            if (out.elem.axis < 0 || out.elem.axis >= out.rank) fail(VF_ERR_SHAPE, "Quantized axis is out of main type rank");
+            if (int64_t(out.elem.scales.size()) != out.shape[out.elem.axis])
+                fail(VF_ERR_SHAPE, "Number of scales in per-axis quantized type do not match the quantized dimension size");
+        }
         break;
     }
     case VF_T_REORDER:      // reorder.cpp:60-77: changeDimsOrder
@@ -789,6 +814,39 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
         out_splat = false;
         break;
     }
+    case VF_T_REVERSE: {  // reverse.cpp:35-44; the checks of transform() :46-105
+        if (in.elem.kind == VF_ELEM_QUANT_PER_AXIS) fail(VF_ERR_UNSUPPORTED, "Unexpected data type");
+        const int dt = in.elem.dtype;
+        if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32)
+            fail(VF_ERR_UNSUPPORTED, "Unexpected data type: %d", dt);
+        if (!in_splat && (t.a[0] < 0 || t.a[0] >= in.rank - 1))
+            fail(VF_ERR_INVALID_ARG, "Const::Content::reverse: got unexpected content dimension %lld", (long long)t.a[0]);
+        break;
+    }
+    case VF_T_BROADCAST: {  // broadcast.cpp:66-83
+        const int64_t axis = t.a[0], value = t.a[1];
+        if (axis < 0 || axis >= in.rank) fail(VF_ERR_INVALID_ARG, "Broadcast axis");
+        if (value < in.shape[axis]) fail(VF_ERR_SHAPE, "Value cannot be broadcasted due to new value's size is less than old one");
+        vf_transform pad{};
+        pad.kind = VF_T_PAD_WITH_ZERO;
+        pad.rank = in.rank;
+        pad.b[axis] = value - in.shape[axis];
+        bool ignored;
+        out = infer_one(in, in_splat, pad, ignored);
+        break;
+    }
+    case VF_T_EXPAND_DILATED: {  // expand_dilated.cpp:72-82 with getDilatedType, VC/src/utils/dilated_utils.cpp:11-34
+        if (in.rank != 4) fail(VF_ERR_SHAPE, "Got invalid tensor rank");
+        if (t.a[0] < 1 || t.a[1] < 1) fail(VF_ERR_INVALID_ARG, "dilations must be positive");
+        out.shape[2] = in.shape[2] + (in.shape[2] - 1) * (t.a[0] - 1);
+        out.shape[3] = in.shape[3] + (in.shape[3] - 1) * (t.a[1] - 1);
+        if (out.elem.kind == VF_ELEM_QUANT_PER_AXIS && int64_t(out.elem.scales.size()) != out.shape[out.elem.axis])
+            fail(VF_ERR_SHAPE, "Number of scales in per-axis quantized type do not match the quantized dimension size");
+        out_splat = false;
+        break;
+    }
+    case VF_T_SCALAR_MULT_INVERSE:  // inverse.cpp:40-50
+        break;
     case VF_T_RELOCATE_WEIGHTS_TABLE: {  // relocate_weights_table.cpp:194-200
         const vf_relocate& r = t.relocate;
         if (r.n_clusters < 1 || r.n_clusters > VF_MAX_CLUSTERS) fail(VF_ERR_INVALID_ARG, "RelocateWeightsTable with %d clusters", r.n_clusters);
@@ -1383,6 +1441,93 @@ Content tf_swizzle(const Content& in, const vf_transform& t) {
     return out;
 }
 
+// ReverseAttr::transform — CD/attributes/reverse.cpp:46-105
+Content tf_reverse(Content& in, const vf_transform& t) {
+    bool osplat;
+    const Type outType = infer_one(in.type, in.splat, t, osplat);
+    if (in.splat) return move_buffer(in, outType);
+    int64_t spatialDims = 1;
+    for (int i = in.type.rank - 1; i > t.a[0]; --i) spatialDims *= in.type.shape[i];
+    Content out = Content::alloc(outType, outType.elem.dtype, false);
+    const uint64_t es = uint64_t(dtype_bits(outType.elem.dtype) / 8);
+    copy_to(in, out.mdata(), type_bytes(in.type));  // getValues<StorageType>() copied into the new buffer
+    const int64_t n = outType.numel();
+    uint8_t* p = out.mdata();
+    std::vector<uint8_t> tmp(es);
+    for (int64_t first = 0; first + spatialDims <= n; first += spatialDims)
+        for (int64_t lo = first, hi = first + spatialDims - 1; lo < hi; ++lo, --hi) {
+            std::memcpy(tmp.data(), p + uint64_t(lo) * es, es);
+            std::memcpy(p + uint64_t(lo) * es, p + uint64_t(hi) * es, es);
+            std::memcpy(p + uint64_t(hi) * es, tmp.data(), es);
+        }
+    return out;
+}
+
+// BroadcastAttr::transform — CD/attributes/broadcast.cpp:85-124
+Content tf_broadcast(Content& in, const vf_transform& t) {
+    bool osplat;
+    const Type outType = infer_one(in.type, in.splat, t, osplat);
+    if (in.splat) return move_buffer(in, outType);  // the single element is copied (:91-93)
+    if (dtype_bits(in.storage) < 8) fail(VF_ERR_UNSUPPORTED, "Broadcast of sub-byte storage");
+    Content out = Content::alloc(outType, in.storage, false);
+    int perm[VF_MAX_RANK];
+    int64_t ms[VF_MAX_RANK];
+    order_to_perm(in.type.order ? in.type.order : identity_order(in.type.rank), in.type.rank, perm);
+    for (int i = 0; i < in.type.rank; ++i) ms[i] = in.type.shape[perm[i]];
+    int index = 0;
+    for (int i = 0; i < in.type.rank; ++i)
+        if (perm[i] == t.a[0]) index = i;
+    int64_t preDims = 1, afterDims = 1;
+    for (int i = 0; i < index; ++i) preDims *= ms[i];
+    for (int i = index; i < in.type.rank; ++i) afterDims *= ms[i];
+    const int64_t expandDim = ms[index], value = t.a[1];
+    if (expandDim == 0 || value % expandDim) fail(VF_ERR_SHAPE, "Can't broadcast from %lld to %lld", (long long)expandDim, (long long)value);
+    const int64_t factor = value / expandDim;
+    const uint64_t singleCopySize = uint64_t(afterDims) * uint64_t(dtype_bits(in.storage) / 8);
+    for (int64_t pre = 0; pre < preDims; ++pre)
+        for (int64_t f = 0; f < factor; ++f)
+            std::memcpy(out.mdata() + singleCopySize * uint64_t(pre * factor + f), in.ptr + singleCopySize * uint64_t(pre), singleCopySize);
+    return out;
+}
+
+// ExpandDilatedAttr::transform — CD/attributes/expand_dilated.cpp:88-131
+Content tf_expand_dilated(const Content& in, const vf_transform& t) {
+    bool osplat;
+    const Type outType = infer_one(in.type, in.splat, t, osplat);
+    if (dtype_bits(in.storage) < 8) fail(VF_ERR_UNSUPPORTED, "ExpandDilated of sub-byte storage");
+    Content out = Content::alloc(outType, in.storage, false);
+    fill_with_zero(out);
+    const uint64_t es = uint64_t(dtype_bits(in.storage) / 8);
+    const int64_t OC = in.type.shape[0], IC = in.type.shape[1], KY = in.type.shape[2], KX = in.type.shape[3];
+    const int64_t dKY = outType.shape[2], dKX = outType.shape[3];
+    for (int64_t oc = 0; oc < OC; ++oc)
+        for (int64_t ic = 0; ic < IC; ++ic)
+            for (int64_t ky = 0; ky < KY; ++ky)
+                for (int64_t kx = 0; kx < KX; ++kx) {
+                    const int64_t dky = ky + (t.a[0] - 1) * ky, dkx = kx + (t.a[1] - 1) * kx;
+                    const int64_t outRawInd = dkx + dky * dKX + ic * dKX * dKY + oc * dKX * dKY * IC;
+                    const int64_t inRawInd = kx + ky * KX + ic * KX * KY + oc * KX * KY * IC;
+                    std::memcpy(out.mdata() + uint64_t(outRawInd) * es, in.ptr + (in.splat ? 0 : uint64_t(inRawInd) * es), es);
+                }
+    return out;
+}
+
+// ScalarMultInverseAttr::transform — CD/attributes/inverse.cpp:52-66
+Content tf_inverse(const Content& in, const vf_transform& t) {
+    bool osplat;
+    const Type outType = infer_one(in.type, in.splat, t, osplat);
+    Content out = Content::alloc(outType, VF_DT_F32, in.splat);
+    Reader r(in);
+    float* o = reinterpret_cast<float*>(out.mdata());
+    const int64_t n = out.splat ? 1 : outType.numel();
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = r.f(i);
+        if (!std::isnormal(v)) fail(VF_ERR_NOT_NORMAL, "Taking inverse of a non-normal (e.g. zero/nan/...) float");
+        o[i] = 1.f / v;
+    }
+    return out;
+}
+
 // RelocateWeightsTableAttr::transform — CD/attributes/relocate_weights_table.cpp:203-292
 Content tf_relocate(const Content& in, const vf_transform& t) {
     bool osplat;
@@ -1454,6 +1599,7 @@ Content apply(Content& in, const vf_transform& t, int nthreads) {
     switch (t.kind) {
     case VF_T_CAST_ELEM_TYPE:
     case VF_T_RESHAPE:
+    case VF_T_CHANGE_SHAPE_AND_ELEM_TYPE:  // change_shape_and_elem_type.cpp:77-79
     case VF_T_LAYOUT_CAST: {  // moveBuffer: cast_elem_type.cpp:35-37, reshape.cpp:87-89, layout_cast.cpp:82-84
         const Type ty = infer_one(in.type, in.splat, t, osplat);
         return move_buffer(in, ty);
@@ -1473,6 +1619,10 @@ Content apply(Content& in, const vf_transform& t, int nthreads) {
     case VF_T_SPARSIFY: return tf_sparsify(in, t, nthreads);
     case VF_T_SWIZZLE_CONSTANT: return tf_swizzle(in, t);
     case VF_T_RELOCATE_WEIGHTS_TABLE: return tf_relocate(in, t);
+    case VF_T_REVERSE: return tf_reverse(in, t);
+    case VF_T_BROADCAST: return tf_broadcast(in, t);
+    case VF_T_EXPAND_DILATED: return tf_expand_dilated(in, t);
+    case VF_T_SCALAR_MULT_INVERSE: return tf_inverse(in, t);
     default: fail(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }

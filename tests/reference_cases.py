@@ -431,6 +431,88 @@ def relocate_weights_table(be):
         [100, 7, 3, 3, 100, 7, 3, 3]
 
 
+def reverse(be):
+    """UT:813-846 ReverseCWise, UT:848-881 ReverseNWise, UT:883-906 Reverse_Splat: the dims behind the axis are
+    reversed as one run."""
+    N, C, H, W = 2, 3, 4, 5
+    t = TType([N, C, H, W], F32)
+    vals = np.arange(N * C * H * W, dtype=np.float32)
+    x = vals.reshape(N, C, H, W)
+    out = ContentAttr(vals, t, ContentSetup(t).reverse(1)).fold(be)
+    assert out.type == t and not out.is_splat
+    assert np.array_equal(out.values(np.float32).reshape(N, C, H, W), x[:, :, ::-1, ::-1])
+    out = ContentAttr(vals, t, ContentSetup(t).reverse(0)).fold(be)
+    assert np.array_equal(out.values(np.float32).reshape(N, C, H, W), x[:, ::-1, ::-1, ::-1])
+    out = ContentAttr(np.array([42.0], np.float32), t, ContentSetup(t).reverse(0), is_splat=True).fold(be)
+    assert out.is_splat and out.values(np.float32).tolist() == [42.0] * (N * C * H * W)
+
+
+def expand_dilated(be):
+    """UT:1435-1482 ExpandDilated, UT:1484-1533 ExpandDilated_Splat: a 5x5 kernel with dilations 3x3 becomes
+    13x13 with zeros between the taps; the result is never a splat."""
+    OC, IC, KY, KX, dil = 2, 2, 5, 5, 3
+    I32 = abi.VF_DT_I32
+    t = TType([OC, IC, KY, KX], I32)
+    dK = KY + (KY - 1) * (dil - 1)
+    for vals in (np.arange(OC * IC * KY * KX, dtype=np.int32), np.full(OC * IC * KY * KX, 42, np.int32)):
+        out = ContentAttr(vals, t, ContentSetup(t).expandDilated([dil, dil])).fold(be)
+        assert out.type == TType([OC, IC, dK, dK], I32) and not out.is_splat
+        exp = np.zeros((OC, IC, dK, dK), np.int32)
+        exp[:, :, ::dil, ::dil] = vals.reshape(OC, IC, KY, KX)
+        assert np.array_equal(out.values(np.int32).reshape(OC, IC, dK, dK), exp)
+
+
+def scalar_mult_inverse(be):
+    """UT:2181-2211 ScalarMultInverse, UT:2213-2238 ScalarMultInverse_Splat: 1.f / v in f32."""
+    t = TType([1, 2, 3, 4], F32)
+    vals = np.arange(24, dtype=np.float32)
+    vals[0] = 42.0
+    out = ContentAttr(vals, t, ContentSetup(t).scalarMultInverse()).fold(be)
+    assert out.type == t and not out.is_splat
+    assert np.array_equal(out.values(np.float32), np.float32(1.0) / vals)
+    out = ContentAttr(np.array([42.0], np.float32), t, ContentSetup(t).scalarMultInverse(), is_splat=True).fold(be)
+    assert out.is_splat and np.array_equal(out.values(np.float32), np.full(24, np.float32(1.0) / np.float32(42.0)))
+
+
+def change_shape_and_elem_type(be):
+    """UT:1752-1776, UT:1778-1820 (per-axis types whose axis moves with the shape), UT:1822-1843 (float storage
+    read as si32): only the type changes, the bytes stay."""
+    t = TType([2, 1, 1, 8], U8)
+    vals = np.arange(16, dtype=np.uint8)
+    q = Elem.uniform(U8, F32, 0.078431372549019607, 128, 0, 255)
+    out = ContentAttr(vals, t, ContentSetup(t).changeShapeAndElemType([1, 2, 1, 8], q)).fold(be)
+    assert out.type == TType([1, 2, 1, 8], q) and not out.is_splat and out.bytes().tolist() == vals.tolist()
+    q1 = Elem.per_axis(U8, F16, [0.5, 0.5], [127, 127], 0, 0, 255)
+    q2 = Elem.per_axis(U8, F16, [0.5, 0.5], [127, 127], 1, 0, 255)
+    s1 = ContentSetup(t).castElemType(q1)
+    o1 = ContentAttr(vals, t, s1).fold(be)
+    o2 = ContentAttr(vals, t, s1.changeShapeAndElemType([1, 2, 1, 8], q2)).fold(be)
+    assert o1.type == TType([2, 1, 1, 8], q1) and o2.type == TType([1, 2, 1, 8], q2) and o1.type != o2.type
+    assert o1.bytes().tolist() == vals.tolist() and o2.bytes().tolist() == vals.tolist()
+    tf = TType([2, 1, 1, 8], F32)
+    fv = np.arange(16, dtype=np.float32)
+    out = ContentAttr(fv, tf, ContentSetup(tf).changeShapeAndElemType([1, 2, 1, 8], abi.VF_DT_I32)).fold(be)
+    assert out.type == TType([1, 2, 1, 8], abi.VF_DT_I32) and out.values(np.int32).tolist() == list(range(16))
+
+
+def broadcast(be):
+    """lit dialect/VPU/passes/multi_cluster_for_concat_37XX.mlir:234 and add_explicit_padding_before_nce_permute.mlir:265
+    (the lists only; no folded values are checked there): a 1x1x1x1 constant broadcast over dim 0, two broadcasts in a
+    row, and a non-splat block repeated along a middle dim (broadcast.cpp:94-121)."""
+    t = TType([1, 1, 1, 1], F32)
+    s = ContentSetup(t).broadcast(0, 16).reshape([16, 1, 1, 1]).castElemType(F16)
+    out = ContentAttr(np.array([0.015625], np.float32), t, s).fold(be)
+    assert out.type == TType([16, 1, 1, 1], F16) and out.values(np.float16).tolist() == [0.015625] * 16
+    t2 = TType([1, 1], F16)
+    out = ContentAttr(np.array([3.0], np.float16), t2, ContentSetup(t2).broadcast(1, 77).broadcast(0, 77)).fold(be)
+    assert out.type == TType([77, 77], F16) and out.values(np.float16).tolist() == [3.0] * (77 * 77)
+    t3 = TType([2, 3, 2], U8)
+    x = np.arange(12, dtype=np.uint8).reshape(2, 3, 2)
+    out = ContentAttr(x, t3, ContentSetup(t3).broadcast(1, 6)).fold(be)
+    assert out.type == TType([2, 6, 2], U8)
+    assert np.array_equal(out.values(np.uint8).reshape(2, 6, 2), np.concatenate([x, x], axis=1))
+
+
 def sparsity_ptr_stepping(be):
     """lit dialect/VPU/passes/recompute_sparsity_ptrs.mlir:12-31: a 16x16x4x4 filter has sparsity-map rows of
     align(256, 128) / 8 = 32 bytes (map type 16x1x1x256xi1), so the sparsity pointers step by 32"""
@@ -448,5 +530,6 @@ FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequ
               pad_uniform_quant, pad_per_axis_quant, bit_pack, bit_pack_quant, get_sparsity_map,
               get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
               convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain, copy_to_i4,
-              copy_to_i1, convert_elem_type_sub_byte, swizzle_constant, relocate_weights_table]
+              copy_to_i1, convert_elem_type_sub_byte, swizzle_constant, relocate_weights_table, reverse, expand_dilated,
+              scalar_mult_inverse, change_shape_and_elem_type, broadcast]
 TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale, sparsity_ptr_stepping]

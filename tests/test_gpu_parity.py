@@ -766,3 +766,123 @@ def test_relocate_weights_table_errors(gpu, oracle):
     with pytest.raises(VfoldError) as e:  # not a table of 32-bit integers
         ContentAttr(tab.astype(np.float32), f, ContentSetup(f).relocateWeightsTablePointers([0], 0, [0], 64, 16)).fold(gpu)
     assert e.value.status == abi.VF_ERR_UNSUPPORTED
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Reverse / Broadcast / ExpandDilated / ScalarMultInverse / ChangeShapeAndElemType and Reshape's type rules
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [F32, F16, abi.VF_DT_BF16, I8, U8])
+@pytest.mark.parametrize("axis", [0, 1, 2])
+def test_reverse(gpu, oracle, dt, axis):
+    rng = np.random.default_rng(axis * 7 + dt)
+    shape = [3, 5, 4, 7]
+    t = TType(shape, dt)
+    x = rng.integers(0, 200, shape).astype(abi.DTYPE_NUMPY.get(dt, np.uint16))
+    both(ContentAttr(x, t, ContentSetup(t).reverse(axis)), gpu, oracle)
+    if dt == F32:  # storage f32 under an f16 type: the values are converted on the way
+        both(ContentAttr(x * 0.37, t, ContentSetup(t).castElemType(F16).reverse(axis)), gpu, oracle)
+    if dt == U8:
+        q = Elem.uniform(U8, F32, 0.1, 3, 0, 255)
+        both(ContentAttr(x, t, ContentSetup(t).castElemType(q).reorder(abi.ORDER_NHWC).reverse(axis)), gpu, oracle)
+
+
+@pytest.mark.gpu
+def test_reverse_errors(gpu):
+    from vpux_plugin_b200.lib import VfoldError
+    t = TType([2, 3, 4], abi.VF_DT_I32)
+    with pytest.raises(VfoldError) as e:
+        ContentAttr(np.zeros(24, np.int32), t, ContentSetup(t).reverse(0)).fold(gpu)
+    assert e.value.status == abi.VF_ERR_UNSUPPORTED
+    t = TType([2, 3, 4], F32)
+    with pytest.raises(VfoldError) as e:
+        ContentAttr(np.zeros(24, np.float32), t, ContentSetup(t).reverse(2)).fold(gpu)
+    assert e.value.status == abi.VF_ERR_INVALID_ARG
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("order", [0x1234, abi.ORDER_NHWC, 0x4321])
+@pytest.mark.parametrize("axis,value", [(0, 6), (1, 9), (2, 4), (3, 10)])
+def test_broadcast(gpu, oracle, order, axis, value):
+    rng = np.random.default_rng(axis + order)
+    shape = [2, 3, 4, 5]
+    t = TType(shape, F16)
+    x = rng.standard_normal(shape).astype(np.float16)
+    s = ContentSetup(t).reorder(order).broadcast(axis, value)
+    if value % shape[axis]:
+        from vpux_plugin_b200.lib import VfoldError
+        with pytest.raises(VfoldError) as e:
+            ContentAttr(x, t, s).fold(gpu)
+        assert e.value.status == abi.VF_ERR_SHAPE
+        with pytest.raises(Exception):
+            ContentAttr(x, t, s).fold(oracle)
+    else:
+        both(ContentAttr(x, t, s), gpu, oracle)
+    one = TType([1, 1, 1, 1], F32)
+    both(ContentAttr(np.array([2.5], np.float32), one, ContentSetup(one).broadcast(axis, value), is_splat=True), gpu, oracle)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dil", [(1, 1), (2, 3), (3, 1)])
+def test_expand_dilated(gpu, oracle, dil):
+    rng = np.random.default_rng(dil[0] * 5 + dil[1])
+    shape = [4, 6, 3, 5]
+    t = TType(shape, U8)
+    x = rng.integers(0, 256, shape).astype(np.uint8)
+    both(ContentAttr(x, t, ContentSetup(t).expandDilated(dil)), gpu, oracle)
+    q = Elem.uniform(U8, F32, 0.05, 131, 0, 255)  # the gaps hold the zero point
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(q).expandDilated(dil)), gpu, oracle)
+    qa = Elem.per_axis(U8, F32, [0.1, 0.2, 0.3, 0.4], [1, 20, 3, 40], 0, 0, 255)  # ... of their output channel
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(qa).expandDilated(dil)), gpu, oracle)
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(qa).reorder(abi.ORDER_NHWC).expandDilated(dil)), gpu, oracle)
+    tf = TType(shape, F16)
+    both(ContentAttr(np.array([1.5], np.float16), tf, ContentSetup(tf).expandDilated(dil), is_splat=True), gpu, oracle)
+
+
+@pytest.mark.gpu
+def test_scalar_mult_inverse(gpu, oracle):
+    from vpux_plugin_b200.lib import VfoldError
+    rng = np.random.default_rng(12)
+    t = TType([64, 129], F32)
+    x = (rng.standard_normal((64, 129)) * 100).astype(np.float32)
+    x[x == 0] = 1.0
+    both(ContentAttr(x, t, ContentSetup(t).scalarMultInverse()), gpu, oracle)
+    h = TType([64, 129], F16)
+    both(ContentAttr(x.astype(np.float16), h, ContentSetup(h).scalarMultInverse()), gpu, oracle)
+    for bad in (0.0, np.inf, np.nan, 1e-40):
+        y = x.copy()
+        y[17, 5] = bad
+        for be in (gpu, oracle):
+            with pytest.raises(Exception) as e:
+                ContentAttr(y, t, ContentSetup(t).scalarMultInverse()).fold(be)
+            assert e.value.status == abi.VF_ERR_NOT_NORMAL
+    # the context is usable afterwards
+    both(ContentAttr(x, t, ContentSetup(t).scalarMultInverse()), gpu, oracle)
+
+
+@pytest.mark.gpu
+def test_reshape_type_rules(gpu, oracle):
+    """changeShape (core/type_interfaces.cpp:208-231): a non-identity order survives a reshape of the same rank
+    and rejects another rank; a per-axis type follows its axis into the new shape."""
+    rng = np.random.default_rng(13)
+    t = TType([2, 3, 4, 5], F16)
+    x = rng.standard_normal([2, 3, 4, 5]).astype(np.float16)
+    a = both(ContentAttr(x, t, ContentSetup(t).reorder(abi.ORDER_NHWC).reshape([6, 1, 4, 5]).reorder(0x1234)), gpu, oracle)
+    assert a.type.order in (0, 0x1234)
+    mid = ContentAttr(x, t, ContentSetup(t).reorder(abi.ORDER_NHWC).reshape([6, 1, 4, 5])).infer(gpu)[0]
+    assert mid.order == abi.ORDER_NHWC
+    for be in (gpu, oracle):
+        with pytest.raises(Exception) as e:
+            ContentAttr(x, t, ContentSetup(t).reorder(abi.ORDER_NHWC).reshape([6, 20])).fold(be)
+        assert e.value.status == abi.VF_ERR_SHAPE
+    q = Elem.per_axis(U8, F32, [0.5, 0.25, 0.125], [1, 2, 3], 1, 0, 255)
+    tu = TType([2, 3, 4, 5], U8)
+    u = rng.integers(0, 256, [2, 3, 4, 5]).astype(np.uint8)
+    s = ContentSetup(tu).castElemType(q)
+    out = both(ContentAttr(u, tu, s.reshape([2, 3, 20]).dequantize()), gpu, oracle)
+    assert out.type.shape[:3] == [2, 3, 20]
+    moved = ContentAttr(u, tu, s.reshape([1, 2, 3, 20])).infer(gpu)[0]
+    assert moved.elem.axis == 2
+    for be in (gpu, oracle):  # the axis cannot be found in the new shape and no longer fits it
+        with pytest.raises(Exception) as e:
+            ContentAttr(u, tu, s.reshape([6, 4, 5])).fold(be)
+        assert e.value.status == abi.VF_ERR_SHAPE

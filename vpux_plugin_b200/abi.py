@@ -25,6 +25,7 @@ VF_ERR_BUFFER_TOO_SMALL = -10
 VF_ERR_ALIGNMENT = -11
 VF_ERR_RANGE = -12
 VF_ERR_QUANT_RANGE = -13
+VF_ERR_NOT_NORMAL = -14
 VF_ERR_CUDA = -20
 VF_ERR_NO_DEVICE = -21
 VF_ERR_OOM = -22
@@ -50,7 +51,8 @@ VF_MEM_HOST, VF_MEM_HOST_PINNED, VF_MEM_DEVICE = 0, 1, 2
 
 (VF_T_CAST_ELEM_TYPE, VF_T_CONVERT_ELEM_TYPE, VF_T_DEQUANTIZE, VF_T_QUANTIZE, VF_T_RESCALE, VF_T_ADD, VF_T_RESHAPE,
  VF_T_REORDER, VF_T_MEM_PERMUTE, VF_T_TRANSPOSE, VF_T_LAYOUT_CAST, VF_T_PAD_WITH_ZERO, VF_T_BIT_PACK,
- VF_T_GET_SPARSITY_MAP, VF_T_SPARSIFY, VF_T_SUBVIEW, VF_T_SWIZZLE_CONSTANT, VF_T_RELOCATE_WEIGHTS_TABLE) = range(1, 19)
+ VF_T_GET_SPARSITY_MAP, VF_T_SPARSIFY, VF_T_SUBVIEW, VF_T_SWIZZLE_CONSTANT, VF_T_RELOCATE_WEIGHTS_TABLE, VF_T_REVERSE,
+ VF_T_BROADCAST, VF_T_EXPAND_DILATED, VF_T_SCALAR_MULT_INVERSE, VF_T_CHANGE_SHAPE_AND_ELEM_TYPE) = range(1, 24)
 VF_ARCH_NPU37XX, VF_ARCH_NPU40XX = 3, 4
 
 VF_RANGE_MINMAX, VF_RANGE_ABSMAX = 0, 1

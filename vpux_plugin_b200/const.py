@@ -164,6 +164,36 @@ class ContentSetup:
             r.alignment = int(weights_compression.get("alignment", 0) or 0)
         return self._add(t, keep)
 
+    def reverse(self, axis):
+        t = self._t(abi.VF_T_REVERSE)
+        t.rank = 1
+        t.a[0] = int(axis)
+        return self._add(t)
+
+    def broadcast(self, axis, value):
+        t = self._t(abi.VF_T_BROADCAST)
+        t.rank = 2
+        t.a[0], t.a[1] = int(axis), int(value)
+        return self._add(t)
+
+    def expandDilated(self, dilations):
+        t = self._t(abi.VF_T_EXPAND_DILATED)
+        t.rank = 2
+        t.a[0], t.a[1] = int(dilations[0]), int(dilations[1])
+        return self._add(t)
+
+    def scalarMultInverse(self):
+        return self._add(self._t(abi.VF_T_SCALAR_MULT_INVERSE))
+
+    def changeShapeAndElemType(self, shape, elem):
+        elem = elem if isinstance(elem, Elem) else Elem(elem)
+        t = self._t(abi.VF_T_CHANGE_SHAPE_AND_ELEM_TYPE)
+        t.rank = len(shape)
+        for i, s in enumerate(shape):
+            t.a[i] = int(s)
+        t.elem = elem.pod()
+        return self._add(t, elem)
+
     def getSparsityMap(self):
         return self._add(self._t(abi.VF_T_GET_SPARSITY_MAP))
 

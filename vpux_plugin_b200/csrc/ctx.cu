@@ -114,6 +114,7 @@ void flags_check(vf_ctx* ctx) {
     if (f[2]) raise(VF_ERR_SHAPE, "numActualElements smaller than the number of non-sparse elements");
     if (f[3]) raise(VF_ERR_RANGE, "weights table: scale needs a post-shift or rescaled bias is out of range");
     if (f[4]) raise(VF_ERR_ALIGNMENT, "weights table: pointer must be a multiple of 16");
+    if (f[6]) raise(VF_ERR_NOT_NORMAL, "Taking inverse of a non-normal (e.g. zero/nan/...) float");
 }
 
 }  // namespace vf

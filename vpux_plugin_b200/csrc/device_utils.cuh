@@ -20,7 +20,8 @@ enum : int {
     VF_FLAG_OVERFLOW = 2,      // an output buffer was too small (Sparsify with supplied counts)
     VF_FLAG_TABLE_RANGE = 3,   // weights table: post-shift needed / bias outside int32
     VF_FLAG_TABLE_ALIGN = 4,   // weights table: pointer not 16-byte aligned
-    VF_FLAG_NAN = 5            // NaN met where the reference's behaviour is undefined
+    VF_FLAG_NAN = 5,           // NaN met where the reference's behaviour is undefined
+    VF_FLAG_NOT_NORMAL = 6     // ScalarMultInverse of zero, a subnormal, an infinity or NaN
 };
 
 __device__ __forceinline__ void set_flag(int* flags, int slot) {

@@ -299,6 +299,31 @@ DContent do_transpose(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     return do_permute(ctx, in, ot, mp);
 }
 
+// fill values of Content::fillWithZero (utils/content.cpp:190-237) for a buffer of type `ot` stored as `storage`:
+// zero, the zero point, or one zero point per output channel (`fill_dim` = memory dim that holds dim 0)
+void zero_fill_values(const Type& ot, int storage, std::vector<uint8_t>& fill, int64_t& n_fill, int& fill_dim) {
+    const int es = dtype_bits(storage) / 8;
+    int p[VF_MAX_RANK];
+    ot.perm(p);
+    n_fill = 1;
+    fill_dim = 0;
+    const Elem& e = ot.elem;
+    if (e.kind == VF_ELEM_QUANT_PER_AXIS) {
+        if (ot.rank != 4) raise(VF_ERR_UNSUPPORTED, "Unsupported shape size %d", ot.rank);
+        if (e.axis != 0) raise(VF_ERR_UNSUPPORTED, "Only per-channel quantization is supported");
+        n_fill = ot.shape[0];
+        fill.assign(size_t(n_fill) * es, 0);
+        for (int64_t i = 0; i < n_fill; ++i) zp_to_storage(storage, e.zps[size_t(i)], fill.data() + i * es);
+        for (int i = 0; i < ot.rank; ++i)
+            if (p[i] == 0) fill_dim = i;
+    } else if (e.kind == VF_ELEM_QUANT_UNIFORM) {
+        fill.assign(size_t(es), 0);
+        zp_to_storage(storage, e.zps[0], fill.data());
+    } else {
+        fill.assign(size_t(es), 0);
+    }
+}
+
 DContent do_pad(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     bool os;
     const Type ot = infer_one(in.type, in.splat, t, os);
@@ -321,25 +346,10 @@ DContent do_pad(vf_ctx* ctx, DContent& in, const vf_transform& t) {
         g.src_stride[i] = ist[i];
         g.offset[i] = t.a[p[i]];
     }
-    // fill values — Content::fillWithZero, utils/content.cpp:190-237
     std::vector<uint8_t> fill;
     int64_t n_fill = 1;
     int fill_dim = 0;
-    const Elem& e = ot.elem;
-    if (e.kind == VF_ELEM_QUANT_PER_AXIS) {
-        if (ot.rank != 4) raise(VF_ERR_UNSUPPORTED, "Unsupported shape size %d", ot.rank);
-        if (e.axis != 0) raise(VF_ERR_UNSUPPORTED, "Only per-channel quantization is supported");
-        n_fill = ot.shape[0];
-        fill.assign(size_t(n_fill) * es, 0);
-        for (int64_t i = 0; i < n_fill; ++i) zp_to_storage(in.storage, e.zps[size_t(i)], fill.data() + i * es);
-        for (int i = 0; i < rank; ++i)
-            if (p[i] == 0) fill_dim = i;
-    } else if (e.kind == VF_ELEM_QUANT_UNIFORM) {
-        fill.assign(size_t(es), 0);
-        zp_to_storage(in.storage, e.zps[0], fill.data());
-    } else {
-        fill.assign(size_t(es), 0);
-    }
+    zero_fill_values(ot, in.storage, fill, n_fill, fill_dim);
     DBuf dfill = upload_vec(ctx, fill);
     launch_pad(ctx, in.d, in.splat, out.own.p, g, es, dfill.p, n_fill, fill_dim);
     return out;
@@ -449,12 +459,17 @@ DContent do_sparsify(vf_ctx* ctx, DContent& in, const vf_transform& t, DBuf* kee
 
 DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t);
 DContent do_relocate(vf_ctx* ctx, DContent& in, const vf_transform& t);
+DContent do_reverse(vf_ctx* ctx, DContent& in, const vf_transform& t);
+DContent do_broadcast(vf_ctx* ctx, DContent& in, const vf_transform& t);
+DContent do_expand_dilated(vf_ctx* ctx, DContent& in, const vf_transform& t);
+DContent do_inverse(vf_ctx* ctx, DContent& in, const vf_transform& t);
 
 DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     bool os;
     switch (t.kind) {
     case VF_T_CAST_ELEM_TYPE:
     case VF_T_RESHAPE:
+    case VF_T_CHANGE_SHAPE_AND_ELEM_TYPE:
     case VF_T_LAYOUT_CAST: {
         const Type ot = infer_one(in.type, in.splat, t, os);
         return move_buffer(in, ot);
@@ -474,6 +489,10 @@ DContent apply(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     case VF_T_SPARSIFY: return do_sparsify(ctx, in, t);
     case VF_T_SWIZZLE_CONSTANT: return do_swizzle(ctx, in, t);
     case VF_T_RELOCATE_WEIGHTS_TABLE: return do_relocate(ctx, in, t);
+    case VF_T_REVERSE: return do_reverse(ctx, in, t);
+    case VF_T_BROADCAST: return do_broadcast(ctx, in, t);
+    case VF_T_EXPAND_DILATED: return do_expand_dilated(ctx, in, t);
+    case VF_T_SCALAR_MULT_INVERSE: return do_inverse(ctx, in, t);
     default: raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
 }
@@ -634,6 +653,74 @@ DContent do_relocate(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     }
     if (out.nbytes) VF_CUDA(cudaMemcpyAsync(out.own.p, lin.d, out.nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
     launch_relocate(ctx, static_cast<const int32_t*>(lin.d), out.own.as<int32_t>(), a);
+    return out;
+}
+
+// Reverse — attributes/reverse.cpp:46-105: the content in its logical element type, every run of the dims
+// behind `axis` reversed in place (raw buffer order)
+DContent do_reverse(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    if (in.splat) return move_buffer(in, ot);
+    int64_t run = 1;
+    for (int i = in.type.rank - 1; i > t.a[0]; --i) run *= in.type.shape[i];
+    DContent lin = materialise_logical(ctx, in);
+    DContent out = alloc_like(ctx, ot, ot.elem.dtype, false);
+    launch_reverse(ctx, lin.d, out.own.p, ot.numel(), std::max<int64_t>(run, 1), dtype_bits(ot.elem.dtype) / 8);
+    return out;
+}
+
+// Broadcast — attributes/broadcast.cpp:85-124: storage bytes; the block from the broadcast memory dim inwards
+// is repeated value / extent times
+DContent do_broadcast(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    if (in.splat) return move_buffer(in, ot);
+    const int bits = dtype_bits(in.storage);
+    if (bits < 8) raise(VF_ERR_UNSUPPORTED, "Broadcast of sub-byte storage");
+    int p[VF_MAX_RANK];
+    int64_t ims[VF_MAX_RANK];
+    in.type.perm(p);
+    in.type.mem_shape(ims);
+    int index = 0;
+    for (int i = 0; i < in.type.rank; ++i)
+        if (p[i] == t.a[0]) index = i;
+    int64_t after = 1;
+    for (int i = index; i < in.type.rank; ++i) after *= ims[i];
+    const int64_t extent = ims[index], value = t.a[1];
+    if (extent == 0 || value % extent) raise(VF_ERR_SHAPE, "Can't broadcast from %lld to %lld", (long long)extent, (long long)value);
+    DContent out = alloc_like(ctx, ot, in.storage, false);
+    launch_broadcast(ctx, in.d, out.own.p, ot.numel(), after, value / extent, bits / 8);
+    return out;
+}
+
+// ExpandDilated — attributes/expand_dilated.cpp:88-131
+DContent do_expand_dilated(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    const int bits = dtype_bits(in.storage);
+    if (bits < 8) raise(VF_ERR_UNSUPPORTED, "ExpandDilated of sub-byte storage");
+    DContent out = alloc_like(ctx, ot, in.storage, false);
+    std::vector<uint8_t> fill;
+    int64_t n_fill = 1;
+    int fill_dim = 0;
+    zero_fill_values(ot, in.storage, fill, n_fill, fill_dim);
+    int64_t oms[VF_MAX_RANK];
+    ot.mem_shape(oms);
+    int64_t fill_stride = 1;
+    for (int i = fill_dim + 1; i < ot.rank; ++i) fill_stride *= oms[i];
+    DBuf dfill = upload_vec(ctx, fill);
+    launch_expand_dilated(ctx, in.d, in.splat, out.own.p, ot.numel(), ot.shape[2], ot.shape[3], in.type.shape[2], in.type.shape[3],
+                          t.a[0], t.a[1], dfill.p, n_fill, fill_stride, oms[fill_dim], bits / 8);
+    return out;
+}
+
+// ScalarMultInverse — attributes/inverse.cpp:52-66
+DContent do_inverse(vf_ctx* ctx, DContent& in, const vf_transform& t) {
+    bool os;
+    const Type ot = infer_one(in.type, in.splat, t, os);
+    DContent out = alloc_like(ctx, ot, VF_DT_F32, in.splat);
+    launch_inverse(ctx, in.d, in.storage, out.own.as<float>(), out.count());
     return out;
 }
 

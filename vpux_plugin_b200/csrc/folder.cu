@@ -118,6 +118,16 @@ void put_transform(std::string& s, const vf_transform& t) {
     case VF_T_RESCALE:
     case VF_T_ADD: put(s, t.value); break;
     case VF_T_RESHAPE: put_array(s, t.a, t.rank); break;
+    case VF_T_CHANGE_SHAPE_AND_ELEM_TYPE:
+        put_array(s, t.a, t.rank);
+        put_elem(s, t.elem);
+        break;
+    case VF_T_REVERSE: put(s, t.a[0]); break;
+    case VF_T_BROADCAST:
+    case VF_T_EXPAND_DILATED:
+        put(s, t.a[0]);
+        put(s, t.a[1]);
+        break;
     case VF_T_REORDER:
     case VF_T_TRANSPOSE:
     case VF_T_LAYOUT_CAST: put(s, t.order); break;
@@ -153,7 +163,7 @@ void put_transform(std::string& s, const vf_transform& t) {
         }
         break;
     }
-    default: break;  // Dequantize, GetSparsityMap: no parameters
+    default: break;  // Dequantize, GetSparsityMap, ScalarMultInverse: no parameters
     }
 }
 

@@ -114,6 +114,16 @@ void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table);
 // All tables of `tabs` (each with its d_table) in one launch over a device copy of the list.
 void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs);
 
+// Reverse: every run of `run` consecutive elements reversed; Broadcast: every block of `after` elements written
+// `factor` times; ExpandDilated: OIYX taps spread by the dilations, the gaps filled from `d_fill` (n_fill == 1:
+// one value, else indexed by (o / fill_stride) % fill_extent); ScalarMultInverse: 1.f / v as f32
+void launch_reverse(vf_ctx* ctx, const void* in, void* out, int64_t n, int64_t run, int es);
+void launch_broadcast(vf_ctx* ctx, const void* in, void* out, int64_t n_out, int64_t after, int64_t factor, int es);
+void launch_expand_dilated(vf_ctx* ctx, const void* in, bool in_splat, void* out, int64_t n_out, int64_t dky, int64_t dkx,
+                           int64_t ky, int64_t kx, int64_t dil_y, int64_t dil_x, const void* d_fill, int64_t n_fill,
+                           int64_t fill_stride, int64_t fill_extent, int es);
+void launch_inverse(vf_ctx* ctx, const void* in, int in_dt, float* out, int64_t n);
+
 // RelocateWeightsTable: rows [0, oc) of a weights table `in` -> `out` with columns 0 / 1 rebased
 struct RelocateArgs {
     int64_t oc;                            // rows to patch

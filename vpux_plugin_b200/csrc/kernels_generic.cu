@@ -485,6 +485,72 @@ __global__ void k_weights_table_batch(const TableArgs* __restrict__ tabs, int n,
     weights_table_row(a, u - a.unit_begin, a.d_table, flags);
 }
 
+// ---- Reverse / Broadcast / ExpandDilated / ScalarMultInverse ------------------------------------------
+template <int ES>
+struct ElemBits;
+template <>
+struct ElemBits<1> { using type = uint8_t; };
+template <>
+struct ElemBits<2> { using type = uint16_t; };
+template <>
+struct ElemBits<4> { using type = uint32_t; };
+template <>
+struct ElemBits<8> { using type = uint64_t; };
+
+// Reverse — attributes/reverse.cpp:46-80: every run of `run` consecutive elements of the buffer is reversed
+template <int ES>
+__global__ void k_reverse(const void* __restrict__ in, void* __restrict__ out, int64_t n, int64_t run) {
+    using T = typename ElemBits<ES>::type;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t r = i % run;
+        static_cast<T*>(out)[i] = static_cast<const T*>(in)[i - r + (run - 1 - r)];
+    }
+}
+
+// Broadcast — attributes/broadcast.cpp:85-124: each block of `after` elements is written `factor` times in a row
+template <int ES>
+__global__ void k_broadcast(const void* __restrict__ in, void* __restrict__ out, int64_t n_out, int64_t after, int64_t factor) {
+    using T = typename ElemBits<ES>::type;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int64_t group = after * factor;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += stride) {
+        const int64_t pre = o / group;
+        static_cast<T*>(out)[o] = static_cast<const T*>(in)[pre * after + (o - pre * group) % after];
+    }
+}
+
+// ExpandDilated — attributes/expand_dilated.cpp:88-131: raw OIYX index arithmetic whatever the dims order;
+// positions between the taps hold the fill value (zero, or the zero point of output channel `fill` index)
+template <int ES>
+__global__ void k_expand_dilated(const void* __restrict__ in, int in_splat, void* __restrict__ out, int64_t n_out, int64_t dky,
+                                 int64_t dkx, int64_t ky, int64_t kx, int64_t dil_y, int64_t dil_x,
+                                 const void* __restrict__ fill, int64_t n_fill, int64_t fill_stride, int64_t fill_extent) {
+    using T = typename ElemBits<ES>::type;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += stride) {
+        const int64_t x = o % dkx, y = (o / dkx) % dky, plane = o / (dkx * dky);
+        T v;
+        if (y % dil_y == 0 && x % dil_x == 0) {
+            v = static_cast<const T*>(in)[in_splat ? 0 : (plane * ky + y / dil_y) * kx + x / dil_x];
+        } else {
+            v = static_cast<const T*>(fill)[n_fill > 1 ? (o / fill_stride) % fill_extent : 0];
+        }
+        static_cast<T*>(out)[o] = v;
+    }
+}
+
+// ScalarMultInverse — attributes/inverse.cpp:52-66: 1.f / v in f32; zero, subnormal, infinite or NaN input throws
+__global__ void k_inverse(const void* __restrict__ in, int in_dt, float* __restrict__ out, int64_t n, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = load_as_f32(in, in_dt, i, flags);
+        const uint32_t e = (__float_as_uint(v) >> 23) & 0xFFu;
+        if (e == 0u || e == 0xFFu) set_flag(flags, VF_FLAG_NOT_NORMAL);
+        out[i] = __fdiv_rn(1.0f, v);
+    }
+}
+
 // RelocateWeightsTable — attributes/relocate_weights_table.cpp:203-292. One thread per table row of four
 // 32-bit entries: columns 0 and 1 are rewritten from the cluster's base pointers, columns 2 and 3 are copied.
 // The steps between consecutive channels come from the first two rows of the INPUT table, so the pass writes a
@@ -788,6 +854,42 @@ void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
 void launch_relocate(vf_ctx* ctx, const int32_t* in, int32_t* out, const RelocateArgs& a) {
     if (a.oc <= 0) return;
     k_relocate<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(in, out, a, ctx->d_flags);
+    post_launch(ctx);
+}
+
+#define VF_BY_ELEM_SIZE(es, CALL)                                                   \
+    switch (es) {                                                                   \
+    case 1: { constexpr int ES = 1; CALL; break; }                                  \
+    case 2: { constexpr int ES = 2; CALL; break; }                                  \
+    case 4: { constexpr int ES = 4; CALL; break; }                                  \
+    case 8: { constexpr int ES = 8; CALL; break; }                                  \
+    default: raise(VF_ERR_UNSUPPORTED, "element size %d", es);                      \
+    }
+
+void launch_reverse(vf_ctx* ctx, const void* in, void* out, int64_t n, int64_t run, int es) {
+    if (n <= 0) return;
+    VF_BY_ELEM_SIZE(es, (k_reverse<ES><<<grid_for(n), kBlock, 0, ctx->stream>>>(in, out, n, run)));
+    post_launch(ctx);
+}
+
+void launch_broadcast(vf_ctx* ctx, const void* in, void* out, int64_t n_out, int64_t after, int64_t factor, int es) {
+    if (n_out <= 0) return;
+    VF_BY_ELEM_SIZE(es, (k_broadcast<ES><<<grid_for(n_out), kBlock, 0, ctx->stream>>>(in, out, n_out, after, factor)));
+    post_launch(ctx);
+}
+
+void launch_expand_dilated(vf_ctx* ctx, const void* in, bool in_splat, void* out, int64_t n_out, int64_t dky, int64_t dkx,
+                           int64_t ky, int64_t kx, int64_t dil_y, int64_t dil_x, const void* d_fill, int64_t n_fill,
+                           int64_t fill_stride, int64_t fill_extent, int es) {
+    if (n_out <= 0) return;
+    VF_BY_ELEM_SIZE(es, (k_expand_dilated<ES><<<grid_for(n_out), kBlock, 0, ctx->stream>>>(
+                                in, in_splat ? 1 : 0, out, n_out, dky, dkx, ky, kx, dil_y, dil_x, d_fill, n_fill, fill_stride, fill_extent)));
+    post_launch(ctx);
+}
+
+void launch_inverse(vf_ctx* ctx, const void* in, int in_dt, float* out, int64_t n) {
+    if (n <= 0) return;
+    k_inverse<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, out, n, ctx->d_flags);
     post_launch(ctx);
 }
 

@@ -386,7 +386,7 @@ extern "C" int vf_optimize_transforms(const vf_tensor_type* base, const vf_trans
             Item it;
             it.t = t[i];
             const int k = t[i].kind;
-            if (k == VF_T_CAST_ELEM_TYPE || k == VF_T_CONVERT_ELEM_TYPE || k == VF_T_QUANTIZE) it.elem = Elem::from(t[i].elem);
+            if (k == VF_T_CAST_ELEM_TYPE || k == VF_T_CONVERT_ELEM_TYPE || k == VF_T_QUANTIZE || k == VF_T_CHANGE_SHAPE_AND_ELEM_TYPE) it.elem = Elem::from(t[i].elem);
             if (k == VF_T_SPARSIFY && t[i].num_actual) it.counts.assign(t[i].num_actual, t[i].num_actual + t[i].n_num_actual);
             add_transformation(l, std::move(it), bt);
         }

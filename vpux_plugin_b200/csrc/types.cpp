@@ -178,6 +178,20 @@ static void check_per_axis(const Type& t) {
               t.elem.scales.size(), (long long)t.shape[t.elem.axis]);
 }
 
+// getQuantizedAxis (utils/types.cpp:140-162): where the quantized axis lands after a reshape, or -1
+int quantized_axis(int axis, const int64_t* prev, int prev_rank, const int64_t* next, int next_rank) {
+    if (axis < 0 || axis >= prev_rank || prev[axis] == 1) return -1;
+    int64_t full = 1;
+    for (int i = 0; i <= axis; ++i) full *= prev[i];
+    int64_t acc = 1;
+    for (int i = 0; i < next_rank; ++i) {
+        acc *= next[i];
+        if (acc == full && next[i] == prev[axis]) return i;
+        if (acc > full) break;
+    }
+    return -1;
+}
+
 Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_splat) {
     Type out = in;
     out_splat = in_splat;
@@ -207,15 +221,28 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
     case VF_T_ADD:
         return out;
 
-    case VF_T_RESHAPE: {
+    case VF_T_RESHAPE:
+    case VF_T_CHANGE_SHAPE_AND_ELEM_TYPE: {
+        // changeShape / changeShapeElemType of a ranked tensor (core/type_interfaces.cpp:208-231, 253-269): an
+        // identity order follows the new rank, any other order must fit it; a per-axis type keeps its axis where
+        // getQuantizedAxis finds it in the new shape
         if (t.rank < 1 || t.rank > VF_MAX_RANK) raise(VF_ERR_INVALID_ARG, "Reshape rank %d", t.rank);
-        if (in.elem.kind == VF_ELEM_QUANT_PER_AXIS) raise(VF_ERR_UNSUPPORTED, "Reshape of a per-axis quantized constant is not supported");
         int64_t n = 1;
         for (int i = 0; i < t.rank; ++i) n *= t.a[i];
         if (n != in.numel()) raise(VF_ERR_SHAPE, "Reshape to %lld elements from %lld", (long long)n, (long long)in.numel());
         out.rank = t.rank;
         for (int i = 0; i < VF_MAX_RANK; ++i) out.shape[i] = i < t.rank ? t.a[i] : 0;
-        out.order = identity_order(t.rank);
+        if (in.order == identity_order(in.rank)) out.order = identity_order(t.rank);
+        else if (t.rank != in.rank) raise(VF_ERR_SHAPE, "Order '%x' is incompatible with the new shape", in.order);
+        if (t.kind == VF_T_CHANGE_SHAPE_AND_ELEM_TYPE) {
+            out.elem = Elem::from(t.elem);
+        } else if (in.elem.kind == VF_ELEM_QUANT_PER_AXIS) {
+            const int axis = quantized_axis(in.elem.axis, in.shape, in.rank, t.a, t.rank);
+            if (axis >= 0) out.elem.axis = axis;
+        }
+        if (out.elem.kind == VF_ELEM_QUANT_PER_AXIS && (out.elem.axis < 0 || out.elem.axis >= out.rank))
+            raise(VF_ERR_SHAPE, "Quantized axis '%d' is out of main type rank '%d'", out.elem.axis, out.rank);
+        check_per_axis(out);
         return out;
     }
 
@@ -350,6 +377,44 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
         return out;
     }
 
+    case VF_T_REVERSE: {  // reverse.cpp:35-44, 46-105
+        Elem e = in.elem;
+        if (e.kind == VF_ELEM_QUANT_PER_AXIS) raise(VF_ERR_UNSUPPORTED, "Unexpected data type: per-axis quantized");
+        const int dt = e.dtype;
+        if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32)
+            raise(VF_ERR_UNSUPPORTED, "Unexpected data type: %d", dt);
+        if (!in_splat && (t.a[0] < 0 || t.a[0] >= in.rank - 1))
+            raise(VF_ERR_INVALID_ARG, "Const::Content::reverse: got unexpected content dimension %lld", (long long)t.a[0]);
+        return out;
+    }
+
+    case VF_T_BROADCAST: {  // broadcast.cpp:66-83: the type is padded behind `axis` up to `value`
+        const int64_t axis = t.a[0], value = t.a[1];
+        if (axis < 0 || axis >= in.rank) raise(VF_ERR_INVALID_ARG, "Broadcast axis %lld", (long long)axis);
+        if (value < in.shape[axis])
+            raise(VF_ERR_SHAPE, "Value cannot be broadcasted due to new value's size is less than old one: %lld < %lld", (long long)value, (long long)in.shape[axis]);
+        vf_transform pad{};
+        pad.kind = VF_T_PAD_WITH_ZERO;
+        pad.rank = in.rank;
+        pad.b[axis] = value - in.shape[axis];
+        bool ignored;
+        out = infer_one(in, in_splat, pad, ignored);
+        return out;  // splatness passes through
+    }
+
+    case VF_T_EXPAND_DILATED: {  // getDilatedType, utils/dilated_utils.cpp:11-34
+        if (in.rank != 4) raise(VF_ERR_SHAPE, "Got invalid tensor rank '4'");
+        if (t.a[0] < 1 || t.a[1] < 1) raise(VF_ERR_INVALID_ARG, "dilations must be positive");
+        out.shape[2] = in.shape[2] + (in.shape[2] - 1) * (t.a[0] - 1);
+        out.shape[3] = in.shape[3] + (in.shape[3] - 1) * (t.a[1] - 1);
+        check_per_axis(out);
+        out_splat = false;
+        return out;
+    }
+
+    case VF_T_SCALAR_MULT_INVERSE:  // inverse.cpp:40-50
+        return out;
+
     default:
         raise(VF_ERR_INVALID_ARG, "unknown transformation kind %d", t.kind);
     }
@@ -411,6 +476,7 @@ const char* vf_status_string(int s) {
     case VF_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
     case VF_ERR_RANGE: return "value outside representable range";
     case VF_ERR_QUANT_RANGE: return "cannot derive scale / zero point from range";
+    case VF_ERR_NOT_NORMAL: return "inverse of a non-normal float";
     case VF_ERR_CUDA: return "CUDA error";
     case VF_ERR_NO_DEVICE: return "no CUDA device";
     case VF_ERR_OOM: return "out of memory";
