@@ -569,6 +569,8 @@ int vf_folder_fold(vf_folder* folder, const vf_content* base, uint64_t base_id, 
 int vf_folder_remove(vf_folder* folder, const vf_content* base, uint64_t base_id, const vf_transform* t, int n,
                      char* err, size_t errlen);
 int vf_folder_statistics(vf_folder* folder, vf_folder_stats* out);
+/* Message of the last request that failed in a worker (empty if none). */
+int vf_folder_last_error(vf_folder* folder, char* buf, size_t buflen);
 /* 128-bit hash of a content's storage bytes, computed on the GPU (host memory is uploaded first). The same
  * bytes give the same hash wherever they live and however the buffer is aligned. */
 int vf_content_hash(vf_ctx* ctx, const vf_content* content, uint64_t out[2], char* err, size_t errlen);

@@ -234,6 +234,7 @@ static void foldingInBackground() {  // constant_folding_in_background_tests.cpp
     const auto attr1 = Const::ContentSetup(baseType).subview({0}, {50}).subview({10}, {30}).get(&baseValue, sizeof(baseValue), true);
     const auto attr2 = Const::ContentSetup(baseType).subview({0}, {30}).get(&baseValue, sizeof(baseValue), true);
     folding.enqueueRequest(attr1);
+    folding.waitIdle();  // with two workers the equivalence request could otherwise overtake the fold of attr1
     folding.enqueueRequest(attr1, attr2);
     folding.waitIdle();
     EXPECT(folding.hasContent(attr2));

@@ -222,9 +222,10 @@ def test_many_requests_from_many_workers(oracle):
         q = Elem.uniform(I8, F32, 0.02, 0, -127, 127)
         attrs = []
         for i in range(24):
-            oc, ic = int(rng.integers(8, 40)), int(rng.integers(8, 40)) * 4
+            oc, ic = int(rng.integers(8, 40)), int(rng.integers(4, 20)) * 8
             t = TType([oc, ic, 1, 1], F32)
             x = rng.standard_normal((oc, ic, 1, 1)).astype(np.float32)
+            x[rng.random(x.shape) < 0.5] = 0.0  # sparse enough for the compacted data to fit the dense size
             s = ContentSetup(t).quantize(q).castElemType(q).reorder(abi.ORDER_NHWC)
             if i % 3 == 0:
                 s = s.getSparsityMap()
@@ -236,8 +237,8 @@ def test_many_requests_from_many_workers(oracle):
             folder.enqueue(attrs[i])
         folder.wait_idle()
         st = folder.statistics()
-        assert st["failed"] == 0 and st["cache_size"] == len(attrs)
-        assert st["added"] + st["duplicated"] == len(order)
+        assert st["failed"] == 0, folder.last_error()
+        assert st["cache_size"] == len(attrs) and st["added"] + st["duplicated"] == len(order)
         for a in attrs:
             _same(folder, oracle, a, True)
     finally:

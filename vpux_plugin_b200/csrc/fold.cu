@@ -851,11 +851,21 @@ static void quantize_fold_general(vf_ctx* ctx, DContent& base, const vf_quant_sp
 }
 
 // ---- folding without copyTo (the background folder's cache keeps Const::Content objects) -----------------
-Folded fold_keep(vf_ctx* ctx, const vf_content& base, const vf_transform* t, int n) {
-    if ((n > 0 && !t) || n < 0) raise(VF_ERR_INVALID_ARG, "NULL argument");
+static DContent borrow(const Folded& f) {  // a cached content as the executor's working type (nothing owned)
+    DContent c;
+    c.type = f.type;
+    c.storage = f.storage;
+    c.splat = f.splat;
+    c.d = f.data;
+    c.nbytes = f.nbytes;
+    return c;
+}
+
+Folded fold_keep(vf_ctx* ctx, const vf_content* base, const Folded* resume, const vf_transform* t, int n) {
+    if ((n > 0 && !t) || n < 0 || (!base && !resume)) raise(VF_ERR_INVALID_ARG, "NULL argument");
     check_positions(t, n);
     CallScope scope(ctx, nullptr);
-    DContent cur = upload_base(ctx, base, nullptr);
+    DContent cur = resume ? borrow(*resume) : upload_base(ctx, *base, nullptr);
     for (int i = 0; i < n; ++i) {
         DContent next = apply(ctx, cur, t[i]);
         cur = std::move(next);
@@ -901,17 +911,14 @@ void* upload_keep(vf_ctx* ctx, const vf_content& base, uint64_t* nbytes) {
     return d;
 }
 
-vf_content as_content(const Folded& f, std::vector<double>& sb, std::vector<int64_t>& zb) {
-    vf_content c{};
-    sb.assign(std::max<size_t>(f.type.elem.scales.size(), 1), 0.0);
-    zb.assign(std::max<size_t>(f.type.elem.zps.size(), 1), 0);
-    f.type.export_to(&c.type, sb.data(), zb.data(), int64_t(sb.size()));
-    c.storage_dtype = f.storage;
-    c.is_splat = f.splat ? 1 : 0;
-    c.mem_kind = VF_MEM_DEVICE;
-    c.data = f.data;
-    c.nbytes = f.nbytes;
-    return c;
+uint64_t copy_folded(vf_ctx* ctx, const Folded& f, void* dst, uint64_t dst_bytes, int dst_mem_kind, vf_tensor_type* out_type,
+                     double* scales_buf, int64_t* zps_buf, int64_t params_cap) {
+    CallScope scope(ctx, nullptr);
+    DContent cur = borrow(f);
+    cur.type.export_to(out_type, scales_buf, zps_buf, params_cap);
+    const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_mem_kind, nullptr);
+    scope.finish();
+    return w;
 }
 
 }  // namespace vf

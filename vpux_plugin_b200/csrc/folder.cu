@@ -453,10 +453,7 @@ struct vf_folder {
         const std::string partial_key = base.key + list_key(req.list.t.data(), idx);
         std::shared_ptr<Entry> partial = get_content(partial_key);
         if (!partial) return false;
-        std::vector<double> sb;
-        std::vector<int64_t> zb;
-        const vf_content from = as_content(partial->f, sb, zb);
-        Folded f = fold_keep(ctx, from, req.list.t.data() + idx, n - idx);
+        Folded f = fold_keep(ctx, nullptr, &partial->f, req.list.t.data() + idx, n - idx);
         add_content(key, std::move(f));
         remove_content(partial_key);
         count(&vf_folder_stats::partial);
@@ -476,7 +473,7 @@ struct vf_folder {
             return;
         }
         if (try_partial(ctx, req, base, key)) return;
-        Folded f = fold_keep(ctx, base.c, req.list.t.data(), int(req.list.t.size()));
+        Folded f = fold_keep(ctx, &base.c, nullptr, req.list.t.data(), int(req.list.t.size()));
         add_content(key, std::move(f));
     }
 
@@ -653,20 +650,24 @@ int vf_folder_fold(vf_folder* f, const vf_content* base, uint64_t base_id, const
         resolve(f->front, b, r);
         std::shared_ptr<Entry> hit = f->get_content(r.key + list_key(t, n));
         if (from_cache) *from_cache = hit ? 1 : 0;
-        char e[512] = {0};
-        int st;
         if (hit) {  // Content::copyTo of the cached content
-            std::vector<double> sb;
-            std::vector<int64_t> zb;
-            const vf_content c = as_content(hit->f, sb, zb);
-            st = vf_fold(f->front, &c, nullptr, 0, dst, dst_bytes, dst_mem_kind, dst_written, out_type, scales_buf, zps_buf,
-                         params_cap, nullptr, e, sizeof(e));
-        } else {  // fold(bypassCache): not added to the cache, as in the reference
-            st = vf_fold(f->front, &r.c, t, n, dst, dst_bytes, dst_mem_kind, dst_written, out_type, scales_buf, zps_buf,
-                         params_cap, nullptr, e, sizeof(e));
+            const uint64_t w = copy_folded(f->front, hit->f, dst, dst_bytes, dst_mem_kind, out_type, scales_buf, zps_buf, params_cap);
+            if (dst_written) *dst_written = w;
+            return;
         }
+        // fold(bypassCache): not added to the cache, as in the reference
+        char e[512] = {0};
+        const int st = vf_fold(f->front, &r.c, t, n, dst, dst_bytes, dst_mem_kind, dst_written, out_type, scales_buf, zps_buf,
+                               params_cap, nullptr, e, sizeof(e));
         if (st != VF_OK) raise(st, "%s", e);
     });
+}
+
+int vf_folder_last_error(vf_folder* f, char* buf, size_t buflen) {
+    if (!f || !buf || !buflen) return VF_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(f->smu);
+    snprintf(buf, buflen, "%s", f->last_error.c_str());
+    return VF_OK;
 }
 
 int vf_folder_statistics(vf_folder* f, vf_folder_stats* out) {

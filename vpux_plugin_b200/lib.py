@@ -350,6 +350,12 @@ class Folder:
         err = C.create_string_buffer(512)
         self._check(self.lib.vf_folder_remove(self.h, C.byref(content), C.c_uint64(base_id), tr, n, err, C.c_size_t(512)), err)
 
+    def last_error(self):
+        buf = C.create_string_buffer(512)
+        self.lib.vf_folder_last_error.restype = C.c_int
+        self.lib.vf_folder_last_error(self.h, buf, C.c_size_t(512))
+        return buf.value.decode(errors="replace")
+
     def statistics(self):
         s = abi.FolderStats()
         self.lib.vf_folder_statistics(self.h, C.byref(s))
