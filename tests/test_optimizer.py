@@ -39,6 +39,12 @@ def _items(setup):
             n = e.nparams if e.kind != K.VF_ELEM_PLAIN else 0
             out.append(("cast" if k == K.VF_T_CAST_ELEM_TYPE else "convert", e.kind, e.dtype,
                         [e.scales[i] for i in range(n)], [e.zps[i] for i in range(n)]))
+        elif k == K.VF_T_CHANGE_SHAPE_AND_ELEM_TYPE:
+            e = t.elem
+            n = e.nparams if e.kind != K.VF_ELEM_PLAIN else 0
+            out.append(("changeshape", list(t.a[:r]), e.axis, [e.scales[i] for i in range(n)]))
+        elif k == K.VF_T_DEQUANTIZE:
+            out.append(("dequantize",))
         elif k == K.VF_T_RELOCATE_WEIGHTS_TABLE:
             r = t.relocate
             out.append(("relocate", list(r.weights_ptr[:r.n_clusters]), r.sparsity_ptr, list(r.offsets[:r.n_clusters]),
@@ -221,6 +227,79 @@ def test_relocate_swap_folds_to_the_same_table_on_the_oracle(oracle):
 @pytest.mark.gpu
 def test_relocate_swap_folds_to_the_same_table_on_the_gpu(gpu):
     _relocate_fold_pair(gpu, 32)
+
+
+def _per_axis(axis, n):
+    # the reference's test types: u8 storage, f16 expressed, scales 1..n, zero points 0 (CS:478-496)
+    return Elem.per_axis(U8, F16, [float(i + 1) for i in range(n)], [0] * n, axis, 0, 255)
+
+
+# CS:1377-1403 swapChangeShapeAndElemTypeAndSubViewParams: base shape, (cast axis, n), (changeShape shape, axis, n),
+# SubView -> expected cast scales, changeShape (shape, axis, scales), SubView. The reference's fifth case has rank 6.
+CHANGE_SHAPE_SWAPS = [
+    ([1, 4, 1, 2], (1, 4), ([4, 2, 1, 1], 0, 4), ([0, 0, 0, 0], [3, 2, 1, 1]),
+     [1.0, 2.0, 3.0], ([3, 2, 1, 1], 0, [1.0, 2.0, 3.0]), ([0, 0, 0, 0], [1, 3, 1, 2])),
+    ([1, 4, 1, 2], (1, 4), ([4, 2, 1, 1], 0, 4), ([1, 0, 0, 0], [2, 2, 1, 1]),
+     [2.0, 3.0], ([2, 2, 1, 1], 0, [2.0, 3.0]), ([0, 1, 0, 0], [1, 2, 1, 2])),
+    ([1, 4, 2, 2], (1, 4), ([1, 4, 4], 1, 4), ([0, 0, 0], [1, 2, 4]),
+     [1.0, 2.0], ([1, 2, 4], 1, [1.0, 2.0]), ([0, 0, 0, 0], [1, 2, 2, 2])),
+    ([1, 8, 4], (1, 8), ([1, 8, 2, 2], 1, 8), ([0, 1, 0, 0], [1, 4, 2, 2]),
+     [2.0, 3.0, 4.0, 5.0], ([1, 4, 2, 2], 1, [2.0, 3.0, 4.0, 5.0]), ([0, 1, 0], [1, 4, 4])),
+]
+
+
+@pytest.mark.parametrize("base,cast,change,sub,exp_cast,exp_change,exp_sub", CHANGE_SHAPE_SWAPS)
+def test_swap_change_shape_and_elem_type_and_subview(base, cast, change, sub, exp_cast, exp_change, exp_sub):
+    s = S(base, U8).castElemType(_per_axis(*cast)).changeShapeAndElemType(change[0], _per_axis(change[1], change[2]))
+    got = _items(s.subview(*sub).optimized())
+    assert got[0] == ("subview", exp_sub[0], exp_sub[1])
+    assert got[1][0] == "cast" and got[1][3] == exp_cast
+    assert got[2] == ("changeshape", exp_change[0], exp_change[1], exp_change[2])
+    assert len(got) == 3
+
+
+@pytest.mark.parametrize("base,cast,change,sub", [
+    ([1, 4, 1, 2], (1, 4), ([8, 1], 0, 8), ([0, 0], [4, 1])),
+    ([1, 8, 8, 2], (1, 8), ([1, 8, 4, 4], 1, 8), ([0, 0, 3, 0], [1, 8, 1, 4]))])
+def test_do_not_swap_change_shape_and_elem_type_and_subview(base, cast, change, sub):
+    # CS:1433-1440
+    s = S(base, U8).castElemType(_per_axis(*cast)).changeShapeAndElemType(change[0], _per_axis(change[1], change[2]))
+    got = _items(s.subview(*sub).optimized())
+    assert [g[0] for g in got] == ["cast", "changeshape", "subview"]
+    assert got[1] == ("changeshape", change[0], change[1], [float(i + 1) for i in range(change[2])])
+    assert got[2] == ("subview", sub[0], sub[1])
+
+
+@pytest.mark.parametrize("base,reshape,cast_axis,new_axis", [
+    ([2, 3, 1, 1], [1, 2, 3, 1], 1, 2), ([1, 2, 3, 1], [2, 1, 3, 1], 2, 2), ([1, 3, 1, 2], [3, 2, 1, 1], 1, 0)])
+def test_swap_quantize_transformations_and_reshape(base, reshape, cast_axis, new_axis):
+    # CS:1547-1576: a Reshape behind the Dequantize of a per-axis type moves in front of it as a
+    # ChangeShapeAndElemType with the axis found in the new shape
+    got = _items(S(base, U8).castElemType(_per_axis(cast_axis, 3)).dequantize().reshape(reshape).optimized())
+    assert got[0][0] == "cast" and got[0][3] == [1.0, 2.0, 3.0]
+    assert got[1] == ("changeshape", reshape, new_axis, [1.0, 2.0, 3.0])
+    assert got[2] == ("dequantize",) and len(got) == 3
+
+
+def test_swap_per_tensor_quantize_transformations_and_reshape():
+    # CS:1578-1602: per-tensor types need no ChangeShapeAndElemType
+    q = Elem.uniform(U8, F32, 0.078, 128, 0, 255)
+    got = _items(S([16, 32, 1, 1], U8).castElemType(q).dequantize().reshape([16, 8, 2, 2]).optimized())
+    assert [g[0] for g in got] == ["cast", "reshape", "dequantize"] and got[1] == ("reshape", [16, 8, 2, 2])
+
+
+def test_per_axis_reshape_rewrites_fold_to_the_same_bytes(oracle):
+    rng = np.random.default_rng(41)
+    for base, reshape, axis in (([2, 3, 1, 1], [1, 2, 3, 1], 1), ([1, 2, 3, 1], [2, 1, 3, 1], 2), ([4, 6, 2, 2], [4, 6, 4], 1)):
+        t = TType(base, U8)
+        x = rng.integers(0, 256, base).astype(np.uint8)
+        n = base[axis]
+        q = Elem.per_axis(U8, F32, [0.5 * (i + 1) for i in range(n)], [int(v) for v in rng.integers(0, 9, n)], axis, 0, 255)
+        s = ContentSetup(t).castElemType(q).dequantize().reshape(reshape)
+        so = s.optimized()
+        assert K.VF_T_CHANGE_SHAPE_AND_ELEM_TYPE in so.names()
+        a, b = ContentAttr(x, t, s).fold(oracle), ContentAttr(x, t, so).fold(oracle)
+        assert a.type == b.type and np.array_equal(a.bytes(), b.bytes())
 
 
 def test_move_reshape_before_and_chains():

@@ -7,9 +7,8 @@
 //   moveReshapeBefore               utils/transformations.cpp:657-712
 // Pure host code. A shorter list means fewer passes over the data on the device, and a SubView moved to the
 // front means only the needed slab is uploaded and folded.
-// Not covered (their transformations are outside this library): ChangeShapeAndElemType and Fuse as list
-// entries; a Reshape is therefore not moved before a Dequantize of a per-axis type (that rewrite needs
-// ChangeShapeAndElemType, transformations.cpp:338-378).
+// Not covered: Fuse as a list entry (moveTransformationIntoFuse); the library folds fused constants through
+// vf_fuse, whose parts carry their own lists.
 #include <algorithm>
 #include <functional>
 
@@ -232,6 +231,24 @@ Result move_subview_before(List& l, size_t cur, const Type& base) {
         }
         break;
     }
+    case VF_T_CHANGE_SHAPE_AND_ELEM_TYPE: {  // prepareChangeShapeSwap (:125-155)
+        int64_t no[VF_MAX_RANK], ns[VF_MAX_RANK];
+        if (!slice_input_shape(prev_in.shape, prev_in.rank, prev.t.a, prev.t.rank, sub.t.a, sub.t.b, no, ns)) return {cur, false};
+        if (prev.elem.kind == VF_ELEM_QUANT_PER_AXIS) {  // the type of the slice: parameters of the kept channels
+            const int ax = prev.elem.axis;
+            if (ax < 0 || ax >= rank || sub.t.a[ax] < 0 || sub.t.a[ax] + sub.t.b[ax] > int64_t(prev.elem.scales.size())) return {cur, false};
+            prev.elem.scales.assign(prev.elem.scales.begin() + sub.t.a[ax], prev.elem.scales.begin() + sub.t.a[ax] + sub.t.b[ax]);
+            prev.elem.zps.assign(prev.elem.zps.begin() + sub.t.a[ax], prev.elem.zps.begin() + sub.t.a[ax] + sub.t.b[ax]);
+        }
+        prev.t.rank = sub.t.rank;
+        for (int i = 0; i < sub.t.rank; ++i) prev.t.a[i] = sub.t.b[i];
+        sub.t.rank = prev_in.rank;
+        for (int i = 0; i < prev_in.rank; ++i) {
+            sub.t.a[i] = no[i];
+            sub.t.b[i] = ns[i];
+        }
+        break;
+    }
     case VF_T_PAD_WITH_ZERO: {  // preparePadWithZeroSwap
         int64_t no[VF_MAX_RANK], ns[VF_MAX_RANK], pb[VF_MAX_RANK], pa[VF_MAX_RANK];
         for (int i = 0; i < rank; ++i) {
@@ -331,7 +348,24 @@ Result move_reshape_before(List& l, size_t cur, const Type& base) {
         if (prev_in.elem.quantized() || prev.elem.quantized()) return {cur, false};
         break;
     case VF_T_DEQUANTIZE:
-        if (prev_in.elem.kind == VF_ELEM_QUANT_PER_AXIS) return {cur, false};  // needs ChangeShapeAndElemType
+        if (prev_in.elem.kind == VF_ELEM_QUANT_PER_AXIS) {  // prepareDequantizeSwap (:338-378)
+            // the quantized axis must be found again in the new shape, counting from the innermost dim; the
+            // Reshape then becomes a ChangeShapeAndElemType that carries the per-axis type with the new axis
+            Item& reshape = l[cur];
+            const int dim = prev_in.elem.axis;
+            int64_t in_lower = 1;
+            for (int i = dim; i < prev_in.rank; ++i) in_lower *= prev_in.shape[i];
+            int64_t out_lower = 1;
+            int new_dim = reshape.t.rank - 1;
+            for (; new_dim >= 0; --new_dim) {
+                out_lower *= reshape.t.a[new_dim];
+                if (out_lower >= in_lower) break;
+            }
+            if (new_dim < 0 || out_lower != in_lower || reshape.t.a[new_dim] != prev_in.shape[dim]) return {cur, false};
+            reshape.t.kind = VF_T_CHANGE_SHAPE_AND_ELEM_TYPE;
+            reshape.elem = prev_in.elem;
+            reshape.elem.axis = new_dim;
+        }
         break;
     default: return {cur, false};
     }
