@@ -82,7 +82,9 @@ typedef enum vf_dtype {
     VF_DT_U64 = 12,
     VF_DT_I4 = 13,
     VF_DT_U4 = 14,
-    VF_DT_I1 = 15 /* 1-bit, signless; sparsity maps */
+    VF_DT_I1 = 15, /* 1-bit, signless; sparsity maps */
+    VF_DT_F8E4M3FN = 16, /* vpux::type::float8_e4m3 (no infinities) */
+    VF_DT_F8E5M2 = 17    /* vpux::type::float8_e5m2 */
 } vf_dtype;
 
 typedef enum vf_elem_kind {

@@ -51,6 +51,12 @@ class Oracle:
         L.orc_f32_to_bf16.argtypes = [C.c_uint32]
         L.orc_bf16_to_f32.restype = C.c_uint32
         L.orc_bf16_to_f32.argtypes = [C.c_uint16]
+        for name in ("orc_f32_to_f8e4m3", "orc_f32_to_f8e5m2"):
+            getattr(L, name).restype = C.c_uint8
+            getattr(L, name).argtypes = [C.c_uint32]
+        for name in ("orc_f8e4m3_to_f32", "orc_f8e5m2_to_f32"):
+            getattr(L, name).restype = C.c_uint32
+            getattr(L, name).argtypes = [C.c_uint8]
         L.orc_calc_scale_zp.argtypes = [C.c_double, C.c_double, C.c_double, C.c_double, C.POINTER(C.c_double),
                                         C.POINTER(C.c_int64)]
         L.orc_fake_quantize.restype = C.c_float
@@ -86,6 +92,15 @@ class Oracle:
 
     def f32_to_bf16(self, bits):
         return self.lib.orc_f32_to_bf16(int(bits))
+
+    def f32_to_f8(self, value, e5m2=False):
+        """float -> float8_e4m3 / float8_e5m2 bits"""
+        bits = int(np.float32(value).view(np.uint32))
+        return int(self.lib.orc_f32_to_f8e5m2(bits) if e5m2 else self.lib.orc_f32_to_f8e4m3(bits))
+
+    def f8_to_f32(self, code, e5m2=False):
+        bits = self.lib.orc_f8e5m2_to_f32(int(code)) if e5m2 else self.lib.orc_f8e4m3_to_f32(int(code))
+        return float(np.uint32(bits).view(np.float32))
 
     def calc_scale_zp(self, qmin, qmax, rmin, rmax):
         s, z = C.c_double(), C.c_int64()

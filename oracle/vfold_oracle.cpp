@@ -164,6 +164,70 @@ uint16_t f32_to_f16_clamped(float v) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// 8-bit floats — src/vpux_utils/src/core/type/float8_e4m3.cpp, float8_e5m2.cpp
+// ---------------------------------------------------------------------------------------------
+// float8_e4m3::operator float (:125-129): the reference looks |bits| up in a table of the 128 magnitudes
+// (subnormals m * 2^-9, normals (1 + m/8) * 2^(e-7), 0x7f = NaN) and ors the sign in.
+float f8e4m3_to_f32(uint8_t b) {
+    const uint32_t mag = b & 0x7Fu;
+    float v;
+    if (mag == 0x7Fu) v = std::numeric_limits<float>::quiet_NaN();
+    else if ((mag >> 3) == 0) v = std::ldexp(float(mag & 7u), -9);
+    else v = std::ldexp(1.0f + float(mag & 7u) / 8.0f, int(mag >> 3) - 7);
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    u |= uint32_t(b & 0x80u) << 24;
+    memcpy(&v, &u, 4);
+    return v;
+}
+// f32_to_f8e4m3_bits (:52-113). For |value| < 2^-37 the reference shifts a 32-bit word by 32 or more, which is
+// undefined; every defined shift of that branch yields a signed zero and so does this restatement.
+uint8_t f32_to_f8e4m3(float value) {
+    const uint32_t f32_s_mask = 0x80000000u, f32_e_mask = 0x7F800000u, f32_m_mask = 0x007FFFFFu;
+    const uint32_t f8_e_mask = 0x78u << 24, f8_m_mask = 0x07u << 24, f8_m_hidden_one_mask = 0x08000000u;
+    const uint32_t round_half = 0x01FFFFFFu, round_norm = 0x007FFFFFu, round_even = 0x00800000u, round_odd = 0x01800000u;
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    uint8_t f8 = uint8_t((bits & f32_s_mask) >> 24);
+    const uint32_t e_field = bits & f32_e_mask;
+    if (e_field == f32_e_mask) return uint8_t(f8 | 0x7Fu);  // no infinity in this type: NaN
+    if (e_field == 0) return f8;
+    int32_t exp8 = int32_t(e_field >> 23) - (127 - 7);
+    uint32_t fractional = (bits & f32_m_mask) << 4;
+    if ((fractional & round_half) == round_odd || (fractional & round_norm) != 0) {
+        fractional += round_even;
+        if (fractional & f8_e_mask) {
+            fractional &= f8_e_mask;
+            ++exp8;
+        }
+    }
+    fractional &= f8_m_mask;
+    if (exp8 > 15) return uint8_t(f8 | 0x7Fu);
+    if (exp8 > 0) return uint8_t(f8 | (exp8 << 3) | (fractional >> 24));
+    fractional = f8_m_hidden_one_mask | ((bits & f32_m_mask) << 4);
+    const int32_t by = 1 - exp8;
+    if (by >= 32) return f8;
+    const int32_t shift = exp8 < -15 ? 0 : int32_t(1u << by);
+    const uint32_t sticky = (fractional & uint32_t(shift - 1)) ? 1u : 0u;
+    fractional = (fractional >> by) | sticky;
+    if ((fractional & round_half) == round_odd || (fractional & round_norm) != 0) fractional += round_even;
+    return uint8_t(f8 | (fractional >> 24));
+}
+// f32_to_f8e5m2_bits (:76-80) over emulate_f8e5m2_on_fp16 (:27-74); float8_e5m2::operator float (:94-96)
+uint8_t f32_to_f8e5m2(float value) {
+    uint16_t h = f32_to_f16(value);
+    const bool can_round = (h & 0x7F00) < 0x7B00;
+    const bool is_naninf = (h & 0x7C00) == 0x7C00;
+    const uint16_t rnmask = h & 0x00FF, rnmask_tie = h & 0x0180;
+    if (!is_naninf && can_round) h = uint16_t(h + (((rnmask > 0x0080) || (rnmask_tie == 0x0180)) << 8));
+    h &= 0xFF00;
+    return uint8_t(h >> 8);
+}
+float f8e5m2_to_f32(uint8_t b) {
+    return f16_to_f32(uint16_t(uint16_t(b) << 8));
+}
+
+// ---------------------------------------------------------------------------------------------
 // dtype helpers
 // ---------------------------------------------------------------------------------------------
 int dtype_bits(int dt) {
@@ -173,6 +237,7 @@ int dtype_bits(int dt) {
     case VF_DT_BF16: return 16;
     case VF_DT_F64: return 64;
     case VF_DT_I8: case VF_DT_U8: return 8;
+    case VF_DT_F8E4M3FN: case VF_DT_F8E5M2: return 8;
     case VF_DT_I16: case VF_DT_U16: return 16;
     case VF_DT_I32: case VF_DT_U32: return 32;
     case VF_DT_I64: case VF_DT_U64: return 64;
@@ -182,7 +247,7 @@ int dtype_bits(int dt) {
     }
 }
 bool dtype_is_float(int dt) {
-    return dt == VF_DT_F32 || dt == VF_DT_F16 || dt == VF_DT_BF16 || dt == VF_DT_F64;
+    return dt == VF_DT_F32 || dt == VF_DT_F16 || dt == VF_DT_BF16 || dt == VF_DT_F64 || dt == VF_DT_F8E4M3FN || dt == VF_DT_F8E5M2;
 }
 bool dtype_is_signed_int(int dt) {
     return dt == VF_DT_I8 || dt == VF_DT_I16 || dt == VF_DT_I32 || dt == VF_DT_I64 || dt == VF_DT_I4;
@@ -344,6 +409,8 @@ Val load_val(const uint8_t* p, int dt, int64_t idx) {
     case VF_DT_F16: { uint16_t h; memcpy(&h, p + idx * 2, 2); v.is_float = true; v.ff = f16_to_f32(h); v.f = v.ff; break; }
     case VF_DT_BF16: { uint16_t h; memcpy(&h, p + idx * 2, 2); v.is_float = true; v.ff = bf16_to_f32(h); v.f = v.ff; break; }
     case VF_DT_F64: { double d; memcpy(&d, p + idx * 8, 8); v.is_float = true; v.f = d; break; }
+    case VF_DT_F8E4M3FN: v.is_float = true; v.ff = f8e4m3_to_f32(p[idx]); v.f = v.ff; break;
+    case VF_DT_F8E5M2: v.is_float = true; v.ff = f8e5m2_to_f32(p[idx]); v.f = v.ff; break;
     case VF_DT_I8: v.i = int8_t(p[idx]); break;
     case VF_DT_U8: v.is_unsigned = true; v.u = p[idx]; v.i = p[idx]; break;
     case VF_DT_I16: { int16_t x; memcpy(&x, p + idx * 2, 2); v.i = x; break; }
@@ -1276,8 +1343,10 @@ struct SparseReader {
     float fval;
     int64_t ival;
     SparseReader(const Content& c, int64_t value): r(c), dt(c.type.elem.dtype) {
-        if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32)
+        const bool f8 = dt == VF_DT_F8E4M3FN || dt == VF_DT_F8E5M2;  // sparsify.cpp:197-200, get_sparsity_map.cpp:111-116
+        if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32 && !f8)
             fail(VF_ERR_UNSUPPORTED, "Unexpected weights data type");
+        if (f8 && value != 0) fail(VF_ERR_UNSUPPORTED, "8-bit float storage with a non-zero zero point");
         es = dtype_bits(dt) / 8;
         ival = value;
         if (dt == VF_DT_I8 && (value < -128 || value > 127)) fail(VF_ERR_CHECKED_CAST, "sparsify value outside i8");
@@ -1306,6 +1375,16 @@ struct SparseReader {
             const uint16_t h = f32_to_bf16(r.f(i));
             memcpy(e.bytes, &h, 2);
             e.is_zero = bf16_to_f32(h) == fval;
+            break;
+        }
+        case VF_DT_F8E4M3FN: {
+            e.bytes[0] = f32_to_f8e4m3(r.f(i));
+            e.is_zero = f8e4m3_to_f32(e.bytes[0]) == fval;
+            break;
+        }
+        case VF_DT_F8E5M2: {
+            e.bytes[0] = f32_to_f8e5m2(r.f(i));
+            e.is_zero = f8e5m2_to_f32(e.bytes[0]) == fval;
             break;
         }
         default: {
@@ -1707,6 +1786,8 @@ uint64_t copy_to(const Content& c, uint8_t* dst, uint64_t dst_bytes) {
             memcpy(dst + i * 2, &h, 2);
             break;
         }
+        case VF_DT_F8E4M3FN: dst[i] = f32_to_f8e4m3(r.f(i)); break;  // CvtHelper<float8_e4m3>, content.hpp:66-71
+        case VF_DT_F8E5M2: dst[i] = f32_to_f8e5m2(r.f(i)); break;    // CvtHelper<float8_e5m2>, content.hpp:74-79
         case VF_DT_F64: {
             const Val v = r.at(i);
             const double d = v.is_float ? v.f : (v.is_unsigned ? double(v.u) : double(v.i));
@@ -1857,6 +1938,19 @@ uint32_t orc_bf16_to_f32(uint16_t h) {
 }
 uint16_t orc_f32_to_f16_clamped(uint32_t b) {
     return f32_to_f16_clamped(u2f(b));
+}
+
+uint8_t orc_f32_to_f8e4m3(uint32_t b) {
+    return f32_to_f8e4m3(u2f(b));
+}
+uint32_t orc_f8e4m3_to_f32(uint8_t v) {
+    return f2u(f8e4m3_to_f32(v));
+}
+uint8_t orc_f32_to_f8e5m2(uint32_t b) {
+    return f32_to_f8e5m2(u2f(b));
+}
+uint32_t orc_f8e5m2_to_f32(uint8_t v) {
+    return f2u(f8e5m2_to_f32(v));
 }
 
 void orc_f32_to_f16_n(const uint32_t* in, uint16_t* out, uint64_t n) {

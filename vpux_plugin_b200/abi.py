@@ -33,17 +33,18 @@ VF_ERR_CAPACITY = -23
 
 # vf_dtype
 (VF_DT_INVALID, VF_DT_F32, VF_DT_F16, VF_DT_BF16, VF_DT_F64, VF_DT_I8, VF_DT_U8, VF_DT_I16, VF_DT_U16, VF_DT_I32,
- VF_DT_U32, VF_DT_I64, VF_DT_U64, VF_DT_I4, VF_DT_U4, VF_DT_I1) = range(16)
+ VF_DT_U32, VF_DT_I64, VF_DT_U64, VF_DT_I4, VF_DT_U4, VF_DT_I1, VF_DT_F8E4M3FN, VF_DT_F8E5M2) = range(18)
 
 DTYPE_BITS = {
     VF_DT_F32: 32, VF_DT_F16: 16, VF_DT_BF16: 16, VF_DT_F64: 64, VF_DT_I8: 8, VF_DT_U8: 8, VF_DT_I16: 16,
     VF_DT_U16: 16, VF_DT_I32: 32, VF_DT_U32: 32, VF_DT_I64: 64, VF_DT_U64: 64, VF_DT_I4: 4, VF_DT_U4: 4, VF_DT_I1: 1,
+    VF_DT_F8E4M3FN: 8, VF_DT_F8E5M2: 8,
 }
 # numpy carrier for the raw bytes of each dtype (bf16 travels as uint16 bit patterns)
 DTYPE_NUMPY = {
     VF_DT_F32: np.float32, VF_DT_F16: np.float16, VF_DT_BF16: np.uint16, VF_DT_F64: np.float64, VF_DT_I8: np.int8,
     VF_DT_U8: np.uint8, VF_DT_I16: np.int16, VF_DT_U16: np.uint16, VF_DT_I32: np.int32, VF_DT_U32: np.uint32,
-    VF_DT_I64: np.int64, VF_DT_U64: np.uint64,
+    VF_DT_I64: np.int64, VF_DT_U64: np.uint64, VF_DT_F8E4M3FN: np.uint8, VF_DT_F8E5M2: np.uint8,
 }
 
 VF_ELEM_PLAIN, VF_ELEM_QUANT_UNIFORM, VF_ELEM_QUANT_PER_AXIS = 0, 1, 2

@@ -79,8 +79,12 @@ __device__ __forceinline__ uint16_t f32_to_f16_clamped_bits(float f) {
     if ((h & 0x7FFFu) == 0x7C00u) h = uint16_t((h & 0x8000u) | 0x7BFFu);
     return h;
 }
+// float16::operator float (src/vpux_utils/src/core/type/float16.cpp:118-144) widens the bits, so a NaN keeps its
+// sign and payload; the hardware conversion would return the canonical NaN.
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
-    return __half2float(__ushort_as_half(h));
+    const float f = __half2float(__ushort_as_half(h));
+    const bool nan = (h & 0x7C00u) == 0x7C00u && (h & 0x03FFu) != 0;
+    return nan ? __uint_as_float((uint32_t(h & 0x8000u) << 16) | 0x7F800000u | (uint32_t(h & 0x03FFu) << 13)) : f;
 }
 // bfloat16::round_to_nearest_even (src/vpux_utils/include/vpux/utils/core/type/bfloat16.hpp:85-87):
 // half an ulp is added only when the kept LSB is 1, then the low half is truncated.
@@ -92,6 +96,60 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {
     return __uint_as_float(uint32_t(b) << 16);
 }
 
+// float8_e4m3 (src/vpux_utils/src/core/type/float8_e4m3.cpp): no infinities, 0x7f / 0xff are NaN.
+// Decoding (:125-129) is a table lookup in the reference; the table holds sign-less (exp, mantissa) values.
+__host__ __device__ __forceinline__ uint32_t f8e4m3_bits_to_f32_bits(uint8_t b) {
+    const uint32_t sign = uint32_t(b & 0x80u) << 24, mag = b & 0x7Fu;
+    if (mag == 0x7Fu) return sign | 0x7FC00000u;
+    const uint32_t e = mag >> 3, m = mag & 7u;
+    if (e == 0) {  // subnormal: m * 2^-9, exact in f32
+        if (m == 0) return sign;
+        const int lead = m >= 4 ? 2 : (m >= 2 ? 1 : 0);  // position of the leading one
+        return sign | (uint32_t(127 - 9 + lead) << 23) | ((m << (23 - lead)) & 0x007FFFFFu);
+    }
+    return sign | ((e + 120u) << 23) | (m << 20);
+}
+// f32_to_f8e4m3_bits (:52-113): round to nearest even on the 3 kept mantissa bits, overflow and NaN / Inf
+// give NaN, f32 subnormals give a signed zero. Inputs below 2^-37 make the reference shift a 32-bit value by
+// 32 or more (undefined); they give a signed zero here, the value every in-range shift produces.
+__host__ __device__ __forceinline__ uint8_t f32_bits_to_f8e4m3_bits(uint32_t u) {
+    uint8_t out = uint8_t((u & 0x80000000u) >> 24);
+    const uint32_t e_field = u & 0x7F800000u;
+    if (e_field == 0x7F800000u) return out | 0x7Fu;
+    if (e_field == 0) return out;
+    int32_t e8 = int32_t(e_field >> 23) - 120;
+    uint32_t frac = (u & 0x007FFFFFu) << 4;  // f8 mantissa in bits 24..26, the rest below
+    if ((frac & 0x01FFFFFFu) == 0x01800000u || (frac & 0x007FFFFFu) != 0) {
+        frac += 0x00800000u;
+        if (frac & 0x78000000u) {
+            frac &= 0x78000000u;
+            ++e8;
+        }
+    }
+    frac &= 0x07000000u;
+    if (e8 > 15) return out | 0x7Fu;
+    if (e8 > 0) return out | uint8_t((uint32_t(e8) << 3) | (frac >> 24));
+    frac = 0x08000000u | ((u & 0x007FFFFFu) << 4);  // hidden one restored
+    const int rshift = 1 - e8;                        // >= 1
+    if (rshift >= 32) return out;
+    const uint32_t lost_mask = e8 < -15 ? 0xFFFFFFFFu : ((1u << rshift) - 1u);
+    const uint32_t sticky = (frac & lost_mask) ? 1u : 0u;
+    frac = (frac >> rshift) | sticky;
+    if ((frac & 0x01FFFFFFu) == 0x01800000u || (frac & 0x007FFFFFu) != 0) frac += 0x00800000u;
+    return out | uint8_t(frac >> 24);
+}
+// float8_e5m2 (src/vpux_utils/src/core/type/float8_e5m2.cpp:27-84): the value goes through float16, whose
+// low byte is rounded to nearest even unless the result would leave the finite range, then truncated.
+__host__ __device__ __forceinline__ uint8_t f16_bits_to_f8e5m2_bits(uint16_t h) {
+    const bool can_round = (h & 0x7F00u) < 0x7B00u;
+    const bool is_naninf = (h & 0x7C00u) == 0x7C00u;
+    if (!is_naninf && can_round) {
+        const uint16_t grs = h & 0x00FFu, tie = h & 0x0180u;
+        h = uint16_t(h + ((grs > 0x0080u || tie == 0x0180u) ? 0x0100u : 0u));
+    }
+    return uint8_t(h >> 8);
+}
+
 // ---- getValues<float>() / getValues<intN>() element reads -------------------------------------------
 // Content::getValues<T>() converts the storage element through checked_cast
 // (src/vpux_utils/include/vpux/utils/core/checked_cast.hpp:43-141); a failing check sets VF_FLAG_CHECKED_CAST.
@@ -100,6 +158,8 @@ __device__ __forceinline__ float load_as_f32(const void* p, int dt, int64_t i, i
     case VF_DT_F32: return static_cast<const float*>(p)[i];
     case VF_DT_F16: return f16_bits_to_f32(static_cast<const uint16_t*>(p)[i]);
     case VF_DT_BF16: return bf16_bits_to_f32(static_cast<const uint16_t*>(p)[i]);
+    case VF_DT_F8E4M3FN: return __uint_as_float(f8e4m3_bits_to_f32_bits(static_cast<const uint8_t*>(p)[i]));
+    case VF_DT_F8E5M2: return f16_bits_to_f32(uint16_t(uint16_t(static_cast<const uint8_t*>(p)[i]) << 8));
     case VF_DT_F64: {
         const double d = static_cast<const double*>(p)[i];
         const float f = __double2float_rn(d);
@@ -158,7 +218,9 @@ __device__ __forceinline__ long long load_as_int(const void* p, int dt, int64_t 
     switch (dt) {
     case VF_DT_F32:
     case VF_DT_F16:
-    case VF_DT_BF16: {
+    case VF_DT_BF16:
+    case VF_DT_F8E4M3FN:
+    case VF_DT_F8E5M2: {
         // checked_cast<Int>(float): compared in float against float(limit), then truncated (:106-117)
         const float f = load_as_f32(p, dt, i, nullptr);
         const float fhi = __double2float_rn(hi), flo = __double2float_rn(lo);
@@ -312,6 +374,8 @@ __device__ __forceinline__ bool is_dense(const void* p, int dt, int64_t i, long 
     case VF_DT_U8: return static_cast<const uint8_t*>(p)[i] != uint8_t(iv);
     case VF_DT_F16: return f16_bits_to_f32(static_cast<const uint16_t*>(p)[i]) != fv;
     case VF_DT_BF16: return bf16_bits_to_f32(static_cast<const uint16_t*>(p)[i]) != fv;
+    case VF_DT_F8E4M3FN:
+    case VF_DT_F8E5M2: return (static_cast<const uint8_t*>(p)[i] & 0x7Fu) != 0;  // compared as float with 0: -0 is zero, NaN is not
     default: return static_cast<const float*>(p)[i] != fv;
     }
 }

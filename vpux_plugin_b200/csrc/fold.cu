@@ -133,11 +133,14 @@ int64_t sparsify_value(const Elem& e) {
     if (!e.quantized()) return 0;
     int64_t zp;
     if (!e.single_zp(zp)) raise(VF_ERR_ZERO_POINTS, "Not all zero-points are equal");
+    if (zp != 0 && (e.dtype == VF_DT_F8E4M3FN || e.dtype == VF_DT_F8E5M2))
+        raise(VF_ERR_UNSUPPORTED, "8-bit float storage with a non-zero zero point");
     return zp;
 }
 
 void check_sparse_dtype(int dt) {
-    if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32)
+    if (dt != VF_DT_I8 && dt != VF_DT_U8 && dt != VF_DT_F16 && dt != VF_DT_BF16 && dt != VF_DT_F32 && dt != VF_DT_F8E4M3FN &&
+        dt != VF_DT_F8E5M2)
         raise(VF_ERR_UNSUPPORTED, "Unexpected weights data type: %d", dt);
 }
 
@@ -802,7 +805,8 @@ static void quantize_fold_general(vf_ctx* ctx, DContent& base, const vf_quant_sp
     int64_t unit_len = 0;
     const int64_t units = unit_count(base.type, spec, unit_len);
     if (base.splat) raise(VF_ERR_SPLAT, "weight quantization of a splat constant is not supported");
-    if (!dtype_is_float(base.storage)) raise(VF_ERR_UNSUPPORTED, "weight quantization takes f32 / f16 / bf16 input");
+    if (base.storage != VF_DT_F32 && base.storage != VF_DT_F16 && base.storage != VF_DT_BF16)
+        raise(VF_ERR_UNSUPPORTED, "weight quantization takes f32 / f16 / bf16 input");
     DBuf ds(ctx, size_t(units) * 8), dz(ctx, size_t(units) * 8);
     launch_unit_stats(ctx, base.d, base.storage, units, unit_len, spec.range_mode, spec.qmin, spec.qmax, ds.as<double>(),
                       dz.as<int64_t>(), nullptr, nullptr);

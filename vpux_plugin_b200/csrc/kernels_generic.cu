@@ -71,10 +71,13 @@ __global__ void k_convert(const void* __restrict__ in, int in_dt, int in_splat, 
         case VF_DT_F32: static_cast<float*>(out)[i] = load_as_f32(in, in_dt, s, flags); break;
         case VF_DT_F16: static_cast<uint16_t*>(out)[i] = f32_to_f16_clamped_bits(load_as_f32(in, in_dt, s, flags)); break;
         case VF_DT_BF16: static_cast<uint16_t*>(out)[i] = f32_to_bf16_bits(load_as_f32(in, in_dt, s, flags)); break;
+        case VF_DT_F8E4M3FN: static_cast<uint8_t*>(out)[i] = f32_bits_to_f8e4m3_bits(__float_as_uint(load_as_f32(in, in_dt, s, flags))); break;
+        case VF_DT_F8E5M2: static_cast<uint8_t*>(out)[i] = f16_bits_to_f8e5m2_bits(f32_to_f16_bits(load_as_f32(in, in_dt, s, flags))); break;
         case VF_DT_F64: {
             double d;
             if (in_dt == VF_DT_F64) d = static_cast<const double*>(in)[s];
-            else if (in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16) d = double(load_as_f32(in, in_dt, s, flags));
+            else if (in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16 || in_dt == VF_DT_F8E4M3FN || in_dt == VF_DT_F8E5M2)
+                d = double(load_as_f32(in, in_dt, s, flags));
             else if (in_dt == VF_DT_U64) d = double(static_cast<const unsigned long long*>(in)[s]);
             else d = double(load_as_int(in, in_dt, s, VF_DT_I64, flags));
             static_cast<double*>(out)[i] = d;

@@ -42,7 +42,9 @@ __device__ __forceinline__ uint32_t dense_mask(const uint4& v, int dt, uint32_t 
     if (ES == 1) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const uint32_t ne = __vcmpne4(w[k], iv_rep);  // 0xff in every byte that differs
+            // 8-bit floats compare as float with zero: the sign bit does not count
+            const uint32_t x = (dt == VF_DT_F8E4M3FN || dt == VF_DT_F8E5M2) ? (w[k] & 0x7F7F7F7Fu) : w[k];
+            const uint32_t ne = __vcmpne4(x, iv_rep);  // 0xff in every byte that differs
             m |= (((ne & 0x08040201u) * 0x01010101u) >> 24) << (4 * k);
         }
     } else if (ES == 2) {

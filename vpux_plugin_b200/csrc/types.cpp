@@ -18,12 +18,12 @@ void raise(int code, const char* fmt, ...) {
 }
 
 int dtype_bits(int dt) {
-    static const int bits[] = {0, 32, 16, 16, 64, 8, 8, 16, 16, 32, 32, 64, 64, 4, 4, 1};
-    if (dt <= VF_DT_INVALID || dt > VF_DT_I1) raise(VF_ERR_INVALID_ARG, "invalid dtype %d", dt);
+    static const int bits[] = {0, 32, 16, 16, 64, 8, 8, 16, 16, 32, 32, 64, 64, 4, 4, 1, 8, 8};
+    if (dt <= VF_DT_INVALID || dt > VF_DT_F8E5M2) raise(VF_ERR_INVALID_ARG, "invalid dtype %d", dt);
     return bits[dt];
 }
 bool dtype_is_float(int dt) {
-    return dt == VF_DT_F32 || dt == VF_DT_F16 || dt == VF_DT_BF16 || dt == VF_DT_F64;
+    return dt == VF_DT_F32 || dt == VF_DT_F16 || dt == VF_DT_BF16 || dt == VF_DT_F64 || dt == VF_DT_F8E4M3FN || dt == VF_DT_F8E5M2;
 }
 bool dtype_is_int(int dt) {
     return dt >= VF_DT_I8 && dt <= VF_DT_I1;
