@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Weight-fold benchmark: input GB/s of the Const fold hot path on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c5slab|c2|c3|c1] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c5slab|c2|c3|c1|next] [--impl reference]
 
 One step = one pass of the fold over the whole workload (every tensor of this rank's shard). The default
 workload is the Llama-2-7B-shaped set (fp16 -> per-group-128 asymmetric u4, bit-packed, fp16 scales and packed
@@ -15,6 +15,9 @@ sharded across ranks (longest-processing-time-first, no collective). Prints ONE 
            HBM copy peak.
 `cpu_baseline`: the CPU oracle (a port of the reference's fold code) on a bounded sample, host threads.
 `--impl reference`: times that CPU port alone, on all host threads, each step a bounded sample.
+`--workload next`: not a headline line — the kernels of the rows around the hot path (SwizzleConstant, sub-byte
+           unpack, Reverse, Broadcast, ExpandDilated, ScalarMultInverse, 8-bit float conversion, RelocateWeightsTable,
+           the content hash), one at a time, each with its own GB/s, share of the HBM peak and CPU-oracle figure.
 """
 import argparse
 import ctypes as C
@@ -630,9 +633,139 @@ def conv_arm(args, workload):
     emit(line)
 
 
+def next_arm(args):
+    """--workload next: the kernels behind the callers and data formats either side of the hot path (blob assembly,
+    import-side unpacking, the remaining transformations, the content hash of the folding cache), one at a time on
+    inputs larger than L2, each through vf_fold with device buffers. Per kernel: algorithmic bytes (input + output)
+    over the CUDA-event time of the call, against the measured HBM copy peak, and the CPU oracle on a bounded
+    sample of the same input beside it."""
+    import torch
+
+    from oracle import Oracle
+    from vpux_plugin_b200.const import ContentSetup
+    from vpux_plugin_b200.lib import Library, content_hash
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    lib = Library(device=0, stream=stream.cuda_stream)
+    orc = Oracle(nthreads=1)
+    F32, F16, U8, I8, I32 = abi.VF_DT_F32, abi.VF_DT_F16, abi.VF_DT_U8, abi.VF_DT_I8, abi.VF_DT_I32
+    TT = abi.TType
+    mib = max(16, int(512 * args.scale))
+    n8 = mib << 20  # bytes of the 8-bit inputs
+    oc = 4096
+    ops = [  # name, reference site, base type, storage dtype, list builder
+        ("SwizzleConstant", "swizzle_transform.cpp:163-215", TT([n8], U8), U8, lambda s: s.swizzleConstant(5, abi.VF_ARCH_NPU40XX)),
+        ("subByteConversion u4->u8", "convert_utils.cpp:17-75", TT([oc, n8 // oc], abi.VF_DT_U4), abi.VF_DT_U4, lambda s: s.convertElemType(U8)),
+        ("Reverse f16", "reverse.cpp:46-105", TT([oc, 4, n8 // oc // 8], F16), F16, lambda s: s.reverse(0)),
+        ("Broadcast x4 u8", "broadcast.cpp:85-124", TT([oc, 1, n8 // oc // 4], U8), U8, lambda s: s.broadcast(1, 4)),
+        ("ExpandDilated 3x3 d2 f16", "expand_dilated.cpp:88-131", TT([n8 // 2 // 25 // 64, 64, 3, 3], F16), F16, lambda s: s.expandDilated([2, 2])),
+        ("ScalarMultInverse f32", "inverse.cpp:52-66", TT([n8 // 4], F32), F32, lambda s: s.scalarMultInverse()),
+        ("CastElemType f32->f8e4m3 + copyTo", "content.hpp:66-71", TT([n8 // 4], F32), F32, lambda s: s.castElemType(abi.VF_DT_F8E4M3FN)),
+        ("RelocateWeightsTable 1M rows", "relocate_weights_table.cpp:203-292", TT([1 << 20, 1, 1, 4], I32), I32,
+         lambda s: s.relocateWeightsTablePointers([1 << 10, 1 << 20], 64, [0, 1 << 19], 16 << 20, 16)),
+    ]
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(0).uuid).replace("GPU-", ""))
+    rows = []
+    total_bytes = total_ms = 0.0
+    launches0 = lib.launch_count
+    for name, site, t, storage, build in ops:
+        setup = build(ContentSetup(t))
+        tr, n = setup.transforms()
+        in_bytes = t.numel() * abi.DTYPE_BITS[storage] // 8
+        src = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
+        if storage == I32:  # a table whose pointer columns step by 16
+            src.view(torch.int32).copy_(torch.arange(in_bytes // 4, device=dev, dtype=torch.int32) // 4 * 16 % (1 << 20))
+        else:
+            src.random_(1, 120)
+        if storage == F32:  # finite, normal floats
+            src.view(torch.float32).copy_(torch.rand(in_bytes // 4, device=dev) + 0.5)
+        if storage == F16:
+            src.view(torch.float16).copy_((torch.rand(in_bytes // 2, device=dev) - 0.5).half())
+        c, keep = abi.make_content(t, None, storage, False, abi.VF_MEM_DEVICE, ptr=src.data_ptr(), nbytes=in_bytes)
+        _, _, out_bytes = lib.infer_type(t, False, tr, n)
+        dst = torch.empty(out_bytes, dtype=torch.uint8, device=dev)
+        for _ in range(max(3, args.warmup)):
+            lib.fold(c, tr, n, dst.data_ptr(), out_bytes, dst_mem_kind=abi.VF_MEM_DEVICE)
+        torch.cuda.synchronize()
+        ms = 0.0
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            lib.fold(c, tr, n, dst.data_ptr(), out_bytes, dst_mem_kind=abi.VF_MEM_DEVICE)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms += e0.elapsed_time(e1)
+        ms /= args.steps
+        # CPU oracle on a bounded sample: the first rows of the same input
+        cpu = None
+        if not args.no_cpu:
+            rows_all = t.shape[0]
+            take = max(1, min(rows_all, int(rows_all * (8 << 20) / max(in_bytes, 1))))
+            if name.startswith("Relocate"):
+                take = rows_all  # the table is its own sample (the transformation's size is in its parameters)
+            ts = TT([take] + list(t.shape[1:]), t.elem.dtype, t.order) if take != rows_all else t
+            sb = in_bytes * take // rows_all
+            host = src[:sb].cpu().numpy()
+            hs = build(ContentSetup(ts))
+            htr, hn = hs.transforms()
+            hc, hkeep = abi.make_content(ts, host, storage, False)
+            _, _, hob = orc.infer_type(ts, False, htr, hn)
+            hdst = np.zeros(max(hob, 1), np.uint8)
+            t0 = time.perf_counter()
+            orc.fold(hc, htr, hn, hdst, hob)
+            cpu = (sb + hob) / (time.perf_counter() - t0) / 1e9
+        alg = in_bytes + out_bytes
+        rows.append({"kernel": name, "reference": site, "input_bytes": in_bytes, "output_bytes": out_bytes, "ms": ms,
+                     "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac": alg / (ms * 1e-3) / 1e9 / peak, "cpu_oracle_gbs": cpu})
+        total_bytes += alg
+        total_ms += ms
+        del src, dst
+    # the content hash of the folding cache (vf_content_hash): one read of the buffer
+    hb = n8
+    src = torch.empty(hb, dtype=torch.uint8, device=dev).random_(0, 255)
+    c, keep = abi.make_content(TT([hb], U8), None, U8, False, abi.VF_MEM_DEVICE, ptr=src.data_ptr(), nbytes=hb)
+    for _ in range(3):
+        content_hash(lib, c)
+    ms = 0.0
+    for _ in range(args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        content_hash(lib, c)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms += e0.elapsed_time(e1)
+    ms /= args.steps
+    rows.append({"kernel": "content hash (k_hash128)", "reference": "constant_folding_cache.hpp:62-79 (hash of the attribute)",
+                 "input_bytes": hb, "output_bytes": 16, "ms": ms, "achieved_gbs": hb / (ms * 1e-3) / 1e9,
+                 "frac": hb / (ms * 1e-3) / 1e9 / peak, "cpu_oracle_gbs": None})
+    total_bytes += hb
+    total_ms += ms
+    clocks = sampler.stop()
+    emit({"metric": "next_rows_throughput", "value": total_bytes / (total_ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+          "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms, "higher_is_better": True,
+          "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+          "config": {"workload": "next: one kernel at a time, %d MiB of 8-bit input each (larger than the 126 MB L2)" % mib},
+          "roofline": {"bound": "hbm", "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                       "achieved": total_bytes / (total_ms * 1e-3) / 1e9, "frac": total_bytes / (total_ms * 1e-3) / 1e9 / peak,
+                       "traffic": None, "note": "input + output bytes of every call over its CUDA-event time; per kernel in `kernels`"},
+          "kernels": rows, "cpu_baseline": None, "e2e": None, "clocks": clocks,
+          "gpu_launches": int(lib.launch_count - launches0)})
+
+
 def main():
     args = parse()
     claim_stdout()
+    if args.workload == "next":
+        next_arm(args)
+        return
     workload = Workload(args.workload, args.scale)
     if args.impl == "reference":
         reference_arm(args, workload)

@@ -886,3 +886,40 @@ def test_reshape_type_rules(gpu, oracle):
         with pytest.raises(Exception) as e:
             ContentAttr(u, tu, s.reshape([6, 4, 5])).fold(be)
         assert e.value.status == abi.VF_ERR_SHAPE
+
+
+@pytest.mark.gpu
+def test_fold_into_device_memory_matches_fold_into_host_memory(gpu):
+    """With a device destination the last transformation writes its output there directly; the bytes are the
+    ones a host destination receives, also when the destination is the base buffer itself (in place)."""
+    import torch
+    rng = np.random.default_rng(77)
+    t = TType([6, 8, 3, 5], F32)
+    x = rng.standard_normal(t.shape).astype(np.float32)
+    q = Elem.uniform(I8, F32, 0.05, 0, -127, 127)
+    setups = [ContentSetup(t).quantize(q), ContentSetup(t).reorder(abi.ORDER_NHWC), ContentSetup(t).padWithZero([0, 0, 1, 1], [2, 0, 0, 1]),
+              ContentSetup(t).subview([1, 2, 0, 1], [3, 4, 3, 2]), ContentSetup(t).castElemType(F16).reverse(1),
+              ContentSetup(t).rescale(0.5).add(1.0), ContentSetup(t).castElemType(F16), ContentSetup(t).swizzleConstant(3, abi.VF_ARCH_NPU40XX),
+              ContentSetup(t).transpose(0x2143), ContentSetup(t).broadcast(0, 12), ContentSetup(t).scalarMultInverse()]
+    xd = torch.from_numpy(x).cuda()
+    for s in setups:
+        attr = ContentAttr(x, t, s)
+        ref = attr.fold(gpu)
+        tr, n = s.transforms()
+        for in_place in (False, True):
+            src = xd.clone()
+            c, keep = abi.make_content(t, None, F32, False, abi.VF_MEM_DEVICE, ptr=src.data_ptr(), nbytes=x.nbytes)
+            cap = max(ref.written, 1)
+            if in_place:
+                if cap > x.nbytes:
+                    continue
+                dst = src.view(torch.uint8)
+            else:
+                dst = torch.full((cap + 64,), 0xAB, dtype=torch.uint8, device="cuda")
+            written, ftype = gpu.fold(c, tr, n, dst.data_ptr(), cap, dst_mem_kind=abi.VF_MEM_DEVICE)
+            torch.cuda.synchronize()
+            out = dst.cpu().numpy()
+            assert written == ref.written and ftype == ref.type
+            assert np.array_equal(out[:written], ref.bytes()), (s.names(), in_place)
+            if not in_place:
+                assert (out[cap:] == 0xAB).all()

@@ -142,6 +142,10 @@ struct vf_ctx {
     uint64_t launches = 0;
     int32_t opt_flags = 0;
     bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device
+    // vf_fold, last transformation, device destination: the output buffer may be the destination itself, which
+    // saves the final copy (see alloc_like)
+    void* final_dst = nullptr;
+    uint64_t final_bytes = 0;
     std::mutex mu;  // serialises calls on this context
 };
 
@@ -191,8 +195,14 @@ struct DBuf {  // RAII scratch buffer
         reset();
     }
     void reset() {
-        if (p) dfree(ctx, p);
+        if (p && ctx) dfree(ctx, p);
         p = nullptr;
+    }
+    static DBuf borrow(void* ptr, size_t n) {  // caller-owned memory: never freed (ctx stays NULL)
+        DBuf b;
+        b.p = ptr;
+        b.bytes = n;
+        return b;
     }
     template <class T>
     T* as() const {

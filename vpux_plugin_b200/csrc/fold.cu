@@ -52,7 +52,16 @@ DContent alloc_like(vf_ctx* ctx, const Type& type, int storage, bool splat, int6
     c.storage = storage;
     c.splat = splat;
     c.nbytes = raw_bytes >= 0 ? uint64_t(raw_bytes) : (uint64_t(dtype_bits(storage)) * uint64_t(c.count()) + 7u) / 8u;
-    c.own = DBuf(ctx, c.nbytes);
+    // A dense buffer whose storage is the logical element type is what copyTo would copy byte for byte: write it
+    // where it has to end up. (If this turns out to be a scratch buffer of the transformation, the result is
+    // copied over it afterwards, in stream order.)
+    if (ctx->final_dst && !splat && storage == type.elem.dtype && dtype_bits(storage) >= 8 && c.nbytes > 0 &&
+        c.nbytes <= ctx->final_bytes && (reinterpret_cast<uintptr_t>(ctx->final_dst) & 15u) == 0) {
+        c.own = DBuf::borrow(ctx->final_dst, c.nbytes);
+        ctx->final_dst = nullptr;
+    } else {
+        c.own = DBuf(ctx, c.nbytes);
+    }
     c.d = c.own.p;
     return c;
 }
@@ -507,7 +516,7 @@ uint64_t copy_to(vf_ctx* ctx, DContent& c, void* dst, uint64_t dst_bytes, int ds
     const bool to_dev = dst_kind == VF_MEM_DEVICE;
     uint64_t written = 0;
     auto emit = [&](const void* dev_src, uint64_t n) {  // result already in a device buffer
-        copy_out(ctx, dst, dst_kind, dev_src, n);
+        if (dev_src != dst) copy_out(ctx, dst, dst_kind, dev_src, n);
         if (!to_dev && stats) stats->d2h_bytes += n;
         written = n;
     };
@@ -939,10 +948,25 @@ int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, v
         check_positions(t, n);
         CallScope scope(ctx, stats);
         DContent cur = upload_base(ctx, *base, stats);
+        // the destination doubles as the last transformation's output buffer when it is device memory that does
+        // not overlap the base content
+        const char* b0 = static_cast<const char*>(base->data);
+        const char* d0 = static_cast<const char*>(dst);
+        const bool direct = dst && dst_mem_kind == VF_MEM_DEVICE &&
+                            (base->mem_kind != VF_MEM_DEVICE || d0 + dst_bytes <= b0 || b0 + base->nbytes <= d0);
+        struct Hint {
+            vf_ctx* c;
+            ~Hint() { c->final_dst = nullptr; }
+        } hint{ctx};
         for (int i = 0; i < n; ++i) {  // ContentAttr::fold — attributes/content.cpp:392-394
+            if (direct && i == n - 1) {
+                ctx->final_dst = dst;
+                ctx->final_bytes = dst_bytes;
+            }
             DContent next = apply(ctx, cur, t[i]);
             cur = std::move(next);
         }
+        ctx->final_dst = nullptr;
         cur.type.export_to(out_type, scales_buf, zps_buf, params_cap);
         const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_mem_kind, stats);
         if (dst_written) *dst_written = w;
