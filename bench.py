@@ -679,7 +679,8 @@ def next_arm(args):
     for name, site, t, storage, build in ops:
         setup = build(ContentSetup(t))
         tr, n = setup.transforms()
-        in_bytes = t.numel() * abi.DTYPE_BITS[storage] // 8
+        numel = int(np.prod(t.shape))
+        in_bytes = numel * abi.DTYPE_BITS[storage] // 8
         src = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
         if storage == I32:  # a table whose pointer columns step by 16
             src.view(torch.int32).copy_(torch.arange(in_bytes // 4, device=dev, dtype=torch.int32) // 4 * 16 % (1 << 20))

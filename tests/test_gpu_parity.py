@@ -913,12 +913,12 @@ def test_fold_into_device_memory_matches_fold_into_host_memory(gpu):
             if in_place:
                 if cap > x.nbytes:
                     continue
-                dst = src.view(torch.uint8)
+                dst = src.view(torch.uint8).reshape(-1)
             else:
                 dst = torch.full((cap + 64,), 0xAB, dtype=torch.uint8, device="cuda")
             written, ftype = gpu.fold(c, tr, n, dst.data_ptr(), cap, dst_mem_kind=abi.VF_MEM_DEVICE)
             torch.cuda.synchronize()
-            out = dst.cpu().numpy()
+            out = dst.cpu().numpy().reshape(-1)
             assert written == ref.written and ftype == ref.type
             assert np.array_equal(out[:written], ref.bytes()), (s.names(), in_place)
             if not in_place:

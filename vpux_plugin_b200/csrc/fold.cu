@@ -594,6 +594,14 @@ DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     const Type ot = infer_one(in.type, in.splat, t, os);
     const uint64_t in_total = in.type.alloc_bytes();
     const uint64_t new_size = uint64_t(align_up(int64_t(in_total), swizzle_size_alignment(int(t.a[1]))));
+    DContent out;
+    const bool plain = !in.splat && in.storage == in.type.elem.dtype && dtype_bits(in.storage) >= 8 && in.nbytes == in_total &&
+                       (reinterpret_cast<uintptr_t>(in.d) & 15u) == 0;
+    if (plain) {  // the storage bytes are what copyTo would produce: permute them straight from where they are
+        out = alloc_like(ctx, ot, ot.elem.dtype, false, int64_t(new_size));
+        launch_swizzle(ctx, in.d, in_total, 0, out.own.p, new_size, int(t.a[0]), int(t.a[1]));
+        return out;
+    }
     DBuf lin(ctx, new_size);
     copy_to(ctx, in, lin.p, in_total, VF_MEM_DEVICE, nullptr);
     if (new_size > in_total) {
@@ -604,11 +612,11 @@ DContent do_swizzle(vf_ctx* ctx, DContent& in, const vf_transform& t) {
         }
         launch_fill_bytes(ctx, lin.as<uint8_t>() + in_total, pad, new_size - in_total);
     }
-    DContent out = alloc_like(ctx, ot, ot.elem.dtype, false, int64_t(new_size));
+    out = alloc_like(ctx, ot, ot.elem.dtype, false, int64_t(new_size));
     if (in.splat) {  // every chunk holds the same bytes: nothing to permute
         VF_CUDA(cudaMemcpyAsync(out.own.p, lin.p, new_size, cudaMemcpyDeviceToDevice, ctx->stream));
     } else {
-        launch_swizzle(ctx, lin.p, out.own.p, new_size, int(t.a[0]), int(t.a[1]));
+        launch_swizzle(ctx, lin.p, new_size, 0, out.own.p, new_size, int(t.a[0]), int(t.a[1]));
     }
     return out;
 }
@@ -663,7 +671,10 @@ DContent do_relocate(vf_ctx* ctx, DContent& in, const vf_transform& t) {
         d_steps = upload_vec(ctx, steps);
         a.d_steps = d_steps.as<int64_t>();
     }
-    if (out.nbytes) VF_CUDA(cudaMemcpyAsync(out.own.p, lin.d, out.nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    const uint64_t patched = uint64_t(std::max<int64_t>(a.oc, 0)) * 16;  // the kernel writes these rows whole
+    if (out.nbytes > patched)
+        VF_CUDA(cudaMemcpyAsync(static_cast<char*>(out.own.p) + patched, static_cast<const char*>(lin.d) + patched, out.nbytes - patched,
+                                cudaMemcpyDeviceToDevice, ctx->stream));
     launch_relocate(ctx, static_cast<const int32_t*>(lin.d), out.own.as<int32_t>(), a);
     return out;
 }

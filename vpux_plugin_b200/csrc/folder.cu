@@ -33,24 +33,46 @@ __host__ __device__ inline uint64_t mix64(uint64_t z) {
 }
 
 // Sum over the 8-byte words w of mix(word ^ f(index)): addition commutes, so the result does not depend on how
-// the words are spread over threads. A buffer that is not 8-byte aligned, and the last partial word, are
-// assembled from bytes (missing bytes read as zero).
-__global__ void k_hash128(const uint8_t* __restrict__ p, uint64_t nbytes, unsigned long long* __restrict__ acc) {
+// the words are spread over threads. A 16-byte aligned buffer is read two words per load; any other buffer, and
+// the last partial word, are assembled from 8-byte or single-byte loads (missing bytes read as zero).
+__device__ __forceinline__ uint64_t word_from_bytes(const uint8_t* __restrict__ p, uint64_t nbytes, uint64_t w) {
+    uint64_t v = 0;
+    for (int b = 0; b < 8; ++b)
+        if (w * 8 + b < nbytes) v |= uint64_t(p[w * 8 + b]) << (8 * b);
+    return v;
+}
+
+__global__ void __launch_bounds__(256) k_hash128(const uint8_t* __restrict__ p, uint64_t nbytes, unsigned long long* __restrict__ acc) {
     const uint64_t words = (nbytes + 7) / 8;
-    const bool aligned = (reinterpret_cast<uintptr_t>(p) & 7u) == 0;
+    const uint64_t tid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
     uint64_t h1 = 0, h2 = 0;
-    for (uint64_t w = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; w < words; w += stride) {
-        uint64_t v = 0;
-        if (aligned && (w + 1) * 8 <= nbytes) {
-            v = reinterpret_cast<const uint64_t*>(p)[w];
-        } else {
-            for (int b = 0; b < 8; ++b)
-                if (w * 8 + b < nbytes) v |= uint64_t(p[w * 8 + b]) << (8 * b);
-        }
-        const uint64_t x = mix64(v ^ ((w + 1) * 0x9E3779B97F4A7C15ull));
+    constexpr uint64_t K = 0x9E3779B97F4A7C15ull, K2 = 0xD6E8FEB86659FD93ull;
+    // word w enters as mix(word ^ (w + 1) * K); the second sum reuses the mixed value with one more multiply
+    auto add = [&](uint64_t kw, uint64_t v) {
+        const uint64_t x = mix64(v ^ kw);
         h1 += x;
-        h2 += mix64(x + 0xD6E8FEB86659FD93ull);
+        h2 += (x ^ (x >> 29)) * K2;
+    };
+    const unsigned mis = unsigned(reinterpret_cast<uintptr_t>(p) & 15u);
+    if (mis == 0) {
+        const uint64_t nvec = nbytes / 16;
+        const uint4* __restrict__ q = reinterpret_cast<const uint4*>(p);
+        uint64_t kw = (2 * tid + 1) * K;  // (w + 1) * K for w = 2 * v, advanced by additions
+        const uint64_t kstep = 2 * stride * K;
+        for (uint64_t v = tid; v < nvec; v += stride, kw += kstep) {
+            const uint4 x = __ldg(q + v);
+            add(kw, uint64_t(x.x) | (uint64_t(x.y) << 32));
+            add(kw + K, uint64_t(x.z) | (uint64_t(x.w) << 32));
+        }
+        if (tid == 0)
+            for (uint64_t w = 2 * nvec; w < words; ++w) add((w + 1) * K, word_from_bytes(p, nbytes, w));
+    } else {
+        const bool aligned8 = (mis & 7u) == 0;
+        for (uint64_t w = tid; w < words; w += stride) {
+            const bool whole = (w + 1) * 8 <= nbytes;
+            add((w + 1) * K, aligned8 && whole ? reinterpret_cast<const uint64_t*>(p)[w] : word_from_bytes(p, nbytes, w));
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         h1 += __shfl_down_sync(0xFFFFFFFFu, h1, o);
@@ -74,7 +96,7 @@ void hash_device(vf_ctx* ctx, const void* d, uint64_t nbytes, uint64_t out[2]) {
     VF_CUDA(cudaMemsetAsync(acc.p, 0, 16, ctx->stream));
     const uint64_t words = (nbytes + 7) / 8;
     if (words) {
-        const uint64_t blocks = std::min<uint64_t>((words + 255) / 256, 148 * 8);
+        const uint64_t blocks = std::min<uint64_t>((words / 2 + 255) / 256 + 1, 148 * 8);
         k_hash128<<<int(blocks), 256, 0, ctx->stream>>>(static_cast<const uint8_t*>(d), nbytes, acc.as<unsigned long long>());
         VF_CUDA(cudaGetLastError());
         ++ctx->launches;

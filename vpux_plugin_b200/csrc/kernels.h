@@ -31,7 +31,8 @@ void launch_pack_subbyte(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, i
 // subByteConversion: `n_out` elements of `bits` (1 / 2 / 4) bits each, low bits first, to one byte each
 void launch_unpack_subbyte(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t n_out, int bits, bool sign_extend);
 // SwizzleConstant: permutes the 16- / 32-byte chunks of a buffer whose size is a multiple of 512 / 1024 bytes
-void launch_swizzle(vf_ctx* ctx, const void* in, void* out, uint64_t bytes, int swizzle_key, int arch);
+// `in` holds in_bytes valid bytes (16-byte aligned start); the rest of the `bytes` of the swizzled buffer reads as `pad`
+void launch_swizzle(vf_ctx* ctx, const void* in, uint64_t in_bytes, uint8_t pad, void* out, uint64_t bytes, int swizzle_key, int arch);
 // BitPack<4>: reads pairs through getValues<uint8_t>()
 void launch_bitpack4(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in);
 void launch_fill_bytes(vf_ctx* ctx, void* out, uint8_t value, uint64_t bytes);

@@ -16,6 +16,10 @@ inline int grid_for(int64_t n, int per_thread = 1) {
     return int(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
 }
 
+inline bool aligned16(const void* a, const void* b) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
+}
+
 // ------------------------------------------------------------------------------------------------------
 // Quantize — attributes/quantize.cpp:108-212
 // ------------------------------------------------------------------------------------------------------
@@ -108,8 +112,42 @@ __global__ void k_pack_subbyte(const void* __restrict__ in, int in_dt, uint8_t* 
 // each. A thread expands 8 elements: it reads `BITS` input bytes as one word and writes 8 bytes. `sign` selects
 // the sign-extending branch (:47-66), otherwise the masking branch (:28-46).
 template <int BITS>
-__global__ void k_unpack_subbyte(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n_out, int sign) {
+__device__ __forceinline__ uint2 expand8(uint32_t w, int sign) {  // eight elements of BITS bits -> eight bytes
     constexpr unsigned kMask = (1u << BITS) - 1u;
+    uint32_t r[2] = {0u, 0u};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        uint32_t v = (w >> (k * BITS)) & kMask;
+        if (sign) v = uint32_t(int32_t(v << (32 - BITS)) >> (32 - BITS)) & 0xFFu;
+        r[k >> 2] |= v << (8 * (k & 3));
+    }
+    return make_uint2(r[0], r[1]);
+}
+
+// 32 elements per thread step: 4 * BITS input bytes in one load, two 16-byte stores (both buffers aligned)
+template <int BITS>
+__global__ void k_unpack_subbyte_x32(const uint8_t* __restrict__ in, uint4* __restrict__ out, int64_t n_steps, int sign) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t < n_steps; t += stride) {
+        uint32_t w[4];
+        if (BITS == 4) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(in) + t);
+            w[0] = x.x, w[1] = x.y, w[2] = x.z, w[3] = x.w;
+        } else if (BITS == 2) {
+            const uint2 x = __ldg(reinterpret_cast<const uint2*>(in) + t);
+            w[0] = x.x & 0xFFFFu, w[1] = x.x >> 16, w[2] = x.y & 0xFFFFu, w[3] = x.y >> 16;
+        } else {
+            const uint32_t x = __ldg(reinterpret_cast<const uint32_t*>(in) + t);
+            w[0] = x & 0xFFu, w[1] = (x >> 8) & 0xFFu, w[2] = (x >> 16) & 0xFFu, w[3] = x >> 24;
+        }
+        const uint2 a = expand8<BITS>(w[0], sign), b = expand8<BITS>(w[1], sign), c = expand8<BITS>(w[2], sign), d = expand8<BITS>(w[3], sign);
+        out[2 * t] = make_uint4(a.x, a.y, b.x, b.y);
+        out[2 * t + 1] = make_uint4(c.x, c.y, d.x, d.y);
+    }
+}
+
+template <int BITS>
+__global__ void k_unpack_subbyte(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n_out, int sign) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     const int64_t groups = (n_out + 7) / 8;
     const bool aligned = (reinterpret_cast<uintptr_t>(in) % BITS) == 0 && (reinterpret_cast<uintptr_t>(out) % 8) == 0;
@@ -125,16 +163,11 @@ __global__ void k_unpack_subbyte(const uint8_t* __restrict__ in, uint8_t* __rest
             const int nbytes = (left * BITS + 7) / 8;
             for (int b = 0; b < nbytes; ++b) w |= uint32_t(in[g * BITS + b]) << (8 * b);
         }
-        uint32_t r[2] = {0u, 0u};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            uint32_t v = (w >> (k * BITS)) & kMask;
-            if (sign) v = uint32_t(int32_t(v << (32 - BITS)) >> (32 - BITS)) & 0xFFu;
-            r[k >> 2] |= v << (8 * (k & 3));
-        }
+        const uint2 r2 = expand8<BITS>(w, sign);
         if (aligned && left == 8) {
-            *reinterpret_cast<uint2*>(out + o0) = make_uint2(r[0], r[1]);
+            *reinterpret_cast<uint2*>(out + o0) = r2;
         } else {
+            const uint32_t r[2] = {r2.x, r2.y};
             for (int k = 0; k < left; ++k) out[o0 + k] = uint8_t(r[k >> 2] >> (8 * (k & 3)));
         }
     }
@@ -144,10 +177,25 @@ __global__ void k_unpack_subbyte(const uint8_t* __restrict__ in, uint8_t* __rest
 // AddressTransform::getPhysicalAddress (attributes/swizzle_transform.cpp:71-83): every chunk of the RAM-cut
 // data width (16 bytes on NPU37XX, 32 on NPU40XX) moves to its staggered address inside its RAM-cut block.
 // A pure permutation of 16-byte vectors: one vector per thread step, loads and stores both 16 bytes wide.
-__global__ void k_swizzle(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t n_vec, uint32_t log2w,
-                          uint32_t stagger_mask, uint32_t shift, uint32_t cut_mask) {
+// The source holds `in_bytes` valid bytes; what lies behind them up to the swizzled size reads as `pad`.
+__global__ void k_swizzle(const uint4* __restrict__ in, uint64_t in_bytes, uint32_t pad, uint4* __restrict__ out, int64_t n_vec,
+                          uint32_t log2w, uint32_t stagger_mask, uint32_t shift, uint32_t cut_mask) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int64_t full = int64_t(in_bytes / 16);
+    const uint32_t pad4 = pad * 0x01010101u;
     for (int64_t v = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
+        uint4 x;
+        if (v < full) {
+            x = __ldg(in + v);
+        } else {  // the vector that straddles the end of the data, and the padding behind it
+            uint32_t w[4] = {pad4, pad4, pad4, pad4};
+            const uint8_t* b = reinterpret_cast<const uint8_t*>(in);
+            for (int k = 0; k < 16; ++k) {
+                const uint64_t at = uint64_t(v) * 16 + k;
+                if (at < in_bytes) w[k >> 2] = (w[k >> 2] & ~(0xFFu << (8 * (k & 3)))) | (uint32_t(b[at]) << (8 * (k & 3)));
+            }
+            x = make_uint4(w[0], w[1], w[2], w[3]);
+        }
         const uint32_t addr = uint32_t(v) << 4;
         const uint32_t dpu = addr & ~((1u << log2w) - 1u);  // the chunk this vector belongs to
         uint32_t s = dpu >> log2w;
@@ -157,7 +205,7 @@ __global__ void k_swizzle(const uint4* __restrict__ in, uint4* __restrict__ out,
         s <<= shift;
         uint32_t phy = (dpu + s) & cut_mask;
         phy += dpu & ~cut_mask;
-        out[(phy + (addr - dpu)) >> 4] = in[v];
+        out[(phy + (addr - dpu)) >> 4] = x;
     }
 }
 
@@ -500,57 +548,138 @@ struct ElemBits<4> { using type = uint32_t; };
 template <>
 struct ElemBits<8> { using type = uint64_t; };
 
-// Reverse — attributes/reverse.cpp:46-80: every run of `run` consecutive elements of the buffer is reversed
+template <>
+struct ElemBits<16> { using type = uint4; };
+
+// Index arithmetic runs in 32 bits whenever the buffer has fewer than 2^31 elements (64-bit divisions cost an
+// order of magnitude more).
+template <typename I>
+__device__ __forceinline__ I first_index() {
+    return I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x);
+}
+template <typename I>
+__device__ __forceinline__ I index_stride() {
+    return I(gridDim.x) * I(blockDim.x);
+}
+
+// the elements of one 16-byte vector in reverse order
 template <int ES>
-__global__ void k_reverse(const void* __restrict__ in, void* __restrict__ out, int64_t n, int64_t run) {
+__device__ __forceinline__ uint4 reverse_vec(uint4 v) {
+    if (ES == 1) return make_uint4(__byte_perm(v.w, 0, 0x0123), __byte_perm(v.z, 0, 0x0123), __byte_perm(v.y, 0, 0x0123), __byte_perm(v.x, 0, 0x0123));
+    if (ES == 2) return make_uint4(__byte_perm(v.w, 0, 0x1032), __byte_perm(v.z, 0, 0x1032), __byte_perm(v.y, 0, 0x1032), __byte_perm(v.x, 0, 0x1032));
+    if (ES == 4) return make_uint4(v.w, v.z, v.y, v.x);
+    return make_uint4(v.z, v.w, v.x, v.y);
+}
+
+// Reverse — attributes/reverse.cpp:46-80: every run of `run` consecutive elements of the buffer is reversed.
+// Vector form (run a multiple of the 16 / ES elements of a vector, both buffers 16-byte aligned): output vector
+// j of a run is input vector (last - j) with its elements reversed.
+template <int ES, typename I>
+__global__ void k_reverse_vec(const uint4* __restrict__ in, uint4* __restrict__ out, I n_vec, I run_vec) {
+    const I stride = index_stride<I>();
+    for (I v = first_index<I>(); v < n_vec; v += stride) {
+        const I r = v % run_vec;
+        out[v] = reverse_vec<ES>(__ldg(in + (v - r + (run_vec - 1 - r))));
+    }
+}
+template <int ES, typename I>
+__global__ void k_reverse(const void* __restrict__ in, void* __restrict__ out, I n, I run) {
     using T = typename ElemBits<ES>::type;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const int64_t r = i % run;
+    const I stride = index_stride<I>();
+    for (I i = first_index<I>(); i < n; i += stride) {
+        const I r = i % run;
         static_cast<T*>(out)[i] = static_cast<const T*>(in)[i - r + (run - 1 - r)];
     }
 }
 
-// Broadcast — attributes/broadcast.cpp:85-124: each block of `after` elements is written `factor` times in a row
-template <int ES>
-__global__ void k_broadcast(const void* __restrict__ in, void* __restrict__ out, int64_t n_out, int64_t after, int64_t factor) {
+// Broadcast — attributes/broadcast.cpp:85-124: each block of `after` elements is written `factor` times in a row.
+// ES is the widest power of two (up to 16 bytes) that divides the block size and both addresses.
+template <int ES, typename I>
+__global__ void k_broadcast(const void* __restrict__ in, void* __restrict__ out, I n_out, I after, I factor) {
     using T = typename ElemBits<ES>::type;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    const int64_t group = after * factor;
-    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += stride) {
-        const int64_t pre = o / group;
+    const I stride = index_stride<I>();
+    const I group = after * factor;
+    for (I o = first_index<I>(); o < n_out; o += stride) {
+        const I pre = o / group;
         static_cast<T*>(out)[o] = static_cast<const T*>(in)[pre * after + (o - pre * group) % after];
     }
 }
 
 // ExpandDilated — attributes/expand_dilated.cpp:88-131: raw OIYX index arithmetic whatever the dims order;
 // positions between the taps hold the fill value (zero, or the zero point of output channel `fill` index)
-template <int ES>
-__global__ void k_expand_dilated(const void* __restrict__ in, int in_splat, void* __restrict__ out, int64_t n_out, int64_t dky,
-                                 int64_t dkx, int64_t ky, int64_t kx, int64_t dil_y, int64_t dil_x,
-                                 const void* __restrict__ fill, int64_t n_fill, int64_t fill_stride, int64_t fill_extent) {
+template <int ES, typename I>
+__global__ void k_expand_dilated(const void* __restrict__ in, int in_splat, void* __restrict__ out, I n_out, I dky, I dkx, I ky,
+                                 I kx, I dil_y, I dil_x, const void* __restrict__ fill, I n_fill, I fill_stride, I fill_extent) {
     using T = typename ElemBits<ES>::type;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += stride) {
-        const int64_t x = o % dkx, y = (o / dkx) % dky, plane = o / (dkx * dky);
+    const I stride = index_stride<I>();
+    for (I o = first_index<I>(); o < n_out; o += stride) {
+        const I row = o / dkx, x = o - row * dkx;
+        const I plane = row / dky, y = row - plane * dky;
         T v;
         if (y % dil_y == 0 && x % dil_x == 0) {
-            v = static_cast<const T*>(in)[in_splat ? 0 : (plane * ky + y / dil_y) * kx + x / dil_x];
+            v = static_cast<const T*>(in)[in_splat ? I(0) : (plane * ky + y / dil_y) * kx + x / dil_x];
         } else {
-            v = static_cast<const T*>(fill)[n_fill > 1 ? (o / fill_stride) % fill_extent : 0];
+            v = static_cast<const T*>(fill)[n_fill > 1 ? (o / fill_stride) % fill_extent : I(0)];
         }
         static_cast<T*>(out)[o] = v;
     }
 }
 
 // ScalarMultInverse — attributes/inverse.cpp:52-66: 1.f / v in f32; zero, subnormal, infinite or NaN input throws
+__device__ __forceinline__ float inverse_checked(float v, int* flags) {
+    const uint32_t e = (__float_as_uint(v) >> 23) & 0xFFu;
+    if (e == 0u || e == 0xFFu) set_flag(flags, VF_FLAG_NOT_NORMAL);
+    return __fdiv_rn(1.0f, v);
+}
 __global__ void k_inverse(const void* __restrict__ in, int in_dt, float* __restrict__ out, int64_t n, int* flags) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float v = load_as_f32(in, in_dt, i, flags);
-        const uint32_t e = (__float_as_uint(v) >> 23) & 0xFFu;
-        if (e == 0u || e == 0xFFu) set_flag(flags, VF_FLAG_NOT_NORMAL);
-        out[i] = __fdiv_rn(1.0f, v);
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = inverse_checked(load_as_f32(in, in_dt, i, flags), flags);
+}
+__global__ void k_inverse_f32x4(const float4* __restrict__ in, float4* __restrict__ out, int64_t n_vec, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+        const float4 v = __ldg(in + i);
+        out[i] = make_float4(inverse_checked(v.x, flags), inverse_checked(v.y, flags), inverse_checked(v.z, flags), inverse_checked(v.w, flags));
+    }
+}
+
+// copyTo between floating types, eight elements per thread step (16-byte accesses where the type allows):
+// the same conversions as k_convert, chosen at compile time.
+template <int DT>
+struct FloatBytes { static constexpr int value = DT == VF_DT_F32 ? 4 : (DT == VF_DT_F16 || DT == VF_DT_BF16) ? 2 : 1; };
+template <int IN, int OUT>
+__global__ void k_convert_float8(const void* __restrict__ in, void* __restrict__ out, int64_t n_groups, int* flags) {
+    constexpr int IB = FloatBytes<IN>::value * 8, OB = FloatBytes<OUT>::value * 8;  // bytes of eight elements
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        __align__(16) uint8_t ib[IB];
+        __align__(16) uint8_t ob[OB];
+        if (IB == 32) {
+            reinterpret_cast<uint4*>(ib)[0] = __ldg(reinterpret_cast<const uint4*>(in) + 2 * g);
+            reinterpret_cast<uint4*>(ib)[1] = __ldg(reinterpret_cast<const uint4*>(in) + 2 * g + 1);
+        } else if (IB == 16) {
+            reinterpret_cast<uint4*>(ib)[0] = __ldg(reinterpret_cast<const uint4*>(in) + g);
+        } else {
+            reinterpret_cast<uint2*>(ib)[0] = __ldg(reinterpret_cast<const uint2*>(in) + g);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float f = load_as_f32(ib, IN, k, flags);
+            if (OUT == VF_DT_F32) reinterpret_cast<float*>(ob)[k] = f;
+            else if (OUT == VF_DT_F16) reinterpret_cast<uint16_t*>(ob)[k] = f32_to_f16_clamped_bits(f);
+            else if (OUT == VF_DT_BF16) reinterpret_cast<uint16_t*>(ob)[k] = f32_to_bf16_bits(f);
+            else if (OUT == VF_DT_F8E4M3FN) ob[k] = f32_bits_to_f8e4m3_bits(__float_as_uint(f));
+            else ob[k] = f16_bits_to_f8e5m2_bits(f32_to_f16_bits(f));
+        }
+        if (OB == 32) {
+            reinterpret_cast<uint4*>(out)[2 * g] = reinterpret_cast<uint4*>(ob)[0];
+            reinterpret_cast<uint4*>(out)[2 * g + 1] = reinterpret_cast<uint4*>(ob)[1];
+        } else if (OB == 16) {
+            reinterpret_cast<uint4*>(out)[g] = reinterpret_cast<uint4*>(ob)[0];
+        } else {
+            reinterpret_cast<uint2*>(out)[g] = reinterpret_cast<uint2*>(ob)[0];
+        }
     }
 }
 
@@ -680,10 +809,44 @@ void launch_rescale_add(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, f
     post_launch(ctx);
 }
 
+template <int IN>
+bool launch_convert_float8_out(vf_ctx* ctx, const void* in, void* out, int out_dt, int64_t groups) {
+    const int grid = grid_for(groups);
+    switch (out_dt) {
+    case VF_DT_F32: k_convert_float8<IN, VF_DT_F32><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, ctx->d_flags); return true;
+    case VF_DT_F16: k_convert_float8<IN, VF_DT_F16><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, ctx->d_flags); return true;
+    case VF_DT_BF16: k_convert_float8<IN, VF_DT_BF16><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, ctx->d_flags); return true;
+    case VF_DT_F8E4M3FN: k_convert_float8<IN, VF_DT_F8E4M3FN><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, ctx->d_flags); return true;
+    case VF_DT_F8E5M2: k_convert_float8<IN, VF_DT_F8E5M2><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, ctx->d_flags); return true;
+    default: return false;
+    }
+}
+
 void launch_convert(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void* out, int out_dt, int64_t n) {
     if (n <= 0) return;
-    k_convert<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, out_dt, n, ctx->d_flags);
-    post_launch(ctx);
+    int64_t done = 0;
+    if (!in_splat && n >= 8 && in_dt != out_dt && aligned16(in, out)) {  // float -> float, eight elements per thread step
+        const int64_t groups = n / 8;
+        bool ok = false;
+        switch (in_dt) {
+        case VF_DT_F32: ok = launch_convert_float8_out<VF_DT_F32>(ctx, in, out, out_dt, groups); break;
+        case VF_DT_F16: ok = launch_convert_float8_out<VF_DT_F16>(ctx, in, out, out_dt, groups); break;
+        case VF_DT_BF16: ok = launch_convert_float8_out<VF_DT_BF16>(ctx, in, out, out_dt, groups); break;
+        case VF_DT_F8E4M3FN: ok = launch_convert_float8_out<VF_DT_F8E4M3FN>(ctx, in, out, out_dt, groups); break;
+        case VF_DT_F8E5M2: ok = launch_convert_float8_out<VF_DT_F8E5M2>(ctx, in, out, out_dt, groups); break;
+        default: break;
+        }
+        if (ok) {
+            post_launch(ctx);
+            done = groups * 8;
+        }
+    }
+    if (done < n) {
+        const char* tin = static_cast<const char*>(in) + (in_splat ? 0 : done * (dtype_bits(in_dt) / 8));
+        char* tout = static_cast<char*>(out) + done * (dtype_bits(out_dt) / 8);
+        k_convert<<<grid_for(n - done), kBlock, 0, ctx->stream>>>(tin, in_dt, in_splat, tout, out_dt, n - done, ctx->d_flags);
+        post_launch(ctx);
+    }
 }
 
 void launch_pack_subbyte(vf_ctx* ctx, const void* in, int in_dt, uint8_t* out, int64_t n_in, int per_byte) {
@@ -811,7 +974,7 @@ void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table) {
     post_launch(ctx);
 }
 
-void launch_swizzle(vf_ctx* ctx, const void* in, void* out, uint64_t bytes, int swizzle_key, int arch) {
+void launch_swizzle(vf_ctx* ctx, const void* in, uint64_t in_bytes, uint8_t pad, void* out, uint64_t bytes, int swizzle_key, int arch) {
     if (!bytes) return;
     if (bytes >= (1ull << 32)) raise(VF_ERR_UNSUPPORTED, "swizzled constants are addressed with 32 bits");
     // AddressTransform::setStaggerBits — attributes/swizzle_transform.cpp:37-56
@@ -823,22 +986,35 @@ void launch_swizzle(vf_ctx* ctx, const void* in, void* out, uint64_t bytes, int 
         cut_mask = (1u << 10) - 1u;
     }
     const int64_t n_vec = int64_t(bytes / 16);
-    k_swizzle<<<grid_for(n_vec), kBlock, 0, ctx->stream>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec, log2w,
-                                                          (1u << bits) - 1u, shift, cut_mask);
+    k_swizzle<<<grid_for(n_vec), kBlock, 0, ctx->stream>>>(static_cast<const uint4*>(in), std::min<uint64_t>(in_bytes, bytes), pad,
+                                                          static_cast<uint4*>(out), n_vec, log2w, (1u << bits) - 1u, shift, cut_mask);
     post_launch(ctx);
+}
+
+template <int BITS>
+void launch_unpack_bits(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t n_out, int s) {
+    int64_t done = 0;
+    if (n_out >= 32 && (reinterpret_cast<uintptr_t>(in) % (4 * BITS)) == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0) {
+        const int64_t steps = n_out / 32;
+        k_unpack_subbyte_x32<BITS><<<grid_for(steps), kBlock, 0, ctx->stream>>>(in, reinterpret_cast<uint4*>(out), steps, s);
+        post_launch(ctx);
+        done = steps * 32;
+    }
+    if (done < n_out) {
+        k_unpack_subbyte<BITS><<<grid_for((n_out - done + 7) / 8), kBlock, 0, ctx->stream>>>(in + done * BITS / 8, out + done, n_out - done, s);
+        post_launch(ctx);
+    }
 }
 
 void launch_unpack_subbyte(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t n_out, int bits, bool sign_extend) {
     if (n_out <= 0) return;
-    const int grid = grid_for((n_out + 7) / 8);
     const int s = sign_extend ? 1 : 0;
     switch (bits) {
-    case 1: k_unpack_subbyte<1><<<grid, kBlock, 0, ctx->stream>>>(in, out, n_out, s); break;
-    case 2: k_unpack_subbyte<2><<<grid, kBlock, 0, ctx->stream>>>(in, out, n_out, s); break;
-    case 4: k_unpack_subbyte<4><<<grid, kBlock, 0, ctx->stream>>>(in, out, n_out, s); break;
+    case 1: launch_unpack_bits<1>(ctx, in, out, n_out, s); break;
+    case 2: launch_unpack_bits<2>(ctx, in, out, n_out, s); break;
+    case 4: launch_unpack_bits<4>(ctx, in, out, n_out, s); break;
     default: raise(VF_ERR_UNSUPPORTED, "Invalid number of elements per byte for %d-bit elements", bits);
     }
-    post_launch(ctx);
 }
 
 void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
@@ -866,18 +1042,35 @@ void launch_relocate(vf_ctx* ctx, const int32_t* in, int32_t* out, const Relocat
     case 2: { constexpr int ES = 2; CALL; break; }                                  \
     case 4: { constexpr int ES = 4; CALL; break; }                                  \
     case 8: { constexpr int ES = 8; CALL; break; }                                  \
+    case 16: { constexpr int ES = 16; CALL; break; }                                \
     default: raise(VF_ERR_UNSUPPORTED, "element size %d", es);                      \
     }
+// I = uint32_t while every index of the launch stays below 2^31, int64_t otherwise
+#define VF_BY_INDEX_WIDTH(n, CALL)                                                  \
+    if ((n) < (int64_t(1) << 31)) { using I = uint32_t; CALL; } else { using I = int64_t; CALL; }
 
 void launch_reverse(vf_ctx* ctx, const void* in, void* out, int64_t n, int64_t run, int es) {
     if (n <= 0) return;
-    VF_BY_ELEM_SIZE(es, (k_reverse<ES><<<grid_for(n), kBlock, 0, ctx->stream>>>(in, out, n, run)));
+    const int epv = 16 / es;
+    if (es <= 8 && run % epv == 0 && aligned16(in, out)) {
+        const int64_t nv = n / epv, rv = run / epv;
+        VF_BY_ELEM_SIZE(es, VF_BY_INDEX_WIDTH(nv, (k_reverse_vec<ES, I><<<grid_for(nv), kBlock, 0, ctx->stream>>>(
+                                                          static_cast<const uint4*>(in), static_cast<uint4*>(out), I(nv), I(rv)))));
+    } else {
+        VF_BY_ELEM_SIZE(es, VF_BY_INDEX_WIDTH(n, (k_reverse<ES, I><<<grid_for(n), kBlock, 0, ctx->stream>>>(in, out, I(n), I(run)))));
+    }
     post_launch(ctx);
 }
 
 void launch_broadcast(vf_ctx* ctx, const void* in, void* out, int64_t n_out, int64_t after, int64_t factor, int es) {
     if (n_out <= 0) return;
-    VF_BY_ELEM_SIZE(es, (k_broadcast<ES><<<grid_for(n_out), kBlock, 0, ctx->stream>>>(in, out, n_out, after, factor)));
+    // copy in the widest unit that divides the repeated block and both addresses
+    int wide = es;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out);
+    while (wide < 16 && (after * es) % (wide * 2) == 0 && (addr % uintptr_t(wide * 2)) == 0) wide *= 2;
+    const int64_t k = wide / es;
+    const int64_t n = n_out / k, a = after / k;
+    VF_BY_ELEM_SIZE(wide, VF_BY_INDEX_WIDTH(n, (k_broadcast<ES, I><<<grid_for(n), kBlock, 0, ctx->stream>>>(in, out, I(n), I(a), I(factor)))));
     post_launch(ctx);
 }
 
@@ -885,15 +1078,25 @@ void launch_expand_dilated(vf_ctx* ctx, const void* in, bool in_splat, void* out
                            int64_t ky, int64_t kx, int64_t dil_y, int64_t dil_x, const void* d_fill, int64_t n_fill,
                            int64_t fill_stride, int64_t fill_extent, int es) {
     if (n_out <= 0) return;
-    VF_BY_ELEM_SIZE(es, (k_expand_dilated<ES><<<grid_for(n_out), kBlock, 0, ctx->stream>>>(
-                                in, in_splat ? 1 : 0, out, n_out, dky, dkx, ky, kx, dil_y, dil_x, d_fill, n_fill, fill_stride, fill_extent)));
+    VF_BY_ELEM_SIZE(es, VF_BY_INDEX_WIDTH(n_out, (k_expand_dilated<ES, I><<<grid_for(n_out), kBlock, 0, ctx->stream>>>(
+                                                         in, in_splat ? 1 : 0, out, I(n_out), I(dky), I(dkx), I(ky), I(kx), I(dil_y), I(dil_x),
+                                                         d_fill, I(n_fill), I(fill_stride), I(fill_extent)))));
     post_launch(ctx);
 }
 
 void launch_inverse(vf_ctx* ctx, const void* in, int in_dt, float* out, int64_t n) {
     if (n <= 0) return;
-    k_inverse<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, out, n, ctx->d_flags);
-    post_launch(ctx);
+    int64_t done = 0;
+    if (in_dt == VF_DT_F32 && n >= 4 && aligned16(in, out)) {
+        done = n / 4 * 4;
+        k_inverse_f32x4<<<grid_for(done / 4), kBlock, 0, ctx->stream>>>(static_cast<const float4*>(in), reinterpret_cast<float4*>(out), done / 4, ctx->d_flags);
+        post_launch(ctx);
+    }
+    if (done < n) {
+        k_inverse<<<grid_for(n - done), kBlock, 0, ctx->stream>>>(static_cast<const char*>(in) + done * (dtype_bits(in_dt) / 8), in_dt, out + done,
+                                                                 n - done, ctx->d_flags);
+        post_launch(ctx);
+    }
 }
 
 void launch_synth(vf_ctx* ctx, const vf_synth_spec& s, void* dst, uint64_t count) {
