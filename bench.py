@@ -653,7 +653,7 @@ def next_arm(args):
     orc = Oracle(nthreads=1)
     F32, F16, U8, I8, I32 = abi.VF_DT_F32, abi.VF_DT_F16, abi.VF_DT_U8, abi.VF_DT_I8, abi.VF_DT_I32
     TT = abi.TType
-    mib = max(16, int(512 * args.scale))
+    mib = max(16, int(2048 * args.scale))
     n8 = mib << 20  # bytes of the 8-bit inputs
     oc = 4096
     ops = [  # name, reference site, base type, storage dtype, list builder

@@ -607,21 +607,32 @@ __global__ void k_broadcast(const void* __restrict__ in, void* __restrict__ out,
 
 // ExpandDilated — attributes/expand_dilated.cpp:88-131: raw OIYX index arithmetic whatever the dims order;
 // positions between the taps hold the fill value (zero, or the zero point of output channel `fill` index)
+// One output row (dkx elements) per thread step: the divisions happen once per row, the taps of a row are
+// consecutive input elements, and neighbouring threads write neighbouring rows.
 template <int ES, typename I>
-__global__ void k_expand_dilated(const void* __restrict__ in, int in_splat, void* __restrict__ out, I n_out, I dky, I dkx, I ky,
+__global__ void k_expand_dilated(const void* __restrict__ in, int in_splat, void* __restrict__ out, I n_rows, I dky, I dkx, I ky,
                                  I kx, I dil_y, I dil_x, const void* __restrict__ fill, I n_fill, I fill_stride, I fill_extent) {
     using T = typename ElemBits<ES>::type;
     const I stride = index_stride<I>();
-    for (I o = first_index<I>(); o < n_out; o += stride) {
-        const I row = o / dkx, x = o - row * dkx;
+    for (I row = first_index<I>(); row < n_rows; row += stride) {
         const I plane = row / dky, y = row - plane * dky;
-        T v;
-        if (y % dil_y == 0 && x % dil_x == 0) {
-            v = static_cast<const T*>(in)[in_splat ? I(0) : (plane * ky + y / dil_y) * kx + x / dil_x];
-        } else {
-            v = static_cast<const T*>(fill)[n_fill > 1 ? (o / fill_stride) % fill_extent : I(0)];
+        const I ty = y / dil_y;
+        const bool tap_row = ty * dil_y == y;
+        const T* src = static_cast<const T*>(in) + (in_splat ? I(0) : (plane * ky + ty) * kx);
+        T* dst = static_cast<T*>(out) + row * dkx;
+        I next_tap = 0, tap = 0;  // x of the next tap and its index in the input row
+        for (I x = 0; x < dkx; ++x) {
+            T v;
+            if (tap_row && x == next_tap) {
+                v = src[in_splat ? I(0) : tap];
+                ++tap;
+                next_tap += dil_x;
+            } else {
+                const I o = row * dkx + x;
+                v = static_cast<const T*>(fill)[n_fill > 1 ? (o / fill_stride) % fill_extent : I(0)];
+            }
+            dst[x] = v;
         }
-        static_cast<T*>(out)[o] = v;
     }
 }
 
@@ -1078,8 +1089,9 @@ void launch_expand_dilated(vf_ctx* ctx, const void* in, bool in_splat, void* out
                            int64_t ky, int64_t kx, int64_t dil_y, int64_t dil_x, const void* d_fill, int64_t n_fill,
                            int64_t fill_stride, int64_t fill_extent, int es) {
     if (n_out <= 0) return;
-    VF_BY_ELEM_SIZE(es, VF_BY_INDEX_WIDTH(n_out, (k_expand_dilated<ES, I><<<grid_for(n_out), kBlock, 0, ctx->stream>>>(
-                                                         in, in_splat ? 1 : 0, out, I(n_out), I(dky), I(dkx), I(ky), I(kx), I(dil_y), I(dil_x),
+    const int64_t n_rows = n_out / dkx;
+    VF_BY_ELEM_SIZE(es, VF_BY_INDEX_WIDTH(n_out, (k_expand_dilated<ES, I><<<grid_for(n_rows), kBlock, 0, ctx->stream>>>(
+                                                         in, in_splat ? 1 : 0, out, I(n_rows), I(dky), I(dkx), I(ky), I(kx), I(dil_y), I(dil_x),
                                                          d_fill, I(n_fill), I(fill_stride), I(fill_extent)))));
     post_launch(ctx);
 }
