@@ -83,6 +83,30 @@ static void inferTypes() {
     EXPECT(thrown);
 }
 
+static void remainingTransformationTypes() {
+    // reverse.cpp:35-44 and inverse.cpp:40-50 keep the type; getDilatedType (utils/dilated_utils.cpp:11-34);
+    // broadcast.cpp:66-83 pads the type behind the axis; change_shape_and_elem_type.cpp:62-66
+    const TensorType f32({2, 3, 4, 5}, VF_DT_F32);
+    const std::vector<float> vals(120, 1.0f);
+    EXPECT((Const::ContentSetup(f32).reverse(1).get(vals.data(), bytesOf(vals)).getType().getShape() == std::vector<int64_t>{2, 3, 4, 5}));
+    EXPECT((Const::ContentSetup(f32).expandDilated({3, 2}).get(vals.data(), bytesOf(vals)).getType().getShape() ==
+            std::vector<int64_t>{2, 3, 10, 9}));
+    EXPECT((Const::ContentSetup(f32).broadcast(1, 6).get(vals.data(), bytesOf(vals)).getType().getShape() == std::vector<int64_t>{2, 6, 4, 5}));
+    EXPECT(Const::ContentSetup(f32).scalarMultInverse().get(vals.data(), bytesOf(vals)).getType().getElementType().dtype() == VF_DT_F32);
+    const auto q = ElemType::perAxis(VF_DT_U8, VF_DT_F16, {0.5, 0.5}, {127, 127}, 1, 0, 255);
+    const TensorType u8({2, 1, 1, 8}, VF_DT_U8);
+    const std::vector<uint8_t> bytes(16, 7);
+    const TensorType changed = Const::ContentSetup(u8).changeShapeAndElemType({1, 2, 1, 8}, q).get(bytes.data(), bytesOf(bytes)).getType();
+    EXPECT((changed.getShape() == std::vector<int64_t>{1, 2, 1, 8}) && changed.getElementType().kind() == VF_ELEM_QUANT_PER_AXIS);
+    bool thrown = false;
+    try {  // a broadcast below the current extent
+        (void)Const::ContentSetup(f32).broadcast(1, 2).get(vals.data(), bytesOf(vals)).getType();
+    } catch (const Exception& e) {
+        thrown = e.status() == VF_ERR_SHAPE;
+    }
+    EXPECT(thrown);
+}
+
 static void optimizedLists() {
     // content_setup.cpp:720-747 FuseSubView
     const TensorType i8({1, 7, 5}, VF_DT_I8);
@@ -260,6 +284,7 @@ int main(int argc, char** argv) {
     EXPECT(vf_abi_version() == VF_ABI_VERSION);
     positionRequirement();
     inferTypes();
+    remainingTransformationTypes();
     optimizedLists();
     if (!hostOnly) {
         try {
