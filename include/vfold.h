@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define VF_MAX_RANK 5
+#define VF_MAX_RANK 6
 #define VF_ABI_VERSION 1
 
 /* ------------------------------------------------------------------ */

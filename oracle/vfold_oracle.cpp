@@ -289,7 +289,7 @@ struct Type {
     Elem elem;
     int rank = 0;
     uint32_t order = 0;
-    int64_t shape[VF_MAX_RANK] = {0, 0, 0, 0, 0};
+    int64_t shape[VF_MAX_RANK] = {};
     int64_t numel() const {
         int64_t n = 1;
         for (int i = 0; i < rank; ++i) n *= shape[i];

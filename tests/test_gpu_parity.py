@@ -923,3 +923,17 @@ def test_fold_into_device_memory_matches_fold_into_host_memory(gpu):
             assert np.array_equal(out[:written], ref.bytes()), (s.names(), in_place)
             if not in_place:
                 assert (out[cap:] == 0xAB).all()
+
+
+@pytest.mark.gpu
+def test_rank_six_layout_transformations(gpu, oracle):
+    rng = np.random.default_rng(66)
+    shape = [2, 3, 2, 4, 3, 5]
+    t = TType(shape, F16)
+    x = rng.standard_normal(shape).astype(np.float16)
+    for s in (ContentSetup(t).reorder(0x132546), ContentSetup(t).transpose(0x654321),
+              ContentSetup(t).padWithZero([0, 1, 0, 0, 2, 0], [1, 0, 0, 3, 0, 1]),
+              ContentSetup(t).subview([1, 0, 1, 2, 0, 1], [1, 3, 1, 2, 3, 3]),
+              ContentSetup(t).reorder(0x213465).subview([0, 1, 0, 0, 1, 2], [2, 2, 2, 4, 2, 3]).reorder(0x123456).reshape([2, 2, 8, 6]),
+              ContentSetup(t).reverse(2), ContentSetup(t).broadcast(2, 6).reorder(0x654321)):
+        both(ContentAttr(x, t, s), gpu, oracle)

@@ -235,7 +235,7 @@ def _per_axis(axis, n):
 
 
 # CS:1377-1403 swapChangeShapeAndElemTypeAndSubViewParams: base shape, (cast axis, n), (changeShape shape, axis, n),
-# SubView -> expected cast scales, changeShape (shape, axis, scales), SubView. The reference's fifth case has rank 6.
+# SubView -> expected cast scales, changeShape (shape, axis, scales), SubView.
 CHANGE_SHAPE_SWAPS = [
     ([1, 4, 1, 2], (1, 4), ([4, 2, 1, 1], 0, 4), ([0, 0, 0, 0], [3, 2, 1, 1]),
      [1.0, 2.0, 3.0], ([3, 2, 1, 1], 0, [1.0, 2.0, 3.0]), ([0, 0, 0, 0], [1, 3, 1, 2])),
@@ -245,6 +245,8 @@ CHANGE_SHAPE_SWAPS = [
      [1.0, 2.0], ([1, 2, 4], 1, [1.0, 2.0]), ([0, 0, 0, 0], [1, 2, 2, 2])),
     ([1, 8, 4], (1, 8), ([1, 8, 2, 2], 1, 8), ([0, 1, 0, 0], [1, 4, 2, 2]),
      [2.0, 3.0, 4.0, 5.0], ([1, 4, 2, 2], 1, [2.0, 3.0, 4.0, 5.0]), ([0, 1, 0], [1, 4, 4])),
+    ([1, 8, 6, 4, 3, 3], (1, 8), ([8, 6, 4, 9], 0, 8), ([2, 1, 0, 0], [4, 3, 4, 9]),
+     [3.0, 4.0, 5.0, 6.0], ([4, 3, 4, 9], 0, [3.0, 4.0, 5.0, 6.0]), ([0, 2, 1, 0, 0, 0], [1, 4, 3, 4, 3, 3])),
 ]
 
 

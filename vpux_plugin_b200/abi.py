@@ -8,7 +8,7 @@ import ctypes as C
 
 import numpy as np
 
-VF_MAX_RANK = 5
+VF_MAX_RANK = 6
 
 # vf_status
 VF_OK = 0

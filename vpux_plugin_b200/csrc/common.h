@@ -92,7 +92,7 @@ struct Type {
     Elem elem;
     int rank = 0;
     uint32_t order = 0;
-    int64_t shape[VF_MAX_RANK] = {0, 0, 0, 0, 0};
+    int64_t shape[VF_MAX_RANK] = {};
 
     static Type from(const vf_tensor_type& t);
     int64_t numel() const;

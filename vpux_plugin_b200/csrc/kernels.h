@@ -6,7 +6,7 @@
 
 namespace vf {
 
-struct Geom {  // index geometry shared by the layout kernels (rank <= 5, memory order)
+struct Geom {  // index geometry shared by the layout kernels (rank <= VF_MAX_RANK, memory order)
     int rank;
     int64_t in_shape[VF_MAX_RANK];   // input memory shape
     int64_t out_shape[VF_MAX_RANK];  // output memory shape
