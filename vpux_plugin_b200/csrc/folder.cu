@@ -559,7 +559,9 @@ int vf_folder_create(int device, const vf_folder_options* opts, vf_folder** out,
         char e[256];
         auto make_ctx = [&] {
             vf_ctx* c = nullptr;
-            const int st = vf_ctx_create(device, nullptr, nullptr, &c, e, sizeof(e));
+            vf_options o{};
+            o.staging_bytes = 16u << 20;  // per bounce buffer; a folder holds one context per worker plus one
+            const int st = vf_ctx_create(device, &o, nullptr, &c, e, sizeof(e));
             if (st != VF_OK) raise(st, "%s", e);
             return c;
         };
