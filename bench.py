@@ -506,7 +506,8 @@ def conv_arm(args, workload):
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
-    lib = Library(device=0, stream=stream.cuda_stream)
+    # the calls of a step are enqueued without a synchronisation in between (VF_OPT_ASYNC); every step ends with one
+    lib = Library(device=0, stream=stream.cuda_stream, pipelined=not args.sync_calls)
     key = workload.key
     specs = workload.tensors
     jobs = (abi.QuantJob * len(specs))()
@@ -593,6 +594,7 @@ def conv_arm(args, workload):
         e0.record(stream)
         step()
         e1.record(stream)
+        lib.synchronize()  # reports what the step's kernels flagged
         torch.cuda.synchronize()
         ms += e0.elapsed_time(e1)
     launches = (lib.launch_count - l0) // args.steps
@@ -622,7 +624,8 @@ def conv_arm(args, workload):
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload.desc, "input_bytes": in_bytes, "tensors_rank0": len(specs),
-                   "l2": "256 MiB written between timed steps (inputs fit the 126 MB L2)"},
+                   "l2": "256 MiB written between timed steps (inputs fit the 126 MB L2)",
+                   "calls": "synchronous" if args.sync_calls else "pipelined (VF_OPT_ASYNC) within a step, one synchronisation per step"},
         "roofline": {"bound": "hbm", "kernel": workload.kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
                      "note": "whole step (all launches of the step, host gaps between synchronous calls included)"},
