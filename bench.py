@@ -669,6 +669,18 @@ def next_arm(args):
         ("CastElemType f32->f8e4m3 + copyTo", "content.hpp:66-71", TT([n8 // 4], F32), F32, lambda s: s.castElemType(abi.VF_DT_F8E4M3FN)),
         ("RelocateWeightsTable 1M rows", "relocate_weights_table.cpp:203-292", TT([1 << 20, 1, 1, 4], I32), I32,
          lambda s: s.relocateWeightsTablePointers([1 << 10, 1 << 20], 64, [0, 1 << 19], 16 << 20, 16)),
+        # the general (unfused) kernels of the path itself, one transformation per call
+        ("Quantize per-axis f32->i8", "quantize.cpp:108-212", TT([oc, n8 // oc // 4], F32), F32,
+         lambda s: s.quantize(abi.Elem.per_axis(I8, F32, [0.01 + 1e-5 * i for i in range(oc)], [0] * oc, 0, -127, 127))),
+        ("Dequantize per-axis i8->f32", "dequantize.cpp:42-108", TT([oc, n8 // oc // 4], I8), I8,
+         lambda s: s.castElemType(abi.Elem.per_axis(I8, F32, [0.01 + 1e-5 * i for i in range(oc)], [0] * oc, 0, -127, 127)).dequantize()),
+        ("Rescale f32", "rescale.cpp:67-82", TT([n8 // 4], F32), F32, lambda s: s.rescale(0.5)),
+        ("Reorder OIYX->OYXI f16", "reorder.cpp:79-99", TT([oc, 64, 3, n8 // 2 // oc // 64 // 3], F16), F16, lambda s: s.reorder(abi.ORDER_NHWC)),
+        ("PadWithZero IC 48->64 f16", "pad_with_zero.cpp:111-268", TT([oc, 48, 3, n8 // 2 // oc // 48 // 3], F16), F16,
+         lambda s: s.padWithZero([0, 0, 0, 0], [0, 16, 0, 0])),
+        ("SubView half the channels f16", "subview.cpp:390-432", TT([oc, n8 // 2 // oc], F16), F16,
+         lambda s: s.subview([oc // 4, 0], [oc // 2, n8 // 2 // oc])),
+        ("BitPack<4> u8", "bit_pack.cpp:132-154", TT([n8], U8), U8, lambda s: s.bitPack(4)),
     ]
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
@@ -687,6 +699,8 @@ def next_arm(args):
         src = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
         if storage == I32:  # a table whose pointer columns step by 16
             src.view(torch.int32).copy_(torch.arange(in_bytes // 4, device=dev, dtype=torch.int32) // 4 * 16 % (1 << 20))
+        elif name.startswith("BitPack"):
+            src.random_(0, 16)
         else:
             src.random_(1, 120)
         if storage == F32:  # finite, normal floats

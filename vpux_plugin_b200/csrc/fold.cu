@@ -55,7 +55,9 @@ DContent alloc_like(vf_ctx* ctx, const Type& type, int storage, bool splat, int6
     // A dense buffer whose storage is the logical element type is what copyTo would copy byte for byte: write it
     // where it has to end up. (If this turns out to be a scratch buffer of the transformation, the result is
     // copied over it afterwards, in stream order.)
-    if (ctx->final_dst && !splat && storage == type.elem.dtype && dtype_bits(storage) >= 8 && c.nbytes > 0 &&
+    // (a sub-byte logical type is copied as stored whenever the destination holds all of it)
+    const bool as_stored = (storage == type.elem.dtype && dtype_bits(storage) >= 8) || dtype_bits(type.elem.dtype) < 8;
+    if (ctx->final_dst && !splat && as_stored && c.nbytes > 0 &&
         c.nbytes <= ctx->final_bytes && (reinterpret_cast<uintptr_t>(ctx->final_dst) & 15u) == 0) {
         c.own = DBuf::borrow(ctx->final_dst, c.nbytes);
         ctx->final_dst = nullptr;

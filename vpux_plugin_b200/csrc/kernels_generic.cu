@@ -20,6 +20,19 @@ inline bool aligned16(const void* a, const void* b) {
     return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
 }
 
+#define VF_BY_ELEM_SIZE(es, CALL)                                                   \
+    switch (es) {                                                                   \
+    case 1: { constexpr int ES = 1; CALL; break; }                                  \
+    case 2: { constexpr int ES = 2; CALL; break; }                                  \
+    case 4: { constexpr int ES = 4; CALL; break; }                                  \
+    case 8: { constexpr int ES = 8; CALL; break; }                                  \
+    case 16: { constexpr int ES = 16; CALL; break; }                                \
+    default: raise(VF_ERR_UNSUPPORTED, "element size %d", es);                      \
+    }
+// I = uint32_t while every index of the launch stays below 2^31, int64_t otherwise
+#define VF_BY_INDEX_WIDTH(n, CALL)                                                  \
+    if ((n) < (int64_t(1) << 31)) { using I = uint32_t; CALL; } else { using I = int64_t; CALL; }
+
 // ------------------------------------------------------------------------------------------------------
 // Quantize — attributes/quantize.cpp:108-212
 // ------------------------------------------------------------------------------------------------------
@@ -62,6 +75,92 @@ __global__ void k_rescale_add(const void* __restrict__ in, int in_dt, int in_spl
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float v = load_as_f32(in, in_dt, in_splat ? 0 : i, flags);
         out[i] = is_add ? __fadd_rn(v, c) : __fmul_rn(v, c);
+    }
+}
+
+// ---- eight elements per thread step ---------------------------------------------------------------------
+// The elementwise transformations on dense float / 8-bit buffers: one 16-byte load (two for f32) and one or two
+// 16-byte stores per step, the per-axis parameters looked up once per step (the launchers take this path only
+// when a step never straddles two channels: inner % 8 == 0).
+template <int DT>
+struct Bytes8 { static constexpr int value = (DT == VF_DT_F32 ? 4 : (DT == VF_DT_F16 || DT == VF_DT_BF16) ? 2 : 1) * 8; };
+
+template <int DT>
+__device__ __forceinline__ void load8(const void* __restrict__ in, int64_t g, uint8_t* buf) {
+    if (Bytes8<DT>::value == 32) {
+        reinterpret_cast<uint4*>(buf)[0] = __ldg(reinterpret_cast<const uint4*>(in) + 2 * g);
+        reinterpret_cast<uint4*>(buf)[1] = __ldg(reinterpret_cast<const uint4*>(in) + 2 * g + 1);
+    } else if (Bytes8<DT>::value == 16) {
+        reinterpret_cast<uint4*>(buf)[0] = __ldg(reinterpret_cast<const uint4*>(in) + g);
+    } else {
+        reinterpret_cast<uint2*>(buf)[0] = __ldg(reinterpret_cast<const uint2*>(in) + g);
+    }
+}
+template <int BYTES>
+__device__ __forceinline__ void store8(void* __restrict__ out, int64_t g, const uint8_t* buf) {
+    if (BYTES == 32) {
+        reinterpret_cast<uint4*>(out)[2 * g] = reinterpret_cast<const uint4*>(buf)[0];
+        reinterpret_cast<uint4*>(out)[2 * g + 1] = reinterpret_cast<const uint4*>(buf)[1];
+    } else if (BYTES == 16) {
+        reinterpret_cast<uint4*>(out)[g] = reinterpret_cast<const uint4*>(buf)[0];
+    } else {
+        reinterpret_cast<uint2*>(out)[g] = reinterpret_cast<const uint2*>(buf)[0];
+    }
+}
+
+template <int IN, typename I>
+__global__ void k_quantize8(const void* __restrict__ in, uint8_t* __restrict__ out, I n_groups, const double* __restrict__ scales,
+                            const int64_t* __restrict__ zps, I axis_size, I inner8, long long qmin, long long qmax, int* flags) {
+    const I stride = I(gridDim.x) * I(blockDim.x);
+    for (I g = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); g < n_groups; g += stride) {
+        const I a = axis_size > 1 ? (g / inner8) % axis_size : I(0);
+        const QuantParams qp = make_quant_params(scales[a], zps[a], qmin, qmax);
+        __align__(16) uint8_t ib[Bytes8<IN>::value];
+        __align__(8) uint8_t ob[8];
+        load8<IN>(in, int64_t(g), ib);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float x = load_as_f32(ib, IN, k, flags);
+            if (x != x) set_flag(flags, VF_FLAG_NAN);
+            ob[k] = uint8_t(quantize_exact(x, qp));
+        }
+        store8<8>(out, int64_t(g), ob);
+    }
+}
+
+template <int IN, typename I>
+__global__ void k_dequantize8(const void* __restrict__ in, float* __restrict__ out, I n_groups, const double* __restrict__ scales,
+                              const int64_t* __restrict__ zps, I axis_size, I inner8) {
+    const I stride = I(gridDim.x) * I(blockDim.x);
+    for (I g = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); g < n_groups; g += stride) {
+        const I a = axis_size > 1 ? (g / inner8) % axis_size : I(0);
+        const double scale = scales[a];
+        const long long zp = zps[a];
+        __align__(8) uint8_t ib[8];
+        __align__(16) float ob[8];
+        load8<IN>(in, int64_t(g), ib);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const long long q = IN == VF_DT_I8 ? (long long)(int8_t(ib[k])) : (long long)(ib[k]);
+            ob[k] = dequantize_exact(q, scale, zp);
+        }
+        store8<32>(out, int64_t(g), reinterpret_cast<const uint8_t*>(ob));
+    }
+}
+
+template <int IN>
+__global__ void k_rescale_add8(const void* __restrict__ in, float* __restrict__ out, int64_t n_groups, float c, int is_add, int* flags) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        __align__(16) uint8_t ib[Bytes8<IN>::value];
+        __align__(16) float ob[8];
+        load8<IN>(in, g, ib);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float v = load_as_f32(ib, IN, k, flags);
+            ob[k] = is_add ? __fadd_rn(v, c) : __fmul_rn(v, c);
+        }
+        store8<32>(out, g, reinterpret_cast<const uint8_t*>(ob));
     }
 }
 
@@ -251,67 +350,131 @@ template <> struct ElemOf<1> { using T = uint8_t; };
 template <> struct ElemOf<2> { using T = uint16_t; };
 template <> struct ElemOf<4> { using T = uint32_t; };
 template <> struct ElemOf<8> { using T = uint64_t; };
+template <> struct ElemOf<16> { using T = uint4; };
+
+// The layout kernels work on a geometry the launchers have simplified on the host: neighbouring dims that are
+// contiguous on both sides are merged, a contiguous innermost dim is regrouped into elements of up to 16 bytes,
+// and the index arithmetic runs in 32 bits (I = uint32_t) whenever all extents allow it.
 
 // memPermuteTransformation — utils/transformations.cpp:889-939, gathered from the output side so that the
 // stores are coalesced
-template <int ES>
-__global__ void k_permute(const void* __restrict__ in, void* __restrict__ out, Geom g, int64_t n) {
+template <int ES, typename I>
+__global__ void k_permute(const void* __restrict__ in, void* __restrict__ out, Geom g, I n) {
     using T = typename ElemOf<ES>::T;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
-        int64_t rem = o, src = 0;
+    const I stride = I(gridDim.x) * I(blockDim.x);
+    for (I o = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); o < n; o += stride) {
+        I rem = o, src = 0;
 #pragma unroll
         for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
             if (d < g.rank) {
-                const int64_t c = rem % g.out_shape[d];
-                rem /= g.out_shape[d];
-                src += c * g.src_stride[d];
+                const I os = I(g.out_shape[d]);
+                const I q = rem / os;
+                src += (rem - q * os) * I(g.src_stride[d]);
+                rem = q;
             }
         }
         static_cast<T*>(out)[o] = static_cast<const T*>(in)[src];
     }
 }
 
-// PadWithZero — attributes/pad_with_zero.cpp:111-268 + Content::fillWithZero utils/content.cpp:190-237
-template <int ES>
-__global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restrict__ out, Geom g, int64_t n,
-                      const void* __restrict__ fill, int64_t n_fill, int fill_dim) {
+// The same permutation through a 32 x 32 shared-memory tile, for geometries whose innermost output dim is not
+// the innermost input dim: dim `a` (innermost on the output side) and dim `b` (the one with source stride 1)
+// span the tile, so that the loads run along b and the stores along a, both coalesced. One CTA of 32 x 8 threads
+// per tile; blockIdx.x enumerates (other dims, tiles along a, tiles along b).
+template <int ES, typename I>
+__global__ void k_permute_tiled(const void* __restrict__ in, void* __restrict__ out, Geom g, int b, I tiles_a, I tiles_b,
+                                I dst_stride_b) {
     using T = typename ElemOf<ES>::T;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
-        int64_t rem = o, src = 0, fc = 0;
+    __shared__ T tile[32][33];
+    const int a = g.rank - 1;
+    I rem = I(blockIdx.x);
+    const I tb = rem % tiles_b;
+    rem /= tiles_b;
+    const I ta = rem % tiles_a;
+    rem /= tiles_a;
+    I src0 = 0, dst0 = 0, dst_mul = 1;  // base offsets from the coordinates of the other dims
+#pragma unroll
+    for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+        if (d < g.rank) {
+            const I os = I(g.out_shape[d]);
+            if (d != a && d != b) {
+                const I q = rem / os;
+                const I c = rem - q * os;
+                rem = q;
+                src0 += c * I(g.src_stride[d]);
+                dst0 += c * dst_mul;
+            }
+            dst_mul *= os;
+        }
+    }
+    const I ea = I(g.out_shape[a]), eb = I(g.out_shape[b]);
+    const I a0 = ta * 32, b0 = tb * 32;
+    const I sa = I(g.src_stride[a]);
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {  // rows of the tile run along a, columns along b (source stride 1)
+        const I ia = a0 + threadIdx.y + i, ib = b0 + threadIdx.x;
+        if (ia < ea && ib < eb) tile[threadIdx.y + i][threadIdx.x] = static_cast<const T*>(in)[src0 + ia * sa + ib];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {  // stores: rows along b, columns along a (destination stride 1)
+        const I ib = b0 + threadIdx.y + i, ia = a0 + threadIdx.x;
+        if (ia < ea && ib < eb) static_cast<T*>(out)[dst0 + ib * dst_stride_b + ia] = tile[threadIdx.x][threadIdx.y + i];
+    }
+}
+
+template <int ES>
+__device__ __forceinline__ typename ElemOf<ES>::T wide_fill(const uint8_t* __restrict__ fill, int fill_es) {
+    // the fill element (fill_es bytes) repeated over the ES bytes of a regrouped element
+    __align__(16) uint8_t buf[ES];
+#pragma unroll
+    for (int k = 0; k < ES; ++k) buf[k] = fill[k % fill_es];
+    return *reinterpret_cast<typename ElemOf<ES>::T*>(buf);
+}
+
+// PadWithZero — attributes/pad_with_zero.cpp:111-268 + Content::fillWithZero utils/content.cpp:190-237
+template <int ES, typename I>
+__global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restrict__ out, Geom g, I n,
+                      const uint8_t* __restrict__ fill, int fill_es, I n_fill, int fill_dim) {
+    using T = typename ElemOf<ES>::T;
+    const I stride = I(gridDim.x) * I(blockDim.x);
+    for (I o = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); o < n; o += stride) {
+        I rem = o, src = 0, fc = 0;
         bool inside = true;
 #pragma unroll
         for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
             if (d < g.rank) {
-                const int64_t c = rem % g.out_shape[d];
-                rem /= g.out_shape[d];
+                const I os = I(g.out_shape[d]);
+                const I q = rem / os;
+                const I c = rem - q * os;
+                rem = q;
                 if (d == fill_dim) fc = c;
-                const int64_t ci = c - g.offset[d];
-                inside &= (ci >= 0) && (ci < g.in_shape[d]);
-                src += ci * g.src_stride[d];
+                const I ci = c - I(g.offset[d]);  // wraps below zero for I = uint32_t: caught by the range test
+                inside &= c >= I(g.offset[d]) && ci < I(g.in_shape[d]);
+                src += ci * I(g.src_stride[d]);
             }
         }
         T v;
-        if (inside) v = static_cast<const T*>(in)[in_splat ? 0 : src];
-        else v = static_cast<const T*>(fill)[n_fill > 1 ? fc : 0];
+        if (inside) v = static_cast<const T*>(in)[in_splat ? I(0) : src];
+        else v = wide_fill<ES>(fill + (n_fill > 1 ? fc : I(0)) * I(fill_es), fill_es);
         static_cast<T*>(out)[o] = v;
     }
 }
 
 // SubView — attributes/subview.cpp:390-432
-template <int ES>
-__global__ void k_subview(const void* __restrict__ in, void* __restrict__ out, Geom g, int64_t n) {
+template <int ES, typename I>
+__global__ void k_subview(const void* __restrict__ in, void* __restrict__ out, Geom g, I n) {
     using T = typename ElemOf<ES>::T;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
-        int64_t rem = o, src = 0;
+    const I stride = I(gridDim.x) * I(blockDim.x);
+    for (I o = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); o < n; o += stride) {
+        I rem = o, src = 0;
 #pragma unroll
         for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
             if (d < g.rank) {
-                const int64_t c = rem % g.out_shape[d];
-                rem /= g.out_shape[d];
-                src += (c + g.offset[d]) * g.src_stride[d];
+                const I os = I(g.out_shape[d]);
+                const I q = rem / os;
+                src += (rem - q * os + I(g.offset[d])) * I(g.src_stride[d]);
+                rem = q;
             }
         }
         static_cast<T*>(out)[o] = static_cast<const T*>(in)[src];
@@ -800,6 +963,22 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
                      const double* d_scales, const int64_t* d_zps, int64_t axis_size, int64_t inner, int64_t qmin,
                      int64_t qmax) {
     if (n <= 0) return;
+    const bool f_in = in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16;
+    if (!in_splat && f_in && (out_dt == VF_DT_I8 || out_dt == VF_DT_U8) && n % 8 == 0 && (axis_size <= 1 || inner % 8 == 0) &&
+        aligned16(in, out)) {
+        const int64_t groups = n / 8, inner8 = axis_size > 1 ? inner / 8 : 1;
+        const int grid = grid_for(groups);
+        uint8_t* o = static_cast<uint8_t*>(out);
+#define VF_Q8(IN)                                                                                                             \
+    VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps, I(axis_size), \
+                                                                                    I(inner8), qmin, qmax, ctx->d_flags)))
+        if (in_dt == VF_DT_F32) { VF_Q8(VF_DT_F32); }
+        else if (in_dt == VF_DT_F16) { VF_Q8(VF_DT_F16); }
+        else { VF_Q8(VF_DT_BF16); }
+#undef VF_Q8
+        post_launch(ctx);
+        return;
+    }
     k_quantize<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, out_dt, n, d_scales, d_zps, axis_size,
                                                         inner, qmin, qmax, ctx->d_flags);
     post_launch(ctx);
@@ -808,6 +987,20 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
 void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, float* out, int64_t n,
                        const double* d_scales, const int64_t* d_zps, int64_t axis_size, int64_t inner) {
     if (n <= 0) return;
+    if (!in_splat && (in_dt == VF_DT_I8 || in_dt == VF_DT_U8) && n % 8 == 0 && (axis_size <= 1 || inner % 8 == 0) &&
+        aligned16(in, out)) {
+        const int64_t groups = n / 8, inner8 = axis_size > 1 ? inner / 8 : 1;
+        const int grid = grid_for(groups);
+        if (in_dt == VF_DT_I8) {
+            VF_BY_INDEX_WIDTH(groups, (k_dequantize8<VF_DT_I8, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, I(groups), d_scales, d_zps,
+                                                                                                    I(axis_size), I(inner8))));
+        } else {
+            VF_BY_INDEX_WIDTH(groups, (k_dequantize8<VF_DT_U8, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, I(groups), d_scales, d_zps,
+                                                                                                    I(axis_size), I(inner8))));
+        }
+        post_launch(ctx);
+        return;
+    }
     k_dequantize<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, n, d_scales, d_zps, axis_size, inner,
                                                           ctx->d_flags);
     post_launch(ctx);
@@ -816,8 +1009,21 @@ void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, fl
 void launch_rescale_add(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, float* out, int64_t n, float c,
                         bool is_add) {
     if (n <= 0) return;
-    k_rescale_add<<<grid_for(n), kBlock, 0, ctx->stream>>>(in, in_dt, in_splat, out, n, c, is_add, ctx->d_flags);
-    post_launch(ctx);
+    int64_t done = 0;
+    if (!in_splat && n >= 8 && aligned16(in, out) && (in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16)) {
+        const int64_t groups = n / 8;
+        const int grid = grid_for(groups);
+        if (in_dt == VF_DT_F32) k_rescale_add8<VF_DT_F32><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, c, is_add, ctx->d_flags);
+        else if (in_dt == VF_DT_F16) k_rescale_add8<VF_DT_F16><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, c, is_add, ctx->d_flags);
+        else k_rescale_add8<VF_DT_BF16><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, c, is_add, ctx->d_flags);
+        post_launch(ctx);
+        done = groups * 8;
+    }
+    if (done < n) {
+        k_rescale_add<<<grid_for(n - done), kBlock, 0, ctx->stream>>>(static_cast<const char*>(in) + done * (dtype_bits(in_dt) / 8), in_dt,
+                                                                      in_splat, out + done, n - done, c, is_add, ctx->d_flags);
+        post_launch(ctx);
+    }
 }
 
 template <int IN>
@@ -892,45 +1098,142 @@ static int64_t out_numel(const Geom& g) {
     return n;
 }
 
-void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es) {
+// ---- host-side simplification of a layout geometry ---------------------------------------------------------
+// kind: 0 permute (offset / in_shape unused), 1 subview (source coordinate = c + offset), 2 pad (c - offset,
+// inside while below in_shape). `keep` is a dim that must stay as it is (the per-channel fill dim of a pad), or -1.
+static void merge_dims(Geom& g, int kind, int& keep) {
+    for (int d = g.rank - 2; d >= 0; --d) {
+        const int e = d + 1;
+        if (d == keep || e == keep) continue;
+        bool ok;
+        if (kind == 0) {
+            ok = g.src_stride[d] == g.src_stride[e] * g.out_shape[e];
+        } else {  // the inner dim is taken whole, and the outer one steps over exactly one inner extent
+            ok = g.offset[e] == 0 && g.out_shape[e] == g.in_shape[e] && g.src_stride[d] == g.src_stride[e] * g.in_shape[e];
+        }
+        if (!ok) continue;
+        g.offset[d] = g.offset[d] * g.out_shape[e];
+        g.in_shape[d] = g.in_shape[d] * g.in_shape[e];
+        g.out_shape[d] = g.out_shape[d] * g.out_shape[e];
+        g.src_stride[d] = g.src_stride[e];
+        for (int k = e; k + 1 < g.rank; ++k) {
+            g.out_shape[k] = g.out_shape[k + 1];
+            g.in_shape[k] = g.in_shape[k + 1];
+            g.src_stride[k] = g.src_stride[k + 1];
+            g.offset[k] = g.offset[k + 1];
+        }
+        --g.rank;
+        if (keep > e) --keep;
+    }
+}
+
+// Regroups a contiguous innermost dim into elements of up to 16 bytes; returns the new element size.
+static int widen(Geom& g, int kind, int es, const void* in, const void* out, bool in_splat, int keep) {
+    const int L = g.rank - 1;
+    if (L < 0 || g.src_stride[L] != 1 || in_splat || L == keep) return es;
+    int w = es;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out);
+    while (w < 16) {
+        const int64_t k = 2 * w / es;  // elements per regrouped element if we double once more
+        bool ok = g.out_shape[L] % k == 0 && (addr % uintptr_t(2 * w)) == 0;
+        if (kind != 0) ok = ok && g.in_shape[L] % k == 0 && g.offset[L] % k == 0;
+        for (int d = 0; d < L && ok; ++d) ok = g.src_stride[d] % k == 0;
+        if (!ok) break;
+        w *= 2;
+    }
+    const int64_t k = w / es;
+    if (k > 1) {
+        g.out_shape[L] /= k;
+        g.in_shape[L] /= k;
+        g.offset[L] /= k;
+        for (int d = 0; d < L; ++d) g.src_stride[d] /= k;
+    }
+    return w;
+}
+
+static int64_t max_index(const Geom& g, int kind) {  // largest element index any side of the launch can reach
+    int64_t src = 0;
+    for (int d = 0; d < g.rank; ++d) {
+        const int64_t ext = kind == 0 ? g.out_shape[d] : (kind == 1 ? g.out_shape[d] + g.offset[d] : std::max(g.in_shape[d], g.out_shape[d]));
+        src += ext * g.src_stride[d];
+    }
+    return std::max(src, out_numel(g));
+}
+
+void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int es0) {
+    Geom g = g0;
+    if (out_numel(g) <= 0) return;
+    int keep = -1;
+    merge_dims(g, 0, keep);
+    const int es = widen(g, 0, es0, in, out, false, -1);
     const int64_t n = out_numel(g);
-    if (n <= 0) return;
+    const bool small = max_index(g, 0) < (int64_t(1) << 31);
+    // a dim other than the innermost output dim is contiguous in the source: transpose through shared memory
+    int b = -1;
+    const int a = g.rank - 1;
+    for (int d = 0; d < a; ++d)
+        if (g.src_stride[d] == 1 && g.out_shape[d] >= 8) b = d;
+    if (small && es <= 8 && b >= 0 && g.src_stride[a] != 1 && g.out_shape[a] >= 8) {
+        const int64_t ta = (g.out_shape[a] + 31) / 32, tb = (g.out_shape[b] + 31) / 32;
+        int64_t others = 1, dst_stride_b = 1;
+        for (int d = 0; d < g.rank; ++d)
+            if (d != a && d != b) others *= g.out_shape[d];
+        for (int d = b + 1; d < g.rank; ++d) dst_stride_b *= g.out_shape[d];
+        const int64_t blocks = others * ta * tb;
+        if (blocks < (int64_t(1) << 31)) {
+            const dim3 block(32, 8);
+            using I = uint32_t;
+            VF_BY_ELEM_SIZE(es, (k_permute_tiled<(ES > 8 ? 8 : ES), I><<<unsigned(blocks), block, 0, ctx->stream>>>(in, out, g, b, I(ta), I(tb), I(dst_stride_b))));
+            post_launch(ctx);
+            return;
+        }
+    }
     const int grid = grid_for(n);
-    switch (es) {
-    case 1: k_permute<1><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    case 2: k_permute<2><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    case 4: k_permute<4><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    case 8: k_permute<8><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    default: raise(VF_ERR_UNSUPPORTED, "permute of %d-byte elements", es);
+    if (small) {
+        using I = uint32_t;
+        VF_BY_ELEM_SIZE(es, (k_permute<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, I(n))));
+    } else {
+        using I = int64_t;
+        VF_BY_ELEM_SIZE(es, (k_permute<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, I(n))));
     }
     post_launch(ctx);
 }
 
-void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geom& g, int es, const void* d_fill,
+void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geom& g0, int es0, const void* d_fill,
                 int64_t n_fill, int fill_dim) {
+    Geom g = g0;
+    if (out_numel(g) <= 0) return;
+    int keep = n_fill > 1 ? fill_dim : -1;
+    if (!in_splat) merge_dims(g, 2, keep);
+    const int es = widen(g, 2, es0, in, out, in_splat, keep);
     const int64_t n = out_numel(g);
-    if (n <= 0) return;
     const int grid = grid_for(n);
-    switch (es) {
-    case 1: k_pad<1><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
-    case 2: k_pad<2><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
-    case 4: k_pad<4><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
-    case 8: k_pad<8><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, n, d_fill, n_fill, fill_dim); break;
-    default: raise(VF_ERR_UNSUPPORTED, "pad of %d-byte elements", es);
+    const uint8_t* fill = static_cast<const uint8_t*>(d_fill);
+    const int fd = n_fill > 1 ? keep : 0;
+    if (max_index(g, 2) < (int64_t(1) << 31)) {
+        using I = uint32_t;
+        VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, I(n), fill, es0, I(n_fill), fd)));
+    } else {
+        using I = int64_t;
+        VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, I(n), fill, es0, I(n_fill), fd)));
     }
     post_launch(ctx);
 }
 
-void launch_subview(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es) {
+void launch_subview(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int es0) {
+    Geom g = g0;
+    if (out_numel(g) <= 0) return;
+    int keep = -1;
+    merge_dims(g, 1, keep);
+    const int es = widen(g, 1, es0, in, out, false, -1);
     const int64_t n = out_numel(g);
-    if (n <= 0) return;
     const int grid = grid_for(n);
-    switch (es) {
-    case 1: k_subview<1><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    case 2: k_subview<2><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    case 4: k_subview<4><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    case 8: k_subview<8><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, n); break;
-    default: raise(VF_ERR_UNSUPPORTED, "subview of %d-byte elements", es);
+    if (max_index(g, 1) < (int64_t(1) << 31)) {
+        using I = uint32_t;
+        VF_BY_ELEM_SIZE(es, (k_subview<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, I(n))));
+    } else {
+        using I = int64_t;
+        VF_BY_ELEM_SIZE(es, (k_subview<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, g, I(n))));
     }
     post_launch(ctx);
 }
@@ -1046,19 +1349,6 @@ void launch_relocate(vf_ctx* ctx, const int32_t* in, int32_t* out, const Relocat
     k_relocate<<<int((a.oc + 127) / 128), 128, 0, ctx->stream>>>(in, out, a, ctx->d_flags);
     post_launch(ctx);
 }
-
-#define VF_BY_ELEM_SIZE(es, CALL)                                                   \
-    switch (es) {                                                                   \
-    case 1: { constexpr int ES = 1; CALL; break; }                                  \
-    case 2: { constexpr int ES = 2; CALL; break; }                                  \
-    case 4: { constexpr int ES = 4; CALL; break; }                                  \
-    case 8: { constexpr int ES = 8; CALL; break; }                                  \
-    case 16: { constexpr int ES = 16; CALL; break; }                                \
-    default: raise(VF_ERR_UNSUPPORTED, "element size %d", es);                      \
-    }
-// I = uint32_t while every index of the launch stays below 2^31, int64_t otherwise
-#define VF_BY_INDEX_WIDTH(n, CALL)                                                  \
-    if ((n) < (int64_t(1) << 31)) { using I = uint32_t; CALL; } else { using I = int64_t; CALL; }
 
 void launch_reverse(vf_ctx* ctx, const void* in, void* out, int64_t n, int64_t run, int es) {
     if (n <= 0) return;
