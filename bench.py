@@ -741,6 +741,8 @@ def next_arm(args):
             orc.fold(hc, htr, hn, hdst, hob)
             cpu = (sb + hob) / (time.perf_counter() - t0) / 1e9
         alg = in_bytes + out_bytes
+        if name.startswith("SubView"):
+            alg = 2 * out_bytes  # only the viewed part of the input has to be read
         rows.append({"kernel": name, "reference": site, "input_bytes": in_bytes, "output_bytes": out_bytes, "ms": ms,
                      "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac": alg / (ms * 1e-3) / 1e9 / peak, "cpu_oracle_gbs": cpu})
         total_bytes += alg

@@ -937,3 +937,36 @@ def test_rank_six_layout_transformations(gpu, oracle):
               ContentSetup(t).reorder(0x213465).subview([0, 1, 0, 0, 1, 2], [2, 2, 2, 4, 2, 3]).reorder(0x123456).reshape([2, 2, 8, 6]),
               ContentSetup(t).reverse(2), ContentSetup(t).broadcast(2, 6).reorder(0x654321)):
         both(ContentAttr(x, t, s), gpu, oracle)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [F32, F16])
+@pytest.mark.parametrize("qmin,qmax,storage", [(0, 255, U8), (-128, 127, I8), (-127, 127, I8), (0, 15, U8), (-120, 120, I8)])
+def test_general_quantize_on_rounding_boundaries(gpu, oracle, dt, qmin, qmax, storage):
+    """Quantize with given parameters (quantize.cpp:108-212): values on and next to the .5 boundaries of every
+    level, where the fast evaluation must hand over to the exact sequence; [-120, 120] is a range whose
+    fakeQuantize tail is not the identity (all elements take the exact sequence)."""
+    rng = np.random.default_rng(qmax * 3 + dt)
+    oc, inner = 24, 512
+    scales = rng.uniform(0.003, 0.9, oc)
+    zps = rng.integers(qmin, qmax + 1, oc) if qmin == 0 else np.zeros(oc, np.int64)
+    levels = qmax - qmin
+    x = np.empty((oc, inner), np.float64)
+    for c in range(oc):
+        lo = (qmin - zps[c]) * scales[c]
+        step = (qmax - qmin) * scales[c] / levels
+        k = rng.integers(-2, levels + 2, inner)
+        x[c] = lo + (k + 0.5) * step
+    x32 = x.astype(np.float32)
+    near = np.stack([np.nextafter(x32, np.float32(np.inf)), x32, np.nextafter(x32, np.float32(-np.inf))], 0)
+    data = np.concatenate([near[i] for i in range(3)], axis=1)  # [oc, 3 * inner]
+    np_dt = np.float32 if dt == F32 else np.float16
+    data = data.astype(np_dt)
+    t = TType([oc, 3 * inner], dt)
+    q = Elem.per_axis(storage, F32, scales.tolist(), [int(z) for z in zps], 0, qmin, qmax)
+    both(ContentAttr(data, t, ContentSetup(t).quantize(q)), gpu, oracle)
+    qt = Elem.uniform(storage, F32, float(scales[0]), int(zps[0]), qmin, qmax)
+    both(ContentAttr(data, t, ContentSetup(t).quantize(qt)), gpu, oracle)
+    special = data.copy()
+    special[0, :8] = [np.inf, -np.inf, 1e30 if dt == F32 else 6e4, -1e30 if dt == F32 else -6e4, 0.0, -0.0, 1e-30 if dt == F32 else 6e-8, 3.0]
+    both(ContentAttr(special, t, ContentSetup(t).quantize(q)), gpu, oracle)

@@ -111,6 +111,10 @@ void check_positions(const vf_transform* t, int n);
 int64_t swizzle_size_alignment(int arch);  // bytes a swizzled buffer's size is aligned to
 Type compress_type(const Type& in, const int64_t* counts, int64_t n);
 
+// Whether the tail of fakeQuantize (/(L-1) * (qHigh-qLow) + qLow, truncate) maps every index n to n + qmin for
+// this storage range, evaluated with the reference's fp32 operations (fold_fused.cu).
+bool tail_is_identity(int64_t qmin, int64_t qmax);
+
 // calcScaleAndZeroPoint on the host (used for validation of tiny inputs and by tests of the planner)
 bool calc_scale_zp_host(double qmin, double qmax, double rmin, double rmax, double& scale, int64_t& zp);
 

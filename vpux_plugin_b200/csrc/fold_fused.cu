@@ -16,6 +16,8 @@ namespace {
 // for every range (e.g. -120..120), so it is evaluated here with the same fp32 operations.
 bool tail_is_identity_uncached(int64_t qmin, int64_t qmax);
 
+}  // namespace
+
 bool tail_is_identity(int64_t qmin, int64_t qmax) {  // a batch asks the same question for every job
     static thread_local int64_t last_min = 1, last_max = 0;
     static thread_local bool last = false;
@@ -26,6 +28,8 @@ bool tail_is_identity(int64_t qmin, int64_t qmax) {  // a batch asks the same qu
     }
     return last;
 }
+
+namespace {
 
 bool tail_is_identity_uncached(int64_t qmin, int64_t qmax) {
     const volatile float lm1 = float(qmax - qmin + 1) - 1.0f;

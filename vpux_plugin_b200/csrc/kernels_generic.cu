@@ -108,13 +108,23 @@ __device__ __forceinline__ void store8(void* __restrict__ out, int64_t g, const 
     }
 }
 
-template <int IN, typename I>
+// FAST: the element is first quantized as round(fma(x, inv, c)) with inv = fl((L-1)/range), c = fl(-inLow*inv);
+// it differs from the reference's individually rounded sequence by less than 4.2e-7 * L, so only elements whose
+// rounding residual comes within 8e-7 * L of a half are recomputed with the exact sequence. The host enables it
+// when the tail of fakeQuantize is the identity on the indices of this storage range (tail_is_identity).
+template <int IN, typename I, bool FAST>
 __global__ void k_quantize8(const void* __restrict__ in, uint8_t* __restrict__ out, I n_groups, const double* __restrict__ scales,
                             const int64_t* __restrict__ zps, I axis_size, I inner8, long long qmin, long long qmax, int* flags) {
     const I stride = I(gridDim.x) * I(blockDim.x);
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    constexpr int kMagicBits = 0x4B400000;
     for (I g = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); g < n_groups; g += stride) {
         const I a = axis_size > 1 ? (g / inner8) % axis_size : I(0);
         const QuantParams qp = make_quant_params(scales[a], zps[a], qmin, qmax);
+        const float inv = __fdiv_rn(qp.levels_m1, qp.range);
+        const float c = __fmul_rn(-qp.in_low, inv);
+        const float thr = 0.5f - 8.0e-7f * (qp.levels_m1 + 1.0f);
+        const int lm1 = int(qmax - qmin);
         __align__(16) uint8_t ib[Bytes8<IN>::value];
         __align__(8) uint8_t ob[8];
         load8<IN>(in, int64_t(g), ib);
@@ -122,7 +132,21 @@ __global__ void k_quantize8(const void* __restrict__ in, uint8_t* __restrict__ o
         for (int k = 0; k < 8; ++k) {
             const float x = load_as_f32(ib, IN, k, flags);
             if (x != x) set_flag(flags, VF_FLAG_NAN);
-            ob[k] = uint8_t(quantize_exact(x, qp));
+            if (FAST) {
+                const float t = __fmaf_rn(x, inv, c);
+                const float m = __fadd_rn(t, kMagic);
+                const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
+                int code;
+                if (fabsf(resid) <= thr) {  // false for NaN as well
+                    const int n = __float_as_int(m) - kMagicBits;
+                    code = min(max(n, 0), lm1) + int(qmin);
+                } else {
+                    code = int(quantize_exact(x, qp));
+                }
+                ob[k] = uint8_t(code);
+            } else {
+                ob[k] = uint8_t(quantize_exact(x, qp));
+            }
         }
         store8<8>(out, int64_t(g), ob);
     }
@@ -377,15 +401,16 @@ __global__ void k_permute(const void* __restrict__ in, void* __restrict__ out, G
     }
 }
 
-// The same permutation through a 32 x 32 shared-memory tile, for geometries whose innermost output dim is not
+// The same permutation through a 64 x 64 shared-memory tile, for geometries whose innermost output dim is not
 // the innermost input dim: dim `a` (innermost on the output side) and dim `b` (the one with source stride 1)
 // span the tile, so that the loads run along b and the stores along a, both coalesced. One CTA of 32 x 8 threads
 // per tile; blockIdx.x enumerates (other dims, tiles along a, tiles along b).
+constexpr int kTile = 64;
 template <int ES, typename I>
-__global__ void k_permute_tiled(const void* __restrict__ in, void* __restrict__ out, Geom g, int b, I tiles_a, I tiles_b,
-                                I dst_stride_b) {
+__global__ void __launch_bounds__(256) k_permute_tiled(const void* __restrict__ in, void* __restrict__ out, Geom g, int b, I tiles_a,
+                                                       I tiles_b, I dst_stride_b) {
     using T = typename ElemOf<ES>::T;
-    __shared__ T tile[32][33];
+    __shared__ T tile[kTile][kTile + 1];
     const int a = g.rank - 1;
     I rem = I(blockIdx.x);
     const I tb = rem % tiles_b;
@@ -408,18 +433,26 @@ __global__ void k_permute_tiled(const void* __restrict__ in, void* __restrict__ 
         }
     }
     const I ea = I(g.out_shape[a]), eb = I(g.out_shape[b]);
-    const I a0 = ta * 32, b0 = tb * 32;
+    const I a0 = ta * kTile, b0 = tb * kTile;
     const I sa = I(g.src_stride[a]);
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {  // rows of the tile run along a, columns along b (source stride 1)
-        const I ia = a0 + threadIdx.y + i, ib = b0 + threadIdx.x;
-        if (ia < ea && ib < eb) tile[threadIdx.y + i][threadIdx.x] = static_cast<const T*>(in)[src0 + ia * sa + ib];
+    for (int i = 0; i < kTile; i += 8) {  // rows of the tile run along a, columns along b (source stride 1)
+        const I ia = a0 + threadIdx.y + i;
+#pragma unroll
+        for (int c = 0; c < kTile; c += 32) {
+            const I ib = b0 + threadIdx.x + c;
+            if (ia < ea && ib < eb) tile[threadIdx.y + i][threadIdx.x + c] = static_cast<const T*>(in)[src0 + ia * sa + ib];
+        }
     }
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {  // stores: rows along b, columns along a (destination stride 1)
-        const I ib = b0 + threadIdx.y + i, ia = a0 + threadIdx.x;
-        if (ia < ea && ib < eb) static_cast<T*>(out)[dst0 + ib * dst_stride_b + ia] = tile[threadIdx.x][threadIdx.y + i];
+    for (int i = 0; i < kTile; i += 8) {  // stores: rows along b, columns along a (destination stride 1)
+        const I ib = b0 + threadIdx.y + i;
+#pragma unroll
+        for (int c = 0; c < kTile; c += 32) {
+            const I ia = a0 + threadIdx.x + c;
+            if (ia < ea && ib < eb) static_cast<T*>(out)[dst0 + ib * dst_stride_b + ia] = tile[threadIdx.x + c][threadIdx.y + i];
+        }
     }
 }
 
@@ -969,9 +1002,15 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
         const int64_t groups = n / 8, inner8 = axis_size > 1 ? inner / 8 : 1;
         const int grid = grid_for(groups);
         uint8_t* o = static_cast<uint8_t*>(out);
-#define VF_Q8(IN)                                                                                                             \
-    VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps, I(axis_size), \
-                                                                                    I(inner8), qmin, qmax, ctx->d_flags)))
+        const bool fast = qmax - qmin <= 255 && qmax > qmin && tail_is_identity(qmin, qmax);
+#define VF_Q8(IN)                                                                                                                       \
+    if (fast) {                                                                                                                         \
+        VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I, true><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps,        \
+                                                                                              I(axis_size), I(inner8), qmin, qmax, ctx->d_flags))); \
+    } else {                                                                                                                            \
+        VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I, false><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps,       \
+                                                                                               I(axis_size), I(inner8), qmin, qmax, ctx->d_flags))); \
+    }
         if (in_dt == VF_DT_F32) { VF_Q8(VF_DT_F32); }
         else if (in_dt == VF_DT_F16) { VF_Q8(VF_DT_F16); }
         else { VF_Q8(VF_DT_BF16); }
@@ -1174,7 +1213,7 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
     for (int d = 0; d < a; ++d)
         if (g.src_stride[d] == 1 && g.out_shape[d] >= 8) b = d;
     if (small && es <= 8 && b >= 0 && g.src_stride[a] != 1 && g.out_shape[a] >= 8) {
-        const int64_t ta = (g.out_shape[a] + 31) / 32, tb = (g.out_shape[b] + 31) / 32;
+        const int64_t ta = (g.out_shape[a] + kTile - 1) / kTile, tb = (g.out_shape[b] + kTile - 1) / kTile;
         int64_t others = 1, dst_stride_b = 1;
         for (int d = 0; d < g.rank; ++d)
             if (d != a && d != b) others *= g.out_shape[d];
