@@ -679,7 +679,7 @@ def next_arm(args):
         ("PadWithZero IC 48->64 f16", "pad_with_zero.cpp:111-268", TT([oc, 48, 3, n8 // 2 // oc // 48 // 3], F16), F16,
          lambda s: s.padWithZero([0, 0, 0, 0], [0, 16, 0, 0])),
         ("SubView half the channels f16", "subview.cpp:390-432", TT([oc, n8 // 2 // oc], F16), F16,
-         lambda s: s.subview([oc // 4, 0], [oc // 2, n8 // 2 // oc])),
+         lambda s: s.subview([s.base_type.shape[0] // 4, 0], [s.base_type.shape[0] // 2, s.base_type.shape[1]])),
         ("BitPack<4> u8", "bit_pack.cpp:132-154", TT([n8], U8), U8, lambda s: s.bitPack(4)),
     ]
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -729,8 +729,13 @@ def next_arm(args):
             take = max(1, min(rows_all, int(rows_all * (8 << 20) / max(in_bytes, 1))))
             if name.startswith("Relocate"):
                 take = rows_all  # the table is its own sample (the transformation's size is in its parameters)
-            ts = TT([take] + list(t.shape[1:]), t.elem.dtype, t.order) if take != rows_all else t
-            sb = in_bytes * take // rows_all
+            if "per-axis" in name:  # the parameters are per row: keep the rows, shorten them
+                last = max(8, t.shape[-1] * take // rows_all // 8 * 8)
+                ts = TT(list(t.shape[:-1]) + [last], t.elem.dtype, t.order)
+                sb = in_bytes // t.shape[-1] * last
+            else:
+                ts = TT([take] + list(t.shape[1:]), t.elem.dtype, t.order) if take != rows_all else t
+                sb = in_bytes * take // rows_all
             host = src[:sb].cpu().numpy()
             hs = build(ContentSetup(ts))
             htr, hn = hs.transforms()
