@@ -970,3 +970,35 @@ def test_general_quantize_on_rounding_boundaries(gpu, oracle, dt, qmin, qmax, st
     special = data.copy()
     special[0, :8] = [np.inf, -np.inf, 1e30 if dt == F32 else 6e4, -1e30 if dt == F32 else -6e4, 0.0, -0.0, 1e-30 if dt == F32 else 6e-8, 3.0]
     both(ContentAttr(special, t, ContentSetup(t).quantize(q)), gpu, oracle)
+
+
+@pytest.mark.gpu
+def test_layout_kernels_beyond_two_to_the_31_elements(gpu):
+    """More than 2^31 elements switch the layout kernels to 64-bit index arithmetic: a transpose applied twice and a
+    pad followed by the view of the original region both give the input back (checked on the device)."""
+    import torch
+    rows, cols = 65544, 32768  # 2.15e9 u8 elements
+    x = torch.randint(0, 256, (rows, cols), dtype=torch.uint8, device="cuda")
+    n = rows * cols
+    t = TType([rows, cols], U8)
+
+    def run(ttype, src, setup, out_elems):
+        c, keep = abi.make_content(ttype, None, U8, False, abi.VF_MEM_DEVICE, ptr=src.data_ptr(), nbytes=src.numel())
+        dst = torch.empty(out_elems, dtype=torch.uint8, device="cuda")
+        tr, k = setup.transforms()
+        written, ftype = gpu.fold(c, tr, k, dst.data_ptr(), out_elems, dst_mem_kind=abi.VF_MEM_DEVICE)
+        assert written == out_elems
+        return dst, ftype
+
+    y, ty = run(t, x, ContentSetup(t).transpose(0x21), n)
+    assert ty.shape == [cols, rows]
+    assert torch.equal(y.view(cols, rows)[:7, :9], x[:9, :7].t())
+    z, tz = run(ty, y, ContentSetup(ty).transpose(0x21), n)
+    assert torch.equal(z.view(rows, cols), x)
+    del y, z
+    p, tp = run(t, x, ContentSetup(t).padWithZero([3, 0], [0, 5]), (rows + 3) * (cols + 5))
+    assert tp.shape == [rows + 3, cols + 5]
+    pv = p.view(rows + 3, cols + 5)
+    assert int(pv[:3].max()) == 0 and int(pv[:, cols:].max()) == 0
+    v, tv = run(tp, p, ContentSetup(tp).subview([3, 0], [rows, cols]), n)
+    assert torch.equal(v.view(rows, cols), x)
