@@ -1212,7 +1212,7 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
     const int a = g.rank - 1;
     for (int d = 0; d < a; ++d)
         if (g.src_stride[d] == 1 && g.out_shape[d] >= 8) b = d;
-    if (small && es <= 8 && b >= 0 && g.src_stride[a] != 1 && g.out_shape[a] >= 8) {
+    if (es <= 8 && b >= 0 && g.src_stride[a] != 1 && g.out_shape[a] >= 8) {
         const int64_t ta = (g.out_shape[a] + kTile - 1) / kTile, tb = (g.out_shape[b] + kTile - 1) / kTile;
         int64_t others = 1, dst_stride_b = 1;
         for (int d = 0; d < g.rank; ++d)
@@ -1221,8 +1221,13 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
         const int64_t blocks = others * ta * tb;
         if (blocks < (int64_t(1) << 31)) {
             const dim3 block(32, 8);
-            using I = uint32_t;
-            VF_BY_ELEM_SIZE(es, (k_permute_tiled<(ES > 8 ? 8 : ES), I><<<unsigned(blocks), block, 0, ctx->stream>>>(in, out, g, b, I(ta), I(tb), I(dst_stride_b))));
+            if (small) {
+                using I = uint32_t;
+                VF_BY_ELEM_SIZE(es, (k_permute_tiled<(ES > 8 ? 8 : ES), I><<<unsigned(blocks), block, 0, ctx->stream>>>(in, out, g, b, I(ta), I(tb), I(dst_stride_b))));
+            } else {
+                using I = int64_t;
+                VF_BY_ELEM_SIZE(es, (k_permute_tiled<(ES > 8 ? 8 : ES), I><<<unsigned(blocks), block, 0, ctx->stream>>>(in, out, g, b, I(ta), I(tb), I(dst_stride_b))));
+            }
             post_launch(ctx);
             return;
         }
