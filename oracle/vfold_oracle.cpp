@@ -1278,7 +1278,6 @@ Content tf_subview(Content& in, const vf_transform& t, int nthreads) {
     }
     Content out = Content::alloc(outType, in.storage, false);
     const int es = dtype_bits(in.storage) / 8;
-    if (es < 1) fail(VF_ERR_UNSUPPORTED, "sub-byte subview");
     const int rank = in.type.rank;
     int perm[VF_MAX_RANK];
     int64_t ims[VF_MAX_RANK], oms[VF_MAX_RANK], ist[VF_MAX_RANK], moff[VF_MAX_RANK];
@@ -1288,6 +1287,22 @@ Content tf_subview(Content& in, const vf_transform& t, int nthreads) {
     strides_of(ims, rank, ist);
     for (int i = 0; i < rank; ++i) moff[i] = t.a[perm[i]];
     const int64_t n = outType.numel();
+    if (es < 1) {  // subByteTransform — subview.cpp:20-160: bit fields, low bits first, into a zeroed buffer
+        const int storageElemTypeSize = dtype_bits(in.storage);
+        const int64_t elemPerByte = 8 / storageElemTypeSize;
+        const unsigned mask = (1u << storageElemTypeSize) - 1u;
+        std::memset(out.mdata(), 0, out.nbytes);
+        for (int64_t outMemInd1D = 0; outMemInd1D < n; ++outMemInd1D) {
+            int64_t rem = outMemInd1D, inMemInd1D = 0;
+            for (int d = rank - 1; d >= 0; --d) {
+                inMemInd1D += (rem % oms[d] + moff[d]) * ist[d];
+                rem /= oms[d];
+            }
+            const unsigned subByteValue = (unsigned(in.data()[inMemInd1D / elemPerByte]) >> ((inMemInd1D % elemPerByte) * storageElemTypeSize)) & mask;
+            out.mdata()[outMemInd1D / elemPerByte] |= uint8_t(subByteValue << ((outMemInd1D % elemPerByte) * storageElemTypeSize));
+        }
+        return out;
+    }
     parallel_nd(nthreads, {n}, [&](const int64_t* b, const int64_t* e) {
         for (int64_t lin = b[0]; lin < e[0]; ++lin) {
             int64_t rem = lin, s = 0;

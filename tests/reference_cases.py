@@ -513,6 +513,131 @@ def broadcast(be):
     assert np.array_equal(out.values(np.uint8).reshape(2, 6, 2), np.concatenate([x, x], axis=1))
 
 
+def subview_sub_byte(be):
+    """lit dialect/const/passes/constant_folding.mlir:56-314 (I1Subview*, I4Subview*): SubView on 1- and 4-bit
+    storage gathers bit fields, low bits first (subview.cpp:20-160)."""
+    I1, I4 = abi.VF_DT_I1, abi.VF_DT_I4
+
+    def bits(vals):  # 1-bit values -> packed bytes, element 0 in bit 0
+        return np.packbits(np.asarray(vals, np.uint8), bitorder="little")
+
+    def run(raw, shape, dt, off, shp, convert=None, splat=False):
+        t = TType(shape, dt)
+        s = ContentSetup(t).subview(off, shp)
+        if convert is not None:
+            s = s.convertElemType(convert)
+        out = ContentAttr(np.asarray(raw, np.uint8), t, s, is_splat=splat, storage_dtype=dt).fold(be)
+        return out
+
+    def unbits(out, n):
+        return np.unpackbits(out.bytes(), bitorder="little")[:n].tolist()
+
+    o = run([0xFF], [1, 32, 3, 3], I1, [0, 16, 0, 0], [1, 16, 3, 3], splat=True)               # :56-67 splat stays true
+    assert o.is_splat and set(unbits(o, 144)) == {1}
+    assert unbits(run(bits([1, 0, 0, 1, 1, 1, 0, 1, 1, 0]), [10], I1, [3], [4]), 4) == [1, 1, 1, 0]   # :72-85
+    assert unbits(run(bits([1, 0, 1, 0]), [1, 4], I1, [0, 2], [1, 2]), 2) == [1, 0]                     # :90-102
+    d3 = [0, 0, 1, 1, 0, 1, 1, 1, 1, 0, 0, 1, 1, 1, 0, 1, 0, 0, 0, 1, 0, 1, 1, 1, 0, 1, 0, 1, 1, 0, 1, 0]
+    assert unbits(run(bits(d3), [1, 4, 8], I1, [0, 2, 4], [1, 2, 4]), 8) == [0, 1, 1, 1, 1, 0, 1, 0]  # :107-122
+    d4 = [0] * 8 + [1] * 8 + [0, 1] * 4 + [1, 0] * 4
+    assert unbits(run(bits(d4), [1, 32, 1, 1], I1, [0, 16, 0, 0], [1, 16, 1, 1]), 16) == [0, 1] * 4 + [1, 0] * 4  # :127-145
+    d5 = [0, 1, 1, 0, 1, 1, 0, 0, 1, 0, 1, 0, 1, 1, 1, 0, 0, 0, 1, 1, 0, 1, 0, 1]
+    assert unbits(run(bits(d5), [1, 2, 3, 4, 1], I1, [0, 1, 1, 1, 0], [1, 1, 2, 3, 1]), 6) == [0, 1, 1, 1, 0, 1]  # :150-163
+    I8 = abi.VF_DT_I8
+    assert run([0x22, 0x22], [4], I4, [2], [2], I8).values(np.int8).tolist() == [2, 2]                 # :168-188 blob 2222
+    assert run([0x21, 0x43], [4], I4, [2], [2], I8).values(np.int8).tolist() == [3, 4]                 # :192-212
+    b8 = [0x10, 0x32, 0x54, 0x76]
+    assert run(b8, [2, 4], I4, [1, 2], [1, 2], I8).values(np.int8).tolist() == [6, 7]                  # :216-237
+    assert run(b8, [2, 4, 1], I4, [1, 2, 0], [1, 2, 1], I8).values(np.int8).tolist() == [6, 7]         # :241-262
+    b16 = b8 + [0x67, 0x45, 0x23, 0x01]
+    assert run(b16, [2, 4, 2, 1], I4, [1, 2, 1, 0], [1, 2, 1, 1], I8).values(np.int8).tolist() == [2, 0]        # :266-287
+    assert run(b16, [2, 4, 2, 1, 1], I4, [1, 2, 1, 0, 0], [1, 2, 1, 1, 1], I8).values(np.int8).tolist() == [2, 0]  # :291-312
+
+
+def broadcast_non_splat(be):
+    """lit dialect/const/passes/constant_folding.mlir:316-417 (broadcastNonSplat*): the block from the broadcast
+    dim inwards is repeated."""
+    def run(vals, dt, setup_fn):
+        vals = np.asarray(vals)
+        t = TType(list(vals.shape), dt)
+        return ContentAttr(vals, t, setup_fn(ContentSetup(t))).fold(be)
+
+    i8 = lambda v: np.asarray(v, np.int8)
+    o = run(i8([1, 2, 3]), I8, lambda s: s.reshape([1, 3, 1, 1]).broadcast(0, 3).reshape([1, 9, 1, 1]))          # :316-326
+    assert o.values(np.int8).tolist() == [1, 2, 3] * 3
+    o = run(i8([1, 2, 3]), I8, lambda s: s.reshape([1, 3, 1, 1]).broadcast(2, 3).reshape([1, 9, 1, 1]))          # :330-340
+    assert o.values(np.int8).tolist() == [1, 1, 1, 2, 2, 2, 3, 3, 3]
+    o = run(i8([1, 2, 3, 4, 5, 6]), I8, lambda s: s.reshape([1, 3, 1, 2]).broadcast(2, 2))                       # :344-356
+    assert o.type.shape == [1, 3, 2, 2] and o.values(np.int8).tolist() == [1, 2, 1, 2, 3, 4, 3, 4, 5, 6, 5, 6]
+    o = run(i8(range(1, 13)), I8, lambda s: s.reshape([1, 3, 2, 2]).broadcast(2, 4))                             # :360-371
+    assert o.values(np.int8).tolist() == [1, 2, 3, 4, 1, 2, 3, 4, 5, 6, 7, 8, 5, 6, 7, 8, 9, 10, 11, 12, 9, 10, 11, 12]
+    h = np.asarray([[[[1, 2, 3, 4]]]], np.float16)
+    o = run(h, F16, lambda s: s.castElemType(F16).reshape([1, 1, 1, 4]).broadcast(1, 4).broadcast(2, 4))         # :375-392
+    assert o.type.shape == [1, 4, 4, 4] and o.values(np.float16).tolist() == [1.0, 2.0, 3.0, 4.0] * 16
+    h = np.asarray([[[[1], [2], [3], [4]]]], np.float16)
+    o = run(h, F16, lambda s: s.castElemType(F16).reshape([1, 1, 4, 1]).broadcast(1, 4).broadcast(3, 4))         # :396-413
+    assert o.values(np.float16).tolist() == [v for _ in range(4) for v in (1.0, 2.0, 3.0, 4.0) for _ in range(4)]
+
+
+def const_fold_i4(be):
+    """lit dialect/const/passes/constant_folding.mlir:416-428 ConstFoldI4: f16 [1,0,1,2] cast to a quantized si4 type and
+    reordered folds to the packed bytes [1, 33] (element 0 in the low nibble)."""
+    t = TType([1, 4, 1, 1], F16)
+    q = Elem.uniform(abi.VF_DT_I4, F16, 0.0039215686274509803, 0, -8, 7)
+    s = ContentSetup(t).castElemType(abi.VF_DT_I4).castElemType(q).reorder(0x3412)
+    out = ContentAttr(np.array([1, 0, 1, 2], np.float16).reshape(1, 4, 1, 1), t, s).fold(be)
+    assert out.type.shape == [1, 4, 1, 1] and out.type.order == 0x3412
+    assert out.bytes().tolist() == [1, 33]
+
+
+def dequantize_per_axis_splat(be):
+    """lit dialect/const/passes/constant_folding.mlir:466-563 ConstFoldDequantizeAxis0..4: a splat 1.0 cast to a per-axis
+    u8 type dequantizes to (1 - zp[c]) * scale[c] along the quantized axis."""
+    sc = [1.0, 0.5, 0.25, 0.125, 0.1, 0.2, 0.4, 0.8]
+    zp = [128, 64, 32, 16, 128, 128, 128, 128]
+    want = [-127.0, -31.5, -7.75, -1.875, -12.7031, -25.4063, -50.8125, -101.625]   # as printed at :539
+    for shape, axis in (([1, 2, 4, 8], 0), ([1, 2, 4, 8], 1), ([1, 2, 4, 8], 2), ([1, 2, 4, 8], 3), ([2, 2, 2, 2, 2], 4)):
+        n = shape[axis]
+        t = TType(shape, F16)
+        q = Elem.per_axis(U8, F16, sc[:n], zp[:n], axis, 0, 255)
+        s = ContentSetup(t).castElemType(U8).castElemType(q).dequantize()
+        out = ContentAttr(np.array([1.0], np.float16), t, s, is_splat=True).fold(be)
+        assert out.type == TType(shape, F16)
+        got = out.values(np.float16).reshape(shape).astype(np.float64)
+        idx = np.arange(n).reshape([n if d == axis else 1 for d in range(len(shape))])
+        exp = np.broadcast_to(np.asarray(want[:n])[idx], shape)
+        assert np.abs(got - exp).max() <= 1e-4 * 128, (axis, got.ravel()[:8])           # 6 printed digits
+        exact = np.asarray([np.float16(np.float32((1 - z) * s_)) for s_, z in zip(sc[:n], zp[:n])], np.float64)
+        assert (got == np.broadcast_to(exact[idx], shape)).all()
+
+
+def fold_with_swizzling(be):
+    """lit dialect/const/passes/constant_folding.mlir:849-910 ConstFoldWithSwizzling*: SwizzleConstant works on the
+    content its predecessors produced (not the raw storage), 1-bit constants keep their type, and the result has
+    the aligned size whatever the shape before it."""
+    arch = abi.VF_ARCH_NPU37XX
+    t = TType([100, 1, 1, 384], abi.VF_DT_I1)                                           # :849-851
+    out = ContentAttr(np.array([0xFF], np.uint8), t, ContentSetup(t).swizzleConstant(5, arch), is_splat=True,
+                      storage_dtype=abi.VF_DT_I1).fold(be)
+    assert out.type == TType([40960, 1, 1, 1], abi.VF_DT_I1) and out.written == 5120
+    assert (out.bytes()[:4800] == 0xFF).all()                                           # dense<true> of the check line
+    t = TType([32, 1, 1, 1], F16)                                                       # :881-897
+    q = Elem.uniform(U8, F16, 1.0, 0, 0, 254)
+    s = (ContentSetup(t).castElemType(U8).castElemType(q).reorder(0x1342).reorder(0x1234).reshape([32, 1, 1, 1])
+         .padWithZero([0, 0, 0, 0], [0, 15, 0, 0]).reorder(0x1342).subview([0, 0, 0, 0], [16, 16, 1, 1])
+         .swizzleConstant(5, arch))
+    out = ContentAttr(np.array([1.0], np.float16), t, s, is_splat=True).fold(be)
+    assert out.type.shape == [512, 1, 1, 1] and out.written == 512
+    assert out.bytes()[:16].tolist() == [1] + [0] * 15                                  # prefix of the check line
+    b = out.bytes()
+    assert int(b.sum()) == 16 and sorted(set(np.flatnonzero(b) % 16)) == [0]
+    t = TType([1, 1, 3, 1], U8)                                                         # :902-908
+    s = ContentSetup(t).reshape([3, 1, 1, 1]).broadcast(0, 768).swizzleConstant(5, arch)
+    out = ContentAttr(np.array([1, 2, 3], np.uint8).reshape(1, 1, 3, 1), t, s).fold(be)
+    assert out.type == TType([1024, 1, 1, 1], U8) and out.written == 1024      # content shape != the op's 768
+    b = out.bytes()
+    assert b[:16].tolist() == ([1, 2, 3] * 6)[:16] and np.bincount(b, minlength=4).tolist() == [256, 256, 256, 256]
+
+
 def sparsity_ptr_stepping(be):
     """lit dialect/VPU/passes/recompute_sparsity_ptrs.mlir:12-31: a 16x16x4x4 filter has sparsity-map rows of
     align(256, 128) / 8 = 32 bytes (map type 16x1x1x256xi1), so the sparsity pointers step by 32"""
@@ -531,5 +656,6 @@ FOLD_CASES = [quantize, per_axis_quantize, dequantize_quantize, quant_cast, dequ
               get_sparsity_map_quantized, sparsify, sparsify_true, sparsify_quantized, position_requirement,
               convert_elem_type_i8_u8, convert_elem_type_u4_i4, quantize_splat, const_fold_chain, copy_to_i4,
               copy_to_i1, convert_elem_type_sub_byte, swizzle_constant, relocate_weights_table, reverse, expand_dilated,
-              scalar_mult_inverse, change_shape_and_elem_type, broadcast]
+              scalar_mult_inverse, change_shape_and_elem_type, broadcast, subview_sub_byte, broadcast_non_splat,
+              const_fold_i4, dequantize_per_axis_splat, fold_with_swizzling]
 TABLE_CASES = [weights_table_fixed_point, weights_table_float_scale, sparsity_ptr_stepping]

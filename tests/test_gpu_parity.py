@@ -926,6 +926,38 @@ def test_fold_into_device_memory_matches_fold_into_host_memory(gpu):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dt", [abi.VF_DT_I1, abi.VF_DT_U4, abi.VF_DT_I4])
+@pytest.mark.parametrize("shape,off,sub", [
+    ([1001], [37], [555]),
+    ([7, 13, 5, 3], [1, 2, 0, 1], [5, 9, 5, 2]),
+    ([3, 64, 9, 32], [1, 16, 2, 8], [2, 32, 5, 16]),
+    ([2, 3, 4, 5, 6], [0, 1, 1, 2, 3], [2, 2, 2, 3, 3]),
+    ([64, 4096], [3, 1024], [40, 2047]),
+])
+def test_subview_of_sub_byte_storage(gpu, oracle, dt, shape, off, sub):
+    """subview.cpp:20-160 (subByteTransform): bit fields gathered into a freshly packed buffer; the oracle walks
+    element by element, the kernel packs one output byte per thread."""
+    bits = 1 if dt == abi.VF_DT_I1 else 4
+    n = int(np.prod(shape))
+    rng = np.random.default_rng(n + bits)
+    raw = rng.integers(0, 256, (n * bits + 7) // 8, dtype=np.uint8)
+    t = TType(shape, dt)
+    attr = ContentAttr(raw, t, ContentSetup(t).subview(off, sub), storage_dtype=dt)
+    out = both(attr, gpu, oracle)
+    assert out.type.shape == sub and out.written == (int(np.prod(sub)) * bits + 7) // 8
+    # independent check against numpy on the unpacked values
+    per = 8 // bits
+    vals = ((raw[:, None] >> (np.arange(per) * bits)) & ((1 << bits) - 1)).reshape(-1)[:n].reshape(shape)
+    want = vals[tuple(slice(o, o + s) for o, s in zip(off, sub))].reshape(-1)
+    got = ((out.bytes()[:, None] >> (np.arange(per) * bits)) & ((1 << bits) - 1)).reshape(-1)[:want.size]
+    assert np.array_equal(got, want)
+    # followed by a conversion to bytes (the shape the reference's lit cases have)
+    conv = ContentAttr(raw, t, ContentSetup(t).subview(off, sub).convertElemType(U8 if dt == abi.VF_DT_U4 else I8),
+                       storage_dtype=dt)
+    both(conv, gpu, oracle)
+
+
+@pytest.mark.gpu
 def test_rank_six_layout_transformations(gpu, oracle):
     rng = np.random.default_rng(66)
     shape = [2, 3, 2, 4, 3, 5]

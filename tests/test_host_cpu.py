@@ -202,4 +202,4 @@ def test_two_rank_sharding_reassembles_bit_identically():
 
 
 def test_reference_case_list_is_complete():
-    assert len(rc.FOLD_CASES) == 32 and len(rc.TABLE_CASES) == 3
+    assert len(rc.FOLD_CASES) == 37 and len(rc.TABLE_CASES) == 3

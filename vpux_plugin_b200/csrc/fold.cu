@@ -374,7 +374,6 @@ DContent do_subview(vf_ctx* ctx, DContent& in, const vf_transform& t) {
     const Type ot = infer_one(in.type, in.splat, t, os);
     if (in.splat) return move_buffer(in, ot);
     const int bits = dtype_bits(in.storage);
-    if (bits < 8) raise(VF_ERR_UNSUPPORTED, "SubView of sub-byte storage");
     DContent out = alloc_like(ctx, ot, in.storage, false);
     const int rank = in.type.rank;
     int p[VF_MAX_RANK];
@@ -391,7 +390,8 @@ DContent do_subview(vf_ctx* ctx, DContent& in, const vf_transform& t) {
         g.src_stride[i] = ist[i];
         g.offset[i] = t.a[p[i]];
     }
-    launch_subview(ctx, in.d, out.own.p, g, bits / 8);
+    if (bits < 8) launch_subview_subbyte(ctx, in.d, out.own.p, g, bits);  // subByteTransform, subview.cpp:20-160
+    else launch_subview(ctx, in.d, out.own.p, g, bits / 8);
     return out;
 }
 

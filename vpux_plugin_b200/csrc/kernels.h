@@ -46,6 +46,8 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g, int e
 void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geom& g, int es, const void* d_fill,
                 int64_t n_fill, int fill_dim);
 void launch_subview(vf_ctx* ctx, const void* in, void* out, const Geom& g, int es);
+// the same on 1- / 2- / 4-bit storage (bit fields, low bits first)
+void launch_subview_subbyte(vf_ctx* ctx, const void* in, void* out, const Geom& g, int bits);
 
 // ---- sparsity --------------------------------------------------------------------------------------
 // Per output channel: non-sparse count and (optionally) the sparsity bitmap row.

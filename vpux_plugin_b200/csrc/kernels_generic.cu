@@ -456,6 +456,35 @@ __global__ void __launch_bounds__(256) k_permute_tiled(const void* __restrict__ 
     }
 }
 
+// SubView of 1- / 2- / 4-bit storage — subByteTransform, attributes/subview.cpp:20-160: elements are gathered bit
+// field by bit field, low bits first. One thread per output byte (its 8 / BITS elements), so no two threads
+// touch the same byte.
+__global__ void k_subview_subbyte(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, int64_t n_elems, int bits) {
+    const int per = 8 / bits;
+    const unsigned mask = (1u << bits) - 1u;
+    const int64_t n_bytes = (n_elems + per - 1) / per;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t ob = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; ob < n_bytes; ob += stride) {
+        unsigned byte = 0;
+        for (int k = 0; k < per; ++k) {
+            const int64_t o = ob * per + k;
+            if (o >= n_elems) break;
+            int64_t rem = o, src = 0;
+#pragma unroll
+            for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+                if (d < g.rank) {
+                    const int64_t c = rem % g.out_shape[d];
+                    rem /= g.out_shape[d];
+                    src += (c + g.offset[d]) * g.src_stride[d];
+                }
+            }
+            const unsigned v = (unsigned(in[src / per]) >> (unsigned(src % per) * bits)) & mask;
+            byte |= v << (k * bits);
+        }
+        out[ob] = uint8_t(byte);
+    }
+}
+
 template <int ES>
 __device__ __forceinline__ typename ElemOf<ES>::T wide_fill(const uint8_t* __restrict__ fill, int fill_es) {
     // the fill element (fill_es bytes) repeated over the ES bytes of a regrouped element
@@ -1261,6 +1290,14 @@ void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geo
         using I = int64_t;
         VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, I(n), fill, es0, I(n_fill), fd)));
     }
+    post_launch(ctx);
+}
+
+void launch_subview_subbyte(vf_ctx* ctx, const void* in, void* out, const Geom& g, int bits) {
+    const int64_t n = out_numel(g);
+    if (n <= 0) return;
+    const int64_t n_bytes = (n * bits + 7) / 8;
+    k_subview_subbyte<<<grid_for(n_bytes), kBlock, 0, ctx->stream>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, n, bits);
     post_launch(ctx);
 }
 
