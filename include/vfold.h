@@ -60,7 +60,8 @@ typedef enum vf_status {
     VF_ERR_CUDA = -20,            /* a CUDA runtime call failed; message carries cudaGetErrorString    */
     VF_ERR_NO_DEVICE = -21,       /* no usable CUDA device                                             */
     VF_ERR_OOM = -22,             /* device or pinned allocation failed                                */
-    VF_ERR_CAPACITY = -23         /* fixed-capacity entry point: request exceeds the built-in maximum  */
+    VF_ERR_CAPACITY = -23,        /* fixed-capacity entry point: request exceeds the built-in maximum  */
+    VF_ERR_NOT_RUN = -24          /* a job of a batch that an earlier job's failure kept from running  */
 } vf_status;
 
 /* ------------------------------------------------------------------ */
@@ -495,6 +496,55 @@ typedef struct vf_quant_job {
  * the call synchronises once at the end. Mirrors ConstantFoldingPass folding a
  * batch of constants concurrently (const/passes/constant_folding.cpp:85-159). */
 int vf_quantize_fold_batch(vf_ctx* ctx, vf_quant_job* jobs, int njobs, vf_stats* stats, char* err, size_t errlen);
+
+/* = getMaxIntermediateSize (const/passes/constant_folding.cpp:20-31): the largest total allocation size among
+ * the base type and the type after each transformation. Pure host function. */
+int vf_max_intermediate_size(const vf_tensor_type* base, int base_is_splat, const vf_transform* t, int n,
+                             uint64_t* out_bytes, char* err, size_t errlen);
+
+/* One constant of a ConstantFoldingPass run. */
+typedef struct vf_fold_job {
+    vf_content base;
+    const vf_transform* t;
+    int32_t n;
+    int32_t dst_mem_kind;
+    void* dst;
+    uint64_t dst_bytes;
+    uint64_t dst_written;      /* out: as vf_fold */
+    uint64_t max_intermediate; /* out: vf_max_intermediate_size of the job */
+    int32_t group;             /* out: VF_GROUP_TINY, VF_GROUP_ALONE, or the index (0, 1, ...) of the group it ran in */
+    int32_t status;            /* out: VF_OK once the job has been folded */
+} vf_fold_job;
+#define VF_GROUP_TINY (-1)
+#define VF_GROUP_ALONE (-2)
+
+typedef struct vf_fold_batch_options {
+    uint64_t threshold_bytes;      /* the pass's size threshold (0 = 300 MiB, constant_folding.cpp:74) */
+    uint64_t tiny_threshold_bytes; /* constants up to this size are folded first (0 = 1024, :83) */
+} vf_fold_batch_options;
+
+typedef struct vf_fold_batch_stats {
+    int32_t tiny;             /* jobs folded in the first sweep */
+    int32_t alone;            /* jobs above the threshold, folded one at a time */
+    int32_t groups;           /* groups of jobs folded concurrently */
+    int32_t synchronisations; /* host waits of the whole call */
+    uint64_t max_group_bytes; /* largest sum of max_intermediate over a group */
+} vf_fold_batch_stats;
+
+/* = ConstantFoldingPass::safeRunOnFunc (const/passes/constant_folding.cpp:85-159) over `jobs` in place of the
+ * function's const.Declare ops, each folded as foldSingleConstant does (fold + copyTo into the job's
+ * destination, :33-43). The schedule is the pass's: constants whose largest intermediate is at most
+ * `tiny_threshold_bytes` are folded first; the others are walked in order — one above `threshold_bytes` is
+ * folded on its own, the rest are collected into groups while the running sum of their sizes has not passed the
+ * threshold (so a group may end one job above it, as in the pass). Where the pass hands a group to its thread
+ * pool, the jobs of a group are enqueued back to back on the context's stream here and the host waits once per
+ * group: the threshold bounds the device memory in flight exactly as it bounds the pass's host memory.
+ * The first failing job ends the call with its status (its index is in `err`); jobs folded before it keep
+ * VF_OK, the others VF_ERR_NOT_RUN. A transformation list whose types do not infer fails before any job runs,
+ * since the sizes of all constants are computed first. What a kernel reports for a group (a checked_cast ...) is returned when
+ * the group is waited for and names the group. */
+int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch_options* opts,
+                  vf_fold_batch_stats* batch_stats, vf_stats* stats, char* err, size_t errlen);
 
 /* Shard planner for multi-GPU runs (pure host). Units are independent, so
  * there is no collective: `mode` 0 assigns whole tensors to ranks by

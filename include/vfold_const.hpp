@@ -327,6 +327,7 @@ private:
 };
 
 class ContentAttr;
+class Content;
 
 // ---------------------------------------------------------------------------------------------------------
 // Const::ContentSetup: collects the transformation list. Every builder returns a new setup (the reference
@@ -650,6 +651,8 @@ public:
 
 private:
     friend class BackgroundConstantFolding;
+    friend std::vector<Content> foldConstants(const Context&, const std::vector<ContentAttr>&, uint64_t, uint64_t, vf_fold_batch_stats*,
+                                              std::vector<int>*);
     static constexpr int64_t kParamsCap = 1 << 16;
     TensorType infer(bool& splat, uint64_t& bytes) const {
         const vf_tensor_type base = _setup.getBaseType().pod();
@@ -683,6 +686,49 @@ inline ContentAttr ContentSetup::get(const void* base, size_t baseBytes, bool is
 // device and the folded contents are cached there; fold() is ContentAttr::fold() through that cache.
 // The base buffer of a queued attribute must stay valid until waitIdle() (or the destructor) returns.
 // ---------------------------------------------------------------------------------------------------------
+// ConstantFoldingPass::safeRunOnFunc (const/passes/constant_folding.cpp:85-159) over a list of attributes in place
+// of a function's const.Declare ops: every constant is folded into a buffer of its own with the pass's schedule.
+// `threshold` / `tinyThreshold` of 0 are the pass's 300 MB / 1 KB; `groups` receives where each constant ran.
+inline std::vector<Content> foldConstants(const Context& ctx, const std::vector<ContentAttr>& attrs, uint64_t threshold = 0,
+                                          uint64_t tinyThreshold = 0, vf_fold_batch_stats* batchStats = nullptr,
+                                          std::vector<int>* groups = nullptr) {
+    const size_t n = attrs.size();
+    std::vector<vf_fold_job> jobs(n);
+    std::vector<std::vector<vf_transform>> lists(n);
+    std::vector<std::vector<uint8_t>> dst(n);
+    std::vector<TensorType> types;
+    std::vector<char> splats(n);
+    types.reserve(n);
+    for (size_t j = 0; j < n; ++j) {
+        bool splat;
+        uint64_t need;
+        types.push_back(attrs[j].infer(splat, need));
+        splats[j] = splat;
+        lists[j] = attrs[j].transform().pods();
+        dst[j].resize(size_t(need ? need : 1));
+        vf_fold_job& jb = jobs[j];
+        jb = vf_fold_job{};
+        jb.base = attrs[j].basePod();
+        jb.t = lists[j].data();
+        jb.n = int(lists[j].size());
+        jb.dst_mem_kind = VF_MEM_HOST;
+        jb.dst = dst[j].data();
+        jb.dst_bytes = need;
+    }
+    const vf_fold_batch_options opts{threshold, tinyThreshold};
+    char err[512] = {0};
+    details::check(vf_fold_batch(ctx.get(), jobs.data(), int(n), &opts, batchStats, nullptr, err, sizeof(err)), err);
+    std::vector<Content> out;
+    out.reserve(n);
+    if (groups) groups->clear();
+    for (size_t j = 0; j < n; ++j) {
+        dst[j].resize(size_t(jobs[j].dst_written));
+        out.emplace_back(types[j], splats[j] != 0, std::move(dst[j]));
+        if (groups) groups->push_back(jobs[j].group);
+    }
+    return out;
+}
+
 class BackgroundConstantFolding {
 public:
     // memoryUsageLimit in MB as in the reference (0 = the library's default)

@@ -241,6 +241,33 @@ static void relocateWeightsTable(const Context& ctx) {  // lit const/passes/cons
     EXPECT(content.getValues<int32_t>() == expected);
 }
 
+static void constantFoldingPass(const Context& ctx) {  // const/passes/constant_folding.cpp:85-159
+    std::vector<float> small(64), mid(64 * 1024), large(512 * 1024);
+    for (size_t i = 0; i < small.size(); ++i) small[i] = float(i) * 0.5f;
+    for (size_t i = 0; i < mid.size(); ++i) mid[i] = float(int(i % 255) - 127);
+    for (size_t i = 0; i < large.size(); ++i) large[i] = float(int(i % 63) - 31) * 0.25f;
+    std::vector<Const::ContentAttr> attrs;
+    attrs.push_back(Const::ContentSetup(TensorType({64}, VF_DT_F32)).castElemType(VF_DT_F16).get(small.data(), small.size() * 4));
+    attrs.push_back(Const::ContentSetup(TensorType({512, 1024}, VF_DT_F32)).castElemType(VF_DT_F16).get(large.data(), large.size() * 4));
+    attrs.push_back(Const::ContentSetup(TensorType({64, 1024}, VF_DT_F32)).castElemType(VF_DT_F16).get(mid.data(), mid.size() * 4));
+    attrs.push_back(Const::ContentSetup(TensorType({64, 1024}, VF_DT_F32)).add(1.0).get(mid.data(), mid.size() * 4));
+    vf_fold_batch_stats stats{};
+    std::vector<int> groups;
+    // threshold 1 MiB: the 2 MiB constant that opens the walk is folded alone, the two 256 KiB ones share a
+    // group, the small one is tiny
+    const auto folded = Const::foldConstants(ctx, attrs, 1u << 20, 0, &stats, &groups);
+    EXPECT(groups == (std::vector<int>{VF_GROUP_TINY, VF_GROUP_ALONE, 0, 0}));
+    EXPECT(stats.tiny == 1 && stats.alone == 1 && stats.groups == 1 && stats.synchronisations == 3);
+    EXPECT(stats.max_group_bytes == 2u * 64 * 1024 * 4);
+    EXPECT(folded.size() == 4);
+    for (size_t j = 0; j < folded.size(); ++j) {
+        const auto single = attrs[j].fold(ctx);
+        EXPECT(folded[j].getRawStorageBuf() == single.getRawStorageBuf());
+        EXPECT(folded[j].getType().getShape() == single.getType().getShape());
+    }
+    EXPECT(folded[3].getValues<float>()[5] == mid[5] + 1.0f);
+}
+
 static void foldingInBackground() {  // constant_folding_in_background_tests.cpp:36-52, 88-106 and :156-196
     Const::BackgroundConstantFolding folding(0, 2, true, 3 * 1024, 0.8);
     const TensorType baseType({100}, VF_DT_F32);
@@ -299,6 +326,7 @@ int main(int argc, char** argv) {
             dequantizeQuantize(ctx);
             relocateWeightsTable(ctx);
             copyToTooSmall(ctx);
+            constantFoldingPass(ctx);
             foldingInBackground();
         } catch (const Exception& e) {
             std::printf("unexpected vfold::Exception %d: %s\n", e.status(), e.what());

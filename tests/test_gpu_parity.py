@@ -839,6 +839,21 @@ def test_expand_dilated(gpu, oracle, dil):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dt,np_dt", [(U8, np.uint8), (F16, np.float16), (F32, np.float32)])
+@pytest.mark.parametrize("shape,dil", [([5, 7, 3, 3], (2, 2)), ([33, 17, 5, 1], (4, 2)), ([3, 3, 1, 7], (1, 5)), ([16, 31, 3, 3], (6, 6))])
+def test_expand_dilated_vector_steps(gpu, oracle, dt, np_dt, shape, dil):
+    """Output sizes that are not multiples of the 16-byte store unit, rows shorter and longer than one unit."""
+    rng = np.random.default_rng(sum(shape) + dil[0])
+    x = rng.integers(1, 120, shape).astype(np_dt)
+    t = TType(shape, dt)
+    out = both(ContentAttr(x, t, ContentSetup(t).expandDilated(dil)), gpu, oracle)
+    dky, dkx = (shape[2] - 1) * dil[0] + 1, (shape[3] - 1) * dil[1] + 1
+    want = np.zeros(shape[:2] + [dky, dkx], np_dt)
+    want[:, :, ::dil[0], ::dil[1]] = x
+    assert np.array_equal(out.values(np_dt).reshape(want.shape), want)
+
+
+@pytest.mark.gpu
 def test_scalar_mult_inverse(gpu, oracle):
     from vpux_plugin_b200.lib import VfoldError
     rng = np.random.default_rng(12)

@@ -203,3 +203,23 @@ def test_two_rank_sharding_reassembles_bit_identically():
 
 def test_reference_case_list_is_complete():
     assert len(rc.FOLD_CASES) == 37 and len(rc.TABLE_CASES) == 3
+
+
+def test_max_intermediate_size_follows_the_pass():
+    """getMaxIntermediateSize (const/passes/constant_folding.cpp:20-31): the largest allocation among the base type
+    and the type after each transformation."""
+    from vpux_plugin_b200 import lib
+    from vpux_plugin_b200.abi import TType
+    from vpux_plugin_b200.const import ContentSetup
+    t = TType([16, 3, 3, 3], abi.VF_DT_F32)                                   # 1728 bytes
+    tr, n = ContentSetup(t).transforms()
+    assert lib.max_intermediate_size(t, False, tr, n) == 1728
+    tr, n = ContentSetup(t).castElemType(abi.VF_DT_F16).transforms()           # shrinks: the base stays the largest
+    assert lib.max_intermediate_size(t, False, tr, n) == 1728
+    s = ContentSetup(t).padWithZero([0, 0, 0, 0], [0, 13, 0, 0]).castElemType(abi.VF_DT_F16)
+    tr, n = s.transforms()                                                     # 16x16x3x3 f32 in the middle
+    assert lib.max_intermediate_size(t, False, tr, n) == 16 * 16 * 9 * 4
+    s = ContentSetup(t).castElemType(abi.VF_DT_F16).subview([0, 0, 0, 0], [4, 3, 3, 3]).broadcast(0, 64)
+    tr, n = s.transforms()
+    assert lib.max_intermediate_size(t, False, tr, n) == 64 * 27 * 2
+    assert lib.raw().vf_status_string(abi.VF_ERR_NOT_RUN) == b"job not run"

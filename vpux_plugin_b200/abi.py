@@ -30,6 +30,8 @@ VF_ERR_CUDA = -20
 VF_ERR_NO_DEVICE = -21
 VF_ERR_OOM = -22
 VF_ERR_CAPACITY = -23
+VF_ERR_NOT_RUN = -24
+VF_GROUP_TINY, VF_GROUP_ALONE = -1, -2
 
 # vf_dtype
 (VF_DT_INVALID, VF_DT_F32, VF_DT_F16, VF_DT_BF16, VF_DT_F64, VF_DT_I8, VF_DT_U8, VF_DT_I16, VF_DT_U16, VF_DT_I32,
@@ -130,6 +132,21 @@ class QuantJob(C.Structure):
     _fields_ = [("base", Content), ("spec", QuantSpec), ("t", C.POINTER(Transform)), ("n", C.c_int32),
                 ("dst_mem_kind", C.c_int32), ("dst", C.c_void_p), ("dst_bytes", C.c_uint64), ("outs", QuantOutputs),
                 ("dst_written", C.c_uint64), ("status", C.c_int32), ("reserved", C.c_int32)]
+
+
+class FoldJob(C.Structure):
+    _fields_ = [("base", Content), ("t", C.POINTER(Transform)), ("n", C.c_int32), ("dst_mem_kind", C.c_int32),
+                ("dst", C.c_void_p), ("dst_bytes", C.c_uint64), ("dst_written", C.c_uint64),
+                ("max_intermediate", C.c_uint64), ("group", C.c_int32), ("status", C.c_int32)]
+
+
+class FoldBatchOptions(C.Structure):
+    _fields_ = [("threshold_bytes", C.c_uint64), ("tiny_threshold_bytes", C.c_uint64)]
+
+
+class FoldBatchStats(C.Structure):
+    _fields_ = [("tiny", C.c_int32), ("alone", C.c_int32), ("groups", C.c_int32), ("synchronisations", C.c_int32),
+                ("max_group_bytes", C.c_uint64)]
 
 
 class WeightsTableJob(C.Structure):

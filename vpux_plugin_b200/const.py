@@ -271,3 +271,25 @@ class ContentAttr:
         written, ftype = backend.fold(content, tr, n, dst, cap)
         del keep
         return Folded(ftype, out_splat, dst, written)
+
+
+def foldConstants(library, attrs, threshold_bytes=0, tiny_threshold_bytes=0):
+    """ConstantFoldingPass over a list of ContentAttr (const/passes/constant_folding.cpp:85-159): every constant
+    is folded into a host buffer of its own with the pass's schedule (the small ones first, the large ones in
+    groups under the size threshold). Returns ([Folded], abi.FoldBatchStats, [group of each constant])."""
+    jobs = (abi.FoldJob * len(attrs))()
+    keep, outs, types = [], [], []
+    for j, a in enumerate(attrs):
+        tr, n = a.setup.transforms()
+        content, k = abi.make_content(a.base_type, a.base, a.storage_dtype, a.is_splat)
+        out_type, out_splat, need = library.infer_type(a.base_type, a.is_splat, tr, n)
+        dst = np.zeros(max(int(need), 1), dtype=np.uint8)
+        jobs[j].base, jobs[j].t, jobs[j].n = content, tr, n
+        jobs[j].dst_mem_kind, jobs[j].dst, jobs[j].dst_bytes = abi.VF_MEM_HOST, dst.ctypes.data, int(need)
+        keep.append((tr, k, content))
+        outs.append(dst)
+        types.append((out_type, out_splat))
+    stats = library.fold_batch(jobs, threshold_bytes, tiny_threshold_bytes)
+    folded = [Folded(t, s, d, int(jobs[j].dst_written)) for j, ((t, s), d) in enumerate(zip(types, outs))]
+    del keep
+    return folded, stats, [int(jobs[j].group) for j in range(len(attrs))]

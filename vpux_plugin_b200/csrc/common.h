@@ -107,6 +107,7 @@ void order_to_perm(uint32_t order, int rank, int* perm);
 
 // inferOutputType / inferOutputSplat of one transformation (pure host)
 Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_splat);
+uint64_t max_intermediate_size(Type ty, bool splat, const vf_transform* t, int n);
 void check_positions(const vf_transform* t, int n);
 int64_t swizzle_size_alignment(int arch);  // bytes a swizzled buffer's size is aligned to
 Type compress_type(const Type& in, const int64_t* counts, int64_t n);

@@ -947,6 +947,36 @@ uint64_t copy_folded(vf_ctx* ctx, const Folded& f, void* dst, uint64_t dst_bytes
     return w;
 }
 
+// ContentAttr::fold() + Content::copyTo() of one constant, enqueued on the context's stream (the caller owns the
+// call scope and decides when the host waits). Returns the bytes written.
+uint64_t fold_one(vf_ctx* ctx, const vf_content& base, const vf_transform* t, int n, void* dst, uint64_t dst_bytes, int dst_mem_kind,
+                  vf_tensor_type* out_type, double* scales_buf, int64_t* zps_buf, int64_t params_cap, vf_stats* stats) {
+    DContent cur = upload_base(ctx, base, stats);
+    // the destination doubles as the last transformation's output buffer when it is device memory that does
+    // not overlap the base content
+    const char* b0 = static_cast<const char*>(base.data);
+    const char* d0 = static_cast<const char*>(dst);
+    const bool direct = dst && dst_mem_kind == VF_MEM_DEVICE &&
+                        (base.mem_kind != VF_MEM_DEVICE || d0 + dst_bytes <= b0 || b0 + base.nbytes <= d0);
+    struct Hint {
+        vf_ctx* c;
+        ~Hint() { c->final_dst = nullptr; }
+    } hint{ctx};
+    for (int i = 0; i < n; ++i) {  // ContentAttr::fold — attributes/content.cpp:392-394
+        if (direct && i == n - 1) {
+            ctx->final_dst = dst;
+            ctx->final_bytes = dst_bytes;
+        }
+        DContent next = apply(ctx, cur, t[i]);
+        cur = std::move(next);
+    }
+    ctx->final_dst = nullptr;
+    cur.type.export_to(out_type, scales_buf, zps_buf, params_cap);
+    const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_mem_kind, stats);
+    if (stats) stats->bytes_out += w;
+    return w;
+}
+
 }  // namespace vf
 
 using namespace vf;
@@ -960,31 +990,94 @@ int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, v
         if (!base || (n > 0 && !t) || n < 0) raise(VF_ERR_INVALID_ARG, "NULL argument");
         check_positions(t, n);
         CallScope scope(ctx, stats);
-        DContent cur = upload_base(ctx, *base, stats);
-        // the destination doubles as the last transformation's output buffer when it is device memory that does
-        // not overlap the base content
-        const char* b0 = static_cast<const char*>(base->data);
-        const char* d0 = static_cast<const char*>(dst);
-        const bool direct = dst && dst_mem_kind == VF_MEM_DEVICE &&
-                            (base->mem_kind != VF_MEM_DEVICE || d0 + dst_bytes <= b0 || b0 + base->nbytes <= d0);
-        struct Hint {
-            vf_ctx* c;
-            ~Hint() { c->final_dst = nullptr; }
-        } hint{ctx};
-        for (int i = 0; i < n; ++i) {  // ContentAttr::fold — attributes/content.cpp:392-394
-            if (direct && i == n - 1) {
-                ctx->final_dst = dst;
-                ctx->final_bytes = dst_bytes;
-            }
-            DContent next = apply(ctx, cur, t[i]);
-            cur = std::move(next);
-        }
-        ctx->final_dst = nullptr;
-        cur.type.export_to(out_type, scales_buf, zps_buf, params_cap);
-        const uint64_t w = copy_to(ctx, cur, dst, dst_bytes, dst_mem_kind, stats);
+        const uint64_t w = fold_one(ctx, *base, t, n, dst, dst_bytes, dst_mem_kind, out_type, scales_buf, zps_buf, params_cap, stats);
         if (dst_written) *dst_written = w;
-        if (stats) stats->bytes_out += w;
         scope.finish();
+    });
+}
+
+int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch_options* opts,
+                  vf_fold_batch_stats* batch_stats, vf_stats* stats, char* err, size_t errlen) {
+    return guard(err, errlen, [&] {
+        if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        const uint64_t threshold = opts && opts->threshold_bytes ? opts->threshold_bytes : 300ull * 1024 * 1024;
+        const uint64_t tiny = opts && opts->tiny_threshold_bytes ? opts->tiny_threshold_bytes : 1024;
+        vf_fold_batch_stats bs{};
+        for (int j = 0; j < njobs; ++j) {
+            vf_fold_job& jb = jobs[j];
+            jb.status = VF_ERR_NOT_RUN;
+            jb.dst_written = 0;
+            if ((jb.n > 0 && !jb.t) || jb.n < 0) raise(VF_ERR_INVALID_ARG, "job %d: NULL transformation list", j);
+        }
+        for (int j = 0; j < njobs; ++j) {  // the sizes of all constants come first, as in the pass (:100-104)
+            vf_fold_job& jb = jobs[j];
+            try {
+                check_positions(jb.t, jb.n);
+                jb.max_intermediate = max_intermediate_size(Type::from(jb.base.type), jb.base.is_splat != 0, jb.t, jb.n);
+            } catch (const Error& e) {
+                jb.status = e.code;
+                raise(e.code, "job %d: %s", j, e.what());
+            }
+        }
+        CallScope scope(ctx, stats);
+        auto run = [&](int j, int group) {
+            vf_fold_job& jb = jobs[j];
+            jb.group = group;
+            try {
+                jb.dst_written = fold_one(ctx, jb.base, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, nullptr, nullptr, nullptr, 0, stats);
+                jb.status = VF_OK;
+            } catch (const Error& e) {
+                jb.status = e.code;
+                raise(e.code, "job %d: %s", j, e.what());
+            }
+        };
+        // What the kernels of the jobs enqueued so far have found is read here, once per group: the host waits
+        // for the stream, so everything those jobs allocated is free again before the next group starts.
+        auto wait = [&](const char* what, int index) {
+            ++bs.synchronisations;
+            try {
+                flags_check(ctx);
+                ctx->table_used = 0;  // nothing is in flight: the job-table area starts over
+            } catch (const Error& e) {
+                if (index < 0) raise(e.code, "%s: %s", what, e.what());
+                raise(e.code, "%s %d: %s", what, index, e.what());
+            }
+        };
+        // the first sweep: constants within the tiny threshold (constant_folding.cpp:100-109)
+        std::vector<int> big;
+        for (int j = 0; j < njobs; ++j) {
+            if (jobs[j].max_intermediate > tiny) {
+                big.push_back(j);
+                continue;
+            }
+            run(j, VF_GROUP_TINY);
+            ++bs.tiny;
+        }
+        if (bs.tiny) wait("the constants within the tiny threshold", -1);
+        // the others in order (constant_folding.cpp:113-158)
+        size_t at = 0;
+        while (at < big.size()) {
+            const int j = big[at];
+            if (jobs[j].max_intermediate > threshold) {
+                run(j, VF_GROUP_ALONE);
+                wait("job", j);
+                ++bs.alone;
+                ++at;
+                continue;
+            }
+            uint64_t in_flight = 0;
+            const int group = bs.groups++;
+            while (in_flight <= threshold && at < big.size()) {
+                in_flight += jobs[big[at]].max_intermediate;
+                run(big[at], group);
+                ++at;
+            }
+            bs.max_group_bytes = std::max(bs.max_group_bytes, in_flight);
+            wait("group", group);
+        }
+        if (batch_stats) *batch_stats = bs;
+        scope.finished = true;
+        if (stats) stats->kernels_launched = int32_t(ctx->launches - scope.launches0);
     });
 }
 

@@ -452,6 +452,18 @@ bool calc_scale_zp_host(double qmin, double qmax, double rmin, double rmax, doub
     return true;
 }
 
+// getMaxIntermediateSize — const/passes/constant_folding.cpp:20-31
+uint64_t max_intermediate_size(Type ty, bool splat, const vf_transform* t, int n) {
+    uint64_t most = ty.alloc_bytes();
+    for (int i = 0; i < n; ++i) {
+        bool s;
+        ty = infer_one(ty, splat, t[i], s);
+        splat = s;
+        most = std::max<uint64_t>(most, ty.alloc_bytes());
+    }
+    return most;
+}
+
 }  // namespace vf
 
 extern "C" {
@@ -481,6 +493,7 @@ const char* vf_status_string(int s) {
     case VF_ERR_NO_DEVICE: return "no CUDA device";
     case VF_ERR_OOM: return "out of memory";
     case VF_ERR_CAPACITY: return "request exceeds built-in capacity";
+    case VF_ERR_NOT_RUN: return "job not run";
     default: return "unknown status";
     }
 }
@@ -501,6 +514,14 @@ int vf_infer_type(const vf_tensor_type* base, int base_is_splat, const vf_transf
         ty.export_to(out, scales_buf, zps_buf, params_cap);
         if (out_is_splat) *out_is_splat = splat ? 1 : 0;
         if (out_bytes) *out_bytes = ty.alloc_bytes();
+    });
+}
+
+int vf_max_intermediate_size(const vf_tensor_type* base, int base_is_splat, const vf_transform* t, int n,
+                             uint64_t* out_bytes, char* err, size_t errlen) {
+    return vf::guard(err, errlen, [&] {
+        if (!base || !out_bytes || (n > 0 && !t) || n < 0) vf::raise(VF_ERR_INVALID_ARG, "NULL argument");
+        *out_bytes = vf::max_intermediate_size(vf::Type::from(*base), base_is_splat != 0, t, n);
     });
 }
 

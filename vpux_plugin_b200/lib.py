@@ -29,7 +29,7 @@ def _load():
     lib = C.CDLL(LIB_PATH)
     for name in ("vf_infer_type", "vf_optimize_transforms", "vf_fold", "vf_fuse", "vf_row_stats", "vf_quantize_fold", "vf_quantize_fold_batch",
                  "vf_nnz_per_oc", "vf_sparsify", "vf_sparsify_batch", "vf_weights_table", "vf_weights_table_batch", "vf_synth_fill", "vf_plan_shards",
-                 "vf_ctx_create", "vf_ctx_synchronize", "vf_abi_version", "vf_ctx_device"):
+                 "vf_ctx_create", "vf_ctx_synchronize", "vf_abi_version", "vf_ctx_device", "vf_fold_batch", "vf_max_intermediate_size"):
         getattr(lib, name).restype = C.c_int
     lib.vf_ctx_destroy.restype = None
     lib.vf_ctx_destroy.argtypes = [C.c_void_p]
@@ -91,6 +91,17 @@ def infer_type(base_type, is_splat, transforms, n, params_cap=1 << 16):
     if st != 0:
         raise VfoldError(st, err.value.decode(errors="replace"))
     return abi.TType.from_pod(out), bool(osplat.value), nbytes.value
+
+
+def max_intermediate_size(base_type, is_splat, transforms, n):
+    """vf_max_intermediate_size (pure host) = getMaxIntermediateSize, const/passes/constant_folding.cpp:20-31."""
+    out = C.c_uint64(0)
+    err = C.create_string_buffer(512)
+    bt = base_type.pod()
+    st = raw().vf_max_intermediate_size(C.byref(bt), int(is_splat), transforms, n, C.byref(out), err, C.c_size_t(512))
+    if st != 0:
+        raise VfoldError(st, err.value.decode(errors="replace"))
+    return out.value
 
 
 def optimize_transforms(base_type, transforms, n, params_cap=1 << 16):
@@ -221,6 +232,18 @@ class Library:
         err = self._err()
         st = self.lib.vf_quantize_fold_batch(self.ctx, jobs, len(jobs), C.byref(self.last_stats), err, C.c_size_t(512))
         self._check(st, err)
+
+    def fold_batch(self, jobs, threshold_bytes=0, tiny_threshold_bytes=0):
+        """jobs: ctypes array of abi.FoldJob, folded with ConstantFoldingPass's schedule
+        (const/passes/constant_folding.cpp:85-159). Returns abi.FoldBatchStats; every job's `dst_written`,
+        `max_intermediate`, `group` and `status` are filled in, also when the call raises."""
+        opts = abi.FoldBatchOptions(int(threshold_bytes), int(tiny_threshold_bytes))
+        bs = abi.FoldBatchStats()
+        err = self._err()
+        st = self.lib.vf_fold_batch(self.ctx, jobs, len(jobs), C.byref(opts), C.byref(bs), C.byref(self.last_stats), err,
+                                    C.c_size_t(512))
+        self._check(st, err)
+        return bs
 
     def nnz_per_oc(self, content, oc):
         counts = np.zeros(oc, np.int64)
