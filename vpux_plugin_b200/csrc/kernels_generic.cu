@@ -862,59 +862,51 @@ __global__ void k_expand_dilated(const void* __restrict__ in, int in_splat, void
 }
 
 // The same transformation, output-centric: each thread step produces 16 bytes of consecutive output (full-width
-// coalesced stores) and walks (plane, y, x) incrementally, so the divisions happen once per step. The taps are
-// gathered with scalar loads; every input element is read exactly once and neighbouring threads read
-// neighbouring elements. Needs a 16-byte aligned output and ES < 16.
+// coalesced stores). A table in shared memory maps a position inside one dilated plane (dky * dkx elements) to
+// the tap it copies, or to -1 for a gap, so a step costs one division (its plane) and per element one table
+// read and one gathered load. Every input element is read exactly once. Needs a 16-byte aligned output,
+// ES < 16 and a plane that fits the table.
 template <int ES, typename I>
-__global__ void k_expand_dilated_vec(const void* __restrict__ in, int in_splat, void* __restrict__ out, I n_out, I dky, I dkx,
+__global__ void k_expand_dilated_lut(const void* __restrict__ in, int in_splat, void* __restrict__ out, I n_out, I dky, I dkx,
                                      I ky, I kx, I dil_y, I dil_x, const void* __restrict__ fill, I n_fill, I fill_stride,
                                      I fill_extent) {
     using T = typename ElemBits<ES>::type;
     constexpr int VEC = 16 / ES;
+    extern __shared__ int tap_of[];
+    const I plane_out = dky * dkx, plane_in = ky * kx;
+    for (I p = threadIdx.x; p < plane_out; p += blockDim.x) {
+        const I y = p / dkx, x = p - y * dkx;
+        const I ty = y / dil_y, tx = x / dil_x;
+        tap_of[p] = (ty * dil_y == y && tx * dil_x == x) ? int(ty * kx + tx) : -1;
+    }
+    __syncthreads();
     const T* src = static_cast<const T*>(in);
     const T* fv = static_cast<const T*>(fill);
     const T fill0 = fv[0];
     const I n_steps = (n_out + I(VEC - 1)) / I(VEC);
     const I stride = index_stride<I>();
     for (I step = first_index<I>(); step < n_steps; step += stride) {
-        I o = step * I(VEC);
-        const I row = o / dkx;
-        I x = o - row * dkx;
-        I plane = row / dky;
-        I y = row - plane * dky;
-        I ty = y / dil_y, ry = y - ty * dil_y;
-        I tx = x / dil_x, rx = x - tx * dil_x;
-        I src_row = (plane * ky + ty) * kx;
+        const I o = step * I(VEC);
+        I plane = o / plane_out;
+        I p = o - plane * plane_out;
+        I base = in_splat ? I(0) : plane * plane_in;
         union {
             T v[VEC];
             uint4 q;
         } pack;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
+            const int tap = tap_of[p];
             T v;
-            if (ry == 0 && rx == 0) {
-                v = src[in_splat ? I(0) : src_row + tx];
+            if (tap >= 0) {
+                v = src[in_splat ? I(0) : base + I(tap)];
             } else {
                 v = n_fill > 1 ? fv[((o + I(k)) / fill_stride) % fill_extent] : fill0;
             }
             pack.v[k] = v;
-            ++x;
-            if (++rx == dil_x) {
-                rx = 0;
-                ++tx;
-            }
-            if (x == dkx) {
-                x = 0, rx = 0, tx = 0;
-                ++y;
-                if (++ry == dil_y) {
-                    ry = 0;
-                    ++ty;
-                }
-                if (y == dky) {
-                    y = 0, ry = 0, ty = 0;
-                    ++plane;
-                }
-                src_row = (plane * ky + ty) * kx;
+            if (++p == plane_out) {
+                p = 0;
+                base += in_splat ? I(0) : plane_in;
             }
         }
         if (o + I(VEC) <= n_out) {
@@ -1525,20 +1517,22 @@ void launch_expand_dilated(vf_ctx* ctx, const void* in, bool in_splat, void* out
                            int64_t fill_stride, int64_t fill_extent, int es) {
     if (n_out <= 0) return;
     const int64_t n_rows = n_out / dkx;
-    if (es < 16 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+    constexpr int64_t kMaxPlane = 8192;  // table entries (32 KiB of shared memory)
+    if (es < 16 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && dky * dkx <= kMaxPlane) {
         const int64_t n_steps = (n_out * es + 15) / 16;
+        const size_t smem = size_t(dky * dkx) * sizeof(int);
         switch (es) {
-#define VF_EXPAND_VEC(ES_)                                                                                                          \
+#define VF_EXPAND_LUT(ES_)                                                                                                          \
     case ES_:                                                                                                                       \
-        VF_BY_INDEX_WIDTH(n_out + 16, (k_expand_dilated_vec<ES_, I><<<grid_for(n_steps), kBlock, 0, ctx->stream>>>(                 \
+        VF_BY_INDEX_WIDTH(n_out + 16, (k_expand_dilated_lut<ES_, I><<<grid_for(n_steps), kBlock, smem, ctx->stream>>>(              \
                                           in, in_splat ? 1 : 0, out, I(n_out), I(dky), I(dkx), I(ky), I(kx), I(dil_y), I(dil_x), d_fill, \
                                           I(n_fill), I(fill_stride), I(fill_extent))));                                            \
         break;
-            VF_EXPAND_VEC(1)
-            VF_EXPAND_VEC(2)
-            VF_EXPAND_VEC(4)
-            VF_EXPAND_VEC(8)
-#undef VF_EXPAND_VEC
+            VF_EXPAND_LUT(1)
+            VF_EXPAND_LUT(2)
+            VF_EXPAND_LUT(4)
+            VF_EXPAND_LUT(8)
+#undef VF_EXPAND_LUT
         default: raise(VF_ERR_UNSUPPORTED, "ExpandDilated: element size");
         }
         post_launch(ctx);
