@@ -989,12 +989,13 @@ def test_rank_six_layout_transformations(gpu, oracle):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dt", [F32, F16])
 @pytest.mark.parametrize("qmin,qmax,storage", [(0, 255, U8), (-128, 127, I8), (-127, 127, I8), (0, 15, U8), (-120, 120, I8)])
-def test_general_quantize_on_rounding_boundaries(gpu, oracle, dt, qmin, qmax, storage):
+@pytest.mark.parametrize("inner", [512, 3000])  # 3000: rows long enough for the by-rows kernel, with a ragged last chunk
+def test_general_quantize_on_rounding_boundaries(gpu, oracle, dt, qmin, qmax, storage, inner):
     """Quantize with given parameters (quantize.cpp:108-212): values on and next to the .5 boundaries of every
     level, where the fast evaluation must hand over to the exact sequence; [-120, 120] is a range whose
     fakeQuantize tail is not the identity (all elements take the exact sequence)."""
     rng = np.random.default_rng(qmax * 3 + dt)
-    oc, inner = 24, 512
+    oc = 24
     scales = rng.uniform(0.003, 0.9, oc)
     zps = rng.integers(qmin, qmax + 1, oc) if qmin == 0 else np.zeros(oc, np.int64)
     levels = qmax - qmin
@@ -1017,6 +1018,27 @@ def test_general_quantize_on_rounding_boundaries(gpu, oracle, dt, qmin, qmax, st
     special = data.copy()
     special[0, :8] = [np.inf, -np.inf, 1e30 if dt == F32 else 6e4, -1e30 if dt == F32 else -6e4, 0.0, -0.0, 1e-30 if dt == F32 else 6e-8, 3.0]
     both(ContentAttr(special, t, ContentSetup(t).quantize(q)), gpu, oracle)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("storage,np_dt,qmin,qmax", [(I8, np.int8, -128, 127), (U8, np.uint8, 0, 255)])
+@pytest.mark.parametrize("shape,axis", [([6, 9000], 0), ([3, 5, 8200], 1), ([4, 16, 8], 0), ([2, 70000], 1)])
+def test_general_dequantize_by_rows(gpu, oracle, storage, np_dt, qmin, qmax, shape, axis):
+    """Dequantize (dequantize.cpp:42-108) of every code, with rows inside the quantized axis long and short, whole
+    and ragged against the kernel's chunk size; per-axis and per-tensor."""
+    rng = np.random.default_rng(shape[-1] + axis)
+    n = shape[axis]
+    x = rng.integers(qmin, qmax + 1, shape).astype(np_dt)
+    x.reshape(-1)[:qmax - qmin + 1] = np.arange(qmin, qmax + 1).astype(np_dt)
+    t = TType(shape, storage)
+    if n <= 64:
+        qa = Elem.per_axis(storage, F32, rng.uniform(1e-3, 2.0, n).tolist(), [int(z) for z in rng.integers(qmin, qmax + 1, n)], axis, qmin, qmax)
+        both(ContentAttr(x, t, ContentSetup(t).castElemType(qa).dequantize()), gpu, oracle)
+    qt = Elem.uniform(storage, F16, 0.0123456789, int(rng.integers(qmin, qmax + 1)), qmin, qmax)
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(qt).dequantize()), gpu, oracle)
+    for zp in ((1 << 30) - 1, 1 << 30, -(1 << 30), (1 << 33) + 5, -(1 << 40)):  # around and beyond the 32-bit difference
+        qz = Elem.uniform(storage, F32, 0.37, zp, qmin, qmax)
+        both(ContentAttr(x, t, ContentSetup(t).castElemType(qz).dequantize()), gpu, oracle)
 
 
 @pytest.mark.gpu

@@ -152,6 +152,98 @@ __global__ void k_quantize8(const void* __restrict__ in, uint8_t* __restrict__ o
     }
 }
 
+// The same two kernels by rows: a block iteration covers a chunk of kRowUnroll * blockDim groups of ONE row of the
+// quantized axis, so the row's parameters (two FP64 products, a division) and the row index (two integer
+// divisions) are computed once per chunk instead of once per group. Used when a row holds at least one chunk's
+// worth of groups; a per-tensor type is one row.
+constexpr int kRowUnroll = 4;
+template <int IN, typename I, bool FAST>
+__global__ void k_quantize8_rows(const void* __restrict__ in, uint8_t* __restrict__ out, I n_rows, I chunks_per_row,
+                                 const double* __restrict__ scales, const int64_t* __restrict__ zps, I axis_size, I inner8,
+                                 long long qmin, long long qmax, int* flags) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    constexpr int kMagicBits = 0x4B400000;
+    const I n_chunks = n_rows * chunks_per_row;
+    const int lm1 = int(qmax - qmin);
+    for (I chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+        const I row = chunk / chunks_per_row, c_in_row = chunk - row * chunks_per_row;
+        const I a = axis_size > 1 ? row % axis_size : I(0);
+        const QuantParams qp = make_quant_params(scales[a], zps[a], qmin, qmax);
+        const float inv = __fdiv_rn(qp.levels_m1, qp.range);
+        const float c = __fmul_rn(-qp.in_low, inv);
+        const float thr = 0.5f - 8.0e-7f * (qp.levels_m1 + 1.0f);
+        const I g0 = c_in_row * I(kRowUnroll) * I(blockDim.x) + I(threadIdx.x);
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) {
+            const I gr = g0 + I(u) * I(blockDim.x);
+            if (gr >= inner8) break;
+            const int64_t g = int64_t(row) * int64_t(inner8) + int64_t(gr);
+            __align__(16) uint8_t ib[Bytes8<IN>::value];
+            __align__(8) uint8_t ob[8];
+            load8<IN>(in, g, ib);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float x = load_as_f32(ib, IN, k, flags);
+                if (x != x) set_flag(flags, VF_FLAG_NAN);
+                if (FAST) {
+                    const float t = __fmaf_rn(x, inv, c);
+                    const float m = __fadd_rn(t, kMagic);
+                    const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
+                    int code;
+                    if (fabsf(resid) <= thr) {  // false for NaN as well
+                        const int n = __float_as_int(m) - kMagicBits;
+                        code = min(max(n, 0), lm1) + int(qmin);
+                    } else {
+                        code = int(quantize_exact(x, qp));
+                    }
+                    ob[k] = uint8_t(code);
+                } else {
+                    ob[k] = uint8_t(quantize_exact(x, qp));
+                }
+            }
+            store8<8>(out, g, ob);
+        }
+    }
+}
+
+template <int IN, typename I>
+__global__ void k_dequantize8_rows(const void* __restrict__ in, float* __restrict__ out, I n_rows, I chunks_per_row,
+                                   const double* __restrict__ scales, const int64_t* __restrict__ zps, I axis_size, I inner8) {
+    const I n_chunks = n_rows * chunks_per_row;
+    for (I chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+        const I row = chunk / chunks_per_row, c_in_row = chunk - row * chunks_per_row;
+        const I a = axis_size > 1 ? row % axis_size : I(0);
+        const double scale = scales[a];
+        const long long zp = zps[a];
+        // q - zp as a 32-bit integer turns into a double without the conversion unit: the integer, biased by 2^31,
+        // is placed in the low word of 2^52 + 2^51 and the bias subtracted again (exact); zero points beyond 2^30
+        // take the plain conversion
+        const bool small_zp = zp > -(1ll << 30) && zp < (1ll << 30);
+        const int zp32 = int(zp);
+        const I g0 = c_in_row * I(kRowUnroll) * I(blockDim.x) + I(threadIdx.x);
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) {
+            const I gr = g0 + I(u) * I(blockDim.x);
+            if (gr >= inner8) break;
+            const int64_t g = int64_t(row) * int64_t(inner8) + int64_t(gr);
+            __align__(8) uint8_t ib[8];
+            __align__(16) float ob[8];
+            load8<IN>(in, g, ib);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int q32 = IN == VF_DT_I8 ? int(int8_t(ib[k])) : int(ib[k]);
+                if (small_zp) {
+                    const double d = __dsub_rn(__hiloint2double(0x43380000, (q32 - zp32) ^ int(0x80000000)), 6755401588539392.0);
+                    ob[k] = __double2float_rn(__dmul_rn(d, scale));
+                } else {
+                    ob[k] = dequantize_exact((long long)(q32), scale, zp);
+                }
+            }
+            store8<32>(out, g, reinterpret_cast<const uint8_t*>(ob));
+        }
+    }
+}
+
 template <int IN, typename I>
 __global__ void k_dequantize8(const void* __restrict__ in, float* __restrict__ out, I n_groups, const double* __restrict__ scales,
                               const int64_t* __restrict__ zps, I axis_size, I inner8) {
@@ -1088,6 +1180,27 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
         const int grid = grid_for(groups);
         uint8_t* o = static_cast<uint8_t*>(out);
         const bool fast = qmax - qmin <= 255 && qmax > qmin && tail_is_identity(qmin, qmax);
+        // by rows: the quantized axis and everything outside it index the row, what is inside it is the row
+        const int64_t row_len = axis_size > 1 ? inner8 : groups, n_rows = groups / row_len;
+        const int64_t chunk = int64_t(kRowUnroll) * kBlock, chunks_per_row = (row_len + chunk - 1) / chunk;
+        if (row_len >= chunk && row_len < (int64_t(1) << 31) && n_rows * chunks_per_row < (int64_t(1) << 31)) {
+            const int64_t n_chunks = n_rows * chunks_per_row;
+            const int rgrid = int(n_chunks < 148 * 16 ? n_chunks : 148 * 16);
+            using I = uint32_t;
+#define VF_Q8R(IN)                                                                                                                      \
+    if (fast)                                                                                                                           \
+        k_quantize8_rows<IN, I, true><<<rgrid, kBlock, 0, ctx->stream>>>(in, o, I(n_rows), I(chunks_per_row), d_scales, d_zps,         \
+                                                                         I(axis_size), I(row_len), qmin, qmax, ctx->d_flags);         \
+    else                                                                                                                                \
+        k_quantize8_rows<IN, I, false><<<rgrid, kBlock, 0, ctx->stream>>>(in, o, I(n_rows), I(chunks_per_row), d_scales, d_zps,        \
+                                                                          I(axis_size), I(row_len), qmin, qmax, ctx->d_flags);
+            if (in_dt == VF_DT_F32) { VF_Q8R(VF_DT_F32) }
+            else if (in_dt == VF_DT_F16) { VF_Q8R(VF_DT_F16) }
+            else { VF_Q8R(VF_DT_BF16) }
+#undef VF_Q8R
+            post_launch(ctx);
+            return;
+        }
 #define VF_Q8(IN)                                                                                                                       \
     if (fast) {                                                                                                                         \
         VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I, true><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps,        \
@@ -1115,6 +1228,21 @@ void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, fl
         aligned16(in, out)) {
         const int64_t groups = n / 8, inner8 = axis_size > 1 ? inner / 8 : 1;
         const int grid = grid_for(groups);
+        const int64_t row_len = axis_size > 1 ? inner8 : groups, n_rows = groups / row_len;
+        const int64_t chunk = int64_t(kRowUnroll) * kBlock, chunks_per_row = (row_len + chunk - 1) / chunk;
+        if (row_len >= chunk && row_len < (int64_t(1) << 31) && n_rows * chunks_per_row < (int64_t(1) << 31)) {
+            const int64_t n_chunks = n_rows * chunks_per_row;
+            const int rgrid = int(n_chunks < 148 * 16 ? n_chunks : 148 * 16);
+            using I = uint32_t;
+            if (in_dt == VF_DT_I8)
+                k_dequantize8_rows<VF_DT_I8, I><<<rgrid, kBlock, 0, ctx->stream>>>(in, out, I(n_rows), I(chunks_per_row), d_scales, d_zps,
+                                                                                   I(axis_size), I(row_len));
+            else
+                k_dequantize8_rows<VF_DT_U8, I><<<rgrid, kBlock, 0, ctx->stream>>>(in, out, I(n_rows), I(chunks_per_row), d_scales, d_zps,
+                                                                                   I(axis_size), I(row_len));
+            post_launch(ctx);
+            return;
+        }
         if (in_dt == VF_DT_I8) {
             VF_BY_INDEX_WIDTH(groups, (k_dequantize8<VF_DT_I8, I><<<grid, kBlock, 0, ctx->stream>>>(in, out, I(groups), d_scales, d_zps,
                                                                                                     I(axis_size), I(inner8))));
