@@ -221,14 +221,21 @@ __global__ void k_dequantize8_rows(const void* __restrict__ in, float* __restric
         const bool small_zp = zp > -(1ll << 30) && zp < (1ll << 30);
         const int zp32 = int(zp);
         const I g0 = c_in_row * I(kRowUnroll) * I(blockDim.x) + I(threadIdx.x);
+        // all loads of the chunk are issued before the first value is needed
+        __align__(8) uint8_t ibs[kRowUnroll][8];
+        const int64_t row0 = int64_t(row) * int64_t(inner8);
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) {
+            const I gr = g0 + I(u) * I(blockDim.x);
+            if (gr < inner8) load8<IN>(in, row0 + int64_t(gr), ibs[u]);
+        }
 #pragma unroll
         for (int u = 0; u < kRowUnroll; ++u) {
             const I gr = g0 + I(u) * I(blockDim.x);
             if (gr >= inner8) break;
-            const int64_t g = int64_t(row) * int64_t(inner8) + int64_t(gr);
-            __align__(8) uint8_t ib[8];
+            const int64_t g = row0 + int64_t(gr);
+            const uint8_t* ib = ibs[u];
             __align__(16) float ob[8];
-            load8<IN>(in, g, ib);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const int q32 = IN == VF_DT_I8 ? int(int8_t(ib[k])) : int(ib[k]);
