@@ -293,3 +293,118 @@ def foldConstants(library, attrs, threshold_bytes=0, tiny_threshold_bytes=0):
     folded = [Folded(t, s, d, int(jobs[j].dst_written)) for j, ((t, s), d) in enumerate(zip(types, outs))]
     del keep
     return folded, stats, [int(jobs[j].group) for j in range(len(attrs))]
+
+
+class FusedConstant:
+    """Const::FuseAttr (attributes/fuse_transform.cpp:31-63) with the list that follows it: the constants of one
+    NCE operation — weights table, weights, sparsity map, activations — folded one after the other into one flat
+    buffer of `fused_type`. `subview` and `relocateWeightsTablePointers` apply the rules that move a following
+    transformation into the Fuse (moveTransformationIntoFuse, utils/transformations.cpp:831-862); what cannot
+    be moved stays behind the Fuse and is applied to the fused bytes."""
+
+    def __init__(self, fused_type, weightsTable=None, weights=None, sparsity=None, activations=None, trailing=None):
+        self.fused_type = fused_type
+        self.weightsTable, self.weights, self.sparsity, self.activations = weightsTable, weights, sparsity, activations
+        self.trailing = trailing if trailing is not None else ContentSetup(fused_type)
+
+    def parts(self):
+        return [self.weightsTable, self.weights, self.sparsity, self.activations]
+
+    @staticmethod
+    def _type_of(attr):
+        from . import lib
+        tr, n = attr.setup.transforms()
+        t, _, nbytes = lib.infer_type(attr.base_type, attr.is_splat, tr, n)
+        return t, int(nbytes)
+
+    @staticmethod
+    def _with(attr, setup):
+        return ContentAttr(attr.base, attr.base_type, setup.optimized(), attr.is_splat, attr.storage_dtype)
+
+    # -- moveTransformationIntoFuse: RelocateWeightsTable joins the weights table's own list (:842-846) ----------
+    def relocateWeightsTablePointers(self, *args, **kwargs):
+        if self.trailing.names() or self.weightsTable is None:
+            return self._behind(self.trailing.relocateWeightsTablePointers(*args, **kwargs))
+        wt = self._with(self.weightsTable, self.weightsTable.setup.relocateWeightsTablePointers(*args, **kwargs))
+        return FusedConstant(self.fused_type, wt, self.weights, self.sparsity, self.activations)
+
+    def _behind(self, trailing):
+        return FusedConstant(self.fused_type, self.weightsTable, self.weights, self.sparsity, self.activations, trailing)
+
+    # -- moveSubViewIntoFuse (:687-826) ----------------------------------------------------------------------
+    def subview(self, offset, shape):
+        offset, shape = [int(v) for v in offset], [int(v) for v in shape]
+        fs = list(self.fused_type.shape)
+        movable = (not self.trailing.names() and self.sparsity is None and len(fs) == 4 and len(offset) == 4 and
+                   len(shape) == 4 and all(fs[d] == 1 and offset[d] == 0 and shape[d] == 1 for d in range(3)))
+        if not movable:
+            return self._behind(self.trailing.subview(offset, shape))
+        elem_bytes = abi.DTYPE_BITS[self.fused_type.elem.dtype] // 8
+        sub_start = offset[3] * elem_bytes
+        sub_end = sub_start + shape[3] * elem_bytes
+        at = 0
+        new = []
+        for attr in (self.weightsTable, self.weights, self.activations):
+            if attr is None:
+                new.append(None)
+                continue
+            moved, at = self._slice_part(attr, at, sub_start, sub_end)
+            new.append(moved)
+        ft = TType([1, 1, 1, shape[3]], self.fused_type.elem, self.fused_type.order)
+        return FusedConstant(ft, new[0], new[1], None, new[2])
+
+    @classmethod
+    def _slice_part(cls, attr, c_start, sub_start, sub_end):
+        """getNewConstant (:757-805): the part of `attr` inside [sub_start, sub_end) of the fused buffer, as a
+        SubView on its own shape plus, where that cannot express it, a flat Reshape + SubView."""
+        ctype, cbytes = cls._type_of(attr)
+        c_end = c_start + cbytes
+        if ctype.elem.quantized:  # sliced quantized axes would no longer match their parameters: storage type
+            attr = cls._with(attr, attr.setup.castElemType(ctype.elem.dtype))
+            ctype, cbytes = cls._type_of(attr)
+        bits = abi.DTYPE_BITS[ctype.elem.dtype]
+        # getOverlapRegionBounds (:716-727), kept as written: a view that starts before the constant and ends
+        # at or behind its end does not count as overlapping
+        lo = hi = 0
+        if c_end > c_start and sub_end > sub_start and ((c_start <= sub_start < c_end) or (c_start < sub_end < c_end)):
+            lo = max(sub_start, c_start)
+            hi = min(sub_end, c_end)
+        if lo == 0 and hi == 0:
+            return None, c_end
+        flat_off = (lo - c_start) * 8 // bits
+        flat_n = (hi - lo) * 8 // bits
+        # getNonFlatSubViewOffsetAndShape (:729-755): slice the outermost dim that covers the range
+        dims = list(ctype.shape)
+        off = [0] * len(dims)
+        shp = list(dims)
+        prev_stride, num, d = 1, 1, len(dims) - 1
+        while d >= 0:
+            num *= dims[d]
+            if num >= flat_n + flat_off:
+                break
+            prev_stride = num
+            d -= 1
+        off[d] = flat_off // prev_stride
+        covered = off[d] * prev_stride
+        shp[d] = -(-(flat_n + flat_off) // prev_stride) - off[d]
+        for k in range(d):
+            shp[k] = 1
+        if shp != dims:
+            attr = cls._with(attr, attr.setup.subview(off, shp))
+        _, nbytes = cls._type_of(attr)
+        flat_total = nbytes * 8 // bits
+        if not (flat_total == flat_n and flat_off - covered == 0):
+            attr = cls._with(attr, attr.setup.reshape([1, 1, 1, flat_total])
+                             .subview([0, 0, 0, flat_off - covered], [1, 1, 1, flat_n]))
+        return attr, c_end
+
+    # -- folding ----------------------------------------------------------------------------------------------
+    def fold(self, library):
+        """vf_fuse over the parts, then whatever stayed behind the Fuse through vf_fold on the fused bytes."""
+        need = int(np.prod(self.fused_type.shape)) * abi.DTYPE_BITS[self.fused_type.elem.dtype] // 8
+        raw, _ = library.fuse(self.parts(), need)
+        if not self.trailing.names():
+            return Folded(self.fused_type, False, np.ascontiguousarray(raw), len(raw))
+        base = np.zeros(need, np.uint8)
+        base[:len(raw)] = raw
+        return ContentAttr(base.view(abi.DTYPE_NUMPY[self.fused_type.elem.dtype]), self.fused_type, self.trailing).fold(library)
