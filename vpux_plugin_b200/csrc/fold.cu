@@ -947,17 +947,49 @@ uint64_t copy_folded(vf_ctx* ctx, const Folded& f, void* dst, uint64_t dst_bytes
     return w;
 }
 
+// Fused jobs of a batch that wait for their shared launch (vf_fold_batch): the uploaded bases stay alive until then.
+struct FusedBatch {
+    std::vector<FusedJob> jobs;
+    std::vector<DContent> bases;
+    std::vector<int> owner;
+};
+constexpr uint64_t kFoldDeferred = ~uint64_t(0);
+
 // ContentAttr::fold() + Content::copyTo() of one constant, enqueued on the context's stream (the caller owns the
-// call scope and decides when the host waits). Returns the bytes written.
+// call scope and decides when the host waits). Returns the bytes written. A list that starts with a parameterised
+// Quantize and that a single-pass kernel covers (fused_prepare_given) runs as ONE launch instead of one launch and
+// one intermediate buffer per transformation; with `batch` such a job is only collected (kFoldDeferred is
+// returned) so that the jobs of a group share their launches.
 uint64_t fold_one(vf_ctx* ctx, const vf_content& base, const vf_transform* t, int n, void* dst, uint64_t dst_bytes, int dst_mem_kind,
-                  vf_tensor_type* out_type, double* scales_buf, int64_t* zps_buf, int64_t params_cap, vf_stats* stats) {
+                  vf_tensor_type* out_type, double* scales_buf, int64_t* zps_buf, int64_t params_cap, vf_stats* stats,
+                  FusedBatch* batch = nullptr, int owner = 0) {
     DContent cur = upload_base(ctx, base, stats);
     // the destination doubles as the last transformation's output buffer when it is device memory that does
     // not overlap the base content
     const char* b0 = static_cast<const char*>(base.data);
     const char* d0 = static_cast<const char*>(dst);
-    const bool direct = dst && dst_mem_kind == VF_MEM_DEVICE &&
-                        (base.mem_kind != VF_MEM_DEVICE || d0 + dst_bytes <= b0 || b0 + base.nbytes <= d0);
+    const bool disjoint = base.mem_kind != VF_MEM_DEVICE || dst_mem_kind != VF_MEM_DEVICE || d0 + dst_bytes <= b0 || b0 + base.nbytes <= d0;
+    if (!(ctx->opt_flags & VF_OPT_DISABLE_FUSION) && n > 0 && disjoint) {
+        FusedJob fj;
+        Type ot;
+        if (fused_prepare_given(ctx, cur, t, n, dst, dst_bytes, dst_mem_kind, fj, &ot)) {
+            ot.export_to(out_type, scales_buf, zps_buf, params_cap);
+            if (stats) stats->fused = 1;
+            if (batch) {
+                batch->jobs.push_back(std::move(fj));
+                batch->bases.push_back(std::move(cur));
+                batch->owner.push_back(owner);
+                return kFoldDeferred;
+            }
+            std::vector<FusedJob> one;
+            one.push_back(std::move(fj));
+            fused_launch(ctx, one, 0, 1);
+            uint64_t w = 0;
+            fused_finish(ctx, one[0], &w, stats);
+            return w;
+        }
+    }
+    const bool direct = dst && dst_mem_kind == VF_MEM_DEVICE && disjoint;
     struct Hint {
         vf_ctx* c;
         ~Hint() { c->final_dst = nullptr; }
@@ -1020,21 +1052,57 @@ int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch
             }
         }
         CallScope scope(ctx, stats);
+        // Jobs a single-pass kernel covers are collected while their group is walked and launched together when
+        // the group closes: compatible jobs share one launch, and two lists over the same constant (codes and
+        // dequantized copy) one pass.
+        FusedBatch fused;
+        bool all_device = true;
+        for (int j = 0; j < njobs; ++j) all_device &= jobs[j].base.mem_kind == VF_MEM_DEVICE && jobs[j].dst_mem_kind == VF_MEM_DEVICE;
+        auto launch_fused = [&]() {
+            if (fused.jobs.empty()) return;
+            fused_merge_pairs(fused.jobs);
+            fused_launch(ctx, fused.jobs, 0, fused.jobs.size());
+            for (size_t k = 0; k < fused.jobs.size(); ++k) {
+                uint64_t w = 0;
+                fused_finish(ctx, fused.jobs[k], &w, stats);
+                jobs[fused.owner[k]].dst_written = w;
+                jobs[fused.owner[k]].status = VF_OK;
+            }
+            fused.jobs.clear();
+            fused.bases.clear();
+            fused.owner.clear();
+        };
         auto run = [&](int j, int group) {
             vf_fold_job& jb = jobs[j];
             jb.group = group;
             try {
-                jb.dst_written = fold_one(ctx, jb.base, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, nullptr, nullptr, nullptr, 0, stats);
+                const uint64_t w = fold_one(ctx, jb.base, jb.t, jb.n, jb.dst, jb.dst_bytes, jb.dst_mem_kind, nullptr, nullptr, nullptr, 0,
+                                            stats, &fused, j);
+                if (w == kFoldDeferred) return;
+                jb.dst_written = w;
                 jb.status = VF_OK;
             } catch (const Error& e) {
                 jb.status = e.code;
+                try {  // the jobs collected before this one still run, as they would have in list order
+                    launch_fused();
+                } catch (const Error&) {
+                }
                 raise(e.code, "job %d: %s", j, e.what());
             }
         };
         // What the kernels of the jobs enqueued so far have found is read here, once per group: the host waits
         // for the stream, so everything those jobs allocated is free again before the next group starts.
+        bool last_wait = false;
         auto wait = [&](const char* what, int index) {
+            launch_fused();
             ++bs.synchronisations;
+            if (last_wait && all_device && (ctx->opt_flags & VF_OPT_ASYNC)) {
+                // pipelined batches over device memory: what the last group's kernels report is returned by the
+                // context's next synchronising call
+                VF_CUDA(cudaGetLastError());
+                ctx->deferred = true;
+                return;
+            }
             try {
                 flags_check(ctx);
                 ctx->table_used = 0;  // nothing is in flight: the job-table area starts over
@@ -1053,13 +1121,17 @@ int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch
             run(j, VF_GROUP_TINY);
             ++bs.tiny;
         }
-        if (bs.tiny) wait("the constants within the tiny threshold", -1);
+        if (bs.tiny) {
+            last_wait = big.empty();
+            wait("the constants within the tiny threshold", -1);
+        }
         // the others in order (constant_folding.cpp:113-158)
         size_t at = 0;
         while (at < big.size()) {
             const int j = big[at];
             if (jobs[j].max_intermediate > threshold) {
                 run(j, VF_GROUP_ALONE);
+                last_wait = at + 1 == big.size();
                 wait("job", j);
                 ++bs.alone;
                 ++at;
@@ -1073,6 +1145,7 @@ int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch
                 ++at;
             }
             bs.max_group_bytes = std::max(bs.max_group_bytes, in_flight);
+            last_wait = at == big.size();
             wait("group", group);
         }
         if (batch_stats) *batch_stats = bs;

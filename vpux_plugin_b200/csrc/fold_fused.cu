@@ -2,6 +2,7 @@
 // that upstream passes build for weights (Quantize [+ Reorder<NHWC>] [+ PadWithZero] | [+ BitPack]) and maps
 // them onto the job tables of kernels_rowquant.cu. Anything else is declined and takes the general path.
 #include <algorithm>
+#include <cstring>
 
 #include "fused.h"
 
@@ -155,10 +156,148 @@ bool fused_prepare(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec,
     return job.kind != 0;
 }
 
+namespace {
+
+bool same_params(const vf_elem_type& a, const vf_elem_type& b) {
+    if (a.kind != b.kind || a.dtype != b.dtype || a.axis != b.axis || a.qmin != b.qmin || a.qmax != b.qmax || a.nparams != b.nparams ||
+        a.expressed != b.expressed)
+        return false;
+    if (a.scales != b.scales && std::memcmp(a.scales, b.scales, size_t(a.nparams) * sizeof(double)) != 0) return false;
+    if (a.zps != b.zps && std::memcmp(a.zps, b.zps, size_t(a.nparams) * sizeof(int64_t)) != 0) return false;
+    return true;
+}
+
+}  // namespace
+
+bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* t, int n, void* dst, uint64_t dst_bytes,
+                         int dst_kind, FusedJob& job, Type* out_type) {
+    if (n < 1 || base.splat || base.type.elem.quantized()) return false;
+    if (base.storage != VF_DT_F32 && base.storage != VF_DT_F16 && base.storage != VF_DT_BF16) return false;
+    if (base.storage != base.type.elem.dtype) return false;
+    if (base.type.order != identity_order(base.type.rank) || base.type.numel() == 0) return false;
+    int i = 0;
+    Type ty = base.type;
+    bool splat = false;
+    if (t[i].kind == VF_T_RESHAPE && n >= 2) {  // a leading Reshape only renames the units
+        if (t[i].rank != 2) return false;
+        ty = infer_one(ty, splat, t[i], splat);
+        ++i;
+    }
+    if (t[i].kind != VF_T_QUANTIZE) return false;
+    const vf_elem_type& q = t[i].elem;
+    if (q.kind != VF_ELEM_QUANT_PER_AXIS || q.axis != 0 || (q.dtype != VF_DT_I8 && q.dtype != VF_DT_U8)) return false;
+    if (!q.scales || !q.zps || q.nparams != ty.shape[0] || q.qmax <= q.qmin || q.qmax - q.qmin > 255) return false;
+    double lo, hi;
+    dtype_int_limits(q.dtype, lo, hi);
+    if (double(q.qmin) < lo || double(q.qmax) > hi || !tail_is_identity(q.qmin, q.qmax)) return false;
+    for (int64_t k = 0; k < q.nparams; ++k)  // anything but a positive finite scale takes the general path
+        if (!(q.scales[k] > 0.0) || !(q.scales[k] < 1.0e300)) return false;
+    const int qi = i;
+    ty = infer_one(ty, splat, t[i], splat);
+    ++i;
+
+    RowQuantArgs& a = job.a;
+    a = RowQuantArgs{};
+    a.in = base.d;
+    a.in_dt = base.storage;
+    a.range_mode = VF_RANGE_MINMAX;
+    a.qmin = q.qmin;
+    a.qmax = q.qmax;
+    a.out_signed = q.dtype == VF_DT_I8;
+    a.rows = ty.shape[0];
+    a.cols = ty.numel() / a.rows;
+    a.rows_pad = a.rows;
+    uint64_t out_bytes = uint64_t(ty.numel());
+    bool to_dequant = false;
+    if (i < n && t[i].kind == VF_T_BIT_PACK) {
+        if (t[i].width != 4 || ty.rank != 2 || (a.cols != 32 && a.cols != 64 && a.cols != 128) || ty.numel() % 2 != 0) return false;
+        a.group = a.cols;  // every row is one group: the per-group kernel with one group per unit
+        a.pack4 = 1;
+        out_bytes = uint64_t(ty.numel() / 2);
+        ty = infer_one(ty, splat, t[i], splat);
+        ++i;
+    } else if (i + 1 < n && t[i].kind == VF_T_CAST_ELEM_TYPE && t[i + 1].kind == VF_T_DEQUANTIZE) {
+        if (!same_params(q, t[i].elem)) return false;
+        const int ddt = q.expressed;
+        if (ddt != VF_DT_F16 && ddt != VF_DT_F32 && ddt != VF_DT_BF16) return false;
+        ty = infer_one(ty, splat, t[i], splat);
+        ty = infer_one(ty, splat, t[i + 1], splat);
+        a.dequant_dt = ddt;
+        to_dequant = true;
+        i += 2;
+    } else if (i < n && t[i].kind == VF_T_REORDER) {
+        if (ty.rank != 4 || t[i].order != VF_ORDER_NHWC) return false;
+        a.ic = ty.shape[1];
+        a.khw = ty.shape[2] * ty.shape[3];
+        a.ic_pad = a.ic;
+        ty = infer_one(ty, splat, t[i], splat);
+        ++i;
+        if (i < n && t[i].kind == VF_T_PAD_WITH_ZERO) {
+            const vf_transform& p = t[i];
+            if (p.rank != 4 || p.a[0] || p.a[1] || p.a[2] || p.a[3] || p.b[2] || p.b[3] || p.b[0] < 0 || p.b[1] < 0) return false;
+            a.rows_pad = a.rows + p.b[0];
+            a.ic_pad = a.ic + p.b[1];
+            ty = infer_one(ty, splat, t[i], splat);
+            ++i;
+        }
+        if (a.khw == 1 && a.ic_pad == a.ic) a.khw = 0;
+        out_bytes = uint64_t(a.rows_pad) * uint64_t(a.khw > 0 ? a.khw * a.ic_pad : a.cols);
+    }
+    if (i != n) return false;
+    (void)qi;
+
+    if (!dst) raise(VF_ERR_INVALID_ARG, "dst is NULL");
+    job.dst_is_dequant = to_dequant;
+    job.out_bytes = to_dequant ? 0 : out_bytes;
+    job.dq_bytes = to_dequant ? uint64_t(ty.numel()) * uint64_t(dtype_bits(a.dequant_dt) / 8) : 0;
+    const uint64_t need = to_dequant ? job.dq_bytes : out_bytes;
+    // probe which kernel would take the job before anything is allocated (pointers only matter for alignment)
+    a.codes = to_dequant ? nullptr : (dst_kind == VF_MEM_DEVICE ? dst : reinterpret_cast<void*>(uintptr_t(256)));
+    a.dequant = to_dequant ? (dst_kind == VF_MEM_DEVICE ? dst : reinterpret_cast<void*>(uintptr_t(256))) : nullptr;
+    a.given_scales = reinterpret_cast<const double*>(uintptr_t(256));
+    if (rowquant_kind(a) == 0) return false;
+    if (dst_bytes < need) raise(VF_ERR_BUFFER_TOO_SMALL, "Byte sizes of the target buffer '%llu' is smaller then storage buffer '%llu'", (unsigned long long)dst_bytes, (unsigned long long)need);
+    if (to_dequant) a.dequant = job.td.bind(ctx, dst, dst_kind, need);
+    else a.codes = job.tc.bind(ctx, dst, dst_kind, need);
+    job.gscales = DBuf(ctx, size_t(q.nparams) * 8);
+    job.gzps = DBuf(ctx, size_t(q.nparams) * 8);
+    copy_in(ctx, job.gscales.p, q.scales, size_t(q.nparams) * 8, VF_MEM_HOST);
+    copy_in(ctx, job.gzps.p, q.zps, size_t(q.nparams) * 8, VF_MEM_HOST);
+    a.given_scales = job.gscales.as<double>();
+    a.given_zps = job.gzps.as<int64_t>();
+    job.h_scales = q.scales;
+    job.h_zps = q.zps;
+    job.n_params = q.nparams;
+    job.kind = rowquant_kind(a);
+    if (out_type) *out_type = ty;
+    return job.kind != 0;
+}
+
+void fused_merge_pairs(std::vector<FusedJob>& jobs) {
+    for (size_t i = 0; i < jobs.size(); ++i) {
+        FusedJob& c = jobs[i];  // candidate that writes codes only
+        if (c.merged || c.kind != 2 || !c.a.given_scales || c.dst_is_dequant || c.a.dequant) continue;
+        for (size_t k = 0; k < jobs.size(); ++k) {
+            FusedJob& d = jobs[k];
+            if (k == i || d.merged || d.kind != 2 || !d.dst_is_dequant || d.a.codes) continue;
+            if (d.a.in != c.a.in || d.a.rows != c.a.rows || d.a.cols != c.a.cols || d.a.qmin != c.a.qmin || d.a.qmax != c.a.qmax ||
+                d.a.in_dt != c.a.in_dt || d.n_params != c.n_params)
+                continue;
+            if (d.h_scales != c.h_scales && std::memcmp(d.h_scales, c.h_scales, size_t(c.n_params) * 8) != 0) continue;
+            if (d.h_zps != c.h_zps && std::memcmp(d.h_zps, c.h_zps, size_t(c.n_params) * 8) != 0) continue;
+            c.a.dequant = d.a.dequant;
+            c.a.dequant_dt = d.a.dequant_dt;
+            d.merged = true;
+            break;
+        }
+    }
+}
+
 void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end) {
     // jobs are independent, so they are regrouped: all jobs with the same kernel and launch-uniform parameters
     // share one launch, wherever they sit in the batch
     std::vector<char> done(end - begin, 0);
+    for (size_t i = begin; i < end; ++i) done[i - begin] = jobs[i].merged ? 1 : 0;
     std::vector<RowQuantArgs> table;
     for (size_t i = begin; i < end; ++i) {
         if (done[i - begin]) continue;
@@ -180,7 +319,7 @@ void fused_finish(vf_ctx* ctx, FusedJob& job, uint64_t* dst_written, vf_stats* s
     job.t16.flush(ctx, stats);
     job.t4.flush(ctx, stats);
     job.td.flush(ctx, stats);
-    if (dst_written) *dst_written = job.out_bytes;
+    if (dst_written) *dst_written = job.dst_is_dequant ? job.dq_bytes : job.out_bytes;
     if (stats) stats->bytes_out += job.out_bytes + job.dq_bytes;
 }
 

@@ -23,11 +23,31 @@ struct FusedJob {
     int kind = 0;  // rowquant_kind
     OutStage tc, ts, tz, t16, t4, td;
     uint64_t out_bytes = 0, dq_bytes = 0;
+    // parameterised Quantize (fused_prepare_given): device copies of the attribute's scales / zero points, where
+    // the host arrays are (to recognise two lists over the same constant), and which output the destination is
+    DBuf gscales, gzps;
+    const double* h_scales = nullptr;
+    const int64_t* h_zps = nullptr;
+    int64_t n_params = 0;
+    bool dst_is_dequant = false;  // the list ends in Dequantize: the destination receives the dequantized copy
+    bool merged = false;          // this job's output is written by another job's launch entry (fused_merge_pairs)
 };
 
 // Fills `job` when (spec, t[0..n)) is a pattern the fused kernels cover; false otherwise (nothing launched).
 bool fused_prepare(vf_ctx* ctx, const DContent& base, const vf_quant_spec& spec, const vf_transform* t, int n,
                    void* dst, uint64_t dst_bytes, int dst_kind, const vf_quant_outputs* outs, FusedJob& job);
+// The same for the list shapes a compiler pass builds, where the Quantize attribute carries its parameters
+// (attributes/quantize.cpp:108-212):
+//   [Quantize<per-axis(0)>]                                         -> codes
+//   [Quantize<per-axis(0)>, Reorder<NHWC> [, PadWithZero]]          -> codes in OYXI order, channels padded
+//   [[Reshape<[units, G]>,] Quantize<per-axis(0)>, BitPack<4>]      -> packed codes (G = 32 / 64 / 128)
+//   [Quantize<per-axis(0)>, CastElemType<the same type>, Dequantize]-> the dequantized copy in the expressed type
+// `out_type` receives the type of the folded content. False: not covered, nothing was launched or allocated.
+bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* t, int n, void* dst, uint64_t dst_bytes,
+                         int dst_kind, FusedJob& job, Type* out_type);
+// Two jobs of a batch that quantize the same constant with the same parameters, one for the codes and one for
+// the dequantized copy, become one entry of the launch: the input is read once for both outputs.
+void fused_merge_pairs(std::vector<FusedJob>& jobs);
 // Launches jobs[begin, end): consecutive compatible jobs share one kernel launch.
 void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end);
 // Copies host-bound outputs out (asynchronously on the context's stream) and reports sizes.

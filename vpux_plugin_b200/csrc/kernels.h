@@ -168,6 +168,11 @@ struct RowQuantArgs {
     uint8_t* zps_u4;
     void* dequant;
     int dequant_dt;
+    // parameters supplied by the caller (the Quantize attribute's scales / zero points, device arrays with one
+    // entry per unit) instead of derived from the data; NULL: derive them. `codes` may then be NULL when only
+    // the dequantized copy is wanted (row kernel).
+    const double* given_scales;
+    const int64_t* given_zps;
     int64_t unit_begin;      // filled by launch_rowquant_batch: index of this job's first chunk / row in the launch
 };
 // Launches all `jobs` (same kind, pairwise rowquant_compatible) with ONE kernel over a device job table.

@@ -3,15 +3,21 @@
 // input. All of them are bandwidth-bound: the unit (group chunk or row) is staged in shared memory with
 // 16-byte asynchronous copies (cp.async), statistics run on packed 16-bit pairs, the quantization sweep
 // re-reads shared memory, stores are 16 bytes per lane. One launch processes a whole table of tensors so that
-// small tensors do not pay a launch and a tail each.
+// small tensors do not pay a launch and a tail each. The per-unit parameters are either derived from the
+// unit's own range or supplied by the caller (the Quantize attribute's scales and zero points).
 //
-// Arithmetic contract: codes equal the reference's fakeQuantize chain bit for bit. The per-element fast path
-// evaluates  t = fma(x, inv, c)  with inv = fl((L-1)/range), c = fl(-inLow*inv)  instead of the reference's
-// fl(fl((x-inLow)/range) * (L-1)). Six roundings separate the two (constant, reciprocal, fma; subtraction,
-// division, multiplication), each at most 2^-24 * (L-1) in absolute terms, plus one more when qmin is folded
-// into the constant: |t - reference| < 4.2e-7 * L. Whenever t is further than guard = 8e-7 * L from a rounding
-// boundary (x.5) both round to the same integer; elements inside the guard band (2e-4 wide for 8-bit ranges,
-// 1.3e-5 for 4-bit) are recomputed with the exact operation sequence.
+// Arithmetic contract: codes equal the reference's fakeQuantize chain bit for bit. With the ideal index
+//   T = x / scale + (zp - qmin)
+// the reference evaluates e = fl(fl(fl(x - inLow) / range) * (L-1)) on the fp32 constants inLow = fl((qmin-zp)*scale),
+// range = fl(inHigh - inLow) and rounds e half away from zero. The fast path evaluates ONE fused multiply-add
+//   mm = fma(x, inv, magic + K),   inv = fl((L-1) / range),  magic = 1.5 * 2^23,  K an integer constant
+// whose product is exact and whose sum is rounded once, to an integer (the ulp at magic is 1): the low bits of
+// mm hold round(x * inv) + K. Against e the index x * inv + (zp - qmin) differs by at most 7 * 2^-24 * L
+// (one rounding each in inv, inLow, the subtraction, the division and the multiplication, two in range),
+// i.e. 4.2e-7 * L, so whenever x * inv is further than guard = 8e-7 * L from a rounding boundary (n + 0.5)
+// both round to the same integer. The distance is the residual r = x * inv - round(x * inv), one more exact
+// fused multiply-add; elements inside the guard band (2e-4 wide for 8-bit ranges, 1.3e-5 for 4-bit) are
+// recomputed with the reference's own operation sequence.
 #include <algorithm>
 #include <vector>
 
@@ -28,7 +34,7 @@ constexpr float kGuardPerLevel = 8.0e-7f;
 
 struct UnitQ {  // per-unit constants
     float inv;     // fl((L-1) / range)
-    float c;       // fl(-inLow * inv) (+ qmin where noted)
+    float zq;      // float(zp - qmin): index n = round(x * inv) + zq
     float in_low;  // exact path
     float range;   // fl(inHigh - inLow)
 };
@@ -38,9 +44,18 @@ struct LaunchParams {  // uniform over all jobs of one launch
     int qmin, qmax, lm1;
     int dequant_dt;
     int njobs;
+    int given;            // parameters come from the jobs' given_scales / given_zps
     float thr;            // 0.5 - guard: largest rounding residual the fast path accepts
     int64_t total_units;  // chunks (k_group) or rows (k_row / k_conv) over all jobs
 };
+
+__device__ __forceinline__ void unit_consts(double scale, long long zp, const LaunchParams& p, UnitQ& u) {
+    u.in_low = dequantize_exact(p.qmin, scale, zp);
+    const float in_high = dequantize_exact(p.qmax, scale, zp);
+    u.range = __fsub_rn(in_high, u.in_low);
+    u.inv = __fdiv_rn(float(p.lm1), u.range);
+    u.zq = float(zp - p.qmin);
+}
 
 // Per-unit parameters from the unit's range.
 __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchParams& p, double& scale, long long& zp,
@@ -58,16 +73,20 @@ __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchPara
         zp = 0;
     }
     zp = zp < p.qmin ? p.qmin : (zp > p.qmax ? p.qmax : zp);
-    u.in_low = dequantize_exact(p.qmin, scale, zp);
-    const float in_high = dequantize_exact(p.qmax, scale, zp);
-    u.range = __fsub_rn(in_high, u.in_low);
-    u.inv = __fdiv_rn(float(p.lm1), u.range);
-    u.c = __fmul_rn(-u.in_low, u.inv);
+    unit_consts(scale, zp, p, u);
+}
+
+// Supplied parameters need not cover the data. The fast path has no clamp, so it is used only when every
+// element's index stays inside [-0.45, L-1 + 0.45] (anything closer to +-0.5 is in the guard band anyway) and
+// the zero point lies in the storage range; other units take the exact sequence for every element.
+__device__ __forceinline__ bool unit_fits(const UnitQ& u, float mn, float mx, long long zp, const LaunchParams& p) {
+    const float lo = __fmaf_rn(mn, u.inv, u.zq), hi = __fmaf_rn(mx, u.inv, u.zq);
+    return zp >= p.qmin && zp <= p.qmax && u.range > 0.f && lo >= -0.45f && hi <= float(p.lm1) + 0.45f;
 }
 
 // The exact operation sequence of fakeQuantize's middle branch, as an index n in [0, L-1]. The first two
-// branches (x <= inLow -> qLow, x > inHigh -> qHigh) coincide with the clamp: x <= inLow gives a <= 0,
-// x > inHigh gives fl(x - inLow) >= range.
+// branches (x <= inLow -> qLow, x > inHigh -> qHigh) coincide with the clamp for any x: x <= inLow gives
+// fl(x - inLow) <= 0, x > inHigh gives fl(x - inLow) >= range (rounding is monotonic).
 __device__ __noinline__ int quant_index_exact(float x, float in_low, float range, int lm1) {
     const float a = __fsub_rn(x, in_low);
     float e = __fdiv_rn(a, range);
@@ -132,94 +151,117 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, boo
     const int n = valid ? 16 : 0;  // src-size 0: the 16 destination bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gsrc), "r"(n) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {  // at most N committed groups still in flight
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+    cp_async_commit();
+    cp_async_wait<0>();
 }
 
-// Fast quantization of the eight elements of one vector: returns the eight rounded values as floats with the
-// magic constant still added (bit pattern = kMagicBits + n) and whether any of them fell into the guard band.
-// The largest rounding residual is tracked with max (no per-element branch); one comparison per vector.
-// quant8_worst folds the vector's largest residual into `worst`, so a caller can test several vectors at once.
-template <typename InT>
-__device__ __forceinline__ void quant8_worst(const uint4& d, float inv, float c, float* m, float& worst) {
-    // Packed two-wide fp32 instructions (sm_100): each is the same IEEE round-to-nearest operation on both
-    // halves, so the results equal the scalar sequence bit for bit at half the issue slots. t - s is formed
-    // as fma(s, -1, t): the product is exact, so it rounds once like the subtraction.
+// ---- the fast quantizer on packed pairs --------------------------------------------------------------------
+// Packed two-wide fp32 instructions (sm_100): each is the same IEEE round-to-nearest operation on both halves,
+// so the results equal the scalar sequence bit for bit at half the issue slots.
+struct PairQ {  // launch / unit constants duplicated into both halves
+    float2 inv, ninv;  // inv, -inv
+    float2 cm, ncm;    // magic + K, -(magic + K)
+};
+__device__ __forceinline__ float2 dup(float v) {
+    return make_float2(v, v);
+}
+__device__ __forceinline__ PairQ pair_consts(float inv, float k) {
+    PairQ q;
+    const float cm = __fadd_rn(kMagic, k);  // exact: |k| is a small integer
+    q.inv = dup(inv);
+    q.ninv = dup(-inv);
+    q.cm = dup(cm);
+    q.ncm = dup(-cm);
+    return q;
+}
+// One pair: mm = magic + K + round(x * inv) (as a float), s = round(x * inv), and the largest |residual| so far.
+// The residual is formed with the sign flipped (s - x * inv): the product is exact, one rounding.
+__device__ __forceinline__ void quant2(const float2 x, const PairQ& q, float2& mm, float2& s, float& worst) {
+    mm = __ffma2_rn(x, q.inv, q.cm);
+    s = __fadd2_rn(mm, q.ncm);  // exact
+    const float2 r = __ffma2_rn(x, q.ninv, s);
+    worst = fmaxf(worst, fmaxf(fabsf(r.x), fabsf(r.y)));
+}
+
+// Eight elements -> eight code bytes. K = zp, so the low byte of mm is the code in two's complement. `s` (optional)
+// receives code - zp of every element as floats, in element order.
+template <typename InT, bool WANT_S>
+__device__ __forceinline__ uint2 quant8_bytes(const uint4& d, const PairQ& q, float& worst, float2* s_out) {
     const uint32_t w[4] = {d.x, d.y, d.z, d.w};
-    const float2 inv2 = make_float2(inv, inv), c2 = make_float2(c, c);
-    const float2 mg = make_float2(kMagic, kMagic), nmg = make_float2(-kMagic, -kMagic), neg1 = make_float2(-1.f, -1.f);
+    uint32_t b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 x = P2<InT>::both(w[i]);
-        const float2 t = __ffma2_rn(x, inv2, c2);
-        const float2 mm = __fadd2_rn(t, mg);
-        const float2 s = __fadd2_rn(mm, nmg);
-        const float2 r = __ffma2_rn(s, neg1, t);
-        m[2 * i] = mm.x;
-        m[2 * i + 1] = mm.y;
-        worst = fmaxf(worst, fmaxf(fabsf(r.x), fabsf(r.y)));
+        float2 mm, s;
+        quant2(P2<InT>::both(w[i]), q, mm, s, worst);
+        b[i] = __byte_perm(__float_as_uint(mm.x), __float_as_uint(mm.y), 0x0040);
+        if (WANT_S) s_out[i] = s;
     }
-}
-template <typename InT>
-__device__ __forceinline__ bool quant8(const uint4& d, float inv, float c, float thr, float* m) {
-    float worst = 0.f;
-    quant8_worst<InT>(d, inv, c, m, worst);
-    return worst > thr;
+    return make_uint2(__byte_perm(b[0], b[1], 0x5410), __byte_perm(b[2], b[3], 0x5410));
 }
 
-// Repair of a vector that has an element in the guard band (rare): every element is re-evaluated, those inside
-// the band with the exact sequence. Everything travels by value so that the caller's registers never need an
-// address; returns the eight indices n (0..255) as bytes. `bias` is what the caller folded into c.
-__device__ __forceinline__ uint32_t quant1_fix(float x, float inv, float c, float thr, float in_low, float range,
-                                               int lm1, int bias) {
-    const float t = __fmaf_rn(x, inv, c);
-    const float m = __fadd_rn(t, kMagic);
-    const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
-    int n = (__float_as_int(m) - kMagicBits) - bias;
-    if (fabsf(resid) > thr) n = quant_index_exact(x, in_low, range, lm1);
+// Eight elements -> one word of eight nibbles, element 0 in the low nibble (BitPack<4>). The unsigned index
+// n = round(x * inv) + zq of an even element (K = 17 zq) and sixteen times the rounded product of its odd
+// neighbour (K = zq) are added in floating point: the low byte of the sum is n_even + 16 n_odd.
+template <typename InT>
+__device__ __forceinline__ uint32_t quant8_nibbles(const uint4& d, const PairQ& qa, const PairQ& qb, float& worst) {
+    const float2 p16 = dup(16.f);
+    const float2 e01 = P2<InT>::both(d.x), e23 = P2<InT>::both(d.y), e45 = P2<InT>::both(d.z), e67 = P2<InT>::both(d.w);
+    float2 mma, sa, mmb, sb;
+    quant2(make_float2(e01.x, e23.x), qa, mma, sa, worst);
+    quant2(make_float2(e01.y, e23.y), qb, mmb, sb, worst);
+    const float2 c0 = __ffma2_rn(sb, p16, mma);  // exact: small integers on top of magic
+    quant2(make_float2(e45.x, e67.x), qa, mma, sa, worst);
+    quant2(make_float2(e45.y, e67.y), qb, mmb, sb, worst);
+    const float2 c1 = __ffma2_rn(sb, p16, mma);
+    const uint32_t lo = __byte_perm(__float_as_uint(c0.x), __float_as_uint(c0.y), 0x0040);
+    const uint32_t hi = __byte_perm(__float_as_uint(c1.x), __float_as_uint(c1.y), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+// Repair of a vector that has an element in the guard band (rare), and the path of units the fast evaluation
+// does not cover (`all`): every element is re-evaluated, those inside the band (or all) with the exact sequence.
+// Everything travels by value so that the caller's registers never need an address; returns the eight indices
+// n (0 .. L-1) as bytes.
+__device__ __forceinline__ uint32_t quant1_fix(float x, const UnitQ u, float thr, int lm1, bool all) {
+    const float cm = __fadd_rn(kMagic, u.zq);
+    const float m = __fmaf_rn(x, u.inv, cm);
+    const float s = __fsub_rn(m, cm);
+    const float resid = __fmaf_rn(x, -u.inv, s);
+    int n = __float_as_int(m) - kMagicBits;
+    if (all || !(fabsf(resid) <= thr)) n = quant_index_exact(x, u.in_low, u.range, lm1);
     return uint32_t(min(max(n, 0), lm1));
 }
 template <typename InT>
-__device__ __noinline__ uint2 quant8_fix_bytes(uint4 d, float inv, float c, float thr, float in_low, float range,
-                                               int lm1, int bias) {
+__device__ __noinline__ uint2 quant8_fix_idx(uint4 d, UnitQ u, float thr, int lm1, bool all) {
     uint2 r;
-    r.x = quant1_fix(P2<InT>::lo(d.x), inv, c, thr, in_low, range, lm1, bias) |
-          (quant1_fix(P2<InT>::hi(d.x), inv, c, thr, in_low, range, lm1, bias) << 8) |
-          (quant1_fix(P2<InT>::lo(d.y), inv, c, thr, in_low, range, lm1, bias) << 16) |
-          (quant1_fix(P2<InT>::hi(d.y), inv, c, thr, in_low, range, lm1, bias) << 24);
-    r.y = quant1_fix(P2<InT>::lo(d.z), inv, c, thr, in_low, range, lm1, bias) |
-          (quant1_fix(P2<InT>::hi(d.z), inv, c, thr, in_low, range, lm1, bias) << 8) |
-          (quant1_fix(P2<InT>::lo(d.w), inv, c, thr, in_low, range, lm1, bias) << 16) |
-          (quant1_fix(P2<InT>::hi(d.w), inv, c, thr, in_low, range, lm1, bias) << 24);
+    r.x = quant1_fix(P2<InT>::lo(d.x), u, thr, lm1, all) | (quant1_fix(P2<InT>::hi(d.x), u, thr, lm1, all) << 8) |
+          (quant1_fix(P2<InT>::lo(d.y), u, thr, lm1, all) << 16) | (quant1_fix(P2<InT>::hi(d.y), u, thr, lm1, all) << 24);
+    r.y = quant1_fix(P2<InT>::lo(d.z), u, thr, lm1, all) | (quant1_fix(P2<InT>::hi(d.z), u, thr, lm1, all) << 8) |
+          (quant1_fix(P2<InT>::lo(d.w), u, thr, lm1, all) << 16) | (quant1_fix(P2<InT>::hi(d.w), u, thr, lm1, all) << 24);
     return r;
 }
-
-// Overwrites m[] with the patterns kMagicBits + n + bias of the repaired vector.
-#define VF_QUANT8_FIX(InT, d, u, thr, lm1, bias, m)                                                        \
-    do {                                                                                                   \
-        const uint2 ex_ = quant8_fix_bytes<InT>(d, (u).inv, (u).c, thr, (u).in_low, (u).range, lm1, bias); \
-        _Pragma("unroll") for (int k_ = 0; k_ < 4; ++k_) {                                                 \
-            m[k_] = __int_as_float(kMagicBits + int((ex_.x >> (8 * k_)) & 0xFFu) + (bias));                \
-            m[4 + k_] = __int_as_float(kMagicBits + int((ex_.y >> (8 * k_)) & 0xFFu) + (bias));            \
-        }                                                                                                  \
-    } while (0)
-
-// eight patterns (kMagicBits + n) -> eight nibbles of n in one word, element 0 in the low nibble (BitPack<4>)
-__device__ __forceinline__ uint32_t pack_nibbles(const float* m) {
-    // summed as a tree (three dependent multiply-adds instead of seven)
-    const uint32_t a = __float_as_uint(m[0]) + (__float_as_uint(m[1]) << 4);
-    const uint32_t b = __float_as_uint(m[2]) + (__float_as_uint(m[3]) << 4);
-    const uint32_t c = __float_as_uint(m[4]) + (__float_as_uint(m[5]) << 4);
-    const uint32_t d = __float_as_uint(m[6]) + (__float_as_uint(m[7]) << 4);
-    const uint32_t w = (a + (b << 8)) + ((c + (d << 8)) << 16);
-    constexpr uint32_t kC = uint32_t(kMagicBits) * 0x11111111u;  // the magic part of the sum
-    return w - kC;
+// index bytes -> code bytes (n + qmin in every byte, modulo 256)
+__device__ __forceinline__ uint32_t idx_to_codes4(uint32_t idx, int qmin) {
+    const uint32_t q = (uint32_t(qmin) & 0xFFu) * 0x01010101u;
+    // byte-wise addition without carries between bytes
+    return ((idx & 0x7F7F7F7Fu) + (q & 0x7F7F7F7Fu)) ^ ((idx ^ q) & 0x80808080u);
 }
-// four patterns -> four low bytes
-__device__ __forceinline__ uint32_t pack_bytes4(const float* m) {
-    const uint32_t a = __byte_perm(__float_as_uint(m[0]), __float_as_uint(m[1]), 0x0040);
-    const uint32_t b = __byte_perm(__float_as_uint(m[2]), __float_as_uint(m[3]), 0x0040);
-    return __byte_perm(a, b, 0x5410);
+// four index bytes (each < 16) -> four nibbles in the low half word
+__device__ __forceinline__ uint32_t idx_to_nibbles4(uint32_t idx) {
+    return (idx & 0xFu) | ((idx >> 4) & 0xF0u) | ((idx >> 8) & 0xF00u) | ((idx >> 12) & 0xF000u);
+}
+// a word of unsigned 4-bit indices -> codes n + qmin, every nibble modulo 16
+__device__ __forceinline__ uint32_t nibbles_add(uint32_t w, int qmin) {
+    const uint32_t qq = (uint32_t(qmin) & 0xFu) * 0x01010101u;
+    return (((w & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) | (((((w >> 4) & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) << 4);
 }
 
 // Dequantize + copyTo of one code into a 16-bit float type
@@ -261,150 +303,232 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
 // K_group: units of G consecutive elements (per-group quantization), 2-byte input.
 // A warp owns a chunk of 32 consecutive groups (32*G elements, contiguous in memory). The chunk is copied
 // into the warp's shared-memory stage with coalesced 16-byte cp.async (lane l copies vectors l, l+32, ...);
-// afterwards LANE g OWNS GROUP g: it reads the group's V = G/8 vectors back (XOR-swizzled so that both access
-// patterns are free of bank conflicts), reduces min/max on packed pairs, derives scale / zero point (all 32
-// lanes busy in the FP64 section), quantizes and stores its own 16-byte pieces. No shuffles on the data path.
-// Warps loop over the chunks of all jobs of the launch.
+// afterwards LANE g OWNS GROUP g: it reads the group's V = G/8 vectors back (one vector of padding per group
+// keeps both access patterns free of bank conflicts), reduces min/max on packed pairs, derives scale / zero
+// point (all 32 lanes busy in the FP64 section) and quantizes. The packed codes go back into the stage (over
+// vectors the lane has already consumed) and leave as contiguous 16-byte stores of the whole warp. With two
+// stages per warp the copy of the warp's next chunk is in flight while the current one is processed. Warps
+// loop over the chunks of all jobs of the launch.
+// MODE: 0 = one code byte per element, 1 = BitPack<4> with qmin == 0, 2 = BitPack<4> with qmin != 0.
 // ======================================================================================================
-template <typename InT, int G, bool PACK4>
-__global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
-    constexpr int V = G / 8;  // vectors per group = vectors per lane per chunk
-    extern __shared__ uint4 smem_u4[];
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    uint4* stage = smem_u4 + wid * ((V + 1) * 32);
-    const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
+struct GroupJob {  // the job a warp is working on
+    const void* in;
+    uint8_t* codes;
+    double* o_scales;
+    int64_t* o_zps;
+    uint16_t* o_f16;
+    uint8_t* o_u4;
+    void* o_deq;
+    const double* g_scales;
+    const int64_t* g_zps;
+    int64_t total_groups, unit_begin, job_end;
+};
+struct GroupSrc {  // what the copy of a chunk needs
+    const void* in;
+    int64_t total_groups, unit_begin, job_end;
+};
 
-    int j = 0;
-    int64_t job_end = 0;  // first chunk of the next job
-    // job fields, reloaded only when the warp moves to another job
-    const InT* in = nullptr;
-    uint8_t* codes = nullptr;
-    double* o_scales = nullptr;
-    int64_t* o_zps = nullptr;
-    uint16_t* o_f16 = nullptr;
-    uint8_t* o_u4 = nullptr;
-    void* o_deq = nullptr;
-    int64_t total_groups = 0, unit_begin = 0;
-
-    for (int64_t chunk = int64_t(blockIdx.x) * (blockDim.x >> 5) + wid; chunk < p.total_units; chunk += nwarps) {
-        if (chunk >= job_end) {
-            j = find_job(jobs, p.njobs, chunk);
-            const RowQuantArgs J = jobs[j];
-            in = static_cast<const InT*>(J.in);
-            codes = static_cast<uint8_t*>(J.codes);
-            o_scales = J.scales;
-            o_zps = J.zps;
-            o_f16 = J.scales_f16;
-            o_u4 = J.zps_u4;
-            o_deq = J.dequant;
-            total_groups = J.rows * (J.cols / G);
-            unit_begin = J.unit_begin;
-            job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
-        }
-        const int64_t g0 = (chunk - unit_begin) * 32;
-        const int64_t total_elems = total_groups * G;
-        const int64_t e0 = g0 * G;
-        const uint4* src = reinterpret_cast<const uint4*>(in + e0);
-
-        // vector i of the chunk is stored at i + i / V: every group's V vectors are followed by one vector of
-        // padding, so the copy (lanes write consecutive vectors) and the sweeps (lane g reads group g, lane
-        // stride V + 1 vectors) both spread over all banks
-        const uint4* src_l = src + lane;
-        uint4* dst_l = stage + lane + lane / V;
-        if (e0 + int64_t(32) * G <= total_elems) {
+template <typename InT, int G>
+__device__ __forceinline__ void group_issue(uint4* stage, const GroupSrc& S, int64_t chunk, int lane) {
+    constexpr int V = G / 8;
+    const int64_t e0 = (chunk - S.unit_begin) * 32 * G;
+    const int64_t total_elems = S.total_groups * G;
+    // vector i of the chunk is stored at i + i / V: every group's V vectors are followed by one vector of
+    // padding, so the copy (lanes write consecutive vectors) and the sweeps (lane g reads group g, lane
+    // stride V + 1 vectors) both spread over all banks
+    const uint4* src_l = reinterpret_cast<const uint4*>(static_cast<const InT*>(S.in) + e0) + lane;
+    uint4* dst_l = stage + lane + lane / V;
+    if (e0 + int64_t(32) * G <= total_elems) {
 #pragma unroll
-            for (int v = 0; v < V; ++v) cp_async16(dst_l + v * 32 + (v * 32) / V, src_l + v * 32, true);
-        } else {
+        for (int v = 0; v < V; ++v) cp_async16(dst_l + v * 32 + (v * 32) / V, src_l + v * 32, true);
+    } else {
 #pragma unroll
-            for (int v = 0; v < V; ++v)
-                cp_async16(dst_l + v * 32 + (v * 32) / V, src_l + v * 32, e0 + int64_t(v * 32 + lane) * 8 < total_elems);
-        }
-        cp_async_wait_all();
-        __syncwarp();  // lanes read vectors copied by other lanes
+        for (int v = 0; v < V; ++v)
+            cp_async16(dst_l + v * 32 + (v * 32) / V, src_l + v * 32, e0 + int64_t(v * 32 + lane) * 8 < total_elems);
+    }
+}
 
-        // ---- statistics of group g0+lane ----------------------------------------------------------------
-        const uint4* mine = stage + lane * (V + 1);
-#define VF_MINE(k) mine[(k)]
-        MinMax2<InT> mm;
+template <typename InT, int G, int MODE>
+__device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int64_t chunk, const LaunchParams& p, int lane,
+                                            int* flags) {
+    constexpr int V = G / 8;
+    constexpr bool PACK4 = MODE != 0;
+    constexpr int VPS = PACK4 ? 4 : 2;  // input vectors per 16 bytes of codes
+    constexpr int OV = V / VPS;         // 16-byte code vectors per group
+    const int64_t g0 = (chunk - J.unit_begin) * 32;
+    const int64_t e0 = g0 * G;
+    uint4* mine = stage + lane * (V + 1);
+
+    // ---- statistics of group g0 + lane --------------------------------------------------------------------
+    MinMax2<InT> mm;
 #pragma unroll
-        for (int k = 0; k < V; ++k) mm.add(VF_MINE(k));
+    for (int k = 0; k < V; ++k) mm.add(mine[k]);
 
-        double scale;
-        long long zp;
-        UnitQ u;
+    const int64_t g = g0 + lane;
+    const bool g_ok = g < J.total_groups;
+    double scale;
+    long long zp;
+    UnitQ u;
+    bool fast = true;
+    if (p.given) {
+        scale = g_ok ? J.g_scales[g] : 1.0;
+        zp = g_ok ? J.g_zps[g] : 0;
+        unit_consts(scale, zp, p, u);
+        fast = unit_fits(u, mm.min_f(), mm.max_f(), zp, p);
+    } else {
         derive_unit(mm.min_f(), mm.max_f(), p, scale, zp, u, flags);
-        const int64_t g = g0 + lane;
-        const bool g_ok = g < total_groups;
         if (g_ok) {
-            if (o_scales) o_scales[g] = scale;
-            if (o_zps) o_zps[g] = zp;
-            if (o_f16) o_f16[g] = f32_to_f16_bits(__double2float_rn(scale));
+            if (J.o_scales) J.o_scales[g] = scale;
+            if (J.o_zps) J.o_zps[g] = zp;
+            if (J.o_f16) J.o_f16[g] = f32_to_f16_bits(__double2float_rn(scale));
         }
-        if (o_u4) {
+        if (J.o_u4) {
             const int hi = __shfl_down_sync(0xffffffffu, int(zp), 1);
             if ((lane & 1) == 0 && g_ok) {
-                const int hv = (g + 1 < total_groups) ? (hi & 0xF) : 0;
-                o_u4[g >> 1] = uint8_t((hv << 4) | (int(zp) & 0xF));
+                const int hv = (g + 1 < J.total_groups) ? (hi & 0xF) : 0;
+                J.o_u4[g >> 1] = uint8_t((hv << 4) | (int(zp) & 0xF));
             }
         }
+    }
 
-        // ---- quantize + store: the lane's group is G consecutive codes ----------------------------------
-        const int add = p.qmin;  // code = n + qmin
-        if (PACK4) {
-            uint4* dst = reinterpret_cast<uint4*>(codes + (e0 >> 1) + int64_t(lane) * (G / 2));
+    if (J.o_deq && g_ok) {  // optional Dequantize copy (not on the benchmarked path): exact FP64 formula
+        const int64_t eg = e0 + int64_t(lane) * G;
 #pragma unroll 1
-            for (int k4 = 0; k4 < V / 4; ++k4) {  // four vectors = 32 codes = 16 packed bytes
-                // (one guard-band test per vector: testing the four vectors of a step together measured 9 % slower)
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint4 d = VF_MINE(k4 * 4 + q);
-                    float m[8];
-                    if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, 0, m);
-                    w[q] = pack_nibbles(m);
-                    if (add != 0) {  // signed 4-bit ranges: add qmin to every nibble, modulo 16
-                        const uint32_t qq = (uint32_t(add) & 0xFu) * 0x01010101u;
-                        w[q] = (((w[q] & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) | (((((w[q] >> 4) & 0x0F0F0F0Fu) + qq) & 0x0F0F0F0Fu) << 4);
-                    }
-                }
-                if (g_ok) st_global_v4(dst + k4, w[0], w[1], w[2], w[3]);
-            }
-        } else {
-            uint4* dst = reinterpret_cast<uint4*>(codes + e0 + int64_t(lane) * G);
+        for (int k = 0; k < V; ++k) {
+            const uint2 idx = quant8_fix_idx<InT>(mine[k], u, p.thr, p.lm1, !fast);
 #pragma unroll 1
-            for (int k2 = 0; k2 < V / 2; ++k2) {  // two vectors = 16 codes = 16 bytes
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const uint4 d = VF_MINE(k2 * 2 + q);
-                    float m[8];
-                    if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, 0, m);
-                    if (add != 0) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) m[i] = __int_as_float(__float_as_int(m[i]) + add);
-                    }
-                    w[2 * q] = pack_bytes4(m);
-                    w[2 * q + 1] = pack_bytes4(m + 4);
-                }
-                if (g_ok) st_global_v4(dst + k2, w[0], w[1], w[2], w[3]);
+            for (int i = 0; i < 8; ++i) {
+                const int q = int(((i < 4 ? idx.x : idx.y) >> (8 * (i & 3))) & 0xFFu) + p.qmin;
+                if (p.dequant_dt == VF_DT_F32) static_cast<float*>(J.o_deq)[eg + k * 8 + i] = dequantize_exact(q, scale, zp);
+                else static_cast<uint16_t*>(J.o_deq)[eg + k * 8 + i] = dequant16(q, zp, scale, p.dequant_dt);
             }
         }
-        if (o_deq && g_ok) {  // optional Dequantize copy (not on the benchmarked path): exact FP64 formula
-            const int64_t eg = e0 + int64_t(lane) * G;
-#pragma unroll 1
-            for (int k = 0; k < V; ++k) {
-                const uint4 d = VF_MINE(k);
-                float m[8];
-                if (quant8<InT>(d, u.inv, u.c, p.thr, m)) VF_QUANT8_FIX(InT, d, u, p.thr, p.lm1, 0, m);
-#pragma unroll 1
-                for (int i = 0; i < 8; ++i) {
-                    const int q = (__float_as_int(m[i]) - kMagicBits) + add;
-                    if (p.dequant_dt == VF_DT_F32) static_cast<float*>(o_deq)[eg + k * 8 + i] = dequantize_exact(q, scale, zp);
-                    else static_cast<uint16_t*>(o_deq)[eg + k * 8 + i] = dequant16(q, zp, scale, p.dequant_dt);
+    }
+
+    // ---- quantize: the lane's group is G consecutive codes; code vector k replaces input vector k ----------
+    if (PACK4) {
+        const PairQ qa = pair_consts(u.inv, 17.f * u.zq), qb = pair_consts(u.inv, u.zq);
+#pragma unroll
+        for (int k4 = 0; k4 < OV; ++k4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 d = mine[k4 * 4 + q];
+                float worst = 0.f;
+                w[q] = quant8_nibbles<InT>(d, qa, qb, worst);
+                if (!fast || !(worst <= p.thr)) {  // (one test per vector: testing several together measured slower)
+                    const uint2 idx = quant8_fix_idx<InT>(d, u, p.thr, p.lm1, !fast);
+                    w[q] = idx_to_nibbles4(idx.x) | (idx_to_nibbles4(idx.y) << 16);
+                }
+                if (MODE == 2) w[q] = nibbles_add(w[q], p.qmin);
+            }
+            mine[k4] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        const float zpf = __fadd_rn(u.zq, float(p.qmin));  // K = zp: the low byte of mm is the code
+        const PairQ qc = pair_consts(u.inv, zpf);
+#pragma unroll
+        for (int k2 = 0; k2 < OV; ++k2) {
+            uint2 c[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const uint4 d = mine[k2 * 2 + q];
+                float worst = 0.f;
+                c[q] = quant8_bytes<InT, false>(d, qc, worst, nullptr);
+                if (!fast || !(worst <= p.thr)) {
+                    const uint2 idx = quant8_fix_idx<InT>(d, u, p.thr, p.lm1, !fast);
+                    c[q] = make_uint2(idx_to_codes4(idx.x, p.qmin), idx_to_codes4(idx.y, p.qmin));
                 }
             }
+            mine[k2] = make_uint4(c[0].x, c[0].y, c[1].x, c[1].y);
         }
-        __syncwarp();  // the stage is overwritten by the next chunk's copies
+    }
+    __syncwarp();
+    // ---- copy-out: the chunk's codes are 32 * OV consecutive 16-byte vectors --------------------------------
+    uint4* outv = reinterpret_cast<uint4*>(J.codes + (PACK4 ? (e0 >> 1) : e0));
+#pragma unroll
+    for (int it = 0; it < OV; ++it) {
+        const int o = it * 32 + lane;
+        const int gg = o / OV, k = o % OV;
+        if (g0 + gg < J.total_groups) {
+            const uint4 v = stage[gg * (V + 1) + k];
+            st_global_v4(outv + o, v.x, v.y, v.z, v.w);
+        }
+    }
+}
+
+__device__ __forceinline__ void load_group_job(GroupJob& J, const RowQuantArgs* __restrict__ jobs, const LaunchParams& p, int64_t chunk,
+                                               int G) {
+    const int j = find_job(jobs, p.njobs, chunk);
+    const RowQuantArgs& A = jobs[j];
+    J.in = A.in;
+    J.codes = static_cast<uint8_t*>(A.codes);
+    J.o_scales = A.scales;
+    J.o_zps = A.zps;
+    J.o_f16 = A.scales_f16;
+    J.o_u4 = A.zps_u4;
+    J.o_deq = A.dequant;
+    J.g_scales = A.given_scales;
+    J.g_zps = A.given_zps;
+    J.total_groups = A.rows * (A.cols / G);
+    J.unit_begin = A.unit_begin;
+    J.job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+}
+__device__ __forceinline__ void load_group_src(GroupSrc& S, const RowQuantArgs* __restrict__ jobs, const LaunchParams& p, int64_t chunk,
+                                               int G) {
+    const int j = find_job(jobs, p.njobs, chunk);
+    const RowQuantArgs& A = jobs[j];
+    S.in = A.in;
+    S.total_groups = A.rows * (A.cols / G);
+    S.unit_begin = A.unit_begin;
+    S.job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+}
+
+template <typename InT, int G, int MODE, int STAGES>
+__global__ void __launch_bounds__(256 / STAGES, 3) k_group(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
+    constexpr int V = G / 8;
+    constexpr int kStageVecs = (V + 1) * 32;
+    extern __shared__ uint4 smem_u4[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int wpb = blockDim.x >> 5;
+    uint4* stage0 = smem_u4 + wid * (STAGES * kStageVecs);
+    const int64_t nwarps = int64_t(gridDim.x) * wpb;
+    int64_t chunk = int64_t(blockIdx.x) * wpb + wid;
+    if (chunk >= p.total_units) return;
+
+    GroupJob J;
+    J.job_end = 0;
+    if (STAGES == 1) {
+        for (; chunk < p.total_units; chunk += nwarps) {
+            if (chunk >= J.job_end) load_group_job(J, jobs, p, chunk, G);
+            GroupSrc S{J.in, J.total_groups, J.unit_begin, J.job_end};
+            group_issue<InT, G>(stage0, S, chunk, lane);
+            cp_async_wait_all();
+            __syncwarp();  // lanes read vectors copied by other lanes
+            group_chunk<InT, G, MODE>(stage0, J, chunk, p, lane, flags);
+            __syncwarp();  // the stage is overwritten by the next chunk's copies
+        }
+    } else {
+        GroupSrc S;
+        load_group_src(S, jobs, p, chunk, G);
+        group_issue<InT, G>(stage0, S, chunk, lane);
+        cp_async_commit();
+        int b = 0;
+        for (; chunk < p.total_units; chunk += nwarps) {
+            const int64_t next = chunk + nwarps;
+            if (next < p.total_units) {
+                if (next >= S.job_end) load_group_src(S, jobs, p, next, G);
+                group_issue<InT, G>(stage0 + (b ^ 1) * kStageVecs, S, next, lane);
+            }
+            cp_async_commit();     // (an empty group after the last chunk keeps the count uniform)
+            cp_async_wait<1>();    // everything but the copy just issued has landed
+            __syncwarp();
+            if (chunk >= J.job_end) load_group_job(J, jobs, p, chunk, G);
+            group_chunk<InT, G, MODE>(stage0 + b * kStageVecs, J, chunk, p, lane, flags);
+            __syncwarp();  // this buffer is refilled in the next iteration
+            b ^= 1;
+        }
+        cp_async_wait<0>();
     }
 }
 
@@ -413,9 +537,13 @@ __global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict
 // linear weights), 2-byte input. A CTA of 256 threads is split into 256 / T independent row groups: the T
 // threads of a group stage one row in shared memory and walk the rows of all jobs on their own, synchronising
 // through the group's named barrier only. While one group sits in the scalar FP64 derivation of its row's
-// scale, the other groups of the SM keep sweeping. The optional Dequantize copy uses a per-row table of the L
-// possible outputs (each entry computed with the exact FP64 formula, indexed by the code byte), so the sweep
-// costs one shared-memory lookup per element.
+// scale, the other groups of the SM keep sweeping.
+// The optional Dequantize copy in float16 is computed arithmetically: code - zp is already at hand as a float,
+// one packed multiply by fl32(scale) and one packed conversion give two outputs. That product can differ from
+// the reference's fl32(double(code - zp) * scale) by one ulp, which changes the float16 only next to a float16
+// rounding boundary, in the subnormal range or at the overflow clamp: per row, every code whose product lies
+// there is compared with the exact FP64 formula, and a row with a differing code falls back to a table of the L
+// exact outputs indexed by the code byte (also used for float32 and bfloat16 copies).
 // ======================================================================================================
 template <int T>
 __device__ __forceinline__ void group_sync(int bar_id) {
@@ -435,6 +563,8 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
         UnitQ u;
         double scale;
         long long zp;
+        int fast;           // the fast evaluation covers this row (always, unless the parameters were supplied)
+        int need_lut;       // the arithmetic float16 copy is not exact for this row
         int fix[kFixCap];   // vectors with an element in the guard band
         int fix2[kFixCap];  // elements in the guard band
         int nfix, nfix2;
@@ -452,10 +582,12 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
     int* const s_fix = gs.fix;
     uint4* const smem_u4 = smem_all + size_t(grp) * size_t(stage_vecs);
     const int bar_id = 1 + grp;
-    const int bias = p.qmin;  // code = n + qmin
+    const int qmin = p.qmin;
+    const bool arith_dt = DQ == 1 && p.dequant_dt == VF_DT_F16;
     if (tid == 0) {  // made visible by the first barrier of the row loop
         gs.nfix = 0;
         gs.nfix2 = 0;
+        gs.need_lut = 0;
     }
 
     int j = 0;
@@ -466,6 +598,8 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
     int64_t* o_zps = nullptr;
     uint16_t* o_f16 = nullptr;
     uint8_t* o_deq = nullptr;
+    const double* g_scales = nullptr;
+    const int64_t* g_zps = nullptr;
     int64_t cols = 0, unit_begin = 0;
 
     const int64_t row_stride = int64_t(gridDim.x) * kGroups;
@@ -479,6 +613,8 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
             o_zps = J.zps;
             o_f16 = J.scales_f16;
             o_deq = static_cast<uint8_t*>(J.dequant);
+            g_scales = J.given_scales;
+            g_zps = J.given_zps;
             cols = J.cols;
             unit_begin = J.unit_begin;
             job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
@@ -506,79 +642,146 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
                 double scale;
                 long long zp;
                 UnitQ u;
-                derive_unit(mn, mx, p, scale, zp, u, flags);
-                // shift the rounding target by qmin so that the low byte of (t + magic) is the code in two's
-                // complement; the extra rounding of the constant stays inside the guard band (|c + qmin| <= 255)
-                u.c = __fadd_rn(u.c, float(bias));
+                int fast = 1;
+                if (p.given) {
+                    scale = g_scales[r];
+                    zp = g_zps[r];
+                    unit_consts(scale, zp, p, u);
+                    fast = unit_fits(u, mn, mx, zp, p) ? 1 : 0;
+                } else {
+                    derive_unit(mn, mx, p, scale, zp, u, flags);
+                    if (o_scales) o_scales[r] = scale;
+                    if (o_zps) o_zps[r] = zp;
+                    if (o_f16) o_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+                }
                 gs.u = u;
                 gs.scale = scale;
                 gs.zp = zp;
-                if (o_scales) o_scales[r] = scale;
-                if (o_zps) o_zps[r] = zp;
-                if (o_f16) o_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+                gs.fast = fast;
             }
         }
         group_sync<T>(bar_id);
         const UnitQ u = gs.u;
-        if (DQ != 0) {
+        const bool fast = gs.fast != 0;
+        const float sh = __double2float_rn(gs.scale);
+        bool lut = DQ != 0 && !arith_dt;
+        if (arith_dt) {
+            // which codes could the arithmetic copy get wrong? (see the kernel's header)
             const double scale = gs.scale;
             const long long zp = gs.zp;
             for (int n = tid; n <= p.lm1; n += THREADS) {
-                const int code = n + bias;
+                const int code = n + qmin;
+                const float prod = __fmul_rn(float(code - int(zp)), sh);
+                const uint32_t a = __float_as_uint(prod) & 0x7FFFFFFFu, m13 = a & 0x1FFFu;
+                const bool safe = code == int(zp) || (a >= 0x38800000u && a < 0x477FE000u && (m13 < 0x0FFFu || m13 > 0x1001u));
+                if (!safe) {
+                    const uint16_t exact = f32_to_f16_clamped_bits(dequantize_exact(code, scale, zp));
+                    if (exact != __half_as_ushort(__float2half_rn(prod))) atomicOr(&gs.need_lut, 1);
+                }
+            }
+            group_sync<T>(bar_id);
+            lut = gs.need_lut != 0;
+        }
+        if (lut) {
+            const double scale = gs.scale;
+            const long long zp = gs.zp;
+            for (int n = tid; n <= p.lm1; n += THREADS) {
+                const int code = n + qmin;
                 const float f = dequantize_exact(code, scale, zp);
                 if (DQ == 2) s_lut[code & 0xFF] = __float_as_uint(f);
                 else reinterpret_cast<uint16_t*>(s_lut)[code & 0xFF] = p.dequant_dt == VF_DT_F16 ? f32_to_f16_clamped_bits(f) : f32_to_bf16_bits(f);
             }
             group_sync<T>(bar_id);
         }
-        uint8_t* const codes_row = o_codes + r * cols;
+        uint8_t* const codes_row = o_codes ? o_codes + r * cols : nullptr;
         uint8_t* const deq_row = DQ == 0 ? nullptr : o_deq + r * cols * (DQ == 1 ? 2 : 4);
         const float thr = p.thr;
-        // The sweep handles kBatch vectors per step: all shared-memory loads of the step are issued first, then
-        // the independent arithmetic chains and the stores.
-        constexpr int kBatch = 4;
-        for (int i0 = tid; i0 < nvec; i0 += kBatch * THREADS) {
-            uint4 d[kBatch];
+        // K = zp: the low byte of mm is the code in two's complement, s = code - zp
+        const PairQ qc = pair_consts(u.inv, __fadd_rn(u.zq, float(qmin)));
+        const float2 sh2 = dup(sh);
+        if (fast) {
+            // The sweep handles kBatch vectors per step: all shared-memory loads of the step are issued first, then
+            // the independent arithmetic chains and the stores.
+            constexpr int kBatch = 4;
+            for (int i0 = tid; i0 < nvec; i0 += kBatch * THREADS) {
+                uint4 d[kBatch];
 #pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const int i = i0 + b * THREADS;
-                d[b] = i < nvec ? smem_u4[i] : make_uint4(0u, 0u, 0u, 0u);
+                for (int b = 0; b < kBatch; ++b) {
+                    const int i = i0 + b * THREADS;
+                    d[b] = i < nvec ? smem_u4[i] : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                    const int i = i0 + b * THREADS;
+                    if (i >= nvec) break;
+                    float worst = 0.f;
+                    float2 s[4];
+                    uint2 c = quant8_bytes<InT, DQ == 1>(d[b], qc, worst, s);
+                    if (!(worst <= thr)) {
+                        // a vector with an element in the guard band is noted and repaired after the sweep, so the
+                        // sweep itself never diverges into the exact sequence
+                        const int slot = atomicAdd(&gs.nfix, 1);
+                        if (slot < kFixCap) {
+                            s_fix[slot] = i;
+                        } else {
+                            const uint2 idx = quant8_fix_idx<InT>(d[b], u, thr, p.lm1, false);
+                            c = make_uint2(idx_to_codes4(idx.x, qmin), idx_to_codes4(idx.y, qmin));
+                            if (DQ == 1 && !lut) {  // the arithmetic copy follows the repaired codes
+                                const int zpi = int(gs.zp);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const uint32_t cw = k < 2 ? c.x : c.y;
+                                    const uint32_t b0 = (cw >> (16 * (k & 1))) & 0xFFu, b1 = (cw >> (16 * (k & 1) + 8)) & 0xFFu;
+                                    s[k] = make_float2(float((qmin < 0 ? int(int8_t(b0)) : int(b0)) - zpi),
+                                                       float((qmin < 0 ? int(int8_t(b1)) : int(b1)) - zpi));
+                                }
+                            }
+                        }
+                    }
+                    if (codes_row) st_global_v2(codes_row + size_t(i) * 8, c.x, c.y);
+                    if (DQ == 1 && !lut) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float2 v = __fmul2_rn(s[k], sh2);
+                            h[k] = as_u32(__floats2half2_rn(v.x, v.y));
+                        }
+                        st_global_v4(deq_row + size_t(i) * 16, h[0], h[1], h[2], h[3]);
+                    } else if (DQ != 0) {
+                        // table entry of byte k of w: shift the byte to the entry's offset, mask it and OR the table's
+                        // (size-aligned) shared-memory address in, all in one logic instruction after the shift
+                        constexpr int kSh = DQ == 1 ? 1 : 2;
+                        constexpr uint32_t kMask = DQ == 1 ? 0x1FEu : 0x3FCu;
+                        const uint32_t w0 = c.x, w1 = c.y;
+                        uint32_t q[8];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t o0 = ((k == 0 ? (w0 << kSh) : (w0 >> (8 * k - kSh))) & kMask) | lut_sh;
+                            const uint32_t o1 = ((k == 0 ? (w1 << kSh) : (w1 >> (8 * k - kSh))) & kMask) | lut_sh;
+                            q[k] = DQ == 1 ? lds_u16(o0) : lds_u32(o0);
+                            q[4 + k] = DQ == 1 ? lds_u16(o1) : lds_u32(o1);
+                        }
+                        if (DQ == 2) {
+                            st_global_v4(deq_row + size_t(i) * 32, q[0], q[1], q[2], q[3]);
+                            st_global_v4(deq_row + size_t(i) * 32 + 16, q[4], q[5], q[6], q[7]);
+                        } else {
+                            st_global_v4(deq_row + size_t(i) * 16, __byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
+                                         __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
+                        }
+                    }
+                }
             }
-#pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const int i = i0 + b * THREADS;
-                if (i >= nvec) break;
-                float m[8];
-                if (quant8<InT>(d[b], u.inv, u.c, thr, m)) {
-                    // a vector with an element in the guard band is noted and repaired after the sweep, so the
-                    // sweep itself never diverges into the exact sequence
-                    const int slot = atomicAdd(&gs.nfix, 1);
-                    if (slot < kFixCap) s_fix[slot] = i;
-                    else VF_QUANT8_FIX(InT, d[b], u, thr, p.lm1, bias, m);
-                }
-                const uint32_t w0 = pack_bytes4(m), w1 = pack_bytes4(m + 4);
-                st_global_v2(codes_row + size_t(i) * 8, w0, w1);
-                if (DQ != 0) {
-                    // table entry of byte k of w: shift the byte to the entry's offset, mask it and OR the table's
-                    // (size-aligned) shared-memory address in, all in one logic instruction after the shift
-                    constexpr int kSh = DQ == 1 ? 1 : 2;
-                    constexpr uint32_t kMask = DQ == 1 ? 0x1FEu : 0x3FCu;
-                    uint32_t q[8];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint32_t o0 = ((k == 0 ? (w0 << kSh) : (w0 >> (8 * k - kSh))) & kMask) | lut_sh;
-                        const uint32_t o1 = ((k == 0 ? (w1 << kSh) : (w1 >> (8 * k - kSh))) & kMask) | lut_sh;
-                        q[k] = DQ == 1 ? lds_u16(o0) : lds_u32(o0);
-                        q[4 + k] = DQ == 1 ? lds_u16(o1) : lds_u32(o1);
-                    }
-                    if (DQ == 2) {
-                        st_global_v4(deq_row + size_t(i) * 32, q[0], q[1], q[2], q[3]);
-                        st_global_v4(deq_row + size_t(i) * 32 + 16, q[4], q[5], q[6], q[7]);
-                    } else {
-                        st_global_v4(deq_row + size_t(i) * 16, __byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
-                                     __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
-                    }
-                }
+        } else {
+            // supplied parameters that do not cover the row: the exact sequence for every element
+            const uint16_t* row16 = reinterpret_cast<const uint16_t*>(smem_u4);
+            const double scale = gs.scale;
+            const long long zp = gs.zp;
+            for (int idx = tid; idx < int(cols); idx += THREADS) {
+                const float x = P2<InT>::lo(uint32_t(row16[idx]));
+                const int code = quant_index_exact(x, u.in_low, u.range, p.lm1) + qmin;
+                if (codes_row) codes_row[idx] = uint8_t(code);
+                if (DQ == 1) reinterpret_cast<uint16_t*>(deq_row)[idx] = dequant16(code, zp, scale, p.dequant_dt);
+                if (DQ == 2) reinterpret_cast<float*>(deq_row)[idx] = dequantize_exact(code, scale, zp);
             }
         }
         group_sync<T>(bar_id);
@@ -588,19 +791,19 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
         const int nfix = min(gs.nfix, kFixCap);
         if (nfix > 0) {
             const uint16_t* row16 = reinterpret_cast<const uint16_t*>(smem_u4);
+            const float cm = __fadd_rn(kMagic, u.zq);
             auto patch = [&](int idx) {
                 const float x = P2<InT>::lo(uint32_t(row16[idx]));
-                const int code = quant_index_exact(x, u.in_low, u.range, p.lm1) + bias;
-                codes_row[idx] = uint8_t(code);
-                if (DQ == 1) reinterpret_cast<uint16_t*>(deq_row)[idx] = reinterpret_cast<const uint16_t*>(s_lut)[code & 0xFF];
-                if (DQ == 2) reinterpret_cast<uint32_t*>(deq_row)[idx] = s_lut[code & 0xFF];
+                const int code = quant_index_exact(x, u.in_low, u.range, p.lm1) + qmin;
+                if (codes_row) codes_row[idx] = uint8_t(code);
+                if (DQ == 1) reinterpret_cast<uint16_t*>(deq_row)[idx] = dequant16(code, gs.zp, gs.scale, p.dequant_dt);
+                if (DQ == 2) reinterpret_cast<float*>(deq_row)[idx] = dequantize_exact(code, gs.scale, gs.zp);
             };
             for (int e = tid; e < nfix * 8; e += THREADS) {
                 const int idx = s_fix[e >> 3] * 8 + (e & 7);
                 const float x = P2<InT>::lo(uint32_t(row16[idx]));
-                const float t = __fmaf_rn(x, u.inv, u.c);
-                const float mg = __fadd_rn(t, kMagic);
-                if (fabsf(__fsub_rn(t, __fsub_rn(mg, kMagic))) > thr) {
+                const float mg = __fmaf_rn(x, u.inv, cm);
+                if (!(fabsf(__fmaf_rn(x, -u.inv, __fsub_rn(mg, cm))) <= thr)) {
                     const int slot = atomicAdd(&gs.nfix2, 1);
                     if (slot < kFixCap) gs.fix2[slot] = idx;
                     else patch(idx);
@@ -614,6 +817,7 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
         if (tid == 0) {
             gs.nfix = 0;
             gs.nfix2 = 0;
+            gs.need_lut = 0;
         }
     }
 }
@@ -656,28 +860,37 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
         double scale = 0.0;
         long long zp = 0;
         UnitQ u;
-        u.inv = u.c = u.in_low = u.range = 0.f;
+        u.inv = u.zq = u.in_low = u.range = 0.f;
+        int fast = 1;
         if (lane == 0) {
-            derive_unit(mn, mx, p, scale, zp, u, flags);
-            if (J.scales) J.scales[r] = scale;
-            if (J.zps) J.zps[r] = zp;
-            if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+            if (p.given) {
+                scale = J.given_scales[r];
+                zp = J.given_zps[r];
+                unit_consts(scale, zp, p, u);
+                fast = unit_fits(u, mn, mx, zp, p) ? 1 : 0;
+            } else {
+                derive_unit(mn, mx, p, scale, zp, u, flags);
+                if (J.scales) J.scales[r] = scale;
+                if (J.zps) J.zps[r] = zp;
+                if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+            }
         }
         u.inv = __shfl_sync(0xffffffffu, u.inv, 0);
-        u.c = __shfl_sync(0xffffffffu, u.c, 0);
+        u.zq = __shfl_sync(0xffffffffu, u.zq, 0);
         u.in_low = __shfl_sync(0xffffffffu, u.in_low, 0);
         u.range = __shfl_sync(0xffffffffu, u.range, 0);
+        fast = __shfl_sync(0xffffffffu, fast, 0);
         if (ic_pad != ic) {
             for (int64_t b = lane; b < out_row_bytes; b += 32) stage[b] = 0;
             __syncwarp();
         }
+        const float cm = __fadd_rn(kMagic, u.zq);
         for (int64_t i = lane; i < J.cols; i += 32) {
             const float x = load_as_f32(J.in, in_dt, base + i, nullptr);
-            const float t = __fmaf_rn(x, u.inv, u.c);
-            const float m = __fadd_rn(t, kMagic);
+            const float m = __fmaf_rn(x, u.inv, cm);
             int n = __float_as_int(m) - kMagicBits;
-            const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
-            if (fabsf(resid) > p.thr) n = quant_index_exact(x, u.in_low, u.range, p.lm1);
+            const float resid = __fmaf_rn(x, -u.inv, __fsub_rn(m, cm));
+            if (!fast || !(fabsf(resid) <= p.thr)) n = quant_index_exact(x, u.in_low, u.range, p.lm1);
             n = min(max(n, 0), p.lm1);
             // input index i = icIdx * khw + s  ->  output index s * ic_pad + icIdx
             const int64_t ici = i / khw, s = i - ici * khw;
@@ -698,19 +911,49 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
 // ======================================================================================================
 // K_convv: the vectorised form of K_conv for 2-byte inputs whose rows are 16-byte multiples (every ResNet-style
 // convolution with IC % 8 == 0). One warp per output channel: the row is copied into the warp's shared-memory
-// stage with cp.async, min/max run on packed pairs, the codes are written back into the stage in input order
-// (8 bytes per vector, over the vector they came from) and then copied out — straight for 1x1 kernels, transposed OIYX->OYXI otherwise
-// (for every kernel tap s the lanes gather four codes of consecutive input channels and store one word).
+// stage with cp.async, min/max run on packed pairs, the codes are written back into the stage as a dense byte
+// row in input order (the eight codes of vector v at byte 8 v: only over vectors every lane has consumed) and
+// then copied out — straight for 1x1 kernels, transposed OIYX->OYXI otherwise: the (tap, channel block) pairs of
+// the output row are dealt out over the lanes, every lane gathers the codes of 16 (or 4) consecutive input
+// channels of one tap and stores them as one vector.
 // ======================================================================================================
+template <int W>  // bytes per lane and store: 16 or 4
+__device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, int khw, int ic, int ic_pad, int lane) {
+    const int blocks = ic_pad / W;           // channel blocks per tap
+    const int total = khw * blocks;          // stores of the row
+    const int q32 = 32 / blocks, r32 = 32 % blocks;
+    int s = lane / blocks, cblk = lane % blocks;
+    for (int o = lane; o < total; o += 32) {
+        const int c0 = cblk * W;
+        uint32_t w[W / 4];
+#pragma unroll
+        for (int k = 0; k < W / 4; ++k) {
+            uint32_t word = 0;
+            const int c = c0 + 4 * k;
+            if (c < ic) {  // ic is a multiple of 4: a word is either all data or all padding
+                const uint8_t* src = cb + c * khw + s;  // input index = channel * khw + tap
+                word = uint32_t(src[0]) | (uint32_t(src[khw]) << 8) | (uint32_t(src[2 * khw]) << 16) | (uint32_t(src[3 * khw]) << 24);
+            }
+            w[k] = word;
+        }
+        uint8_t* dst = out + size_t(s) * ic_pad + c0;
+        if (W == 16) st_global_v4(dst, w[0], w[1], w[2], w[3]);
+        else *reinterpret_cast<uint32_t*>(dst) = w[0];
+        s += q32;
+        cblk += r32;
+        if (cblk >= blocks) {
+            cblk -= blocks;
+            ++s;
+        }
+    }
+}
+
 template <typename InT>
-__global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int in_vecs,
-                                               int code_bytes, int* flags) {
+__global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int in_vecs, int* flags) {
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint4* in_stage = smem_u4 + size_t(wid) * size_t(in_vecs);
-    // the codes of vector v (8 bytes) overwrite the first half of the 16-byte slot the vector was read from
     const uint8_t* code_bytes_p = reinterpret_cast<const uint8_t*>(in_stage);
-    (void)code_bytes;
     const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
     const float thr = p.thr;
     int64_t job_end = 0;
@@ -726,10 +969,12 @@ __global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ 
         const int khw = J.khw > 0 ? int(J.khw) : 1;
         const int ic = J.khw > 0 ? int(J.ic) : int(J.cols);
         const int ic_pad = J.khw > 0 ? int(J.ic_pad) : int(J.cols);
-        const int out_words = (khw * ic_pad) >> 2;
-        uint32_t* out = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(J.codes) + r * (int64_t(khw) * ic_pad));
+        const int out_bytes = khw * ic_pad;
+        uint8_t* out = static_cast<uint8_t*>(J.codes) + r * int64_t(out_bytes);
+        const bool out16 = (reinterpret_cast<uintptr_t>(J.codes) & 15) == 0 && (out_bytes & 15) == 0;
         if (r >= J.rows) {  // padded output channel
-            for (int w = lane; w < out_words; w += 32) out[w] = 0u;
+            uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+            for (int w = lane; w < (out_bytes >> 2); w += 32) o32[w] = 0u;
             continue;
         }
         const int nvec = int(J.cols >> 3);
@@ -741,47 +986,65 @@ __global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ 
         for (int v = lane; v < nvec; v += 32) mm.add(in_stage[v]);
         const float mn = warp_min(mm.min_f()), mx = warp_max(mm.max_f());
         UnitQ u;
-        u.inv = u.c = u.in_low = u.range = 0.f;
+        u.inv = u.zq = u.in_low = u.range = 0.f;
+        int fast = 1;
         if (lane == 0) {
             double scale;
             long long zp;
-            derive_unit(mn, mx, p, scale, zp, u, flags);
-            u.c = __fadd_rn(u.c, float(p.qmin));  // low byte of (t + magic) = code
-            if (J.scales) J.scales[r] = scale;
-            if (J.zps) J.zps[r] = zp;
-            if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+            if (p.given) {
+                scale = J.given_scales[r];
+                zp = J.given_zps[r];
+                unit_consts(scale, zp, p, u);
+                fast = unit_fits(u, mn, mx, zp, p) ? 1 : 0;
+            } else {
+                derive_unit(mn, mx, p, scale, zp, u, flags);
+                if (J.scales) J.scales[r] = scale;
+                if (J.zps) J.zps[r] = zp;
+                if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+            }
         }
         u.inv = __shfl_sync(0xffffffffu, u.inv, 0);
-        u.c = __shfl_sync(0xffffffffu, u.c, 0);
+        u.zq = __shfl_sync(0xffffffffu, u.zq, 0);
         u.in_low = __shfl_sync(0xffffffffu, u.in_low, 0);
         u.range = __shfl_sync(0xffffffffu, u.range, 0);
+        fast = __shfl_sync(0xffffffffu, fast, 0);
 
-        for (int v = lane; v < nvec; v += 32) {
-            const uint4 d = in_stage[v];
-            float m[8];
-            if (quant8<InT>(d, u.inv, u.c, thr, m)) VF_QUANT8_FIX(InT, d, u, thr, p.lm1, p.qmin, m);
-            *reinterpret_cast<uint2*>(in_stage + v) = make_uint2(pack_bytes4(m), pack_bytes4(m + 4));
+        const PairQ qc = pair_consts(u.inv, __fadd_rn(u.zq, float(p.qmin)));  // K = zp: low byte of mm = code
+        for (int v0 = 0; v0 < nvec; v0 += 32) {
+            const int v = v0 + lane;
+            uint2 c = make_uint2(0u, 0u);
+            if (v < nvec) {
+                const uint4 d = in_stage[v];
+                float worst = 0.f;
+                c = quant8_bytes<InT, false>(d, qc, worst, nullptr);
+                if (!fast || !(worst <= thr)) {
+                    const uint2 idx = quant8_fix_idx<InT>(d, u, thr, p.lm1, !fast);
+                    c = make_uint2(idx_to_codes4(idx.x, p.qmin), idx_to_codes4(idx.y, p.qmin));
+                }
+            }
+            // the codes of vectors [v0, v0 + 32) go to bytes [8 v0, 8 v0 + 256): vectors up to v0 / 2 + 16 of the stage,
+            // all of them consumed once every lane holds this step's vector in registers
+            __syncwarp();
+            if (v < nvec) reinterpret_cast<uint2*>(in_stage)[v] = c;
         }
         __syncwarp();
         if (J.khw <= 0) {
-            const uint32_t* c32 = reinterpret_cast<const uint32_t*>(in_stage);
-            for (int w = lane; w < out_words; w += 32) out[w] = c32[(w >> 1) * 4 + (w & 1)];
-        } else {
-            const int icw = ic >> 2, padw = ic_pad >> 2;
-            for (int s = 0; s < khw; ++s) {
-                uint32_t* orow = out + s * padw;
-                for (int w = lane; w < padw; w += 32) {
-                    uint32_t word = 0;
-                    if (w < icw) {
-                        const int i0 = (w * 4) * khw + s;  // input index = channel * khw + tap
-                        auto code_at = [&](int i) { return uint32_t(code_bytes_p[(i >> 3) * 16 + (i & 7)]); };
-                        word = code_at(i0) | (code_at(i0 + khw) << 8) | (code_at(i0 + 2 * khw) << 16) | (code_at(i0 + 3 * khw) << 24);
-                    }
-                    orow[w] = word;
+            if (out16) {
+                for (int w = lane; w < (out_bytes >> 4); w += 32) {
+                    const uint4 vv = in_stage[w];
+                    st_global_v4(out + size_t(w) * 16, vv.x, vv.y, vv.z, vv.w);
                 }
+            } else {
+                const uint32_t* c32 = reinterpret_cast<const uint32_t*>(in_stage);
+                uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+                for (int w = lane; w < (out_bytes >> 2); w += 32) o32[w] = c32[w];
             }
+        } else if (out16 && (ic_pad & 15) == 0) {
+            convv_copy_out<16>(code_bytes_p, out, khw, ic, ic_pad, lane);
+        } else {
+            convv_copy_out<4>(code_bytes_p, out, khw, ic, ic_pad, lane);
         }
-        __syncwarp();  // both stages are rewritten by the next row
+        __syncwarp();  // the stage is rewritten by the next row
     }
 }
 
@@ -795,20 +1058,30 @@ void set_smem(K kernel, size_t bytes) {
     VF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
 }
 
+template <typename InT, int G, int MODE, int STAGES>
+void launch_group_s(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p) {
+    constexpr int kWarps = 8 / STAGES;
+    const size_t smem = size_t(8) * (G / 8 + 1) * 32 * 16;  // eight stages of 32 groups x (G/8 + 1 padding) vectors
+    // persistent grid: three CTAs per SM (launch bounds), every warp strides over the chunk list
+    const int64_t want = (p.total_units + kWarps - 1) / kWarps;
+    const int grid = int(std::min<int64_t>(want, int64_t(ctx->sm_count) * 3));
+    set_smem(k_group<InT, G, MODE, STAGES>, smem);
+    k_group<InT, G, MODE, STAGES><<<grid, 32 * kWarps, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    post_launch(ctx);
+}
+
 template <typename InT, int G>
 void launch_group_g(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, bool pack4) {
-    const size_t smem = size_t(8) * (G / 8 + 1) * 32 * 16;  // 8 warps x 32 groups x (G/8 + 1 padding) vectors
-    // persistent grid: three CTAs per SM (launch bounds), every warp strides over the chunk list
-    const int64_t want = (p.total_units + 7) / 8;
-    const int grid = int(std::min<int64_t>(want, 148 * 3));
-    if (pack4) {
-        set_smem(k_group<InT, G, true>, smem);
-        k_group<InT, G, true><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    const int mode = !pack4 ? 0 : (p.qmin == 0 ? 1 : 2);
+    const int stages = ctx->tune_group_stages;
+    if (mode == 1) {
+        if (stages == 2) launch_group_s<InT, G, 1, 2>(ctx, d_jobs, p);
+        else launch_group_s<InT, G, 1, 1>(ctx, d_jobs, p);
+    } else if (mode == 2) {
+        launch_group_s<InT, G, 2, 1>(ctx, d_jobs, p);
     } else {
-        set_smem(k_group<InT, G, false>, smem);
-        k_group<InT, G, false><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+        launch_group_s<InT, G, 0, 1>(ctx, d_jobs, p);
     }
-    post_launch(ctx);
 }
 
 template <typename InT>
@@ -835,7 +1108,7 @@ void launch_row_n(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p
     };
     const int per_sm = dq == 0 ? ctas_per_sm(k_row<InT, T, 0>) : dq == 1 ? ctas_per_sm(k_row<InT, T, 1>) : ctas_per_sm(k_row<InT, T, 2>);
     const int64_t ctas = (p.total_units + kGroups - 1) / kGroups;
-    const int grid = int(std::min<int64_t>(ctas, int64_t(148) * int64_t(per_sm)));
+    const int grid = int(std::min<int64_t>(ctas, int64_t(ctx->sm_count) * int64_t(per_sm)));
     if (dq == 0) {
         k_row<InT, T, 0><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
     } else if (dq == 1) {
@@ -871,7 +1144,7 @@ int rowquant_kind(const RowQuantArgs& a) {
         a.cols >= 1024 && a.cols <= 96 * 1024 && reinterpret_cast<uintptr_t>(a.codes) % 8 == 0 &&
         (!a.dequant || reinterpret_cast<uintptr_t>(a.dequant) % 16 == 0))
         return 2;
-    if (!a.pack4 && !a.dequant && !a.zps_u4) {
+    if (!a.pack4 && !a.dequant && !a.zps_u4 && a.codes) {
         const int64_t out_row = a.khw > 0 ? a.khw * a.ic_pad : a.cols;
         const int64_t ic = a.khw > 0 ? a.ic : a.cols, ic_pad = a.khw > 0 ? a.ic_pad : a.cols;
         if (two_byte && aligned16 && a.cols % 8 == 0 && a.cols <= 4608 && out_row <= 4608 && ic % 4 == 0 && ic_pad % 4 == 0 &&
@@ -894,6 +1167,7 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
     p.lm1 = int(a0.qmax - a0.qmin);
     p.dequant_dt = a0.dequant_dt;
     p.njobs = int(jobs.size());
+    p.given = a0.given_scales != nullptr;
     p.thr = 0.5f - kGuardPerLevel * float(p.lm1 + 1);
     int64_t units = 0, max_cols = 0, max_out_row = 0;
     for (auto& a : jobs) {
@@ -918,17 +1192,16 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         else launch_row_t<__nv_bfloat16>(ctx, d_jobs, p, max_cols, dq);
     } else if (kind == 4) {
         const int in_vecs = int((max_cols + 7) / 8);
-        const int code_bytes = int((std::max(max_cols, max_out_row) + 15) & ~int64_t(15));
         const size_t smem = size_t(8) * size_t(in_vecs) * 16;
         const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024)));
         const int64_t blocks = (units + 7) / 8;
-        const int grid = int(std::min<int64_t>(blocks, int64_t(148) * int64_t(per_sm)));
+        const int grid = int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * int64_t(per_sm)));
         if (a0.in_dt == VF_DT_F16) {
             set_smem(k_convv<__half>, smem);
-            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, code_bytes, ctx->d_flags);
+            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, ctx->d_flags);
         } else {
             set_smem(k_convv<__nv_bfloat16>, smem);
-            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, code_bytes, ctx->d_flags);
+            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, ctx->d_flags);
         }
         post_launch(ctx);
     } else if (kind == 3) {
@@ -936,7 +1209,7 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         const size_t smem = size_t(stage_bytes) * 8;
         set_smem(k_conv, std::max<size_t>(smem, 16));
         const int64_t blocks = (units + 7) / 8;
-        k_conv<<<int(std::min<int64_t>(blocks, 148 * 8)), 256, smem, ctx->stream>>>(d_jobs, p, a0.in_dt, stage_bytes, ctx->d_flags);
+        k_conv<<<int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * 8)), 256, smem, ctx->stream>>>(d_jobs, p, a0.in_dt, stage_bytes, ctx->d_flags);
         post_launch(ctx);
     } else {
         raise(VF_ERR_UNSUPPORTED, "no fused kernel for this weight quantization pattern");
@@ -949,7 +1222,8 @@ bool rowquant_compatible(const RowQuantArgs& a, const RowQuantArgs& b) {
     const bool long_a = a.group == 0 && a.cols > 8192, long_b = b.group == 0 && b.cols > 8192;
     return a.in_dt == b.in_dt && a.group == b.group && a.range_mode == b.range_mode && a.qmin == b.qmin && a.qmax == b.qmax &&
            a.pack4 == b.pack4 && a.dequant_dt == b.dequant_dt && a.out_signed == b.out_signed &&
-           (a.dequant != nullptr) == (b.dequant != nullptr) && long_a == long_b;
+           (a.dequant != nullptr) == (b.dequant != nullptr) && long_a == long_b &&
+           (a.given_scales != nullptr) == (b.given_scales != nullptr);
 }
 
 }  // namespace vf
