@@ -310,6 +310,10 @@ Elem elem_from_pod(const vf_elem_type& e) {
         r.scales.assign(e.scales, e.scales + e.nparams);
         r.zps.assign(e.zps, e.zps + e.nparams);
         if (r.kind == VF_ELEM_QUANT_UNIFORM && e.nparams != 1) fail(VF_ERR_SHAPE, "uniform type needs 1 param");
+        // a quantized type cannot be built with such a scale: mlir::quant::UniformQuantized[PerAxis]Type::verify
+        // rejects scale <= 0, infinities and NaN ("illegal scale")
+        for (double sc : r.scales)
+            if (!(sc > 0.0) || std::isinf(sc)) fail(VF_ERR_INVALID_ARG, "illegal scale");
     }
     return r;
 }

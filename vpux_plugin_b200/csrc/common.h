@@ -147,7 +147,6 @@ struct vf_ctx {
     uint64_t launches = 0;
     int32_t opt_flags = 0;
     int sm_count = 1;            // multiprocessors of the device: persistent grids are sized in multiples of it
-    int tune_group_stages = 1;   // shared-memory stages per warp of the per-group kernel
     bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device
     // vf_fold, last transformation, device destination: the output buffer may be the destination itself, which
     // saves the final copy (see alloc_like)

@@ -1,7 +1,6 @@
 // Context: one device, one stream, stream-ordered scratch from the device memory pool, pinned bounce
 // buffers for pageable host memory, and the device-side error flags.
 #include <algorithm>
-#include <cstdlib>
 
 #include "common.h"
 
@@ -137,7 +136,6 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
         try {
             c->device = device;
             VF_CUDA(cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device));
-            if (const char* e = getenv("VF_TUNE_GROUP_STAGES")) c->tune_group_stages = atoi(e) == 2 ? 2 : 1;
             if (external_stream) {
                 c->stream = static_cast<cudaStream_t>(external_stream);
             } else {

@@ -973,6 +973,7 @@ uint64_t fold_one(vf_ctx* ctx, const vf_content& base, const vf_transform* t, in
         FusedJob fj;
         Type ot;
         if (fused_prepare_given(ctx, cur, t, n, dst, dst_bytes, dst_mem_kind, fj, &ot)) {
+            fj.h_base = base.data;
             ot.export_to(out_type, scales_buf, zps_buf, params_cap);
             if (stats) stats->fused = 1;
             if (batch) {

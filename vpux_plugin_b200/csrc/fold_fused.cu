@@ -210,7 +210,8 @@ bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* 
     uint64_t out_bytes = uint64_t(ty.numel());
     bool to_dequant = false;
     if (i < n && t[i].kind == VF_T_BIT_PACK) {
-        if (t[i].width != 4 || ty.rank != 2 || (a.cols != 32 && a.cols != 64 && a.cols != 128) || ty.numel() % 2 != 0) return false;
+        // (BitPack reads its input through getValues<uint8_t>(): negative codes fail the checked cast, bit_pack.cpp:146-151)
+        if (t[i].width != 4 || q.qmin < 0 || ty.rank != 2 || (a.cols != 32 && a.cols != 64 && a.cols != 128) || ty.numel() % 2 != 0) return false;
         a.group = a.cols;  // every row is one group: the per-group kernel with one group per unit
         a.pack4 = 1;
         out_bytes = uint64_t(ty.numel() / 2);
@@ -280,7 +281,7 @@ void fused_merge_pairs(std::vector<FusedJob>& jobs) {
         for (size_t k = 0; k < jobs.size(); ++k) {
             FusedJob& d = jobs[k];
             if (k == i || d.merged || d.kind != 2 || !d.dst_is_dequant || d.a.codes) continue;
-            if (d.a.in != c.a.in || d.a.rows != c.a.rows || d.a.cols != c.a.cols || d.a.qmin != c.a.qmin || d.a.qmax != c.a.qmax ||
+            if (d.h_base != c.h_base || d.a.rows != c.a.rows || d.a.cols != c.a.cols || d.a.qmin != c.a.qmin || d.a.qmax != c.a.qmax ||
                 d.a.in_dt != c.a.in_dt || d.n_params != c.n_params)
                 continue;
             if (d.h_scales != c.h_scales && std::memcmp(d.h_scales, c.h_scales, size_t(c.n_params) * 8) != 0) continue;

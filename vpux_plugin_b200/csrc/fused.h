@@ -29,6 +29,7 @@ struct FusedJob {
     const double* h_scales = nullptr;
     const int64_t* h_zps = nullptr;
     int64_t n_params = 0;
+    const void* h_base = nullptr;  // where the caller's base content lives (host or device)
     bool dst_is_dequant = false;  // the list ends in Dequantize: the destination receives the dequantized copy
     bool merged = false;          // this job's output is written by another job's launch entry (fused_merge_pairs)
 };

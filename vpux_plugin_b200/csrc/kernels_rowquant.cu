@@ -18,7 +18,17 @@
 // both round to the same integer. The distance is the residual r = x * inv - round(x * inv), one more exact
 // fused multiply-add; elements inside the guard band (2e-4 wide for 8-bit ranges, 1.3e-5 for 4-bit) are
 // recomputed with the reference's own operation sequence.
+//
+// Where rounding boundaries are hit often (8-bit ranges, and bfloat16 data whose few mantissa bits put many
+// elements exactly on a boundary) the kernels evaluate the reference's sequence itself, branch-free on packed
+// pairs: a = fl(x - inLow); the division fl(a / range) as q0 = fl(a y), q = fma(fma(-q0, range, a), y, q0) with
+// y = RN(1 / range), which is the correctly rounded quotient (Markstein's correction step with a correctly
+// rounded reciprocal); e = fl(q (L-1)); and roundf(e) = floor(e + 1/2) as two additions rounded toward minus
+// infinity, the second one onto the integer grid at 1.5 * 2^23. The clamps of fakeQuantize's outer branches are
+// not evaluated per element: every step is monotonic in x, so a unit whose smallest and largest element stay
+// inside [0, L-1] needs none, and a unit where they do not takes the scalar sequence.
 #include <algorithm>
+#include <type_traits>
 #include <vector>
 
 #include "device_utils.cuh"
@@ -33,10 +43,11 @@ constexpr int kMagicBits = 0x4B400000; // its bit pattern; the low byte is zero
 constexpr float kGuardPerLevel = 8.0e-7f;
 
 struct UnitQ {  // per-unit constants
-    float inv;     // fl((L-1) / range)
+    float inv;     // (L-1) / range within a few ulps: the fast path only proposes, the guard band decides
     float zq;      // float(zp - qmin): index n = round(x * inv) + zq
     float in_low;  // exact path
     float range;   // fl(inHigh - inLow)
+    float y;       // RN(1 / range): the exact path's division
 };
 
 struct LaunchParams {  // uniform over all jobs of one launch
@@ -46,6 +57,7 @@ struct LaunchParams {  // uniform over all jobs of one launch
     int njobs;
     int given;            // parameters come from the jobs' given_scales / given_zps
     float thr;            // 0.5 - guard: largest rounding residual the fast path accepts
+    double den, inv_den;  // qmax - qmin and RN(1 / (qmax - qmin))
     int64_t total_units;  // chunks (k_group) or rows (k_row / k_conv) over all jobs
 };
 
@@ -53,11 +65,16 @@ __device__ __forceinline__ void unit_consts(double scale, long long zp, const La
     u.in_low = dequantize_exact(p.qmin, scale, zp);
     const float in_high = dequantize_exact(p.qmax, scale, zp);
     u.range = __fsub_rn(in_high, u.in_low);
-    u.inv = __fdiv_rn(float(p.lm1), u.range);
+    u.inv = __fdividef(float(p.lm1), u.range);
+    u.y = __frcp_rn(u.range);
     u.zq = float(zp - p.qmin);
 }
 
-// Per-unit parameters from the unit's range.
+// Per-unit parameters from the unit's range: calcScaleAndZeroPoint (utils/quantization.cpp:574-636) with the two
+// FP64 divisions made cheap. scale = (rMax - rMin) / (qMax - qMin) divides by a launch constant: one
+// multiplication by the correctly rounded reciprocal and one correction step give the correctly rounded
+// quotient. zp = round(qMin - rMin / scale) is an integer in the storage range: it is evaluated in fp32 first
+// (error below 1e-4) and only a value within 1e-3 of a rounding boundary takes the FP64 division.
 __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchParams& p, double& scale, long long& zp,
                                             UnitQ& u, int* flags) {
     mn = fminf(mn, 0.f);  // the range always contains zero (calcScaleAndZeroPoint requires it)
@@ -67,7 +84,19 @@ __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchPara
         mn = -a;
         mx = a;
     }
-    if (!calc_scale_zp(double(p.qmin), double(p.qmax), double(mn), double(mx), scale, zp)) {
+    const float df = __fsub_rn(mx, mn);
+    if (df >= 7.8886091e-31f && df <= 1.2676506e30f) {  // 2^-100 .. 2^100: nothing under- or overflows below
+        const double d = __dsub_rn(double(mx), double(mn));
+        const double q0 = __dmul_rn(d, p.inv_den);
+        scale = __fma_rn(__fma_rn(-q0, p.den, d), p.inv_den, q0);
+        const float xf = __fmaf_rn(-mn, __fdividef(float(p.lm1), df), float(p.qmin));
+        const float fl = floorf(xf);
+        if (fabsf(__fsub_rn(__fsub_rn(xf, fl), 0.5f)) < 1.0e-3f) {
+            zp = (long long)(round(__dsub_rn(double(p.qmin), __ddiv_rn(double(mn), scale))));
+        } else {
+            zp = (long long)(floorf(__fadd_rn(xf, 0.5f)));
+        }
+    } else if (!calc_scale_zp(double(p.qmin), double(p.qmax), double(mn), double(mx), scale, zp)) {
         set_flag(flags, VF_FLAG_QUANT_RANGE);
         scale = 1.0;
         zp = 0;
@@ -81,7 +110,8 @@ __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchPara
 // the zero point lies in the storage range; other units take the exact sequence for every element.
 __device__ __forceinline__ bool unit_fits(const UnitQ& u, float mn, float mx, long long zp, const LaunchParams& p) {
     const float lo = __fmaf_rn(mn, u.inv, u.zq), hi = __fmaf_rn(mx, u.inv, u.zq);
-    return zp >= p.qmin && zp <= p.qmax && u.range > 0.f && lo >= -0.45f && hi <= float(p.lm1) + 0.45f;
+    return zp >= p.qmin && zp <= p.qmax && u.range >= 7.8886091e-31f && u.range <= 1.2676506e30f && lo >= -0.45f &&
+           hi <= float(p.lm1) + 0.45f;
 }
 
 // The exact operation sequence of fakeQuantize's middle branch, as an index n in [0, L-1]. The first two
@@ -166,29 +196,93 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // ---- the fast quantizer on packed pairs --------------------------------------------------------------------
 // Packed two-wide fp32 instructions (sm_100): each is the same IEEE round-to-nearest operation on both halves,
 // so the results equal the scalar sequence bit for bit at half the issue slots.
-struct PairQ {  // launch / unit constants duplicated into both halves
-    float2 inv, ninv;  // inv, -inv
-    float2 cm, ncm;    // magic + K, -(magic + K)
+struct PairQ {  // unit constants duplicated into both halves
+    float2 inv;  // (L-1) / range
+    float2 cm;   // magic + K
 };
 __device__ __forceinline__ float2 dup(float v) {
     return make_float2(v, v);
 }
 __device__ __forceinline__ PairQ pair_consts(float inv, float k) {
     PairQ q;
-    const float cm = __fadd_rn(kMagic, k);  // exact: |k| is a small integer
     q.inv = dup(inv);
-    q.ninv = dup(-inv);
-    q.cm = dup(cm);
-    q.ncm = dup(-cm);
+    q.cm = dup(__fadd_rn(kMagic, k));  // exact: |k| is a small integer
     return q;
 }
-// One pair: mm = magic + K + round(x * inv) (as a float), s = round(x * inv), and the largest |residual| so far.
-// The residual is formed with the sign flipped (s - x * inv): the product is exact, one rounding.
-__device__ __forceinline__ void quant2(const float2 x, const PairQ& q, float2& mm, float2& s, float& worst) {
+// One pair: mm = magic + K + round(x * inv) (as a float), sneg = -round(x * inv), and the largest |residual| so
+// far. Only inv and cm are per-unit constants (few live registers: the sweep is unrolled over a whole group);
+// negations go through multiplications by -1, which are exact.
+__device__ __forceinline__ void quant2(const float2 x, const PairQ& q, float2& mm, float2& sneg, float& worst) {
+    const float2 neg1 = dup(-1.f);
     mm = __ffma2_rn(x, q.inv, q.cm);
-    s = __fadd2_rn(mm, q.ncm);  // exact
-    const float2 r = __ffma2_rn(x, q.ninv, s);
+    sneg = __ffma2_rn(mm, neg1, q.cm);  // cm - mm, exact
+    const float2 r = __ffma2_rn(x, q.inv, sneg);  // x * inv - round(x * inv): exact product, one rounding
     worst = fmaxf(worst, fmaxf(fabsf(r.x), fabsf(r.y)));
+}
+
+// ---- the exact sequence on packed pairs -------------------------------------------------------------------
+struct ExactQ {
+    float2 nlow, y, nrange, lm1, half;
+    float2 cm;  // magic + K: the low bits of the result hold n + K
+};
+__device__ __forceinline__ ExactQ exact_consts(const UnitQ& u, int lm1, float k) {
+    ExactQ q;
+    q.nlow = dup(-u.in_low);
+    q.y = dup(u.y);
+    q.nrange = dup(-u.range);
+    q.lm1 = dup(float(lm1));
+    q.half = dup(0.5f);
+    q.cm = dup(__fadd_rn(kMagic, k));
+    return q;
+}
+// magic + K + roundf(fl(fl(fl(x - inLow) / range) * (L-1))) for both halves, unclamped
+__device__ __forceinline__ float2 exact2(const float2 x, const ExactQ& q) {
+    const float2 a = __fadd2_rn(x, q.nlow);
+    const float2 q0 = __fmul2_rn(a, q.y);
+    const float2 d = __ffma2_rn(__ffma2_rn(q0, q.nrange, a), q.y, q0);  // = fl(a / range)
+    const float2 e = __fmul2_rn(d, q.lm1);
+    return __fadd2_rd(__fadd2_rd(e, q.half), q.cm);  // floor(e + 1/2) on the integer grid
+}
+__device__ __forceinline__ float exact1_v(float x, const UnitQ& u, int lm1) {  // e + 1/2 rounded down, one element
+    const float a = __fsub_rn(x, u.in_low);
+    const float q0 = __fmul_rn(a, u.y);
+    const float d = __fmaf_rn(__fmaf_rn(-q0, u.range, a), u.y, q0);
+    return __fadd_rd(__fmul_rn(d, float(lm1)), 0.5f);
+}
+// The packed exact sequence has no clamp and divides through the reciprocal: it covers a unit whose range is
+// far from the ends of the exponent range and whose smallest and largest element (every step is monotonic)
+// give an index inside [0, L-1].
+__device__ __forceinline__ bool unit_exact_ok(const UnitQ& u, float mn, float mx, const LaunchParams& p) {
+    return u.range >= 7.8886091e-31f && u.range <= 1.2676506e30f && exact1_v(mn, u, p.lm1) >= 0.f &&
+           exact1_v(mx, u, p.lm1) < float(p.lm1 + 1);
+}
+// Eight elements -> eight code bytes with the exact sequence (K = qmin: the low byte is the code). `s` (optional)
+// receives code - zp of every element as floats; zpk = magic + zp.
+template <typename InT, bool WANT_S>
+__device__ __forceinline__ uint2 exact8_bytes(const uint4& d, const ExactQ& q, float2 nzpk, float2* s_out) {
+    const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+    uint32_t b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 m = exact2(P2<InT>::both(w[i]), q);
+        b[i] = __byte_perm(__float_as_uint(m.x), __float_as_uint(m.y), 0x0040);
+        if (WANT_S) s_out[i] = __fadd2_rn(m, nzpk);  // exact
+    }
+    return make_uint2(__byte_perm(b[0], b[1], 0x5410), __byte_perm(b[2], b[3], 0x5410));
+}
+// Eight elements -> eight nibbles with the exact sequence (K = 0: unsigned indices)
+template <typename InT>
+__device__ __forceinline__ uint32_t exact8_nibbles(const uint4& d, const ExactQ& q) {
+    const float2 p16 = dup(16.f), nmg = dup(-kMagic);
+    const float2 e01 = P2<InT>::both(d.x), e23 = P2<InT>::both(d.y), e45 = P2<InT>::both(d.z), e67 = P2<InT>::both(d.w);
+    float2 ma = exact2(make_float2(e01.x, e23.x), q), mb = exact2(make_float2(e01.y, e23.y), q);
+    const float2 c0 = __ffma2_rn(__fadd2_rn(mb, nmg), p16, ma);
+    ma = exact2(make_float2(e45.x, e67.x), q);
+    mb = exact2(make_float2(e45.y, e67.y), q);
+    const float2 c1 = __ffma2_rn(__fadd2_rn(mb, nmg), p16, ma);
+    const uint32_t lo = __byte_perm(__float_as_uint(c0.x), __float_as_uint(c0.y), 0x0040);
+    const uint32_t hi = __byte_perm(__float_as_uint(c1.x), __float_as_uint(c1.y), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
 }
 
 // Eight elements -> eight code bytes. K = zp, so the low byte of mm is the code in two's complement. `s` (optional)
@@ -199,10 +293,10 @@ __device__ __forceinline__ uint2 quant8_bytes(const uint4& d, const PairQ& q, fl
     uint32_t b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float2 mm, s;
-        quant2(P2<InT>::both(w[i]), q, mm, s, worst);
+        float2 mm, sneg;
+        quant2(P2<InT>::both(w[i]), q, mm, sneg, worst);
         b[i] = __byte_perm(__float_as_uint(mm.x), __float_as_uint(mm.y), 0x0040);
-        if (WANT_S) s_out[i] = s;
+        if (WANT_S) s_out[i] = __ffma2_rn(sneg, dup(-1.f), dup(0.f));
     }
     return make_uint2(__byte_perm(b[0], b[1], 0x5410), __byte_perm(b[2], b[3], 0x5410));
 }
@@ -212,15 +306,15 @@ __device__ __forceinline__ uint2 quant8_bytes(const uint4& d, const PairQ& q, fl
 // neighbour (K = zq) are added in floating point: the low byte of the sum is n_even + 16 n_odd.
 template <typename InT>
 __device__ __forceinline__ uint32_t quant8_nibbles(const uint4& d, const PairQ& qa, const PairQ& qb, float& worst) {
-    const float2 p16 = dup(16.f);
+    const float2 n16 = dup(-16.f);
     const float2 e01 = P2<InT>::both(d.x), e23 = P2<InT>::both(d.y), e45 = P2<InT>::both(d.z), e67 = P2<InT>::both(d.w);
     float2 mma, sa, mmb, sb;
     quant2(make_float2(e01.x, e23.x), qa, mma, sa, worst);
     quant2(make_float2(e01.y, e23.y), qb, mmb, sb, worst);
-    const float2 c0 = __ffma2_rn(sb, p16, mma);  // exact: small integers on top of magic
+    const float2 c0 = __ffma2_rn(sb, n16, mma);  // exact: small integers on top of magic
     quant2(make_float2(e45.x, e67.x), qa, mma, sa, worst);
     quant2(make_float2(e45.y, e67.y), qb, mmb, sb, worst);
-    const float2 c1 = __ffma2_rn(sb, p16, mma);
+    const float2 c1 = __ffma2_rn(sb, n16, mma);
     const uint32_t lo = __byte_perm(__float_as_uint(c0.x), __float_as_uint(c0.y), 0x0040);
     const uint32_t hi = __byte_perm(__float_as_uint(c1.x), __float_as_uint(c1.y), 0x0040);
     return __byte_perm(lo, hi, 0x5410);
@@ -306,9 +400,8 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
 // afterwards LANE g OWNS GROUP g: it reads the group's V = G/8 vectors back (one vector of padding per group
 // keeps both access patterns free of bank conflicts), reduces min/max on packed pairs, derives scale / zero
 // point (all 32 lanes busy in the FP64 section) and quantizes. The packed codes go back into the stage (over
-// vectors the lane has already consumed) and leave as contiguous 16-byte stores of the whole warp. With two
-// stages per warp the copy of the warp's next chunk is in flight while the current one is processed. Warps
-// loop over the chunks of all jobs of the launch.
+// vectors the lane has already consumed) and leave as contiguous 16-byte stores of the whole warp. Warps loop
+// over the chunks of all jobs of the launch.
 // MODE: 0 = one code byte per element, 1 = BitPack<4> with qmin == 0, 2 = BitPack<4> with qmin != 0.
 // ======================================================================================================
 struct GroupJob {  // the job a warp is working on
@@ -323,13 +416,8 @@ struct GroupJob {  // the job a warp is working on
     const int64_t* g_zps;
     int64_t total_groups, unit_begin, job_end;
 };
-struct GroupSrc {  // what the copy of a chunk needs
-    const void* in;
-    int64_t total_groups, unit_begin, job_end;
-};
-
 template <typename InT, int G>
-__device__ __forceinline__ void group_issue(uint4* stage, const GroupSrc& S, int64_t chunk, int lane) {
+__device__ __forceinline__ void group_issue(uint4* stage, const GroupJob& S, int64_t chunk, int lane) {
     constexpr int V = G / 8;
     const int64_t e0 = (chunk - S.unit_begin) * 32 * G;
     const int64_t total_elems = S.total_groups * G;
@@ -348,11 +436,56 @@ __device__ __forceinline__ void group_issue(uint4* stage, const GroupSrc& S, int
     }
 }
 
+// What the repair of a guard-band element needs beyond the fast path's constants: inLow, range and RN(1 / range).
+struct UnitX {
+    float in_low, range, y;
+};
+// The reference's sequence for one element with its clamp, division through the correctly rounded reciprocal
+// (exact2, scalar): index n in [0, L-1].
+__device__ __forceinline__ uint32_t exact1_index(float x, const UnitX& u, int lm1) {
+    const float a = __fsub_rn(x, u.in_low);
+    const float q0 = __fmul_rn(a, u.y);
+    const float d = __fmaf_rn(__fmaf_rn(-q0, u.range, a), u.y, q0);
+    const float v = __fadd_rd(__fmul_rn(d, float(lm1)), 0.5f);
+    return uint32_t(min(max(int(floorf(v)), 0), lm1));
+}
+
+// Repair of a vector with an element in the guard band (about one vector in 500 of fp16 weights: mostly exact
+// ties x * (L-1) / range = n + 1/2, which 16-bit data on a common grid produce), out of line so that the sweep
+// stays small: every element is re-evaluated, those in the band (all of them in a unit the fast evaluation does
+// not cover) with the exact sequence. A fast value can lie one outside [0, L-1] next to the ends of the range —
+// always inside the band — which is why the word is rebuilt instead of patched. `have_x`: inLow / range / y are
+// valid; otherwise they are derived here from the unit's range and zero point.
+template <typename InT>
+__device__ __noinline__ uint32_t repair8_nibbles(uint4 d, float inv, float zq, float thr, int lm1, bool fast, float in_low, float range,
+                                                float y) {
+    UnitX ux;
+    ux.in_low = in_low;
+    ux.range = range;
+    ux.y = y;
+    const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
+    uint32_t r = 0;
+    const float cm = __fadd_rn(kMagic, zq);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x = (i & 1) ? P2<InT>::hi(wd[i >> 1]) : P2<InT>::lo(wd[i >> 1]);
+        const float m = __fmaf_rn(x, inv, cm);
+        const float resid = __fmaf_rn(x, -inv, __fsub_rn(m, cm));
+        int n = __float_as_int(m) - kMagicBits;
+        if (!fast) n = quant_index_exact(x, ux.in_low, ux.range, lm1);
+        else if (!(fabsf(resid) <= thr)) n = int(exact1_index(x, ux, lm1));
+        r |= uint32_t(min(max(n, 0), lm1)) << (4 * i);
+    }
+    return r;
+}
+
 template <typename InT, int G, int MODE>
 __device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int64_t chunk, const LaunchParams& p, int lane,
                                             int* flags) {
     constexpr int V = G / 8;
     constexpr bool PACK4 = MODE != 0;
+    // bfloat16 data sits on rounding boundaries too often for the guard-band scheme: exact sequence throughout
+    constexpr bool EXACT = !std::is_same<InT, __half>::value;
     constexpr int VPS = PACK4 ? 4 : 2;  // input vectors per 16 bytes of codes
     constexpr int OV = V / VPS;         // 16-byte code vectors per group
     const int64_t g0 = (chunk - J.unit_begin) * 32;
@@ -363,30 +496,35 @@ __device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int
     MinMax2<InT> mm;
 #pragma unroll
     for (int k = 0; k < V; ++k) mm.add(mine[k]);
+    const float mn = mm.min_f(), mx = mm.max_f();
 
     const int64_t g = g0 + lane;
     const bool g_ok = g < J.total_groups;
-    double scale;
-    long long zp;
+    double scale = 1.0;
+    long long zp = 0;
     UnitQ u;
+    u.inv = u.zq = u.in_low = u.range = u.y = 0.f;
     bool fast = true;
     if (p.given) {
         scale = g_ok ? J.g_scales[g] : 1.0;
         zp = g_ok ? J.g_zps[g] : 0;
         unit_consts(scale, zp, p, u);
-        fast = unit_fits(u, mm.min_f(), mm.max_f(), zp, p);
+        fast = EXACT ? unit_exact_ok(u, mn, mx, p) : unit_fits(u, mn, mx, zp, p);
     } else {
-        derive_unit(mm.min_f(), mm.max_f(), p, scale, zp, u, flags);
+        derive_unit(mn, mx, p, scale, zp, u, flags);
+        fast = EXACT ? unit_exact_ok(u, mn, mx, p) : (u.range >= 7.8886091e-31f && u.range <= 1.2676506e30f);
+        const int zpi = int(zp);
+        const uint32_t s16 = f32_to_f16_bits(__double2float_rn(scale));
         if (g_ok) {
             if (J.o_scales) J.o_scales[g] = scale;
             if (J.o_zps) J.o_zps[g] = zp;
-            if (J.o_f16) J.o_f16[g] = f32_to_f16_bits(__double2float_rn(scale));
+            if (J.o_f16) J.o_f16[g] = uint16_t(s16);
         }
         if (J.o_u4) {
-            const int hi = __shfl_down_sync(0xffffffffu, int(zp), 1);
+            const int hi = __shfl_down_sync(0xffffffffu, zpi, 1);
             if ((lane & 1) == 0 && g_ok) {
                 const int hv = (g + 1 < J.total_groups) ? (hi & 0xF) : 0;
-                J.o_u4[g >> 1] = uint8_t((hv << 4) | (int(zp) & 0xF));
+                J.o_u4[g >> 1] = uint8_t((hv << 4) | (zpi & 0xF));
             }
         }
     }
@@ -406,7 +544,8 @@ __device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int
     }
 
     // ---- quantize: the lane's group is G consecutive codes; code vector k replaces input vector k ----------
-    if (PACK4) {
+    if (PACK4 && !EXACT) {
+        // guard-band path; a vector with an element in the band is rebuilt by repair8_nibbles
         const PairQ qa = pair_consts(u.inv, 17.f * u.zq), qb = pair_consts(u.inv, u.zq);
 #pragma unroll
         for (int k4 = 0; k4 < OV; ++k4) {
@@ -416,8 +555,24 @@ __device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int
                 const uint4 d = mine[k4 * 4 + q];
                 float worst = 0.f;
                 w[q] = quant8_nibbles<InT>(d, qa, qb, worst);
-                if (!fast || !(worst <= p.thr)) {  // (one test per vector: testing several together measured slower)
-                    const uint2 idx = quant8_fix_idx<InT>(d, u, p.thr, p.lm1, !fast);
+                if (!fast || !(worst <= p.thr))  // (one test per vector: testing several together measured slower)
+                    w[q] = repair8_nibbles<InT>(d, u.inv, u.zq, p.thr, p.lm1, fast, u.in_low, u.range, u.y);
+                if (MODE == 2) w[q] = nibbles_add(w[q], p.qmin);
+            }
+            mine[k4] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else if (PACK4) {
+        const ExactQ eq = exact_consts(u, p.lm1, 0.f);
+#pragma unroll
+        for (int k4 = 0; k4 < OV; ++k4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 d = mine[k4 * 4 + q];
+                if (fast) {
+                    w[q] = exact8_nibbles<InT>(d, eq);
+                } else {
+                    const uint2 idx = quant8_fix_idx<InT>(d, u, p.thr, p.lm1, true);
                     w[q] = idx_to_nibbles4(idx.x) | (idx_to_nibbles4(idx.y) << 16);
                 }
                 if (MODE == 2) w[q] = nibbles_add(w[q], p.qmin);
@@ -427,15 +582,22 @@ __device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int
     } else {
         const float zpf = __fadd_rn(u.zq, float(p.qmin));  // K = zp: the low byte of mm is the code
         const PairQ qc = pair_consts(u.inv, zpf);
+        const ExactQ eq = exact_consts(u, p.lm1, float(p.qmin));
 #pragma unroll
         for (int k2 = 0; k2 < OV; ++k2) {
             uint2 c[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const uint4 d = mine[k2 * 2 + q];
-                float worst = 0.f;
-                c[q] = quant8_bytes<InT, false>(d, qc, worst, nullptr);
-                if (!fast || !(worst <= p.thr)) {
+                bool redo = !fast;
+                if (EXACT) {
+                    c[q] = exact8_bytes<InT, false>(d, eq, dup(0.f), nullptr);
+                } else {
+                    float worst = 0.f;
+                    c[q] = quant8_bytes<InT, false>(d, qc, worst, nullptr);
+                    redo |= !(worst <= p.thr);
+                }
+                if (redo) {
                     const uint2 idx = quant8_fix_idx<InT>(d, u, p.thr, p.lm1, !fast);
                     c[q] = make_uint2(idx_to_codes4(idx.x, p.qmin), idx_to_codes4(idx.y, p.qmin));
                 }
@@ -474,61 +636,24 @@ __device__ __forceinline__ void load_group_job(GroupJob& J, const RowQuantArgs* 
     J.unit_begin = A.unit_begin;
     J.job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
 }
-__device__ __forceinline__ void load_group_src(GroupSrc& S, const RowQuantArgs* __restrict__ jobs, const LaunchParams& p, int64_t chunk,
-                                               int G) {
-    const int j = find_job(jobs, p.njobs, chunk);
-    const RowQuantArgs& A = jobs[j];
-    S.in = A.in;
-    S.total_groups = A.rows * (A.cols / G);
-    S.unit_begin = A.unit_begin;
-    S.job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
-}
-
-template <typename InT, int G, int MODE, int STAGES>
-__global__ void __launch_bounds__(256 / STAGES, 3) k_group(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
+template <typename InT, int G, int MODE>
+__global__ void __launch_bounds__(256, 3) k_group(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int* flags) {
     constexpr int V = G / 8;
     constexpr int kStageVecs = (V + 1) * 32;
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int wpb = blockDim.x >> 5;
-    uint4* stage0 = smem_u4 + wid * (STAGES * kStageVecs);
+    uint4* stage = smem_u4 + wid * kStageVecs;
     const int64_t nwarps = int64_t(gridDim.x) * wpb;
-    int64_t chunk = int64_t(blockIdx.x) * wpb + wid;
-    if (chunk >= p.total_units) return;
-
     GroupJob J;
     J.job_end = 0;
-    if (STAGES == 1) {
-        for (; chunk < p.total_units; chunk += nwarps) {
-            if (chunk >= J.job_end) load_group_job(J, jobs, p, chunk, G);
-            GroupSrc S{J.in, J.total_groups, J.unit_begin, J.job_end};
-            group_issue<InT, G>(stage0, S, chunk, lane);
-            cp_async_wait_all();
-            __syncwarp();  // lanes read vectors copied by other lanes
-            group_chunk<InT, G, MODE>(stage0, J, chunk, p, lane, flags);
-            __syncwarp();  // the stage is overwritten by the next chunk's copies
-        }
-    } else {
-        GroupSrc S;
-        load_group_src(S, jobs, p, chunk, G);
-        group_issue<InT, G>(stage0, S, chunk, lane);
-        cp_async_commit();
-        int b = 0;
-        for (; chunk < p.total_units; chunk += nwarps) {
-            const int64_t next = chunk + nwarps;
-            if (next < p.total_units) {
-                if (next >= S.job_end) load_group_src(S, jobs, p, next, G);
-                group_issue<InT, G>(stage0 + (b ^ 1) * kStageVecs, S, next, lane);
-            }
-            cp_async_commit();     // (an empty group after the last chunk keeps the count uniform)
-            cp_async_wait<1>();    // everything but the copy just issued has landed
-            __syncwarp();
-            if (chunk >= J.job_end) load_group_job(J, jobs, p, chunk, G);
-            group_chunk<InT, G, MODE>(stage0 + b * kStageVecs, J, chunk, p, lane, flags);
-            __syncwarp();  // this buffer is refilled in the next iteration
-            b ^= 1;
-        }
-        cp_async_wait<0>();
+    for (int64_t chunk = int64_t(blockIdx.x) * wpb + wid; chunk < p.total_units; chunk += nwarps) {
+        if (chunk >= J.job_end) load_group_job(J, jobs, p, chunk, G);
+        group_issue<InT, G>(stage, J, chunk, lane);
+        cp_async_wait_all();
+        __syncwarp();  // lanes read vectors copied by other lanes
+        group_chunk<InT, G, MODE>(stage, J, chunk, p, lane, flags);
+        __syncwarp();  // the stage is overwritten by the next chunk's copies
     }
 }
 
@@ -556,18 +681,14 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
                                              int* flags) {
     constexpr int THREADS = T;
     constexpr int kGroups = 256 / T;
-    constexpr int kFixCap = 128;  // vectors noted for repair per row; beyond that the sweep repairs inline
     extern __shared__ uint4 smem_all[];
     struct GroupShared {
         float mn[T / 32], mx[T / 32];
         UnitQ u;
         double scale;
         long long zp;
-        int fast;           // the fast evaluation covers this row (always, unless the parameters were supplied)
-        int need_lut;       // the arithmetic float16 copy is not exact for this row
-        int fix[kFixCap];   // vectors with an element in the guard band
-        int fix2[kFixCap];  // elements in the guard band
-        int nfix, nfix2;
+        int fast;      // the packed exact sequence covers this row (unit_exact_ok)
+        int need_lut;  // the arithmetic float16 copy is not exact for this row
     };
     __shared__ GroupShared gs_all[kGroups];
     // dequantized value of code byte b: 16-bit entries (DQ == 1) or 32-bit entries; aligned to its size so that
@@ -579,16 +700,11 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
     float* const s_mx = gs.mx;
     uint32_t* const s_lut = s_lut_all[grp];
     const uint32_t lut_sh = uint32_t(__cvta_generic_to_shared(s_lut));
-    int* const s_fix = gs.fix;
     uint4* const smem_u4 = smem_all + size_t(grp) * size_t(stage_vecs);
     const int bar_id = 1 + grp;
     const int qmin = p.qmin;
     const bool arith_dt = DQ == 1 && p.dequant_dt == VF_DT_F16;
-    if (tid == 0) {  // made visible by the first barrier of the row loop
-        gs.nfix = 0;
-        gs.nfix2 = 0;
-        gs.need_lut = 0;
-    }
+    if (tid == 0) gs.need_lut = 0;  // made visible by the first barrier of the row loop
 
     int j = 0;
     int64_t job_end = 0;
@@ -642,12 +758,10 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
                 double scale;
                 long long zp;
                 UnitQ u;
-                int fast = 1;
                 if (p.given) {
                     scale = g_scales[r];
                     zp = g_zps[r];
                     unit_consts(scale, zp, p, u);
-                    fast = unit_fits(u, mn, mx, zp, p) ? 1 : 0;
                 } else {
                     derive_unit(mn, mx, p, scale, zp, u, flags);
                     if (o_scales) o_scales[r] = scale;
@@ -657,13 +771,14 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
                 gs.u = u;
                 gs.scale = scale;
                 gs.zp = zp;
-                gs.fast = fast;
+                gs.fast = unit_exact_ok(u, mn, mx, p) ? 1 : 0;
             }
         }
         group_sync<T>(bar_id);
         const UnitQ u = gs.u;
         const bool fast = gs.fast != 0;
         const float sh = __double2float_rn(gs.scale);
+        const int zpi = int(gs.zp);
         bool lut = DQ != 0 && !arith_dt;
         if (arith_dt) {
             // which codes could the arithmetic copy get wrong? (see the kernel's header)
@@ -671,9 +786,9 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
             const long long zp = gs.zp;
             for (int n = tid; n <= p.lm1; n += THREADS) {
                 const int code = n + qmin;
-                const float prod = __fmul_rn(float(code - int(zp)), sh);
+                const float prod = __fmul_rn(float(code - zpi), sh);
                 const uint32_t a = __float_as_uint(prod) & 0x7FFFFFFFu, m13 = a & 0x1FFFu;
-                const bool safe = code == int(zp) || (a >= 0x38800000u && a < 0x477FE000u && (m13 < 0x0FFFu || m13 > 0x1001u));
+                const bool safe = code == zpi || (a >= 0x38800000u && a < 0x477FE000u && (m13 < 0x0FFFu || m13 > 0x1001u));
                 if (!safe) {
                     const uint16_t exact = f32_to_f16_clamped_bits(dequantize_exact(code, scale, zp));
                     if (exact != __half_as_ushort(__float2half_rn(prod))) atomicOr(&gs.need_lut, 1);
@@ -695,84 +810,70 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
         }
         uint8_t* const codes_row = o_codes ? o_codes + r * cols : nullptr;
         uint8_t* const deq_row = DQ == 0 ? nullptr : o_deq + r * cols * (DQ == 1 ? 2 : 4);
-        const float thr = p.thr;
-        // K = zp: the low byte of mm is the code in two's complement, s = code - zp
-        const PairQ qc = pair_consts(u.inv, __fadd_rn(u.zq, float(qmin)));
-        const float2 sh2 = dup(sh);
         if (fast) {
+            // K = qmin: the low byte of the result is the code in two's complement; minus (magic + zp): code - zp
+            const ExactQ eq = exact_consts(u, p.lm1, float(qmin));
+            const float2 nzpk = dup(-__fadd_rn(kMagic, float(zpi)));
+            const float2 sh2 = dup(sh);
+            constexpr int kDeqBytes = DQ == 2 ? 32 : 16;  // dequantized bytes per vector
+            auto one = [&](const uint4& d, uint8_t* cdst, uint8_t* ddst) {
+                float2 s[4];
+                const uint2 c = exact8_bytes<InT, DQ == 1>(d, eq, nzpk, s);
+                if (codes_row) st_global_v2(cdst, c.x, c.y);
+                if (DQ == 1 && !lut) {
+                    uint32_t h[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 v = __fmul2_rn(s[k], sh2);
+                        h[k] = as_u32(__floats2half2_rn(v.x, v.y));
+                    }
+                    st_global_v4(ddst, h[0], h[1], h[2], h[3]);
+                } else if (DQ != 0) {
+                    // table entry of byte k of w: shift the byte to the entry's offset, mask it and OR the table's
+                    // (size-aligned) shared-memory address in, all in one logic instruction after the shift
+                    constexpr int kSh = DQ == 1 ? 1 : 2;
+                    constexpr uint32_t kMask = DQ == 1 ? 0x1FEu : 0x3FCu;
+                    const uint32_t w0 = c.x, w1 = c.y;
+                    uint32_t q[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t o0 = ((k == 0 ? (w0 << kSh) : (w0 >> (8 * k - kSh))) & kMask) | lut_sh;
+                        const uint32_t o1 = ((k == 0 ? (w1 << kSh) : (w1 >> (8 * k - kSh))) & kMask) | lut_sh;
+                        q[k] = DQ == 1 ? lds_u16(o0) : lds_u32(o0);
+                        q[4 + k] = DQ == 1 ? lds_u16(o1) : lds_u32(o1);
+                    }
+                    if (DQ == 2) {
+                        st_global_v4(ddst, q[0], q[1], q[2], q[3]);
+                        st_global_v4(ddst + 16, q[4], q[5], q[6], q[7]);
+                    } else {
+                        st_global_v4(ddst, __byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
+                                     __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
+                    }
+                }
+            };
             // The sweep handles kBatch vectors per step: all shared-memory loads of the step are issued first, then
-            // the independent arithmetic chains and the stores.
+            // the independent arithmetic chains and the stores. Pointers advance by constants; the ragged end of the
+            // row is a loop of its own.
             constexpr int kBatch = 4;
-            for (int i0 = tid; i0 < nvec; i0 += kBatch * THREADS) {
+            const int full = nvec / (kBatch * THREADS);
+            const uint4* sp = smem_u4 + tid;
+            uint8_t* cp = codes_row + size_t(tid) * 8;
+            uint8_t* dp = deq_row + size_t(tid) * kDeqBytes;
+            for (int it = 0; it < full; ++it) {
                 uint4 d[kBatch];
 #pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                    const int i = i0 + b * THREADS;
-                    d[b] = i < nvec ? smem_u4[i] : make_uint4(0u, 0u, 0u, 0u);
-                }
+                for (int b = 0; b < kBatch; ++b) d[b] = sp[b * THREADS];
 #pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                    const int i = i0 + b * THREADS;
-                    if (i >= nvec) break;
-                    float worst = 0.f;
-                    float2 s[4];
-                    uint2 c = quant8_bytes<InT, DQ == 1>(d[b], qc, worst, s);
-                    if (!(worst <= thr)) {
-                        // a vector with an element in the guard band is noted and repaired after the sweep, so the
-                        // sweep itself never diverges into the exact sequence
-                        const int slot = atomicAdd(&gs.nfix, 1);
-                        if (slot < kFixCap) {
-                            s_fix[slot] = i;
-                        } else {
-                            const uint2 idx = quant8_fix_idx<InT>(d[b], u, thr, p.lm1, false);
-                            c = make_uint2(idx_to_codes4(idx.x, qmin), idx_to_codes4(idx.y, qmin));
-                            if (DQ == 1 && !lut) {  // the arithmetic copy follows the repaired codes
-                                const int zpi = int(gs.zp);
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const uint32_t cw = k < 2 ? c.x : c.y;
-                                    const uint32_t b0 = (cw >> (16 * (k & 1))) & 0xFFu, b1 = (cw >> (16 * (k & 1) + 8)) & 0xFFu;
-                                    s[k] = make_float2(float((qmin < 0 ? int(int8_t(b0)) : int(b0)) - zpi),
-                                                       float((qmin < 0 ? int(int8_t(b1)) : int(b1)) - zpi));
-                                }
-                            }
-                        }
-                    }
-                    if (codes_row) st_global_v2(codes_row + size_t(i) * 8, c.x, c.y);
-                    if (DQ == 1 && !lut) {
-                        uint32_t h[4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const float2 v = __fmul2_rn(s[k], sh2);
-                            h[k] = as_u32(__floats2half2_rn(v.x, v.y));
-                        }
-                        st_global_v4(deq_row + size_t(i) * 16, h[0], h[1], h[2], h[3]);
-                    } else if (DQ != 0) {
-                        // table entry of byte k of w: shift the byte to the entry's offset, mask it and OR the table's
-                        // (size-aligned) shared-memory address in, all in one logic instruction after the shift
-                        constexpr int kSh = DQ == 1 ? 1 : 2;
-                        constexpr uint32_t kMask = DQ == 1 ? 0x1FEu : 0x3FCu;
-                        const uint32_t w0 = c.x, w1 = c.y;
-                        uint32_t q[8];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint32_t o0 = ((k == 0 ? (w0 << kSh) : (w0 >> (8 * k - kSh))) & kMask) | lut_sh;
-                            const uint32_t o1 = ((k == 0 ? (w1 << kSh) : (w1 >> (8 * k - kSh))) & kMask) | lut_sh;
-                            q[k] = DQ == 1 ? lds_u16(o0) : lds_u32(o0);
-                            q[4 + k] = DQ == 1 ? lds_u16(o1) : lds_u32(o1);
-                        }
-                        if (DQ == 2) {
-                            st_global_v4(deq_row + size_t(i) * 32, q[0], q[1], q[2], q[3]);
-                            st_global_v4(deq_row + size_t(i) * 32 + 16, q[4], q[5], q[6], q[7]);
-                        } else {
-                            st_global_v4(deq_row + size_t(i) * 16, __byte_perm(q[0], q[1], 0x5410), __byte_perm(q[2], q[3], 0x5410),
-                                         __byte_perm(q[4], q[5], 0x5410), __byte_perm(q[6], q[7], 0x5410));
-                        }
-                    }
-                }
+                for (int b = 0; b < kBatch; ++b) one(d[b], cp + b * THREADS * 8, dp + b * THREADS * kDeqBytes);
+                sp += kBatch * THREADS;
+                cp += kBatch * THREADS * 8;
+                dp += kBatch * THREADS * kDeqBytes;
             }
+            for (int i = full * kBatch * THREADS + tid; i < nvec; i += THREADS)
+                one(smem_u4[i], codes_row + size_t(i) * 8, deq_row + size_t(i) * kDeqBytes);
         } else {
-            // supplied parameters that do not cover the row: the exact sequence for every element
+            // a row the packed sequence does not cover (parameters that do not contain the data, a range at the end
+            // of the exponent range): the scalar sequence with its clamp for every element
             const uint16_t* row16 = reinterpret_cast<const uint16_t*>(smem_u4);
             const double scale = gs.scale;
             const long long zp = gs.zp;
@@ -784,41 +885,8 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
                 if (DQ == 2) reinterpret_cast<float*>(deq_row)[idx] = dequantize_exact(code, scale, zp);
             }
         }
-        group_sync<T>(bar_id);
-        // Repair in two steps so that the exact sequence runs on full warps: first one thread per element of
-        // every noted vector lists the elements that really lie in the guard band, then the listed elements are
-        // recomputed exactly and patched in place (the others keep what the sweep stored).
-        const int nfix = min(gs.nfix, kFixCap);
-        if (nfix > 0) {
-            const uint16_t* row16 = reinterpret_cast<const uint16_t*>(smem_u4);
-            const float cm = __fadd_rn(kMagic, u.zq);
-            auto patch = [&](int idx) {
-                const float x = P2<InT>::lo(uint32_t(row16[idx]));
-                const int code = quant_index_exact(x, u.in_low, u.range, p.lm1) + qmin;
-                if (codes_row) codes_row[idx] = uint8_t(code);
-                if (DQ == 1) reinterpret_cast<uint16_t*>(deq_row)[idx] = dequant16(code, gs.zp, gs.scale, p.dequant_dt);
-                if (DQ == 2) reinterpret_cast<float*>(deq_row)[idx] = dequantize_exact(code, gs.scale, gs.zp);
-            };
-            for (int e = tid; e < nfix * 8; e += THREADS) {
-                const int idx = s_fix[e >> 3] * 8 + (e & 7);
-                const float x = P2<InT>::lo(uint32_t(row16[idx]));
-                const float mg = __fmaf_rn(x, u.inv, cm);
-                if (!(fabsf(__fmaf_rn(x, -u.inv, __fsub_rn(mg, cm))) <= thr)) {
-                    const int slot = atomicAdd(&gs.nfix2, 1);
-                    if (slot < kFixCap) gs.fix2[slot] = idx;
-                    else patch(idx);
-                }
-            }
-            group_sync<T>(bar_id);
-            const int nfix2 = min(gs.nfix2, kFixCap);
-            for (int e = tid; e < nfix2; e += THREADS) patch(gs.fix2[e]);
-        }
-        group_sync<T>(bar_id);  // u, the table and the repair list are rewritten by the next row
-        if (tid == 0) {
-            gs.nfix = 0;
-            gs.nfix2 = 0;
-            gs.need_lut = 0;
-        }
+        group_sync<T>(bar_id);  // the stage, u and the table are rewritten by the next row
+        if (tid == 0) gs.need_lut = 0;
     }
 }
 
@@ -860,7 +928,7 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
         double scale = 0.0;
         long long zp = 0;
         UnitQ u;
-        u.inv = u.zq = u.in_low = u.range = 0.f;
+        u.inv = u.zq = u.in_low = u.range = u.y = 0.f;
         int fast = 1;
         if (lane == 0) {
             if (p.given) {
@@ -870,6 +938,7 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
                 fast = unit_fits(u, mn, mx, zp, p) ? 1 : 0;
             } else {
                 derive_unit(mn, mx, p, scale, zp, u, flags);
+                fast = (u.range >= 7.8886091e-31f && u.range <= 1.2676506e30f) ? 1 : 0;
                 if (J.scales) J.scales[r] = scale;
                 if (J.zps) J.zps[r] = zp;
                 if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
@@ -986,7 +1055,7 @@ __global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ 
         for (int v = lane; v < nvec; v += 32) mm.add(in_stage[v]);
         const float mn = warp_min(mm.min_f()), mx = warp_max(mm.max_f());
         UnitQ u;
-        u.inv = u.zq = u.in_low = u.range = 0.f;
+        u.inv = u.zq = u.in_low = u.range = u.y = 0.f;
         int fast = 1;
         if (lane == 0) {
             double scale;
@@ -995,30 +1064,31 @@ __global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ 
                 scale = J.given_scales[r];
                 zp = J.given_zps[r];
                 unit_consts(scale, zp, p, u);
-                fast = unit_fits(u, mn, mx, zp, p) ? 1 : 0;
             } else {
                 derive_unit(mn, mx, p, scale, zp, u, flags);
                 if (J.scales) J.scales[r] = scale;
                 if (J.zps) J.zps[r] = zp;
                 if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
             }
+            fast = unit_exact_ok(u, mn, mx, p) ? 1 : 0;
         }
         u.inv = __shfl_sync(0xffffffffu, u.inv, 0);
         u.zq = __shfl_sync(0xffffffffu, u.zq, 0);
         u.in_low = __shfl_sync(0xffffffffu, u.in_low, 0);
         u.range = __shfl_sync(0xffffffffu, u.range, 0);
+        u.y = __shfl_sync(0xffffffffu, u.y, 0);
         fast = __shfl_sync(0xffffffffu, fast, 0);
 
-        const PairQ qc = pair_consts(u.inv, __fadd_rn(u.zq, float(p.qmin)));  // K = zp: low byte of mm = code
+        const ExactQ eq = exact_consts(u, p.lm1, float(p.qmin));  // K = qmin: the low byte is the code
         for (int v0 = 0; v0 < nvec; v0 += 32) {
             const int v = v0 + lane;
             uint2 c = make_uint2(0u, 0u);
             if (v < nvec) {
                 const uint4 d = in_stage[v];
-                float worst = 0.f;
-                c = quant8_bytes<InT, false>(d, qc, worst, nullptr);
-                if (!fast || !(worst <= thr)) {
-                    const uint2 idx = quant8_fix_idx<InT>(d, u, thr, p.lm1, !fast);
+                if (fast) {
+                    c = exact8_bytes<InT, false>(d, eq, dup(0.f), nullptr);
+                } else {
+                    const uint2 idx = quant8_fix_idx<InT>(d, u, thr, p.lm1, true);
                     c = make_uint2(idx_to_codes4(idx.x, p.qmin), idx_to_codes4(idx.y, p.qmin));
                 }
             }
@@ -1058,30 +1128,22 @@ void set_smem(K kernel, size_t bytes) {
     VF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
 }
 
-template <typename InT, int G, int MODE, int STAGES>
+template <typename InT, int G, int MODE>
 void launch_group_s(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p) {
-    constexpr int kWarps = 8 / STAGES;
-    const size_t smem = size_t(8) * (G / 8 + 1) * 32 * 16;  // eight stages of 32 groups x (G/8 + 1 padding) vectors
+    const size_t smem = size_t(8) * (G / 8 + 1) * 32 * 16;  // 8 warps x 32 groups x (G/8 + 1 padding) vectors
     // persistent grid: three CTAs per SM (launch bounds), every warp strides over the chunk list
-    const int64_t want = (p.total_units + kWarps - 1) / kWarps;
+    const int64_t want = (p.total_units + 7) / 8;
     const int grid = int(std::min<int64_t>(want, int64_t(ctx->sm_count) * 3));
-    set_smem(k_group<InT, G, MODE, STAGES>, smem);
-    k_group<InT, G, MODE, STAGES><<<grid, 32 * kWarps, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
+    set_smem(k_group<InT, G, MODE>, smem);
+    k_group<InT, G, MODE><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, ctx->d_flags);
     post_launch(ctx);
 }
 
 template <typename InT, int G>
 void launch_group_g(vf_ctx* ctx, const RowQuantArgs* d_jobs, const LaunchParams& p, bool pack4) {
-    const int mode = !pack4 ? 0 : (p.qmin == 0 ? 1 : 2);
-    const int stages = ctx->tune_group_stages;
-    if (mode == 1) {
-        if (stages == 2) launch_group_s<InT, G, 1, 2>(ctx, d_jobs, p);
-        else launch_group_s<InT, G, 1, 1>(ctx, d_jobs, p);
-    } else if (mode == 2) {
-        launch_group_s<InT, G, 2, 1>(ctx, d_jobs, p);
-    } else {
-        launch_group_s<InT, G, 0, 1>(ctx, d_jobs, p);
-    }
+    if (!pack4) launch_group_s<InT, G, 0>(ctx, d_jobs, p);
+    else if (p.qmin == 0) launch_group_s<InT, G, 1>(ctx, d_jobs, p);
+    else launch_group_s<InT, G, 2>(ctx, d_jobs, p);
 }
 
 template <typename InT>
@@ -1169,6 +1231,8 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
     p.njobs = int(jobs.size());
     p.given = a0.given_scales != nullptr;
     p.thr = 0.5f - kGuardPerLevel * float(p.lm1 + 1);
+    p.den = double(p.lm1);
+    p.inv_den = 1.0 / p.den;
     int64_t units = 0, max_cols = 0, max_out_row = 0;
     for (auto& a : jobs) {
         a.unit_begin = units;

@@ -78,6 +78,10 @@ Elem Elem::from(const vf_elem_type& e) {
     if (e.kind == VF_ELEM_QUANT_UNIFORM && e.nparams != 1) raise(VF_ERR_SHAPE, "uniform quantized type takes exactly one scale");
     r.scales.assign(e.scales, e.scales + e.nparams);
     r.zps.assign(e.zps, e.zps + e.nparams);
+    // a quantized type cannot be built with such a scale: mlir::quant::UniformQuantized[PerAxis]Type::verify
+    // rejects scale <= 0, infinities and NaN ("illegal scale")
+    for (double sc : r.scales)
+        if (!(sc > 0.0) || std::isinf(sc)) raise(VF_ERR_INVALID_ARG, "illegal scale: %g", sc);
     return r;
 }
 
