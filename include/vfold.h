@@ -57,6 +57,8 @@ typedef enum vf_status {
                                      (quantization.cpp:429-432, nce_sparsity.cpp:340-345)              */
     VF_ERR_QUANT_RANGE = -13,     /* calcScaleAndZeroPoint failure (quantization.cpp:612-625)          */
     VF_ERR_NOT_NORMAL = -14,      /* ScalarMultInverse of a non-normal float (inverse.cpp:58-59)       */
+    VF_ERR_NAN = -15,             /* Quantize met a NaN: the reference converts it to an integer, which
+                                     is undefined (quantize.cpp:91-106); reported after the kernels ran   */
     VF_ERR_CUDA = -20,            /* a CUDA runtime call failed; message carries cudaGetErrorString    */
     VF_ERR_NO_DEVICE = -21,       /* no usable CUDA device                                             */
     VF_ERR_OOM = -22,             /* device or pinned allocation failed                                */
@@ -227,6 +229,9 @@ typedef struct vf_ctx vf_ctx;
  * the next synchronising call of the context — any call that touches host memory, vf_sparsify*, or
  * vf_ctx_synchronize — and the buffers of a deferred call must stay alive until then. */
 #define VF_OPT_ASYNC 2
+/* Synchronous calls that take a vf_stats also measure the device time between their first and their last
+ * enqueued operation (a pair of CUDA events on the context's stream) into vf_stats.device_ms. */
+#define VF_OPT_TIMING 4
 
 typedef struct vf_options {
     uint64_t staging_bytes; /* size of each pinned staging buffer for pageable host I/O (0 = 64 MiB) */
@@ -242,16 +247,18 @@ typedef struct vf_stats {
     uint64_t d2h_bytes;
     int32_t kernels_launched; /* library kernels launched by the call */
     int32_t fused;            /* 1 when the call ran on a fused single-pass kernel */
-    float device_ms;          /* device time between first and last kernel (0 unless VF_FLAG_TIMING) */
+    float device_ms;          /* device time of the call's work on the stream (0 unless the context was created
+                                 with VF_OPT_TIMING and the call synchronised) */
     int32_t reserved;
 } vf_stats;
 
 int vf_abi_version(void);
 const char* vf_status_string(int status);
 
-/* One context = one device + one stream + one scratch pool. `external_stream`
- * (a cudaStream_t, may be NULL) makes the context enqueue on the caller's
- * stream instead of creating its own. */
+/* One context = one device + one stream + one scratch pool of its own (the device's default memory pool is
+ * not touched). `external_stream` (a cudaStream_t, may be NULL) makes the context enqueue on the caller's
+ * stream instead of creating its own. Creation is also where everything vf_sparsify_noalloc needs is set up
+ * (see there): create contexts before an embedding process hands the GPU's memory to its own allocator. */
 int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_ctx** out, char* err, size_t errlen);
 void vf_ctx_destroy(vf_ctx* ctx);
 int vf_ctx_synchronize(vf_ctx* ctx, char* err, size_t errlen);
@@ -282,8 +289,8 @@ int vf_infer_type(const vf_tensor_type* base, int base_is_splat, const vf_transf
  * fewer passes, and a SubView that reaches the front lets the caller upload only the slab it selects.
  * `out` receives at most `out_cap` entries (n is always enough), `*n_out` their number. Quantization
  * parameters of the resulting entries are stored in (scales_buf, zps_buf), `params_cap` entries each;
- * numActualElements arrays keep pointing at the caller's. Pure host function. Rules that involve
- * ChangeShapeAndElemType, RelocateWeightsTable or Fuse are outside this library and never fire. */
+ * numActualElements arrays keep pointing at the caller's. Pure host function. The rules that move a
+ * transformation into a Fuse work on the parts of a fused constant and live in the host mirrors. */
 int vf_optimize_transforms(const vf_tensor_type* base, const vf_transform* t, int n, vf_transform* out, int out_cap,
                            int* n_out, double* scales_buf, int64_t* zps_buf, int64_t params_cap, char* err,
                            size_t errlen);
@@ -415,9 +422,13 @@ int vf_sparsify_batch(vf_ctx* ctx, vf_sparsify_job* jobs, int njobs, int out_mem
  *   weights      : [oc][work] elements of `dtype` (i8 / u8 / f16 / bf16 / f32) in DEVICE memory
  *   sparse_value : element value treated as zero (the zero point; 0 for plain types)
  *   data, map, counts : DEVICE memory, laid out exactly as vf_sparsify writes them; each may be NULL
+ *   data_written : the compressed size; when the call fails with VF_ERR_BUFFER_TOO_SMALL, the size `data` needs
  * All calls on one GPU share the scratch array and it keeps the previous call's contents (everything read is
- * rewritten first); calls that overlap in time on the same GPU race on it — serialise them. The first call on
- * a device looks up the array's device address; issue that first call before any stream capture. */
+ * rewritten first); calls that overlap in time on the same GPU race on it — serialise them.
+ * What has to happen once per device happens in vf_ctx_create, not here: the array's device address is looked
+ * up and the kernels this call launches are loaded. Loading them lets the CUDA driver allocate device memory
+ * (code, and the array itself), so create the context before the embedder's allocator claims the GPU and before
+ * any stream capture; after that no call of this function allocates. */
 #define VF_NOALLOC_MAX_OC 65536
 int vf_sparsify_noalloc(vf_ctx* ctx, const void* weights, int32_t dtype, int64_t oc, int64_t work,
                         int64_t sparse_value, void* data, uint64_t data_bytes, uint64_t* data_written, void* map,

@@ -19,7 +19,8 @@ _REF_LIB = os.path.join(_HERE, "_ref", "libvpux_ref_types.so")
 def build(with_reference=None):
     """Compile liboracle.so; also oracle/_ref when the reference tree is reachable."""
     subprocess.run(["make", "-s", "-C", _HERE], check=True)
-    ref_root = os.environ.get("VPUX_REFERENCE_ROOT", "/root/reference")
+    # the reference tree: named by the environment, else a checkout called `reference` beside this repository
+    ref_root = os.environ.get("VPUX_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     if with_reference is None:
         with_reference = os.path.isdir(os.path.join(ref_root, "src", "vpux_utils"))
     if with_reference:

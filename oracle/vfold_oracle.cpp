@@ -583,6 +583,9 @@ struct Quantizer {
         // the lambda takes a double, fakeQuantize takes float: float -> double -> float is exact
         const double xd = x;
         const float fq = fake_quantize(float(xd), inMin, inMax, qMin, qMax, levels);
+        // a NaN passes both comparisons of fakeQuantize and reaches static_cast<int64_t>(NaN), which is undefined:
+        // both sides of the parity tests refuse it
+        if (std::isnan(fq)) fail(VF_ERR_NAN, "Quantize met a NaN: its conversion to an integer is undefined in the reference");
         return static_cast<int64_t>(fq);
     }
 };

@@ -588,6 +588,34 @@ def test_conv_quantize_reorder_pad_fused(gpu, oracle, dt, shape, pad_oc, pad_ic,
     assert np.array_equal(out.bytes(), ref["codes"])
 
 
+def test_quantize_refuses_nan(gpu, oracle):
+    """fakeQuantize lets a NaN through both comparisons and the result is cast to int64: undefined in the reference,
+    refused on both sides here (VF_ERR_NAN)."""
+    x = np.linspace(-1, 1, 4096).astype(np.float32)
+    x[1234] = np.nan
+    t = TType([4096], F32)
+    for q in (Elem.uniform(I8, F32, 0.01, 0, -127, 127),):
+        for be in (gpu, oracle):
+            with pytest.raises(Exception) as e:
+                ContentAttr(x, t, ContentSetup(t).quantize(q)).fold(be)
+            assert e.value.status == abi.VF_ERR_NAN
+    # the context stays usable
+    x[1234] = 0.0
+    both(ContentAttr(x, t, ContentSetup(t).quantize(q)), gpu, oracle)
+
+
+def test_device_time_of_a_call_is_reported_on_request(oracle):
+    from vpux_plugin_b200.lib import Library
+    lib = Library(device=0, timing=True)
+    x = np.random.default_rng(3).standard_normal((64, 8192)).astype(np.float16)
+    t = TType([64, 8192], F16)
+    ContentAttr(x, t, ContentSetup(t).castElemType(F32).rescale(0.5)).fold(lib)
+    assert 0.0 < lib.last_stats.device_ms < 1000.0
+    plain = Library(device=0)
+    ContentAttr(x, t, ContentSetup(t).castElemType(F32).rescale(0.5)).fold(plain)
+    assert plain.last_stats.device_ms == 0.0
+
+
 def test_quantize_fold_unusual_range_takes_general_path(gpu, oracle):
     """[-120, 120] is a range where fakeQuantize's tail is not the identity; the fused kernels decline it."""
     rng = np.random.default_rng(15)

@@ -26,6 +26,7 @@ VF_ERR_ALIGNMENT = -11
 VF_ERR_RANGE = -12
 VF_ERR_QUANT_RANGE = -13
 VF_ERR_NOT_NORMAL = -14
+VF_ERR_NAN = -15
 VF_ERR_CUDA = -20
 VF_ERR_NO_DEVICE = -21
 VF_ERR_OOM = -22

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <stdexcept>
@@ -68,14 +69,94 @@ inline int64_t align_up(int64_t v, int64_t a) {
 // ------------------------------------------------------------------------------------------------------
 // host type model
 // ------------------------------------------------------------------------------------------------------
+// Scales / zero points of a quantized element type. A type read from the caller's descriptor borrows the caller's
+// arrays (they stay valid for the duration of the call) instead of copying them: per-channel types of large
+// weight tensors carry hundreds of thousands of entries and a fold looks at its types many times. The first
+// modification (padding or slicing the quantized axis) makes a private copy.
+template <class T>
+class Params {
+    const T* p_ = nullptr;
+    size_t n_ = 0;
+    std::vector<T> own_;
+    void sync() {
+        p_ = own_.data();
+        n_ = own_.size();
+    }
+    void materialise() {
+        if (own_.empty() && n_) {
+            std::vector<T> tmp(p_, p_ + n_);
+            own_.swap(tmp);
+            sync();
+        }
+    }
+
+public:
+    Params() = default;
+    Params(const Params& o) {
+        *this = o;
+    }
+    Params& operator=(const Params& o) {
+        if (this == &o) return *this;
+        own_ = o.own_;
+        n_ = o.n_;
+        p_ = o.own_.empty() ? o.p_ : own_.data();
+        return *this;
+    }
+    Params& operator=(const std::vector<T>& v) {
+        own_ = v;
+        sync();
+        return *this;
+    }
+    void borrow(const T* p, size_t n) {
+        own_.clear();
+        p_ = p;
+        n_ = n;
+    }
+    size_t size() const { return n_; }
+    bool empty() const { return n_ == 0; }
+    const T* data() const { return p_; }
+    const T& operator[](size_t i) const { return p_[i]; }
+    const T& front() const { return p_[0]; }
+    const T& back() const { return p_[n_ - 1]; }
+    const T* begin() const { return p_; }
+    const T* end() const { return p_ + n_; }
+    void assign(size_t n, const T& v) {
+        std::vector<T> tmp(n, v);
+        own_.swap(tmp);
+        sync();
+    }
+    template <class It>
+    void assign(It a, It b) {
+        std::vector<T> tmp(a, b);  // the range may lie inside this object
+        own_.swap(tmp);
+        sync();
+    }
+    template <class It>
+    void append(It a, It b) {
+        std::vector<T> tmp(a, b);
+        materialise();
+        own_.insert(own_.end(), tmp.begin(), tmp.end());
+        sync();
+    }
+    void append(size_t n, const T& v) {
+        materialise();
+        own_.insert(own_.end(), n, v);
+        sync();
+    }
+    void own() { materialise(); }  // for a type that outlives the call it was read in
+    std::vector<T> vec() const { return std::vector<T>(begin(), end()); }
+    bool operator==(const Params& o) const { return n_ == o.n_ && std::equal(begin(), end(), o.begin()); }
+    bool operator!=(const Params& o) const { return !(*this == o); }
+};
+
 struct Elem {
     int kind = VF_ELEM_PLAIN;
     int dtype = VF_DT_INVALID;
     int expressed = VF_DT_INVALID;
     int axis = -1;
     int64_t qmin = 0, qmax = 0;
-    std::vector<double> scales;
-    std::vector<int64_t> zps;
+    Params<double> scales;
+    Params<int64_t> zps;
     bool quantized() const {
         return kind != VF_ELEM_PLAIN;
     }
@@ -100,6 +181,16 @@ struct Type {
     void perm(int* p) const;                 // p[memDim] = logical dim
     void mem_shape(int64_t* ms) const;       // shape in memory order
     void export_to(vf_tensor_type* out, double* sb, int64_t* zb, int64_t cap) const;
+};
+
+// While one of these is alive on a thread, Elem::from checks an array of scales only the first time it meets it:
+// a fold parses the same attribute several times (sizes, types, the fold itself), and the arrays of per-channel
+// types are long. Entry points create one for the duration of the call, in which the arrays cannot change.
+struct ParamCheckScope {
+    ParamCheckScope();
+    ~ParamCheckScope();
+    ParamCheckScope(const ParamCheckScope&) = delete;
+    ParamCheckScope& operator=(const ParamCheckScope&) = delete;
 };
 
 uint32_t identity_order(int rank);
@@ -147,6 +238,9 @@ struct vf_ctx {
     uint64_t launches = 0;
     int32_t opt_flags = 0;
     int sm_count = 1;            // multiprocessors of the device: persistent grids are sized in multiples of it
+    cudaMemPool_t pool = nullptr;  // scratch comes from a pool the context owns (the device's default pool stays untouched)
+    void* noalloc_scratch = nullptr;  // device address of vf_sparsify_noalloc's built-in array on this device
+    cudaEvent_t time_ev[2] = {nullptr, nullptr};  // VF_OPT_TIMING
     bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device
     // vf_fold, last transformation, device destination: the output buffer may be the destination itself, which
     // saves the final copy (see alloc_like)
@@ -158,6 +252,10 @@ struct vf_ctx {
 namespace vf {
 
 constexpr int kNumFlags = 8;
+
+// Multiprocessors of the current device (queried once per device): grid-stride launches are capped at a few
+// waves of it.
+int sm_count_hint();
 
 struct DeviceGuard {
     int prev = -1;

@@ -2,13 +2,25 @@
 // buffers for pageable host memory, and the device-side error flags.
 #include <algorithm>
 
-#include "common.h"
+#include "kernels.h"
 
 namespace vf {
 
+int sm_count_hint() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 void* dalloc(vf_ctx* ctx, size_t bytes) {
     void* p = nullptr;
-    VF_CUDA(cudaMallocAsync(&p, bytes ? bytes : 1, ctx->stream));
+    VF_CUDA(cudaMallocFromPoolAsync(&p, bytes ? bytes : 1, ctx->pool, ctx->stream));
     return p;
 }
 
@@ -114,6 +126,7 @@ void flags_check(vf_ctx* ctx) {
     if (f[2]) raise(VF_ERR_SHAPE, "numActualElements smaller than the number of non-sparse elements");
     if (f[3]) raise(VF_ERR_RANGE, "weights table: scale needs a post-shift or rescaled bias is out of range");
     if (f[4]) raise(VF_ERR_ALIGNMENT, "weights table: pointer must be a multiple of 16");
+    if (f[5]) raise(VF_ERR_NAN, "Quantize met a NaN: its conversion to an integer is undefined in the reference");
     if (f[6]) raise(VF_ERR_NOT_NORMAL, "Taking inverse of a non-normal (e.g. zero/nan/...) float");
 }
 
@@ -156,11 +169,19 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
             VF_CUDA(cudaMemset(c->d_flags, 0, sizeof(int) * vf::kNumFlags));
             VF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->table_host), vf_ctx::kTableBytes));
             VF_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->table_dev), vf_ctx::kTableBytes));
-            // keep freed scratch cached in the pool instead of returning it to the driver on every sync
-            cudaMemPool_t pool;
-            VF_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
+            // scratch pool of this context: freed scratch stays cached in it instead of going back to the driver on
+            // every synchronisation; the device's default pool (and whoever else uses it) is left as it is
+            cudaMemPoolProps props{};
+            props.allocType = cudaMemAllocationTypePinned;
+            props.handleTypes = cudaMemHandleTypeNone;
+            props.location.type = cudaMemLocationTypeDevice;
+            props.location.id = device;
+            VF_CUDA(cudaMemPoolCreate(&c->pool, &props));
             uint64_t thr = UINT64_MAX;
-            VF_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr));
+            VF_CUDA(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thr));
+            if (c->opt_flags & VF_OPT_TIMING)
+                for (int k = 0; k < 2; ++k) VF_CUDA(cudaEventCreate(&c->time_ev[k]));
+            vf::noalloc_prepare(c);
         } catch (...) {
             vf_ctx_destroy(c);
             throw;
@@ -185,6 +206,9 @@ void vf_ctx_destroy(vf_ctx* c) {
     for (int k = 0; k < 2; ++k)
         if (c->lane_ev[k]) cudaEventDestroy(c->lane_ev[k]);
     if (c->lane_stream) cudaStreamDestroy(c->lane_stream);
+    for (int k = 0; k < 2; ++k)
+        if (c->time_ev[k]) cudaEventDestroy(c->time_ev[k]);
+    if (c->pool) cudaMemPoolDestroy(c->pool);
     if (c->own_stream && c->main_stream) cudaStreamDestroy(c->main_stream);
     delete c;
 }

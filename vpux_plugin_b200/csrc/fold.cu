@@ -24,6 +24,12 @@ DBuf upload_vec(vf_ctx* ctx, const std::vector<T>& v) {
     copy_in(ctx, b.p, v.data(), v.size() * sizeof(T), VF_MEM_HOST);
     return b;
 }
+template <class T>
+DBuf upload_vec(vf_ctx* ctx, const Params<T>& v) {
+    DBuf b(ctx, v.size() * sizeof(T));
+    copy_in(ctx, b.p, v.data(), v.size() * sizeof(T), VF_MEM_HOST);
+    return b;
+}
 
 // wrapBaseContent (attributes/content.cpp:310-318): device memory is borrowed, host memory is uploaded
 DContent upload_base(vf_ctx* ctx, const vf_content& b, vf_stats* stats) {
@@ -758,6 +764,7 @@ struct CallScope {  // per-call bookkeeping: context lock, device, error flags, 
     CallScope(vf_ctx* c, vf_stats* s): ctx(check(c)), lock(c->mu), dev(c->device), launches0(c->launches), stats(s) {
         if (stats) std::memset(stats, 0, sizeof(*stats));
         flags_clear(ctx);
+        if (stats && ctx->time_ev[0]) cudaEventRecord(ctx->time_ev[0], ctx->stream);
     }
     static vf_ctx* check(vf_ctx* c) {
         if (!c) raise(VF_ERR_INVALID_ARG, "ctx is NULL");
@@ -770,7 +777,10 @@ struct CallScope {  // per-call bookkeeping: context lock, device, error flags, 
             VF_CUDA(cudaGetLastError());
             ctx->deferred = true;  // the next synchronising call reports what these kernels found
         } else {
+            const bool timed = stats && ctx->time_ev[0] && ctx->stream == ctx->main_stream;
+            if (timed) cudaEventRecord(ctx->time_ev[1], ctx->stream);
             flags_check(ctx);
+            if (timed) cudaEventElapsedTime(&stats->device_ms, ctx->time_ev[0], ctx->time_ev[1]);
         }
         finished = true;
         if (stats) stats->kernels_launched = int32_t(ctx->launches - launches0);
@@ -898,6 +908,8 @@ Folded fold_keep(vf_ctx* ctx, const vf_content* base, const Folded* resume, cons
     }
     Folded f;
     f.type = cur.type;
+    f.type.elem.scales.own();  // the cache entry outlives the request whose arrays the type may borrow
+    f.type.elem.zps.own();
     f.storage = cur.storage;
     f.splat = cur.splat;
     f.nbytes = cur.nbytes;
@@ -984,6 +996,8 @@ uint64_t fold_one(vf_ctx* ctx, const vf_content& base, const vf_transform* t, in
             }
             std::vector<FusedJob> one;
             one.push_back(std::move(fj));
+            DBuf params;
+            fused_upload_params(ctx, one, params);
             fused_launch(ctx, one, 0, 1);
             uint64_t w = 0;
             fused_finish(ctx, one[0], &w, stats);
@@ -1021,6 +1035,7 @@ int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, v
             int64_t params_cap, vf_stats* stats, char* err, size_t errlen) {
     return guard(err, errlen, [&] {
         if (!base || (n > 0 && !t) || n < 0) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        ParamCheckScope checked;
         check_positions(t, n);
         CallScope scope(ctx, stats);
         const uint64_t w = fold_one(ctx, *base, t, n, dst, dst_bytes, dst_mem_kind, out_type, scales_buf, zps_buf, params_cap, stats);
@@ -1033,6 +1048,7 @@ int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch
                   vf_fold_batch_stats* batch_stats, vf_stats* stats, char* err, size_t errlen) {
     return guard(err, errlen, [&] {
         if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
+        ParamCheckScope checked;
         const uint64_t threshold = opts && opts->threshold_bytes ? opts->threshold_bytes : 300ull * 1024 * 1024;
         const uint64_t tiny = opts && opts->tiny_threshold_bytes ? opts->tiny_threshold_bytes : 1024;
         vf_fold_batch_stats bs{};
@@ -1062,6 +1078,8 @@ int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch
         auto launch_fused = [&]() {
             if (fused.jobs.empty()) return;
             fused_merge_pairs(fused.jobs);
+            DBuf params;
+            fused_upload_params(ctx, fused.jobs, params);
             fused_launch(ctx, fused.jobs, 0, fused.jobs.size());
             for (size_t k = 0; k < fused.jobs.size(); ++k) {
                 uint64_t w = 0;
@@ -1491,7 +1509,7 @@ static TableArgs table_prepare(vf_ctx* ctx, const vf_weights_table_desc* d, cons
             a.d_wscale = w_kind == VF_MEM_DEVICE ? w_scales : static_cast<const double*>(upload(w_scales, size_t(oc) * 8, w_kind));
             a.n_wscale = oc;
         } else {
-            const std::vector<double> ws = a.weights_quantized ? w.scales : std::vector<double>{1.0};
+            const std::vector<double> ws = a.weights_quantized ? w.scales.vec() : std::vector<double>{1.0};
             a.d_wscale = static_cast<const double*>(upload(ws.data(), ws.size() * 8, VF_MEM_HOST));
             a.n_wscale = int64_t(ws.size());
         }

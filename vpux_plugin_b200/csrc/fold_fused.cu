@@ -3,6 +3,7 @@
 // them onto the job tables of kernels_rowquant.cu. Anything else is declined and takes the general path.
 #include <algorithm>
 #include <cstring>
+#include <unordered_map>
 
 #include "fused.h"
 
@@ -190,8 +191,6 @@ bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* 
     double lo, hi;
     dtype_int_limits(q.dtype, lo, hi);
     if (double(q.qmin) < lo || double(q.qmax) > hi || !tail_is_identity(q.qmin, q.qmax)) return false;
-    for (int64_t k = 0; k < q.nparams; ++k)  // anything but a positive finite scale takes the general path
-        if (!(q.scales[k] > 0.0) || !(q.scales[k] < 1.0e300)) return false;
     const int qi = i;
     ty = infer_one(ty, splat, t[i], splat);
     ++i;
@@ -260,12 +259,7 @@ bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* 
     if (dst_bytes < need) raise(VF_ERR_BUFFER_TOO_SMALL, "Byte sizes of the target buffer '%llu' is smaller then storage buffer '%llu'", (unsigned long long)dst_bytes, (unsigned long long)need);
     if (to_dequant) a.dequant = job.td.bind(ctx, dst, dst_kind, need);
     else a.codes = job.tc.bind(ctx, dst, dst_kind, need);
-    job.gscales = DBuf(ctx, size_t(q.nparams) * 8);
-    job.gzps = DBuf(ctx, size_t(q.nparams) * 8);
-    copy_in(ctx, job.gscales.p, q.scales, size_t(q.nparams) * 8, VF_MEM_HOST);
-    copy_in(ctx, job.gzps.p, q.zps, size_t(q.nparams) * 8, VF_MEM_HOST);
-    a.given_scales = job.gscales.as<double>();
-    a.given_zps = job.gzps.as<int64_t>();
+    // (a.given_scales keeps its non-NULL placeholder until fused_upload_params has made the device copies)
     job.h_scales = q.scales;
     job.h_zps = q.zps;
     job.n_params = q.nparams;
@@ -275,14 +269,22 @@ bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* 
 }
 
 void fused_merge_pairs(std::vector<FusedJob>& jobs) {
+    // candidates that write the dequantized copy only, by the base content they read
+    std::unordered_multimap<const void*, size_t> by_base;
+    for (size_t k = 0; k < jobs.size(); ++k) {
+        const FusedJob& d = jobs[k];
+        if (!d.merged && d.kind == 2 && d.dst_is_dequant && !d.a.codes) by_base.emplace(d.h_base, k);
+    }
+    if (by_base.empty()) return;
     for (size_t i = 0; i < jobs.size(); ++i) {
         FusedJob& c = jobs[i];  // candidate that writes codes only
         if (c.merged || c.kind != 2 || !c.a.given_scales || c.dst_is_dequant || c.a.dequant) continue;
-        for (size_t k = 0; k < jobs.size(); ++k) {
-            FusedJob& d = jobs[k];
-            if (k == i || d.merged || d.kind != 2 || !d.dst_is_dequant || d.a.codes) continue;
-            if (d.h_base != c.h_base || d.a.rows != c.a.rows || d.a.cols != c.a.cols || d.a.qmin != c.a.qmin || d.a.qmax != c.a.qmax ||
-                d.a.in_dt != c.a.in_dt || d.n_params != c.n_params)
+        const auto range = by_base.equal_range(c.h_base);
+        for (auto it = range.first; it != range.second; ++it) {
+            FusedJob& d = jobs[it->second];
+            if (it->second == i || d.merged) continue;
+            if (d.a.rows != c.a.rows || d.a.cols != c.a.cols || d.a.qmin != c.a.qmin || d.a.qmax != c.a.qmax || d.a.in_dt != c.a.in_dt ||
+                d.n_params != c.n_params)
                 continue;
             if (d.h_scales != c.h_scales && std::memcmp(d.h_scales, c.h_scales, size_t(c.n_params) * 8) != 0) continue;
             if (d.h_zps != c.h_zps && std::memcmp(d.h_zps, c.h_zps, size_t(c.n_params) * 8) != 0) continue;
@@ -291,6 +293,40 @@ void fused_merge_pairs(std::vector<FusedJob>& jobs) {
             d.merged = true;
             break;
         }
+    }
+}
+
+void fused_upload_params(vf_ctx* ctx, std::vector<FusedJob>& jobs, DBuf& holder) {
+    size_t total = 0;
+    for (const FusedJob& j : jobs)
+        if (!j.merged && j.h_scales) total += size_t(j.n_params) * 16;
+    if (!total) return;
+    holder = DBuf(ctx, total);
+    char* dev = holder.as<char>();
+    const bool staged = total <= ctx->staging_bytes;
+    char* host = nullptr;
+    if (staged) {
+        VF_CUDA(cudaEventSynchronize(ctx->staging_ev[0]));  // the buffer's previous transfer is done
+        host = static_cast<char*>(ctx->staging[0]);
+    }
+    size_t at = 0;
+    for (FusedJob& j : jobs) {
+        if (j.merged || !j.h_scales) continue;
+        const size_t nb = size_t(j.n_params) * 8;
+        if (staged) {
+            std::memcpy(host + at, j.h_scales, nb);
+            std::memcpy(host + at + nb, j.h_zps, nb);
+        } else {
+            copy_in(ctx, dev + at, j.h_scales, nb, VF_MEM_HOST);
+            copy_in(ctx, dev + at + nb, j.h_zps, nb, VF_MEM_HOST);
+        }
+        j.a.given_scales = reinterpret_cast<const double*>(dev + at);
+        j.a.given_zps = reinterpret_cast<const int64_t*>(dev + at + nb);
+        at += 2 * nb;
+    }
+    if (staged) {
+        VF_CUDA(cudaMemcpyAsync(dev, host, total, cudaMemcpyHostToDevice, ctx->stream));
+        VF_CUDA(cudaEventRecord(ctx->staging_ev[0], ctx->stream));
     }
 }
 

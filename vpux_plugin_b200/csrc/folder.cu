@@ -48,11 +48,12 @@ __global__ void __launch_bounds__(256) k_hash128(const uint8_t* __restrict__ p, 
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
     uint64_t h1 = 0, h2 = 0;
     constexpr uint64_t K = 0x9E3779B97F4A7C15ull, K2 = 0xD6E8FEB86659FD93ull;
-    // word w enters as mix(word ^ (w + 1) * K); the second sum reuses the mixed value with one more multiply
+    // word w enters the first sum as mix(word ^ (w + 1) * K) and the second one through a mix of its own (a
+    // different key, another multiplier), so the two halves are independent functions of the (word, index) pairs
+    constexpr uint64_t K3 = 0xA0761D6478BD642Full;
     auto add = [&](uint64_t kw, uint64_t v) {
-        const uint64_t x = mix64(v ^ kw);
-        h1 += x;
-        h2 += (x ^ (x >> 29)) * K2;
+        h1 += mix64(v ^ kw);
+        h2 += mix64((v ^ kw ^ K2) + K3) * K3;
     };
     const unsigned mis = unsigned(reinterpret_cast<uintptr_t>(p) & 15u);
     if (mis == 0) {
@@ -96,7 +97,7 @@ void hash_device(vf_ctx* ctx, const void* d, uint64_t nbytes, uint64_t out[2]) {
     VF_CUDA(cudaMemsetAsync(acc.p, 0, 16, ctx->stream));
     const uint64_t words = (nbytes + 7) / 8;
     if (words) {
-        const uint64_t blocks = std::min<uint64_t>((words / 2 + 255) / 256 + 1, 148 * 8);
+        const uint64_t blocks = std::min<uint64_t>((words / 2 + 255) / 256 + 1, uint64_t(ctx->sm_count) * 8);
         k_hash128<<<int(blocks), 256, 0, ctx->stream>>>(static_cast<const uint8_t*>(d), nbytes, acc.as<unsigned long long>());
         VF_CUDA(cudaGetLastError());
         ++ctx->launches;

@@ -23,9 +23,9 @@ struct FusedJob {
     int kind = 0;  // rowquant_kind
     OutStage tc, ts, tz, t16, t4, td;
     uint64_t out_bytes = 0, dq_bytes = 0;
-    // parameterised Quantize (fused_prepare_given): device copies of the attribute's scales / zero points, where
-    // the host arrays are (to recognise two lists over the same constant), and which output the destination is
-    DBuf gscales, gzps;
+    // parameterised Quantize (fused_prepare_given): where the attribute's scales / zero points are on the host (also
+    // to recognise two lists over the same constant), and which output the destination is. Their device copies
+    // are made for all jobs of a launch at once (fused_upload_params).
     const double* h_scales = nullptr;
     const int64_t* h_zps = nullptr;
     int64_t n_params = 0;
@@ -49,6 +49,10 @@ bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* 
 // Two jobs of a batch that quantize the same constant with the same parameters, one for the codes and one for
 // the dequantized copy, become one entry of the launch: the input is read once for both outputs.
 void fused_merge_pairs(std::vector<FusedJob>& jobs);
+// Copies the supplied scales / zero points of all (unmerged) jobs to the device in ONE transfer through the
+// context's pinned staging buffer and points the jobs at their slices; `holder` owns the device memory and must
+// outlive the launch's enqueue.
+void fused_upload_params(vf_ctx* ctx, std::vector<FusedJob>& jobs, DBuf& holder);
 // Launches jobs[begin, end): consecutive compatible jobs share one kernel launch.
 void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end);
 // Copies host-bound outputs out (asynchronously on the context's stream) and reports sizes.

@@ -88,6 +88,12 @@ struct OffsetsJob {
 };
 void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs);
 
+// Makes the runtime load the kernels of the three launchers above (cudaFuncGetAttributes, nothing is launched):
+// module loading may allocate device memory, which vf_sparsify_noalloc must not do once the embedder owns the GPU.
+void preload_sparsity_kernels();
+// Set-up of vf_sparsify_noalloc for a new context (noalloc.cu); the context's device is current.
+void noalloc_prepare(vf_ctx* ctx);
+
 // ---- statistics --------------------------------------------------------------------------------------
 // min/max (over values and 0) or absmax per unit of `unit_len` consecutive elements, then
 // calcScaleAndZeroPoint. Any output may be NULL.

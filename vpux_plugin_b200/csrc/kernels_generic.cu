@@ -12,8 +12,9 @@ constexpr int kBlock = 256;
 
 inline int grid_for(int64_t n, int per_thread = 1) {
     const int64_t blocks = (n + int64_t(kBlock) * per_thread - 1) / (int64_t(kBlock) * per_thread);
-    // grid-stride loops: cap at a few waves of the 148 SMs
-    return int(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+    // grid-stride loops: cap at a few waves of the device's SMs
+    const int64_t cap = int64_t(sm_count_hint()) * 16;
+    return int(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
 inline bool aligned16(const void* a, const void* b) {
@@ -1192,7 +1193,7 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
         const int64_t chunk = int64_t(kRowUnroll) * kBlock, chunks_per_row = (row_len + chunk - 1) / chunk;
         if (row_len >= chunk && row_len < (int64_t(1) << 31) && n_rows * chunks_per_row < (int64_t(1) << 31)) {
             const int64_t n_chunks = n_rows * chunks_per_row;
-            const int rgrid = int(n_chunks < 148 * 16 ? n_chunks : 148 * 16);
+            const int rgrid = int(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * 16));
             using I = uint32_t;
 #define VF_Q8R(IN)                                                                                                                      \
     if (fast)                                                                                                                           \
@@ -1239,7 +1240,7 @@ void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, fl
         const int64_t chunk = int64_t(kRowUnroll) * kBlock, chunks_per_row = (row_len + chunk - 1) / chunk;
         if (row_len >= chunk && row_len < (int64_t(1) << 31) && n_rows * chunks_per_row < (int64_t(1) << 31)) {
             const int64_t n_chunks = n_rows * chunks_per_row;
-            const int rgrid = int(n_chunks < 148 * 16 ? n_chunks : 148 * 16);
+            const int rgrid = int(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * 16));
             using I = uint32_t;
             if (in_dt == VF_DT_I8)
                 k_dequantize8_rows<VF_DT_I8, I><<<rgrid, kBlock, 0, ctx->stream>>>(in, out, I(n_rows), I(chunks_per_row), d_scales, d_zps,
@@ -1510,11 +1511,20 @@ void launch_subview(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
     post_launch(ctx);
 }
 
+void preload_sparsity_kernels() {
+    cudaFuncAttributes a;
+    VF_CUDA(cudaFuncGetAttributes(&a, k_sparsity_scan));
+    VF_CUDA(cudaFuncGetAttributes(&a, k_sparse_offsets));
+    VF_CUDA(cudaFuncGetAttributes(&a, k_sparse_compact<1>));
+    VF_CUDA(cudaFuncGetAttributes(&a, k_sparse_compact<2>));
+    VF_CUDA(cudaFuncGetAttributes(&a, k_sparse_compact<4>));
+}
+
 void launch_sparsity_scan(vf_ctx* ctx, const void* in, int dt, int64_t oc, int64_t work, int64_t sparse_value,
                           int64_t* d_counts, uint8_t* d_map, int64_t map_row_bytes) {
     if (oc <= 0) return;
     const int64_t blocks = (oc + 7) / 8;  // 8 warps per block, one channel per warp
-    k_sparsity_scan<<<int(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value,
+    k_sparsity_scan<<<int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * 8)), 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value,
                                                                                       d_counts, d_map, map_row_bytes);
     post_launch(ctx);
 }
@@ -1528,7 +1538,7 @@ void launch_sparse_compact(vf_ctx* ctx, const void* in, int dt, int64_t oc, int6
                            const int64_t* d_offsets, uint8_t* out, uint64_t capacity) {
     if (oc <= 0) return;
     const int64_t blocks = (oc + 7) / 8;
-    const int grid = int(blocks > 148 * 8 ? 148 * 8 : blocks);
+    const int grid = int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * 8));
     const int es = dtype_bits(dt) / 8;
     switch (es) {
     case 1: k_sparse_compact<1><<<grid, 256, 0, ctx->stream>>>(in, dt, oc, work, sparse_value, d_offsets, out, capacity, ctx->d_flags); break;
@@ -1542,7 +1552,7 @@ void launch_unit_stats(vf_ctx* ctx, const void* in, int in_dt, int64_t units, in
                        int64_t qmin, int64_t qmax, double* d_scales, int64_t* d_zps, float* d_rmin, float* d_rmax) {
     if (units <= 0) return;
     const int64_t blocks = (units + 7) / 8;
-    k_unit_stats<<<int(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, ctx->stream>>>(
+    k_unit_stats<<<int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * 16)), 256, 0, ctx->stream>>>(
             in, in_dt, units, unit_len, range_mode, qmin, qmax, d_scales, d_zps, d_rmin, d_rmax, ctx->d_flags);
     post_launch(ctx);
 }

@@ -328,7 +328,7 @@ void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d
     }
     DBuf table;
     const SparseJob* d_jobs = static_cast<const SparseJob*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(SparseJob), table));
-    const int grid = int(std::min<int64_t>((units + kWarps - 1) / kWarps, int64_t(148) * 8));
+    const int grid = int(std::min<int64_t>((units + kWarps - 1) / kWarps, int64_t(ctx->sm_count) * 8));
     const int njobs = int(jobs.size());
     k_sparse_scan_batch<<<grid, kWarps * 32, 0, ctx->stream>>>(d_jobs, njobs, units);
     VF_CUDA(cudaGetLastError());

@@ -13,38 +13,35 @@
 // are read, nothing relies on zeros), and two calls that overlap on the GPU — different contexts or streams on
 // the same device — would overwrite each other's offsets. Callers must serialise their calls per device.
 //
-// Set-up: the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
-// device current) and remembers it. Make that first call before starting any stream capture on the device.
-#include <mutex>
-
+// Set-up happens in vf_ctx_create, not in the entry point: with the context's device current it looks up the
+// array's device address (cudaGetSymbolAddress; in host code the array's name is only a handle for the runtime, not
+// an address a kernel could use) and makes the runtime load the three kernels the entry point launches. Loading a
+// module lets the driver allocate device memory for its code and for this array, which is exactly what must not
+// happen later inside the embedder's allocation-free phase — so create the context before the embedder's allocator
+// claims the GPU, and before any stream capture. The address is kept in the context: a context created after a
+// cudaDeviceReset looks it up again.
 #include "kernels.h"
 
 namespace {
 
 constexpr int64_t kMaxOC = VF_NOALLOC_MAX_OC;
-constexpr int kMaxDevices = 64;
 
 // counts[kMaxOC] followed by offsets[kMaxOC + 1], both int64
 static __device__ __align__(256) unsigned char g_noalloc_scratch[(2 * kMaxOC + 1) * 8 + 248];
 
-// `g_noalloc_scratch` in host code is only a handle for the runtime, not an address a kernel can use: the
-// device address is looked up once per device with that device current.
-std::mutex g_mu;
-void* g_scratch_dev[kMaxDevices] = {nullptr};
+}  // namespace
 
-void* scratch_for_device(int device) {
-    if (device < 0 || device >= kMaxDevices) vf::raise(VF_ERR_INVALID_ARG, "device index %d outside 0..%d", device, kMaxDevices - 1);
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (!g_scratch_dev[device]) {
-        void* p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // caller made `device` current
-        if (e != cudaSuccess || !p) vf::raise(VF_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(e));
-        g_scratch_dev[device] = p;
-    }
-    return g_scratch_dev[device];
+namespace vf {
+
+void noalloc_prepare(vf_ctx* ctx) {  // the context's device is current
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) raise(VF_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(e));
+    ctx->noalloc_scratch = p;
+    preload_sparsity_kernels();
 }
 
-}  // namespace
+}  // namespace vf
 
 extern "C" int vf_sparsify_noalloc(vf_ctx* ctx, const void* weights, int32_t dtype, int64_t oc, int64_t work,
                                    int64_t sparse_value, void* data, uint64_t data_bytes, uint64_t* data_written,
@@ -69,7 +66,8 @@ extern "C" int vf_sparsify_noalloc(vf_ctx* ctx, const void* weights, int32_t dty
 
         std::unique_lock<std::mutex> lock(ctx->mu);
         DeviceGuard dev(ctx->device);
-        unsigned char* scratch = static_cast<unsigned char*>(scratch_for_device(ctx->device));
+        unsigned char* scratch = static_cast<unsigned char*>(ctx->noalloc_scratch);
+        if (!scratch) raise(VF_ERR_INVALID_ARG, "context without the built-in scratch");
         int64_t* d_counts = counts ? counts : reinterpret_cast<int64_t*>(scratch);
         int64_t* d_offsets = reinterpret_cast<int64_t*>(scratch + size_t(kMaxOC) * 8);
 
@@ -84,11 +82,10 @@ extern "C" int vf_sparsify_noalloc(vf_ctx* ctx, const void* weights, int32_t dty
             VF_CUDA(cudaStreamSynchronize(ctx->stream));
             total_host = uint64_t(total);
         }
+        if (data_written) *data_written = total_host;  // also when the buffer is too small: the size that is needed
         if (data && total_host > data_bytes) {
-            VF_CUDA(cudaStreamSynchronize(ctx->stream));
             raise(VF_ERR_BUFFER_TOO_SMALL, "compressed weights need %llu bytes, buffer holds %llu", (unsigned long long)total_host, (unsigned long long)data_bytes);
         }
         flags_check(ctx);  // synchronises
-        if (data_written) *data_written = total_host;
     });
 }

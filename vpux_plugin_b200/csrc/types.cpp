@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cmath>
 #include <limits>
+#include <unordered_map>
 
 #include "common.h"
 
@@ -63,6 +64,17 @@ void order_to_perm(uint32_t order, int rank, int* perm) {
 }
 
 // ------------------------------------------------------------------------------------------------------
+namespace {
+thread_local std::unordered_map<const double*, int64_t> tl_checked;
+thread_local int tl_check_depth = 0;
+}  // namespace
+ParamCheckScope::ParamCheckScope() {
+    if (tl_check_depth++ == 0) tl_checked.clear();
+}
+ParamCheckScope::~ParamCheckScope() {
+    if (--tl_check_depth == 0) tl_checked.clear();
+}
+
 Elem Elem::from(const vf_elem_type& e) {
     Elem r;
     r.kind = e.kind;
@@ -76,12 +88,17 @@ Elem Elem::from(const vf_elem_type& e) {
     r.qmax = e.qmax;
     if (!e.scales || !e.zps || e.nparams < 1) raise(VF_ERR_INVALID_ARG, "quantized element type without scales/zero points");
     if (e.kind == VF_ELEM_QUANT_UNIFORM && e.nparams != 1) raise(VF_ERR_SHAPE, "uniform quantized type takes exactly one scale");
-    r.scales.assign(e.scales, e.scales + e.nparams);
-    r.zps.assign(e.zps, e.zps + e.nparams);
+    r.scales.borrow(e.scales, size_t(e.nparams));
+    r.zps.borrow(e.zps, size_t(e.nparams));
     // a quantized type cannot be built with such a scale: mlir::quant::UniformQuantized[PerAxis]Type::verify
     // rejects scale <= 0, infinities and NaN ("illegal scale")
-    for (double sc : r.scales)
+    if (tl_check_depth > 0 && e.nparams > 64) {
+        const auto it = tl_checked.find(e.scales);
+        if (it != tl_checked.end() && it->second >= e.nparams) return r;
+    }
+    for (const double sc : r.scales)
         if (!(sc > 0.0) || std::isinf(sc)) raise(VF_ERR_INVALID_ARG, "illegal scale: %g", sc);
+    if (tl_check_depth > 0 && e.nparams > 64) tl_checked[e.scales] = e.nparams;
     return r;
 }
 
@@ -301,8 +318,8 @@ Type infer_one(const Type& in, bool in_splat, const vf_transform& t, bool& out_s
                 int64_t zp;
                 if (!in.elem.single_zp(zp)) raise(VF_ERR_ZERO_POINTS, "All zero points should be equal");
                 out.elem.scales.assign(size_t(pb), in.elem.scales.front());
-                out.elem.scales.insert(out.elem.scales.end(), in.elem.scales.begin(), in.elem.scales.end());
-                out.elem.scales.insert(out.elem.scales.end(), size_t(pa), in.elem.scales.back());
+                out.elem.scales.append(in.elem.scales.begin(), in.elem.scales.end());
+                out.elem.scales.append(size_t(pa), in.elem.scales.back());
                 out.elem.zps.assign(out.elem.scales.size(), zp);
             }
         }
@@ -493,6 +510,7 @@ const char* vf_status_string(int s) {
     case VF_ERR_RANGE: return "value outside representable range";
     case VF_ERR_QUANT_RANGE: return "cannot derive scale / zero point from range";
     case VF_ERR_NOT_NORMAL: return "inverse of a non-normal float";
+    case VF_ERR_NAN: return "NaN met by Quantize";
     case VF_ERR_CUDA: return "CUDA error";
     case VF_ERR_NO_DEVICE: return "no CUDA device";
     case VF_ERR_OOM: return "out of memory";

@@ -122,14 +122,15 @@ def optimize_transforms(base_type, transforms, n, params_cap=1 << 16):
 class Library:
     """One vf_ctx (device + stream + scratch pool)."""
 
-    def __init__(self, device=0, stream=None, disable_fusion=False, staging_bytes=0, pipelined=False):
+    def __init__(self, device=0, stream=None, disable_fusion=False, staging_bytes=0, pipelined=False, timing=False):
         """pipelined=True sets VF_OPT_ASYNC: batch calls over device memory return once enqueued; call
-        synchronize() to wait and to learn what their kernels reported."""
+        synchronize() to wait and to learn what their kernels reported. timing=True sets VF_OPT_TIMING:
+        synchronous calls report their device time in last_stats.device_ms."""
         self.lib = raw()
         self.ctx = C.c_void_p()
         opts = abi.Options()
         opts.staging_bytes = staging_bytes
-        opts.flags = (1 if disable_fusion else 0) | (2 if pipelined else 0)
+        opts.flags = (1 if disable_fusion else 0) | (2 if pipelined else 0) | (4 if timing else 0)
         err = C.create_string_buffer(512)
         st = self.lib.vf_ctx_create(int(device), C.byref(opts), C.c_void_p(stream) if stream else None,
                                     C.byref(self.ctx), err, C.c_size_t(512))
