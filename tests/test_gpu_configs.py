@@ -250,3 +250,118 @@ def test_c5_llama3_70b_slab_full_size_spot_checked(gpu, oracle):
     assert torch.allclose(deq, codes.double() * side["scales"].view(-1, 1), rtol=2 ** -10, atol=1e-7)
     del outs, keep
     torch.cuda.empty_cache()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# whole-output digests: every byte of a full-size output is compared, through the 128-bit content hash
+# ---------------------------------------------------------------------------------------------------------
+def _mix64(z):
+    z = z ^ (z >> np.uint64(33))
+    z = z * np.uint64(0xFF51AFD7ED558CCD)
+    z = z ^ (z >> np.uint64(33))
+    z = z * np.uint64(0xC4CEB9FE1A85EC53)
+    return z ^ (z >> np.uint64(33))
+
+
+def hash128_host(buf):
+    """vf_content_hash restated with numpy (sums of mixed (word, index) pairs over the 8-byte words, length mixed in
+    last), for hashing the oracle's outputs."""
+    b = np.ascontiguousarray(buf).view(np.uint8).reshape(-1)
+    n = b.size
+    if n % 8:
+        b = np.concatenate([b, np.zeros(8 - n % 8, np.uint8)])
+    v = b.view(np.uint64)
+    K, K2, K3 = np.uint64(0x9E3779B97F4A7C15), np.uint64(0xD6E8FEB86659FD93), np.uint64(0xA0761D6478BD642F)
+    with np.errstate(over="ignore"):
+        kw = np.arange(1, v.size + 1, dtype=np.uint64) * K
+        h1 = _mix64(v ^ kw).sum(dtype=np.uint64)
+        h2 = (_mix64((v ^ kw ^ K2) + K3) * K3).sum(dtype=np.uint64)
+        return int(_mix64(h1 ^ np.uint64(n))), int(_mix64(h2 + np.uint64(n)))
+
+
+def _device_hash(gpu, t):
+    from vpux_plugin_b200.lib import content_hash
+    n = int(t.numel() * t.element_size())
+    c, k = abi.make_content(TType([n], abi.VF_DT_U8), None, abi.VF_DT_U8, False, abi.VF_MEM_DEVICE, ptr=t.data_ptr(), nbytes=n)
+    return content_hash(gpu, c)
+
+
+def test_hash_restatement_matches_the_device_hash(gpu):
+    import torch
+    rng = np.random.default_rng(5)
+    for n in (1, 7, 8, 4096, 100003):
+        x = rng.integers(0, 256, n).astype(np.uint8)
+        t = torch.from_numpy(x).cuda()
+        assert _device_hash(gpu, t) == hash128_host(x), n
+
+
+def test_c4_whole_tensor_digest(gpu, oracle_mt):
+    """Every byte of the folded lm_head (32000 x 4096 fp16 -> 65.5 MB of packed codes, 1 M scales and zero points):
+    the device hash of the GPU's outputs against the same hash of the oracle's."""
+    import torch
+    t = wl.llama2_7b_tensors()[-1]
+    assert t.name == "lm_head"
+    seed = wl.SEEDS["c4"]
+    outs, keep = _device_batch(gpu, torch, [t], seed, wl.spec_u4_group(128), [wl.t_bitpack()], True)
+    dst, side, _, rows, cols = outs[0]
+    n = rows * cols
+    x = oracle_mt.synth_fill(t.synth_spec(seed, 0), n)
+    c, k = abi.make_content(TType([rows, cols], t.dtype), x)
+    ref = np.zeros(n // 2, np.uint8)
+    o, res = _outs(n // 128, f16=True, u4=True)
+    oracle_mt.quantize_fold(c, wl.spec_u4_group(128), abi.make_transforms([wl.t_bitpack()]), 1, ref, ref.size, o)
+    assert _device_hash(gpu, dst) == hash128_host(ref)
+    assert _device_hash(gpu, side["f16"]) == hash128_host(res["f16"])
+    assert _device_hash(gpu, side["u4"]) == hash128_host(res["u4"])
+
+
+@pytest.mark.parametrize("name,slab", [("l0.k", 0), ("l0.q", 3), ("l0.down", 7)])
+def test_c5_whole_slab_digest(gpu, oracle_mt, name, slab):
+    """One whole output-channel slab per row width of the per-channel kernel (8192 columns on 64 and 128 threads'
+    rows, 28672 columns on 256): codes, dequantized fp16 copy and scales, every byte through the digest."""
+    import torch
+    from vpux_plugin_b200.lib import plan_shards
+    tensors = wl.llama3_70b_tensors(layers=1)
+    t = [x for x in tensors if x.name == name][0]
+    rb, re_ = plan_shards(1, 8, [t.nbytes], [t.rows], 1)
+    r0, r1 = int(rb[0, slab]), int(re_[0, slab])
+    seed = wl.SEEDS["c5"]
+    outs, keep = _device_batch(gpu, torch, [t], seed, wl.spec_i8_sym(abi.VF_DT_F16), [], False, [(r0, r1)])
+    dst, side, _, rows, cols = outs[0]
+    n = rows * cols
+    x = oracle_mt.synth_fill(t.synth_spec(seed, r0 * cols), n)
+    c, k = abi.make_content(TType([rows, cols], t.dtype), x)
+    ref = np.zeros(n, np.uint8)
+    o, res = _outs(rows)
+    dq = np.zeros(n, np.uint16)
+    o.dequant, o.dequant_dtype, o.dequant_bytes = dq.ctypes.data, abi.VF_DT_F16, dq.nbytes
+    oracle_mt.quantize_fold(c, wl.spec_i8_sym(abi.VF_DT_F16), abi.make_transforms([]), 0, ref, ref.size, o)
+    assert _device_hash(gpu, dst) == hash128_host(ref)
+    assert _device_hash(gpu, side["dequant"]) == hash128_host(dq)
+    assert _device_hash(gpu, side["scales"]) == hash128_host(res["scales"])
+
+
+def test_c5_first_and_last_rows_of_every_slab(gpu, oracle):
+    """The rows at both ends of all eight output-channel slabs of one tensor of each shape."""
+    import torch
+    from vpux_plugin_b200.lib import plan_shards
+    tensors = wl.llama3_70b_tensors(layers=1)
+    seed = wl.SEEDS["c5"]
+    for t in [x for x in tensors if x.name in ("l0.q", "l0.k", "l0.gate", "l0.down", "lm_head")]:
+        rb, re_ = plan_shards(1, 8, [t.nbytes], [t.rows], 1)
+        cols = t.row_len
+        for slab in range(8):
+            r0, r1 = int(rb[0, slab]), int(re_[0, slab])
+            for a, b in ((r0, r0 + 2), (r1 - 2, r1)):
+                outs, keep = _device_batch(gpu, torch, [t], seed, wl.spec_i8_sym(abi.VF_DT_F16), [], False, [(a, b)])
+                dst, side, _, rows, _ = outs[0]
+                x = oracle.synth_fill(t.synth_spec(seed, a * cols), rows * cols)
+                c, k = abi.make_content(TType([rows, cols], t.dtype), x)
+                ref = np.zeros(rows * cols, np.uint8)
+                o, res = _outs(rows)
+                dq = np.zeros(rows * cols, np.uint16)
+                o.dequant, o.dequant_dtype, o.dequant_bytes = dq.ctypes.data, abi.VF_DT_F16, dq.nbytes
+                oracle.quantize_fold(c, wl.spec_i8_sym(abi.VF_DT_F16), abi.make_transforms([]), 0, ref, ref.size, o)
+                assert np.array_equal(dst.cpu().numpy(), ref), (t.name, slab, a)
+                assert np.array_equal(side["dequant"].cpu().numpy().view(np.uint16), dq), (t.name, slab, a)
+                assert np.array_equal(side["scales"].cpu().numpy(), res["scales"]), (t.name, slab, a)

@@ -221,6 +221,7 @@ def test_device_resident_fold_of_a_list(gpu, oracle):
     for setup, nbytes in ((ContentSetup(t).quantize(q), rows * cols), (ContentSetup(t).quantize(q).castElemType(q).dequantize(), rows * cols * 2)):
         tr, n = setup.transforms()
         dst = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()  # the fill runs on torch's stream, the library on its own
         w, _ = gpu.fold(c, tr, n, dst.data_ptr(), nbytes, dst_mem_kind=abi.VF_MEM_DEVICE)
         assert gpu.last_stats.fused == 1 and gpu.last_stats.kernels_launched == 1
         ref = ContentAttr(x, t, setup).fold(oracle)

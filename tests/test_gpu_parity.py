@@ -671,6 +671,7 @@ def test_pipelined_batches_defer_kernel_errors_to_the_next_synchronisation(oracl
     def job(scales):
         d, keep = wl.weights_table_desc(oc, scales, 576)
         tab = torch.full((oc * 4,), -1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()  # the fill runs on torch's stream, the library on its own
         jobs = (abi.WeightsTableJob * 1)()
         jobs[0].desc, jobs[0].table = d, tab.data_ptr()
         return jobs, tab, d, keep
@@ -959,6 +960,7 @@ def test_fold_into_device_memory_matches_fold_into_host_memory(gpu):
                 dst = src.view(torch.uint8).reshape(-1)
             else:
                 dst = torch.full((cap + 64,), 0xAB, dtype=torch.uint8, device="cuda")
+                torch.cuda.synchronize()  # the fill runs on torch's stream, the library on its own
             written, ftype = gpu.fold(c, tr, n, dst.data_ptr(), cap, dst_mem_kind=abi.VF_MEM_DEVICE)
             torch.cuda.synchronize()
             out = dst.cpu().numpy().reshape(-1)

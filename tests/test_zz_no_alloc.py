@@ -41,8 +41,10 @@ def _run_pair(gpu, oracle, torch, rng, oc, work, dtype, np_dtype, density):
     xd = torch.from_numpy(x.view(np.uint8).copy()).to(dev)
 
     def bufs():
-        return (torch.full((cap,), 0xAB, dtype=torch.uint8, device=dev), torch.full((oc * row,), 0xCD, dtype=torch.uint8, device=dev),
-                torch.full((oc,), -7, dtype=torch.int64, device=dev))
+        b = (torch.full((cap,), 0xAB, dtype=torch.uint8, device=dev), torch.full((oc * row,), 0xCD, dtype=torch.uint8, device=dev),
+             torch.full((oc,), -7, dtype=torch.int64, device=dev))
+        torch.cuda.synchronize()  # the fills run on torch's stream, the library on its own: finish them first
+        return b
 
     # existing entry point, device outputs
     d0, m0, c0 = bufs()
@@ -103,9 +105,11 @@ def test_noalloc_requests_no_device_memory_and_handles_the_limit(gpu):
     d0 = torch.zeros(cap, dtype=torch.uint8, device=dev)
     m0 = torch.zeros(oc * row, dtype=torch.uint8, device=dev)
     c0 = torch.zeros(oc, dtype=torch.int64, device=dev)
+    torch.cuda.synchronize()  # the fills run on torch's stream, the library on its own
     content, keep = abi.make_content(TType([oc, work, 1, 1], abi.VF_DT_U8), None, ptr=xd.data_ptr(), nbytes=oc * work, mem_kind=abi.VF_MEM_DEVICE)
     w0 = gpu.sparsify(content, d0.data_ptr(), m0.data_ptr(), c0.data_ptr(), out_mem_kind=abi.VF_MEM_DEVICE, data_bytes=cap, map_bytes=oc * row)
     d1, m1 = torch.zeros_like(d0), torch.zeros_like(m0)
+    torch.cuda.synchronize()
     st, w, msg = _noalloc(gpu, xd.data_ptr(), abi.VF_DT_U8, oc, work, d1.data_ptr(), cap, m1.data_ptr(), oc * row, None)  # warm-up
     assert st == 0, msg
     d1.zero_()

@@ -1202,18 +1202,23 @@ int rowquant_kind(const RowQuantArgs& a) {
             return 1;
         return 0;
     }
-    if (two_byte && aligned16 && a.khw == 0 && a.rows_pad == a.rows && !a.pack4 && !a.zps_u4 && a.cols % 8 == 0 &&
-        a.cols >= 1024 && a.cols <= 96 * 1024 && reinterpret_cast<uintptr_t>(a.codes) % 8 == 0 &&
-        (!a.dequant || reinterpret_cast<uintptr_t>(a.dequant) % 16 == 0))
-        return 2;
+    const bool row_ok = two_byte && aligned16 && a.khw == 0 && a.rows_pad == a.rows && !a.pack4 && !a.zps_u4 && a.cols % 8 == 0 &&
+                        a.cols >= 1024 && a.cols <= 96 * 1024 && reinterpret_cast<uintptr_t>(a.codes) % 8 == 0 &&
+                        (!a.dequant || reinterpret_cast<uintptr_t>(a.dequant) % 16 == 0);
+    bool convv_ok = false, conv_ok = false;
     if (!a.pack4 && !a.dequant && !a.zps_u4 && a.codes) {
         const int64_t out_row = a.khw > 0 ? a.khw * a.ic_pad : a.cols;
         const int64_t ic = a.khw > 0 ? a.ic : a.cols, ic_pad = a.khw > 0 ? a.ic_pad : a.cols;
-        if (two_byte && aligned16 && a.cols % 8 == 0 && a.cols <= 4608 && out_row <= 4608 && ic % 4 == 0 && ic_pad % 4 == 0 &&
-            reinterpret_cast<uintptr_t>(a.codes) % 4 == 0)
-            return 4;
-        if (out_row <= 24 * 1024) return 3;
+        convv_ok = two_byte && aligned16 && a.cols % 8 == 0 && a.cols <= 4608 && out_row <= 4608 && ic % 4 == 0 && ic_pad % 4 == 0 &&
+                   reinterpret_cast<uintptr_t>(a.codes) % 4 == 0;
+        conv_ok = out_row <= 24 * 1024;
     }
+    // a convolution weight (it came with an OIYX -> OYXI reorder: ic is set) stays with the other convolutions of its
+    // network in one launch, also where its 1x1 rows would suit the row kernel
+    if (convv_ok && a.ic > 0) return 4;
+    if (row_ok) return 2;
+    if (convv_ok) return 4;
+    if (conv_ok) return 3;
     return 0;
 }
 
