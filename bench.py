@@ -1058,7 +1058,8 @@ def next_arm(args):
         if sample is None:
             continue
         ts, host, sb = sample
-        htr, hn = build(ContentSetup(ts)).transforms()
+        hsetup = build(ContentSetup(ts))  # keeps the attribute's parameter arrays alive
+        htr, hn = hsetup.transforms()
         hc, hkeep = abi.make_content(ts, host, storage, False)
         _, _, hob = orc.infer_type(ts, False, htr, hn)
         hdst = np.zeros(max(hob, 1), np.uint8)
