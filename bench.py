@@ -561,6 +561,9 @@ def seam_c5(torch, lib, case, steps, warmup, stream, peak):
     torch.cuda.synchronize()
     launches = lib.launch_count - l0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # steady state of a pipelined pass: the timed region starts when an untimed call's kernels end, so the host-side
+    # preparation of every timed call (milliseconds for 1124 jobs) overlaps the kernels of the call before it
+    fn()
     e0.record(stream)
     t0 = time.perf_counter()
     for _ in range(steps):

@@ -241,6 +241,14 @@ struct vf_ctx {
     cudaMemPool_t pool = nullptr;  // scratch comes from a pool the context owns (the device's default pool stays untouched)
     void* noalloc_scratch = nullptr;  // device address of vf_sparsify_noalloc's built-in array on this device
     cudaEvent_t time_ev[2] = {nullptr, nullptr};  // VF_OPT_TIMING
+    // device copies of supplied quantization parameters: two persistent buffers used in turn, filled on the second
+    // stream so that the upload for one call overlaps the kernels of the call before it
+    void* param_dev[2] = {nullptr, nullptr};
+    size_t param_cap[2] = {0, 0};
+    cudaEvent_t param_ready_ev = nullptr;             // the upload has landed
+    cudaEvent_t param_used_ev[2] = {nullptr, nullptr};  // the kernels that read buffer k have been enqueued before this
+    bool param_used[2] = {false, false};
+    int param_turn = 0;
     bool conv_smem_set = false;  // dynamic shared memory limit of the conv kernel raised on this device
     // vf_fold, last transformation, device destination: the output buffer may be the destination itself, which
     // saves the final copy (see alloc_like)

@@ -179,6 +179,8 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
             VF_CUDA(cudaMemPoolCreate(&c->pool, &props));
             uint64_t thr = UINT64_MAX;
             VF_CUDA(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thr));
+            VF_CUDA(cudaEventCreateWithFlags(&c->param_ready_ev, cudaEventDisableTiming));
+            for (int k = 0; k < 2; ++k) VF_CUDA(cudaEventCreateWithFlags(&c->param_used_ev[k], cudaEventDisableTiming));
             if (c->opt_flags & VF_OPT_TIMING)
                 for (int k = 0; k < 2; ++k) VF_CUDA(cudaEventCreate(&c->time_ev[k]));
             vf::noalloc_prepare(c);
@@ -206,8 +208,12 @@ void vf_ctx_destroy(vf_ctx* c) {
     for (int k = 0; k < 2; ++k)
         if (c->lane_ev[k]) cudaEventDestroy(c->lane_ev[k]);
     if (c->lane_stream) cudaStreamDestroy(c->lane_stream);
-    for (int k = 0; k < 2; ++k)
+    for (int k = 0; k < 2; ++k) {
         if (c->time_ev[k]) cudaEventDestroy(c->time_ev[k]);
+        if (c->param_used_ev[k]) cudaEventDestroy(c->param_used_ev[k]);
+        if (c->param_dev[k]) cudaFree(c->param_dev[k]);
+    }
+    if (c->param_ready_ev) cudaEventDestroy(c->param_ready_ev);
     if (c->pool) cudaMemPoolDestroy(c->pool);
     if (c->own_stream && c->main_stream) cudaStreamDestroy(c->main_stream);
     delete c;

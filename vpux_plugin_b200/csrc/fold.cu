@@ -999,6 +999,7 @@ uint64_t fold_one(vf_ctx* ctx, const vf_content& base, const vf_transform* t, in
             DBuf params;
             fused_upload_params(ctx, one, params);
             fused_launch(ctx, one, 0, 1);
+            fused_params_enqueued(ctx);
             uint64_t w = 0;
             fused_finish(ctx, one[0], &w, stats);
             return w;
@@ -1081,6 +1082,7 @@ int vf_fold_batch(vf_ctx* ctx, vf_fold_job* jobs, int njobs, const vf_fold_batch
             DBuf params;
             fused_upload_params(ctx, fused.jobs, params);
             fused_launch(ctx, fused.jobs, 0, fused.jobs.size());
+            fused_params_enqueued(ctx);
             for (size_t k = 0; k < fused.jobs.size(); ++k) {
                 uint64_t w = 0;
                 fused_finish(ctx, fused.jobs[k], &w, stats);

@@ -301,13 +301,29 @@ void fused_upload_params(vf_ctx* ctx, std::vector<FusedJob>& jobs, DBuf& holder)
     for (const FusedJob& j : jobs)
         if (!j.merged && j.h_scales) total += size_t(j.n_params) * 16;
     if (!total) return;
-    holder = DBuf(ctx, total);
-    char* dev = holder.as<char>();
     const bool staged = total <= ctx->staging_bytes;
+    char* dev = nullptr;
     char* host = nullptr;
+    int turn = 0;
     if (staged) {
-        VF_CUDA(cudaEventSynchronize(ctx->staging_ev[0]));  // the buffer's previous transfer is done
+        turn = ctx->param_turn ^= 1;
+        if (ctx->param_cap[turn] < total) {  // grow (rare): nothing may still read the old buffer
+            VF_CUDA(cudaStreamSynchronize(ctx->stream));
+            VF_CUDA(cudaStreamSynchronize(ctx->lane_stream));
+            if (ctx->param_dev[turn]) VF_CUDA(cudaFree(ctx->param_dev[turn]));
+            ctx->param_dev[turn] = nullptr;
+            ctx->param_cap[turn] = 0;
+            const size_t cap = std::max<size_t>(total + total / 4, size_t(1) << 20);
+            VF_CUDA(cudaMalloc(&ctx->param_dev[turn], cap));
+            ctx->param_cap[turn] = cap;
+            ctx->param_used[turn] = false;
+        }
+        dev = static_cast<char*>(ctx->param_dev[turn]);
+        VF_CUDA(cudaEventSynchronize(ctx->staging_ev[0]));  // the staging buffer's previous transfer is done
         host = static_cast<char*>(ctx->staging[0]);
+    } else {
+        holder = DBuf(ctx, total);
+        dev = holder.as<char>();
     }
     size_t at = 0;
     for (FusedJob& j : jobs) {
@@ -325,9 +341,20 @@ void fused_upload_params(vf_ctx* ctx, std::vector<FusedJob>& jobs, DBuf& holder)
         at += 2 * nb;
     }
     if (staged) {
-        VF_CUDA(cudaMemcpyAsync(dev, host, total, cudaMemcpyHostToDevice, ctx->stream));
-        VF_CUDA(cudaEventRecord(ctx->staging_ev[0], ctx->stream));
+        cudaStream_t up = ctx->lane_stream;
+        // the kernels that read this buffer two uploads ago must be done before it is overwritten
+        if (ctx->param_used[turn]) VF_CUDA(cudaStreamWaitEvent(up, ctx->param_used_ev[turn], 0));
+        VF_CUDA(cudaMemcpyAsync(dev, host, total, cudaMemcpyHostToDevice, up));
+        VF_CUDA(cudaEventRecord(ctx->staging_ev[0], up));
+        VF_CUDA(cudaEventRecord(ctx->param_ready_ev, up));
+        VF_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->param_ready_ev, 0));
+        ctx->param_used[turn] = true;  // fused_params_enqueued records the event
     }
+}
+
+void fused_params_enqueued(vf_ctx* ctx) {
+    const int turn = ctx->param_turn;
+    if (ctx->param_used[turn]) VF_CUDA(cudaEventRecord(ctx->param_used_ev[turn], ctx->stream));
 }
 
 void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end) {

@@ -49,10 +49,13 @@ bool fused_prepare_given(vf_ctx* ctx, const DContent& base, const vf_transform* 
 // Two jobs of a batch that quantize the same constant with the same parameters, one for the codes and one for
 // the dequantized copy, become one entry of the launch: the input is read once for both outputs.
 void fused_merge_pairs(std::vector<FusedJob>& jobs);
-// Copies the supplied scales / zero points of all (unmerged) jobs to the device in ONE transfer through the
-// context's pinned staging buffer and points the jobs at their slices; `holder` owns the device memory and must
-// outlive the launch's enqueue.
+// Copies the supplied scales / zero points of all (unmerged) jobs to the device in ONE transfer and points the jobs
+// at their slices. The transfer goes through the context's pinned staging buffer into one of two persistent
+// device buffers on the context's second stream, so in pipelined use it overlaps the previous call's kernels; the
+// launching stream waits for it. Call fused_params_enqueued once the launches that read the parameters are enqueued.
+// (`holder` owns the memory of the rare transfer that does not fit the staging buffer.)
 void fused_upload_params(vf_ctx* ctx, std::vector<FusedJob>& jobs, DBuf& holder);
+void fused_params_enqueued(vf_ctx* ctx);
 // Launches jobs[begin, end): consecutive compatible jobs share one kernel launch.
 void fused_launch(vf_ctx* ctx, std::vector<FusedJob>& jobs, size_t begin, size_t end);
 // Copies host-bound outputs out (asynchronously on the context's stream) and reports sizes.
