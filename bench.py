@@ -941,7 +941,7 @@ def next_arm(args):
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
-    lib = Library(device=0, stream=stream.cuda_stream)
+    lib = Library(device=0, stream=stream.cuda_stream, pipelined=True)
     orc = Oracle(nthreads=1)
     F32, F16, U8, I8, I32 = abi.VF_DT_F32, abi.VF_DT_F16, abi.VF_DT_U8, abi.VF_DT_I8, abi.VF_DT_I32
     TT = abi.TType
@@ -1001,16 +1001,18 @@ def next_arm(args):
         dst = torch.empty(out_bytes, dtype=torch.uint8, device=dev)
         for _ in range(max(3, args.warmup)):
             lib.fold(c, tr, n, dst.data_ptr(), out_bytes, dst_mem_kind=abi.VF_MEM_DEVICE)
+        lib.synchronize()
         torch.cuda.synchronize()
-        ms = 0.0
+        # the calls are pipelined (VF_OPT_ASYNC): each returns once its work is enqueued, so the stream runs the
+        # kernels of consecutive calls back to back and the per-call figure is device time, not launch latency
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
         for _ in range(args.steps):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
             lib.fold(c, tr, n, dst.data_ptr(), out_bytes, dst_mem_kind=abi.VF_MEM_DEVICE)
-            e1.record(stream)
-            torch.cuda.synchronize()
-            ms += e0.elapsed_time(e1)
-        ms /= args.steps
+        e1.record(stream)
+        lib.synchronize()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
         # the CPU oracle runs on a bounded sample of the same input AFTER all GPU timings (an idle GPU between two
         # kernels would drop its clocks): keep the sample's type and bytes
         sample = None

@@ -221,8 +221,8 @@ typedef struct vf_transform {
 typedef struct vf_ctx vf_ctx;
 
 #define VF_OPT_DISABLE_FUSION 1 /* run vf_quantize_fold through the unfused general kernels (for cross-checks) */
-/* Pipelined batches: vf_quantize_fold_batch and vf_weights_table_batch calls whose tensors ALL live in device
- * memory return as soon as their work is enqueued on the context's stream, so the host prepares the next
+/* Pipelined calls: vf_fold, vf_fold_batch, vf_quantize_fold_batch and vf_weights_table_batch calls whose tensors
+ * ALL live in device memory return as soon as their work is enqueued on the context's stream, so the host prepares the next
  * batch while the GPU runs this one (what the background folder does with its thread pool,
  * const/utils/constant_folding_in_background.cpp:154-194). Host-side checks (shapes, types, sizes) still fail
  * the call itself; what a kernel reports (a checked_cast, a range without zero, a table range) is returned by

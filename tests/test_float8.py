@@ -92,6 +92,27 @@ def test_float8_conversions_match_the_oracle(gpu, oracle, dt):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dt", [E4, E5])
+def test_float8_rounding_of_every_exponent_and_boundary(gpu, oracle, dt):
+    """Every sign, exponent and leading seven mantissa bits of a float (all rounding boundaries of a 2- or 3-bit
+    mantissa lie there, subnormal results included) with the bits below them all clear, lowest set, just below,
+    on and just above the half, and all set; from f32, and the f16 / bf16 values among them from their own type."""
+    hi = np.arange(65536, dtype=np.uint32) << 16
+    lows = np.array([0x0000, 0x0001, 0x7FFF, 0x8000, 0x8001, 0xFFFF], np.uint32)
+    vals = (hi[:, None] | lows[None, :]).reshape(-1).view(np.float32)
+    t = TType([len(vals)], F32)
+    a = ContentAttr(vals, t, ContentSetup(t).castElemType(dt)).fold(gpu).bytes()
+    b = ContentAttr(vals, t, ContentSetup(t).castElemType(dt)).fold(oracle).bytes()
+    assert np.array_equal(a, b), vals[np.nonzero(a != b)[0][:8]]
+    halves = np.arange(65536, dtype=np.uint16)
+    for src in (abi.VF_DT_F16, abi.VF_DT_BF16):
+        th = TType([65536], src)
+        a = ContentAttr(halves, th, ContentSetup(th).castElemType(dt)).fold(gpu).bytes()
+        b = ContentAttr(halves, th, ContentSetup(th).castElemType(dt)).fold(oracle).bytes()
+        assert np.array_equal(a, b), halves[np.nonzero(a != b)[0][:8]]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [E4, E5])
 def test_float8_sparsity(gpu, oracle, dt):
     rng = np.random.default_rng(dt)
     shape = [24, 16, 3, 3]

@@ -604,6 +604,45 @@ def test_quantize_refuses_nan(gpu, oracle):
     both(ContentAttr(x, t, ContentSetup(t).quantize(q)), gpu, oracle)
 
 
+@pytest.mark.parametrize("dt", [F32, F16, BF16])
+def test_fused_kernels_refuse_nan(gpu, oracle, dt):
+    """The single-pass kernels (groups, long rows, convolution rows with and without a transposed copy-out; ranges
+    derived from the data or supplied) report a NaN like the general path, and the context stays usable."""
+    rng = np.random.default_rng(77)
+
+    def nan_at(x, i):
+        bad = x.copy()
+        if dt == BF16:
+            bad.reshape(-1)[i] = 0x7FC0
+        else:
+            bad.reshape(-1)[i] = np.nan
+        return bad
+
+    def conv(x):
+        return x if dt == F32 else (x.astype(np.float16) if dt == F16 else bf16_bits(x))
+
+    cases = []
+    for shape in ((12, 64, 3, 3), (40, 256, 1, 1), (9, 3, 7, 7)):  # transposed rows, straight rows, the scalar kernel
+        x = conv(rng.standard_normal(shape).astype(np.float32) * 0.05)
+        ts, oshape = wl.conv_pipeline(shape, None, None)
+        cases.append((shape, x, wl.spec_i8_sym(), ts, int(np.prod(oshape)), shape[0]))
+    if dt != F32:
+        x = conv(rng.standard_normal((3, 8192)).astype(np.float32) * 0.02)
+        cases.append(((3, 8192), x, wl.spec_i8_sym(), [], 3 * 8192, 3))
+        cases.append(((3, 8192), x, wl.spec_u4_group(128), [wl.t_bitpack()], 3 * 8192 // 2, 3 * 64))
+    for shape, x, spec, ts, nbytes, units in cases:
+        bad = nan_at(x, x.size * 2 // 3 + 5)
+        for be in (gpu, oracle):
+            assert _status(lambda: _quant_fold(be, shape, bad, spec, ts, nbytes, units)) == abi.VF_ERR_NAN, (shape, be)
+        _same(_quant_fold(gpu, shape, x, spec, ts, nbytes, units), _quant_fold(oracle, shape, x, spec, ts, nbytes, units))
+        if len(shape) == 4:  # the same through vf_fold with supplied parameters
+            t = TType(list(shape), dt)
+            q = Elem.per_axis(I8, F16, rng.uniform(1e-3, 1e-2, shape[0]).tolist(), [0] * shape[0], 0, -127, 127)
+            for be in (gpu, oracle):
+                assert _status(lambda: ContentAttr(bad, t, ContentSetup(t).quantize(q).reorder(abi.ORDER_NHWC)).fold(be)) == abi.VF_ERR_NAN
+            both(ContentAttr(x, t, ContentSetup(t).quantize(q).reorder(abi.ORDER_NHWC)), gpu, oracle)
+
+
 def test_device_time_of_a_call_is_reported_on_request(oracle):
     from vpux_plugin_b200.lib import Library
     lib = Library(device=0, timing=True)
@@ -1069,6 +1108,76 @@ def test_general_dequantize_by_rows(gpu, oracle, storage, np_dt, qmin, qmax, sha
     for zp in ((1 << 30) - 1, 1 << 30, -(1 << 30), (1 << 33) + 5, -(1 << 40)):  # around and beyond the 32-bit difference
         qz = Elem.uniform(storage, F32, 0.37, zp, qmin, qmax)
         both(ContentAttr(x, t, ContentSetup(t).castElemType(qz).dequantize()), gpu, oracle)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [F32, F16, BF16])
+@pytest.mark.parametrize("storage,qmin,qmax", [(I8, -128, 127), (U8, 0, 255), (U8, 0, 15)])
+def test_general_quantize_by_rows_ranges_and_special_values(gpu, oracle, dt, storage, qmin, qmax):
+    """Quantize with given parameters over rows of several lengths (shorter than, equal to and ragged against a warp's
+    unit), scales from far below to far above the bounds of the packed sequence (those rows take fakeQuantize as
+    written), data well outside the quantized range, infinities, zeros and denormals; NaN is refused."""
+    rng = np.random.default_rng(qmax + dt)
+    for inner, oc in ((8, 40), (512, 12), (1032, 7), (4096 + 24, 3)):
+        mags = np.array([1e-36, 1e-33, 3e-31, 1e-20, 1e-3, 0.05, 7.0, 1e20, 1e28, 4e29, 1e33])
+        if dt == F16:
+            mags = np.array([1e-36, 1e-9, 1e-5, 1e-3, 0.05, 7.0, 200.0, 1e20])
+        scales = rng.choice(mags, oc) * rng.uniform(0.5, 2.0, oc)
+        zps = rng.integers(qmin, qmax + 1, oc)
+        x = rng.standard_normal((oc, inner)) * (scales * (qmax - qmin) * 0.7)[:, None] + ((((qmin + qmax) / 2) - zps) * scales)[:, None]
+        x = np.clip(x, -3e38, 3e38)
+        x[0, :8] = [np.inf, -np.inf, 3e38, -3e38, 0.0, -0.0, 1e-45, -1e-40]
+        t = TType([oc, inner], dt)
+        if dt == F32:
+            data = x.astype(np.float32)
+        elif dt == F16:
+            data = np.clip(x, -65504, 65504).astype(np.float16)
+            data[0, :2] = [np.inf, -np.inf]
+        else:
+            data = bf16_bits(x.astype(np.float32))
+        q = Elem.per_axis(storage, F32, scales.tolist(), [int(z) for z in zps], 0, qmin, qmax)
+        both(ContentAttr(data, t, ContentSetup(t).quantize(q)), gpu, oracle)
+        qt = Elem.uniform(storage, F32, float(scales[-1]), int(zps[-1]), qmin, qmax)
+        both(ContentAttr(data, t, ContentSetup(t).quantize(qt)), gpu, oracle)
+    bad = data.copy()
+    bad.reshape(-1)[5000 % bad.size] = np.float32(np.nan) if dt != BF16 else 0x7FC1
+    for be in (gpu, oracle):
+        assert _status(lambda: ContentAttr(bad, t, ContentSetup(t).quantize(q)).fold(be)) == abi.VF_ERR_NAN
+    both(ContentAttr(data, t, ContentSetup(t).quantize(q)), gpu, oracle)  # the context stays usable
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("storage,np_dt,qmin,qmax", [(I8, np.int8, -128, 127), (U8, np.uint8, 0, 255)])
+def test_general_dequantize_scales_next_to_rounding_boundaries(gpu, oracle, storage, np_dt, qmin, qmax):
+    """Dequantize is the FP64 product rounded to fp32. Scales built so that (code - zp) * scale lies within an FP64
+    rounding error of the midpoint of two floats for one code per row, scales whose products are denormal or
+    overflow, and zero points around 2^20, where the fp32 evaluation has to hand over to the FP64 one."""
+    rng = np.random.default_rng(7 + qmax)
+    rows = 96
+    scales = np.empty(rows, np.float64)
+    zps = rng.integers(qmin, qmax + 1, rows)
+    for r in range(rows):
+        n = 2 * (r % 60) + 3  # an odd multiplier: n * scale sits on the midpoint, up to the rounding of the scale
+        s_hi = np.float64(np.float32(rng.uniform(1e-3, 2.0)))
+        p = n * s_hi
+        ulp = 2.0 ** (np.floor(np.log2(p)) - 23)
+        tie = (np.floor(p / ulp) + 0.5) * ulp
+        scales[r] = s_hi - (p - tie) / n
+        code = int(zps[r]) + n
+        if code > qmax:
+            zps[r] = qmax - n if qmax - n >= qmin else qmin
+    scales[-6:] = [1e-42, 3e-39, 2.9e36, 1e38, 1.0000000001, 0.1]
+    zps[-3:] = [(1 << 20) - 1, 1 << 20, -(1 << 20) - 7]
+    shape = [rows, 1544]
+    x = rng.integers(qmin, qmax + 1, shape).astype(np_dt)
+    x[:, :qmax - qmin + 1] = np.arange(qmin, qmax + 1).astype(np_dt)[None, :]
+    t = TType(shape, storage)
+    qa = Elem.per_axis(storage, F32, scales.tolist(), [int(z) for z in zps], 0, qmin, qmax)
+    both(ContentAttr(x, t, ContentSetup(t).castElemType(qa).dequantize()), gpu, oracle)
+    t2 = TType([2, rows, 264], storage)
+    qa2 = Elem.per_axis(storage, F32, scales.tolist(), [int(z) for z in zps], 1, qmin, qmax)
+    both(ContentAttr(np.ascontiguousarray(x[:, :528].reshape(rows, 2, 264).transpose(1, 0, 2)), t2,
+                     ContentSetup(t2).castElemType(qa2).dequantize()), gpu, oracle)
 
 
 @pytest.mark.gpu

@@ -165,7 +165,8 @@ struct Elem {
         e.dtype = dt;
         return e;
     }
-    static Elem from(const vf_elem_type& e);
+    // check_scales = false: the caller does not use the type's scales (they are supplied elsewhere)
+    static Elem from(const vf_elem_type& e, bool check_scales = true);
     bool single_zp(int64_t& zp) const;  // extractSingleZeroPoint
 };
 

@@ -1041,6 +1041,7 @@ int vf_fold(vf_ctx* ctx, const vf_content* base, const vf_transform* t, int n, v
         CallScope scope(ctx, stats);
         const uint64_t w = fold_one(ctx, *base, t, n, dst, dst_bytes, dst_mem_kind, out_type, scales_buf, zps_buf, params_cap, stats);
         if (dst_written) *dst_written = w;
+        scope.may_defer = base->mem_kind == VF_MEM_DEVICE && (!dst || dst_mem_kind == VF_MEM_DEVICE);
         scope.finish();
     });
 }
@@ -1474,8 +1475,9 @@ int vf_sparsify_batch(vf_ctx* ctx, vf_sparsify_job* jobs, int njobs, int out_mem
 // `keep`; a count array queues an entry in `offs` (the prefix sums are launched by the caller, for all tables at
 // once). `w_scales` / `w_kind`: optional replacement of the weight scales by an array of `oc` values that may
 // already live in device memory (the scales a quantization job of the same tensor derived).
+// `arena`: device memory for the prefix sums of all tables of the call ((oc + 1) * 8 bytes each), carved in order
 static TableArgs table_prepare(vf_ctx* ctx, const vf_weights_table_desc* d, const double* w_scales, int w_kind, int32_t* d_table,
-                               std::vector<DBuf>& keep, std::vector<OffsetsJob>& offs) {
+                               std::vector<DBuf>& keep, std::vector<OffsetsJob>& offs, int64_t*& arena) {
     {
         if (!d) raise(VF_ERR_INVALID_ARG, "NULL argument");
         if (d->oc <= 0) raise(VF_ERR_SHAPE, "OC must be positive");
@@ -1484,7 +1486,7 @@ static TableArgs table_prepare(vf_ctx* ctx, const vf_weights_table_desc* d, cons
         const int64_t oc = d->oc;
         const Elem in = Elem::from(d->in_elem), out = Elem::from(d->out_elem);
         const bool has_w = d->weights_elem.dtype != VF_DT_INVALID;
-        const Elem w = has_w ? Elem::from(d->weights_elem) : Elem();
+        const Elem w = has_w ? Elem::from(d->weights_elem, w_scales == nullptr) : Elem();
         if (has_w && in.quantized() && !w.quantized()) raise(VF_ERR_UNSUPPORTED, "Unsupported In/Wt mixed precision");
         auto check_n = [&](const Elem& e, const char* what) {
             if (e.quantized() && e.scales.size() != 1 && int64_t(e.scales.size()) != oc)
@@ -1528,8 +1530,8 @@ static TableArgs table_prepare(vf_ctx* ctx, const vf_weights_table_desc* d, cons
         if (d->nnz_counts) {
             const int64_t* dc = d->nnz_counts;
             if (d->nnz_mem_kind != VF_MEM_DEVICE) dc = static_cast<const int64_t*>(upload(d->nnz_counts, size_t(oc) * 8, d->nnz_mem_kind));
-            keep.emplace_back(ctx, size_t(oc + 1) * 8);
-            int64_t* doff = keep.back().as<int64_t>();
+            int64_t* doff = arena;
+            arena += oc + 1;
             const int eb = std::max(1, dtype_bits(has_w ? w.dtype : VF_DT_U8) / 8);
             offs.push_back(OffsetsJob{dc, oc, eb, doff});
             a.d_nnz_offsets = doff;
@@ -1556,7 +1558,9 @@ int vf_weights_table(vf_ctx* ctx, const vf_weights_table_desc* d, int32_t* table
         keep.reserve(16);
         DBuf tmp;
         int32_t* dt = static_cast<int32_t*>(out_ptr(ctx, table, out_mem_kind, size_t(d->oc > 0 ? d->oc : 0) * 16, tmp));
-        const TableArgs a = table_prepare(ctx, d, nullptr, VF_MEM_HOST, dt, keep, offs);
+        DBuf sums(ctx, d->nnz_counts && d->oc > 0 ? size_t(d->oc + 1) * 8 : 0);
+        int64_t* arena = sums.as<int64_t>();
+        const TableArgs a = table_prepare(ctx, d, nullptr, VF_MEM_HOST, dt, keep, offs, arena);
         launch_offsets_batch(ctx, offs);
         launch_weights_table(ctx, a, dt);
         out_flush(ctx, table, out_mem_kind, size_t(d->oc) * 16, tmp);
@@ -1573,13 +1577,19 @@ int vf_weights_table_batch(vf_ctx* ctx, vf_weights_table_job* jobs, int njobs, i
         std::vector<TableArgs> tabs;
         std::vector<DBuf> stage(static_cast<size_t>(njobs));
         keep.reserve(size_t(njobs) * 8 + 8);  // pointers into `keep` entries stay valid: no reallocation below
+        tabs.reserve(size_t(njobs));
+        size_t sum_entries = 0;  // one allocation for the prefix sums of all sparse tables
+        for (int j = 0; j < njobs; ++j)
+            if (jobs[j].desc.nnz_counts && jobs[j].desc.oc > 0) sum_entries += size_t(jobs[j].desc.oc) + 1;
+        DBuf sums(ctx, sum_entries * 8);
+        int64_t* arena = sums.as<int64_t>();
         for (int j = 0; j < njobs; ++j) {
             vf_weights_table_job& jb = jobs[j];
             jb.status = VF_OK;
             if (!jb.table) raise(VF_ERR_INVALID_ARG, "job %d: table is NULL", j);
             int32_t* dt = static_cast<int32_t*>(out_ptr(ctx, jb.table, out_mem_kind, size_t(jb.desc.oc > 0 ? jb.desc.oc : 0) * 16, stage[j]));
             try {
-                tabs.push_back(table_prepare(ctx, &jb.desc, jb.weights_scales, jb.scales_mem_kind, dt, keep, offs));
+                tabs.push_back(table_prepare(ctx, &jb.desc, jb.weights_scales, jb.scales_mem_kind, dt, keep, offs, arena));
             } catch (const Error& e) {
                 jb.status = e.code;
                 throw;

@@ -180,6 +180,9 @@ struct RowQuantArgs {
     const double* given_scales;
     const int64_t* given_zps;
     int64_t unit_begin;      // filled by launch_rowquant_batch: index of this job's first chunk / row in the launch
+    int lanes_per_row;       // filled by launch_rowquant_batch (k_convv): 8, 16 or 32 lanes share an output channel
+    int unit_cost;           // (k_convv) relative cost of one of this job's units
+    int64_t work_begin;      // (k_convv) sum of the costs of all units in front of this job
 };
 // Launches all `jobs` (same kind, pairwise rowquant_compatible) with ONE kernel over a device job table.
 void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& jobs);

@@ -1,6 +1,8 @@
 // General-path kernels: one kernel per #const transformation, for every storage type the reference's
 // Content::getValues<T>() accepts. These back vf_fold() for arbitrary transformation lists; the weight
 // quantization hot path has its own fused kernels (kernels_rowquant.cu).
+#include <cuda_fp8.h>
+
 #include "device_utils.cuh"
 #include "kernels.h"
 
@@ -269,6 +271,280 @@ __global__ void k_dequantize8(const void* __restrict__ in, float* __restrict__ o
             ob[k] = dequantize_exact(q, scale, zp);
         }
         store8<32>(out, int64_t(g), reinterpret_cast<const uint8_t*>(ob));
+    }
+}
+
+// ---- Quantize / Dequantize by rows, on packed pairs ------------------------------------------------------------
+// A warp takes a unit: kPairU consecutive 16-byte (Quantize) or 8-byte (Dequantize) loads per lane of ONE row of the
+// quantized axis, all issued before the first value is needed. The row's constants are computed once per unit and
+// the arithmetic runs on packed two-wide fp32 instructions (each half is the same IEEE operation as the scalar one).
+namespace pairs {
+
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: the ulp is 1, the low mantissa bits hold an integer
+constexpr int kPairU = 4;
+constexpr float kRangeLo = 7.8886091e-31f, kRangeHi = 1.2676506e30f;  // 2^-100, 2^100
+
+__device__ __forceinline__ float2 dup(float v) {
+    return make_float2(v, v);
+}
+
+// one 16-byte load of floating-point input as pairs
+template <int IN>
+struct Step;
+template <>
+struct Step<VF_DT_F32> {
+    static constexpr int kElems = 4, kPairs = 2;
+    static __device__ __forceinline__ float2 pair(const uint4& d, int i) {
+        return i == 0 ? make_float2(__uint_as_float(d.x), __uint_as_float(d.y)) : make_float2(__uint_as_float(d.z), __uint_as_float(d.w));
+    }
+    static __device__ __forceinline__ bool has_nan(const uint4& d) {
+        return (d.x & 0x7FFFFFFFu) > 0x7F800000u || (d.y & 0x7FFFFFFFu) > 0x7F800000u || (d.z & 0x7FFFFFFFu) > 0x7F800000u ||
+               (d.w & 0x7FFFFFFFu) > 0x7F800000u;
+    }
+};
+__device__ __forceinline__ uint32_t word_of(const uint4& d, int i) {
+    return i == 0 ? d.x : i == 1 ? d.y : i == 2 ? d.z : d.w;
+}
+template <>
+struct Step<VF_DT_F16> {
+    static constexpr int kElems = 8, kPairs = 4;
+    static __device__ __forceinline__ float2 pair(const uint4& d, int i) {
+        uint32_t w = word_of(d, i);
+        return __half22float2(*reinterpret_cast<__half2*>(&w));
+    }
+    static __device__ __forceinline__ bool has_nan(const uint4& d) {
+        bool r = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = word_of(d, i);
+            r |= (w & 0x7FFFu) > 0x7C00u || ((w >> 16) & 0x7FFFu) > 0x7C00u;
+        }
+        return r;
+    }
+};
+template <>
+struct Step<VF_DT_BF16> {
+    static constexpr int kElems = 8, kPairs = 4;
+    static __device__ __forceinline__ float2 pair(const uint4& d, int i) {
+        const uint32_t w = word_of(d, i);
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    }
+    static __device__ __forceinline__ bool has_nan(const uint4& d) {
+        bool r = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = word_of(d, i);
+            r |= (w & 0x7FFFu) > 0x7F80u || ((w >> 16) & 0x7FFFu) > 0x7F80u;
+        }
+        return r;
+    }
+};
+
+// fakeQuantize's middle branch with its own operation sequence (utils/quantization.cpp:995-1003), branch-free:
+//   a = fl(x - inLow); the division fl(a / range) as q0 = fl(a y), q = fma(fma(-q0, range, a), y, q0) with
+//   y = RN(1 / range), which is the correctly rounded quotient for 2^-100 <= range <= 2^100; e = fl(q (L-1));
+//   roundf(e) = floor(e + 1/2) as two additions rounded toward minus infinity, the second onto the integer grid
+//   at 1.5 * 2^23 + qmin, so the low byte of the result is the code in two's complement.
+// The outer branches (x <= inLow -> qmin, x > inHigh -> qmax) coincide with clamping x to [inLow, inHigh] first:
+// x = inLow gives a = 0, x = inHigh gives a = range exactly, and every step is monotonic in x.
+struct RowQ {
+    float lo, hi;
+    float2 nlow, y, nrange, lm1, cm;
+};
+__device__ __forceinline__ RowQ row_consts(const QuantParams& qp, long long qmin) {
+    RowQ q;
+    q.lo = qp.in_low;
+    q.hi = qp.in_high;
+    q.nlow = dup(-qp.in_low);
+    q.y = dup(__frcp_rn(qp.range));
+    q.nrange = dup(-qp.range);
+    q.lm1 = dup(qp.levels_m1);
+    q.cm = dup(__fadd_rn(kMagic, float(qmin)));
+    return q;
+}
+__device__ __forceinline__ float2 quant_pair(float2 x, const RowQ& q, float2& nan_acc) {
+    nan_acc = __ffma2_rn(x, dup(0.f), nan_acc);  // NaN once any element was NaN or infinite
+    x.x = fminf(fmaxf(x.x, q.lo), q.hi);
+    x.y = fminf(fmaxf(x.y, q.lo), q.hi);
+    const float2 a = __fadd2_rn(x, q.nlow);
+    const float2 q0 = __fmul2_rn(a, q.y);
+    const float2 d = __ffma2_rn(__ffma2_rn(q0, q.nrange, a), q.y, q0);
+    const float2 e = __fmul2_rn(d, q.lm1);
+    return __fadd2_rd(__fadd2_rd(e, dup(0.5f)), q.cm);
+}
+// the codes of one load: four bytes (f32 input) or eight
+template <int IN>
+__device__ __forceinline__ uint2 quant_step(const uint4& d, const RowQ& q, float2& nan_acc) {
+    uint32_t b[Step<IN>::kPairs];
+#pragma unroll
+    for (int i = 0; i < Step<IN>::kPairs; ++i) {
+        const float2 m = quant_pair(Step<IN>::pair(d, i), q, nan_acc);
+        b[i] = __byte_perm(__float_as_uint(m.x), __float_as_uint(m.y), 0x0040);
+    }
+    if (Step<IN>::kPairs == 2) return make_uint2(__byte_perm(b[0], b[1], 0x5410), 0u);
+    return make_uint2(__byte_perm(b[0], b[1], 0x5410), __byte_perm(b[2], b[Step<IN>::kPairs - 1], 0x5410));
+}
+// rows whose range is outside the packed sequence's bounds: fakeQuantize as written, one element at a time
+template <int IN>
+__device__ __noinline__ uint2 quant_step_scalar(uint4 d, QuantParams qp, int* flags) {
+    uint32_t r[2] = {0u, 0u};
+#pragma unroll
+    for (int k = 0; k < Step<IN>::kElems; ++k) {
+        const float x = load_as_f32(&d, IN, k, flags);
+        if (x != x) set_flag(flags, VF_FLAG_NAN);
+        r[k >> 2] |= (uint32_t(quantize_exact(x, qp)) & 0xFFu) << (8 * (k & 3));
+    }
+    return make_uint2(r[0], r[1]);
+}
+
+}  // namespace pairs
+
+// Quantize of floating-point input to 8-bit codes when the tail of fakeQuantize is the identity on the indices of
+// the storage range (tail_is_identity): a row is everything inside the quantized axis (the whole tensor for a
+// per-tensor type), row_steps its length in 16-byte loads.
+template <int IN>
+__global__ void __launch_bounds__(256) k_quantize_rows(const uint4* __restrict__ in, uint8_t* __restrict__ out, uint32_t n_units,
+                                                       uint32_t chunks_per_row, uint32_t axis_size, int64_t row_steps,
+                                                       const double* __restrict__ scales, const int64_t* __restrict__ zps,
+                                                       long long qmin, long long qmax, int* flags) {
+    using namespace pairs;
+    using S = Step<IN>;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t unit = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; unit < n_units; unit += n_warps) {
+        const uint32_t row = unit / chunks_per_row, c = unit - row * chunks_per_row;
+        const uint32_t a = axis_size > 1 ? row % axis_size : 0u;
+        const int64_t s0 = int64_t(c) * (kPairU * 32) + lane;
+        const int64_t base = int64_t(row) * row_steps;
+        uint4 d[kPairU];
+#pragma unroll
+        for (int u = 0; u < kPairU; ++u) {
+            const int64_t s = s0 + u * 32;
+            d[u] = s < row_steps ? __ldg(in + base + s) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        const QuantParams qp = make_quant_params(scales[a], zps[a], qmin, qmax);
+        const bool packed = qp.range >= kRangeLo && qp.range <= kRangeHi;  // false for a NaN range as well
+        const RowQ q = row_consts(qp, qmin);
+        float2 nan_acc = dup(0.f);
+#pragma unroll
+        for (int u = 0; u < kPairU; ++u) {
+            const int64_t s = s0 + u * 32;
+            if (s >= row_steps) break;
+            const uint2 codes = packed ? quant_step<IN>(d[u], q, nan_acc) : quant_step_scalar<IN>(d[u], qp, flags);
+            if (S::kElems == 4) reinterpret_cast<uint32_t*>(out)[base + s] = codes.x;
+            else reinterpret_cast<uint2*>(out)[base + s] = codes;
+        }
+        if (nan_acc.x != nan_acc.x || nan_acc.y != nan_acc.y) {  // rare: tell NaN from infinity
+            bool any = false;
+#pragma unroll
+            for (int u = 0; u < kPairU; ++u) any |= S::has_nan(d[u]);
+            if (any) set_flag(flags, VF_FLAG_NAN);
+        }
+    }
+}
+
+// Dequantize of 8-bit codes, fl32(double(q - zp) * scale) (include/vpux/compiler/utils/quantization.hpp:208-210), in
+// fp32: with n = q - zp, s_hi = fl32(scale) and s_lo = fl32(scale - s_hi) the value fma(n, s_hi, fl(n s_lo)) differs
+// from the FP64 product by about 2^-47 of it, so it rounds to the same float unless the product lies that close to
+// a rounding boundary. There are only 256 codes: a preparation launch evaluates both for every code of every entry
+// of the quantized axis and records whether they agree everywhere; entries where they do not, or whose zero point
+// is beyond 2^20, keep the FP64 evaluation.
+struct DequantRow {
+    float s_hi, s_lo, ncz;  // ncz = -(magic + zero point [+ 128 for signed codes])
+    uint32_t ok;
+};
+__global__ void k_dequant_rows_prepare(const double* __restrict__ scales, const int64_t* __restrict__ zps, uint32_t n_axis,
+                                       int is_signed, DequantRow* __restrict__ rows) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t a = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (a >= n_axis) return;
+    const double scale = scales[a];
+    const long long zp = zps[a];
+    bool ok = zp > -(1ll << 20) && zp < (1ll << 20);
+    const float s_hi = __double2float_rn(scale);
+    const float s_lo = __double2float_rn(__dsub_rn(scale, double(s_hi)));
+    if (ok) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int byte = int(lane) + 32 * k;
+            const int code = is_signed ? int(int8_t(byte)) : byte;
+            const float exact = dequantize_exact((long long)(code), scale, zp);
+            const float nf = float(code - int(zp));
+            const float fast = __fmaf_rn(nf, s_hi, __fmul_rn(nf, s_lo));
+            ok &= __float_as_uint(exact) == __float_as_uint(fast);
+        }
+    }
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    if (lane == 0) {
+        DequantRow r;
+        r.s_hi = s_hi;
+        r.s_lo = s_lo;
+        r.ncz = ok ? -(pairs::kMagic + float(int(zp) + (is_signed ? 128 : 0))) : 0.f;
+        r.ok = ok ? 1u : 0u;
+        rows[a] = r;
+    }
+}
+template <int IN>
+__device__ __noinline__ float4 dequant_word_f64(uint32_t w, double scale, long long zp) {
+    float ob[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t b = (w >> (8 * k)) & 0xFFu;
+        ob[k] = dequantize_exact(IN == VF_DT_I8 ? (long long)(int8_t(b)) : (long long)(b), scale, zp);
+    }
+    return make_float4(ob[0], ob[1], ob[2], ob[3]);
+}
+// A lane takes one 32-bit word (four codes) per load and stores one 16-byte vector of four floats: every load and
+// every store of a warp is one contiguous run (128 and 512 bytes). row_words is the row's length in words.
+template <int IN>
+__global__ void __launch_bounds__(256) k_dequantize_rows(const uint32_t* __restrict__ in, float4* __restrict__ out, uint32_t n_units,
+                                                         uint32_t chunks_per_row, uint32_t axis_size, int64_t row_words,
+                                                         const DequantRow* __restrict__ rows, const double* __restrict__ scales,
+                                                         const int64_t* __restrict__ zps) {
+    using namespace pairs;
+    constexpr int kU = 2 * kPairU;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t unit = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; unit < n_units; unit += n_warps) {
+        const uint32_t row = unit / chunks_per_row, c = unit - row * chunks_per_row;
+        const uint32_t a = axis_size > 1 ? row % axis_size : 0u;
+        const int64_t w0 = int64_t(c) * (kU * 32) + lane;
+        const int64_t base = int64_t(row) * row_words;
+        uint32_t d[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int64_t w = w0 + u * 32;
+            d[u] = w < row_words ? __ldg(in + base + w) : 0u;
+        }
+        const uint4 rw = __ldg(reinterpret_cast<const uint4*>(rows) + a);
+        const float2 s_hi = dup(__uint_as_float(rw.x)), s_lo = dup(__uint_as_float(rw.y)), ncz = dup(__uint_as_float(rw.z));
+        if (rw.w) {
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int64_t w = w0 + u * 32;
+                if (w >= row_words) break;
+                const uint32_t x = IN == VF_DT_I8 ? d[u] ^ 0x80808080u : d[u];  // code + 128 as an unsigned byte
+                float2 r[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    // the byte under the bit pattern of the magic constant: magic + byte as a float
+                    const float2 m = make_float2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7650 + 2 * j)),
+                                                 __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7651 + 2 * j)));
+                    const float2 n = __fadd2_rn(m, ncz);  // exact
+                    r[j] = __ffma2_rn(n, s_hi, __fmul2_rn(n, s_lo));
+                }
+                out[base + w] = make_float4(r[0].x, r[0].y, r[1].x, r[1].y);
+            }
+        } else {
+            const double scale = scales[a];
+            const long long zp = zps[a];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int64_t w = w0 + u * 32;
+                if (w >= row_words) break;
+                out[base + w] = dequant_word_f64<IN>(d[u], scale, zp);
+            }
+        }
     }
 }
 
@@ -553,6 +829,104 @@ __global__ void __launch_bounds__(256) k_permute_tiled(const void* __restrict__ 
             const I ia = a0 + threadIdx.x + c;
             if (ia < ea && ib < eb) static_cast<T*>(out)[dst0 + ib * dst_stride_b + ia] = tile[threadIdx.x + c][threadIdx.y + i];
         }
+    }
+}
+
+// The transposition of the two innermost output dims when together they are ONE contiguous block of the source
+// (OIYX -> OYXI: per output channel the IC x KY*KX block becomes KY*KX x IC). A chunk is `rows_per_chunk` source
+// rows (contiguous): it is copied into shared memory with 16-byte asynchronous copies, starting at the 16-byte
+// boundary at or below the chunk, and written out as 16-byte vectors of consecutive a: eight lanes (f16, ea = 64)
+// cover one output row, a warp four rows, contiguous in memory. Each element costs one shared-memory read. The
+// CTAs are persistent and double-buffered: the copy of a CTA's next chunk is in flight while it writes this one.
+__device__ __forceinline__ void cp_async16_part(void* smem_dst, const void* gsrc, int src_bytes) {
+    const uint32_t sdst = uint32_t(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sdst), "l"(gsrc), "r"(src_bytes) : "memory");  // the rest is zero-filled
+}
+template <int ES, typename I>
+__global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, I chunks_a,
+                                                          I n_chunks, uint32_t rows_per_chunk, uint32_t buf_vecs, int64_t total_bytes) {
+    constexpr uint32_t VE = 16 / ES;  // elements per output vector
+    extern __shared__ uint4 slice_smem[];
+    using T = typename ElemOf<ES>::T;
+    const int a = g.rank - 1, b = g.rank - 2;
+    const uint32_t ea = uint32_t(g.out_shape[a]), eb = uint32_t(g.out_shape[b]);
+
+    struct Chunk {
+        int64_t dst0;    // element offset of the (others) slice in the output
+        uint32_t a0, ta; // first row and rows of the chunk
+        uint32_t lead;   // bytes in front of the chunk inside its first vector
+    };
+    // coordinates of chunk `idx` and the copy of its source rows into `buf`
+    auto fetch = [&](I idx, uint4* buf) -> Chunk {
+        Chunk c;
+        I rem = idx;
+        const I ca = rem % chunks_a;
+        rem /= chunks_a;
+        int64_t src0 = 0, dst0 = 0, dst_mul = 1;
+#pragma unroll
+        for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+            if (d < g.rank) {
+                const I os = I(g.out_shape[d]);
+                if (d != a && d != b) {
+                    const I q = rem / os;
+                    const I cc = rem - q * os;
+                    rem = q;
+                    src0 += int64_t(cc) * g.src_stride[d];
+                    dst0 += int64_t(cc) * dst_mul;
+                }
+                dst_mul *= os;
+            }
+        }
+        c.dst0 = dst0;
+        c.a0 = uint32_t(ca) * rows_per_chunk;
+        c.ta = min(rows_per_chunk, ea - c.a0);
+        const int64_t first = (src0 + int64_t(c.a0) * eb) * ES;  // byte offset of the chunk in the source
+        const int64_t start = first & ~int64_t(15);
+        c.lead = uint32_t(first - start);
+        const uint32_t n_vec = (c.lead + c.ta * eb * ES + 15u) >> 4;
+        for (uint32_t v = threadIdx.x; v < n_vec; v += blockDim.x) {
+            const int64_t p = start + int64_t(v) * 16;
+            const int64_t left = total_bytes - p;  // the last vector of the buffer may be cut short
+            cp_async16_part(buf + v, in + p, left >= 16 ? 16 : int(left));
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        return c;
+    };
+
+    I idx = I(blockIdx.x);
+    if (idx >= n_chunks) return;
+    int cur = 0;
+    Chunk c = fetch(idx, slice_smem);
+    for (; idx < n_chunks; idx += I(gridDim.x)) {
+        const I next = idx + I(gridDim.x);
+        Chunk cn = c;
+        if (next < n_chunks) {
+            cn = fetch(next, slice_smem + (cur ^ 1) * buf_vecs);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // every thread's copies of this chunk have landed
+        const T* sm = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(slice_smem + cur * buf_vecs) + c.lead);
+        const uint32_t nab = c.ta / VE, n_out = nab * eb;
+        const uint32_t step_b = blockDim.x / nab, step_a = blockDim.x - step_b * nab;
+        uint32_t ib = threadIdx.x / nab, iab = threadIdx.x - ib * nab;
+        for (uint32_t v = threadIdx.x; v < n_out; v += blockDim.x) {
+            __align__(16) T e[VE];
+            const T* col = sm + iab * VE * eb + ib;
+#pragma unroll
+            for (uint32_t k = 0; k < VE; ++k) e[k] = col[k * eb];
+            *reinterpret_cast<uint4*>(out + (c.dst0 + int64_t(ib) * ea + c.a0 + iab * VE) * ES) = *reinterpret_cast<const uint4*>(e);
+            iab += step_a;
+            ib += step_b;
+            if (iab >= nab) {
+                iab -= nab;
+                ++ib;
+            }
+        }
+        __syncthreads();  // this buffer is the target of the copy issued in the next iteration
+        c = cn;
+        cur ^= 1;
     }
 }
 
@@ -1055,14 +1429,37 @@ __global__ void k_convert_float8(const void* __restrict__ in, void* __restrict__
         } else {
             reinterpret_cast<uint2*>(ib)[0] = __ldg(reinterpret_cast<const uint2*>(in) + g);
         }
+        if (OUT == VF_DT_F8E4M3FN) {
+            // The reference's sequence (src/vpux_utils/src/core/type/float8_e4m3.cpp:52-113) rounds to nearest even
+            // onto 3 mantissa bits and turns everything that would round above 448 (|x| > 464, infinities, NaN)
+            // into the NaN pattern. It rounds the mantissa BEFORE it looks at the exponent: below 2^-7 (subnormal
+            // results) a mantissa of 1.1111... carries into the exponent first and the subnormal is then rounded
+            // from twice the value. The conversion instruction rounds two elements at a time; it is given 2x for
+            // those inputs, and pairs with an element beyond 464 (the instruction would saturate) take the
+            // sequence as written.
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float f = load_as_f32(ib, IN, k, flags);
-            if (OUT == VF_DT_F32) reinterpret_cast<float*>(ob)[k] = f;
-            else if (OUT == VF_DT_F16) reinterpret_cast<uint16_t*>(ob)[k] = f32_to_f16_clamped_bits(f);
-            else if (OUT == VF_DT_BF16) reinterpret_cast<uint16_t*>(ob)[k] = f32_to_bf16_bits(f);
-            else if (OUT == VF_DT_F8E4M3FN) ob[k] = f32_bits_to_f8e4m3_bits(__float_as_uint(f));
-            else ob[k] = f16_bits_to_f8e5m2_bits(f32_to_f16_bits(f));
+            for (int k = 0; k < 8; k += 2) {
+                float f0 = load_as_f32(ib, IN, k, flags), f1 = load_as_f32(ib, IN, k + 1, flags);
+                uint32_t two;
+                if (fabsf(f0) <= 464.f && fabsf(f1) <= 464.f) {  // false for NaN
+                    const uint32_t u0 = __float_as_uint(f0), u1 = __float_as_uint(f1);
+                    if ((u0 & 0x7FFFFFFFu) < 0x3C000000u && (u0 & 0x00780000u) == 0x00780000u) f0 = __fmul_rn(f0, 2.f);
+                    if ((u1 & 0x7FFFFFFFu) < 0x3C000000u && (u1 & 0x00780000u) == 0x00780000u) f1 = __fmul_rn(f1, 2.f);
+                    two = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, __NV_E4M3);
+                } else {
+                    two = uint32_t(f32_bits_to_f8e4m3_bits(__float_as_uint(f0))) | (uint32_t(f32_bits_to_f8e4m3_bits(__float_as_uint(f1))) << 8);
+                }
+                reinterpret_cast<uint16_t*>(ob)[k >> 1] = uint16_t(two);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float f = load_as_f32(ib, IN, k, flags);
+                if (OUT == VF_DT_F32) reinterpret_cast<float*>(ob)[k] = f;
+                else if (OUT == VF_DT_F16) reinterpret_cast<uint16_t*>(ob)[k] = f32_to_f16_clamped_bits(f);
+                else if (OUT == VF_DT_BF16) reinterpret_cast<uint16_t*>(ob)[k] = f32_to_bf16_bits(f);
+                else ob[k] = f16_bits_to_f8e5m2_bits(f32_to_f16_bits(f));
+            }
         }
         if (OB == 32) {
             reinterpret_cast<uint4*>(out)[2 * g] = reinterpret_cast<uint4*>(ob)[0];
@@ -1188,6 +1585,25 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
         const int grid = grid_for(groups);
         uint8_t* o = static_cast<uint8_t*>(out);
         const bool fast = qmax - qmin <= 255 && qmax > qmin && tail_is_identity(qmin, qmax);
+        if (fast) {  // packed pairs, a warp per chunk of a row
+            const int64_t eps = in_dt == VF_DT_F32 ? 4 : 8;
+            const int64_t row_elems = axis_size > 1 ? inner : n, n_rows = n / row_elems, row_steps = row_elems / eps;
+            const int64_t per_unit = int64_t(pairs::kPairU) * 32, chunks_per_row = (row_steps + per_unit - 1) / per_unit;
+            if (chunks_per_row < (int64_t(1) << 31) && n_rows * chunks_per_row < (int64_t(1) << 31)) {
+                const int64_t n_units = n_rows * chunks_per_row;
+                const int rgrid = int(std::min<int64_t>((n_units + 7) / 8, int64_t(ctx->sm_count) * 16));
+                const uint4* src = static_cast<const uint4*>(in);
+#define VF_QR(IN)                                                                                                                 \
+    k_quantize_rows<IN><<<rgrid, kBlock, 0, ctx->stream>>>(src, o, uint32_t(n_units), uint32_t(chunks_per_row), uint32_t(axis_size), \
+                                                           row_steps, d_scales, d_zps, qmin, qmax, ctx->d_flags)
+                if (in_dt == VF_DT_F32) VF_QR(VF_DT_F32);
+                else if (in_dt == VF_DT_F16) VF_QR(VF_DT_F16);
+                else VF_QR(VF_DT_BF16);
+#undef VF_QR
+                post_launch(ctx);
+                return;
+            }
+        }
         // by rows: the quantized axis and everything outside it index the row, what is inside it is the row
         const int64_t row_len = axis_size > 1 ? inner8 : groups, n_rows = groups / row_len;
         const int64_t chunk = int64_t(kRowUnroll) * kBlock, chunks_per_row = (row_len + chunk - 1) / chunk;
@@ -1237,6 +1653,29 @@ void launch_dequantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, fl
         const int64_t groups = n / 8, inner8 = axis_size > 1 ? inner / 8 : 1;
         const int grid = grid_for(groups);
         const int64_t row_len = axis_size > 1 ? inner8 : groups, n_rows = groups / row_len;
+        {  // packed pairs, a warp per chunk of a row; the per-entry constants come from a preparation launch
+            const int64_t row_words = row_len * 2;
+            const int64_t per_unit = int64_t(pairs::kPairU) * 64, cpr = (row_words + per_unit - 1) / per_unit;
+            const int64_t n_axis = axis_size > 1 ? axis_size : 1;
+            if (cpr < (int64_t(1) << 31) && n_rows * cpr < (int64_t(1) << 31) && n_axis < (int64_t(1) << 28)) {
+                const int64_t n_units = n_rows * cpr;
+                DBuf rows(ctx, size_t(n_axis) * sizeof(DequantRow));
+                k_dequant_rows_prepare<<<unsigned((n_axis + 7) / 8), kBlock, 0, ctx->stream>>>(d_scales, d_zps, uint32_t(n_axis), in_dt == VF_DT_I8,
+                                                                                              static_cast<DequantRow*>(rows.p));
+                post_launch(ctx);
+                const int rgrid = int(std::min<int64_t>((n_units + 7) / 8, int64_t(ctx->sm_count) * 16));
+                if (in_dt == VF_DT_I8)
+                    k_dequantize_rows<VF_DT_I8><<<rgrid, kBlock, 0, ctx->stream>>>(static_cast<const uint32_t*>(in), reinterpret_cast<float4*>(out),
+                                                                                   uint32_t(n_units), uint32_t(cpr), uint32_t(axis_size), row_words,
+                                                                                   static_cast<const DequantRow*>(rows.p), d_scales, d_zps);
+                else
+                    k_dequantize_rows<VF_DT_U8><<<rgrid, kBlock, 0, ctx->stream>>>(static_cast<const uint32_t*>(in), reinterpret_cast<float4*>(out),
+                                                                                   uint32_t(n_units), uint32_t(cpr), uint32_t(axis_size), row_words,
+                                                                                   static_cast<const DequantRow*>(rows.p), d_scales, d_zps);
+                post_launch(ctx);
+                return;
+            }
+        }
         const int64_t chunk = int64_t(kRowUnroll) * kBlock, chunks_per_row = (row_len + chunk - 1) / chunk;
         if (row_len >= chunk && row_len < (int64_t(1) << 31) && n_rows * chunks_per_row < (int64_t(1) << 31)) {
             const int64_t n_chunks = n_rows * chunks_per_row;
@@ -1433,6 +1872,40 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
     const int a = g.rank - 1;
     for (int d = 0; d < a; ++d)
         if (g.src_stride[d] == 1 && g.out_shape[d] >= 8) b = d;
+    if (es <= 4 && a >= 1 && g.src_stride[a - 1] == 1 && g.src_stride[a] == g.out_shape[a - 1] && g.out_shape[a - 1] >= 2 &&
+        (g.out_shape[a] * es) % 16 == 0 && aligned16(in, out)) {
+        // the two innermost output dims are one contiguous block of the source: whole chunks through shared memory
+        const int64_t ea = g.out_shape[a], eb = g.out_shape[a - 1], ve = 16 / es;
+        const int64_t budget = 24 * 1024 - 32;  // per buffer, two buffers per CTA
+        int64_t rows = std::min<int64_t>(ea, budget / (eb * es) / ve * ve);
+        const bool bank_stride = (ve * eb * es) % 128 == 0;  // lanes of a store vector would meet in one bank
+        int64_t others = 1;
+        for (int d = 0; d < a - 1; ++d) others *= g.out_shape[d];
+        const int64_t chunks_a = rows > 0 ? (ea + rows - 1) / rows : 0;
+        if (rows * es >= 64 && !bank_stride && chunks_a * others < (int64_t(1) << 31)) {
+            int64_t src_elems = 1;
+            for (int d = 0; d < g.rank; ++d) src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
+            const int64_t total_bytes = src_elems * es;  // the last byte the launch may read lies inside the source buffer
+            const uint32_t buf_vecs = uint32_t((rows * eb * es + 15 + 15) / 16);
+            const size_t smem = size_t(buf_vecs) * 32;
+            const int64_t n_chunks = chunks_a * others;
+            const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (200 * 1024) / int64_t(smem + 1024)));
+            const unsigned blocks = unsigned(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * per_sm));
+            if (small) {
+                using I = uint32_t;
+                VF_BY_ELEM_SIZE(es, (k_transpose_slices<(ES > 4 ? 4 : ES), I><<<blocks, kBlock, smem, ctx->stream>>>(
+                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, I(chunks_a), I(n_chunks), uint32_t(rows), buf_vecs,
+                                        total_bytes)));
+            } else {
+                using I = int64_t;
+                VF_BY_ELEM_SIZE(es, (k_transpose_slices<(ES > 4 ? 4 : ES), I><<<blocks, kBlock, smem, ctx->stream>>>(
+                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, I(chunks_a), I(n_chunks), uint32_t(rows), buf_vecs,
+                                        total_bytes)));
+            }
+            post_launch(ctx);
+            return;
+        }
+    }
     if (es <= 8 && b >= 0 && g.src_stride[a] != 1 && g.out_shape[a] >= 8) {
         const int64_t ta = (g.out_shape[a] + kTile - 1) / kTile, tb = (g.out_shape[b] + kTile - 1) / kTile;
         int64_t others = 1, dst_stride_b = 1;

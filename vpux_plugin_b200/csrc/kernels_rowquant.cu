@@ -59,6 +59,7 @@ struct LaunchParams {  // uniform over all jobs of one launch
     float thr;            // 0.5 - guard: largest rounding residual the fast path accepts
     double den, inv_den;  // qmax - qmin and RN(1 / (qmax - qmin))
     int64_t total_units;  // chunks (k_group) or rows (k_row / k_conv) over all jobs
+    int64_t total_work;   // k_convv: sum of the units' costs
 };
 
 __device__ __forceinline__ void unit_consts(double scale, long long zp, const LaunchParams& p, UnitQ& u) {
@@ -75,6 +76,18 @@ __device__ __forceinline__ void unit_consts(double scale, long long zp, const La
 // multiplication by the correctly rounded reciprocal and one correction step give the correctly rounded
 // quotient. zp = round(qMin - rMin / scale) is an integer in the storage range: it is evaluated in fp32 first
 // (error below 1e-4) and only a value within 1e-3 of a rounding boundary takes the FP64 division.
+// the cases the cheap evaluation leaves out (kept out of line: two FP64 divisions and their temporaries): a zero
+// point next to a rounding boundary (exact = true: scale is already final) and degenerate or extreme ranges
+__device__ __noinline__ long long derive_unit_rare(float mn, float mx, int qmin, int qmax, bool exact, double& scale, int* flags) {
+    long long zp;
+    if (exact) return (long long)(round(__dsub_rn(double(qmin), __ddiv_rn(double(mn), scale))));
+    if (!calc_scale_zp(double(qmin), double(qmax), double(mn), double(mx), scale, zp)) {
+        set_flag(flags, VF_FLAG_QUANT_RANGE);
+        scale = 1.0;
+        zp = 0;
+    }
+    return zp;
+}
 __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchParams& p, double& scale, long long& zp,
                                             UnitQ& u, int* flags) {
     mn = fminf(mn, 0.f);  // the range always contains zero (calcScaleAndZeroPoint requires it)
@@ -92,14 +105,12 @@ __device__ __forceinline__ void derive_unit(float mn, float mx, const LaunchPara
         const float xf = __fmaf_rn(-mn, __fdividef(float(p.lm1), df), float(p.qmin));
         const float fl = floorf(xf);
         if (fabsf(__fsub_rn(__fsub_rn(xf, fl), 0.5f)) < 1.0e-3f) {
-            zp = (long long)(round(__dsub_rn(double(p.qmin), __ddiv_rn(double(mn), scale))));
+            zp = derive_unit_rare(mn, mx, p.qmin, p.qmax, true, scale, flags);
         } else {
             zp = (long long)(floorf(__fadd_rn(xf, 0.5f)));
         }
-    } else if (!calc_scale_zp(double(p.qmin), double(p.qmax), double(mn), double(mx), scale, zp)) {
-        set_flag(flags, VF_FLAG_QUANT_RANGE);
-        scale = 1.0;
-        zp = 0;
+    } else {
+        zp = derive_unit_rare(mn, mx, p.qmin, p.qmax, false, scale, flags);
     }
     zp = zp < p.qmin ? p.qmin : (zp > p.qmax ? p.qmax : zp);
     unit_consts(scale, zp, p, u);
@@ -163,8 +174,15 @@ struct MinMax2 {
     }
     __device__ __forceinline__ void add(const uint4& d) {
         const T2 a = as_p2<InT>(d.x), b = as_p2<InT>(d.y), c = as_p2<InT>(d.z), e = as_p2<InT>(d.w);
-        mn = __hmin2(mn, __hmin2(__hmin2(a, b), __hmin2(c, e)));
+        mn = __hmin2_nan(mn, __hmin2_nan(__hmin2_nan(a, b), __hmin2_nan(c, e)));  // a NaN sticks to the running minimum
         mx = __hmax2(mx, __hmax2(__hmax2(a, b), __hmax2(c, e)));
+    }
+    // Quantize of a NaN is undefined in the reference (a NaN passes both comparisons of fakeQuantize and is cast
+    // to an integer): the kernels report it
+    __device__ __forceinline__ bool saw_nan() const {
+        const uint32_t w = as_u32(mn);
+        const float lo = P2<InT>::lo(w), hi = P2<InT>::hi(w);
+        return lo != lo || hi != hi;
     }
     __device__ __forceinline__ float min_f() const {
         const uint32_t w = as_u32(mn);
@@ -497,6 +515,7 @@ __device__ __forceinline__ void group_chunk(uint4* stage, const GroupJob& J, int
 #pragma unroll
     for (int k = 0; k < V; ++k) mm.add(mine[k]);
     const float mn = mm.min_f(), mx = mm.max_f();
+    if (mm.saw_nan()) set_flag(flags, VF_FLAG_NAN);
 
     const int64_t g = g0 + lane;
     const bool g_ok = g < J.total_groups;
@@ -743,6 +762,7 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
 
         MinMax2<InT> mm;
         for (int i = tid; i < nvec; i += THREADS) mm.add(smem_u4[i]);
+        if (mm.saw_nan()) set_flag(flags, VF_FLAG_NAN);
         float mn = warp_min(mm.min_f()), mx = warp_max(mm.max_f());
         if (lane == 0) {
             s_mn[wid] = mn;
@@ -920,6 +940,7 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
         float mn = 0.f, mx = 0.f;
         for (int64_t i = lane; i < J.cols; i += 32) {
             const float x = load_as_f32(J.in, in_dt, base + i, nullptr);
+            if (x != x) set_flag(flags, VF_FLAG_NAN);  // undefined in the reference: reported
             mn = fminf(mn, x);
             mx = fmaxf(mx, x);
         }
@@ -979,20 +1000,22 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
 
 // ======================================================================================================
 // K_convv: the vectorised form of K_conv for 2-byte inputs whose rows are 16-byte multiples (every ResNet-style
-// convolution with IC % 8 == 0). One warp per output channel: the row is copied into the warp's shared-memory
-// stage with cp.async, min/max run on packed pairs, the codes are written back into the stage as a dense byte
-// row in input order (the eight codes of vector v at byte 8 v: only over vectors every lane has consumed) and
-// then copied out — straight for 1x1 kernels, transposed OIYX->OYXI otherwise: the (tap, channel block) pairs of
-// the output row are dealt out over the lanes, every lane gathers the codes of 16 (or 4) consecutive input
-// channels of one tap and stores them as one vector.
+// convolution with IC % 8 == 0). One warp per output channel, and nothing of the input is staged: the lanes read
+// the row with 16-byte loads into registers, min/max run on packed pairs, and the second pass quantizes the
+// registers (rows longer than 1024 elements read all but their last 1024 again, from the caches). A 1x1 kernel's
+// codes go straight to the output row; otherwise they are collected in the warp's shared-memory stage as a dense
+// byte row in input order and copied out transposed OIYX->OYXI: the (tap, channel block) pairs of the output row
+// are dealt out over the lanes, every lane gathers the codes of 16 (or 4) consecutive input channels of one tap
+// and stores them as one vector. Without an input stage a CTA needs one byte of shared memory per element of its
+// eight rows, so four CTAs fit an SM whatever the row length.
 // ======================================================================================================
-template <int W>  // bytes per lane and store: 16 or 4
-__device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, int khw, int ic, int ic_pad, int lane) {
+template <int W>  // bytes per lane and store: 16 or 4; `lanes` lanes (sub = 0 .. lanes - 1) share the row
+__device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, int khw, int ic, int ic_pad, int sub, int lanes) {
     const int blocks = ic_pad / W;           // channel blocks per tap
     const int total = khw * blocks;          // stores of the row
-    const int q32 = 32 / blocks, r32 = 32 % blocks;
-    int s = lane / blocks, cblk = lane % blocks;
-    for (int o = lane; o < total; o += 32) {
+    const int qs = lanes / blocks, rs = lanes % blocks;
+    int s = sub / blocks, cblk = sub % blocks;
+    for (int o = sub; o < total; o += lanes) {
         const int c0 = cblk * W;
         uint32_t w[W / 4];
 #pragma unroll
@@ -1008,8 +1031,8 @@ __device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, 
         uint8_t* dst = out + size_t(s) * ic_pad + c0;
         if (W == 16) st_global_v4(dst, w[0], w[1], w[2], w[3]);
         else *reinterpret_cast<uint32_t*>(dst) = w[0];
-        s += q32;
-        cblk += r32;
+        s += qs;
+        cblk += rs;
         if (cblk >= blocks) {
             cblk -= blocks;
             ++s;
@@ -1017,104 +1040,200 @@ __device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, 
     }
 }
 
+// A row the packed sequence does not cover (its range or its extreme indices are out of bounds): every element
+// with the scalar sequence, read again from global memory. Rare, and kept out of line.
 template <typename InT>
-__global__ void __launch_bounds__(256) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int in_vecs, int* flags) {
+__device__ __noinline__ void convv_row_scalar(const uint4* src, int nvec, int sub, int lanes, UnitQ u, float thr, int lm1, int qmin, uint2* dst) {
+    for (int v = sub; v < nvec; v += lanes) {
+        const uint2 idx = quant8_fix_idx<InT>(__ldg(src + v), u, thr, lm1, true);
+        dst[v] = make_uint2(idx_to_codes4(idx.x, qmin), idx_to_codes4(idx.y, qmin));
+    }
+}
+
+// The fields of a job K_convv needs, read once per tensor a warp works on
+struct ConvJob {
+    const RowQuantArgs* args;      // the side outputs and supplied parameters are read where they are used
+    const void* in;
+    uint8_t* codes;
+    int rows, rows_pad, row_vecs;  // row_vecs: 16-byte vectors per input row
+    int khw, ic, ic_pad;           // khw == 0: the codes are the output row as they are
+    int out_bytes;                 // bytes of an output row
+    int lpr;
+    int64_t unit_begin, unit_end, work_begin;
+    int unit_cost;
+};
+__device__ __forceinline__ void load_conv_job(const RowQuantArgs* __restrict__ jobs, int j, const LaunchParams& p, ConvJob& J) {
+    const RowQuantArgs& A = jobs[j];
+    J.args = &A;
+    J.in = A.in;
+    J.codes = static_cast<uint8_t*>(A.codes);
+    J.rows = int(A.rows);
+    J.rows_pad = int(A.rows_pad);
+    J.row_vecs = int(A.cols >> 3);
+    J.khw = int(A.khw);
+    J.ic = A.khw > 0 ? int(A.ic) : int(A.cols);
+    J.ic_pad = A.khw > 0 ? int(A.ic_pad) : int(A.cols);
+    J.out_bytes = (A.khw > 0 ? int(A.khw) : 1) * J.ic_pad;
+    J.lpr = A.lanes_per_row;
+    J.unit_begin = A.unit_begin;
+    J.unit_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+    J.work_begin = A.work_begin;
+    J.unit_cost = A.unit_cost;
+}
+
+// One unit of K_convv: 32 / LPR consecutive output channels of one tensor, LPR lanes each. Every group runs the
+// same instruction stream (same tensor, same row length); a group without a row (past the tensor's last channel)
+// loads nothing and stores nothing but takes part in the shuffles.
+template <typename InT>
+__device__ __forceinline__ void convv_unit(const ConvJob& J, int64_t unit_in_job, const LaunchParams& p, uint4* stage, int stage_vecs,
+                                           int lane, int* flags) {
+    constexpr int kB = 4;             // vectors per lane and batch
+    const int LPR = J.lpr;            // 8, 16 or 32 (one code path: the tensor's value is uniform over the warp)
+    const int lpr_shift = LPR == 8 ? 3 : (LPR == 16 ? 4 : 5);
+    const int RPW = 32 >> lpr_shift;  // rows per warp
+    const int sub = lane & (LPR - 1), grp = lane >> lpr_shift;
+    const int r = int(unit_in_job) * RPW + grp;
+    const int out_bytes = J.out_bytes;
+    uint8_t* out = J.codes + int64_t(r) * out_bytes;
+    const bool live = r < J.rows;
+    if (!live && r < J.rows_pad) {  // padded output channel
+        uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+        for (int w = sub; w < (out_bytes >> 2); w += LPR) o32[w] = 0u;
+    }
+    const int row_vecs = J.row_vecs;
+    const int nvec = live ? row_vecs : 0;
+    const int nb = (row_vecs + kB * LPR - 1) / (kB * LPR);
+    const uint4* src = static_cast<const uint4*>(J.in) + int64_t(live ? r : 0) * row_vecs;
+    // first pass: the range. The vectors of the last batch stay in registers for the second pass (rows of up to
+    // 32 LPR elements are read once); earlier batches are read again, from the caches.
+    uint4 d[kB];
+    MinMax2<InT> mm;
+    for (int b = 0; b < nb; ++b) {
+#pragma unroll
+        for (int k = 0; k < kB; ++k) {
+            const int v = (b * kB + k) * LPR + sub;
+            d[k] = make_uint4(0u, 0u, 0u, 0u);  // zeros do not move a range that contains zero
+            if ((b * kB + k) * LPR < row_vecs && v < nvec) d[k] = __ldg(src + v);
+        }
+#pragma unroll
+        for (int k = 0; k < kB; ++k) mm.add(d[k]);
+    }
+    if (mm.saw_nan()) set_flag(flags, VF_FLAG_NAN);
+    float mn = mm.min_f(), mx = mm.max_f();
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        if (o < LPR) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+    }
+    // every lane of the group evaluates the row's parameters (same inputs, same results): nothing to broadcast
+    UnitQ u;
+    {
+        double scale;
+        long long zp;
+        if (p.given) {
+            scale = live ? J.args->given_scales[r] : 1.0;
+            zp = live ? J.args->given_zps[r] : 0;
+            unit_consts(scale, zp, p, u);
+        } else {
+            derive_unit(mn, mx, p, scale, zp, u, flags);
+            if (sub == 0 && live) {
+                const RowQuantArgs& A = *J.args;
+                if (A.scales) A.scales[r] = scale;
+                if (A.zps) A.zps[r] = zp;
+                if (A.scales_f16) A.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
+            }
+        }
+    }
+    const bool fast = unit_exact_ok(u, mn, mx, p);
+
+    // second pass, last batch first. The codes of a 1x1 kernel are the output row as they are; otherwise they
+    // are collected in the group's part of the stage for the transposed copy-out.
+    const bool direct = J.khw <= 0 && (reinterpret_cast<uintptr_t>(J.codes) & 7) == 0;
+    uint4* my_stage = stage + grp * (stage_vecs >> (5 - lpr_shift));
+    uint2* dst2 = reinterpret_cast<uint2*>(direct ? static_cast<void*>(out) : static_cast<void*>(my_stage));
+    const ExactQ eq = exact_consts(u, p.lm1, float(p.qmin));  // K = qmin: the low byte is the code
+    for (int b = nb - 1; b >= 0; --b) {
+        if (b != nb - 1) {
+#pragma unroll
+            for (int k = 0; k < kB; ++k) d[k] = __ldg(src + (b * kB + k) * LPR + sub);  // every batch but the last is full
+        }
+#pragma unroll
+        for (int k = 0; k < kB; ++k) {
+            if ((b * kB + k) * LPR >= row_vecs) break;  // uniform over the warp
+            const int v = (b * kB + k) * LPR + sub;
+            if (v < nvec && fast) dst2[v] = exact8_bytes<InT, false>(d[k], eq, dup(0.f), nullptr);
+        }
+    }
+    if (!fast) convv_row_scalar<InT>(src, nvec, sub, LPR, u, p.thr, p.lm1, p.qmin, dst2);
+    if (direct) return;  // uniform over the warp: a property of the tensor
+    __syncwarp();
+    if (live) {
+        const bool out16 = (reinterpret_cast<uintptr_t>(J.codes) & 15) == 0 && (out_bytes & 15) == 0;
+        if (J.khw <= 0) {
+            const uint32_t* c32 = reinterpret_cast<const uint32_t*>(my_stage);
+            uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+            for (int w = sub; w < (out_bytes >> 2); w += LPR) o32[w] = c32[w];
+        } else if (out16 && (J.ic_pad & 15) == 0) {
+            convv_copy_out<16>(reinterpret_cast<const uint8_t*>(my_stage), out, J.khw, J.ic, J.ic_pad, sub, LPR);
+        } else {
+            convv_copy_out<4>(reinterpret_cast<const uint8_t*>(my_stage), out, J.khw, J.ic, J.ic_pad, sub, LPR);
+        }
+    }
+    __syncwarp();  // the stage is rewritten by the next unit
+}
+
+// lanes per row of K_convv: the fewest (8, 16 or 32) that hold the row in one batch of four vectors per lane
+inline int convv_lanes_per_row(int64_t cols) {
+    return cols <= 256 ? 8 : (cols <= 512 ? 16 : 32);
+}
+// Relative cost of one unit, in warp instructions / 8: what does not depend on the row length plus the batches
+inline int convv_unit_cost(int64_t cols, int64_t khw, int lanes_per_row) {
+    const int64_t steps = (cols / 8 + lanes_per_row - 1) / lanes_per_row;  // vectors per lane
+    return int(30 + steps * (khw > 0 ? 12 : 8));
+}
+
+// The units of all tensors form one list, each with a cost; a warp takes the units whose cumulative cost starts
+// inside its share [W0, W1) of the total. Its units are consecutive, so it meets a new tensor rarely: the job
+// table is searched once per warp, and a tensor's fields are read once per tensor and warp.
+#ifndef VF_GVAR
+#define VF_GVAR 0
+#endif
+#define VF_CONVV_OCC (4 - VF_GVAR)
+template <typename InT>
+__global__ void __launch_bounds__(256, VF_CONVV_OCC) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs, int* flags) {
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    uint4* in_stage = smem_u4 + size_t(wid) * size_t(in_vecs);
-    const uint8_t* code_bytes_p = reinterpret_cast<const uint8_t*>(in_stage);
+    uint4* stage = smem_u4 + size_t(wid) * size_t(stage_vecs);  // codes, one byte per element in input order
     const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
-    const float thr = p.thr;
-    int64_t job_end = 0;
-    RowQuantArgs J;
-
-    for (int64_t row = int64_t(blockIdx.x) * (blockDim.x >> 5) + wid; row < p.total_units; row += nwarps) {
-        if (row >= job_end) {
-            const int j = find_job(jobs, p.njobs, row);
-            J = jobs[j];
-            job_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
+    // warps of one CTA take shares far apart (share = wid * gridDim + blockIdx): a CTA's rows differ in length
+    const int64_t gw = int64_t(wid) * gridDim.x + blockIdx.x;
+    const int64_t W0 = p.total_work / nwarps * gw + min(gw, p.total_work % nwarps);
+    const int64_t W1 = p.total_work / nwarps * (gw + 1) + min(gw + 1, p.total_work % nwarps);
+    if (W0 >= W1) return;
+    int j;
+    {
+        int lo = 0, hi = p.njobs - 1;
+        while (lo < hi) {  // last job whose work_begin <= W0
+            const int mid = (lo + hi + 1) >> 1;
+            if (jobs[mid].work_begin <= W0) lo = mid;
+            else hi = mid - 1;
         }
-        const int64_t r = row - J.unit_begin;
-        const int khw = J.khw > 0 ? int(J.khw) : 1;
-        const int ic = J.khw > 0 ? int(J.ic) : int(J.cols);
-        const int ic_pad = J.khw > 0 ? int(J.ic_pad) : int(J.cols);
-        const int out_bytes = khw * ic_pad;
-        uint8_t* out = static_cast<uint8_t*>(J.codes) + r * int64_t(out_bytes);
-        const bool out16 = (reinterpret_cast<uintptr_t>(J.codes) & 15) == 0 && (out_bytes & 15) == 0;
-        if (r >= J.rows) {  // padded output channel
-            uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
-            for (int w = lane; w < (out_bytes >> 2); w += 32) o32[w] = 0u;
-            continue;
+        j = lo;
+    }
+    ConvJob J;
+    load_conv_job(jobs, j, p, J);
+    int64_t unit = J.unit_begin + (W0 - J.work_begin + J.unit_cost - 1) / J.unit_cost;
+    for (;;) {
+        while (unit >= J.unit_end) {
+            if (++j >= p.njobs) return;
+            load_conv_job(jobs, j, p, J);
         }
-        const int nvec = int(J.cols >> 3);
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(J.in) + r * J.cols);
-        for (int v = lane; v < nvec; v += 32) cp_async16(in_stage + v, src + v, true);
-        cp_async_wait_all();  // each lane reads back only the vectors it copied itself
-
-        MinMax2<InT> mm;
-        for (int v = lane; v < nvec; v += 32) mm.add(in_stage[v]);
-        const float mn = warp_min(mm.min_f()), mx = warp_max(mm.max_f());
-        UnitQ u;
-        u.inv = u.zq = u.in_low = u.range = u.y = 0.f;
-        int fast = 1;
-        if (lane == 0) {
-            double scale;
-            long long zp;
-            if (p.given) {
-                scale = J.given_scales[r];
-                zp = J.given_zps[r];
-                unit_consts(scale, zp, p, u);
-            } else {
-                derive_unit(mn, mx, p, scale, zp, u, flags);
-                if (J.scales) J.scales[r] = scale;
-                if (J.zps) J.zps[r] = zp;
-                if (J.scales_f16) J.scales_f16[r] = f32_to_f16_bits(__double2float_rn(scale));
-            }
-            fast = unit_exact_ok(u, mn, mx, p) ? 1 : 0;
-        }
-        u.inv = __shfl_sync(0xffffffffu, u.inv, 0);
-        u.zq = __shfl_sync(0xffffffffu, u.zq, 0);
-        u.in_low = __shfl_sync(0xffffffffu, u.in_low, 0);
-        u.range = __shfl_sync(0xffffffffu, u.range, 0);
-        u.y = __shfl_sync(0xffffffffu, u.y, 0);
-        fast = __shfl_sync(0xffffffffu, fast, 0);
-
-        const ExactQ eq = exact_consts(u, p.lm1, float(p.qmin));  // K = qmin: the low byte is the code
-        for (int v0 = 0; v0 < nvec; v0 += 32) {
-            const int v = v0 + lane;
-            uint2 c = make_uint2(0u, 0u);
-            if (v < nvec) {
-                const uint4 d = in_stage[v];
-                if (fast) {
-                    c = exact8_bytes<InT, false>(d, eq, dup(0.f), nullptr);
-                } else {
-                    const uint2 idx = quant8_fix_idx<InT>(d, u, thr, p.lm1, true);
-                    c = make_uint2(idx_to_codes4(idx.x, p.qmin), idx_to_codes4(idx.y, p.qmin));
-                }
-            }
-            // the codes of vectors [v0, v0 + 32) go to bytes [8 v0, 8 v0 + 256): vectors up to v0 / 2 + 16 of the stage,
-            // all of them consumed once every lane holds this step's vector in registers
-            __syncwarp();
-            if (v < nvec) reinterpret_cast<uint2*>(in_stage)[v] = c;
-        }
-        __syncwarp();
-        if (J.khw <= 0) {
-            if (out16) {
-                for (int w = lane; w < (out_bytes >> 4); w += 32) {
-                    const uint4 vv = in_stage[w];
-                    st_global_v4(out + size_t(w) * 16, vv.x, vv.y, vv.z, vv.w);
-                }
-            } else {
-                const uint32_t* c32 = reinterpret_cast<const uint32_t*>(in_stage);
-                uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
-                for (int w = lane; w < (out_bytes >> 2); w += 32) o32[w] = c32[w];
-            }
-        } else if (out16 && (ic_pad & 15) == 0) {
-            convv_copy_out<16>(code_bytes_p, out, khw, ic, ic_pad, lane);
-        } else {
-            convv_copy_out<4>(code_bytes_p, out, khw, ic, ic_pad, lane);
-        }
-        __syncwarp();  // the stage is rewritten by the next row
+        const int64_t u = unit - J.unit_begin;
+        if (J.work_begin + u * J.unit_cost >= W1) return;
+        convv_unit<InT>(J, u, p, stage, stage_vecs, lane, flags);
+        ++unit;
     }
 }
 
@@ -1243,7 +1362,15 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         a.unit_begin = units;
         if (kind == 1) units += (a.rows * (a.cols / a.group) + 31) / 32;
         else if (kind == 2) units += a.rows;
-        else units += a.rows_pad;
+        else if (kind == 4) {
+            a.lanes_per_row = convv_lanes_per_row(a.cols);
+            const int64_t rpw = 32 / a.lanes_per_row;
+            const int64_t n_units = (a.rows_pad + rpw - 1) / rpw;
+            a.unit_cost = convv_unit_cost(a.cols, a.khw, a.lanes_per_row);
+            a.work_begin = p.total_work;
+            p.total_work += n_units * a.unit_cost;
+            units += n_units;
+        } else units += a.rows_pad;
         max_cols = std::max(max_cols, a.cols);
         max_out_row = std::max(max_out_row, a.khw > 0 ? a.khw * a.ic_pad : a.cols);
     }
@@ -1260,17 +1387,23 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         if (a0.in_dt == VF_DT_F16) launch_row_t<__half>(ctx, d_jobs, p, max_cols, dq);
         else launch_row_t<__nv_bfloat16>(ctx, d_jobs, p, max_cols, dq);
     } else if (kind == 4) {
-        const int in_vecs = int((max_cols + 7) / 8);
-        const size_t smem = size_t(8) * size_t(in_vecs) * 16;
-        const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024)));
+        // the stage holds codes only, and only rows that are copied out transposed (or to a misaligned buffer) use it:
+        // the rows of a warp side by side, each in a 16-byte multiple
+        int64_t stage_vecs64 = 4;
+        for (auto& a : jobs)
+            if (a.khw > 0 || (reinterpret_cast<uintptr_t>(a.codes) & 7) != 0)
+                stage_vecs64 = std::max(stage_vecs64, ((a.cols + 15) / 16) * (32 / a.lanes_per_row));
+        const int stage_vecs = int(stage_vecs64);
+        const size_t smem = size_t(8) * size_t(stage_vecs) * 16;
+        const size_t per_sm = std::max<size_t>(1, std::min<size_t>(VF_CONVV_OCC, (220 * 1024) / (smem + 1024)));
         const int64_t blocks = (units + 7) / 8;
         const int grid = int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * int64_t(per_sm)));
         if (a0.in_dt == VF_DT_F16) {
             set_smem(k_convv<__half>, smem);
-            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, ctx->d_flags);
+            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
         } else {
             set_smem(k_convv<__nv_bfloat16>, smem);
-            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, in_vecs, ctx->d_flags);
+            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
         }
         post_launch(ctx);
     } else if (kind == 3) {

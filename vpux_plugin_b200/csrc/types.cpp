@@ -75,7 +75,7 @@ ParamCheckScope::~ParamCheckScope() {
     if (--tl_check_depth == 0) tl_checked.clear();
 }
 
-Elem Elem::from(const vf_elem_type& e) {
+Elem Elem::from(const vf_elem_type& e, bool check_scales) {
     Elem r;
     r.kind = e.kind;
     r.dtype = e.dtype;
@@ -92,6 +92,7 @@ Elem Elem::from(const vf_elem_type& e) {
     r.zps.borrow(e.zps, size_t(e.nparams));
     // a quantized type cannot be built with such a scale: mlir::quant::UniformQuantized[PerAxis]Type::verify
     // rejects scale <= 0, infinities and NaN ("illegal scale")
+    if (!check_scales) return r;
     if (tl_check_depth > 0 && e.nparams > 64) {
         const auto it = tl_checked.find(e.scales);
         if (it != tl_checked.end() && it->second >= e.nparams) return r;
