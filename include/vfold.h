@@ -221,13 +221,16 @@ typedef struct vf_transform {
 typedef struct vf_ctx vf_ctx;
 
 #define VF_OPT_DISABLE_FUSION 1 /* run vf_quantize_fold through the unfused general kernels (for cross-checks) */
-/* Pipelined calls: vf_fold, vf_fold_batch, vf_quantize_fold_batch and vf_weights_table_batch calls whose tensors
- * ALL live in device memory return as soon as their work is enqueued on the context's stream, so the host prepares the next
- * batch while the GPU runs this one (what the background folder does with its thread pool,
- * const/utils/constant_folding_in_background.cpp:154-194). Host-side checks (shapes, types, sizes) still fail
- * the call itself; what a kernel reports (a checked_cast, a range without zero, a table range) is returned by
- * the next synchronising call of the context — any call that touches host memory, vf_sparsify*, or
- * vf_ctx_synchronize — and the buffers of a deferred call must stay alive until then. */
+/* Pipelined calls: vf_fold, vf_fold_batch, vf_quantize_fold_batch, vf_weights_table_batch and vf_sparsify_batch
+ * calls whose tensors ALL live in device memory return as soon as their work is enqueued on the context's stream,
+ * so the host prepares the next batch while the GPU runs this one (what the background folder does with its
+ * thread pool, const/utils/constant_folding_in_background.cpp:154-194). Host-side checks (shapes, types, sizes)
+ * still fail the call itself; what a kernel reports (a checked_cast, a range without zero, a table range) is
+ * returned by the next synchronising call of the context — any call that touches host memory, vf_sparsify,
+ * vf_sparsify_noalloc or vf_ctx_synchronize — and the buffers of a deferred call must stay alive until then. A
+ * deferred vf_sparsify_batch leaves `data_written` of its jobs at 0; the synchronising call fills them in (the job
+ * array must stay alive, too) and reports a compressed set that did not fit its buffer (VF_ERR_BUFFER_TOO_SMALL;
+ * nothing is written past a buffer's end). */
 #define VF_OPT_ASYNC 2
 /* Synchronous calls that take a vf_stats also measure the device time between their first and their last
  * enqueued operation (a pair of CUDA events on the context's stream) into vf_stats.device_ms. */

@@ -272,6 +272,63 @@ def test_sparsify_batch_buffer_too_small(gpu):
     assert jobs[0].status == abi.VF_ERR_BUFFER_TOO_SMALL
 
 
+def test_sparsify_batch_pipelined_sizes_arrive_with_the_next_synchronisation(oracle):
+    """VF_OPT_ASYNC, everything in device memory: vf_sparsify_batch returns once enqueued with data_written still 0;
+    vf_ctx_synchronize fills the sizes in, and reports a compressed set that did not fit (nothing written past
+    the end of its buffer)."""
+    import torch
+    from vpux_plugin_b200.lib import Library, VfoldError
+    lib = Library(device=0, pipelined=True)
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(5)
+    shapes = [[64, 128, 3, 3], [33, 64, 1, 1], [130, 16, 1, 1]]
+    jobs = (abi.SparsifyJob * len(shapes))()
+    keep, expect = [], []
+    for j, shape in enumerate(shapes):
+        n = int(np.prod(shape))
+        work = n // shape[0]
+        x = np.where(rng.random(n) < 0.4, rng.integers(1, 100, n), 0).astype(np.int8)
+        hc, hk = abi.make_content(TType(shape, I8), x)
+        row = (work + 127) // 128 * 16
+        cap = n + 16 * shape[0]
+        od, om, oc_ = np.zeros(cap, np.uint8), np.zeros(shape[0] * row, np.uint8), np.zeros(shape[0], np.int64)
+        w = oracle.sparsify(hc, od, om, oc_)
+        src = torch.from_numpy(x.view(np.uint8)).to(dev)
+        data = torch.full((cap + 64,), 0xAB, dtype=torch.uint8, device=dev)
+        mp = torch.zeros(shape[0] * row, dtype=torch.uint8, device=dev)
+        cnt = torch.zeros(shape[0], dtype=torch.int64, device=dev)
+        c, k = abi.make_content(TType(shape, I8), None, ptr=src.data_ptr(), nbytes=n, mem_kind=abi.VF_MEM_DEVICE)
+        jobs[j].content, jobs[j].data, jobs[j].data_bytes = c, data.data_ptr(), cap
+        jobs[j].map, jobs[j].map_bytes, jobs[j].counts = mp.data_ptr(), mp.numel(), cnt.data_ptr()
+        keep += [src, k, hk]
+        expect.append((w, od, om, oc_, data, mp, cnt, cap))
+    torch.cuda.synchronize()
+    for _ in range(3):  # several calls in flight
+        lib.sparsify_batch(jobs, out_mem_kind=abi.VF_MEM_DEVICE)
+    lib.synchronize()
+    for j, (w, od, om, oc_, data, mp, cnt, cap) in enumerate(expect):
+        assert jobs[j].data_written == w, j
+        got = data.cpu().numpy()
+        assert np.array_equal(got[:w], od[:w]) and (got[cap:] == 0xAB).all(), j
+        assert np.array_equal(mp.cpu().numpy(), om) and np.array_equal(cnt.cpu().numpy(), oc_), j
+    # a buffer that is too small: the call returns, the synchronisation reports it, the bytes behind the buffer stay
+    small = expect[0][0] - 48
+    jobs[0].data_bytes = small
+    expect[0][4][small:] = 0xCD
+    torch.cuda.synchronize()
+    lib.sparsify_batch(jobs, out_mem_kind=abi.VF_MEM_DEVICE)
+    with pytest.raises(VfoldError) as e:
+        lib.synchronize()
+    assert e.value.status == abi.VF_ERR_BUFFER_TOO_SMALL and jobs[0].status == abi.VF_ERR_BUFFER_TOO_SMALL
+    assert jobs[0].data_written == expect[0][0]  # the size that is needed
+    assert (expect[0][4].cpu().numpy()[small:] == 0xCD).all()
+    jobs[0].data_bytes = expect[0][7]
+    lib.sparsify_batch(jobs, out_mem_kind=abi.VF_MEM_DEVICE)  # the context stays usable
+    lib.synchronize()
+    assert jobs[0].data_written == expect[0][0]
+    lib.close()
+
+
 @pytest.mark.parametrize("src,dst", [(abi.VF_DT_U4, U8), (abi.VF_DT_I4, I8), (abi.VF_DT_I1, I8), (abi.VF_DT_I1, U8)])
 @pytest.mark.parametrize("n", [1, 7, 8, 9, 63, 4096, 100003])
 def test_convert_elem_type_unpacks_sub_byte(gpu, oracle, src, dst, n):

@@ -236,6 +236,17 @@ struct vf_ctx {
     int* h_flags = nullptr;  // pinned mirror
     bool flags_dirty = false;  // the device flags may be non-zero (a call found something or ended early)
     bool deferred = false;     // VF_OPT_ASYNC: calls have returned whose kernels are still unchecked
+    // VF_OPT_ASYNC, vf_sparsify_batch over device memory: the compressed sizes travel to this pinned area behind the
+    // kernels; the next synchronising call writes them into the callers' jobs and checks the capacities
+    struct PendingSizes {
+        vf_sparsify_job* jobs;
+        int n;
+        size_t first;  // index of the batch's first entry in sizes_host
+    };
+    static constexpr size_t kSizesCap = 8192;
+    int64_t* sizes_host = nullptr;
+    size_t sizes_used = 0;
+    std::vector<PendingSizes> pending_sizes;
     uint64_t launches = 0;
     int32_t opt_flags = 0;
     int sm_count = 1;            // multiprocessors of the device: persistent grids are sized in multiples of it

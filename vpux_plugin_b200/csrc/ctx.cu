@@ -117,10 +117,27 @@ void flags_check(vf_ctx* ctx) {
     VF_CUDA(cudaStreamSynchronize(ctx->stream));
     VF_CUDA(cudaGetLastError());
     ctx->deferred = false;  // everything enqueued so far has finished and is being checked now
+    // deferred vf_sparsify_batch calls: their sizes have arrived
+    const vf_sparsify_job* too_small = nullptr;
+    for (const vf_ctx::PendingSizes& ps : ctx->pending_sizes) {
+        for (int j = 0; j < ps.n; ++j) {
+            vf_sparsify_job& jb = ps.jobs[j];
+            jb.data_written = uint64_t(ctx->sizes_host[ps.first + size_t(j)]);
+            if (jb.data && jb.data_written > jb.data_bytes) {
+                jb.status = VF_ERR_BUFFER_TOO_SMALL;
+                if (!too_small) too_small = &jb;
+            }
+        }
+    }
+    ctx->pending_sizes.clear();
+    ctx->sizes_used = 0;
     const int* f = ctx->h_flags;
     bool any = false;
     for (int i = 0; i < kNumFlags; ++i) any |= f[i] != 0;
     ctx->flags_dirty = any;
+    if (too_small)  // (the compaction kernel's overflow flag is the same finding)
+        raise(VF_ERR_BUFFER_TOO_SMALL, "compressed weights need %llu bytes, buffer holds %llu", (unsigned long long)too_small->data_written,
+              (unsigned long long)too_small->data_bytes);
     if (f[0]) raise(VF_ERR_CHECKED_CAST, "Can not safely cast a value to the destination element type");
     if (f[1]) raise(VF_ERR_QUANT_RANGE, "calcScaleAndZeroPoint failed: range without zero or scale too small");
     if (f[2]) raise(VF_ERR_SHAPE, "numActualElements smaller than the number of non-sparse elements");
@@ -168,6 +185,7 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
             VF_CUDA(cudaMallocHost(&c->h_flags, sizeof(int) * vf::kNumFlags));
             VF_CUDA(cudaMemset(c->d_flags, 0, sizeof(int) * vf::kNumFlags));
             VF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->table_host), vf_ctx::kTableBytes));
+            VF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->sizes_host), vf_ctx::kSizesCap * sizeof(int64_t)));
             VF_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->table_dev), vf_ctx::kTableBytes));
             // scratch pool of this context: freed scratch stays cached in it instead of going back to the driver on
             // every synchronisation; the device's default pool (and whoever else uses it) is left as it is
@@ -201,6 +219,7 @@ void vf_ctx_destroy(vf_ctx* c) {
         if (c->staging_ev[k]) cudaEventDestroy(c->staging_ev[k]);
     }
     if (c->table_host) cudaFreeHost(c->table_host);
+    if (c->sizes_host) cudaFreeHost(c->sizes_host);
     if (c->table_dev) cudaFree(c->table_dev);
     if (c->d_flags) cudaFree(c->d_flags);
     if (c->h_flags) cudaFreeHost(c->h_flags);

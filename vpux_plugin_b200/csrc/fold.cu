@@ -1362,7 +1362,9 @@ int vf_nnz_per_oc(vf_ctx* ctx, const vf_content* content, int64_t* counts, int o
 // Sparsify + GetSparsityMap + counts of `n` tensors: all tensors share three launches (counts and bitmaps,
 // offsets, compaction; the compaction's second read of the weights is served from L2 for anything smaller
 // than the cache) and ONE read-back of the compressed sizes.
-static void sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem_kind, vf_stats* stats) {
+// Returns true when the call was deferred (VF_OPT_ASYNC, everything in device memory): the sizes are still on
+// their way and the next synchronising call completes the jobs.
+static bool sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem_kind, vf_stats* stats, bool may_defer = false) {
     struct PerJob {
         DContent in, v;
         DBuf tcounts, tmap, tdata, counts_dev, offsets;
@@ -1418,6 +1420,16 @@ static void sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem
     }
     DBuf totals(ctx, size_t(n) * 8);
     launch_sparsify_batch(ctx, sj, totals.as<int64_t>());
+    bool all_device = out_mem_kind == VF_MEM_DEVICE;
+    for (int j = 0; j < n; ++j) all_device &= jobs[j].content.mem_kind == VF_MEM_DEVICE;
+    if (may_defer && all_device && (ctx->opt_flags & VF_OPT_ASYNC) && ctx->sizes_host && ctx->sizes_used + size_t(n) <= vf_ctx::kSizesCap) {
+        VF_CUDA(cudaMemcpyAsync(ctx->sizes_host + ctx->sizes_used, totals.p, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        ctx->pending_sizes.push_back(vf_ctx::PendingSizes{jobs, n, ctx->sizes_used});
+        ctx->sizes_used += size_t(n);
+        if (stats)
+            for (int j = 0; j < n; ++j) stats->bytes_out += jobs[j].map ? uint64_t(pj[j].oc * pj[j].row_bytes) : 0;
+        return true;
+    }
     std::vector<int64_t> total_host(static_cast<size_t>(n), 0);
     VF_CUDA(cudaMemcpyAsync(total_host.data(), totals.p, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
     VF_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -1438,6 +1450,7 @@ static void sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem
         jb.data_written = total;
         if (stats) stats->bytes_out += total + (jb.map ? uint64_t(p.oc * p.row_bytes) : 0);
     }
+    return false;
 }
 
 int vf_sparsify(vf_ctx* ctx, const vf_content* content, void* data, uint64_t data_bytes, uint64_t* data_written,
@@ -1464,7 +1477,7 @@ int vf_sparsify_batch(vf_ctx* ctx, vf_sparsify_job* jobs, int njobs, int out_mem
     return guard(err, errlen, [&] {
         if (njobs < 0 || (njobs > 0 && !jobs)) raise(VF_ERR_INVALID_ARG, "NULL argument");
         CallScope scope(ctx, stats);
-        if (njobs > 0) sparsify_many(ctx, jobs, njobs, out_mem_kind, stats);
+        if (njobs > 0) scope.may_defer = sparsify_many(ctx, jobs, njobs, out_mem_kind, stats, true);
         scope.finish();
     });
 }

@@ -837,11 +837,13 @@ __global__ void __launch_bounds__(256) k_permute_tiled(const void* __restrict__ 
 // rows (contiguous): it is copied into shared memory with 16-byte asynchronous copies, starting at the 16-byte
 // boundary at or below the chunk, and written out as 16-byte vectors of consecutive a: eight lanes (f16, ea = 64)
 // cover one output row, a warp four rows, contiguous in memory. Each element costs one shared-memory read. The
-// CTAs are persistent and double-buffered: the copy of a CTA's next chunk is in flight while it writes this one.
+// CTAs are persistent with a ring of three buffers: the copies of a CTA's next two chunks are in flight while it
+// writes this one (it takes more than 100 KB in flight per SM to keep the memory busy).
 __device__ __forceinline__ void cp_async16_part(void* smem_dst, const void* gsrc, int src_bytes) {
     const uint32_t sdst = uint32_t(__cvta_generic_to_shared(smem_dst));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sdst), "l"(gsrc), "r"(src_bytes) : "memory");  // the rest is zero-filled
 }
+constexpr int kSliceStages = 3;  // chunks in flight per CTA: the one being written and the copies of the next two
 template <int ES, typename I>
 __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, I chunks_a,
                                                           I n_chunks, uint32_t rows_per_chunk, uint32_t buf_vecs, int64_t total_bytes) {
@@ -853,11 +855,11 @@ __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restr
 
     struct Chunk {
         int64_t dst0;    // element offset of the (others) slice in the output
+        int64_t start;   // 16-byte aligned byte offset in the source at or below the chunk
         uint32_t a0, ta; // first row and rows of the chunk
         uint32_t lead;   // bytes in front of the chunk inside its first vector
     };
-    // coordinates of chunk `idx` and the copy of its source rows into `buf`
-    auto fetch = [&](I idx, uint4* buf) -> Chunk {
+    auto locate = [&](I idx) -> Chunk {
         Chunk c;
         I rem = idx;
         const I ca = rem % chunks_a;
@@ -881,32 +883,38 @@ __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restr
         c.a0 = uint32_t(ca) * rows_per_chunk;
         c.ta = min(rows_per_chunk, ea - c.a0);
         const int64_t first = (src0 + int64_t(c.a0) * eb) * ES;  // byte offset of the chunk in the source
-        const int64_t start = first & ~int64_t(15);
-        c.lead = uint32_t(first - start);
-        const uint32_t n_vec = (c.lead + c.ta * eb * ES + 15u) >> 4;
-        for (uint32_t v = threadIdx.x; v < n_vec; v += blockDim.x) {
-            const int64_t p = start + int64_t(v) * 16;
-            const int64_t left = total_bytes - p;  // the last vector of the buffer may be cut short
-            cp_async16_part(buf + v, in + p, left >= 16 ? 16 : int(left));
+        c.start = first & ~int64_t(15);
+        c.lead = uint32_t(first - c.start);
+        return c;
+    };
+    // the copy of chunk `idx` into buffer `slot`, as one group of asynchronous copies (an empty group past the end)
+    auto fetch = [&](I idx, int slot) {
+        if (idx < n_chunks) {
+            const Chunk c = locate(idx);
+            uint4* buf = slice_smem + slot * buf_vecs;
+            const uint32_t n_vec = (c.lead + c.ta * eb * ES + 15u) >> 4;
+            for (uint32_t v = threadIdx.x; v < n_vec; v += blockDim.x) {
+                const int64_t p = c.start + int64_t(v) * 16;
+                const int64_t left = total_bytes - p;  // the last vector of the buffer may be cut short
+                cp_async16_part(buf + v, in + p, left >= 16 ? 16 : int(left));
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        return c;
     };
 
     I idx = I(blockIdx.x);
     if (idx >= n_chunks) return;
+    const I stride = I(gridDim.x);
+#pragma unroll
+    for (int s = 0; s < kSliceStages - 1; ++s) fetch(idx + I(s) * stride, s);
     int cur = 0;
-    Chunk c = fetch(idx, slice_smem);
-    for (; idx < n_chunks; idx += I(gridDim.x)) {
-        const I next = idx + I(gridDim.x);
-        Chunk cn = c;
-        if (next < n_chunks) {
-            cn = fetch(next, slice_smem + (cur ^ 1) * buf_vecs);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+    for (; idx < n_chunks; idx += stride) {
+        int ahead = cur + kSliceStages - 1;
+        if (ahead >= kSliceStages) ahead -= kSliceStages;
+        fetch(idx + I(kSliceStages - 1) * stride, ahead);
+        asm volatile("cp.async.wait_group %0;" ::"n"(kSliceStages - 1) : "memory");
         __syncthreads();  // every thread's copies of this chunk have landed
+        const Chunk c = locate(idx);
         const T* sm = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(slice_smem + cur * buf_vecs) + c.lead);
         const uint32_t nab = c.ta / VE, n_out = nab * eb;
         const uint32_t step_b = blockDim.x / nab, step_a = blockDim.x - step_b * nab;
@@ -925,8 +933,7 @@ __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restr
             }
         }
         __syncthreads();  // this buffer is the target of the copy issued in the next iteration
-        c = cn;
-        cur ^= 1;
+        if (++cur == kSliceStages) cur = 0;
     }
 }
 
@@ -1887,10 +1894,16 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
             for (int d = 0; d < g.rank; ++d) src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
             const int64_t total_bytes = src_elems * es;  // the last byte the launch may read lies inside the source buffer
             const uint32_t buf_vecs = uint32_t((rows * eb * es + 15 + 15) / 16);
-            const size_t smem = size_t(buf_vecs) * 32;
+            const size_t smem = size_t(buf_vecs) * 16 * kSliceStages;
             const int64_t n_chunks = chunks_a * others;
-            const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (200 * 1024) / int64_t(smem + 1024)));
+            const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (216 * 1024) / int64_t(smem + 1024)));
             const unsigned blocks = unsigned(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * per_sm));
+            if (smem > 48 * 1024) {
+#define VF_SLICE_SMEM(ES_, I_) VF_CUDA(cudaFuncSetAttribute(k_transpose_slices<ES_, I_>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)))
+                VF_SLICE_SMEM(1, uint32_t); VF_SLICE_SMEM(2, uint32_t); VF_SLICE_SMEM(4, uint32_t);
+                VF_SLICE_SMEM(1, int64_t); VF_SLICE_SMEM(2, int64_t); VF_SLICE_SMEM(4, int64_t);
+#undef VF_SLICE_SMEM
+            }
             if (small) {
                 using I = uint32_t;
                 VF_BY_ELEM_SIZE(es, (k_transpose_slices<(ES > 4 ? 4 : ES), I><<<blocks, kBlock, smem, ctx->stream>>>(

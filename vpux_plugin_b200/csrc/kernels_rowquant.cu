@@ -1022,9 +1022,13 @@ __device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, 
         for (int k = 0; k < W / 4; ++k) {
             uint32_t word = 0;
             const int c = c0 + 4 * k;
-            if (c < ic) {  // ic is a multiple of 4: a word is either all data or all padding
-                const uint8_t* src = cb + c * khw + s;  // input index = channel * khw + tap
+            const uint8_t* src = cb + c * khw + s;  // input index = channel * khw + tap
+            if (c + 3 < ic) {
                 word = uint32_t(src[0]) | (uint32_t(src[khw]) << 8) | (uint32_t(src[2 * khw]) << 16) | (uint32_t(src[3 * khw]) << 24);
+            } else if (c < ic) {  // the last channels of a count that is no multiple of 4; the rest is padding
+                word = uint32_t(src[0]);
+                if (c + 1 < ic) word |= uint32_t(src[khw]) << 8;
+                if (c + 2 < ic) word |= uint32_t(src[2 * khw]) << 16;
             }
             w[k] = word;
         }
@@ -1042,12 +1046,34 @@ __device__ __forceinline__ void convv_copy_out(const uint8_t* cb, uint8_t* out, 
 
 // A row the packed sequence does not cover (its range or its extreme indices are out of bounds): every element
 // with the scalar sequence, read again from global memory. Rare, and kept out of line.
+// A row of 2-byte elements read as 16-byte vectors of eight; rows that are not whole aligned vectors (the stem of
+// a network: 3 x 7 x 7 elements) are assembled from 2-byte loads, the missing elements of the last vector as zeros.
+struct ConvRow {
+    const uint16_t* p;
+    int cols;
+    bool vec_ok;
+    __device__ __forceinline__ uint4 vec(int v) const {
+        if (vec_ok) return __ldg(reinterpret_cast<const uint4*>(p) + v);
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = 8 * v + 2 * i;
+            const uint32_t lo = e < cols ? uint32_t(__ldg(p + e)) : 0u, hi = e + 1 < cols ? uint32_t(__ldg(p + e + 1)) : 0u;
+            w[i] = lo | (hi << 16);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
 template <typename InT>
-__device__ __noinline__ void convv_row_scalar(const uint4* src, int nvec, int sub, int lanes, UnitQ u, float thr, int lm1, int qmin, uint2* dst) {
+__device__ __noinline__ void convv_row_scalar(ConvRow src, int nvec, int sub, int lanes, UnitQ u, float thr, int lm1, int qmin, uint2* dst) {
     for (int v = sub; v < nvec; v += lanes) {
-        const uint2 idx = quant8_fix_idx<InT>(__ldg(src + v), u, thr, lm1, true);
+        const uint2 idx = quant8_fix_idx<InT>(src.vec(v), u, thr, lm1, true);
         dst[v] = make_uint2(idx_to_codes4(idx.x, qmin), idx_to_codes4(idx.y, qmin));
     }
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // The fields of a job K_convv needs, read once per tensor a warp works on
@@ -1055,7 +1081,8 @@ struct ConvJob {
     const RowQuantArgs* args;      // the side outputs and supplied parameters are read where they are used
     const void* in;
     uint8_t* codes;
-    int rows, rows_pad, row_vecs;  // row_vecs: 16-byte vectors per input row
+    int rows, rows_pad, cols, row_vecs;  // row_vecs: 16-byte vectors per input row, the last one possibly ragged
+    int vec_ok;                    // rows are whole, 16-byte aligned vectors
     int khw, ic, ic_pad;           // khw == 0: the codes are the output row as they are
     int out_bytes;                 // bytes of an output row
     int lpr;
@@ -1069,7 +1096,9 @@ __device__ __forceinline__ void load_conv_job(const RowQuantArgs* __restrict__ j
     J.codes = static_cast<uint8_t*>(A.codes);
     J.rows = int(A.rows);
     J.rows_pad = int(A.rows_pad);
-    J.row_vecs = int(A.cols >> 3);
+    J.cols = int(A.cols);
+    J.row_vecs = int((A.cols + 7) >> 3);
+    J.vec_ok = (A.cols & 7) == 0 && (reinterpret_cast<uintptr_t>(A.in) & 15) == 0;
     J.khw = int(A.khw);
     J.ic = A.khw > 0 ? int(A.ic) : int(A.cols);
     J.ic_pad = A.khw > 0 ? int(A.ic_pad) : int(A.cols);
@@ -1079,6 +1108,16 @@ __device__ __forceinline__ void load_conv_job(const RowQuantArgs* __restrict__ j
     J.unit_end = j + 1 < p.njobs ? jobs[j + 1].unit_begin : p.total_units;
     J.work_begin = A.work_begin;
     J.unit_cost = A.unit_cost;
+}
+
+__device__ __forceinline__ void convv_prefetch_unit(const ConvJob& J, int64_t u, int lane) {
+    const int rows_per_unit = 32 / J.lpr;
+    const int64_t r0 = u * rows_per_unit;
+    const int rows_there = min(rows_per_unit, J.rows - int(r0));
+    if (rows_there <= 0) return;
+    const char* base = static_cast<const char*>(J.in) + r0 * int64_t(J.cols) * 2;
+    const int64_t bytes = int64_t(rows_there) * J.cols * 2;
+    for (int64_t o = int64_t(lane) * 128; o < bytes; o += 32 * 128) prefetch_l2(base + o);
 }
 
 // One unit of K_convv: 32 / LPR consecutive output channels of one tensor, LPR lanes each. Every group runs the
@@ -1103,7 +1142,7 @@ __device__ __forceinline__ void convv_unit(const ConvJob& J, int64_t unit_in_job
     const int row_vecs = J.row_vecs;
     const int nvec = live ? row_vecs : 0;
     const int nb = (row_vecs + kB * LPR - 1) / (kB * LPR);
-    const uint4* src = static_cast<const uint4*>(J.in) + int64_t(live ? r : 0) * row_vecs;
+    const ConvRow src{static_cast<const uint16_t*>(J.in) + int64_t(live ? r : 0) * J.cols, J.cols, J.vec_ok != 0};
     // first pass: the range. The vectors of the last batch stay in registers for the second pass (rows of up to
     // 32 LPR elements are read once); earlier batches are read again, from the caches.
     uint4 d[kB];
@@ -1113,7 +1152,7 @@ __device__ __forceinline__ void convv_unit(const ConvJob& J, int64_t unit_in_job
         for (int k = 0; k < kB; ++k) {
             const int v = (b * kB + k) * LPR + sub;
             d[k] = make_uint4(0u, 0u, 0u, 0u);  // zeros do not move a range that contains zero
-            if ((b * kB + k) * LPR < row_vecs && v < nvec) d[k] = __ldg(src + v);
+            if ((b * kB + k) * LPR < row_vecs && v < nvec) d[k] = src.vec(v);
         }
 #pragma unroll
         for (int k = 0; k < kB; ++k) mm.add(d[k]);
@@ -1150,14 +1189,14 @@ __device__ __forceinline__ void convv_unit(const ConvJob& J, int64_t unit_in_job
 
     // second pass, last batch first. The codes of a 1x1 kernel are the output row as they are; otherwise they
     // are collected in the group's part of the stage for the transposed copy-out.
-    const bool direct = J.khw <= 0 && (reinterpret_cast<uintptr_t>(J.codes) & 7) == 0;
+    const bool direct = J.khw <= 0 && J.vec_ok && (reinterpret_cast<uintptr_t>(J.codes) & 7) == 0;
     uint4* my_stage = stage + grp * (stage_vecs >> (5 - lpr_shift));
     uint2* dst2 = reinterpret_cast<uint2*>(direct ? static_cast<void*>(out) : static_cast<void*>(my_stage));
     const ExactQ eq = exact_consts(u, p.lm1, float(p.qmin));  // K = qmin: the low byte is the code
     for (int b = nb - 1; b >= 0; --b) {
         if (b != nb - 1) {
 #pragma unroll
-            for (int k = 0; k < kB; ++k) d[k] = __ldg(src + (b * kB + k) * LPR + sub);  // every batch but the last is full
+            for (int k = 0; k < kB; ++k) d[k] = src.vec((b * kB + k) * LPR + sub);  // every batch but the last is full
         }
 #pragma unroll
         for (int k = 0; k < kB; ++k) {
@@ -1197,12 +1236,8 @@ inline int convv_unit_cost(int64_t cols, int64_t khw, int lanes_per_row) {
 // The units of all tensors form one list, each with a cost; a warp takes the units whose cumulative cost starts
 // inside its share [W0, W1) of the total. Its units are consecutive, so it meets a new tensor rarely: the job
 // table is searched once per warp, and a tensor's fields are read once per tensor and warp.
-#ifndef VF_GVAR
-#define VF_GVAR 0
-#endif
-#define VF_CONVV_OCC (4 - VF_GVAR)
 template <typename InT>
-__global__ void __launch_bounds__(256, VF_CONVV_OCC) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs, int* flags) {
+__global__ void __launch_bounds__(256, 4) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs, int* flags) {
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint4* stage = smem_u4 + size_t(wid) * size_t(stage_vecs);  // codes, one byte per element in input order
@@ -1225,6 +1260,7 @@ __global__ void __launch_bounds__(256, VF_CONVV_OCC) k_convv(const RowQuantArgs*
     ConvJob J;
     load_conv_job(jobs, j, p, J);
     int64_t unit = J.unit_begin + (W0 - J.work_begin + J.unit_cost - 1) / J.unit_cost;
+    bool first = true;
     for (;;) {
         while (unit >= J.unit_end) {
             if (++j >= p.njobs) return;
@@ -1232,6 +1268,11 @@ __global__ void __launch_bounds__(256, VF_CONVV_OCC) k_convv(const RowQuantArgs*
         }
         const int64_t u = unit - J.unit_begin;
         if (J.work_begin + u * J.unit_cost >= W1) return;
+        // the rows of this warp's next unit are on their way into the L2 while this one is worked on (the first
+        // unit's own rows, past the first batch, as well)
+        if (first) convv_prefetch_unit(J, u, lane);
+        first = false;
+        if (unit + 1 < J.unit_end) convv_prefetch_unit(J, u + 1, lane);
         convv_unit<InT>(J, u, p, stage, stage_vecs, lane, flags);
         ++unit;
     }
@@ -1327,9 +1368,11 @@ int rowquant_kind(const RowQuantArgs& a) {
     bool convv_ok = false, conv_ok = false;
     if (!a.pack4 && !a.dequant && !a.zps_u4 && a.codes) {
         const int64_t out_row = a.khw > 0 ? a.khw * a.ic_pad : a.cols;
-        const int64_t ic = a.khw > 0 ? a.ic : a.cols, ic_pad = a.khw > 0 ? a.ic_pad : a.cols;
-        convv_ok = two_byte && aligned16 && a.cols % 8 == 0 && a.cols <= 4608 && out_row <= 4608 && ic % 4 == 0 && ic_pad % 4 == 0 &&
-                   reinterpret_cast<uintptr_t>(a.codes) % 4 == 0;
+        const int64_t ic_pad = a.khw > 0 ? a.ic_pad : a.cols;
+        // rows that are not whole aligned vectors are taken when they are copied out transposed (the stem)
+        const bool vec_rows = aligned16 && a.cols % 8 == 0;
+        convv_ok = two_byte && (vec_rows || a.khw > 0) && a.cols <= 4608 && out_row <= 4608 && ic_pad % 4 == 0 &&
+                   reinterpret_cast<uintptr_t>(a.codes) % 4 == 0 && reinterpret_cast<uintptr_t>(a.in) % 2 == 0;
         conv_ok = out_row <= 24 * 1024;
     }
     // a convolution weight (it came with an OIYX -> OYXI reorder: ic is set) stays with the other convolutions of its
@@ -1395,7 +1438,7 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
                 stage_vecs64 = std::max(stage_vecs64, ((a.cols + 15) / 16) * (32 / a.lanes_per_row));
         const int stage_vecs = int(stage_vecs64);
         const size_t smem = size_t(8) * size_t(stage_vecs) * 16;
-        const size_t per_sm = std::max<size_t>(1, std::min<size_t>(VF_CONVV_OCC, (220 * 1024) / (smem + 1024)));
+        const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024)));
         const int64_t blocks = (units + 7) / 8;
         const int grid = int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * int64_t(per_sm)));
         if (a0.in_dt == VF_DT_F16) {
