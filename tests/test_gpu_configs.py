@@ -263,19 +263,35 @@ def _mix64(z):
     return z ^ (z >> np.uint64(33))
 
 
+def _mulhi64(x, y):
+    """High half of the 128-bit product of two uint64 arrays."""
+    m = np.uint64(0xFFFFFFFF)
+    s32 = np.uint64(32)
+    xl, xh, yl, yh = x & m, x >> s32, y & m, y >> s32
+    ll, lh, hl, hh = xl * yl, xl * yh, xh * yl, xh * yh
+    mid = (ll >> s32) + (lh & m) + (hl & m)
+    return hh + (lh >> s32) + (hl >> s32) + (mid >> s32)
+
+
 def hash128_host(buf):
-    """vf_content_hash restated with numpy (sums of mixed (word, index) pairs over the 8-byte words, length mixed in
-    last), for hashing the oracle's outputs."""
+    """vf_content_hash restated with numpy: the buffer as 16-byte vectors (a, b) of two 8-byte words (missing bytes
+    zero), vector i keyed with (i + 1) * K; two differently keyed 64 x 64 -> 128 bit products per vector, each folded
+    (low ^ high) and summed; the length mixed in last. For hashing the oracle's outputs."""
     b = np.ascontiguousarray(buf).view(np.uint8).reshape(-1)
     n = b.size
-    if n % 8:
-        b = np.concatenate([b, np.zeros(8 - n % 8, np.uint8)])
-    v = b.view(np.uint64)
+    if n % 16:
+        b = np.concatenate([b, np.zeros(16 - n % 16, np.uint8)])
+    v = b.view(np.uint64).reshape(-1, 2)
+    a_, b_ = v[:, 0], v[:, 1]
     K, K2, K3 = np.uint64(0x9E3779B97F4A7C15), np.uint64(0xD6E8FEB86659FD93), np.uint64(0xA0761D6478BD642F)
+    s32 = np.uint64(32)
     with np.errstate(over="ignore"):
-        kw = np.arange(1, v.size + 1, dtype=np.uint64) * K
-        h1 = _mix64(v ^ kw).sum(dtype=np.uint64)
-        h2 = (_mix64((v ^ kw ^ K2) + K3) * K3).sum(dtype=np.uint64)
+        k = np.arange(1, a_.size + 1, dtype=np.uint64) * K
+        ks = (k << s32) | (k >> s32)
+        x, y = a_ ^ k, b_ ^ ks ^ K2
+        h1 = ((x * y) ^ _mulhi64(x, y)).sum(dtype=np.uint64)
+        x2, y2 = (a_ ^ K3) + ks, (b_ ^ K2) + k
+        h2 = ((x2 * y2) ^ _mulhi64(x2, y2)).sum(dtype=np.uint64)
         return int(_mix64(h1 ^ np.uint64(n))), int(_mix64(h2 + np.uint64(n)))
 
 

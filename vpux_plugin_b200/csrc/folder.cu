@@ -32,49 +32,62 @@ __host__ __device__ inline uint64_t mix64(uint64_t z) {
     return z;
 }
 
-// Sum over the 8-byte words w of mix(word ^ f(index)): addition commutes, so the result does not depend on how
-// the words are spread over threads. A 16-byte aligned buffer is read two words per load; any other buffer, and
-// the last partial word, are assembled from 8-byte or single-byte loads (missing bytes read as zero).
+// The buffer is read as 16-byte vectors (a, b) of two 8-byte words, missing bytes as zero. Vector i has the key
+// k = (i + 1) * K; two 64 x 64 -> 128 bit products of differently keyed copies of (a, b) are folded (low ^ high
+// half) and summed into the two halves of the hash. Addition commutes, so the result does not depend on how the
+// vectors are spread over threads; the keys make it depend on where a vector stands. A 16-byte aligned buffer is
+// read one vector per load; any other buffer, and the last partial vector, are assembled from 8-byte or single-byte
+// loads.
 __device__ __forceinline__ uint64_t word_from_bytes(const uint8_t* __restrict__ p, uint64_t nbytes, uint64_t w) {
     uint64_t v = 0;
     for (int b = 0; b < 8; ++b)
         if (w * 8 + b < nbytes) v |= uint64_t(p[w * 8 + b]) << (8 * b);
     return v;
 }
+__host__ __device__ inline uint64_t swap_halves(uint64_t v) {
+    return (v << 32) | (v >> 32);
+}
 
-__global__ void __launch_bounds__(256) k_hash128(const uint8_t* __restrict__ p, uint64_t nbytes, unsigned long long* __restrict__ acc) {
-    const uint64_t words = (nbytes + 7) / 8;
+constexpr int kHashLoads = 8;
+__global__ void __launch_bounds__(256, 4) k_hash128(const uint8_t* __restrict__ p, uint64_t nbytes, unsigned long long* __restrict__ acc) {
+    const uint64_t words = (nbytes + 7) / 8, vecs = (words + 1) / 2;
     const uint64_t tid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
     uint64_t h1 = 0, h2 = 0;
-    constexpr uint64_t K = 0x9E3779B97F4A7C15ull, K2 = 0xD6E8FEB86659FD93ull;
-    // word w enters the first sum as mix(word ^ (w + 1) * K) and the second one through a mix of its own (a
-    // different key, another multiplier), so the two halves are independent functions of the (word, index) pairs
-    constexpr uint64_t K3 = 0xA0761D6478BD642Full;
-    auto add = [&](uint64_t kw, uint64_t v) {
-        h1 += mix64(v ^ kw);
-        h2 += mix64((v ^ kw ^ K2) + K3) * K3;
+    constexpr uint64_t K = 0x9E3779B97F4A7C15ull, K2 = 0xD6E8FEB86659FD93ull, K3 = 0xA0761D6478BD642Full;
+    auto add = [&](uint64_t k, uint64_t a, uint64_t b) {
+        const uint64_t ks = swap_halves(k);
+        const uint64_t x = a ^ k, y = b ^ ks ^ K2;
+        h1 += (x * y) ^ __umul64hi(x, y);
+        const uint64_t x2 = (a ^ K3) + ks, y2 = (b ^ K2) + k;
+        h2 += (x2 * y2) ^ __umul64hi(x2, y2);
     };
     const unsigned mis = unsigned(reinterpret_cast<uintptr_t>(p) & 15u);
-    if (mis == 0) {
-        const uint64_t nvec = nbytes / 16;
+    const uint64_t whole = mis == 0 ? nbytes / 16 : 0;  // vectors read with one 16-byte load
+    {
         const uint4* __restrict__ q = reinterpret_cast<const uint4*>(p);
-        uint64_t kw = (2 * tid + 1) * K;  // (w + 1) * K for w = 2 * v, advanced by additions
-        const uint64_t kstep = 2 * stride * K;
-        for (uint64_t v = tid; v < nvec; v += stride, kw += kstep) {
-            const uint4 x = __ldg(q + v);
-            add(kw, uint64_t(x.x) | (uint64_t(x.y) << 32));
-            add(kw + K, uint64_t(x.z) | (uint64_t(x.w) << 32));
+        uint64_t k = (tid + 1) * K;  // advanced by additions
+        const uint64_t kstep = stride * K;
+        uint64_t v = tid;
+        for (; v + (kHashLoads - 1) * stride < whole; v += kHashLoads * stride) {  // eight loads in flight per thread
+            uint4 x[kHashLoads];
+#pragma unroll
+            for (int u = 0; u < kHashLoads; ++u) x[u] = __ldg(q + v + u * stride);
+#pragma unroll
+            for (int u = 0; u < kHashLoads; ++u, k += kstep)
+                add(k, uint64_t(x[u].x) | (uint64_t(x[u].y) << 32), uint64_t(x[u].z) | (uint64_t(x[u].w) << 32));
         }
-        if (tid == 0)
-            for (uint64_t w = 2 * nvec; w < words; ++w) add((w + 1) * K, word_from_bytes(p, nbytes, w));
-    } else {
-        const bool aligned8 = (mis & 7u) == 0;
-        for (uint64_t w = tid; w < words; w += stride) {
-            const bool whole = (w + 1) * 8 <= nbytes;
-            add((w + 1) * K, aligned8 && whole ? reinterpret_cast<const uint64_t*>(p)[w] : word_from_bytes(p, nbytes, w));
+        for (; v < whole; v += stride, k += kstep) {
+            const uint4 x = __ldg(q + v);
+            add(k, uint64_t(x.x) | (uint64_t(x.y) << 32), uint64_t(x.z) | (uint64_t(x.w) << 32));
         }
     }
+    const bool aligned8 = (mis & 7u) == 0;
+    auto word = [&](uint64_t w) -> uint64_t {
+        if (w >= words) return 0;
+        return aligned8 && (w + 1) * 8 <= nbytes ? reinterpret_cast<const uint64_t*>(p)[w] : word_from_bytes(p, nbytes, w);
+    };
+    for (uint64_t v = whole + tid; v < vecs; v += stride) add((v + 1) * K, word(2 * v), word(2 * v + 1));  // ragged end, or all of a misaligned buffer
     for (int o = 16; o > 0; o >>= 1) {
         h1 += __shfl_down_sync(0xFFFFFFFFu, h1, o);
         h2 += __shfl_down_sync(0xFFFFFFFFu, h2, o);
@@ -97,7 +110,7 @@ void hash_device(vf_ctx* ctx, const void* d, uint64_t nbytes, uint64_t out[2]) {
     VF_CUDA(cudaMemsetAsync(acc.p, 0, 16, ctx->stream));
     const uint64_t words = (nbytes + 7) / 8;
     if (words) {
-        const uint64_t blocks = std::min<uint64_t>((words / 2 + 255) / 256 + 1, uint64_t(ctx->sm_count) * 8);
+        const uint64_t blocks = std::min<uint64_t>((words / 2 + 255) / 256 + 1, uint64_t(ctx->sm_count) * 4);  // four resident CTAs per SM
         k_hash128<<<int(blocks), 256, 0, ctx->stream>>>(static_cast<const uint8_t*>(d), nbytes, acc.as<unsigned long long>());
         VF_CUDA(cudaGetLastError());
         ++ctx->launches;

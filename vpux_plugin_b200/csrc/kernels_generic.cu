@@ -623,25 +623,38 @@ __device__ __forceinline__ uint2 expand8(uint32_t w, int sign) {  // eight eleme
     return make_uint2(r[0], r[1]);
 }
 
-// 32 elements per thread step: 4 * BITS input bytes in one load, two 16-byte stores (both buffers aligned)
+// 16 elements per item: 2 * BITS input bytes in one load, one 16-byte store, so every load and every store of a warp
+// is one contiguous run; four items per thread step, their loads issued together (both buffers aligned)
 template <int BITS>
-__global__ void k_unpack_subbyte_x32(const uint8_t* __restrict__ in, uint4* __restrict__ out, int64_t n_steps, int sign) {
+__global__ void k_unpack_subbyte_x16(const uint8_t* __restrict__ in, uint4* __restrict__ out, int64_t n_items, int sign) {
+    constexpr int kU = 4;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t < n_steps; t += stride) {
-        uint32_t w[4];
-        if (BITS == 4) {
-            const uint4 x = __ldg(reinterpret_cast<const uint4*>(in) + t);
-            w[0] = x.x, w[1] = x.y, w[2] = x.z, w[3] = x.w;
-        } else if (BITS == 2) {
-            const uint2 x = __ldg(reinterpret_cast<const uint2*>(in) + t);
-            w[0] = x.x & 0xFFFFu, w[1] = x.x >> 16, w[2] = x.y & 0xFFFFu, w[3] = x.y >> 16;
-        } else {
-            const uint32_t x = __ldg(reinterpret_cast<const uint32_t*>(in) + t);
-            w[0] = x & 0xFFu, w[1] = (x >> 8) & 0xFFu, w[2] = (x >> 16) & 0xFFu, w[3] = x >> 24;
+    for (int64_t t0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t0 < n_items; t0 += kU * stride) {
+        uint32_t w[kU][2];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int64_t t = t0 + u * stride;
+            w[u][0] = w[u][1] = 0u;
+            if (t < n_items) {
+                if (BITS == 4) {
+                    const uint2 x = __ldg(reinterpret_cast<const uint2*>(in) + t);
+                    w[u][0] = x.x, w[u][1] = x.y;
+                } else if (BITS == 2) {
+                    const uint32_t x = __ldg(reinterpret_cast<const uint32_t*>(in) + t);
+                    w[u][0] = x & 0xFFFFu, w[u][1] = x >> 16;
+                } else {
+                    const uint32_t x = __ldg(reinterpret_cast<const uint16_t*>(in) + t);
+                    w[u][0] = x & 0xFFu, w[u][1] = x >> 8;
+                }
+            }
         }
-        const uint2 a = expand8<BITS>(w[0], sign), b = expand8<BITS>(w[1], sign), c = expand8<BITS>(w[2], sign), d = expand8<BITS>(w[3], sign);
-        out[2 * t] = make_uint4(a.x, a.y, b.x, b.y);
-        out[2 * t + 1] = make_uint4(c.x, c.y, d.x, d.y);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int64_t t = t0 + u * stride;
+            if (t >= n_items) break;
+            const uint2 a = expand8<BITS>(w[u][0], sign), b = expand8<BITS>(w[u][1], sign);
+            out[t] = make_uint4(a.x, a.y, b.x, b.y);
+        }
     }
 }
 
@@ -843,6 +856,88 @@ __device__ __forceinline__ void cp_async16_part(void* smem_dst, const void* gsrc
     const uint32_t sdst = uint32_t(__cvta_generic_to_shared(smem_dst));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sdst), "l"(gsrc), "r"(src_bytes) : "memory");  // the rest is zero-filled
 }
+// The general transposition for 1-, 2- and 4-byte elements whose output rows are whole 16-byte vectors: a tile is 64
+// rows of the source (dim a, the innermost output dim) by 256 bytes along dim b (source stride 1). Source rows
+// start at any element, so every row segment is fetched as the aligned 16-byte vectors that cover it and kept in
+// shared memory with its lead (the bytes in front of the segment); the words of a row are stored at a pitch of 69
+// words, which spreads the eight rows a lane gathers from over the banks. Output: 16-byte vectors of consecutive
+// a, the lanes of a warp covering whole output rows next to each other.
+constexpr int kRowsTile = 64, kRowBytes = 256, kRowPitchWords = kRowBytes / 4 + 5;
+template <int ES, typename I>
+__global__ void __launch_bounds__(256) k_transpose_rows(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, int b, I tiles_a,
+                                                        I tiles_b, int64_t dst_stride_b, int64_t total_bytes) {
+    constexpr uint32_t VE = 16 / ES, TB = kRowBytes / ES, kVecs = kRowBytes / 16 + 1;
+    __shared__ uint32_t tile[kRowsTile * kRowPitchWords];
+    using T = typename ElemOf<ES>::T;
+    const int a = g.rank - 1;
+    I rem = I(blockIdx.x);
+    const I tb_i = rem % tiles_b;
+    rem /= tiles_b;
+    const I ta_i = rem % tiles_a;
+    rem /= tiles_a;
+    int64_t src0 = 0, dst0 = 0, dst_mul = 1;
+#pragma unroll
+    for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+        if (d < g.rank) {
+            const I os = I(g.out_shape[d]);
+            if (d != a && d != b) {
+                const I q = rem / os;
+                const I c = rem - q * os;
+                rem = q;
+                src0 += int64_t(c) * g.src_stride[d];
+                dst0 += int64_t(c) * dst_mul;
+            }
+            dst_mul *= os;
+        }
+    }
+    const uint32_t ea = uint32_t(g.out_shape[a]), eb = uint32_t(g.out_shape[b]);
+    const uint32_t a0 = uint32_t(ta_i) * kRowsTile, b0 = uint32_t(tb_i) * TB;
+    const uint32_t ta = min(uint32_t(kRowsTile), ea - a0), tb = min(TB, eb - b0);
+    const int64_t sa = g.src_stride[a];
+    const int64_t first = (src0 + int64_t(a0) * sa + b0) * ES;  // byte offset of the tile's first segment
+    const uint32_t seg_bytes = tb * ES;
+    for (uint32_t idx = threadIdx.x; idx < ta * kVecs; idx += blockDim.x) {
+        const uint32_t r = idx / kVecs, c = idx - r * kVecs;
+        const int64_t gb = first + int64_t(r) * sa * ES;
+        const uint32_t lead = uint32_t(gb & 15);
+        if (c * 16 < lead + seg_bytes) {
+            const int64_t p = (gb & ~int64_t(15)) + int64_t(c) * 16;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (p + 16 <= total_bytes) {
+                v = __ldg(reinterpret_cast<const uint4*>(in + p));
+            } else {  // the last vector of the buffer may be cut short
+                uint8_t* vb = reinterpret_cast<uint8_t*>(&v);
+                for (int k = 0; k < 16; ++k)
+                    if (p + k < total_bytes) vb[k] = in[p + k];
+            }
+            uint32_t* w = tile + r * kRowPitchWords + c * 4;
+            w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+        }
+    }
+    __syncthreads();
+    const uint32_t nab = ta / VE, n_out = nab * tb;
+    const uint32_t step_b = blockDim.x / nab, step_a = blockDim.x - step_b * nab;
+    uint32_t ib = threadIdx.x / nab, iab = threadIdx.x - ib * nab;
+    const uint32_t lead0 = uint32_t(first & 15), lead_step = uint32_t((sa * ES) & 15);
+    const uint8_t* tb8 = reinterpret_cast<const uint8_t*>(tile);
+    for (uint32_t v = threadIdx.x; v < n_out; v += blockDim.x) {
+        __align__(16) T e[VE];
+#pragma unroll
+        for (uint32_t k = 0; k < VE; ++k) {
+            const uint32_t r = iab * VE + k;
+            const uint32_t lead = (lead0 + r * lead_step) & 15u;
+            e[k] = *reinterpret_cast<const T*>(tb8 + r * (kRowPitchWords * 4) + lead + ib * ES);
+        }
+        *reinterpret_cast<uint4*>(out + (dst0 + int64_t(b0 + ib) * dst_stride_b + a0 + iab * VE) * ES) = *reinterpret_cast<const uint4*>(e);
+        iab += step_a;
+        ib += step_b;
+        if (iab >= nab) {
+            iab -= nab;
+            ++ib;
+        }
+    }
+}
+
 constexpr int kSliceStages = 3;  // chunks in flight per CTA: the one being written and the copies of the next two
 template <int ES, typename I>
 __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, I chunks_a,
@@ -976,31 +1071,47 @@ __device__ __forceinline__ typename ElemOf<ES>::T wide_fill(const uint8_t* __res
 }
 
 // PadWithZero — attributes/pad_with_zero.cpp:111-268 + Content::fillWithZero utils/content.cpp:190-237
+// Four output elements per thread step, their loads issued together (an SM needs on the order of 100 KB in flight
+// to keep the memory busy: one 16-byte load per thread is a third of that).
 template <int ES, typename I>
 __global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restrict__ out, Geom g, I n,
                       const uint8_t* __restrict__ fill, int fill_es, I n_fill, int fill_dim) {
     using T = typename ElemOf<ES>::T;
+    constexpr int kU = 4;
     const I stride = I(gridDim.x) * I(blockDim.x);
-    for (I o = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); o < n; o += stride) {
-        I rem = o, src = 0, fc = 0;
-        bool inside = true;
+    for (I o0 = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); o0 < n; o0 += I(kU) * stride) {
+        T v[kU];
+        I fcs[kU];
+        bool ins[kU];
 #pragma unroll
-        for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
-            if (d < g.rank) {
-                const I os = I(g.out_shape[d]);
-                const I q = rem / os;
-                const I c = rem - q * os;
-                rem = q;
-                if (d == fill_dim) fc = c;
-                const I ci = c - I(g.offset[d]);  // wraps below zero for I = uint32_t: caught by the range test
-                inside &= c >= I(g.offset[d]) && ci < I(g.in_shape[d]);
-                src += ci * I(g.src_stride[d]);
+        for (int u = 0; u < kU; ++u) {
+            const I o = o0 + I(u) * stride;
+            I rem = o, src = 0, fc = 0;
+            bool inside = o < n;
+#pragma unroll
+            for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
+                if (d < g.rank) {
+                    const I os = I(g.out_shape[d]);
+                    const I q = rem / os;
+                    const I c = rem - q * os;
+                    rem = q;
+                    if (d == fill_dim) fc = c;
+                    const I ci = c - I(g.offset[d]);  // wraps below zero for I = uint32_t: caught by the range test
+                    inside &= c >= I(g.offset[d]) && ci < I(g.in_shape[d]);
+                    src += ci * I(g.src_stride[d]);
+                }
             }
+            ins[u] = inside;
+            fcs[u] = fc;
+            if (inside) v[u] = static_cast<const T*>(in)[in_splat ? I(0) : src];
         }
-        T v;
-        if (inside) v = static_cast<const T*>(in)[in_splat ? I(0) : src];
-        else v = wide_fill<ES>(fill + (n_fill > 1 ? fc : I(0)) * I(fill_es), fill_es);
-        static_cast<T*>(out)[o] = v;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const I o = o0 + I(u) * stride;
+            if (o >= n) break;
+            if (!ins[u]) v[u] = wide_fill<ES>(fill + (n_fill > 1 ? fcs[u] : I(0)) * I(fill_es), fill_es);
+            static_cast<T*>(out)[o] = v[u];
+        }
     }
 }
 
@@ -1919,6 +2030,31 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
             return;
         }
     }
+    if (es <= 4 && b >= 0 && g.src_stride[a] != 1 && (g.out_shape[a] * es) % 16 == 0 && aligned16(in, out)) {
+        // output rows of whole 16-byte vectors: 64-row tiles, gathered and written as vectors
+        const int64_t ta = (g.out_shape[a] + kRowsTile - 1) / kRowsTile, tb = (g.out_shape[b] * es + kRowBytes - 1) / kRowBytes;
+        int64_t others = 1, dst_stride_b = 1, src_elems = 1;
+        for (int d = 0; d < g.rank; ++d) {
+            if (d != a && d != b) others *= g.out_shape[d];
+            src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
+        }
+        for (int d = b + 1; d < g.rank; ++d) dst_stride_b *= g.out_shape[d];
+        const int64_t blocks = others * ta * tb;
+        if (blocks < (int64_t(1) << 31) && (dst_stride_b * es) % 16 == 0) {
+            const int64_t total_bytes = src_elems * es;
+            if (small) {
+                using I = uint32_t;
+                VF_BY_ELEM_SIZE(es, (k_transpose_rows<(ES > 4 ? 4 : ES), I><<<unsigned(blocks), kBlock, 0, ctx->stream>>>(
+                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, b, I(ta), I(tb), dst_stride_b, total_bytes)));
+            } else {
+                using I = int64_t;
+                VF_BY_ELEM_SIZE(es, (k_transpose_rows<(ES > 4 ? 4 : ES), I><<<unsigned(blocks), kBlock, 0, ctx->stream>>>(
+                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, b, I(ta), I(tb), dst_stride_b, total_bytes)));
+            }
+            post_launch(ctx);
+            return;
+        }
+    }
     if (es <= 8 && b >= 0 && g.src_stride[a] != 1 && g.out_shape[a] >= 8) {
         const int64_t ta = (g.out_shape[a] + kTile - 1) / kTile, tb = (g.out_shape[b] + kTile - 1) / kTile;
         int64_t others = 1, dst_stride_b = 1;
@@ -1958,7 +2094,7 @@ void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geo
     if (!in_splat) merge_dims(g, 2, keep);
     const int es = widen(g, 2, es0, in, out, in_splat, keep);
     const int64_t n = out_numel(g);
-    const int grid = grid_for(n);
+    const int grid = grid_for(n, 4);
     const uint8_t* fill = static_cast<const uint8_t*>(d_fill);
     const int fd = n_fill > 1 ? keep : 0;
     if (max_index(g, 2) < (int64_t(1) << 31)) {
@@ -2076,11 +2212,11 @@ void launch_swizzle(vf_ctx* ctx, const void* in, uint64_t in_bytes, uint8_t pad,
 template <int BITS>
 void launch_unpack_bits(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t n_out, int s) {
     int64_t done = 0;
-    if (n_out >= 32 && (reinterpret_cast<uintptr_t>(in) % (4 * BITS)) == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0) {
-        const int64_t steps = n_out / 32;
-        k_unpack_subbyte_x32<BITS><<<grid_for(steps), kBlock, 0, ctx->stream>>>(in, reinterpret_cast<uint4*>(out), steps, s);
+    if (n_out >= 16 && (reinterpret_cast<uintptr_t>(in) % (2 * BITS)) == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0) {
+        const int64_t items = n_out / 16;
+        k_unpack_subbyte_x16<BITS><<<grid_for(items, 4), kBlock, 0, ctx->stream>>>(in, reinterpret_cast<uint4*>(out), items, s);
         post_launch(ctx);
-        done = steps * 32;
+        done = items * 16;
     }
     if (done < n_out) {
         k_unpack_subbyte<BITS><<<grid_for((n_out - done + 7) / 8), kBlock, 0, ctx->stream>>>(in + done * BITS / 8, out + done, n_out - done, s);
