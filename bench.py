@@ -964,7 +964,8 @@ def next_arm(args):
         ("Dequantize per-axis i8->f32", "dequantize.cpp:42-108", TT([oc, n8 // oc // 4], I8), I8,
          lambda s: s.castElemType(abi.Elem.per_axis(I8, F32, [0.01 + 1e-5 * i for i in range(oc)], [0] * oc, 0, -127, 127)).dequantize()),
         ("Rescale f32", "rescale.cpp:67-82", TT([n8 // 4], F32), F32, lambda s: s.rescale(0.5)),
-        ("Reorder OIYX->OYXI f16", "reorder.cpp:79-99", TT([oc, 64, 3, n8 // 2 // oc // 64 // 3], F16), F16, lambda s: s.reorder(abi.ORDER_NHWC)),
+        ("Reorder OIYX->OYXI f16, 64 x 3 x 3 kernels", "reorder.cpp:79-99", TT([n8 // 2 // 64 // 9, 64, 3, 3], F16), F16, lambda s: s.reorder(abi.ORDER_NHWC)),
+        ("Reorder OIYX->OYXI f16, rows of 4095", "reorder.cpp:79-99", TT([oc, 64, 3, n8 // 2 // oc // 64 // 3], F16), F16, lambda s: s.reorder(abi.ORDER_NHWC)),
         ("PadWithZero IC 48->64 f16", "pad_with_zero.cpp:111-268", TT([oc, 48, 3, n8 // 2 // oc // 48 // 3], F16), F16,
          lambda s: s.padWithZero([0, 0, 0, 0], [0, 16, 0, 0])),
         ("SubView half the channels f16", "subview.cpp:390-432", TT([oc, n8 // 2 // oc], F16), F16,

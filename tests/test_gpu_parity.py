@@ -135,6 +135,24 @@ def test_reorder(gpu, oracle, dt, es, shape, order_in, order_out):
     both(ContentAttr(x, t, ContentSetup(t).reorder(order_out)), gpu, oracle)
 
 
+@pytest.mark.parametrize("dt,es", [(U8, 1), (F16, 2), (F32, 4)])
+@pytest.mark.parametrize("shape", [
+    [5, 64, 3, 3], [3, 32, 5, 5], [2, 200, 7, 7], [2, 2048, 3, 3], [3, 16, 1, 2],      # whole slices through shared memory
+    [3, 64, 3, 171], [2, 80, 1, 1000], [2, 24, 3, 200], [1, 16, 37, 19], [2, 208, 9, 33],  # slices too large for it: 64 x 64 tiles
+    [4, 48, 4, 4], [2, 16, 8, 16]])                                                      # row strides that are multiples of 128 bytes
+def test_reorder_oiyx_to_oyxi_transposes(gpu, oracle, dt, es, shape):
+    """OIYX -> OYXI through both transposes (slices staged whole in shared memory, and tiles): channel counts of one
+    and several chunks with ragged ends, kernel sizes whose rows start at every alignment, slices of a few hundred
+    bytes up to more than the shared memory holds, and the same shapes with two leading dims."""
+    rng = np.random.default_rng(shape[1] + shape[3])
+    t = TType(shape, dt)
+    x = rng.integers(0, 255, int(np.prod(shape)) * es).astype(np.uint8).view(abi.DTYPE_NUMPY[dt])
+    both(ContentAttr(x, t, ContentSetup(t).reorder(abi.ORDER_NHWC)), gpu, oracle)
+    t5 = TType([2] + shape, dt)
+    x5 = np.concatenate([x, x[::-1]])
+    both(ContentAttr(x5, t5, ContentSetup(t5).reorder(0x12453)), gpu, oracle)
+
+
 def test_transpose_and_mem_permute(gpu, oracle):
     rng = np.random.default_rng(6)
     t = TType([2, 3, 4, 5], F16, abi.ORDER_NHWC)

@@ -846,148 +846,76 @@ __global__ void __launch_bounds__(256) k_permute_tiled(const void* __restrict__ 
 }
 
 // The transposition of the two innermost output dims when together they are ONE contiguous block of the source
-// (OIYX -> OYXI: per output channel the IC x KY*KX block becomes KY*KX x IC). A chunk is `rows_per_chunk` source
-// rows (contiguous): it is copied into shared memory with 16-byte asynchronous copies, starting at the 16-byte
-// boundary at or below the chunk, and written out as 16-byte vectors of consecutive a: eight lanes (f16, ea = 64)
-// cover one output row, a warp four rows, contiguous in memory. Each element costs one shared-memory read. The
-// CTAs are persistent with a ring of three buffers: the copies of a CTA's next two chunks are in flight while it
-// writes this one (it takes more than 100 KB in flight per SM to keep the memory busy).
+// (OIYX -> OYXI: per output channel the IC x KY*KX slice becomes KY*KX x IC). A chunk is a contiguous piece of the
+// source: several whole slices when they are small and follow each other in memory (a 64 x 3 x 3 f16 slice is
+// 1152 bytes), one slice, or `rows` rows of a slice that does not fit. It is copied into shared memory with 16-byte
+// asynchronous copies, starting at the 16-byte boundary at or below the chunk, and written out as 16-byte vectors
+// of consecutive a: eight lanes (f16, ea = 64) cover one output row, a warp four rows, contiguous in memory. Each
+// element costs one shared-memory read. The CTAs are persistent with a ring of three buffers: the copies of a
+// CTA's next two chunks are in flight while it writes this one (it takes more than 100 KB in flight per SM to keep
+// the memory busy).
 __device__ __forceinline__ void cp_async16_part(void* smem_dst, const void* gsrc, int src_bytes) {
     const uint32_t sdst = uint32_t(__cvta_generic_to_shared(smem_dst));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sdst), "l"(gsrc), "r"(src_bytes) : "memory");  // the rest is zero-filled
 }
-// The general transposition for 1-, 2- and 4-byte elements whose output rows are whole 16-byte vectors: a tile is 64
-// rows of the source (dim a, the innermost output dim) by 256 bytes along dim b (source stride 1). Source rows
-// start at any element, so every row segment is fetched as the aligned 16-byte vectors that cover it and kept in
-// shared memory with its lead (the bytes in front of the segment); the words of a row are stored at a pitch of 69
-// words, which spreads the eight rows a lane gathers from over the banks. Output: 16-byte vectors of consecutive
-// a, the lanes of a warp covering whole output rows next to each other.
-constexpr int kRowsTile = 64, kRowBytes = 256, kRowPitchWords = kRowBytes / 4 + 5;
-template <int ES, typename I>
-__global__ void __launch_bounds__(256) k_transpose_rows(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, int b, I tiles_a,
-                                                        I tiles_b, int64_t dst_stride_b, int64_t total_bytes) {
-    constexpr uint32_t VE = 16 / ES, TB = kRowBytes / ES, kVecs = kRowBytes / 16 + 1;
-    __shared__ uint32_t tile[kRowsTile * kRowPitchWords];
-    using T = typename ElemOf<ES>::T;
-    const int a = g.rank - 1;
-    I rem = I(blockIdx.x);
-    const I tb_i = rem % tiles_b;
-    rem /= tiles_b;
-    const I ta_i = rem % tiles_a;
-    rem /= tiles_a;
-    int64_t src0 = 0, dst0 = 0, dst_mul = 1;
-#pragma unroll
-    for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
-        if (d < g.rank) {
-            const I os = I(g.out_shape[d]);
-            if (d != a && d != b) {
-                const I q = rem / os;
-                const I c = rem - q * os;
-                rem = q;
-                src0 += int64_t(c) * g.src_stride[d];
-                dst0 += int64_t(c) * dst_mul;
-            }
-            dst_mul *= os;
-        }
-    }
-    const uint32_t ea = uint32_t(g.out_shape[a]), eb = uint32_t(g.out_shape[b]);
-    const uint32_t a0 = uint32_t(ta_i) * kRowsTile, b0 = uint32_t(tb_i) * TB;
-    const uint32_t ta = min(uint32_t(kRowsTile), ea - a0), tb = min(TB, eb - b0);
-    const int64_t sa = g.src_stride[a];
-    const int64_t first = (src0 + int64_t(a0) * sa + b0) * ES;  // byte offset of the tile's first segment
-    const uint32_t seg_bytes = tb * ES;
-    for (uint32_t idx = threadIdx.x; idx < ta * kVecs; idx += blockDim.x) {
-        const uint32_t r = idx / kVecs, c = idx - r * kVecs;
-        const int64_t gb = first + int64_t(r) * sa * ES;
-        const uint32_t lead = uint32_t(gb & 15);
-        if (c * 16 < lead + seg_bytes) {
-            const int64_t p = (gb & ~int64_t(15)) + int64_t(c) * 16;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (p + 16 <= total_bytes) {
-                v = __ldg(reinterpret_cast<const uint4*>(in + p));
-            } else {  // the last vector of the buffer may be cut short
-                uint8_t* vb = reinterpret_cast<uint8_t*>(&v);
-                for (int k = 0; k < 16; ++k)
-                    if (p + k < total_bytes) vb[k] = in[p + k];
-            }
-            uint32_t* w = tile + r * kRowPitchWords + c * 4;
-            w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
-        }
-    }
-    __syncthreads();
-    const uint32_t nab = ta / VE, n_out = nab * tb;
-    const uint32_t step_b = blockDim.x / nab, step_a = blockDim.x - step_b * nab;
-    uint32_t ib = threadIdx.x / nab, iab = threadIdx.x - ib * nab;
-    const uint32_t lead0 = uint32_t(first & 15), lead_step = uint32_t((sa * ES) & 15);
-    const uint8_t* tb8 = reinterpret_cast<const uint8_t*>(tile);
-    for (uint32_t v = threadIdx.x; v < n_out; v += blockDim.x) {
-        __align__(16) T e[VE];
-#pragma unroll
-        for (uint32_t k = 0; k < VE; ++k) {
-            const uint32_t r = iab * VE + k;
-            const uint32_t lead = (lead0 + r * lead_step) & 15u;
-            e[k] = *reinterpret_cast<const T*>(tb8 + r * (kRowPitchWords * 4) + lead + ib * ES);
-        }
-        *reinterpret_cast<uint4*>(out + (dst0 + int64_t(b0 + ib) * dst_stride_b + a0 + iab * VE) * ES) = *reinterpret_cast<const uint4*>(e);
-        iab += step_a;
-        ib += step_b;
-        if (iab >= nab) {
-            iab -= nab;
-            ++ib;
-        }
-    }
-}
-
+struct SliceGeom {
+    uint32_t ea, eb;          // rows (source) / columns of a slice; the output slice is eb x ea
+    uint32_t rows;            // rows per chunk (== ea unless the slice is cut)
+    uint32_t chunks_a;        // chunks per slice
+    uint32_t per_group;       // whole slices per chunk (1 when the slice is cut)
+    uint32_t groups;          // chunks along the slice-index dim
+    uint32_t n_slices;        // extent of the slice-index dim (the dim just outside the slice; 1 if there is none)
+    int64_t slice_src;        // source stride of the slice-index dim (== ea * eb when per_group > 1)
+    int n_outer;              // dims outside the slice-index dim
+    int64_t outer_shape[VF_MAX_RANK], outer_src[VF_MAX_RANK], outer_dst[VF_MAX_RANK];
+};
 constexpr int kSliceStages = 3;  // chunks in flight per CTA: the one being written and the copies of the next two
-template <int ES, typename I>
-__global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, Geom g, I chunks_a,
-                                                          I n_chunks, uint32_t rows_per_chunk, uint32_t buf_vecs, int64_t total_bytes) {
+template <int ES>
+__global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, SliceGeom g,
+                                                          int64_t n_chunks, uint32_t buf_vecs, int64_t total_bytes) {
     constexpr uint32_t VE = 16 / ES;  // elements per output vector
     extern __shared__ uint4 slice_smem[];
     using T = typename ElemOf<ES>::T;
-    const int a = g.rank - 1, b = g.rank - 2;
-    const uint32_t ea = uint32_t(g.out_shape[a]), eb = uint32_t(g.out_shape[b]);
+    const uint32_t ea = g.ea, eb = g.eb;
 
     struct Chunk {
-        int64_t dst0;    // element offset of the (others) slice in the output
+        int64_t dst0;    // element offset of the chunk's first slice in the output
         int64_t start;   // 16-byte aligned byte offset in the source at or below the chunk
-        uint32_t a0, ta; // first row and rows of the chunk
+        uint32_t a0, ta; // first row and rows (per slice) of the chunk
+        uint32_t ns;     // slices in the chunk
         uint32_t lead;   // bytes in front of the chunk inside its first vector
     };
-    auto locate = [&](I idx) -> Chunk {
+    auto locate = [&](int64_t idx) -> Chunk {
         Chunk c;
-        I rem = idx;
-        const I ca = rem % chunks_a;
-        rem /= chunks_a;
-        int64_t src0 = 0, dst0 = 0, dst_mul = 1;
-#pragma unroll
-        for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
-            if (d < g.rank) {
-                const I os = I(g.out_shape[d]);
-                if (d != a && d != b) {
-                    const I q = rem / os;
-                    const I cc = rem - q * os;
-                    rem = q;
-                    src0 += int64_t(cc) * g.src_stride[d];
-                    dst0 += int64_t(cc) * dst_mul;
-                }
-                dst_mul *= os;
-            }
+        int64_t rem = idx;
+        const uint32_t ca = uint32_t(rem % g.chunks_a);
+        rem /= g.chunks_a;
+        const uint32_t grp = uint32_t(rem % g.groups);
+        rem /= g.groups;
+        const uint32_t s0 = grp * g.per_group;
+        int64_t src0 = int64_t(s0) * g.slice_src, dst0 = int64_t(s0) * ea * eb;
+        for (int k = 0; k < g.n_outer; ++k) {
+            const int64_t q = rem / g.outer_shape[k];
+            const int64_t cc = rem - q * g.outer_shape[k];
+            rem = q;
+            src0 += cc * g.outer_src[k];
+            dst0 += cc * g.outer_dst[k];
         }
         c.dst0 = dst0;
-        c.a0 = uint32_t(ca) * rows_per_chunk;
-        c.ta = min(rows_per_chunk, ea - c.a0);
+        c.ns = min(g.per_group, g.n_slices - s0);
+        c.a0 = ca * g.rows;
+        c.ta = min(g.rows, ea - c.a0);
         const int64_t first = (src0 + int64_t(c.a0) * eb) * ES;  // byte offset of the chunk in the source
         c.start = first & ~int64_t(15);
         c.lead = uint32_t(first - c.start);
         return c;
     };
     // the copy of chunk `idx` into buffer `slot`, as one group of asynchronous copies (an empty group past the end)
-    auto fetch = [&](I idx, int slot) {
+    auto fetch = [&](int64_t idx, int slot) {
         if (idx < n_chunks) {
             const Chunk c = locate(idx);
             uint4* buf = slice_smem + slot * buf_vecs;
-            const uint32_t n_vec = (c.lead + c.ta * eb * ES + 15u) >> 4;
+            const uint32_t n_vec = (c.lead + c.ns * c.ta * eb * ES + 15u) >> 4;
             for (uint32_t v = threadIdx.x; v < n_vec; v += blockDim.x) {
                 const int64_t p = c.start + int64_t(v) * 16;
                 const int64_t left = total_bytes - p;  // the last vector of the buffer may be cut short
@@ -997,34 +925,44 @@ __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restr
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    I idx = I(blockIdx.x);
+    int64_t idx = blockIdx.x;
     if (idx >= n_chunks) return;
-    const I stride = I(gridDim.x);
+    const int64_t stride = gridDim.x;
 #pragma unroll
-    for (int s = 0; s < kSliceStages - 1; ++s) fetch(idx + I(s) * stride, s);
+    for (int s = 0; s < kSliceStages - 1; ++s) fetch(idx + s * stride, s);
     int cur = 0;
     for (; idx < n_chunks; idx += stride) {
         int ahead = cur + kSliceStages - 1;
         if (ahead >= kSliceStages) ahead -= kSliceStages;
-        fetch(idx + I(kSliceStages - 1) * stride, ahead);
+        fetch(idx + (kSliceStages - 1) * stride, ahead);
         asm volatile("cp.async.wait_group %0;" ::"n"(kSliceStages - 1) : "memory");
         __syncthreads();  // every thread's copies of this chunk have landed
         const Chunk c = locate(idx);
         const T* sm = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(slice_smem + cur * buf_vecs) + c.lead);
-        const uint32_t nab = c.ta / VE, n_out = nab * eb;
-        const uint32_t step_b = blockDim.x / nab, step_a = blockDim.x - step_b * nab;
-        uint32_t ib = threadIdx.x / nab, iab = threadIdx.x - ib * nab;
+        // output vectors of the chunk in output order: (slice, column ib, row block iab), iab fastest. With several
+        // slices per chunk a slice is whole (ta == ea) and the chunk's output is one contiguous run.
+        const uint32_t nab = c.ta / VE, per_slice = nab * eb, n_out = c.ns * per_slice;
+        uint32_t sl = threadIdx.x / per_slice, rem = threadIdx.x - sl * per_slice;
+        uint32_t ib = rem / nab, iab = rem - ib * nab;
+        const uint32_t step_s = blockDim.x / per_slice, step_r = blockDim.x - step_s * per_slice;
+        const uint32_t step_b = step_r / nab, step_a = step_r - step_b * nab;
         for (uint32_t v = threadIdx.x; v < n_out; v += blockDim.x) {
             __align__(16) T e[VE];
-            const T* col = sm + iab * VE * eb + ib;
+            const T* col = sm + sl * (c.ta * eb) + iab * VE * eb + ib;
 #pragma unroll
             for (uint32_t k = 0; k < VE; ++k) e[k] = col[k * eb];
-            *reinterpret_cast<uint4*>(out + (c.dst0 + int64_t(ib) * ea + c.a0 + iab * VE) * ES) = *reinterpret_cast<const uint4*>(e);
+            *reinterpret_cast<uint4*>(out + (c.dst0 + int64_t(sl) * ea * eb + int64_t(ib) * ea + c.a0 + iab * VE) * ES) =
+                    *reinterpret_cast<const uint4*>(e);
             iab += step_a;
             ib += step_b;
+            sl += step_s;
             if (iab >= nab) {
                 iab -= nab;
                 ++ib;
+            }
+            if (ib >= eb) {
+                ib -= eb;
+                ++sl;
             }
         }
         __syncthreads();  // this buffer is the target of the copy issued in the next iteration
@@ -1994,63 +1932,53 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
         (g.out_shape[a] * es) % 16 == 0 && aligned16(in, out)) {
         // the two innermost output dims are one contiguous block of the source: whole chunks through shared memory
         const int64_t ea = g.out_shape[a], eb = g.out_shape[a - 1], ve = 16 / es;
-        const int64_t budget = 24 * 1024 - 32;  // per buffer, two buffers per CTA
-        int64_t rows = std::min<int64_t>(ea, budget / (eb * es) / ve * ve);
+        const int64_t budget = 24 * 1024 - 32;  // per buffer, three buffers per CTA
+        const int64_t slice_bytes = ea * eb * es;
+        SliceGeom sg{};
+        sg.ea = uint32_t(ea);
+        sg.eb = uint32_t(eb);
+        const int o = a - 2;  // the dim that enumerates the slices (none for a rank-2 geometry)
+        sg.n_slices = o >= 0 ? uint32_t(g.out_shape[o]) : 1u;
+        sg.slice_src = o >= 0 ? g.src_stride[o] : 0;
+        int64_t rows = ea, per_group = 1;
+        if (slice_bytes > budget) {  // cut the slice into chunks of (nearly) equal row counts
+            const int64_t max_rows = budget / (eb * es) / ve * ve;
+            const int64_t pieces = max_rows > 0 ? (ea + max_rows - 1) / max_rows : 0;
+            rows = pieces > 0 ? ((ea + pieces - 1) / pieces + ve - 1) / ve * ve : 0;
+        } else if (o >= 0 && g.src_stride[o] == ea * eb) {  // consecutive slices are contiguous: several per chunk
+            per_group = std::min<int64_t>(budget / slice_bytes, sg.n_slices);
+        }
+        sg.rows = uint32_t(rows);
+        sg.chunks_a = rows > 0 ? uint32_t((ea + rows - 1) / rows) : 0u;
+        sg.per_group = uint32_t(per_group);
+        sg.groups = uint32_t((sg.n_slices + per_group - 1) / per_group);
+        int64_t n_chunks = int64_t(sg.chunks_a) * sg.groups, dst_stride = ea * eb * int64_t(sg.n_slices);
+        for (int d = o - 1; d >= 0; --d) {  // innermost of the outer dims first: the chunk index is decomposed that way
+            sg.outer_shape[sg.n_outer] = g.out_shape[d];
+            sg.outer_src[sg.n_outer] = g.src_stride[d];
+            sg.outer_dst[sg.n_outer] = dst_stride;
+            ++sg.n_outer;
+            dst_stride *= g.out_shape[d];
+            n_chunks *= g.out_shape[d];
+        }
         const bool bank_stride = (ve * eb * es) % 128 == 0;  // lanes of a store vector would meet in one bank
-        int64_t others = 1;
-        for (int d = 0; d < a - 1; ++d) others *= g.out_shape[d];
-        const int64_t chunks_a = rows > 0 ? (ea + rows - 1) / rows : 0;
-        if (rows * es >= 64 && !bank_stride && chunks_a * others < (int64_t(1) << 31)) {
+        if (rows * es >= 64 && !bank_stride && n_chunks < (int64_t(1) << 40)) {
             int64_t src_elems = 1;
             for (int d = 0; d < g.rank; ++d) src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
             const int64_t total_bytes = src_elems * es;  // the last byte the launch may read lies inside the source buffer
-            const uint32_t buf_vecs = uint32_t((rows * eb * es + 15 + 15) / 16);
+            const uint32_t buf_vecs = uint32_t((per_group * rows * eb * es + 15 + 15) / 16);
             const size_t smem = size_t(buf_vecs) * 16 * kSliceStages;
-            const int64_t n_chunks = chunks_a * others;
             const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (216 * 1024) / int64_t(smem + 1024)));
             const unsigned blocks = unsigned(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * per_sm));
-            if (smem > 48 * 1024) {
-#define VF_SLICE_SMEM(ES_, I_) VF_CUDA(cudaFuncSetAttribute(k_transpose_slices<ES_, I_>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)))
-                VF_SLICE_SMEM(1, uint32_t); VF_SLICE_SMEM(2, uint32_t); VF_SLICE_SMEM(4, uint32_t);
-                VF_SLICE_SMEM(1, int64_t); VF_SLICE_SMEM(2, int64_t); VF_SLICE_SMEM(4, int64_t);
-#undef VF_SLICE_SMEM
-            }
-            if (small) {
-                using I = uint32_t;
-                VF_BY_ELEM_SIZE(es, (k_transpose_slices<(ES > 4 ? 4 : ES), I><<<blocks, kBlock, smem, ctx->stream>>>(
-                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, I(chunks_a), I(n_chunks), uint32_t(rows), buf_vecs,
-                                        total_bytes)));
-            } else {
-                using I = int64_t;
-                VF_BY_ELEM_SIZE(es, (k_transpose_slices<(ES > 4 ? 4 : ES), I><<<blocks, kBlock, smem, ctx->stream>>>(
-                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, I(chunks_a), I(n_chunks), uint32_t(rows), buf_vecs,
-                                        total_bytes)));
-            }
-            post_launch(ctx);
-            return;
-        }
+            const uint8_t* src = static_cast<const uint8_t*>(in);
+            uint8_t* dst = static_cast<uint8_t*>(out);
+#define VF_SLICES(ES_)                                                                                                           \
+    {                                                                                                                            \
+        if (smem > 48 * 1024) VF_CUDA(cudaFuncSetAttribute(k_transpose_slices<ES_>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))); \
+        k_transpose_slices<ES_><<<blocks, kBlock, smem, ctx->stream>>>(src, dst, sg, n_chunks, buf_vecs, total_bytes);          \
     }
-    if (es <= 4 && b >= 0 && g.src_stride[a] != 1 && (g.out_shape[a] * es) % 16 == 0 && aligned16(in, out)) {
-        // output rows of whole 16-byte vectors: 64-row tiles, gathered and written as vectors
-        const int64_t ta = (g.out_shape[a] + kRowsTile - 1) / kRowsTile, tb = (g.out_shape[b] * es + kRowBytes - 1) / kRowBytes;
-        int64_t others = 1, dst_stride_b = 1, src_elems = 1;
-        for (int d = 0; d < g.rank; ++d) {
-            if (d != a && d != b) others *= g.out_shape[d];
-            src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
-        }
-        for (int d = b + 1; d < g.rank; ++d) dst_stride_b *= g.out_shape[d];
-        const int64_t blocks = others * ta * tb;
-        if (blocks < (int64_t(1) << 31) && (dst_stride_b * es) % 16 == 0) {
-            const int64_t total_bytes = src_elems * es;
-            if (small) {
-                using I = uint32_t;
-                VF_BY_ELEM_SIZE(es, (k_transpose_rows<(ES > 4 ? 4 : ES), I><<<unsigned(blocks), kBlock, 0, ctx->stream>>>(
-                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, b, I(ta), I(tb), dst_stride_b, total_bytes)));
-            } else {
-                using I = int64_t;
-                VF_BY_ELEM_SIZE(es, (k_transpose_rows<(ES > 4 ? 4 : ES), I><<<unsigned(blocks), kBlock, 0, ctx->stream>>>(
-                                        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g, b, I(ta), I(tb), dst_stride_b, total_bytes)));
-            }
+            if (es == 1) VF_SLICES(1) else if (es == 2) VF_SLICES(2) else VF_SLICES(4)
+#undef VF_SLICES
             post_launch(ctx);
             return;
         }
