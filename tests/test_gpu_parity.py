@@ -812,6 +812,52 @@ def test_pipelined_batches_defer_kernel_errors_to_the_next_synchronisation(oracl
     lib.close()
 
 
+def test_pipelined_fold_calls_defer_and_report_at_synchronisation(oracle):
+    """VF_OPT_ASYNC: vf_fold over device memory returns once enqueued; results equal the oracle's after
+    vf_ctx_synchronize, and what a kernel finds (a NaN in Quantize) is reported there, not by the call."""
+    import torch
+    from vpux_plugin_b200.lib import Library
+    lib = Library(device=0, pipelined=True)
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(41)
+    shape = [24, 64, 3, 3]
+    t = TType(shape, F16)
+    x = (rng.standard_normal(shape) * 0.05).astype(np.float16)
+    n = x.size
+    q = Elem.per_axis(I8, F16, rng.uniform(1e-3, 1e-2, shape[0]).tolist(), [0] * shape[0], 0, -127, 127)
+    setups = [ContentSetup(t).quantize(q).reorder(abi.ORDER_NHWC), ContentSetup(t).reorder(abi.ORDER_NHWC),
+              ContentSetup(t).castElemType(F32).rescale(0.5), ContentSetup(t).padWithZero([0, 0, 0, 0], [8, 0, 0, 0])]
+    src = torch.from_numpy(x.view(np.uint8).reshape(-1)).to(dev)
+    c, keep = abi.make_content(t, None, F16, False, abi.VF_MEM_DEVICE, ptr=src.data_ptr(), nbytes=n * 2)
+    outs = []
+    for s in setups:
+        tr, k = s.transforms()
+        _, _, nbytes = lib.infer_type(t, False, tr, k)
+        dst = torch.full((nbytes,), 0xEE, dtype=torch.uint8, device=dev)
+        outs.append((s, tr, k, dst, nbytes))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        for s, tr, k, dst, nbytes in outs:
+            lib.fold(c, tr, k, dst.data_ptr(), nbytes, dst_mem_kind=abi.VF_MEM_DEVICE)
+    lib.synchronize()
+    for s, tr, k, dst, nbytes in outs:
+        ref = ContentAttr(x, t, s).fold(oracle)
+        assert np.array_equal(dst.cpu().numpy(), ref.bytes())
+    bad = x.copy()
+    bad.reshape(-1)[77] = np.nan
+    src.copy_(torch.from_numpy(bad.view(np.uint8).reshape(-1)))
+    torch.cuda.synchronize()
+    s, tr, k, dst, nbytes = outs[0]
+    lib.fold(c, tr, k, dst.data_ptr(), nbytes, dst_mem_kind=abi.VF_MEM_DEVICE)  # returns: nothing has been checked yet
+    assert _status(lib.synchronize) == abi.VF_ERR_NAN
+    src.copy_(torch.from_numpy(x.view(np.uint8).reshape(-1)))
+    torch.cuda.synchronize()
+    lib.fold(c, tr, k, dst.data_ptr(), nbytes, dst_mem_kind=abi.VF_MEM_DEVICE)
+    lib.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), ContentAttr(x, t, s).fold(oracle).bytes())
+    lib.close()
+
+
 def test_weights_table_batch(gpu, oracle):
     """Many tables per call (dense and sparse pointers, with and without bias, 1..2500 channels); weight scales
     either inside the descriptor or as a separate FP64 array; one launch for all rows."""

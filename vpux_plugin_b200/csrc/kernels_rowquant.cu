@@ -1373,7 +1373,9 @@ int rowquant_kind(const RowQuantArgs& a) {
         const bool vec_rows = aligned16 && a.cols % 8 == 0;
         convv_ok = two_byte && (vec_rows || a.khw > 0) && a.cols <= 4608 && out_row <= 4608 && ic_pad % 4 == 0 &&
                    reinterpret_cast<uintptr_t>(a.codes) % 4 == 0 && reinterpret_cast<uintptr_t>(a.in) % 2 == 0;
-        conv_ok = out_row <= 24 * 1024;
+        // the scalar kernel is for the short rows of convolutions (fp32 input, odd sizes): a warp walks a row element by
+        // element, so long rows are left to the general kernels, which read them as vectors
+        conv_ok = out_row <= 8192 && a.cols <= 8192;
     }
     // a convolution weight (it came with an OIYX -> OYXI reorder: ic is set) stays with the other convolutions of its
     // network in one launch, also where its 1x1 rows would suit the row kernel
