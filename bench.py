@@ -122,7 +122,8 @@ class Workload:
                          "c3": "c3: ResNet-50 v1.5 weight set, Bernoulli(1/2) masked with 1 channel in 10 dense: c2 fold, then "
                                "Sparsify + GetSparsityMap + per-channel counts on the folded i8 codes"}[key]
             self.alg_bytes_per_elem = {"c1": 4.0 + 64.0 / 60.0, "c2": 3.0, "c3": 2.0 + 1.0 + 1.0 + 0.55 + 0.125}[key]
-            self.kernel = "k_conv (+ k_row for aligned rows >= 1024)" if key != "c3" else "k_conv/k_row + k_sparsity_scan + k_sparse_offsets + k_sparse_compact"
+            self.kernel = {"c1": "k_conv (fp32 input)", "c2": "k_convv<half> + k_weights_table_batch",
+                           "c3": "k_convv<half> + k_sparse_scan_batch + k_sparse_offsets_batch + k_sparse_compact_batch + table kernels"}[key]
             self.shard_mode = 0
             self.seed = wl.SEEDS[key]
             return

@@ -1009,10 +1009,30 @@ __device__ __forceinline__ typename ElemOf<ES>::T wide_fill(const uint8_t* __res
 }
 
 // PadWithZero — attributes/pad_with_zero.cpp:111-268 + Content::fillWithZero utils/content.cpp:190-237
+// Division of a 32-bit index by an extent known at launch (Granlund-Montgomery): q = (t + ((n - t) >> 1)) >> (l - 1)
+// with t = umulhi(m, n), l = ceil(log2 d), m = floor(2^32 (2^l - d) / d) + 1; d = 1 has l = 0 and is passed through.
+struct FastDivs {
+    uint32_t mul[VF_MAX_RANK];
+    uint32_t sh[VF_MAX_RANK];  // l; 0: the divisor is 1
+};
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t l) {
+    if (l == 0) return n;
+    const uint32_t t = __umulhi(mul, n);
+    return (t + ((n - t) >> 1)) >> (l - 1);
+}
+template <typename I>
+__device__ __forceinline__ I div_extent(I n, I d, const FastDivs& f, int k) {
+    return n / d;
+}
+template <>
+__device__ __forceinline__ uint32_t div_extent<uint32_t>(uint32_t n, uint32_t d, const FastDivs& f, int k) {
+    return fast_div(n, f.mul[k], f.sh[k]);
+}
+
 // Four output elements per thread step, their loads issued together (an SM needs on the order of 100 KB in flight
 // to keep the memory busy: one 16-byte load per thread is a third of that).
 template <int ES, typename I>
-__global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restrict__ out, Geom g, I n,
+__global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restrict__ out, Geom g, FastDivs fd, I n,
                       const uint8_t* __restrict__ fill, int fill_es, I n_fill, int fill_dim) {
     using T = typename ElemOf<ES>::T;
     constexpr int kU = 4;
@@ -1030,7 +1050,7 @@ __global__ void k_pad(const void* __restrict__ in, int in_splat, void* __restric
             for (int d = VF_MAX_RANK - 1; d >= 0; --d) {
                 if (d < g.rank) {
                     const I os = I(g.out_shape[d]);
-                    const I q = rem / os;
+                    const I q = div_extent<I>(rem, os, fd, d);
                     const I c = rem - q * os;
                     rem = q;
                     if (d == fill_dim) fc = c;
@@ -1962,7 +1982,8 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
             n_chunks *= g.out_shape[d];
         }
         const bool bank_stride = (ve * eb * es) % 128 == 0;  // lanes of a store vector would meet in one bank
-        if (rows * es >= 64 && !bank_stride && n_chunks < (int64_t(1) << 40)) {
+        const bool fits32 = ea < (int64_t(1) << 31) && eb < (int64_t(1) << 31) && ea * eb < (int64_t(1) << 31) && (o < 0 || g.out_shape[o] < (int64_t(1) << 31));
+        if (rows * es >= 64 && !bank_stride && fits32 && n_chunks < (int64_t(1) << 40)) {
             int64_t src_elems = 1;
             for (int d = 0; d < g.rank; ++d) src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
             const int64_t total_bytes = src_elems * es;  // the last byte the launch may read lies inside the source buffer
@@ -2025,12 +2046,20 @@ void launch_pad(vf_ctx* ctx, const void* in, bool in_splat, void* out, const Geo
     const int grid = grid_for(n, 4);
     const uint8_t* fill = static_cast<const uint8_t*>(d_fill);
     const int fd = n_fill > 1 ? keep : 0;
+    FastDivs divs{};
+    for (int d = 0; d < g.rank; ++d) {  // used by the 32-bit instantiation only (every extent is below 2^31 there)
+        const uint64_t e = uint64_t(g.out_shape[d]);
+        uint32_t l = 0;
+        while ((uint64_t(1) << l) < e) ++l;
+        divs.sh[d] = l;
+        divs.mul[d] = e > 1 ? uint32_t(((uint64_t(1) << 32) * ((uint64_t(1) << l) - e)) / e + 1) : 0u;
+    }
     if (max_index(g, 2) < (int64_t(1) << 31)) {
         using I = uint32_t;
-        VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, I(n), fill, es0, I(n_fill), fd)));
+        VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, divs, I(n), fill, es0, I(n_fill), fd)));
     } else {
         using I = int64_t;
-        VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, I(n), fill, es0, I(n_fill), fd)));
+        VF_BY_ELEM_SIZE(es, (k_pad<ES, I><<<grid, kBlock, 0, ctx->stream>>>(in, in_splat, out, g, divs, I(n), fill, es0, I(n_fill), fd)));
     }
     post_launch(ctx);
 }
