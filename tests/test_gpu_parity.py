@@ -121,6 +121,11 @@ def test_rescale_add(gpu, oracle, dt):
     t = TType([4, 33], dt)
     x = _rand(rng, t.shape, dt) if dt in (F32, F16, BF16) else rng.integers(0, 100, t.shape).astype(abi.DTYPE_NUMPY[dt])
     both(ContentAttr(x, t, ContentSetup(t).rescale(0.37).add(1.25)), gpu, oracle)
+    if dt in (F32, F16, BF16):  # several vector steps per thread and a tail of three elements
+        t2 = TType([5, 4099], dt)
+        x2 = _rand(rng, t2.shape, dt)
+        both(ContentAttr(x2, t2, ContentSetup(t2).rescale(-1.5)), gpu, oracle)
+        both(ContentAttr(x2, t2, ContentSetup(t2).add(0.001)), gpu, oracle)
 
 
 @pytest.mark.parametrize("dt,es", [(U8, 1), (F16, 2), (F32, 4)])

@@ -111,23 +111,16 @@ __device__ __forceinline__ void store8(void* __restrict__ out, int64_t g, const 
     }
 }
 
-// FAST: the element is first quantized as round(fma(x, inv, c)) with inv = fl((L-1)/range), c = fl(-inLow*inv);
-// it differs from the reference's individually rounded sequence by less than 4.2e-7 * L, so only elements whose
-// rounding residual comes within 8e-7 * L of a half are recomputed with the exact sequence. The host enables it
-// when the tail of fakeQuantize is the identity on the indices of this storage range (tail_is_identity).
-template <int IN, typename I, bool FAST>
+// Quantize of floating-point input to 8-bit storage with fakeQuantize as written (ranges whose tail is not the
+// identity on the indices, and launches too large for the 32-bit unit count of k_quantize_rows): eight elements per
+// thread step.
+template <int IN, typename I>
 __global__ void k_quantize8(const void* __restrict__ in, uint8_t* __restrict__ out, I n_groups, const double* __restrict__ scales,
                             const int64_t* __restrict__ zps, I axis_size, I inner8, long long qmin, long long qmax, int* flags) {
     const I stride = I(gridDim.x) * I(blockDim.x);
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-    constexpr int kMagicBits = 0x4B400000;
     for (I g = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); g < n_groups; g += stride) {
         const I a = axis_size > 1 ? (g / inner8) % axis_size : I(0);
         const QuantParams qp = make_quant_params(scales[a], zps[a], qmin, qmax);
-        const float inv = __fdiv_rn(qp.levels_m1, qp.range);
-        const float c = __fmul_rn(-qp.in_low, inv);
-        const float thr = 0.5f - 8.0e-7f * (qp.levels_m1 + 1.0f);
-        const int lm1 = int(qmax - qmin);
         __align__(16) uint8_t ib[Bytes8<IN>::value];
         __align__(8) uint8_t ob[8];
         load8<IN>(in, int64_t(g), ib);
@@ -135,46 +128,26 @@ __global__ void k_quantize8(const void* __restrict__ in, uint8_t* __restrict__ o
         for (int k = 0; k < 8; ++k) {
             const float x = load_as_f32(ib, IN, k, flags);
             if (x != x) set_flag(flags, VF_FLAG_NAN);
-            if (FAST) {
-                const float t = __fmaf_rn(x, inv, c);
-                const float m = __fadd_rn(t, kMagic);
-                const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
-                int code;
-                if (fabsf(resid) <= thr) {  // false for NaN as well
-                    const int n = __float_as_int(m) - kMagicBits;
-                    code = min(max(n, 0), lm1) + int(qmin);
-                } else {
-                    code = int(quantize_exact(x, qp));
-                }
-                ob[k] = uint8_t(code);
-            } else {
-                ob[k] = uint8_t(quantize_exact(x, qp));
-            }
+            ob[k] = uint8_t(quantize_exact(x, qp));
         }
         store8<8>(out, int64_t(g), ob);
     }
 }
 
-// The same two kernels by rows: a block iteration covers a chunk of kRowUnroll * blockDim groups of ONE row of the
-// quantized axis, so the row's parameters (two FP64 products, a division) and the row index (two integer
-// divisions) are computed once per chunk instead of once per group. Used when a row holds at least one chunk's
-// worth of groups; a per-tensor type is one row.
+// The same by rows: a block iteration covers a chunk of kRowUnroll * blockDim groups of ONE row of the quantized
+// axis, so the row's parameters (two FP64 products, a division) and the row index (two integer divisions) are
+// computed once per chunk instead of once per group. Used when a row holds at least one chunk's worth of groups; a
+// per-tensor type is one row.
 constexpr int kRowUnroll = 4;
-template <int IN, typename I, bool FAST>
+template <int IN, typename I>
 __global__ void k_quantize8_rows(const void* __restrict__ in, uint8_t* __restrict__ out, I n_rows, I chunks_per_row,
                                  const double* __restrict__ scales, const int64_t* __restrict__ zps, I axis_size, I inner8,
                                  long long qmin, long long qmax, int* flags) {
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-    constexpr int kMagicBits = 0x4B400000;
     const I n_chunks = n_rows * chunks_per_row;
-    const int lm1 = int(qmax - qmin);
     for (I chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
         const I row = chunk / chunks_per_row, c_in_row = chunk - row * chunks_per_row;
         const I a = axis_size > 1 ? row % axis_size : I(0);
         const QuantParams qp = make_quant_params(scales[a], zps[a], qmin, qmax);
-        const float inv = __fdiv_rn(qp.levels_m1, qp.range);
-        const float c = __fmul_rn(-qp.in_low, inv);
-        const float thr = 0.5f - 8.0e-7f * (qp.levels_m1 + 1.0f);
         const I g0 = c_in_row * I(kRowUnroll) * I(blockDim.x) + I(threadIdx.x);
 #pragma unroll
         for (int u = 0; u < kRowUnroll; ++u) {
@@ -188,21 +161,7 @@ __global__ void k_quantize8_rows(const void* __restrict__ in, uint8_t* __restric
             for (int k = 0; k < 8; ++k) {
                 const float x = load_as_f32(ib, IN, k, flags);
                 if (x != x) set_flag(flags, VF_FLAG_NAN);
-                if (FAST) {
-                    const float t = __fmaf_rn(x, inv, c);
-                    const float m = __fadd_rn(t, kMagic);
-                    const float resid = __fsub_rn(t, __fsub_rn(m, kMagic));
-                    int code;
-                    if (fabsf(resid) <= thr) {  // false for NaN as well
-                        const int n = __float_as_int(m) - kMagicBits;
-                        code = min(max(n, 0), lm1) + int(qmin);
-                    } else {
-                        code = int(quantize_exact(x, qp));
-                    }
-                    ob[k] = uint8_t(code);
-                } else {
-                    ob[k] = uint8_t(quantize_exact(x, qp));
-                }
+                ob[k] = uint8_t(quantize_exact(x, qp));
             }
             store8<8>(out, g, ob);
         }
@@ -548,19 +507,37 @@ __global__ void __launch_bounds__(256) k_dequantize_rows(const uint32_t* __restr
     }
 }
 
+// Rescale / Add with four elements per lane and item: one 16-byte (f32) or 8-byte (16-bit types) load and one 16-byte
+// store, so every access of a warp is one contiguous run of whole sectors; four items per thread step, their loads
+// issued together.
 template <int IN>
-__global__ void k_rescale_add8(const void* __restrict__ in, float* __restrict__ out, int64_t n_groups, float c, int is_add, int* flags) {
+__global__ void k_rescale_add4(const void* __restrict__ in, float4* __restrict__ out, int64_t n_items, float c, int is_add, int* flags) {
+    constexpr int kU = 4;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
-        __align__(16) uint8_t ib[Bytes8<IN>::value];
-        __align__(16) float ob[8];
-        load8<IN>(in, g, ib);
+    for (int64_t t0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t0 < n_items; t0 += kU * stride) {
+        float4 v[kU];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float v = load_as_f32(ib, IN, k, flags);
-            ob[k] = is_add ? __fadd_rn(v, c) : __fmul_rn(v, c);
+        for (int u = 0; u < kU; ++u) {
+            const int64_t t = t0 + u * stride;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < n_items) {
+                if (IN == VF_DT_F32) {
+                    v[u] = __ldg(reinterpret_cast<const float4*>(in) + t);
+                } else {
+                    const uint2 w = __ldg(reinterpret_cast<const uint2*>(in) + t);
+                    v[u] = make_float4(load_as_f32(&w, IN, 0, flags), load_as_f32(&w, IN, 1, flags), load_as_f32(&w, IN, 2, flags),
+                                       load_as_f32(&w, IN, 3, flags));
+                }
+            }
         }
-        store8<32>(out, g, reinterpret_cast<const uint8_t*>(ob));
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int64_t t = t0 + u * stride;
+            if (t >= n_items) break;
+            const float4 x = v[u];
+            out[t] = is_add ? make_float4(__fadd_rn(x.x, c), __fadd_rn(x.y, c), __fadd_rn(x.z, c), __fadd_rn(x.w, c))
+                            : make_float4(__fmul_rn(x.x, c), __fmul_rn(x.y, c), __fmul_rn(x.z, c), __fmul_rn(x.w, c));
+        }
     }
 }
 
@@ -612,6 +589,16 @@ __global__ void k_pack_subbyte(const void* __restrict__ in, int in_dt, uint8_t* 
 // the sign-extending branch (:47-66), otherwise the masking branch (:28-46).
 template <int BITS>
 __device__ __forceinline__ uint2 expand8(uint32_t w, int sign) {  // eight elements of BITS bits -> eight bytes
+    if (BITS == 4) {
+        // even nibbles and odd nibbles as bytes, interleaved by two byte permutes; a set bit 3 times 0x1E is 0xF0, the
+        // sign extension of a 4-bit value (no carry between bytes)
+        uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+        if (sign) {
+            lo |= (lo & 0x08080808u) * 0x1Eu;
+            hi |= (hi & 0x08080808u) * 0x1Eu;
+        }
+        return make_uint2(__byte_perm(lo, hi, 0x5140), __byte_perm(lo, hi, 0x7362));
+    }
     constexpr unsigned kMask = (1u << BITS) - 1u;
     uint32_t r[2] = {0u, 0u};
 #pragma unroll
@@ -1688,12 +1675,8 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
             const int rgrid = int(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * 16));
             using I = uint32_t;
 #define VF_Q8R(IN)                                                                                                                      \
-    if (fast)                                                                                                                           \
-        k_quantize8_rows<IN, I, true><<<rgrid, kBlock, 0, ctx->stream>>>(in, o, I(n_rows), I(chunks_per_row), d_scales, d_zps,         \
-                                                                         I(axis_size), I(row_len), qmin, qmax, ctx->d_flags);         \
-    else                                                                                                                                \
-        k_quantize8_rows<IN, I, false><<<rgrid, kBlock, 0, ctx->stream>>>(in, o, I(n_rows), I(chunks_per_row), d_scales, d_zps,        \
-                                                                          I(axis_size), I(row_len), qmin, qmax, ctx->d_flags);
+    k_quantize8_rows<IN, I><<<rgrid, kBlock, 0, ctx->stream>>>(in, o, I(n_rows), I(chunks_per_row), d_scales, d_zps, I(axis_size),      \
+                                                               I(row_len), qmin, qmax, ctx->d_flags);
             if (in_dt == VF_DT_F32) { VF_Q8R(VF_DT_F32) }
             else if (in_dt == VF_DT_F16) { VF_Q8R(VF_DT_F16) }
             else { VF_Q8R(VF_DT_BF16) }
@@ -1702,13 +1685,8 @@ void launch_quantize(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, void
             return;
         }
 #define VF_Q8(IN)                                                                                                                       \
-    if (fast) {                                                                                                                         \
-        VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I, true><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps,        \
-                                                                                              I(axis_size), I(inner8), qmin, qmax, ctx->d_flags))); \
-    } else {                                                                                                                            \
-        VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I, false><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps,       \
-                                                                                               I(axis_size), I(inner8), qmin, qmax, ctx->d_flags))); \
-    }
+    VF_BY_INDEX_WIDTH(groups, (k_quantize8<IN, I><<<grid, kBlock, 0, ctx->stream>>>(in, o, I(groups), d_scales, d_zps, I(axis_size),    \
+                                                                                    I(inner8), qmin, qmax, ctx->d_flags)));
         if (in_dt == VF_DT_F32) { VF_Q8(VF_DT_F32); }
         else if (in_dt == VF_DT_F16) { VF_Q8(VF_DT_F16); }
         else { VF_Q8(VF_DT_BF16); }
@@ -1785,14 +1763,15 @@ void launch_rescale_add(vf_ctx* ctx, const void* in, int in_dt, bool in_splat, f
                         bool is_add) {
     if (n <= 0) return;
     int64_t done = 0;
-    if (!in_splat && n >= 8 && aligned16(in, out) && (in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16)) {
-        const int64_t groups = n / 8;
-        const int grid = grid_for(groups);
-        if (in_dt == VF_DT_F32) k_rescale_add8<VF_DT_F32><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, c, is_add, ctx->d_flags);
-        else if (in_dt == VF_DT_F16) k_rescale_add8<VF_DT_F16><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, c, is_add, ctx->d_flags);
-        else k_rescale_add8<VF_DT_BF16><<<grid, kBlock, 0, ctx->stream>>>(in, out, groups, c, is_add, ctx->d_flags);
+    if (!in_splat && n >= 4 && aligned16(in, out) && (in_dt == VF_DT_F32 || in_dt == VF_DT_F16 || in_dt == VF_DT_BF16)) {
+        const int64_t items = n / 4;
+        const int grid = grid_for(items, 4);
+        float4* o4 = reinterpret_cast<float4*>(out);
+        if (in_dt == VF_DT_F32) k_rescale_add4<VF_DT_F32><<<grid, kBlock, 0, ctx->stream>>>(in, o4, items, c, is_add, ctx->d_flags);
+        else if (in_dt == VF_DT_F16) k_rescale_add4<VF_DT_F16><<<grid, kBlock, 0, ctx->stream>>>(in, o4, items, c, is_add, ctx->d_flags);
+        else k_rescale_add4<VF_DT_BF16><<<grid, kBlock, 0, ctx->stream>>>(in, o4, items, c, is_add, ctx->d_flags);
         post_launch(ctx);
-        done = groups * 8;
+        done = items * 4;
     }
     if (done < n) {
         k_rescale_add<<<grid_for(n - done), kBlock, 0, ctx->stream>>>(static_cast<const char*>(in) + done * (dtype_bits(in_dt) / 8), in_dt,
