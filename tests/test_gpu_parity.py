@@ -143,6 +143,7 @@ def test_reorder(gpu, oracle, dt, es, shape, order_in, order_out):
 @pytest.mark.parametrize("dt,es", [(U8, 1), (F16, 2), (F32, 4)])
 @pytest.mark.parametrize("shape", [
     [5, 64, 3, 3], [3, 32, 5, 5], [2, 200, 7, 7], [2, 2048, 3, 3], [3, 16, 1, 2],      # whole slices through shared memory
+    [50, 64, 3, 3], [131, 128, 1, 3],                                                  # several slices per chunk, a ragged last chunk
     [3, 64, 3, 171], [2, 80, 1, 1000], [2, 24, 3, 200], [1, 16, 37, 19], [2, 208, 9, 33],  # slices too large for it: 64 x 64 tiles
     [4, 48, 4, 4], [2, 16, 8, 16]])                                                      # row strides that are multiples of 128 bytes
 def test_reorder_oiyx_to_oyxi_transposes(gpu, oracle, dt, es, shape):
