@@ -1035,9 +1035,11 @@ def test_expand_dilated(gpu, oracle, dil):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dt,np_dt", [(U8, np.uint8), (F16, np.float16), (F32, np.float32)])
-@pytest.mark.parametrize("shape,dil", [([5, 7, 3, 3], (2, 2)), ([33, 17, 5, 1], (4, 2)), ([3, 3, 1, 7], (1, 5)), ([16, 31, 3, 3], (6, 6))])
+@pytest.mark.parametrize("shape,dil", [([5, 7, 3, 3], (2, 2)), ([33, 17, 5, 1], (4, 2)), ([3, 3, 1, 7], (1, 5)), ([16, 31, 3, 3], (6, 6)),
+                                       ([61, 37, 3, 3], (2, 2)), ([64, 40, 2, 2], (3, 2)), ([7, 9, 9, 9], (8, 8))])
 def test_expand_dilated_vector_steps(gpu, oracle, dt, np_dt, shape, dil):
-    """Output sizes that are not multiples of the 16-byte store unit, rows shorter and longer than one unit."""
+    """Output sizes that are not multiples of the 16-byte store unit, rows shorter and longer than one unit, plane
+    counts of one partial chunk, several chunks with a ragged last one, and planes too large to be staged."""
     rng = np.random.default_rng(sum(shape) + dil[0])
     x = rng.integers(1, 120, shape).astype(np_dt)
     t = TType(shape, dt)

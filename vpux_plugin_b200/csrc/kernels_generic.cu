@@ -1460,6 +1460,69 @@ __global__ void k_expand_dilated_lut(const void* __restrict__ in, int in_splat, 
     }
 }
 
+// The same transformation a chunk of planes at a time, through shared memory, for a single fill value: the chunk's
+// input planes (contiguous) arrive as 16-byte vectors, the output stage is filled with the fill value by 16-byte
+// stores, every tap is moved to its place in its dilated plane (one 2-byte load and store per input element), and
+// the stage leaves as 16-byte vectors. Per output element that is about one shared-memory access and no index
+// arithmetic, against a table read, a gathered load and a division per vector in the kernel above. A chunk is a
+// multiple of 16 planes, so chunks start on 16-byte boundaries on both sides.
+template <int ES>
+__global__ void __launch_bounds__(256) k_expand_dilated_planes(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n_planes,
+                                                               uint32_t planes_per_chunk, uint32_t plane_in, uint32_t plane_out, uint32_t kx,
+                                                               uint32_t dkx, uint32_t dil_y, uint32_t dil_x, const uint8_t* __restrict__ fill) {
+    using T = typename ElemBits<ES>::type;
+    extern __shared__ uint4 dil_smem[];
+    const uint32_t in_vecs = (planes_per_chunk * plane_in * ES + 15u) / 16u;
+    uint4* s_in = dil_smem;
+    uint4* s_out = dil_smem + in_vecs;
+    __align__(16) uint8_t fb[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) fb[k] = fill[k % ES];
+    const uint4 fill_vec = *reinterpret_cast<const uint4*>(fb);
+    const int64_t n_chunks = (n_planes + planes_per_chunk - 1) / planes_per_chunk;
+    for (int64_t chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+        const int64_t p0 = chunk * planes_per_chunk;
+        const uint32_t np = uint32_t(min(int64_t(planes_per_chunk), n_planes - p0));
+        const uint32_t in_bytes = np * plane_in * ES, out_bytes = np * plane_out * ES;
+        const uint8_t* src = in + p0 * plane_in * ES;
+        uint8_t* dst = out + p0 * plane_out * ES;
+        for (uint32_t v = threadIdx.x; v * 16 < in_bytes; v += blockDim.x) {
+            if (v * 16 + 16 <= in_bytes) {
+                s_in[v] = __ldg(reinterpret_cast<const uint4*>(src) + v);
+            } else {  // the last vector of the last chunk may be cut short
+                uint8_t* sb = reinterpret_cast<uint8_t*>(s_in + v);
+                for (uint32_t k = 0; v * 16 + k < in_bytes; ++k) sb[k] = src[v * 16 + k];
+            }
+        }
+        for (uint32_t v = threadIdx.x; v * 16 < out_bytes; v += blockDim.x) s_out[v] = fill_vec;
+        __syncthreads();
+        const T* ti = reinterpret_cast<const T*>(s_in);
+        T* to = reinterpret_cast<T*>(s_out);
+        for (uint32_t p = threadIdx.x; p < np; p += blockDim.x) {
+            const T* pi = ti + p * plane_in;
+            T* po = to + p * plane_out;
+            uint32_t ty = 0, tx = 0;
+            for (uint32_t t = 0; t < plane_in; ++t) {
+                po[ty * dil_y * dkx + tx * dil_x] = pi[t];
+                if (++tx == kx) {
+                    tx = 0;
+                    ++ty;
+                }
+            }
+        }
+        __syncthreads();
+        for (uint32_t v = threadIdx.x; v * 16 < out_bytes; v += blockDim.x) {
+            if (v * 16 + 16 <= out_bytes) {
+                reinterpret_cast<uint4*>(dst)[v] = s_out[v];
+            } else {
+                const uint8_t* sb = reinterpret_cast<const uint8_t*>(s_out + v);
+                for (uint32_t k = 0; v * 16 + k < out_bytes; ++k) dst[v * 16 + k] = sb[k];
+            }
+        }
+        __syncthreads();  // the stages are rewritten by the next chunk
+    }
+}
+
 // ScalarMultInverse — attributes/inverse.cpp:52-66: 1.f / v in f32; zero, subnormal, infinite or NaN input throws
 __device__ __forceinline__ float inverse_checked(float v, int* flags) {
     const uint32_t e = (__float_as_uint(v) >> 23) & 0xFFu;
@@ -2226,6 +2289,35 @@ void launch_expand_dilated(vf_ctx* ctx, const void* in, bool in_splat, void* out
                            int64_t fill_stride, int64_t fill_extent, int es) {
     if (n_out <= 0) return;
     const int64_t n_rows = n_out / dkx;
+    {  // a single fill value, planes small enough for a chunk of at least 16 in shared memory: whole chunks staged
+        const int64_t plane_in = ky * kx, plane_out = dky * dkx, n_planes = plane_out > 0 ? n_out / plane_out : 0;
+        const int64_t per_plane = (plane_in + plane_out) * es;
+        int64_t ppc = per_plane > 0 ? std::min<int64_t>(256, (40 * 1024) / per_plane) / 16 * 16 : 0;
+        if (!in_splat && n_fill == 1 && es <= 8 && ppc >= 16 && n_planes >= 1 && n_planes * plane_out == n_out && plane_in >= 1 &&
+            aligned16(in, out)) {
+            const uint32_t in_vecs = uint32_t((ppc * plane_in * es + 15) / 16), out_vecs = uint32_t((ppc * plane_out * es + 15) / 16);
+            const size_t smem = size_t(in_vecs + out_vecs) * 16;
+            const int64_t n_chunks = (n_planes + ppc - 1) / ppc;
+            const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (200 * 1024) / int64_t(smem + 1024)));
+            const unsigned blocks = unsigned(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * per_sm));
+            const uint8_t* src = static_cast<const uint8_t*>(in);
+            uint8_t* dst = static_cast<uint8_t*>(out);
+            const uint8_t* fv = static_cast<const uint8_t*>(d_fill);
+#define VF_DIL_PLANES(ES_)                                                                                                           \
+    k_expand_dilated_planes<ES_><<<blocks, kBlock, smem, ctx->stream>>>(src, dst, n_planes, uint32_t(ppc), uint32_t(plane_in),          \
+                                                                      uint32_t(plane_out), uint32_t(kx), uint32_t(dkx), uint32_t(dil_y), \
+                                                                      uint32_t(dil_x), fv)
+            switch (es) {
+            case 1: VF_DIL_PLANES(1); break;
+            case 2: VF_DIL_PLANES(2); break;
+            case 4: VF_DIL_PLANES(4); break;
+            default: VF_DIL_PLANES(8); break;
+            }
+#undef VF_DIL_PLANES
+            post_launch(ctx);
+            return;
+        }
+    }
     constexpr int64_t kMaxPlane = 8192;  // table entries (32 KiB of shared memory)
     if (es < 16 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && dky * dkx <= kMaxPlane) {
         const int64_t n_steps = (n_out * es + 15) / 16;
