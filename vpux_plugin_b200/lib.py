@@ -81,8 +81,8 @@ def infer_type(base_type, is_splat, transforms, n, params_cap=1 << 16):
     """vf_infer_type (pure host; needs no device)."""
     out = abi.TensorType()
     osplat = C.c_int(0)
-    sb = np.zeros(params_cap, np.float64)
-    zb = np.zeros(params_cap, np.int64)
+    sb = np.empty(params_cap, np.float64)  # the library writes what the result type uses
+    zb = np.empty(params_cap, np.int64)
     nbytes = C.c_uint64(0)
     err = C.create_string_buffer(512)
     bt = base_type.pod()
@@ -108,8 +108,8 @@ def optimize_transforms(base_type, transforms, n, params_cap=1 << 16):
     """vf_optimize_transforms (pure host): returns (ctypes array of abi.Transform, count, keepalive)."""
     out = (abi.Transform * max(n, 1))()
     n_out = C.c_int(0)
-    sb = np.zeros(params_cap, np.float64)
-    zb = np.zeros(params_cap, np.int64)
+    sb = np.empty(params_cap, np.float64)  # the library writes what the result type uses
+    zb = np.empty(params_cap, np.int64)
     err = C.create_string_buffer(512)
     bt = base_type.pod()
     st = raw().vf_optimize_transforms(C.byref(bt), transforms, n, out, max(n, 1), C.byref(n_out), _ptr(sb), _ptr(zb),
@@ -178,8 +178,8 @@ class Library:
 
     def fold(self, content, transforms, n, dst, dst_bytes, params_cap=1 << 16, dst_mem_kind=abi.VF_MEM_HOST):
         out = abi.TensorType()
-        sb = np.zeros(params_cap, np.float64)
-        zb = np.zeros(params_cap, np.int64)
+        sb = np.empty(params_cap, np.float64)  # the library writes what the result type uses
+        zb = np.empty(params_cap, np.int64)
         written = C.c_uint64(0)
         err = self._err()
         st = self.lib.vf_fold(self.ctx, C.byref(content), transforms, n, _ptr(dst), C.c_uint64(dst_bytes),
@@ -391,8 +391,8 @@ class Folder:
 
     def fold(self, content, transforms, n, dst, dst_bytes, params_cap=1 << 16, dst_mem_kind=abi.VF_MEM_HOST, base_id=0):
         out = abi.TensorType()
-        sb = np.zeros(params_cap, np.float64)
-        zb = np.zeros(params_cap, np.int64)
+        sb = np.empty(params_cap, np.float64)  # the library writes what the result type uses
+        zb = np.empty(params_cap, np.int64)
         written = C.c_uint64(0)
         hit = C.c_int(0)
         err = C.create_string_buffer(512)
