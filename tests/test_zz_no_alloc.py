@@ -7,6 +7,7 @@ a different shape and sparsity pattern than the first: stale counts or offsets w
 Collected last (file name) so that a failure here cannot hide any other test under `pytest -x`.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -116,11 +117,14 @@ def test_noalloc_requests_no_device_memory_and_handles_the_limit(gpu):
     m1.zero_()
     torch.cuda.synchronize()
 
+    # the device-wide figure only means something while no other process works on the GPU (test workers in parallel do)
+    alone = "PYTEST_XDIST_WORKER" not in os.environ
+
     def call(*a):  # free device memory right before and right after the call (no torch work in between)
         free0 = torch.cuda.mem_get_info(0)[0]
         r = _noalloc(gpu, *a)
         torch.cuda.synchronize()
-        assert torch.cuda.mem_get_info(0)[0] == free0, "a call of vf_sparsify_noalloc changed the free device memory"
+        assert not alone or torch.cuda.mem_get_info(0)[0] == free0, "a call of vf_sparsify_noalloc changed the free device memory"
         return r
 
     st, w, msg = call(xd.data_ptr(), abi.VF_DT_U8, oc, work, d1.data_ptr(), cap, None, 0, None)  # data only
