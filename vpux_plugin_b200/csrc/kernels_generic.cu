@@ -961,116 +961,6 @@ __global__ void __launch_bounds__(256) k_transpose_slices(const uint8_t* __restr
     }
 }
 
-// The transposition of dim a (innermost on the output side) with dim b (source stride 1) for slices that do not fit
-// shared memory: a chunk is up to 64 rows of the source by 240 bytes along b. Source rows start at any element, so a
-// row's segment arrives as the (at most 16) aligned 16-byte vectors that cover it, by asynchronous copies into a
-// ring of three buffers per persistent CTA; consecutive chunks of a CTA's walk lie next to each other along the
-// rows. A row keeps its lead (the bytes in front of its segment) and its vectors sit at position c ^ key with
-// key = (row / VE) & 7: the rows a warp gathers from in one instruction differ in row / VE, so their vectors lie
-// in different banks. Output: 16-byte vectors of VE consecutive a, the lanes of a warp covering whole output rows
-// next to each other.
-struct ColsGeom {
-    uint32_t ea, eb;             // extents of a and b
-    uint32_t tiles_a, tiles_b;
-    int64_t sa;                  // source stride of a (elements)
-    int64_t dst_stride_b;        // output stride of b (elements)
-    int n_other;                 // the remaining dims, innermost first
-    int64_t other_shape[VF_MAX_RANK], other_src[VF_MAX_RANK], other_dst[VF_MAX_RANK];
-};
-constexpr int kColsRows = 64, kColsBytes = 240, kColsStages = 3;
-template <int ES>
-__global__ void __launch_bounds__(256) k_transpose_cols(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, ColsGeom g,
-                                                        int64_t n_chunks, int64_t total_bytes) {
-    constexpr uint32_t VE = 16 / ES, TB = kColsBytes / ES;
-    __shared__ uint4 ring[kColsStages][kColsRows * 16];
-    using T = typename ElemOf<ES>::T;
-
-    struct Chunk {
-        int64_t first;   // byte offset of element (a0, b0) of the slice in the source
-        int64_t dst0;    // element offset of output element (b0, a0)
-        uint32_t ta, tb; // rows and columns of the chunk
-    };
-    auto locate = [&](int64_t idx) -> Chunk {
-        Chunk c;
-        int64_t rem = idx;
-        const uint32_t tb_i = uint32_t(rem % g.tiles_b);
-        rem /= g.tiles_b;
-        const uint32_t ta_i = uint32_t(rem % g.tiles_a);
-        rem /= g.tiles_a;
-        int64_t src0 = 0, dst0 = 0;
-        for (int k = 0; k < g.n_other; ++k) {
-            const int64_t q = rem / g.other_shape[k];
-            const int64_t cc = rem - q * g.other_shape[k];
-            rem = q;
-            src0 += cc * g.other_src[k];
-            dst0 += cc * g.other_dst[k];
-        }
-        const uint32_t a0 = ta_i * kColsRows, b0 = tb_i * TB;
-        c.ta = min(uint32_t(kColsRows), g.ea - a0);
-        c.tb = min(TB, g.eb - b0);
-        c.first = (src0 + int64_t(a0) * g.sa + b0) * ES;
-        c.dst0 = dst0 + int64_t(b0) * g.dst_stride_b + a0;
-        return c;
-    };
-    const int64_t row_bytes = g.sa * ES;
-    auto fetch = [&](int64_t idx, int slot) {
-        if (idx < n_chunks) {
-            const Chunk c = locate(idx);
-            const uint32_t seg = c.tb * ES;
-            for (uint32_t i = threadIdx.x; i < c.ta * 16u; i += blockDim.x) {
-                const uint32_t r = i >> 4, v = i & 15u;
-                const int64_t gb = c.first + int64_t(r) * row_bytes;
-                const uint32_t lead = uint32_t(gb & 15);
-                if (v * 16 < lead + seg) {
-                    const int64_t p = (gb & ~int64_t(15)) + int64_t(v) * 16;
-                    const int64_t left = total_bytes - p;  // the last vector of the buffer may be cut short
-                    cp_async16_part(&ring[slot][r * 16 + (v ^ ((r / VE) & 7u))], in + p, left >= 16 ? 16 : int(left));
-                }
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-
-    int64_t idx = blockIdx.x;
-    if (idx >= n_chunks) return;
-    const int64_t stride = gridDim.x;
-#pragma unroll
-    for (int st = 0; st < kColsStages - 1; ++st) fetch(idx + st * stride, st);
-    int cur = 0;
-    for (; idx < n_chunks; idx += stride) {
-        int ahead = cur + kColsStages - 1;
-        if (ahead >= kColsStages) ahead -= kColsStages;
-        fetch(idx + (kColsStages - 1) * stride, ahead);
-        asm volatile("cp.async.wait_group %0;" ::"n"(kColsStages - 1) : "memory");
-        __syncthreads();  // every thread's copies of this chunk have landed
-        const Chunk c = locate(idx);
-        const uint8_t* tb8 = reinterpret_cast<const uint8_t*>(ring[cur]);
-        const uint32_t lead0 = uint32_t(c.first & 15), lead_step = uint32_t(row_bytes & 15);
-        const uint32_t nab = c.ta / VE, n_out = nab * c.tb;
-        const uint32_t step_b = blockDim.x / nab, step_a = blockDim.x - step_b * nab;
-        uint32_t ib = threadIdx.x / nab, iab = threadIdx.x - ib * nab;
-        for (uint32_t v = threadIdx.x; v < n_out; v += blockDim.x) {
-            const uint32_t key4 = (iab & 7u) << 4;
-            __align__(16) T e[VE];
-#pragma unroll
-            for (uint32_t k = 0; k < VE; ++k) {
-                const uint32_t r = iab * VE + k;
-                const uint32_t t = ((lead0 + r * lead_step) & 15u) + ib * ES;  // byte offset inside the row's cover
-                e[k] = *reinterpret_cast<const T*>(tb8 + r * 256u + (t ^ key4));
-            }
-            *reinterpret_cast<uint4*>(out + (c.dst0 + int64_t(ib) * g.dst_stride_b + iab * VE) * ES) = *reinterpret_cast<const uint4*>(e);
-            iab += step_a;
-            ib += step_b;
-            if (iab >= nab) {
-                iab -= nab;
-                ++ib;
-            }
-        }
-        __syncthreads();  // this buffer is the target of the copy issued in the next iteration
-        if (++cur == kColsStages) cur = 0;
-    }
-}
-
 // SubView of 1- / 2- / 4-bit storage — subByteTransform, attributes/subview.cpp:20-160: elements are gathered bit
 // field by bit field, low bits first. One thread per output byte (its 8 / BITS elements), so no two threads
 // touch the same byte.
@@ -2158,40 +2048,6 @@ void launch_permute(vf_ctx* ctx, const void* in, void* out, const Geom& g0, int 
     }
             if (es == 1) VF_SLICES(1) else if (es == 2) VF_SLICES(2) else VF_SLICES(4)
 #undef VF_SLICES
-            post_launch(ctx);
-            return;
-        }
-    }
-    if (es <= 4 && b >= 0 && g.src_stride[a] != 1 && (g.out_shape[a] * es) % 16 == 0 && aligned16(in, out) &&
-        g.out_shape[a] < (int64_t(1) << 31) && g.out_shape[b] < (int64_t(1) << 31)) {
-        // output rows of whole 16-byte vectors: chunks of 64 rows by 240 bytes through a ring of shared-memory buffers
-        ColsGeom cg{};
-        cg.ea = uint32_t(g.out_shape[a]);
-        cg.eb = uint32_t(g.out_shape[b]);
-        cg.tiles_a = uint32_t((g.out_shape[a] + kColsRows - 1) / kColsRows);
-        cg.tiles_b = uint32_t((g.out_shape[b] * es + kColsBytes - 1) / kColsBytes);
-        cg.sa = g.src_stride[a];
-        int64_t dst_stride = 1, src_elems = 1, n_chunks = int64_t(cg.tiles_a) * cg.tiles_b;
-        for (int d = g.rank - 1; d >= 0; --d) {
-            if (d == b) cg.dst_stride_b = dst_stride;
-            if (d != a && d != b) {
-                cg.other_shape[cg.n_other] = g.out_shape[d];
-                cg.other_src[cg.n_other] = g.src_stride[d];
-                cg.other_dst[cg.n_other] = dst_stride;
-                ++cg.n_other;
-                n_chunks *= g.out_shape[d];
-            }
-            dst_stride *= g.out_shape[d];
-            src_elems += (g.out_shape[d] - 1) * g.src_stride[d];
-        }
-        if ((cg.dst_stride_b * es) % 16 == 0 && n_chunks < (int64_t(1) << 40)) {
-            const int64_t total_bytes = src_elems * es;
-            const unsigned blocks = unsigned(std::min<int64_t>(n_chunks, int64_t(ctx->sm_count) * 4));
-            const uint8_t* src = static_cast<const uint8_t*>(in);
-            uint8_t* dst = static_cast<uint8_t*>(out);
-            if (es == 1) k_transpose_cols<1><<<blocks, kBlock, 0, ctx->stream>>>(src, dst, cg, n_chunks, total_bytes);
-            else if (es == 2) k_transpose_cols<2><<<blocks, kBlock, 0, ctx->stream>>>(src, dst, cg, n_chunks, total_bytes);
-            else k_transpose_cols<4><<<blocks, kBlock, 0, ctx->stream>>>(src, dst, cg, n_chunks, total_bytes);
             post_launch(ctx);
             return;
         }
