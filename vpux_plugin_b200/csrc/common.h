@@ -232,6 +232,12 @@ struct vf_ctx {
     char* table_host = nullptr;
     char* table_dev = nullptr;
     size_t table_used = 0;
+    // The tables travel on a stream of their own, so that an upload does not queue behind the kernels already on
+    // `stream`; the kernel that reads a table waits for `table_ev`. `table_unchecked`: uploads have been issued
+    // since flags_check last waited for the stream (an area restarted in that state is fenced first).
+    cudaStream_t table_stream = nullptr;
+    cudaEvent_t table_ev = nullptr;
+    bool table_unchecked = false;
     int* d_flags = nullptr;  // device error flags (see VF_FLAG_* in device_utils.cuh)
     int* h_flags = nullptr;  // pinned mirror
     bool flags_dirty = false;  // the device flags may be non-zero (a call found something or ended early)

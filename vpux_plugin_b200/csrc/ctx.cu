@@ -92,11 +92,21 @@ const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallb
         ctx->table_used = 0;
     }
     if (ctx->table_host && ctx->table_used + need <= vf_ctx::kTableBytes) {
+        if (ctx->table_used == 0 && ctx->table_unchecked) {
+            // the area starts over although nobody waited for the kernels that read it (a call that ended in an
+            // error): they have to finish before their tables are overwritten
+            VF_CUDA(cudaStreamSynchronize(ctx->main_stream));
+            VF_CUDA(cudaStreamSynchronize(ctx->lane_stream));
+            ctx->table_unchecked = false;
+        }
         char* h = ctx->table_host + ctx->table_used;
         char* d = ctx->table_dev + ctx->table_used;
         ctx->table_used += need;
         std::memcpy(h, src, bytes);
-        VF_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        VF_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, ctx->table_stream));
+        VF_CUDA(cudaEventRecord(ctx->table_ev, ctx->table_stream));
+        VF_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->table_ev, 0));
+        ctx->table_unchecked = true;
         return d;
     }
     fallback = DBuf(ctx, bytes);
@@ -117,6 +127,7 @@ void flags_check(vf_ctx* ctx) {
     VF_CUDA(cudaStreamSynchronize(ctx->stream));
     VF_CUDA(cudaGetLastError());
     ctx->deferred = false;  // everything enqueued so far has finished and is being checked now
+    ctx->table_unchecked = false;
     // deferred vf_sparsify_batch calls: their sizes have arrived
     const vf_sparsify_job* too_small = nullptr;
     for (const vf_ctx::PendingSizes& ps : ctx->pending_sizes) {
@@ -187,6 +198,8 @@ int vf_ctx_create(int device, const vf_options* opts, void* external_stream, vf_
             VF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->table_host), vf_ctx::kTableBytes));
             VF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->sizes_host), vf_ctx::kSizesCap * sizeof(int64_t)));
             VF_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->table_dev), vf_ctx::kTableBytes));
+            VF_CUDA(cudaStreamCreateWithFlags(&c->table_stream, cudaStreamNonBlocking));
+            VF_CUDA(cudaEventCreateWithFlags(&c->table_ev, cudaEventDisableTiming));
             // scratch pool of this context: freed scratch stays cached in it instead of going back to the driver on
             // every synchronisation; the device's default pool (and whoever else uses it) is left as it is
             cudaMemPoolProps props{};
@@ -218,6 +231,11 @@ void vf_ctx_destroy(vf_ctx* c) {
         if (c->staging[k]) cudaFreeHost(c->staging[k]);
         if (c->staging_ev[k]) cudaEventDestroy(c->staging_ev[k]);
     }
+    if (c->table_stream) {
+        cudaStreamSynchronize(c->table_stream);
+        cudaStreamDestroy(c->table_stream);
+    }
+    if (c->table_ev) cudaEventDestroy(c->table_ev);
     if (c->table_host) cudaFreeHost(c->table_host);
     if (c->sizes_host) cudaFreeHost(c->sizes_host);
     if (c->table_dev) cudaFree(c->table_dev);

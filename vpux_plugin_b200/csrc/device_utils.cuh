@@ -2,6 +2,7 @@
 // Every floating-point step that must match the host bit for bit uses a round-to-nearest intrinsic so that
 // no fused multiply-add is formed (the library is also compiled with -fmad=false).
 #pragma once
+#include <utility>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -27,6 +28,36 @@ enum : int {
 __device__ __forceinline__ void set_flag(int* flags, int slot) {
     if (flags) atomicOr(&flags[slot], 1);
 }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------
+// The short kernels of a batch call follow one another on a stream, each reading what the one before wrote. A
+// kernel launched through launch_chained() (below) may be brought onto the SMs while the kernel before it is
+// still draining: chain_enter() is the first statement of every thread of such a kernel. It lets the kernel after
+// this one do the same, and then waits until the kernel before this one has completed and its writes are
+// visible. Without a chained launch on either side both instructions do nothing.
+__device__ __forceinline__ void chain_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+#ifdef __CUDACC__
+// Launches `kernel` so that it may overlap the tail of the kernel enqueued before it on `st`; the kernel's first
+// statement must be chain_enter().
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
 
 // ---- fp16 / bf16 ------------------------------------------------------------------------------------
 // float16::float16(float) (src/vpux_utils/src/core/type/float16.cpp:30-108). An exhaustive sweep of all 2^32

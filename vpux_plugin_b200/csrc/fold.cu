@@ -1608,8 +1608,7 @@ int vf_weights_table_batch(vf_ctx* ctx, vf_weights_table_job* jobs, int njobs, i
                 throw;
             }
         }
-        launch_offsets_batch(ctx, offs);
-        launch_weights_table_batch(ctx, tabs);
+        launch_weights_table_batch(ctx, tabs, &offs);
         for (int j = 0; j < njobs; ++j) out_flush(ctx, jobs[j].table, out_mem_kind, size_t(jobs[j].desc.oc) * 16, stage[j]);
         scope.may_defer = out_mem_kind == VF_MEM_DEVICE;
         scope.finish();

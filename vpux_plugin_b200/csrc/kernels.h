@@ -121,7 +121,8 @@ struct TableArgs {
 };
 void launch_weights_table(vf_ctx* ctx, const TableArgs& a, int32_t* d_table);
 // All tables of `tabs` (each with its d_table) in one launch over a device copy of the list.
-void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs);
+// `offsets_first`: prefix-sum jobs whose results the tables read; their kernel is launched right before the tables'.
+void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs, const std::vector<OffsetsJob>* offsets_first = nullptr);
 
 // Reverse: every run of `run` consecutive elements reversed; Broadcast: every block of `after` elements written
 // `factor` times; ExpandDilated: OIYX taps spread by the dilations, the gaps filled from `d_fill` (n_fill == 1:

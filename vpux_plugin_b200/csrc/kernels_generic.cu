@@ -1290,6 +1290,7 @@ __global__ void k_weights_table(TableArgs a, int32_t* __restrict__ table, int* f
 
 // Many tables per launch: thread u handles row u - unit_begin of the table whose range holds u.
 __global__ void k_weights_table_batch(const TableArgs* __restrict__ tabs, int n, int64_t total, int* flags) {
+    chain_enter();
     const int64_t u = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (u >= total) return;
     int lo = 0, hi = n - 1;
@@ -2240,8 +2241,11 @@ void launch_unpack_subbyte(vf_ctx* ctx, const uint8_t* in, uint8_t* out, int64_t
     }
 }
 
-void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
-    if (tabs.empty()) return;
+void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs, const std::vector<OffsetsJob>* offsets_first) {
+    if (tabs.empty()) {
+        if (offsets_first) launch_offsets_batch(ctx, *offsets_first);
+        return;
+    }
     int64_t total = 0;
     for (auto& t : tabs) {
         t.unit_begin = total;
@@ -2249,8 +2253,10 @@ void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs) {
     }
     DBuf d;
     const TableArgs* d_tabs = static_cast<const TableArgs*>(upload_table(ctx, tabs.data(), tabs.size() * sizeof(TableArgs), d));
-    k_weights_table_batch<<<int((total + 127) / 128), 128, 0, ctx->stream>>>(d_tabs, int(tabs.size()), total, ctx->d_flags);
-    post_launch(ctx);
+    // both job tables are on their way before the first of the two kernels, so that nothing stands between them
+    if (offsets_first) launch_offsets_batch(ctx, *offsets_first);
+    VF_CUDA(launch_chained(k_weights_table_batch, int((total + 127) / 128), 128, 0, ctx->stream, d_tabs, int(tabs.size()), total, ctx->d_flags));
+    ctx->launches += 1;
 }
 
 void launch_relocate(vf_ctx* ctx, const int32_t* in, int32_t* out, const RelocateArgs& a) {

@@ -114,6 +114,7 @@ __device__ __forceinline__ int scan_row_scalar(const SparseJob& J, int64_t c, in
 
 __global__ void __launch_bounds__(kWarps * 32) k_sparse_scan_batch(const SparseJob* __restrict__ jobs, int njobs,
                                                                    int64_t total_units) {
+    chain_enter();
     const int lane = threadIdx.x & 31;
     const int64_t warp = int64_t(blockIdx.x) * kWarps + (threadIdx.x >> 5);
     const int64_t nwarps = int64_t(gridDim.x) * kWarps;
@@ -183,6 +184,7 @@ __device__ __forceinline__ void block_offsets(const int64_t* __restrict__ counts
 
 __global__ void __launch_bounds__(1024) k_sparse_offsets_batch(const SparseJob* __restrict__ jobs,
                                                                int64_t* __restrict__ totals) {
+    chain_enter();
     const SparseJob J = jobs[blockIdx.x];
     if (!J.offsets) {
         if (threadIdx.x == 0) totals[blockIdx.x] = 0;
@@ -192,6 +194,7 @@ __global__ void __launch_bounds__(1024) k_sparse_offsets_batch(const SparseJob* 
 }
 
 __global__ void __launch_bounds__(1024) k_offsets_batch(const OffsetsJob* __restrict__ jobs) {
+    chain_enter();
     const OffsetsJob J = jobs[blockIdx.x];
     block_offsets(J.counts, J.oc, J.es, J.offsets, nullptr);
 }
@@ -289,6 +292,7 @@ __device__ __forceinline__ void compact_row_scalar(const SparseJob& J, int64_t c
 
 __global__ void __launch_bounds__(kWarps * 32) k_sparse_compact_batch(const SparseJob* __restrict__ jobs, int njobs,
                                                                       int64_t total_units, int* flags) {
+    chain_enter();
     __shared__ uint4 stage_all[kWarps][34];
     const int lane = threadIdx.x & 31;
     uint4* stage = stage_all[threadIdx.x >> 5];
@@ -330,14 +334,11 @@ void launch_sparsify_batch(vf_ctx* ctx, std::vector<SparseJob>& jobs, int64_t* d
     const SparseJob* d_jobs = static_cast<const SparseJob*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(SparseJob), table));
     const int grid = int(std::min<int64_t>((units + kWarps - 1) / kWarps, int64_t(ctx->sm_count) * 8));
     const int njobs = int(jobs.size());
-    k_sparse_scan_batch<<<grid, kWarps * 32, 0, ctx->stream>>>(d_jobs, njobs, units);
-    VF_CUDA(cudaGetLastError());
-    k_sparse_offsets_batch<<<njobs, 1024, 0, ctx->stream>>>(d_jobs, d_totals);
-    VF_CUDA(cudaGetLastError());
+    VF_CUDA(launch_chained(k_sparse_scan_batch, grid, kWarps * 32, 0, ctx->stream, d_jobs, njobs, units));
+    VF_CUDA(launch_chained(k_sparse_offsets_batch, njobs, 1024, 0, ctx->stream, d_jobs, d_totals));
     ctx->launches += 2;
     if (any_data) {
-        k_sparse_compact_batch<<<grid, kWarps * 32, 0, ctx->stream>>>(d_jobs, njobs, units, ctx->d_flags);
-        VF_CUDA(cudaGetLastError());
+        VF_CUDA(launch_chained(k_sparse_compact_batch, grid, kWarps * 32, 0, ctx->stream, d_jobs, njobs, units, ctx->d_flags));
         ctx->launches += 1;
     }
 }
@@ -346,8 +347,7 @@ void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs) {
     if (jobs.empty()) return;
     DBuf d;
     const OffsetsJob* d_jobs = static_cast<const OffsetsJob*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(OffsetsJob), d));
-    k_offsets_batch<<<int(jobs.size()), 1024, 0, ctx->stream>>>(d_jobs);
-    VF_CUDA(cudaGetLastError());
+    VF_CUDA(launch_chained(k_offsets_batch, int(jobs.size()), 1024, 0, ctx->stream, d_jobs));
     ctx->launches += 1;
 }
 
