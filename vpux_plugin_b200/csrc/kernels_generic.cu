@@ -1291,12 +1291,21 @@ __global__ void k_weights_table(TableArgs a, int32_t* __restrict__ table, int* f
 // Many tables per launch: thread u handles row u - unit_begin of the table whose range holds u.
 __global__ void k_weights_table_batch(const TableArgs* __restrict__ tabs, int n, int64_t total, int* flags) {
     chain_enter();
+    // the tables' first rows, copied into shared memory once per CTA: the search below is a chain of dependent
+    // loads, each an L2 round trip when it runs on the table in device memory
+    constexpr int kStaged = 512;
+    __shared__ int64_t begins[kStaged];
+    const bool staged = n <= kStaged;
+    if (staged) {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) begins[i] = tabs[i].unit_begin;
+        __syncthreads();
+    }
     const int64_t u = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (u >= total) return;
     int lo = 0, hi = n - 1;
     while (lo < hi) {  // last table whose unit_begin <= u
         const int mid = (lo + hi + 1) >> 1;
-        if (tabs[mid].unit_begin <= u) lo = mid;
+        if ((staged ? begins[mid] : tabs[mid].unit_begin) <= u) lo = mid;
         else hi = mid - 1;
     }
     const TableArgs a = tabs[lo];

@@ -24,9 +24,29 @@ template <> struct ElemT<1> { using T = uint8_t; };
 template <> struct ElemT<2> { using T = uint16_t; };
 template <> struct ElemT<4> { using T = uint32_t; };
 
-__device__ __forceinline__ int find_sparse_job(const SparseJob* __restrict__ jobs, int njobs, int64_t unit) {
+// The search for a unit's job is a chain of dependent loads: on the job table in device memory each step costs an
+// L2 round trip, which for rows of a few hundred bytes is as long as reading the row. A CTA therefore copies the
+// jobs' first units into shared memory once (tables of up to kStagedJobs entries) and searches there.
+constexpr int kStagedJobs = 512;
+
+__device__ __forceinline__ void stage_unit_begins(const SparseJob* __restrict__ jobs, int njobs, int64_t* begins) {
+    if (njobs <= kStagedJobs) {
+        for (int i = threadIdx.x; i < njobs; i += blockDim.x) begins[i] = jobs[i].unit_begin;
+        __syncthreads();
+    }
+}
+
+__device__ __forceinline__ int find_sparse_job(const SparseJob* __restrict__ jobs, const int64_t* begins, int njobs, int64_t unit) {
     int lo = 0, hi = njobs - 1;
-    while (lo < hi) {  // last job whose unit_begin <= unit
+    if (njobs <= kStagedJobs) {
+        while (lo < hi) {  // last job whose unit_begin <= unit
+            const int mid = (lo + hi + 1) >> 1;
+            if (begins[mid] <= unit) lo = mid;
+            else hi = mid - 1;
+        }
+        return lo;
+    }
+    while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
         if (jobs[mid].unit_begin <= unit) lo = mid;
         else hi = mid - 1;
@@ -115,11 +135,13 @@ __device__ __forceinline__ int scan_row_scalar(const SparseJob& J, int64_t c, in
 __global__ void __launch_bounds__(kWarps * 32) k_sparse_scan_batch(const SparseJob* __restrict__ jobs, int njobs,
                                                                    int64_t total_units) {
     chain_enter();
+    __shared__ int64_t begins[kStagedJobs];
+    stage_unit_begins(jobs, njobs, begins);
     const int lane = threadIdx.x & 31;
     const int64_t warp = int64_t(blockIdx.x) * kWarps + (threadIdx.x >> 5);
     const int64_t nwarps = int64_t(gridDim.x) * kWarps;
     for (int64_t u = warp; u < total_units; u += nwarps) {
-        const SparseJob J = jobs[find_sparse_job(jobs, njobs, u)];
+        const SparseJob J = jobs[find_sparse_job(jobs, begins, njobs, u)];
         const int64_t c = u - J.unit_begin;
         const float fv = sparse_value_as_float(J.dt, J.sv);
         const uint32_t iv_rep = uint32_t(uint8_t(J.sv)) * 0x01010101u;
@@ -294,12 +316,14 @@ __global__ void __launch_bounds__(kWarps * 32) k_sparse_compact_batch(const Spar
                                                                       int64_t total_units, int* flags) {
     chain_enter();
     __shared__ uint4 stage_all[kWarps][34];
+    __shared__ int64_t begins[kStagedJobs];
+    stage_unit_begins(jobs, njobs, begins);
     const int lane = threadIdx.x & 31;
     uint4* stage = stage_all[threadIdx.x >> 5];
     const int64_t warp = int64_t(blockIdx.x) * kWarps + (threadIdx.x >> 5);
     const int64_t nwarps = int64_t(gridDim.x) * kWarps;
     for (int64_t u = warp; u < total_units; u += nwarps) {
-        const SparseJob J = jobs[find_sparse_job(jobs, njobs, u)];
+        const SparseJob J = jobs[find_sparse_job(jobs, begins, njobs, u)];
         if (!J.data) continue;
         const int64_t c = u - J.unit_begin;
         const float fv = sparse_value_as_float(J.dt, J.sv);
