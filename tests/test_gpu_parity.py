@@ -283,6 +283,42 @@ def test_sparsify_batch(gpu, oracle, density):
             assert np.array_equal(gc, oc_), j
 
 
+@pytest.mark.parametrize("fill", [0, 1, 0x7F, 0x80, 0xC8, 0xFF])
+def test_sparsify_batch_every_byte_value(gpu, oracle, fill):
+    """8-bit rows that hold every byte value next to the sparsify value `fill`, in runs of every length from 0 to
+    40 kept and dropped elements: the mask arithmetic on whole words and the word-wise compaction see every
+    combination of kept bytes inside a word and every alignment of the compacted run."""
+    rng = np.random.default_rng(fill + 11)
+    oc, work = 24, 4608
+    x = np.empty((oc, work), np.uint8)
+    for r in range(oc):
+        row, at = [], 0
+        while at < work:
+            keep_n, drop_n = int(rng.integers(0, 41)), int(rng.integers(0, 41))
+            vals = rng.integers(0, 256, keep_n)
+            vals[vals == fill] = (fill + 1 + r) % 256 if (fill + 1 + r) % 256 != fill else (fill + 2) % 256
+            row += [vals, np.full(drop_n, fill)]
+            at += keep_n + drop_n
+        x[r] = np.concatenate(row)[:work]
+    x[0, :256] = np.arange(256)  # every value once, `fill` among them
+    shape = [oc, work // 9, 3, 3]
+    elem = U8 if fill == 0 else Elem.uniform(U8, F16, 0.25, fill, 0, 255)
+    c, k = abi.make_content(TType(shape, elem), x.reshape(-1), storage_dtype=U8)
+    row_bytes = (work + 127) // 128 * 16
+    cap = oc * work + 16 * oc
+    od, om, ocnt = np.zeros(cap, np.uint8), np.zeros(oc * row_bytes, np.uint8), np.zeros(oc, np.int64)
+    w = oracle.sparsify(c, od, om, ocnt)
+    gd, gm, gc = np.full(cap, 0xAB, np.uint8), np.full(oc * row_bytes, 0xAB, np.uint8), np.full(oc, -1, np.int64)
+    jobs = (abi.SparsifyJob * 1)()
+    jobs[0].content, jobs[0].data, jobs[0].data_bytes = c, gd.ctypes.data, cap
+    jobs[0].map, jobs[0].map_bytes, jobs[0].counts = gm.ctypes.data, gm.nbytes, gc.ctypes.data
+    gpu.sparsify_batch(jobs)
+    assert jobs[0].data_written == w
+    assert np.array_equal(gc, ocnt)
+    assert np.array_equal(gm, om)
+    assert np.array_equal(gd[:w], od[:w])
+
+
 def test_sparsify_batch_buffer_too_small(gpu):
     x = np.ones([4, 16, 1, 1], np.int8)
     c, _k = abi.make_content(TType([4, 16, 1, 1], I8), x)
