@@ -900,6 +900,103 @@ def test_pipelined_fold_calls_defer_and_report_at_synchronisation(oracle):
     lib.close()
 
 
+def test_pipelined_steps_run_through_the_job_table_area_many_times(gpu, oracle):
+    """VF_OPT_ASYNC, 700 steps of quantize-fold + Sparsify/GetSparsityMap + weights tables of twelve convolution
+    weights without a synchronisation in between: the job tables of the batched launches go through the context's
+    1 MiB area about five times (it starts over only after the calls that still read it have finished), and the
+    queue of deferred compressed sizes fills up once. The outputs of the last step equal those of a single step,
+    which are checked against the oracle."""
+    import torch
+    from vpux_plugin_b200.lib import Library
+    lib = Library(device=0, pipelined=True)
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(77)
+    shapes = [[32, 16, 3, 3], [64, 64, 1, 1], [16, 3, 7, 7], [48, 32, 3, 3], [128, 256, 1, 1], [8, 16, 1, 1],
+              [24, 64, 3, 3], [256, 128, 1, 1], [40, 16, 3, 3], [64, 512, 1, 1], [16, 32, 1, 1], [96, 48, 3, 3]]
+    n_t = len(shapes)
+    qjobs, sjobs, tjobs = (abi.QuantJob * n_t)(), (abi.SparsifyJob * n_t)(), (abi.WeightsTableJob * n_t)()
+    spec = wl.spec_i8_sym()
+    keep, outs, xs = [], [], []
+    for j, shape in enumerate(shapes):
+        x = (rng.standard_normal(shape) * 0.05 * (rng.random(shape) < 0.5)).astype(np.float16)
+        x[0] = np.abs(x[0]) + 0.01  # one dense channel
+        xs.append(x)
+        ts, oshape = wl.conv_pipeline(shape, pad_ic_to=16 if shape[1] == 3 else None)
+        tr = abi.make_transforms(ts)
+        oc, work = oshape[0], oshape[1] * oshape[2] * oshape[3]
+        src = torch.from_numpy(x.view(np.uint8).reshape(-1)).to(dev)
+        codes = torch.empty(oc * work, dtype=torch.uint8, device=dev)
+        sc = torch.empty(oc, dtype=torch.float64, device=dev)
+        o = abi.QuantOutputs()
+        o.mem_kind, o.scales = abi.VF_MEM_DEVICE, sc.data_ptr()
+        c, k = abi.make_content(TType(shape, F16), None, ptr=src.data_ptr(), nbytes=x.nbytes, mem_kind=abi.VF_MEM_DEVICE)
+        qj = qjobs[j]
+        qj.base, qj.spec, qj.t, qj.n = c, spec, tr, len(ts)
+        qj.dst, qj.dst_bytes, qj.dst_mem_kind, qj.outs = codes.data_ptr(), codes.numel(), abi.VF_MEM_DEVICE, o
+        row = (work + 127) // 128 * 16
+        cap = oc * ((work + 15) // 16 * 16)
+        cc, kc = abi.make_content(TType(list(oshape), I8, abi.ORDER_NHWC), None, ptr=codes.data_ptr(), nbytes=codes.numel(), mem_kind=abi.VF_MEM_DEVICE)
+        data = torch.zeros(cap, dtype=torch.uint8, device=dev)
+        mp = torch.empty(oc * row, dtype=torch.uint8, device=dev)
+        cnt = torch.empty(oc, dtype=torch.int64, device=dev)
+        sj = sjobs[j]
+        sj.content, sj.data, sj.data_bytes = cc, data.data_ptr(), cap
+        sj.map, sj.map_bytes, sj.counts = mp.data_ptr(), oc * row, cnt.data_ptr()
+        bias = torch.from_numpy((rng.standard_normal(oc) * 0.01).astype(np.float32)).to(dev)
+        d, kd = wl.weights_table_desc(oc, np.ones(oc), 0)
+        d.has_bias, d.bias, d.bias_mem_kind = 1, bias.data_ptr(), abi.VF_MEM_DEVICE
+        d.nnz_counts, d.nnz_mem_kind = cnt.data_ptr(), abi.VF_MEM_DEVICE
+        d.sparsity_ptr_base, d.sparsity_ptr_step = 0, row
+        tab = torch.empty(oc * 4, dtype=torch.int32, device=dev)
+        tj = tjobs[j]
+        tj.desc, tj.table = d, tab.data_ptr()
+        tj.weights_scales, tj.scales_mem_kind = sc.data_ptr(), abi.VF_MEM_DEVICE
+        keep += [tr, src, k, ts, kc, kd, bias]
+        outs.append({"codes": codes, "scales": sc, "data": data, "map": mp, "counts": cnt, "table": tab, "oshape": oshape})
+
+    def step():
+        lib.quantize_fold_batch(qjobs)
+        lib.sparsify_batch(sjobs, out_mem_kind=abi.VF_MEM_DEVICE)
+        lib.weights_table_batch(tjobs, out_mem_kind=abi.VF_MEM_DEVICE)
+
+    def snapshot():
+        return [{k: v.cpu().numpy().copy() for k, v in o.items() if k != "oshape"} for o in outs]
+
+    step()
+    lib.synchronize()
+    first = snapshot()
+    sizes = [int(sjobs[j].data_written) for j in range(n_t)]
+    for j, (x, o, f) in enumerate(zip(xs, outs, first)):  # the single step against the oracle
+        oshape = o["oshape"]
+        oc, work = oshape[0], oshape[1] * oshape[2] * oshape[3]
+        ts, _ = wl.conv_pipeline(shapes[j], pad_ic_to=16 if shapes[j][1] == 3 else None)
+        cx, kx = abi.make_content(TType(shapes[j], F16), x)
+        ref_codes, ref_scales = np.zeros(oc * work, np.uint8), np.zeros(oc, np.float64)
+        ro = abi.QuantOutputs()
+        ro.mem_kind, ro.scales = abi.VF_MEM_HOST, ref_scales.ctypes.data
+        assert oracle.quantize_fold(cx, spec, abi.make_transforms(ts), len(ts), ref_codes, oc * work, ro) == oc * work
+        assert np.array_equal(f["codes"], ref_codes), j
+        assert np.array_equal(f["scales"], ref_scales), j
+        q = Elem.per_axis(I8, F16, ref_scales, np.zeros(oc, np.int64), 0, -127, 127)
+        c, k = abi.make_content(TType(list(oshape), q, abi.ORDER_NHWC), f["codes"].view(np.int8), storage_dtype=I8)
+        od, om, ocnt = np.zeros(f["data"].size, np.uint8), np.zeros(f["map"].size, np.uint8), np.zeros(oc, np.int64)
+        w = oracle.sparsify(c, od, om, ocnt)
+        assert w == sizes[j] and np.array_equal(f["data"][:w], od[:w]) and np.array_equal(f["map"], om) and np.array_equal(f["counts"], ocnt), j
+    for o in outs:
+        for k, v in o.items():
+            if k != "oshape":
+                v.fill_(0 if k == "data" else 0x5A if v.dtype == torch.uint8 else 0)
+    torch.cuda.synchronize()
+    for _ in range(700):
+        step()
+    lib.synchronize()
+    for j, (a, b) in enumerate(zip(snapshot(), first)):
+        for k in a:
+            assert np.array_equal(a[k], b[k]), (j, k)
+        assert int(sjobs[j].data_written) == sizes[j]
+    lib.close()
+
+
 def test_weights_table_batch(gpu, oracle):
     """Many tables per call (dense and sparse pointers, with and without bias, 1..2500 channels); weight scales
     either inside the descriptor or as a separate FP64 array; one launch for all rows."""
