@@ -97,8 +97,13 @@ Elem Elem::from(const vf_elem_type& e, bool check_scales) {
         const auto it = tl_checked.find(e.scales);
         if (it != tl_checked.end() && it->second >= e.nparams) return r;
     }
-    for (const double sc : r.scales)
-        if (!(sc > 0.0) || std::isinf(sc)) raise(VF_ERR_INVALID_ARG, "illegal scale: %g", sc);
+    // (counted without a branch so that the loop runs on vector registers: a network's per-channel scales are
+    // tens of thousands of values per batch call)
+    size_t illegal = 0;
+    for (const double sc : r.scales) illegal += size_t(!((sc > 0.0) & (sc < HUGE_VAL)));
+    if (illegal)
+        for (const double sc : r.scales)
+            if (!(sc > 0.0) || std::isinf(sc)) raise(VF_ERR_INVALID_ARG, "illegal scale: %g", sc);
     if (tl_check_depth > 0 && e.nparams > 64) tl_checked[e.scales] = e.nparams;
     return r;
 }
