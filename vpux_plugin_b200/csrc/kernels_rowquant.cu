@@ -1233,48 +1233,64 @@ inline int convv_unit_cost(int64_t cols, int64_t khw, int lanes_per_row) {
     return int(30 + steps * (khw > 0 ? 12 : 8));
 }
 
-// The units of all tensors form one list, each with a cost; a warp takes the units whose cumulative cost starts
-// inside its share [W0, W1) of the total. Its units are consecutive, so it meets a new tensor rarely: the job
-// table is searched once per warp, and a tensor's fields are read once per tensor and warp.
+// The units of all tensors form one list, each with a cost, and the total is cut into kConvvChunksPerWarp equal
+// chunks per warp; a chunk's units are those whose cumulative cost starts inside it. A warp starts with the chunk
+// of its own number and then takes the next free one from a counter (a zeroed word behind the job table), so that
+// the warps end together although the cost is only an estimate. A chunk's units are consecutive: the job is
+// searched once per chunk, in a copy of the jobs' first costs in shared memory, and a tensor's fields are read
+// once per tensor and chunk.
+constexpr int kConvvChunksPerWarp = 2;  // (1: 54.4 us, 2: 51.7, 3: 52.4, 5: 55.5, 8: 61.2 for the 54 ResNet-50 tensors: a chunk costs its search)
+constexpr int kConvvStagedJobs = 512;
+
 template <typename InT>
-__global__ void __launch_bounds__(256, 4) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs, int* flags) {
+__global__ void __launch_bounds__(256, 4) k_convv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int stage_vecs,
+                                                  unsigned int* next_chunk, int* flags) {
     extern __shared__ uint4 smem_u4[];
+    __shared__ int64_t s_work_begin[kConvvStagedJobs];
+    const bool staged = p.njobs <= kConvvStagedJobs;
+    if (staged) {
+        for (int i = threadIdx.x; i < p.njobs; i += blockDim.x) s_work_begin[i] = jobs[i].work_begin;
+        __syncthreads();
+    }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint4* stage = smem_u4 + size_t(wid) * size_t(stage_vecs);  // codes, one byte per element in input order
     const int64_t nwarps = int64_t(gridDim.x) * (blockDim.x >> 5);
-    // warps of one CTA take shares far apart (share = wid * gridDim + blockIdx): a CTA's rows differ in length
-    const int64_t gw = int64_t(wid) * gridDim.x + blockIdx.x;
-    const int64_t W0 = p.total_work / nwarps * gw + min(gw, p.total_work % nwarps);
-    const int64_t W1 = p.total_work / nwarps * (gw + 1) + min(gw + 1, p.total_work % nwarps);
-    if (W0 >= W1) return;
-    int j;
-    {
-        int lo = 0, hi = p.njobs - 1;
-        while (lo < hi) {  // last job whose work_begin <= W0
-            const int mid = (lo + hi + 1) >> 1;
-            if (jobs[mid].work_begin <= W0) lo = mid;
-            else hi = mid - 1;
-        }
-        j = lo;
-    }
+    const int64_t nchunks = nwarps * kConvvChunksPerWarp;
+    const int64_t cw = p.total_work / nchunks, cr = p.total_work % nchunks;
+    // warps of one CTA start far apart (chunk = wid * gridDim + blockIdx): a CTA's rows differ in length
+    int64_t chunk = int64_t(wid) * gridDim.x + blockIdx.x;
+    int j = -1;
     ConvJob J;
-    load_conv_job(jobs, j, p, J);
-    int64_t unit = J.unit_begin + (W0 - J.work_begin + J.unit_cost - 1) / J.unit_cost;
-    bool first = true;
     for (;;) {
-        while (unit >= J.unit_end) {
-            if (++j >= p.njobs) return;
-            load_conv_job(jobs, j, p, J);
+        const int64_t W0 = cw * chunk + min(chunk, cr), W1 = cw * (chunk + 1) + min(chunk + 1, cr);
+        if (W0 < W1) {
+            int lo = 0, hi = p.njobs - 1;
+            while (lo < hi) {  // last job whose work_begin <= W0
+                const int mid = (lo + hi + 1) >> 1;
+                if ((staged ? s_work_begin[mid] : jobs[mid].work_begin) <= W0) lo = mid;
+                else hi = mid - 1;
+            }
+            if (lo != j) load_conv_job(jobs, j = lo, p, J);
+            int64_t unit = J.unit_begin + (W0 - J.work_begin + J.unit_cost - 1) / J.unit_cost;
+            bool first = true;
+            for (;;) {
+                while (unit >= J.unit_end && j + 1 < p.njobs) load_conv_job(jobs, ++j, p, J);
+                if (unit >= J.unit_end) break;
+                const int64_t u = unit - J.unit_begin;
+                if (J.work_begin + u * J.unit_cost >= W1) break;
+                // the rows of the chunk's next unit are on their way into the L2 while this one is worked on (the
+                // first unit's own rows, past the first batch, as well)
+                if (first) convv_prefetch_unit(J, u, lane);
+                first = false;
+                if (unit + 1 < J.unit_end) convv_prefetch_unit(J, u + 1, lane);
+                convv_unit<InT>(J, u, p, stage, stage_vecs, lane, flags);
+                ++unit;
+            }
         }
-        const int64_t u = unit - J.unit_begin;
-        if (J.work_begin + u * J.unit_cost >= W1) return;
-        // the rows of this warp's next unit are on their way into the L2 while this one is worked on (the first
-        // unit's own rows, past the first batch, as well)
-        if (first) convv_prefetch_unit(J, u, lane);
-        first = false;
-        if (unit + 1 < J.unit_end) convv_prefetch_unit(J, u + 1, lane);
-        convv_unit<InT>(J, u, p, stage, stage_vecs, lane, flags);
-        ++unit;
+        unsigned int got = 0;
+        if (lane == 0) got = atomicAdd(next_chunk, 1u);
+        chunk = nwarps + int64_t(__shfl_sync(0xffffffffu, got, 0));
+        if (chunk >= nchunks) return;
     }
 }
 
@@ -1390,7 +1406,7 @@ int rowquant_kind(const RowQuantArgs& a) {
 // kernel. The job table is copied to device memory first.
 void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& jobs) {
     if (jobs.empty()) return;
-    const RowQuantArgs& a0 = jobs[0];
+    const RowQuantArgs a0 = jobs[0];
     LaunchParams p{};
     p.range_mode = a0.range_mode;
     p.qmin = int(a0.qmin);
@@ -1420,9 +1436,11 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         max_out_row = std::max(max_out_row, a.khw > 0 ? a.khw * a.ic_pad : a.cols);
     }
     p.total_units = units;
+    if (kind == 4) jobs.push_back(RowQuantArgs{});  // a zeroed entry behind the table: K_convv's chunk counter
     DBuf table;
     const RowQuantArgs* d_jobs =
             static_cast<const RowQuantArgs*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(RowQuantArgs), table));
+    if (kind == 4) jobs.pop_back();
 
     if (kind == 1) {
         if (a0.in_dt == VF_DT_F16) launch_group_t<__half>(ctx, d_jobs, p, a0.group, a0.pack4 != 0);
@@ -1443,12 +1461,13 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
         const size_t per_sm = std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024)));
         const int64_t blocks = (units + 7) / 8;
         const int grid = int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * int64_t(per_sm)));
+        unsigned int* next_chunk = reinterpret_cast<unsigned int*>(const_cast<RowQuantArgs*>(d_jobs + p.njobs));
         if (a0.in_dt == VF_DT_F16) {
             set_smem(k_convv<__half>, smem);
-            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
+            k_convv<__half><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, next_chunk, ctx->d_flags);
         } else {
             set_smem(k_convv<__nv_bfloat16>, smem);
-            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, ctx->d_flags);
+            k_convv<__nv_bfloat16><<<grid, 256, smem, ctx->stream>>>(d_jobs, p, stage_vecs, next_chunk, ctx->d_flags);
         }
         post_launch(ctx);
     } else if (kind == 3) {
