@@ -828,6 +828,14 @@ def gpu_arm(args, workload):
                 del cc
             del flush
             torch.cuda.empty_cache()
+        if world > 1:
+            # the other ranks sleep on the rendezvous store meanwhile: their preparation of the next block (host
+            # work for 1124 jobs each) would share the host's cores with the calls timed above
+            store = dist.distributed_c10d._get_default_store()
+            if rank == 0:
+                store.set("small_configs_done", "1")
+            else:
+                store.wait(["small_configs_done"])
         # the 70B-shaped set by output-channel slabs: every rank folds its slab(s)
         w5 = Workload("c5slab", args.scale)
         slabs, scaling = c5_slabs_of(world, rank)
