@@ -937,13 +937,21 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
             continue;
         }
         const int64_t base = r * J.cols;
+        const int cols = int(J.cols);  // (rows of this kernel are at most 8192 elements)
         float mn = 0.f, mx = 0.f;
-        for (int64_t i = lane; i < J.cols; i += 32) {
-            const float x = load_as_f32(J.in, in_dt, base + i, nullptr);
-            if (x != x) set_flag(flags, VF_FLAG_NAN);  // undefined in the reference: reported
-            mn = fminf(mn, x);
-            mx = fmaxf(mx, x);
+        bool nan = false;
+        for (int i0 = lane; i0 < cols; i0 += 128) {  // four loads on their way before the first is used
+            float x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) x[k] = i0 + 32 * k < cols ? load_as_f32(J.in, in_dt, base + i0 + 32 * k, nullptr) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                nan |= x[k] != x[k];
+                mn = fminf(mn, x[k]);
+                mx = fmaxf(mx, x[k]);
+            }
         }
+        if (nan) set_flag(flags, VF_FLAG_NAN);  // undefined in the reference: reported
         mn = warp_min(mn);
         mx = warp_max(mx);
         double scale = 0.0;
@@ -975,16 +983,32 @@ __global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ j
             __syncwarp();
         }
         const float cm = __fadd_rn(kMagic, u.zq);
-        for (int64_t i = lane; i < J.cols; i += 32) {
-            const float x = load_as_f32(J.in, in_dt, base + i, nullptr);
-            const float m = __fmaf_rn(x, u.inv, cm);
-            int n = __float_as_int(m) - kMagicBits;
-            const float resid = __fmaf_rn(x, -u.inv, __fsub_rn(m, cm));
-            if (!fast || !(fabsf(resid) <= p.thr)) n = quant_index_exact(x, u.in_low, u.range, p.lm1);
-            n = min(max(n, 0), p.lm1);
-            // input index i = icIdx * khw + s  ->  output index s * ic_pad + icIdx
-            const int64_t ici = i / khw, s = i - ici * khw;
-            stage[s * ic_pad + ici] = uint8_t(n + p.qmin);
+        // input index i = icIdx * khw + s  ->  output index s * ic_pad + icIdx; a lane's i advances by 32, so its
+        // (icIdx, s) advance by (32 / khw, 32 % khw) with a carry instead of being divided out per element
+        const int khw32 = int(khw), icp32 = int(ic_pad);
+        const int dq = 32 / khw32, dr = 32 % khw32;
+        int ici = lane / khw32, sp = lane % khw32;
+        for (int i0 = lane; i0 < cols; i0 += 128) {
+            float xs[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) xs[k] = i0 + 32 * k < cols ? load_as_f32(J.in, in_dt, base + i0 + 32 * k, nullptr) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (i0 + 32 * k >= cols) break;
+                const float x = xs[k];
+                const float m = __fmaf_rn(x, u.inv, cm);
+                int n = __float_as_int(m) - kMagicBits;
+                const float resid = __fmaf_rn(x, -u.inv, __fsub_rn(m, cm));
+                if (!fast || !(fabsf(resid) <= p.thr)) n = quant_index_exact(x, u.in_low, u.range, p.lm1);
+                n = min(max(n, 0), p.lm1);
+                stage[sp * icp32 + ici] = uint8_t(n + p.qmin);
+                ici += dq;
+                sp += dr;
+                if (sp >= khw32) {
+                    sp -= khw32;
+                    ++ici;
+                }
+            }
         }
         __syncwarp();
         if (((reinterpret_cast<uintptr_t>(out) | uintptr_t(out_row_bytes)) & 3) == 0) {
