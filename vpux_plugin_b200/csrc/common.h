@@ -238,6 +238,13 @@ struct vf_ctx {
     cudaStream_t table_stream = nullptr;
     cudaEvent_t table_ev = nullptr;
     bool table_unchecked = false;
+    // Scratch that the batched sparsify and weights-table calls need on every call (offsets and totals; prefix
+    // sums): kept between calls and grown when a call needs more, instead of two pool requests and two releases per
+    // call. Every user is enqueued on the context's main stream, so a call's kernels have finished with a slot
+    // before the next call's kernels write it.
+    enum { kScratchSparsify = 0, kScratchTables = 1, kScratchSlots = 2 };
+    void* call_scratch[kScratchSlots] = {nullptr, nullptr};
+    size_t call_scratch_cap[kScratchSlots] = {0, 0};
     int* d_flags = nullptr;  // device error flags (see VF_FLAG_* in device_utils.cuh)
     int* h_flags = nullptr;  // pinned mirror
     bool flags_dirty = false;  // the device flags may be non-zero (a call found something or ended early)
@@ -346,6 +353,9 @@ void copy_out(vf_ctx* ctx, void* dst, int dst_kind, const void* src_dev, size_t 
 // Copies a job table to the device and returns where it is. Small tables go through the context's table area
 // (one asynchronous copy, nothing allocated); `fallback` owns the memory of a table that does not fit.
 const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallback);
+// At least `bytes` of device scratch from slot `slot` of the context (see vf_ctx::call_scratch); NULL when the
+// context is not on its main stream (the caller then takes a buffer of its own).
+void* call_scratch(vf_ctx* ctx, int slot, size_t bytes);
 void flags_clear(vf_ctx* ctx);
 // synchronises the stream and raises if a kernel recorded an error
 void flags_check(vf_ctx* ctx);

@@ -114,6 +114,18 @@ const void* upload_table(vf_ctx* ctx, const void* src, size_t bytes, DBuf& fallb
     return fallback.p;
 }
 
+void* call_scratch(vf_ctx* ctx, int slot, size_t bytes) {
+    if (bytes <= ctx->call_scratch_cap[slot] && ctx->call_scratch[slot]) return ctx->call_scratch[slot];
+    if (ctx->stream != ctx->main_stream) return nullptr;  // (a lane of a batch: the caller takes a buffer of its own)
+    if (ctx->call_scratch[slot]) cudaFreeAsync(ctx->call_scratch[slot], ctx->main_stream);  // after the kernels that read it
+    ctx->call_scratch[slot] = nullptr;
+    ctx->call_scratch_cap[slot] = 0;
+    const size_t cap = std::max<size_t>(bytes + bytes / 2, size_t(64) << 10);
+    VF_CUDA(cudaMallocFromPoolAsync(&ctx->call_scratch[slot], cap, ctx->pool, ctx->main_stream));
+    ctx->call_scratch_cap[slot] = cap;
+    return ctx->call_scratch[slot];
+}
+
 // The flags are zero unless a call found something or ended early: only then is the next call's clearing real.
 void flags_clear(vf_ctx* ctx) {
     if (ctx->deferred) return;  // unchecked work is in flight: its flags and job tables stay as they are
@@ -231,6 +243,9 @@ void vf_ctx_destroy(vf_ctx* c) {
         if (c->staging[k]) cudaFreeHost(c->staging[k]);
         if (c->staging_ev[k]) cudaEventDestroy(c->staging_ev[k]);
     }
+    for (void* sp : c->call_scratch)
+        if (sp) cudaFreeAsync(sp, c->main_stream);
+    if (c->main_stream) cudaStreamSynchronize(c->main_stream);
     if (c->table_stream) {
         cudaStreamSynchronize(c->table_stream);
         cudaStreamDestroy(c->table_stream);

@@ -1411,19 +1411,24 @@ static bool sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem
     size_t off_elems = 0;
     for (int j = 0; j < n; ++j)
         if (sj[j].data) off_elems += size_t(sj[j].oc + 1);
-    DBuf all_offsets(ctx, off_elems * 8);
-    off_elems = 0;
+    DBuf own_scratch;
+    int64_t* scratch = static_cast<int64_t*>(call_scratch(ctx, vf_ctx::kScratchSparsify, (off_elems + size_t(n)) * 8));
+    if (!scratch) {
+        own_scratch = DBuf(ctx, (off_elems + size_t(n)) * 8);
+        scratch = own_scratch.as<int64_t>();
+    }
+    int64_t* const d_totals = scratch;  // [n], then the offsets
+    off_elems = size_t(n);
     for (int j = 0; j < n; ++j) {
         if (!sj[j].data) continue;
-        sj[j].offsets = all_offsets.as<int64_t>() + off_elems;
+        sj[j].offsets = scratch + off_elems;
         off_elems += size_t(sj[j].oc + 1);
     }
-    DBuf totals(ctx, size_t(n) * 8);
-    launch_sparsify_batch(ctx, sj, totals.as<int64_t>());
+    launch_sparsify_batch(ctx, sj, d_totals);
     bool all_device = out_mem_kind == VF_MEM_DEVICE;
     for (int j = 0; j < n; ++j) all_device &= jobs[j].content.mem_kind == VF_MEM_DEVICE;
     if (may_defer && all_device && (ctx->opt_flags & VF_OPT_ASYNC) && ctx->sizes_host && ctx->sizes_used + size_t(n) <= vf_ctx::kSizesCap) {
-        VF_CUDA(cudaMemcpyAsync(ctx->sizes_host + ctx->sizes_used, totals.p, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        VF_CUDA(cudaMemcpyAsync(ctx->sizes_host + ctx->sizes_used, d_totals, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
         ctx->pending_sizes.push_back(vf_ctx::PendingSizes{jobs, n, ctx->sizes_used});
         ctx->sizes_used += size_t(n);
         if (stats)
@@ -1431,7 +1436,7 @@ static bool sparsify_many(vf_ctx* ctx, vf_sparsify_job* jobs, int n, int out_mem
         return true;
     }
     std::vector<int64_t> total_host(static_cast<size_t>(n), 0);
-    VF_CUDA(cudaMemcpyAsync(total_host.data(), totals.p, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    VF_CUDA(cudaMemcpyAsync(total_host.data(), d_totals, size_t(n) * 8, cudaMemcpyDeviceToHost, ctx->stream));
     VF_CUDA(cudaStreamSynchronize(ctx->stream));
     for (int j = 0; j < n; ++j) {
         vf_sparsify_job& jb = jobs[j];
@@ -1594,8 +1599,12 @@ int vf_weights_table_batch(vf_ctx* ctx, vf_weights_table_job* jobs, int njobs, i
         size_t sum_entries = 0;  // one allocation for the prefix sums of all sparse tables
         for (int j = 0; j < njobs; ++j)
             if (jobs[j].desc.nnz_counts && jobs[j].desc.oc > 0) sum_entries += size_t(jobs[j].desc.oc) + 1;
-        DBuf sums(ctx, sum_entries * 8);
-        int64_t* arena = sums.as<int64_t>();
+        DBuf own_sums;
+        int64_t* arena = sum_entries ? static_cast<int64_t*>(call_scratch(ctx, vf_ctx::kScratchTables, sum_entries * 8)) : nullptr;
+        if (sum_entries && !arena) {
+            own_sums = DBuf(ctx, sum_entries * 8);
+            arena = own_sums.as<int64_t>();
+        }
         for (int j = 0; j < njobs; ++j) {
             vf_weights_table_job& jb = jobs[j];
             jb.status = VF_OK;

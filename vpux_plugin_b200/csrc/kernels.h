@@ -87,6 +87,8 @@ struct OffsetsJob {
     int64_t* offsets;       // [oc + 1]
 };
 void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs);
+// The same for a job list that is in device memory already.
+void launch_offsets_batch_at(vf_ctx* ctx, const OffsetsJob* d_jobs, int njobs);
 
 // Makes the runtime load the kernels of the three launchers above (cudaFuncGetAttributes, nothing is launched):
 // module loading may allocate device memory, which vf_sparsify_noalloc must not do once the embedder owns the GPU.

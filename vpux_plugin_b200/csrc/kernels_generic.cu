@@ -2260,10 +2260,16 @@ void launch_weights_table_batch(vf_ctx* ctx, std::vector<TableArgs>& tabs, const
         t.unit_begin = total;
         total += t.oc;
     }
+    // the two job lists travel as one upload, and nothing stands between the two kernels
+    const size_t n_off = offsets_first ? offsets_first->size() : 0;
+    const size_t off_bytes = (n_off * sizeof(OffsetsJob) + 15) & ~size_t(15), tab_bytes = tabs.size() * sizeof(TableArgs);
+    std::vector<char> both(off_bytes + tab_bytes);
+    if (n_off) std::memcpy(both.data(), offsets_first->data(), n_off * sizeof(OffsetsJob));
+    std::memcpy(both.data() + off_bytes, tabs.data(), tab_bytes);
     DBuf d;
-    const TableArgs* d_tabs = static_cast<const TableArgs*>(upload_table(ctx, tabs.data(), tabs.size() * sizeof(TableArgs), d));
-    // both job tables are on their way before the first of the two kernels, so that nothing stands between them
-    if (offsets_first) launch_offsets_batch(ctx, *offsets_first);
+    const char* d_both = static_cast<const char*>(upload_table(ctx, both.data(), both.size(), d));
+    launch_offsets_batch_at(ctx, reinterpret_cast<const OffsetsJob*>(d_both), int(n_off));
+    const TableArgs* d_tabs = reinterpret_cast<const TableArgs*>(d_both + off_bytes);
     VF_CUDA(launch_chained(k_weights_table_batch, int((total + 127) / 128), 128, 0, ctx->stream, d_tabs, int(tabs.size()), total, ctx->d_flags));
     ctx->launches += 1;
 }

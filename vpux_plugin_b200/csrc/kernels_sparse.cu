@@ -371,7 +371,12 @@ void launch_offsets_batch(vf_ctx* ctx, const std::vector<OffsetsJob>& jobs) {
     if (jobs.empty()) return;
     DBuf d;
     const OffsetsJob* d_jobs = static_cast<const OffsetsJob*>(upload_table(ctx, jobs.data(), jobs.size() * sizeof(OffsetsJob), d));
-    VF_CUDA(launch_chained(k_offsets_batch, int(jobs.size()), 1024, 0, ctx->stream, d_jobs));
+    launch_offsets_batch_at(ctx, d_jobs, int(jobs.size()));
+}
+
+void launch_offsets_batch_at(vf_ctx* ctx, const OffsetsJob* d_jobs, int njobs) {
+    if (njobs <= 0) return;
+    VF_CUDA(launch_chained(k_offsets_batch, njobs, 1024, 0, ctx->stream, d_jobs));
     ctx->launches += 1;
 }
 
