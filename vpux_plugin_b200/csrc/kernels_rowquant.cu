@@ -916,8 +916,10 @@ __global__ void __launch_bounds__(256, 3) k_row(const RowQuantArgs* __restrict__
 // shared memory at its OYXI position (ic padded to ic_pad) and written out with coalesced 32-bit stores; rows
 // beyond `rows` (channel padding) are zero. Two sweeps over the row: the second one hits L1/L2.
 // ======================================================================================================
-__global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int in_dt,
+template <int IN_DT>  // the input type as a constant (the element load then has no type switch), 0: `in_dt_arg`
+__global__ void __launch_bounds__(256) k_conv(const RowQuantArgs* __restrict__ jobs, LaunchParams p, int in_dt_arg,
                                               int stage_bytes, int* flags) {
+    const int in_dt = IN_DT ? IN_DT : in_dt_arg;
     extern __shared__ uint4 smem_u4[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint8_t* stage = reinterpret_cast<uint8_t*>(smem_u4) + size_t(wid) * size_t(stage_bytes);
@@ -1497,9 +1499,16 @@ void launch_rowquant_batch(vf_ctx* ctx, int kind, std::vector<RowQuantArgs>& job
     } else if (kind == 3) {
         const int stage_bytes = int((max_out_row + 15) & ~int64_t(15));
         const size_t smem = size_t(stage_bytes) * 8;
-        set_smem(k_conv, std::max<size_t>(smem, 16));
         const int64_t blocks = (units + 7) / 8;
-        k_conv<<<int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * 8)), 256, smem, ctx->stream>>>(d_jobs, p, a0.in_dt, stage_bytes, ctx->d_flags);
+        const int grid = int(std::min<int64_t>(blocks, int64_t(ctx->sm_count) * 8));
+        auto go = [&](auto kernel) {
+            set_smem(kernel, std::max<size_t>(smem, 16));
+            kernel<<<grid, 256, smem, ctx->stream>>>(d_jobs, p, a0.in_dt, stage_bytes, ctx->d_flags);
+        };
+        if (a0.in_dt == VF_DT_F32) go(k_conv<VF_DT_F32>);
+        else if (a0.in_dt == VF_DT_F16) go(k_conv<VF_DT_F16>);
+        else if (a0.in_dt == VF_DT_BF16) go(k_conv<VF_DT_BF16>);
+        else go(k_conv<0>);
         post_launch(ctx);
     } else {
         raise(VF_ERR_UNSUPPORTED, "no fused kernel for this weight quantization pattern");
