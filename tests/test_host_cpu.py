@@ -223,3 +223,26 @@ def test_max_intermediate_size_follows_the_pass():
     tr, n = s.transforms()
     assert lib.max_intermediate_size(t, False, tr, n) == 64 * 27 * 2
     assert lib.raw().vf_status_string(abi.VF_ERR_NOT_RUN) == b"job not run"
+
+
+@pytest.mark.parametrize("bad", [0.0, -0.0, -1e-3, float("inf"), float("-inf"), float("nan")])
+@pytest.mark.parametrize("where", [0, 1, 2047, 4095, 4096, 4999])
+def test_a_quantized_type_with_an_illegal_scale_is_refused_wherever_it_sits(bad, where):
+    """mlir::quant::UniformQuantizedPerAxisType::verify rejects scale <= 0, infinities and NaN ("illegal scale");
+    the library's check runs over the whole array at once, so the position must not matter. Subnormal and
+    very large finite scales are legal."""
+    from vpux_plugin_b200 import lib
+    n = 5000
+    scales = np.linspace(1e-3, 2e-3, n)
+    scales[7], scales[8] = 5e-324, 1.7e308  # legal extremes
+    t = TType([n, 8], abi.VF_DT_F32)
+    q = Elem.per_axis(abi.VF_DT_I8, abi.VF_DT_F16, scales, np.zeros(n, np.int64), 0, -127, 127)
+    tr, k = ContentSetup(t).quantize(q).transforms()
+    out, _, nbytes = lib.infer_type(t, False, tr, k)
+    assert nbytes == n * 8
+    scales[where] = bad
+    q = Elem.per_axis(abi.VF_DT_I8, abi.VF_DT_F16, scales, np.zeros(n, np.int64), 0, -127, 127)
+    tr, k = ContentSetup(t).quantize(q).transforms()
+    with pytest.raises(lib.VfoldError) as e:
+        lib.infer_type(t, False, tr, k)
+    assert e.value.status == abi.VF_ERR_INVALID_ARG and "illegal scale" in str(e.value)
