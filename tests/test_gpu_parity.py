@@ -997,6 +997,41 @@ def test_pipelined_steps_run_through_the_job_table_area_many_times(gpu, oracle):
     lib.close()
 
 
+def test_batches_of_seventy_small_tensors(gpu, oracle):
+    """Seventy tensors of 1-39 channels per call: Sparsify + GetSparsityMap + counts, then weights tables with sparse
+    pointers from those counts (more jobs than any network-shaped case of this suite, most of them a few rows)."""
+    rng = np.random.default_rng(70)
+    n_t = 70
+    sjobs, tjobs = (abi.SparsifyJob * n_t)(), (abi.WeightsTableJob * n_t)()
+    keep, expect, bufs, tabs, texp = [], [], [], [], []
+    for j in range(n_t):
+        oc, ic, k = int(rng.integers(1, 40)), 16 * int(rng.integers(1, 5)), int(rng.choice([1, 3]))
+        shape = [oc, ic, k, k]
+        n, work = int(np.prod(shape)), ic * k * k
+        x = (rng.integers(1, 100, n) * (rng.random(n) < 0.5)).astype(np.int8)
+        c, kc = abi.make_content(TType(shape, I8), x)
+        row, cap = (work + 127) // 128 * 16, n + 16 * oc
+        od, om, ocnt = np.zeros(cap, np.uint8), np.zeros(oc * row, np.uint8), np.zeros(oc, np.int64)
+        w = oracle.sparsify(c, od, om, ocnt)
+        gd, gm, gc = np.full(cap, 0xAB, np.uint8), np.full(oc * row, 0xAB, np.uint8), np.full(oc, -1, np.int64)
+        sjobs[j].content, sjobs[j].data, sjobs[j].data_bytes = c, gd.ctypes.data, cap
+        sjobs[j].map, sjobs[j].map_bytes, sjobs[j].counts = gm.ctypes.data, gm.nbytes, gc.ctypes.data
+        expect.append((w, od, om, ocnt))
+        bufs.append((gd, gm, gc))
+        d, kd = wl.weights_table_desc(oc, rng.uniform(1e-4, 5e-2, oc), 0, None, sparse_counts=ocnt, sparsity_step=row)
+        texp.append(oracle.weights_table(d, oc))
+        tab = np.full(oc * 4, -1, np.int32)
+        tjobs[j].desc, tjobs[j].table = d, tab.ctypes.data
+        tabs.append(tab)
+        keep += [c, kc, x, kd]
+    gpu.sparsify_batch(sjobs)
+    for j, ((w, od, om, ocnt), (gd, gm, gc)) in enumerate(zip(expect, bufs)):
+        assert sjobs[j].data_written == w and np.array_equal(gd[:w], od[:w]) and np.array_equal(gm, om) and np.array_equal(gc, ocnt), j
+    gpu.weights_table_batch(tjobs)
+    for j, (tab, ref) in enumerate(zip(tabs, texp)):
+        assert np.array_equal(tab, ref), j
+
+
 def test_weights_table_batch(gpu, oracle):
     """Many tables per call (dense and sparse pointers, with and without bias, 1..2500 channels); weight scales
     either inside the descriptor or as a separate FP64 array; one launch for all rows."""
